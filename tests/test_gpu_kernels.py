@@ -1,0 +1,138 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 restatements."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda")
+
+
+def _status_ok(dev):
+    from vllm_omni_b200.ops import _native as nv
+    torch.cuda.synchronize()
+    assert int(nv.status_word(dev).item()) == 0
+
+
+@pytest.mark.parametrize("bn", [0, 256, 192, 128])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 264, 136), (1024, 3072, 1024)])
+def test_gemm_plain(dev, M, N, K, bn):
+    from vllm_omni_b200.ops import gemm
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05
+    y = gemm.linear(x, w, force_bn=bn).float()
+    ref = x.float() @ w.float().t()
+    _status_ok(dev)
+    assert (y - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("act", [None, "gelu_tanh", "silu"])
+def test_gemm_epilogue(dev, act):
+    from vllm_omni_b200.ops import gemm
+    torch.manual_seed(1)
+    B, S, K, N = 2, 520, 512, 768
+    x = torch.randn(B, S, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+    res = torch.randn(B, S, N, device=dev, dtype=torch.bfloat16)
+    mod = torch.randn(B, 3 * N, device=dev, dtype=torch.bfloat16)
+    gate = mod[:, N:2 * N]
+    y = gemm.linear(x, w, bias, act, res, gate).float()
+    ref = gemm.linear_reference(x, w, bias, act, res, gate).float()
+    _status_ok(dev)
+    assert (y - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-2
+
+
+def test_gemm_batched_output_rows(dev):
+    from vllm_omni_b200.ops import gemm
+    torch.manual_seed(2)
+    B, S1, S2, K, N = 2, 200, 56, 256, 384
+    x = torch.randn(B, S1, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05
+    joint = torch.zeros(B, S1 + S2, N, device=dev, dtype=torch.bfloat16)
+    gemm.linear(x, w, out=joint[:, :S1], out_rows_per_batch=S1, out_batch_stride=(S1 + S2) * N)
+    ref = (x.float() @ w.float().t())
+    _status_ok(dev)
+    assert (joint[:, :S1].float() - ref).abs().max().item() < 0.05
+    assert joint[:, S1:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,kvl", [(1, 128, 1, 1, None), (1, 384, 2, 1, None), (2, 600, 4, 4, [600, 333]),
+                                           (1, 2100, 3, 3, None)])
+def test_attention(dev, B, S, H, Hkv, kvl):
+    from vllm_omni_b200.ops import attention as A
+    torch.manual_seed(3)
+    qkv = torch.randn(B, S, H + 2 * Hkv, 128, device=dev, dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+    kl = torch.tensor(kvl, dtype=torch.int32, device=dev) if kvl else None
+    o, lse = A.attention(q, k, v, kv_lens=kl, return_lse=True)
+    ref, rl = A.attention_reference(q, k, v, kv_lens=kl, return_lse=True)
+    _status_ok(dev)
+    assert (o.float() - ref.float()).abs().max().item() < 0.02
+    assert (lse - rl).abs().max().item() < 1e-3
+
+
+def test_attention_split_outputs(dev):
+    from vllm_omni_b200.ops import attention as A
+    torch.manual_seed(4)
+    B, S, H, split = 2, 300, 2, 260
+    q, k, v = (torch.randn(B, S, H, 128, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    o1 = torch.empty(B, split, H, 128, device=dev, dtype=torch.bfloat16)
+    o2 = torch.empty(B, S - split, H, 128, device=dev, dtype=torch.bfloat16)
+    A.attention(q, k, v, out=o1, out2=o2, split=split)
+    ref = A.attention_reference(q, k, v)
+    _status_ok(dev)
+    assert (o1.float() - ref[:, :split].float()).abs().max().item() < 0.02
+    assert (o2.float() - ref[:, split:].float()).abs().max().item() < 0.02
+
+
+def test_norm_modulate(dev):
+    from vllm_omni_b200.ops import fused
+    torch.manual_seed(5)
+    B, S, D = 2, 333, 3072
+    x = torch.randn(B, S, D, device=dev, dtype=torch.bfloat16)
+    mod = torch.randn(B, 6 * D, device=dev, dtype=torch.bfloat16) * 0.3
+    y = fused.norm_modulate(x, shift=mod[:, :D], scale=mod[:, D:2 * D])
+    ref = fused.norm_modulate_reference(x, shift=mod[:, :D], scale=mod[:, D:2 * D])
+    assert (y.float() - ref.float()).abs().max().item() < 0.05
+    w = torch.randn(D, device=dev, dtype=torch.bfloat16)
+    y = fused.norm_modulate(x, weight=w, rms=True)
+    ref = fused.norm_modulate_reference(x, weight=w, rms=True)
+    assert (y.float() - ref.float()).abs().max().item() < 0.05
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_qk_norm_rope(dev, interleaved):
+    from vllm_omni_b200.ops import fused
+    torch.manual_seed(6)
+    B, S, H, Dh, s_alt = 2, 300, 6, 128, 263
+    qkv = torch.randn(B, S, 3 * H * Dh, device=dev, dtype=torch.bfloat16)
+    ws = [torch.randn(Dh, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+    ang = torch.randn(S, Dh // 2, device=dev)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    ref = fused.qk_norm_rope_reference(qkv.clone(), H, H, Dh, *ws, s_alt, cos, sin, interleaved, 1e-6)
+    out = fused.qk_norm_rope_(qkv.clone(), H, H, Dh, *ws, s_alt=s_alt, cos=cos, sin=sin, interleaved=interleaved)
+    assert (out.float() - ref.float()).abs().max().item() < 0.05
+
+
+def test_cfg_euler_and_rel_l1(dev):
+    from vllm_omni_b200.ops import fused
+    torch.manual_seed(7)
+    pos = torch.randn(2, 4096, 64, device=dev, dtype=torch.bfloat16)
+    neg = torch.randn_like(pos)
+    lat = torch.randn(2, 4096, 64, device=dev)
+    ref = fused.cfg_euler_step_reference(pos, neg, lat.clone(), 4.0, -0.02, True)
+    lb = torch.empty_like(pos)
+    out = fused.cfg_euler_step_(pos, neg, lat.clone(), 4.0, -0.02, True, lb)
+    assert (out - ref).abs().max().item() < 1e-4
+    assert (lb.float() - ref).abs().max().item() < 0.03
+    a = torch.randn(2, 1000, 3072, device=dev, dtype=torch.bfloat16)
+    b = a + 0.1 * torch.randn_like(a)
+    st = fused.RelL1State(dev, [2.0, 0.5], 10.0)
+    fused.rel_l1_update(a, b, st)
+    rel = float(fused.rel_l1_reference(a, b))
+    got = st.state.tolist()
+    assert abs(got[1] - rel) < 1e-3 * rel and abs(got[0] - (2.0 * rel + 0.5)) < 1e-3 and got[2] == 1.0

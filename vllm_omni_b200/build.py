@@ -1,0 +1,65 @@
+"""In-tree build of the sm_100a CUDA libraries.
+
+Every ``csrc/*.cu`` becomes ``_lib/libomni_<name>.so`` with a plain C ABI that
+``vllm_omni_b200.ops`` loads through ctypes.  nvcc cross-compiles without a GPU, so the
+build runs on CPU-only machines; the resulting libraries are only loaded where a GPU is
+present.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB = PKG / "_lib"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-pthread"]
+
+
+def lib_path(name: str) -> Path:
+    return LIB / f"libomni_{name}.so"
+
+
+def _newest_header_mtime() -> float:
+    hs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    return max((h.stat().st_mtime for h in hs), default=0.0)
+
+
+def _compile(src: Path, force: bool) -> str:
+    out = lib_path(src.stem)
+    dep_m = max(src.stat().st_mtime, _newest_header_mtime())
+    if not force and out.exists() and out.stat().st_mtime >= dep_m:
+        return f"up-to-date {out.name}"
+    if src.suffix == ".cu":
+        nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(out), str(src)]
+    else:
+        cmd = [os.environ.get("CXX", "g++"), *CXX_FLAGS, "-I", str(CSRC), "-o", str(out), str(src), "-lrt"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"build failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    return f"built {out.name}"
+
+
+def build_all(force: bool = False, verbose: bool = True) -> list[str]:
+    LIB.mkdir(exist_ok=True)
+    srcs = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp"))
+    with ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
+        msgs = list(ex.map(lambda s: _compile(s, force), srcs))
+    if verbose:
+        for m in msgs:
+            print("[build]", m)
+    return msgs
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv)

@@ -1,0 +1,357 @@
+// K4: flash-attention forward for sm_100a on tcgen05 tensor cores with TMEM accumulators.
+//
+// Non-causal softmax(Q K^T * scale) V over bf16 inputs, head_dim 128, optional per-batch
+// key lengths (padding mask), GQA, optional log-sum-exp output (used by the ring /
+// peer-KV merge).  Replaces the PyTorch SDPA call the reference makes on Blackwell
+// (vllm_omni/diffusion/attention/backends/sdpa.py:82; its FlashAttention backend is gated
+// off for compute capability >= 10, vllm_omni/platforms/cuda/platform.py:44-51).
+//
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles.
+//   warp 0       TMA producer: Q once, then K and V tiles through two 2-deep rings
+//   warp 1       MMA issuer (one elected thread):
+//                  S_t = Q_t K_j^T      (SS form, both operands K-major in shared memory)
+//                  O_t += P_t V_j       (TS form: P_t read from TMEM, V_j MN-major in smem)
+//   warps 4-7    softmax of tile 0,  warps 8-11 softmax of tile 1: one row per thread;
+//                tcgen05.ld of S, running max, exp2, bf16 P written back with tcgen05.st
+//                over the S columns it came from, then the final O / l epilogue
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases the
+// first 64 columns of S_t.  O is rescaled lazily: only when a row maximum grows by more
+// than 2^8, so the steady state never touches O outside the MMAs.
+// The MMA stream is software-pipelined (PV_t(j) is followed at once by S_t(j+1)) so that
+// the tensor pipe works on one tile while the other tile's softmax runs.
+#include "host_util.h"
+#include "ptx_sm100.cuh"
+
+namespace omni {
+
+constexpr int ATT_D = 128;
+constexpr int ATT_BM = 128;   // rows per query tile
+constexpr int ATT_BN = 128;   // keys per KV tile
+constexpr int ATT_THREADS = 384;
+constexpr int ATT_TILE_BYTES = ATT_BM * ATT_D * 2;  // 32 KiB
+constexpr int ATT_HALF_BYTES = ATT_TILE_BYTES / 2;  // one 64-wide TMA box
+constexpr int ATT_SMEM = 2 * ATT_TILE_BYTES /*Q*/ + 2 * ATT_TILE_BYTES /*K*/ + 2 * ATT_TILE_BYTES /*V*/ + 1024;
+
+struct AttnOut {
+  __nv_bfloat16* o;   // rows [0, split) of every batch
+  __nv_bfloat16* o2;  // rows [split, Sq) (row index s - split); nullptr -> everything in o
+  long o_bs, o_rs, o_hs;     // element strides: batch, row, head
+  long o2_bs, o2_rs, o2_hs;
+  int split;
+  float* lse;  // [B, H, Sq] or nullptr
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, AttnOut out, int Sq, int Skv, int H, int Hkv,
+                const int* __restrict__ kv_lens, float scale_log2, int v_desc_mode, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
+  __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (H / Hkv);
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = smem_base;                         // 2 tiles
+  const uint32_t sK = smem_base + 2 * ATT_TILE_BYTES;    // 2 stages
+  const uint32_t sV = smem_base + 4 * ATT_TILE_BYTES;    // 2 stages
+  const int kv_len = kv_lens ? min(kv_lens[b], Skv) : Skv;
+  const int n_kv = (kv_len + ATT_BN - 1) / ATT_BN;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(smem_u32(&q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&k_full[i]), 1);
+      mbar_init(smem_u32(&k_empty[i]), 1);
+      mbar_init(smem_u32(&v_full[i]), 1);
+      mbar_init(smem_u32(&v_empty[i]), 1);
+      mbar_init(smem_u32(&s_full[i]), 1);
+      mbar_init(smem_u32(&p_full[i]), 128);
+      mbar_init(smem_u32(&o_done[i]), 1);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one() && n_kv > 0) {
+      const uint32_t qb = smem_u32(&q_full);
+      mbar_expect_tx(qb, 2 * ATT_TILE_BYTES);
+      for (int t = 0; t < 2; ++t) {
+        const int s0 = qblk * 2 * ATT_BM + t * ATT_BM;
+        tma_load_4d(sQ + t * ATT_TILE_BYTES, &tmQ, qb, 0, s0, h, b);
+        tma_load_4d(sQ + t * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmQ, qb, 64, s0, h, b);
+      }
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        mbar_wait(smem_u32(&k_empty[st]), ph ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
+        const uint32_t kb = smem_u32(&k_full[st]);
+        mbar_expect_tx(kb, ATT_TILE_BYTES);
+        tma_load_4d(sK + st * ATT_TILE_BYTES, &tmK, kb, 0, j * ATT_BN, hkv, b);
+        tma_load_4d(sK + st * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmK, kb, 64, j * ATT_BN, hkv, b);
+        mbar_wait(smem_u32(&v_empty[st]), ph ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
+        const uint32_t vb = smem_u32(&v_full[st]);
+        mbar_expect_tx(vb, ATT_TILE_BYTES);
+        tma_load_4d(sV + st * ATT_TILE_BYTES, &tmV, vb, 0, j * ATT_BN, hkv, b);
+        tma_load_4d(sV + st * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmV, vb, 64, j * ATT_BN, hkv, b);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (elect_one() && n_kv > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(ATT_BM, ATT_BN, 1, 1, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc(ATT_BM, ATT_D, 1, 1, 0, 1);  // V is MN-major
+      auto issue_s = [&](int t, int st) {
+        const uint32_t d = tmem_base + t * 128;
+#pragma unroll
+        for (int k = 0; k < ATT_D / 16; ++k) {
+          const uint32_t off = (k >> 2) * ATT_HALF_BYTES + (k & 3) * 32;
+          const uint64_t a = umma_desc_kmajor_sw128(sQ + t * ATT_TILE_BYTES + off);
+          const uint64_t bd = umma_desc_kmajor_sw128(sK + st * ATT_TILE_BYTES + off);
+          mma_f16_ss(d, a, bd, idesc_qk, k != 0);
+        }
+      };
+      auto issue_pv = [&](int t, int st, int j) {
+        const uint32_t d = tmem_base + 256 + t * 128;
+        const uint32_t p = tmem_base + t * 128;
+#pragma unroll
+        for (int k = 0; k < ATT_BN / 16; ++k) {
+          // 16 keys = two 8-row groups of 1024 B; the two 64-wide halves of D are
+          // ATT_HALF_BYTES apart
+          const uint32_t addr = sV + st * ATT_TILE_BYTES + k * 2048;
+          const uint64_t bd = v_desc_mode == 0 ? umma_desc_sw128(addr, ATT_HALF_BYTES, 1024)
+                                               : umma_desc_sw128(addr, 1024, ATT_HALF_BYTES);
+          mma_f16_ts(d, p + k * 8, bd, idesc_pv, (j | k) != 0);
+        }
+      };
+      mbar_wait(smem_u32(&q_full), 0, &s_abort, status, ERR_WAIT_FULL);
+      mbar_wait(smem_u32(&k_full[0]), 0, &s_abort, status, ERR_WAIT_FULL);
+      tc_fence_after_sync();
+      for (int t = 0; t < 2; ++t) {
+        issue_s(t, 0);
+        tc_commit(smem_u32(&s_full[t]));
+      }
+      tc_commit(smem_u32(&k_empty[0]));
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const bool more = j + 1 < n_kv;
+        const int st1 = (j + 1) & 1;
+        mbar_wait(smem_u32(&v_full[st]), ph, &s_abort, status, ERR_WAIT_FULL);
+        if (more) mbar_wait(smem_u32(&k_full[st1]), ((j + 1) >> 1) & 1, &s_abort, status, ERR_WAIT_FULL);
+        for (int t = 0; t < 2; ++t) {
+          mbar_wait(smem_u32(&p_full[t]), j & 1, &s_abort, status, ERR_WAIT_SOFTMAX);
+          tc_fence_after_sync();
+          issue_pv(t, st, j);
+          if (more) {
+            issue_s(t, st1);
+            tc_commit(smem_u32(&s_full[t]));
+          } else {
+            tc_commit(smem_u32(&o_done[t]));
+          }
+        }
+        tc_commit(smem_u32(&v_empty[st]));
+        if (more) tc_commit(smem_u32(&k_empty[st1]));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------- softmax + epilogue
+    const int t = (warp - 4) >> 2;       // query tile of this warpgroup
+    const int q = warp & 3;              // TMEM lane quadrant
+    const int row_in_tile = q * 32 + lane;
+    const int srow = qblk * 2 * ATT_BM + t * ATT_BM + row_in_tile;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t tS = tmem_base + lane_addr + t * 128;
+    const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
+    float m = -INFINITY;  // running maximum in log2 units that P and l are relative to
+    float l = 0.f;
+    for (int j = 0; j < n_kv; ++j) {
+      mbar_wait(smem_u32(&s_full[t]), j & 1, &s_abort, status, ERR_WAIT_FULL);
+      tc_fence_after_sync();
+      const int valid = kv_len - j * ATT_BN;  // keys of this tile that exist
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + c * 32, v);
+        tmem_wait_ld();
+        if (valid >= ATT_BN) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c * 32 + e < valid) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      mx *= scale_log2;
+      const float m_new = fmaxf(m, mx);
+      // lazy rescale, decided per warp because tcgen05.ld/st are warp-wide
+      const bool grow = m_new > m + 8.0f;
+      if (j == 0) {
+        m = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = ex2(m - m_new);
+        l *= alpha;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tO + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+          tmem_st_32x32(tO + c * 32, v);
+        }
+        tmem_wait_st();
+        m = m_new;
+      }
+      // pass 2: P = exp2(S * scale - m), written as packed bf16 over the S columns
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + c * 32, v);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = ex2(fmaf(__uint_as_float(v[e]), scale_log2, -m));
+          float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), scale_log2, -m));
+          if (valid < ATT_BN) {
+            if (c * 32 + e >= valid) p0 = 0.f;
+            if (c * 32 + e + 1 >= valid) p1 = 0.f;
+          }
+          l += p0 + p1;
+          pk[e >> 1] = pack_bf16(p0, p1);
+        }
+        tmem_st_32x16(tS + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&p_full[t]));
+    }
+    // epilogue: O / l -> bf16
+    if (n_kv > 0) {
+      mbar_wait(smem_u32(&o_done[t]), 0, &s_abort, status, ERR_WAIT_PV);
+      tc_fence_after_sync();
+    }
+    const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+    __nv_bfloat16* orow = nullptr;
+    if (srow < Sq) {
+      if (out.o2 && srow >= out.split)
+        orow = out.o2 + (long)b * out.o2_bs + (long)(srow - out.split) * out.o2_rs + (long)h * out.o2_hs;
+      else
+        orow = out.o + (long)b * out.o_bs + (long)srow * out.o_rs + (long)h * out.o_hs;
+      if (out.lse) out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32];
+      if (n_kv > 0) {
+        tmem_ld_32x32(tO + c * 32, v);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = 0u;
+      }
+      if (orow) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 o;
+          o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+          o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+          o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+          o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (s_abort) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+static int make_qkv_tmap(CUtensorMap* tm, const void* p, int S, int Hn, int B, long rs, long hs, long bs) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return RC_NO_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(p) & 15) || (rs & 7) || (hs & 7) || (bs & 7)) return RC_BAD_ARG;
+  cuuint64_t gdim[4] = {(cuuint64_t)ATT_D, (cuuint64_t)S, (cuuint64_t)Hn, (cuuint64_t)B};
+  cuuint64_t gstr[3] = {(cuuint64_t)rs * 2, (cuuint64_t)hs * 2, (cuuint64_t)bs * 2};
+  cuuint32_t box[4] = {64, ATT_BM, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(p), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RC_OK : RC_TMAP;
+}
+
+}  // namespace omni
+
+// Strides are in elements: *_rs between consecutive sequence positions, *_hs between heads,
+// *_bs between batches; head_dim (128) is contiguous.  o2/split route query rows >= split
+// of every batch to a second tensor (used to hand text and image rows to their own
+// projections).  kv_lens: optional int32[B] valid key counts.  lse: optional fp32 [B,H,Sq].
+extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, const void* k, long k_rs,
+                             long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
+                             void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
+                             long o2_bs, int split, float* lse, int B, int H, int Hkv, int Sq, int Skv,
+                             int D, const int* kv_lens, float scale, int v_desc_mode, int* status,
+                             void* stream) {
+  using namespace omni;
+  if (D != ATT_D || H <= 0 || Hkv <= 0 || (H % Hkv) || B <= 0) return RC_BAD_ARG;
+  if (Sq <= 0) return RC_OK;
+  if ((o_rs & 7) || (o_hs & 7) || (o_bs & 7) || (o2_rs & 7) || (o2_hs & 7) || (o2_bs & 7)) return RC_BAD_ARG;
+  CUtensorMap tq, tk, tv;
+  int rc = make_qkv_tmap(&tq, q, Sq, H, B, q_rs, q_hs, q_bs);
+  if (rc) return rc;
+  rc = make_qkv_tmap(&tk, k, Skv, Hkv, B, k_rs, k_hs, k_bs);
+  if (rc) return rc;
+  rc = make_qkv_tmap(&tv, v, Skv, Hkv, B, v_rs, v_hs, v_bs);
+  if (rc) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  AttnOut out;
+  out.o = (__nv_bfloat16*)o; out.o2 = (__nv_bfloat16*)o2;
+  out.o_bs = o_bs; out.o_rs = o_rs; out.o_hs = o_hs;
+  out.o2_bs = o2_bs; out.o2_rs = o2_rs; out.o2_hs = o2_hs;
+  out.split = split; out.lse = lse;
+  dim3 grid((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), H, B);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens,
+                                                                         scale_log2, v_desc_mode, status);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,339 @@
+// K1: persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   C[M,N] (bf16) = epilogue( A[M,K] (bf16, row-major) * W[N,K]^T (bf16, row-major) )
+//
+// i.e. the nn.Linear contraction with both operands K-major.  One CTA per SM walks a
+// strided list of 128 x BN output tiles.  Roles:
+//   warp 0    TMA producer: cp.async.bulk.tensor loads of the A / W k-blocks (128-byte
+//             swizzle) into a STAGES-deep shared-memory ring, completion on mbarriers
+//   warp 1    MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) with
+//             the fp32 accumulator in tensor memory; tcgen05.commit hands ring slots back
+//             to the producer and finished accumulators to the epilogue
+//   warps 2-5 epilogue: tcgen05.ld of the accumulator (one row per thread, 32 columns per
+//             instruction), fused bias / GELU-tanh / SiLU / gate*x + residual, bf16 stores
+// Two accumulators live in TMEM so the epilogue of tile i overlaps the main loop of
+// tile i+1.  All mbarrier waits are bounded (see ptx_sm100.cuh); a timeout is reported
+// through *status and the kernel still terminates and frees its TMEM.
+//
+// Replaces the cuBLAS calls behind the reference's vLLM linear layers
+// (vllm_omni/diffusion/models/qwen_image/qwen_image_transformer.py:427-560).
+#include "host_util.h"
+#include "ptx_sm100.cuh"
+
+namespace omni {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+
+enum Act : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2 };
+
+struct GemmEpilogue {
+  const __nv_bfloat16* bias;      // [N] or nullptr
+  const __nv_bfloat16* residual;  // [M, ldr] or nullptr (may alias C)
+  const __nv_bfloat16* gate;      // row (r / rows_per_batch) of a [B, gate_stride] matrix, or nullptr
+  int ldr;
+  int gate_stride;
+  int rows_per_batch;
+  int act;
+  // output row r lands at C + (r / c_rows_per_batch) * c_batch_stride + (r % c_rows_per_batch) * ldc,
+  // which lets two GEMMs write the text and image rows of one joint [B, S_txt + S_img, N] buffer
+  int c_rows_per_batch;  // 0 = plain row-major output
+  long c_batch_stride;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+  static constexpr int ACC_STRIDE = (BN > 128) ? 256 : 128;
+  static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
+  // groups of 8 row-blocks sweep the column blocks together so that the CTAs that run
+  // at the same time share A and W tiles in L2
+  constexpr int GROUP_M = 8;
+  const int group_size = GROUP_M * num_n;
+  const int g = t / group_size;
+  const int first_m = g * GROUP_M;
+  const int gm = min(GROUP_M, num_m - first_m);
+  const int in_g = t - g * group_size;
+  mb = first_m + in_g % gm;
+  nb = in_g / gm;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 __nv_bfloat16* __restrict__ C, int ldc, int M, int N, int K, GemmEpilogue epi,
+                 int* status) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 1);
+      mbar_init(smem_u32(&empty_bar[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tempty_bar[i]), 4);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, num_m, num_n, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+          tma_load_2d(sa, &tmA, fb, kb * BK, mb * BM);
+          tma_load_2d(sa + Cfg::A_BYTES, &tmB, fb, kb * BK, nb * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, &s_abort, status, ERR_WAIT_TMEM_EMPTY);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(smem_u32(&full_bar[stage]), phase, &s_abort, status, ERR_WAIT_FULL);
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint64_t a_desc = umma_desc_kmajor_sw128(sa);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in >>4 units
+            mma_f16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          }
+          tc_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        tc_commit(smem_u32(&tfull_bar[acc]));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int mb, nb;
+      tile_coords(t, num_m, num_n, mb, nb);
+      mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, &s_abort, status, ERR_WAIT_TMEM_FULL);
+      tc_fence_after_sync();
+      const int row = mb * BM + q * 32 + lane;
+      const bool row_ok = row < M;
+      const __nv_bfloat16* gate_row = nullptr;
+      if (epi.gate && row_ok) gate_row = epi.gate + (size_t)(row / epi.rows_per_batch) * epi.gate_stride;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = nb * BN + c * 32;
+        if (col0 >= N) break;
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, v);
+        tmem_wait_ld();
+        if (row_ok) {
+          __nv_bfloat16* out;
+          if (epi.c_rows_per_batch > 0) {
+            const int cb = row / epi.c_rows_per_batch;
+            out = C + (size_t)cb * epi.c_batch_stride + (size_t)(row - cb * epi.c_rows_per_batch) * ldc + col0;
+          } else {
+            out = C + (size_t)row * ldc + col0;
+          }
+          const __nv_bfloat16* res = epi.residual ? epi.residual + (size_t)row * epi.ldr + col0 : nullptr;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {  // 8 columns per 16-byte store
+            if (col0 + j * 8 < N) {
+              float x[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[j * 8 + e]);
+              if (epi.bias) {
+                uint4 b = *reinterpret_cast<const uint4*>(epi.bias + col0 + j * 8);
+                float2 b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y), b2 = unpack_bf16(b.z), b3 = unpack_bf16(b.w);
+                x[0] += b0.x; x[1] += b0.y; x[2] += b1.x; x[3] += b1.y;
+                x[4] += b2.x; x[5] += b2.y; x[6] += b3.x; x[7] += b3.y;
+              }
+              if (epi.act == ACT_GELU_TANH) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = gelu_tanh(x[e]);
+              } else if (epi.act == ACT_SILU) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = silu(x[e]);
+              }
+              if (gate_row) {
+                uint4 g = *reinterpret_cast<const uint4*>(gate_row + col0 + j * 8);
+                float2 g0 = unpack_bf16(g.x), g1 = unpack_bf16(g.y), g2 = unpack_bf16(g.z), g3 = unpack_bf16(g.w);
+                x[0] *= g0.x; x[1] *= g0.y; x[2] *= g1.x; x[3] *= g1.y;
+                x[4] *= g2.x; x[5] *= g2.y; x[6] *= g3.x; x[7] *= g3.y;
+              }
+              if (res) {
+                uint4 r = *reinterpret_cast<const uint4*>(res + j * 8);
+                float2 r0 = unpack_bf16(r.x), r1 = unpack_bf16(r.y), r2 = unpack_bf16(r.z), r3 = unpack_bf16(r.w);
+                x[0] += r0.x; x[1] += r0.y; x[2] += r1.x; x[3] += r1.y;
+                x[4] += r2.x; x[5] += r2.y; x[6] += r3.x; x[7] += r3.y;
+              }
+              uint4 o;
+              o.x = pack_bf16(x[0], x[1]);
+              o.y = pack_bf16(x[2], x[3]);
+              o.z = pack_bf16(x[4], x[5]);
+              o.w = pack_bf16(x[6], x[7]);
+              *reinterpret_cast<uint4*>(out + j * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (s_abort) {
+    // give copies and MMAs that may still be in flight time to land before TMEM and
+    // shared memory are handed back
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, int ldc, int M,
+                       int N, int K, int ldw, const GemmEpilogue& epi, int* status, int max_ctas,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmB;
+  int rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K,
+                        (uint64_t)ldw * 2, BN, BK);
+  if (rc) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
+  gemm_bf16_kernel<BN><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, status);
+  return (int)cudaGetLastError();
+}
+
+static int pick_bn(int M, int N, int ctas) {
+  // minimise waves x tile width (time per tile is proportional to BN); wide tiles win ties
+  const int cand[3] = {256, 192, 128};
+  int best = 256;
+  long best_cost = -1;
+  const int num_m = (M + BM - 1) / BM;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cand[i];
+    const long tiles = (long)num_m * ((N + bn - 1) / bn);
+    const long waves = (tiles + ctas - 1) / ctas;
+    // narrow tiles re-read A more often: charge them a small penalty
+    const long cost = waves * bn * (bn == 128 ? 110 : (bn == 192 ? 103 : 100));
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+}  // namespace omni
+
+// C ABI.  All pointers are device pointers; `status` is a device int32 that receives the
+// first timeout code (0 = none).  Strides are in elements.  force_bn = 0 lets the launcher
+// choose the tile width.
+extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
+                              int M, int N, int K, const void* bias, const void* residual, int ldr,
+                              const void* gate, int gate_stride, int rows_per_batch, int act,
+                              int c_rows_per_batch, long c_batch_stride, int force_bn, int* status,
+                              void* stream) {
+  using namespace omni;
+  if (M <= 0 || N <= 0 || K <= 0) return RC_OK;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7) || (ldr & 7) || (gate_stride & 7))
+    return RC_BAD_ARG;
+  if (gate && rows_per_batch <= 0) return RC_BAD_ARG;
+  CUtensorMap tmA;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K,
+                        (uint64_t)lda * 2, BM, BK);
+  if (rc) return rc;
+  GemmEpilogue epi;
+  epi.bias = static_cast<const __nv_bfloat16*>(bias);
+  epi.residual = static_cast<const __nv_bfloat16*>(residual);
+  epi.gate = static_cast<const __nv_bfloat16*>(gate);
+  epi.ldr = ldr;
+  epi.gate_stride = gate_stride;
+  epi.rows_per_batch = rows_per_batch > 0 ? rows_per_batch : 1;
+  epi.act = act;
+  epi.c_rows_per_batch = c_rows_per_batch;
+  epi.c_batch_stride = c_batch_stride;
+  if (c_rows_per_batch > 0 && (c_batch_stride & 7)) return RC_BAD_ARG;
+  const int ctas = sm_count();
+  const int bn = force_bn ? force_bn : pick_bn(M, N, ctas);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* c = static_cast<__nv_bfloat16*>(C);
+  switch (bn) {
+    case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
+    case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
+    case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
+    default: return RC_BAD_ARG;
+  }
+}

@@ -1,0 +1,364 @@
+"""Qwen-Image-style dual-stream MMDiT, built on the fused sm_100a ops.
+
+Architecture and checkpoint names follow ``QwenImageTransformer2DModel``
+(vllm_omni/diffusion/models/qwen_image/qwen_image_transformer.py:746-1113): 60 blocks, each
+with an image stream and a text stream that share one joint attention; AdaLN modulation
+from the timestep embedding; RMSNorm on q/k heads; complex-pair RoPE with axes (16,56,56).
+
+What is different from the reference's layer-by-layer eager graph:
+  * the AdaLN projections of all blocks and both streams are ONE stacked GEMM per step
+    (``mod`` [L, 2, 6D, D]); blocks read their shift/scale/gate slices as strided views;
+  * both streams' QKV GEMMs write straight into one joint ``[B, S_img+S_txt, 3, H, Dh]``
+    buffer (image rows first, text rows last, so a text padding mask is a key-length);
+  * q/k RMSNorm + RoPE is one in-place kernel over that buffer; attention reads it through
+    strided TMA descriptors and writes image and text rows to their own tensors;
+  * bias, GELU, gate * x + residual run in the GEMM epilogues; LayerNorm + modulation is
+    one kernel.  A block is 14 kernel launches and no layout copies.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ....ops import fused
+from ....ops.attention import attention
+from ...layers.linear import FusedLinear
+
+
+@dataclass
+class QwenImageTransformerConfig:
+    patch_size: int = 2
+    in_channels: int = 64
+    out_channels: int = 16
+    num_layers: int = 60
+    attention_head_dim: int = 128
+    num_attention_heads: int = 24
+    joint_attention_dim: int = 3584
+    axes_dims_rope: tuple = (16, 56, 56)
+    rope_theta: float = 10000.0
+    mlp_ratio: int = 4
+    eps: float = 1e-6
+
+    @property
+    def inner_dim(self) -> int:
+        return self.attention_head_dim * self.num_attention_heads
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "QwenImageTransformerConfig":
+        keys = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items() if k in keys})
+
+
+class QwenEmbedRope:
+    """cos/sin tables of the 3-axis complex RoPE (frame, height, width), scale_rope=True.
+
+    Image token (f, h, w) uses centred height/width indices; text token i uses index
+    max(h//2, w//2) + i on all three axes (qwen_image_transformer.py:298-396).
+    """
+
+    def __init__(self, theta: float, axes_dim, scale_rope: bool = True):
+        self.theta, self.axes_dim, self.scale_rope = theta, tuple(axes_dim), scale_rope
+        self._cache: dict = {}
+
+    def _axis_angles(self, index: torch.Tensor, dim: int) -> torch.Tensor:
+        inv = 1.0 / torch.pow(self.theta, torch.arange(0, dim, 2, dtype=torch.float32) / dim)
+        return torch.outer(index.float(), inv)
+
+    def angles(self, frame: int, height: int, width: int, txt_len: int) -> torch.Tensor:
+        """[frame*height*width + txt_len, sum(axes)/2] rotation angles, image rows first."""
+        a0, a1, a2 = self.axes_dim
+        f_idx = torch.arange(frame)
+        if self.scale_rope:
+            h_idx = torch.cat([torch.arange(-(height - height // 2), 0), torch.arange(height // 2)])
+            w_idx = torch.cat([torch.arange(-(width - width // 2), 0), torch.arange(width // 2)])
+            base = max(height // 2, width // 2)
+        else:
+            h_idx, w_idx = torch.arange(height), torch.arange(width)
+            base = max(height, width)
+        fa = self._axis_angles(f_idx, a0)[:, None, None, :].expand(frame, height, width, -1)
+        ha = self._axis_angles(h_idx, a1)[None, :, None, :].expand(frame, height, width, -1)
+        wa = self._axis_angles(w_idx, a2)[None, None, :, :].expand(frame, height, width, -1)
+        img = torch.cat([fa, ha, wa], dim=-1).reshape(frame * height * width, -1)
+        t_idx = torch.arange(base, base + txt_len)
+        txt = torch.cat([self._axis_angles(t_idx, a) for a in self.axes_dim], dim=-1)
+        return torch.cat([img, txt], dim=0)
+
+    def cos_sin(self, frame, height, width, txt_len, device):
+        key = (frame, height, width, txt_len, str(device))
+        if key not in self._cache:
+            ang = self.angles(frame, height, width, txt_len)
+            self._cache[key] = (ang.cos().contiguous().to(device), ang.sin().contiguous().to(device))
+        return self._cache[key]
+
+
+def timestep_sinusoid(t: torch.Tensor, dim: int = 256, scale: float = 1000.0, max_period: float = 10000.0):
+    """diffusers ``Timesteps(256, flip_sin_to_cos=True, downscale_freq_shift=0, scale=1000)``."""
+    half = dim // 2
+    exponent = -math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half
+    emb = (t.float()[:, None] * scale) * torch.exp(exponent)[None, :]
+    return torch.cat([torch.cos(emb), torch.sin(emb)], dim=-1)
+
+
+class TimestepEmbedder(nn.Module):
+    def __init__(self, dim, dtype, device):
+        super().__init__()
+        self.linear_1 = FusedLinear(256, dim, dtype=dtype, device=device)
+        self.linear_2 = FusedLinear(dim, dim, dtype=dtype, device=device)
+
+    def forward(self, t, dtype):
+        x = timestep_sinusoid(t).to(dtype)
+        return self.linear_2(self.linear_1(x, act="silu"))
+
+
+class StreamParams(nn.Module):
+    """Per-stream weights of one block (the image stream or the text stream)."""
+
+    def __init__(self, dim, heads, head_dim, mlp_ratio, dtype, device):
+        super().__init__()
+        self.to_qkv = FusedLinear(dim, 3 * heads * head_dim, dtype=dtype, device=device)
+        self.to_out = FusedLinear(heads * head_dim, dim, dtype=dtype, device=device)
+        self.norm_q = nn.Parameter(torch.ones(head_dim, dtype=dtype, device=device), requires_grad=False)
+        self.norm_k = nn.Parameter(torch.ones(head_dim, dtype=dtype, device=device), requires_grad=False)
+        self.mlp_up = FusedLinear(dim, mlp_ratio * dim, dtype=dtype, device=device)
+        self.mlp_down = FusedLinear(mlp_ratio * dim, dim, dtype=dtype, device=device)
+
+
+class QwenImageTransformerBlock(nn.Module):
+    def __init__(self, cfg: QwenImageTransformerConfig, dtype, device):
+        super().__init__()
+        d, h, hd = cfg.inner_dim, cfg.num_attention_heads, cfg.attention_head_dim
+        self.img = StreamParams(d, h, hd, cfg.mlp_ratio, dtype, device)
+        self.txt = StreamParams(d, h, hd, cfg.mlp_ratio, dtype, device)
+
+
+@dataclass
+class _Workspace:
+    key: tuple = ()
+    bufs: dict = field(default_factory=dict)
+
+
+class QwenImageTransformer2DModel(nn.Module):
+    # checkpoint name -> (fused parameter, slice index) in the style of the reference's
+    # stacked_params_mapping (qwen_image_transformer.py:1073-1113)
+    _repeated_blocks = ["QwenImageTransformerBlock"]
+    _sp_plan = {
+        "hidden_states": {"split_dim": 1, "expected_dims": 3, "auto_pad": True},
+        "proj_out": {"gather_dim": 1},
+    }
+
+    def __init__(self, cfg: QwenImageTransformerConfig | None = None, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.cfg = cfg = cfg or QwenImageTransformerConfig()
+        self.dtype_ = dtype
+        D = cfg.inner_dim
+        self.img_in = FusedLinear(cfg.in_channels, D, dtype=dtype, device=device)
+        self.txt_norm_weight = nn.Parameter(torch.ones(cfg.joint_attention_dim, dtype=dtype, device=device),
+                                            requires_grad=False)
+        self.txt_in = FusedLinear(cfg.joint_attention_dim, D, dtype=dtype, device=device)
+        self.time_embed = TimestepEmbedder(D, dtype, device)
+        # AdaLN projections of every block and both streams, stacked: [L, 2(img,txt), 6D, D]
+        L = cfg.num_layers
+        self.mod = FusedLinear(D, L * 2 * 6 * D, dtype=dtype, device=device)
+        self.blocks = nn.ModuleList([QwenImageTransformerBlock(cfg, dtype, device) for _ in range(L)])
+        self.norm_out = FusedLinear(D, 2 * D, dtype=dtype, device=device)   # AdaLayerNormContinuous.linear
+        self.proj_out = FusedLinear(D, cfg.patch_size * cfg.patch_size * cfg.out_channels, dtype=dtype,
+                                    device=device)
+        self.rope = QwenEmbedRope(cfg.rope_theta, cfg.axes_dims_rope, scale_rope=True)
+        self._ws = _Workspace()
+        self.attn_impl = attention          # replaced by the sequence-parallel strategies
+        self.block_hook = None              # cache backends (TeaCache / DBCache) wrap the block loop
+
+    # ------------------------------------------------------------------ workspace
+    def _workspace(self, B, S_img, S_txt, device):
+        key = (B, S_img, S_txt, str(device))
+        if self._ws.key != key:
+            cfg, D, dt = self.cfg, self.cfg.inner_dim, self.dtype_
+            S = S_img + S_txt
+            e = lambda *s: torch.empty(*s, dtype=dt, device=device)
+            self._ws = _Workspace(key, dict(
+                qkv=e(B, S, 3 * D), img_n=e(B, S_img, D), txt_n=e(B, S_txt, D),
+                attn_img=e(B, S_img, D), attn_txt=e(B, S_txt, D),
+                mlp_img=e(B, S_img, cfg.mlp_ratio * D), mlp_txt=e(B, S_txt, cfg.mlp_ratio * D)))
+        return self._ws.bufs
+
+    # -------------------------------------------------------------------- forward
+    def block_forward(self, i, img, txt, mods, cos, sin, kv_lens, ws):
+        """One dual-stream block, in place on img [B,S_img,D] and txt [B,S_txt,D]."""
+        cfg = self.cfg
+        D, H, Hd = cfg.inner_dim, cfg.num_attention_heads, cfg.attention_head_dim
+        blk = self.blocks[i]
+        B, S_img, S_txt = img.shape[0], img.shape[1], txt.shape[1]
+        S = S_img + S_txt
+        qkv = ws["qkv"]
+        m = mods[:, i]                       # [B, 2, 6D]
+        for sidx, (sp, x, xn, rows, off) in enumerate(((blk.img, img, ws["img_n"], S_img, 0),
+                                                       (blk.txt, txt, ws["txt_n"], S_txt, S_img))):
+            mm = m[:, sidx]                  # [B, 6D], row stride L*2*6D
+            fused.norm_modulate(x, shift=mm[:, 0:D], scale=mm[:, D:2 * D], eps=cfg.eps, out=xn)
+            sp.to_qkv(xn, out=qkv[:, off:off + rows], out_rows_per_batch=rows, out_batch_stride=S * 3 * D)
+        fused.qk_norm_rope_(qkv, H, H, Hd, wq=blk.img.norm_q, wk=blk.img.norm_k, wq_alt=blk.txt.norm_q,
+                            wk_alt=blk.txt.norm_k, s_alt=S_img, cos=cos, sin=sin, interleaved=True, eps=cfg.eps)
+        q5 = qkv.view(B, S, 3, H, Hd)
+        self.attn_impl(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], kv_lens=kv_lens,
+                       out=ws["attn_img"].view(B, S_img, H, Hd), out2=ws["attn_txt"].view(B, S_txt, H, Hd),
+                       split=S_img)
+        for sidx, (sp, x, xn, att, hbuf) in enumerate(((blk.img, img, ws["img_n"], ws["attn_img"], ws["mlp_img"]),
+                                                       (blk.txt, txt, ws["txt_n"], ws["attn_txt"], ws["mlp_txt"]))):
+            mm = m[:, sidx]
+            sp.to_out(att, residual=x, gate=mm[:, 2 * D:3 * D], out=x)
+            fused.norm_modulate(x, shift=mm[:, 3 * D:4 * D], scale=mm[:, 4 * D:5 * D], eps=cfg.eps, out=xn)
+            sp.mlp_up(xn, act="gelu_tanh", out=hbuf)
+            sp.mlp_down(hbuf, residual=x, gate=mm[:, 5 * D:6 * D], out=x)
+        return img, txt
+
+    def embed(self, hidden_states, encoder_hidden_states, timestep):
+        """Input projections and the stacked AdaLN projection for this step."""
+        cfg, D, L = self.cfg, self.cfg.inner_dim, self.cfg.num_layers
+        img = self.img_in(hidden_states.to(self.dtype_))
+        txt = fused.norm_modulate(encoder_hidden_states.to(self.dtype_), weight=self.txt_norm_weight, rms=True,
+                                  eps=cfg.eps)
+        txt = self.txt_in(txt)
+        temb = self.time_embed(timestep, self.dtype_)                    # [B, D]
+        mods = self.mod(F.silu(temb)).view(-1, L, 2, 6 * D)
+        return img, txt, temb, mods
+
+    def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, txt_seq_lens=None,
+                encoder_hidden_states_mask=None, return_dict=False, **_):
+        """hidden_states [B, S_img, C_in], encoder_hidden_states [B, S_txt, joint_dim], timestep [B]
+        in [0, 1] (sigma), img_shapes (frame, height, width) in latent patches.  Returns the
+        velocity prediction [B, S_img, patch^2 * C_out]."""
+        cfg, D = self.cfg, self.cfg.inner_dim
+        B, S_img, S_txt = hidden_states.shape[0], hidden_states.shape[1], encoder_hidden_states.shape[1]
+        dev = hidden_states.device
+        while isinstance(img_shapes[0], (list, tuple)):   # accept (f,h,w), [(f,h,w)], [[(f,h,w)]]
+            img_shapes = img_shapes[0]
+        frame, height, width = img_shapes
+        cos, sin = self.rope.cos_sin(frame, height, width, S_txt, dev)
+        kv_lens = None
+        if txt_seq_lens is not None and any(int(l) != S_txt for l in txt_seq_lens):
+            kv_lens = torch.tensor([S_img + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
+        img, txt, temb, mods = self.embed(hidden_states, encoder_hidden_states, timestep)
+        ws = self._workspace(B, S_img, S_txt, dev)
+        run_blocks = self._run_blocks
+        if self.block_hook is not None:
+            img, txt = self.block_hook(self, run_blocks, img, txt, mods, cos, sin, kv_lens, ws, temb)
+        else:
+            img, txt = run_blocks(img, txt, mods, cos, sin, kv_lens, ws)
+        ss = self.norm_out(F.silu(temb))                                   # [B, 2D]: scale, shift
+        out = fused.norm_modulate(img, shift=ss[:, D:], scale=ss[:, :D], eps=cfg.eps, out=ws["img_n"])
+        out = self.proj_out(out)
+        return out
+
+    def _run_blocks(self, img, txt, mods, cos, sin, kv_lens, ws, start=0, end=None):
+        end = self.cfg.num_layers if end is None else end
+        for i in range(start, end):
+            self.block_forward(i, img, txt, mods, cos, sin, kv_lens, ws)
+        return img, txt
+
+    # -------------------------------------------------------------------- loading
+    def checkpoint_name_map(self) -> dict:
+        """diffusers parameter name -> (our parameter name, row slice or None)."""
+        cfg, D = self.cfg, self.cfg.inner_dim
+        HD = cfg.num_attention_heads * cfg.attention_head_dim
+        m = {
+            "img_in.weight": ("img_in.weight", None), "img_in.bias": ("img_in.bias", None),
+            "txt_in.weight": ("txt_in.weight", None), "txt_in.bias": ("txt_in.bias", None),
+            "txt_norm.weight": ("txt_norm_weight", None),
+            "norm_out.linear.weight": ("norm_out.weight", None), "norm_out.linear.bias": ("norm_out.bias", None),
+            "proj_out.weight": ("proj_out.weight", None), "proj_out.bias": ("proj_out.bias", None),
+        }
+        for j in (1, 2):
+            for wb in ("weight", "bias"):
+                m[f"time_text_embed.timestep_embedder.linear_{j}.{wb}"] = (f"time_embed.linear_{j}.{wb}", None)
+        for i in range(cfg.num_layers):
+            p, o = f"transformer_blocks.{i}.", f"blocks.{i}."
+            for sidx, (s, modn) in enumerate((("img", "img_mod.1"), ("txt", "txt_mod.1"))):
+                r0 = (i * 2 + sidx) * 6 * D
+                m[p + modn + ".weight"] = ("mod.weight", (r0, r0 + 6 * D))
+                m[p + modn + ".bias"] = ("mod.bias", (r0, r0 + 6 * D))
+            qkv_names = {"img": ("to_q", "to_k", "to_v"), "txt": ("add_q_proj", "add_k_proj", "add_v_proj")}
+            for s in ("img", "txt"):
+                for k, n in enumerate(qkv_names[s]):
+                    for wb in ("weight", "bias"):
+                        m[p + f"attn.{n}.{wb}"] = (o + f"{s}.to_qkv.{wb}", (k * HD, (k + 1) * HD))
+            for wb in ("weight", "bias"):
+                m[p + f"attn.to_out.0.{wb}"] = (o + f"img.to_out.{wb}", None)
+                m[p + f"attn.to_add_out.{wb}"] = (o + f"txt.to_out.{wb}", None)
+                for s in ("img", "txt"):
+                    m[p + f"{s}_mlp.net.0.proj.{wb}"] = (o + f"{s}.mlp_up.{wb}", None)
+                    m[p + f"{s}_mlp.net.2.{wb}"] = (o + f"{s}.mlp_down.{wb}", None)
+            m[p + "attn.norm_q.weight"] = (o + "img.norm_q", None)
+            m[p + "attn.norm_k.weight"] = (o + "img.norm_k", None)
+            m[p + "attn.norm_added_q.weight"] = (o + "txt.norm_q", None)
+            m[p + "attn.norm_added_k.weight"] = (o + "txt.norm_k", None)
+        return m
+
+    @torch.no_grad()
+    def load_weights(self, weights) -> set:
+        """``weights``: iterable of (diffusers name, tensor).  Returns the loaded names."""
+        params = dict(self.named_parameters())
+        nmap = self.checkpoint_name_map()
+        loaded = set()
+        for name, w in weights:
+            if name not in nmap:
+                continue
+            pn, sl = nmap[name]
+            p = params[pn]
+            dst = p if sl is None else p[sl[0]:sl[1]]
+            dst.copy_(w.to(dst.dtype).reshape(dst.shape))
+            loaded.add(name)
+        return loaded
+
+
+def reference_forward(model: QwenImageTransformer2DModel, hidden_states, encoder_hidden_states, timestep,
+                      img_shapes, txt_seq_lens=None):
+    """Straight-line fp32 PyTorch restatement of the same network (concatenates text and
+    image, calls torch softmax attention); the oracle for the fused forward."""
+    cfg, D, L = model.cfg, model.cfg.inner_dim, model.cfg.num_layers
+    H, Hd = cfg.num_attention_heads, cfg.attention_head_dim
+    f = lambda t: t.float()
+    lin = lambda l, x: F.linear(x, f(l.weight), None if l.bias is None else f(l.bias))
+    B, S_img, S_txt = hidden_states.shape[0], hidden_states.shape[1], encoder_hidden_states.shape[1]
+    frame, height, width = img_shapes
+    ang = model.rope.angles(frame, height, width, S_txt).to(hidden_states.device)
+    cos, sin = ang.cos(), ang.sin()
+    img = lin(model.img_in, f(hidden_states))
+    e = f(encoder_hidden_states)
+    txt = e * torch.rsqrt(e.pow(2).mean(-1, keepdim=True) + cfg.eps) * f(model.txt_norm_weight)
+    txt = lin(model.txt_in, txt)
+    temb = lin(model.time_embed.linear_2, F.silu(lin(model.time_embed.linear_1, timestep_sinusoid(timestep))))
+    mods = lin(model.mod, F.silu(temb)).view(B, L, 2, 6 * D)
+    ln = lambda x: F.layer_norm(x, (D,), None, None, cfg.eps)
+    for i, blk in enumerate(model.blocks):
+        qs, ks, vs, gates = [], [], [], []
+        for sidx, (sp, x) in enumerate(((blk.img, img), (blk.txt, txt))):
+            mm = mods[:, i, sidx]
+            xn = ln(x) * (1 + mm[:, None, D:2 * D]) + mm[:, None, 0:D]
+            qkv = lin(sp.to_qkv, xn).view(B, -1, 3, H, Hd)
+            q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+            rn = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.eps) * f(w)
+            qs.append(rn(q, sp.norm_q)); ks.append(rn(k, sp.norm_k)); vs.append(v)
+        q, k, v = torch.cat(qs, 1), torch.cat(ks, 1), torch.cat(vs, 1)
+        q = fused.apply_rope_reference(q, cos, sin, True)
+        k = fused.apply_rope_reference(k, cos, sin, True)
+        s = torch.einsum("bqhd,bkhd->bhqk", q, k) / math.sqrt(Hd)
+        if txt_seq_lens is not None:
+            idx = torch.arange(S_img + S_txt, device=s.device)
+            lens = torch.tensor([S_img + int(l) for l in txt_seq_lens], device=s.device)
+            s = s.masked_fill(idx[None, None, None, :] >= lens[:, None, None, None], float("-inf"))
+        o = torch.einsum("bhqk,bkhd->bqhd", s.softmax(-1), v).reshape(B, S_img + S_txt, H * Hd)
+        outs = []
+        for sidx, (sp, x, att) in enumerate(((blk.img, img, o[:, :S_img]), (blk.txt, txt, o[:, S_img:]))):
+            mm = mods[:, i, sidx]
+            x = x + mm[:, None, 2 * D:3 * D] * lin(sp.to_out, att)
+            xn = ln(x) * (1 + mm[:, None, 4 * D:5 * D]) + mm[:, None, 3 * D:4 * D]
+            x = x + mm[:, None, 5 * D:6 * D] * lin(sp.mlp_down, F.gelu(lin(sp.mlp_up, xn), approximate="tanh"))
+            outs.append(x)
+        img, txt = outs
+    ss = lin(model.norm_out, F.silu(temb))
+    out = ln(img) * (1 + ss[:, None, :D]) + ss[:, None, D:]
+    return lin(model.proj_out, out)

@@ -1,0 +1,79 @@
+"""K4 — flash attention forward on tcgen05/TMEM (csrc/attention_sm100.cu).
+
+``attention`` takes q/k/v as [B, S, H, D] views with a contiguous head dimension and free
+batch / row / head strides, so a packed ``[B, S, 3, H, D]`` projection output is consumed in
+place.  The reference reaches PyTorch SDPA on this hardware
+(vllm_omni/diffusion/attention/backends/sdpa.py:82); ``attention_reference`` restates that
+in fp32 and is the oracle of the numerics tests.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _native as nv
+
+c_int, c_long, c_float = ctypes.c_int, ctypes.c_long, ctypes.c_float
+
+
+def attention_reference(q, k, v, scale=None, kv_lens=None, return_lse=False):
+    """fp32 softmax(q k^T * scale) v.  q: [B,Sq,H,D], k/v: [B,Skv,Hkv,D]."""
+    B, Sq, H, D = q.shape
+    Hkv = k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if kv_lens is not None:
+        idx = torch.arange(k.shape[1], device=q.device)[None, None, None, :]
+        s = s.masked_fill(idx >= kv_lens.to(q.device)[:, None, None, None], float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    o = torch.matmul(torch.softmax(s, dim=-1), vf).permute(0, 2, 1, 3)
+    o = o.to(q.dtype)
+    return (o, lse) if return_lse else o
+
+
+def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, return_lse=False,
+              _v_desc_mode=0):
+    """Non-causal attention.  Returns ``out`` ([B, Sq, H, D], or the given buffer).
+
+    ``out2``/``split``: rows >= split of every batch go to ``out2`` (row index s - split).
+    """
+    B, Sq, H, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        r = attention_reference(q, k, v, scale, kv_lens, return_lse)
+        o, lse = (r if return_lse else (r, None))
+        if out2 is not None:
+            out.copy_(o[:, :split])
+            out2.copy_(o[:, split:])
+        elif out is not None:
+            out.copy_(o)
+        else:
+            out = o
+        return (out, lse) if return_lse else out
+    assert q.dtype == torch.bfloat16 and D == 128, "tcgen05 attention path: bf16, head_dim 128"
+    for t in (q, k, v):
+        assert t.stride(3) == 1
+    if out is None:
+        out = torch.empty(B, Sq, H, D, dtype=q.dtype, device=q.device)
+    assert out.stride(3) == 1 and (out2 is None or out2.stride(3) == 1)
+    lse = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device) if return_lse else None
+    if kv_lens is not None:
+        assert kv_lens.dtype == torch.int32 and kv_lens.is_cuda
+    o2s = (out2.stride(1), out2.stride(2), out2.stride(0)) if out2 is not None else (0, 0, 0)
+    st = nv.status_word(q.device)
+    rc = nv.lib("attention_sm100").omni_attn_fwd(
+        nv.ptr(q), c_long(q.stride(1)), c_long(q.stride(2)), c_long(q.stride(0)),
+        nv.ptr(k), c_long(k.stride(1)), c_long(k.stride(2)), c_long(k.stride(0)),
+        nv.ptr(v), c_long(v.stride(1)), c_long(v.stride(2)), c_long(v.stride(0)),
+        nv.ptr(out), c_long(out.stride(1)), c_long(out.stride(2)), c_long(out.stride(0)),
+        nv.ptr(out2), c_long(o2s[0]), c_long(o2s[1]), c_long(o2s[2]), c_int(split),
+        nv.ptr(lse), c_int(B), c_int(H), c_int(Hkv), c_int(Sq), c_int(Skv), c_int(D), nv.ptr(kv_lens),
+        c_float(scale), c_int(_v_desc_mode), nv.ptr(st), nv.stream_ptr())
+    nv.check_rc(rc, "omni_attn_fwd")
+    return (out, lse) if return_lse else out

@@ -1,0 +1,97 @@
+"""K1 — linear layers on the tcgen05 GEMM (csrc/gemm_sm100.cu).
+
+``linear`` computes ``epilogue(x @ w.T)`` with the bias, activation, per-batch gate and
+residual fused into the GEMM epilogue.  It replaces the cuBLAS path behind the
+reference's vLLM ``ColumnParallelLinear`` / ``RowParallelLinear`` / ``QKVParallelLinear``
+(vllm_omni/diffusion/models/qwen_image/qwen_image_transformer.py:427-560).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _native as nv
+
+ACT = {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def linear_reference(x, w, bias=None, act=None, residual=None, gate=None):
+    """Plain PyTorch restatement (fp32 accumulate) used on CPU and as the test oracle.
+
+    ``gate`` has shape [B, N] and ``x`` [B, S, K] (or [M, K] with B dividing M).
+    """
+    y = F.linear(x.float(), w.float(), None if bias is None else bias.float())
+    if act == "gelu_tanh":
+        y = F.gelu(y, approximate="tanh")
+    elif act == "silu":
+        y = F.silu(y)
+    if gate is not None:
+        B = gate.shape[0]
+        shp = y.shape
+        y = (y.reshape(B, -1, shp[-1]) * gate.float().unsqueeze(1)).reshape(shp)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
+           residual: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+           out: torch.Tensor | None = None, force_bn: int = 0,
+           out_rows_per_batch: int = 0, out_batch_stride: int = 0) -> torch.Tensor:
+    """y = residual + gate * act(x @ w.T + bias).
+
+    ``out_rows_per_batch`` / ``out_batch_stride`` (elements): row r of the result is stored at
+    ``out + (r // rpb) * batch_stride + (r % rpb) * out.stride(-2)``; used to write one stream's
+    rows into a joint [B, S_txt + S_img, N] buffer (pass ``out`` as the [B, S_x, N] slice).
+
+    x: [..., K] bf16 (last dim contiguous), w: [N, K] bf16, bias: [N], residual: [..., N]
+    (may be ``out``), gate: [B, N] view (last dim contiguous, any row stride) where the rows
+    of x split evenly into B batches.
+    """
+    if not x.is_cuda:
+        y = linear_reference(x, w, bias, act, residual, gate)
+        if out is not None:
+            out.copy_(y.reshape(out.shape))
+            return out
+        return y
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "tcgen05 GEMM path is bf16"
+    K = x.shape[-1]
+    N = w.shape[0]
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    if w.stride(-1) != 1:
+        w = w.contiguous()
+    if out is None:
+        out = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
+    if out_rows_per_batch:
+        assert out.stride(-1) == 1
+        ldc = out.stride(-2)
+    else:
+        out2 = out.view(-1, N)
+        ldc = out2.stride(0)
+    res2 = None
+    ldr = 0
+    if residual is not None:
+        res2 = residual.reshape(-1, N)
+        assert res2.stride(-1) == 1
+        ldr = res2.stride(0)
+    gs = 0
+    rpb = 0
+    if gate is not None:
+        assert gate.dim() == 2 and gate.shape[1] == N and gate.stride(1) == 1
+        assert M % gate.shape[0] == 0
+        rpb = M // gate.shape[0]
+        gs = gate.stride(0) if gate.shape[0] > 1 else N
+    st = nv.status_word(x.device)
+    rc = nv.lib("gemm_sm100").omni_gemm_bf16(
+        nv.ptr(x2), ctypes.c_int(x2.stride(0)), nv.ptr(w), ctypes.c_int(w.stride(0)),
+        nv.ptr(out), ctypes.c_int(ldc), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        nv.ptr(bias), nv.ptr(res2), ctypes.c_int(ldr), nv.ptr(gate), ctypes.c_int(gs), ctypes.c_int(rpb),
+        ctypes.c_int(ACT[act]), ctypes.c_int(out_rows_per_batch), ctypes.c_long(out_batch_stride),
+        ctypes.c_int(force_bn), nv.ptr(st), nv.stream_ptr())
+    nv.check_rc(rc, "omni_gemm_bf16")
+    return out
