@@ -381,3 +381,64 @@ extern "C" int omni_rel_l1(const void* a, const void* b, long n, float* scratch,
   rel_l1_finish_kernel<<<1, RL_THREADS, 0, (cudaStream_t)stream>>>(scratch, parts, state, coef, ncoef, thresh, force_compute, sums_out);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------
+// Allocation-free variant of omni_rel_l1 (declared in omni_noalloc.h).
+//
+// The two-stage reduction needs 2 floats of scratch per stage-1 CTA.  The general entry
+// point takes that scratch from the caller; this one keeps it in a file-scope device array
+// so that a caller which owns no allocator can still use the kernel.
+constexpr int RL_NOALLOC_MAX_PARTS = 148 * 4;                 // same cap as omni_rel_l1_parts()
+constexpr long RL_NOALLOC_MAX_ELEMS = 1L << 28;               // 268,435,456 elements per operand
+static __device__ __align__(256) float g_rel_l1_scratch[2 * RL_NOALLOC_MAX_PARTS];  // 4,736 bytes
+
+namespace {
+constexpr int RL_MAX_DEVICES = 64;
+std::mutex g_noalloc_mu;
+float* g_noalloc_ptr[RL_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+extern "C" long omni_rel_l1_noalloc_max_elems(void) { return RL_NOALLOC_MAX_ELEMS; }
+
+extern "C" const char* omni_rel_l1_noalloc_strerror(int rc) {
+  switch (rc) {
+    case 0: return "ok";
+    case RC_BAD_ARG: return "bad argument: n must be a positive multiple of 8 and the pointers non-null";
+    case RC_TOO_LARGE: return "n exceeds omni_rel_l1_noalloc_max_elems() (2^28 elements per operand)";
+    default: return rc > 0 ? "CUDA runtime error (the value is the cudaError_t)" : "unknown error";
+  }
+}
+
+extern "C" int omni_rel_l1_noalloc(const void* a, const void* b, long n, float* sums_out, float* state,
+                                   const float* coef, int ncoef, float thresh, int force_compute,
+                                   void* stream) {
+  if (a == nullptr || b == nullptr || n <= 0 || (n & 7)) return RC_BAD_ARG;
+  if (sums_out == nullptr && state == nullptr) return RC_BAD_ARG;
+  if (n > RL_NOALLOC_MAX_ELEMS) return RC_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= RL_MAX_DEVICES) return RC_BAD_ARG;
+  float* scratch = nullptr;
+  {
+    // First call on this device: resolve the device address of the static array.  The array's
+    // name is only a host-side handle here; a kernel must be given the address the runtime
+    // reports for the current device.
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_rel_l1_scratch);
+      if (e != cudaSuccess) return (int)e;
+      g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  const int parts = omni_rel_l1_parts(n);  // <= RL_NOALLOC_MAX_PARTS by construction
+  // Stage 1 overwrites scratch[0 .. 2*parts) completely and stage 2 reads exactly that range,
+  // so nothing left over from an earlier call is ever read and nothing needs clearing.
+  rel_l1_partial_kernel<<<parts, RL_THREADS, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, n >> 3, scratch);
+  rel_l1_finish_kernel<<<1, RL_THREADS, 0, (cudaStream_t)stream>>>(scratch, parts, state, coef, ncoef, thresh,
+                                                                   force_compute, sums_out);
+  return (int)cudaGetLastError();
+}
