@@ -63,3 +63,35 @@ def test_forward_matches_reference_gpu():
     ref = reference_forward(m, x.bfloat16().float(), e.bfloat16().float(), t, (1, h, w), txt_seq_lens=[40, 17])
     err = (y - ref).abs().max().item()
     assert err < 0.08 * max(1.0, ref.abs().max().item()), err
+
+
+def test_loop_fast_path_matches_forward_cpu():
+    m = _tiny(torch.float32, "cpu")
+    B, h, w, St = 2, 6, 4, 5
+    x = torch.randn(B, h * w, 16)
+    e = torch.randn(B, St, 64)
+    st = m.prepare_loop(e, [0.9, 0.4], (1, h, w), h * w, txt_seq_lens=[5, 4])
+    st.lat_in.copy_(x)
+    for i, sig in enumerate([0.9, 0.4]):
+        y = m.forward_step(st, i).clone()
+        ref = m(x, e, torch.tensor([sig, sig]), (1, h, w), txt_seq_lens=[5, 4])
+        assert torch.allclose(y, ref, atol=1e-5, rtol=1e-4), (i, (y - ref).abs().max())
+
+
+@pytest.mark.gpu
+def test_loop_graph_replay_matches_eager_gpu():
+    dev = torch.device("cuda")
+    m = _tiny(torch.bfloat16, dev, head_dim=128, heads=2, layers=2)
+    B, h, w, St = 2, 16, 12, 40
+    x = torch.randn(B, h * w, 16, device=dev)
+    e = torch.randn(B, St, 64, device=dev)
+    sig = [0.9, 0.7, 0.5, 0.3]
+    st_e = m.prepare_loop(e, sig, (1, h, w), h * w, txt_seq_lens=[40, 17], use_graph=False)
+    st_g = m.prepare_loop(e, sig, (1, h, w), h * w, txt_seq_lens=[40, 17], use_graph=True)
+    st_e.lat_in.copy_(x)
+    st_g.lat_in.copy_(x)
+    for i in range(len(sig)):
+        a = m.forward_step(st_e, i).float().clone()
+        b = m.forward_step(st_g, i).float().clone()
+        assert torch.equal(a, b), (i, (a - b).abs().max().item())
+    assert st_g.graph is not None

@@ -107,6 +107,166 @@ norm_modulate_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restr
   }
 }
 
+// Warp-per-row variant: the row stays packed (bf16) in VPL 16-byte registers per lane, all
+// loads of a row are in flight at once, no shared memory and no block barrier.
+template <int VPL>
+__global__ void __launch_bounds__(256)
+norm_modulate_warp_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int rows,
+                          int D, int ldx, int ldy, const __nv_bfloat16* __restrict__ weight,
+                          const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ shift,
+                          const __nv_bfloat16* __restrict__ scale, int mod_stride, int rows_per_batch,
+                          int rms, float eps) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int nchunk = D >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
+  uint4 v[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + i * 32;
+    v[i] = c < nchunk ? xr[c] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16(w[j]);
+      s += f.x + f.y;
+      ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+    }
+  }
+  s = warp_sum(s);
+  ss = warp_sum(ss);
+  const float inv_d = 1.0f / (float)D;
+  const float mean = rms ? 0.f : s * inv_d;
+  const float var = rms ? ss * inv_d : fmaxf(ss * inv_d - mean * mean, 0.f);
+  const float rstd = rsqrtf(var + eps);
+  const int b = row / rows_per_batch;
+  const __nv_bfloat16* sh = shift ? shift + (size_t)b * mod_stride : nullptr;
+  const __nv_bfloat16* sc = scale ? scale + (size_t)b * mod_stride : nullptr;
+  __nv_bfloat16* yr = y + (size_t)row * ldy;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + i * 32;
+    if (c < nchunk) {
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(w[j]);
+        o[2 * j] = (f.x - mean) * rstd;
+        o[2 * j + 1] = (f.y - mean) * rstd;
+      }
+      if (weight) { float t[8]; load8(weight + c * 8, t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] *= t[e]; }
+      if (bias) { float t[8]; load8(bias + c * 8, t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += t[e]; }
+      if (sc) { float t[8]; load8(sc + c * 8, t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = fmaf(o[e], t[e], o[e]); }
+      if (sh) { float t[8]; load8(sh + c * 8, t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += t[e]; }
+      store8(yr + c * 8, o);
+    }
+  }
+}
+
+// Fast q/k norm + rope for D = 128: one warp per (batch, position) row walks all q and k heads
+// of that row; half a warp owns one head (8 contiguous elements per lane, one 16-byte access),
+// four heads-pairs are in flight per iteration.
+__global__ void __launch_bounds__(256)
+qk_norm_rope128_kernel(__nv_bfloat16* __restrict__ qkv, long rows, int S, int H, int Hkv, int ld,
+                       const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
+                       const __nv_bfloat16* __restrict__ wq_alt, const __nv_bfloat16* __restrict__ wk_alt,
+                       int s_alt, const float* __restrict__ cosb, const float* __restrict__ sinb,
+                       int interleaved, float eps, const int* __restrict__ positions) {
+  constexpr int D = 128;
+  const long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int l16 = lane & 15;
+  const int hsel = lane >> 4;
+  const int s = (int)(row % S);
+  const int pos = positions ? positions[row] : s;
+  const bool alt = s >= s_alt;
+  const __nv_bfloat16* wqq = (alt && wq_alt) ? wq_alt : wq;
+  const __nv_bfloat16* wkk = (alt && wk_alt) ? wk_alt : wk;
+  float wqf[8], wkf[8];
+  if (wqq) { load8(wqq + l16 * 8, wqf); load8(wkk + l16 * 8, wkf); }
+  // rotation coefficients of this lane's elements
+  float cs[8], sn[8];
+  if (cosb) {
+    const float* cr = cosb + (size_t)pos * (D / 2);
+    const float* sr = sinb + (size_t)pos * (D / 2);
+    if (interleaved) {   // elements 8*l16 .. +7 = pairs 4*l16 .. +3
+      const float4 c4 = *reinterpret_cast<const float4*>(cr + 4 * l16);
+      const float4 s4 = *reinterpret_cast<const float4*>(sr + 4 * l16);
+      cs[0] = cs[1] = c4.x; cs[2] = cs[3] = c4.y; cs[4] = cs[5] = c4.z; cs[6] = cs[7] = c4.w;
+      sn[0] = -s4.x; sn[1] = s4.x; sn[2] = -s4.y; sn[3] = s4.y; sn[4] = -s4.z; sn[5] = s4.z; sn[6] = -s4.w; sn[7] = s4.w;
+    } else {             // element i pairs with i +- 64; frequency index i mod 64
+      const int f0 = (l16 & 7) * 8;
+      const float sign = l16 < 8 ? -1.f : 1.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { cs[e] = cr[f0 + e]; sn[e] = sign * sr[f0 + e]; }
+    }
+  }
+  __nv_bfloat16* base = qkv + (size_t)row * ld;
+  const int heads = H + Hkv;
+  constexpr int U = 4;
+  for (int h0 = 0; h0 < heads; h0 += 2 * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int h = h0 + 2 * u + hsel;
+      v[u] = h < heads ? *reinterpret_cast<const uint4*>(base + (size_t)h * D + l16 * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int h = h0 + 2 * u + hsel;
+      const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+      float xv[8];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(w[j]);
+        xv[2 * j] = f.x; xv[2 * j + 1] = f.y;
+        ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+      }
+      if (wqq) {
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float r = rsqrtf(ss * (1.0f / D) + eps);
+        const bool is_k = h >= H;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xv[e] = xv[e] * r * (is_k ? wkf[e] : wqf[e]);
+      }
+      if (cosb) {
+        if (interleaved) {
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const float a = xv[e], bb = xv[e + 1];
+            xv[e] = fmaf(a, cs[e], bb * sn[e]);          // a*c - b*s
+            xv[e + 1] = fmaf(bb, cs[e + 1], a * sn[e + 1]);  // b*c + a*s
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float partner = __shfl_xor_sync(0xffffffffu, xv[e], 8);
+            xv[e] = fmaf(xv[e], cs[e], partner * sn[e]);
+          }
+        }
+      }
+      if (h < heads) store8(base + (size_t)h * D + l16 * 8, xv);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ qk norm + rope
 // qkv: [B, S, 3, H, D] (row pitch ld elements between consecutive s), D in {64, 128}.
 // One warp per (row, head); lane owns D/32 consecutive elements (2 or 4), i.e. whole
@@ -316,10 +476,23 @@ extern "C" int omni_norm_modulate(const void* x, void* y, int rows, int D, int l
   if (rows <= 0) return RC_OK;
   if ((D & 7) || D > NM_THREADS * 8 * NM_MAXV || (ldx & 7) || (ldy & 7) || (mod_stride & 7)) return RC_BAD_ARG;
   if (rows_per_batch <= 0) rows_per_batch = rows;
-  norm_modulate_kernel<<<rows, NM_THREADS, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, D, ldx, ldy, (const __nv_bfloat16*)weight,
-      (const __nv_bfloat16*)bias, (const __nv_bfloat16*)shift, (const __nv_bfloat16*)scale, mod_stride,
-      rows_per_batch, rms, eps);
+  auto xx = (const __nv_bfloat16*)x; auto yy = (__nv_bfloat16*)y;
+  auto w = (const __nv_bfloat16*)weight; auto bb = (const __nv_bfloat16*)bias;
+  auto sh = (const __nv_bfloat16*)shift; auto sc = (const __nv_bfloat16*)scale;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int vpl = ((D >> 3) + 31) / 32;
+  const unsigned wgrid = (unsigned)((rows + 7) / 8);
+#define OMNI_NM_WARP(V) norm_modulate_warp_kernel<V><<<wgrid, 256, 0, st>>>(xx, yy, rows, D, ldx, ldy, w, bb, sh, sc, mod_stride, rows_per_batch, rms, eps)
+  if (vpl <= 2) OMNI_NM_WARP(2);
+  else if (vpl <= 4) OMNI_NM_WARP(4);
+  else if (vpl <= 8) OMNI_NM_WARP(8);
+  else if (vpl <= 12) OMNI_NM_WARP(12);
+  else if (vpl <= 16) OMNI_NM_WARP(16);
+  else if (vpl <= 20) OMNI_NM_WARP(20);
+  else
+    norm_modulate_kernel<<<rows, NM_THREADS, 0, st>>>(xx, yy, rows, D, ldx, ldy, w, bb, sh, sc, mod_stride,
+                                                      rows_per_batch, rms, eps);
+#undef OMNI_NM_WARP
   return (int)cudaGetLastError();
 }
 
@@ -334,7 +507,13 @@ extern "C" int omni_qk_norm_rope(void* qkv, int B, int S, int H, int Hkv, int D,
   auto q = (__nv_bfloat16*)qkv;
   auto a = (const __nv_bfloat16*)wq; auto b = (const __nv_bfloat16*)wk;
   auto c = (const __nv_bfloat16*)wq_alt; auto d = (const __nv_bfloat16*)wk_alt;
-  if (D == 128)
+  const bool have_w = wq != nullptr;
+  if (D == 128 && (ld & 7) == 0 && (wq != nullptr) == (wk != nullptr)) {
+    const long rows = (long)B * S;
+    (void)have_w;
+    qk_norm_rope128_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+        q, rows, S, H, Hkv, ld, a, b, c, d, s_alt, cosb, sinb, interleaved, eps, positions);
+  } else if (D == 128)
     qk_norm_rope_kernel<128><<<grid, wpb * 32, 0, (cudaStream_t)stream>>>(q, B, S, H, Hkv, ld, a, b, c, d, s_alt, cosb, sinb, interleaved, eps, positions);
   else if (D == 64)
     qk_norm_rope_kernel<64><<<grid, wpb * 32, 0, (cudaStream_t)stream>>>(q, B, S, H, Hkv, ld, a, b, c, d, s_alt, cosb, sinb, interleaved, eps, positions);

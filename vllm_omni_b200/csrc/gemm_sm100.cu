@@ -9,7 +9,8 @@
 //   warp 1    MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) with
 //             the fp32 accumulator in tensor memory; tcgen05.commit hands ring slots back
 //             to the producer and finished accumulators to the epilogue
-//   warps 2-5 epilogue: tcgen05.ld of the accumulator (one row per thread, 32 columns per
+//   warps 2-9 epilogue: two warps per TMEM lane quadrant, each draining half of the tile's
+//             columns: tcgen05.ld of the accumulator (one row per thread, 32 columns per
 //             instruction), fused bias / GELU-tanh / SiLU / gate*x + residual, bf16 stores
 // Two accumulators live in TMEM so the epilogue of tile i overlaps the main loop of
 // tile i+1.  All mbarrier waits are bounded (see ptx_sm100.cuh); a timeout is reported
@@ -24,6 +25,7 @@ namespace omni {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 
 enum Act : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SILU = 2 };
 
@@ -66,7 +68,7 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
 }
 
 template <int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  __nv_bfloat16* __restrict__ C, int ldc, int M, int N, int K, GemmEpilogue epi,
                  int* status) {
@@ -98,7 +100,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tempty_bar[i]), 4);
+      mbar_init(smem_u32(&tempty_bar[i]), 8);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -165,7 +167,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const int q = warp & 3;         // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
+    constexpr int CH_PER_WARP = BN / 64;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -178,7 +182,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const __nv_bfloat16* gate_row = nullptr;
       if (epi.gate && row_ok) gate_row = epi.gate + (size_t)(row / epi.rows_per_batch) * epi.gate_stride;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * CH_PER_WARP; c < (half + 1) * CH_PER_WARP; ++c) {
         const int col0 = nb * BN + c * 32;
         if (col0 >= N) break;
         uint32_t v[32];
@@ -272,7 +276,7 @@ static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, 
   }
   const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
-  gemm_bf16_kernel<BN><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, status);
+  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, status);
   return (int)cudaGetLastError();
 }
 

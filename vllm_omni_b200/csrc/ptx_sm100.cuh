@@ -269,15 +269,22 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t M, uint32_t N, uint32
 }
 
 // ------------------------------------------------------------------ numerics
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x);
-  // tanh(u) = 1 - 2 / (exp(2u) + 1)
-  float e = __expf(2.0f * u);
-  float t = 1.0f - 2.0f / (e + 1.0f);
-  return 0.5f * x * (1.0f + t);
+  const float u = k0 * x * fmaf(k1 * x, x, 1.0f);
+  const float hx = 0.5f * x;
+  return fmaf(hx, tanh_approx(u), hx);
 }
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) {
+  // x * sigmoid(x) with sigmoid(x) = 0.5 * (1 + tanh(x / 2)): one MUFU op, no division
+  const float hx = 0.5f * x;
+  return fmaf(hx, tanh_approx(hx), hx);
+}
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

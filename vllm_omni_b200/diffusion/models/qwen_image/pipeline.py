@@ -87,6 +87,7 @@ class QwenImagePipeline(nn.Module):
         self.scheduler = FlowMatchEulerDiscreteScheduler(**(scheduler_config or QWEN_IMAGE_SCHEDULER))
         self.text_encoder = HashTextEncoder(tcfg.joint_attention_dim)
         self.default_sample_size = 128
+        self._loop_cache: dict = {}
         self.cfg_exchange = None        # set by CFG-parallel: fused peer exchange + step
         self.vae_decode = None          # set by VAE patch parallel
 
@@ -140,15 +141,14 @@ class QwenImagePipeline(nn.Module):
             enc, lens, nb = neg_embeds.to(dt_model), neg_mask.sum(1).tolist(), B
         else:
             enc, lens, nb = prompt_embeds.to(dt_model), prompt_mask.sum(1).tolist(), B
-        lat_in = torch.empty(nb, latents.shape[1], latents.shape[2], dtype=dt_model, device=latents.device)
+        use_graph = not self.od_config.enforce_eager
+        st = self._loop_state(enc, lens, img_shape, latents.shape[1], len(timesteps), use_graph)
+        lat_in = st.lat_in
         lat_in[:B].copy_(latents)
         if nb > B:
             lat_in[B:].copy_(lat_in[:B])
-        tvec = torch.empty(nb, dtype=torch.float32, device=latents.device)
         for i in range(len(timesteps)):
-            sigma = float(self.scheduler.sigmas[i])
-            tvec.fill_(sigma)                      # the transformer takes timestep / 1000 = sigma
-            v = self.transformer(lat_in, enc, tvec, img_shape, txt_seq_lens=lens)
+            v = self.transformer.forward_step(st, i)
             dt = self.scheduler.dt(i)
             if cfg_par:
                 self.cfg_exchange.step(v, latents, true_cfg_scale, dt, cfg_normalize, lat_in)
@@ -160,6 +160,25 @@ class QwenImagePipeline(nn.Module):
             if step_callback is not None:
                 step_callback(i, latents)
         return latents
+
+    def _loop_state(self, enc, lens, img_shape, S_img, n_steps, use_graph):
+        """Denoising-loop state; the workspace, and with it a captured CUDA graph, is reused
+        across requests of the same shape (only the request-dependent tensors are refreshed)."""
+        sig = [float(s) for s in self.scheduler.sigmas[:n_steps]]
+        key = (tuple(enc.shape), tuple(int(l) for l in lens), tuple(img_shape), S_img, tuple(sig), use_graph)
+        fresh = self.transformer.prepare_loop(enc, sig, img_shape, S_img, txt_seq_lens=lens, use_graph=use_graph)
+        old = self._loop_cache.get(key)
+        if old is None:
+            if len(self._loop_cache) >= 4:
+                self._loop_cache.pop(next(iter(self._loop_cache)))
+            self._loop_cache[key] = fresh
+            return fresh
+        # same shapes: keep the captured graph and its static buffers, refresh their contents
+        old.txt0.copy_(fresh.txt0)
+        old.mods_all.copy_(fresh.mods_all)
+        old.ss_all.copy_(fresh.ss_all)
+        old.temb_all.copy_(fresh.temb_all)
+        return old
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
