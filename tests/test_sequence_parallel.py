@@ -1,0 +1,67 @@
+"""Ulysses sequence parallelism: sharded run == single-rank run.
+
+CPU: 2 Gloo ranks exercise the layout logic through the all-to-all baseline mode.
+GPU (needs 2 devices): the fused peer-memory path against the same single-rank result.
+"""
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+
+def _build(dtype, device, head_dim, heads):
+    from vllm_omni_b200.diffusion.models.qwen_image.transformer import (QwenImageTransformer2DModel,
+                                                                        QwenImageTransformerConfig)
+    axes = {32: (8, 12, 12), 128: (16, 56, 56)}[head_dim]
+    cfg = QwenImageTransformerConfig(num_layers=2, attention_head_dim=head_dim, num_attention_heads=heads,
+                                     joint_attention_dim=64, in_channels=16, out_channels=4, axes_dims_rope=axes)
+    torch.manual_seed(0)
+    m = QwenImageTransformer2DModel(cfg, dtype=dtype, device=device)
+    g = torch.Generator(device="cpu").manual_seed(1)
+    for p in m.parameters():
+        if p.dim() == 1:
+            p.copy_(torch.randn(p.shape, generator=g) * 0.5)
+        else:
+            p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype))
+    return m
+
+
+def _sp_worker(rank, world, backend, mode, dtype_name, head_dim, heads, tol):
+    from vllm_omni_b200.parallel import parallel_state as ps
+    from vllm_omni_b200.parallel.ulysses import UlyssesJointAttention
+    dtype = getattr(torch, dtype_name)
+    device = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+    ps.init_distributed_environment(world, rank, local_rank=rank, backend=backend)
+    ps.initialize_model_parallel(sequence_parallel_size=world, ulysses_degree=world, backend=backend)
+    m = _build(dtype, device, head_dim, heads)
+    B, h, w, St = 2, 8, 8, 6 * world
+    g = torch.Generator(device="cpu").manual_seed(2)
+    x = torch.randn(B, h * w, 16, generator=g).to(device)
+    e = torch.randn(B, St, 64, generator=g).to(device)
+    t = torch.tensor([0.6, 0.6], device=device)
+    lens = [St, St - 3]
+    ref = m(x, e, t, (1, h, w), txt_seq_lens=lens).float()
+    m.sp = UlyssesJointAttention(ps.get_sp_group().ulysses, heads, head_dim, mode=mode)
+    Si, Sl = h * w // world, St // world
+    y = m(x[:, rank * Si:(rank + 1) * Si].contiguous(), e[:, rank * Sl:(rank + 1) * Sl].contiguous(), t, (1, h, w),
+          txt_seq_lens=lens).float()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+        from vllm_omni_b200.ops import _native as nv
+        assert int(nv.status_word(device).item()) == 0
+    err = (y - ref[:, rank * Si:(rank + 1) * Si]).abs().max().item()
+    assert err < tol * max(1.0, ref.abs().max().item()), f"rank {rank}: {err}"
+    m.sp.close()
+    ps.destroy_distributed_environment()
+
+
+def test_ulysses_matches_single_rank_cpu_gloo():
+    run_distributed(_sp_worker, 2, "gloo", args=("gloo", "nccl", "float32", 32, 4, 2e-4))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
+def test_ulysses_matches_single_rank_gpu(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_distributed(_sp_worker, 2, "nccl", args=("nccl", mode, "bfloat16", 128, 4, 0.06))

@@ -39,6 +39,14 @@ struct AttnOut {
   long o2_bs, o2_rs, o2_hs;
   int split;
   float* lse;  // [B, H, Sq] or nullptr
+  // Fused reverse all-to-all (Ulysses): with n_peers > 1 query row s < split belongs to rank
+  // s / rows_per_rank and is stored, as local row s % rows_per_rank, through o_peers[that rank];
+  // rows >= split use rows_per_rank2 / o2_peers the same way.  The pointers are peer (NVLink)
+  // or local addresses that already include this rank's head offset.
+  int n_peers;
+  int rows_per_rank, rows_per_rank2;
+  __nv_bfloat16* o_peers[16];
+  __nv_bfloat16* o2_peers[16];
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -50,7 +58,7 @@ __device__ __forceinline__ float ex2(float x) {
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnOut out, int Sq, int Skv, int H, int Hkv,
-                const int* __restrict__ kv_lens, float scale_log2, int v_desc_mode, int* status) {
+                const int* __restrict__ kv_lens, float scale_log2, int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
   __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
@@ -142,8 +150,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // 16 keys = two 8-row groups of 1024 B; the two 64-wide halves of D are
           // ATT_HALF_BYTES apart
           const uint32_t addr = sV + st * ATT_TILE_BYTES + k * 2048;
-          const uint64_t bd = v_desc_mode == 0 ? umma_desc_sw128(addr, ATT_HALF_BYTES, 1024)
-                                               : umma_desc_sw128(addr, 1024, ATT_HALF_BYTES);
+          const uint64_t bd = umma_desc_sw128(addr, ATT_HALF_BYTES, 1024);
           mma_f16_ts(d, p + k * 8, bd, idesc_pv, (j | k) != 0);
         }
       };
@@ -260,7 +267,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     const float inv_l = l > 0.f ? 1.0f / l : 0.f;
     __nv_bfloat16* orow = nullptr;
-    if (srow < Sq) {
+    if (srow < Sq && out.n_peers > 1) {
+      if (srow >= out.split) {
+        const int t2 = srow - out.split;
+        const int owner = t2 / out.rows_per_rank2;
+        orow = out.o2_peers[owner] + (long)b * out.o2_bs + (long)(t2 - owner * out.rows_per_rank2) * out.o2_rs + (long)h * out.o2_hs;
+      } else {
+        const int owner = srow / out.rows_per_rank;
+        orow = out.o_peers[owner] + (long)b * out.o_bs + (long)(srow - owner * out.rows_per_rank) * out.o_rs + (long)h * out.o_hs;
+      }
+      if (out.lse) out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    } else if (srow < Sq) {
       if (out.o2 && srow >= out.split)
         orow = out.o2 + (long)b * out.o2_bs + (long)(srow - out.split) * out.o2_rs + (long)h * out.o2_hs;
       else
@@ -325,7 +342,8 @@ extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, con
                              long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
                              void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
                              long o2_bs, int split, float* lse, int B, int H, int Hkv, int Sq, int Skv,
-                             int D, const int* kv_lens, float scale, int v_desc_mode, int* status,
+                             int D, const int* kv_lens, float scale, int n_peers, int rows_per_rank,
+                             int rows_per_rank2, void* const* o_peers, void* const* o2_peers, int* status,
                              void* stream) {
   using namespace omni;
   if (D != ATT_D || H <= 0 || Hkv <= 0 || (H % Hkv) || B <= 0) return RC_BAD_ARG;
@@ -349,9 +367,20 @@ extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, con
   out.o_bs = o_bs; out.o_rs = o_rs; out.o_hs = o_hs;
   out.o2_bs = o2_bs; out.o2_rs = o2_rs; out.o2_hs = o2_hs;
   out.split = split; out.lse = lse;
+  out.n_peers = 0; out.rows_per_rank = 1; out.rows_per_rank2 = 1;
+  for (int i = 0; i < 16; ++i) { out.o_peers[i] = nullptr; out.o2_peers[i] = nullptr; }
+  if (n_peers > 1) {
+    if (n_peers > 16 || rows_per_rank <= 0 || o_peers == nullptr) return RC_BAD_ARG;
+    if (split < Sq && (rows_per_rank2 <= 0 || o2_peers == nullptr)) return RC_BAD_ARG;
+    out.n_peers = n_peers; out.rows_per_rank = rows_per_rank; out.rows_per_rank2 = rows_per_rank2 > 0 ? rows_per_rank2 : 1;
+    for (int i = 0; i < n_peers; ++i) {
+      out.o_peers[i] = (__nv_bfloat16*)o_peers[i];
+      out.o2_peers[i] = o2_peers ? (__nv_bfloat16*)o2_peers[i] : nullptr;
+    }
+  }
   dim3 grid((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), H, B);
   const float scale_log2 = scale * 1.4426950408889634f;
   attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens,
-                                                                         scale_log2, v_desc_mode, status);
+                                                                         scale_log2, status);
   return (int)cudaGetLastError();
 }

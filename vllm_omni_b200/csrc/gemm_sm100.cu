@@ -41,6 +41,13 @@ struct GemmEpilogue {
   // which lets two GEMMs write the text and image rows of one joint [B, S_txt + S_img, N] buffer
   int c_rows_per_batch;  // 0 = plain row-major output
   long c_batch_stride;
+  // Fused all-to-all (Ulysses head scatter): with scatter_P > 1 the output columns are cut into
+  // groups of scatter_G columns (a multiple of 32); group g belongs to rank g % P and lands in
+  // that rank's buffer peer_out[g % P] at column (g / P) * G + (col % G).  peer_out[] are peer
+  // (NVLink-mapped) or local pointers that already include this rank's row offset.
+  int scatter_P;
+  int scatter_G;
+  __nv_bfloat16* peer_out[16];
 };
 
 template <int BN>
@@ -190,11 +197,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_wait_ld();
         if (row_ok) {
           __nv_bfloat16* out;
+          __nv_bfloat16* cbase = C;
+          int dcol = col0;
+          if (epi.scatter_P > 1) {
+            const int g = col0 / epi.scatter_G;
+            cbase = epi.peer_out[g % epi.scatter_P];
+            dcol = (g / epi.scatter_P) * epi.scatter_G + (col0 - g * epi.scatter_G);
+          }
           if (epi.c_rows_per_batch > 0) {
             const int cb = row / epi.c_rows_per_batch;
-            out = C + (size_t)cb * epi.c_batch_stride + (size_t)(row - cb * epi.c_rows_per_batch) * ldc + col0;
+            out = cbase + (size_t)cb * epi.c_batch_stride + (size_t)(row - cb * epi.c_rows_per_batch) * ldc + dcol;
           } else {
-            out = C + (size_t)row * ldc + col0;
+            out = cbase + (size_t)row * ldc + dcol;
           }
           const __nv_bfloat16* res = epi.residual ? epi.residual + (size_t)row * epi.ldr + col0 : nullptr;
 #pragma unroll
@@ -308,8 +322,8 @@ static int pick_bn(int M, int N, int ctas) {
 extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
                               int M, int N, int K, const void* bias, const void* residual, int ldr,
                               const void* gate, int gate_stride, int rows_per_batch, int act,
-                              int c_rows_per_batch, long c_batch_stride, int force_bn, int* status,
-                              void* stream) {
+                              int c_rows_per_batch, long c_batch_stride, int scatter_P, int scatter_G,
+                              void* const* peer_out, int force_bn, int* status, void* stream) {
   using namespace omni;
   if (M <= 0 || N <= 0 || K <= 0) return RC_OK;
   if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7) || (ldr & 7) || (gate_stride & 7))
@@ -330,6 +344,15 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
   epi.c_rows_per_batch = c_rows_per_batch;
   epi.c_batch_stride = c_batch_stride;
   if (c_rows_per_batch > 0 && (c_batch_stride & 7)) return RC_BAD_ARG;
+  epi.scatter_P = 0;
+  epi.scatter_G = 0;
+  for (int i = 0; i < 16; ++i) epi.peer_out[i] = nullptr;
+  if (scatter_P > 1) {
+    if (scatter_P > 16 || scatter_G <= 0 || (scatter_G & 31) || peer_out == nullptr || (N % scatter_G)) return RC_BAD_ARG;
+    epi.scatter_P = scatter_P;
+    epi.scatter_G = scatter_G;
+    for (int i = 0; i < scatter_P; ++i) epi.peer_out[i] = static_cast<__nv_bfloat16*>(peer_out[i]);
+  }
   const int ctas = sm_count();
   const int bn = force_bn ? force_bn : pick_bn(M, N, ctas);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -1,0 +1,115 @@
+// Peer-memory runtime for the fused compute+collective kernels.
+//
+// One process per GPU.  Every rank allocates an arena with cudaMalloc, exports it as a CUDA
+// IPC handle, and maps the arenas of all peers of its group, so that kernels can store to /
+// load from a peer's memory over NVLink with ordinary global accesses.  (The reference has no
+// counterpart: it moves everything through NCCL calls between kernels,
+// vllm_omni/diffusion/distributed/comm.py.)
+//
+// Synchronisation is a flag page per rank: flag[j] on rank i is written only by rank j and
+// holds the number of barriers rank j has entered.  omni_peer_barrier:
+//   1. __threadfence_system(): this rank's earlier stores (peer stores included) are ordered
+//      before the flag stores,
+//   2. bumps a device-resident epoch counter (so the same launch can be replayed from a CUDA
+//      graph) and stores the new epoch into flag[my_rank] of every peer (st.release.sys),
+//   3. spins (ld.acquire.sys) until every peer's flag in the local page reaches the epoch.
+// The spin is bounded: after `timeout_ns` the kernel writes ERR_WAIT_PEER to the status word
+// and returns, leaving the context usable; the host turns that into an exception.
+#include "host_util.h"
+#include "ptx_sm100.cuh"
+
+namespace omni {
+
+constexpr int MAX_PEERS = 16;
+
+struct PeerPtrs {
+  unsigned long long* flags[MAX_PEERS];  // flag page of every rank (index = rank in group)
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void peer_barrier_kernel(PeerPtrs peers, int rank, int world, unsigned long long* epoch_counter,
+                                    unsigned long long timeout_ns, int* status) {
+  __shared__ unsigned long long s_epoch;
+  __threadfence_system();
+  if (threadIdx.x == 0) {
+    s_epoch = *epoch_counter + 1;
+    *epoch_counter = s_epoch;
+  }
+  __syncthreads();
+  const unsigned long long epoch = s_epoch;
+  const int j = threadIdx.x;
+  if (j < world && j != rank) {
+    st_release_sys(peers.flags[j] + rank, epoch);
+    const unsigned long long* mine = peers.flags[rank] + j;
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned it = 0;
+    while (ld_acquire_sys(mine) < epoch) {
+      if ((++it & 0x3f) == 0 && globaltimer_ns() - t0 > timeout_ns) {
+        if (status) atomicCAS(status, 0, ERR_WAIT_PEER);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  __threadfence_system();
+}
+
+}  // namespace omni
+
+using namespace omni;
+
+extern "C" int omni_peer_alloc(size_t bytes, void** out) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) return (int)e;
+  *out = p;
+  return 0;
+}
+
+extern "C" int omni_peer_free(void* p) { return (int)cudaFree(p); }
+
+// handle: 64 bytes
+extern "C" int omni_peer_export(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+
+extern "C" int omni_peer_open(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return (int)e;
+  *out = p;
+  return 0;
+}
+
+extern "C" int omni_peer_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+
+extern "C" int omni_ipc_handle_size(void) { return (int)sizeof(cudaIpcMemHandle_t); }
+
+// flag_pages: `world` device pointers (this rank's own page at index `rank`), each at least
+// `world` u64 entries; epoch_counter: a device u64 owned by this rank.
+extern "C" int omni_peer_barrier(void* const* flag_pages, int rank, int world, void* epoch_counter,
+                                 unsigned long long timeout_ns, int* status, void* stream) {
+  if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world) return RC_BAD_ARG;
+  if (world == 1) return RC_OK;
+  PeerPtrs pp;
+  for (int i = 0; i < MAX_PEERS; ++i) pp.flags[i] = i < world ? (unsigned long long*)flag_pages[i] : nullptr;
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pp, rank, world, (unsigned long long*)epoch_counter,
+                                                          timeout_ns, status);
+  return (int)cudaGetLastError();
+}

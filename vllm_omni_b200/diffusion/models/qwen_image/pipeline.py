@@ -142,6 +142,19 @@ class QwenImagePipeline(nn.Module):
         else:
             enc, lens, nb = prompt_embeds.to(dt_model), prompt_mask.sum(1).tolist(), B
         use_graph = not self.od_config.enforce_eager
+        full_latents = latents
+        sp = self.transformer.sp
+        if sp is not None:
+            # sequence parallel: this rank keeps S/P image rows and L/P text rows for the whole loop
+            P, r = sp.P, sp.rank
+            S = latents.shape[1]
+            if S % P:
+                raise ValueError(f"image tokens ({S}) must be divisible by the sequence-parallel degree ({P})")
+            Lp = (enc.shape[1] + P - 1) // P * P
+            if Lp != enc.shape[1]:
+                enc = torch.nn.functional.pad(enc, (0, 0, 0, Lp - enc.shape[1]))
+            enc = enc[:, r * (Lp // P):(r + 1) * (Lp // P)].contiguous()
+            latents = latents[:, r * (S // P):(r + 1) * (S // P)].contiguous()
         st = self._loop_state(enc, lens, img_shape, latents.shape[1], len(timesteps), use_graph)
         lat_in = st.lat_in
         lat_in[:B].copy_(latents)
@@ -159,6 +172,10 @@ class QwenImagePipeline(nn.Module):
                 fused.cfg_euler_step_(v, None, latents, 1.0, dt, False, lat_in)
             if step_callback is not None:
                 step_callback(i, latents)
+        if sp is not None:
+            parts = sp.group.all_gather(latents, dim=1)       # once per image, before the VAE
+            full_latents.copy_(parts)
+            latents = full_latents
         return latents
 
     def _loop_state(self, enc, lens, img_shape, S_img, n_steps, use_graph):

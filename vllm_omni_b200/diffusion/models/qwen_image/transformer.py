@@ -177,7 +177,8 @@ class QwenImageTransformer2DModel(nn.Module):
                                     device=device)
         self.rope = QwenEmbedRope(cfg.rope_theta, cfg.axes_dims_rope, scale_rope=True)
         self._ws = _Workspace()
-        self.attn_impl = attention          # replaced by the sequence-parallel strategies
+        self.attn_impl = attention
+        self.sp = None                      # UlyssesJointAttention when sequence parallel
         self.block_hook = None              # cache backends (TeaCache / DBCache) wrap the block loop
 
     # ------------------------------------------------------------------ workspace
@@ -201,21 +202,31 @@ class QwenImageTransformer2DModel(nn.Module):
         blk = self.blocks[i]
         B, S_img, S_txt = img.shape[0], img.shape[1], txt.shape[1]
         S = S_img + S_txt
-        qkv = ws["qkv"]
         m = mods[:, i]                       # [B, 2, 6D]
-        for sidx, (sp, x, xn, rows, off) in enumerate(((blk.img, img, ws["img_n"], S_img, 0),
-                                                       (blk.txt, txt, ws["txt_n"], S_txt, S_img))):
+        for sidx, (x, xn) in enumerate(((img, ws["img_n"]), (txt, ws["txt_n"]))):
             mm = m[:, sidx]                  # [B, 6D], row stride L*2*6D
             fused.norm_modulate(x, shift=mm[:, 0:D], scale=mm[:, D:2 * D], eps=cfg.eps, out=xn)
-            sp.to_qkv(xn, out=qkv[:, off:off + rows], out_rows_per_batch=rows, out_batch_stride=S * 3 * D)
-        fused.qk_norm_rope_(qkv, H, H, Hd, wq=blk.img.norm_q, wk=blk.img.norm_k, wq_alt=blk.txt.norm_q,
-                            wk_alt=blk.txt.norm_k, s_alt=S_img, cos=cos, sin=sin, interleaved=True, eps=cfg.eps)
-        q5 = qkv.view(B, S, 3, H, Hd)
-        self.attn_impl(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], kv_lens=kv_lens,
-                       out=ws["attn_img"].view(B, S_img, H, Hd), out2=ws["attn_txt"].view(B, S_txt, H, Hd),
-                       split=S_img)
-        for sidx, (sp, x, xn, att, hbuf) in enumerate(((blk.img, img, ws["img_n"], ws["attn_img"], ws["mlp_img"]),
-                                                       (blk.txt, txt, ws["txt_n"], ws["attn_txt"], ws["mlp_txt"]))):
+        if self.sp is not None:
+            # sequence parallel: img/txt hold this rank's rows; the exchange happens in the
+            # GEMM / attention epilogues (fused) or in all-to-all calls (nccl baseline)
+            self.sp.project_qkv(blk.img.to_qkv, ws["img_n"], blk.txt.to_qkv, ws["txt_n"])
+            self.sp.norm_rope(blk.img.norm_q, blk.img.norm_k, blk.txt.norm_q, blk.txt.norm_k, cos, sin, cfg.eps)
+            attn_img, attn_txt = self.sp.attend(kv_lens, ws)
+        else:
+            qkv = ws["qkv"]
+            for sp, xn, rows, off in ((blk.img, ws["img_n"], S_img, 0), (blk.txt, ws["txt_n"], S_txt, S_img)):
+                sp.to_qkv(xn, out=qkv[:, off:off + rows], out_rows_per_batch=rows, out_batch_stride=S * 3 * D)
+            fused.qk_norm_rope_(qkv, H, H, Hd, wq=blk.img.norm_q, wk=blk.img.norm_k, wq_alt=blk.txt.norm_q,
+                                wk_alt=blk.txt.norm_k, s_alt=S_img, cos=cos, sin=sin, interleaved=True, eps=cfg.eps)
+            q5 = qkv.view(B, S, 3, H, Hd)
+            self.attn_impl(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], kv_lens=kv_lens,
+                           out=ws["attn_img"].view(B, S_img, H, Hd), out2=ws["attn_txt"].view(B, S_txt, H, Hd),
+                           split=S_img)
+            attn_img, attn_txt = ws["attn_img"], ws["attn_txt"]
+        for sidx, (sp, x, xn, att, hbuf) in enumerate(((blk.img, img, ws["img_n"], attn_img, ws["mlp_img"]),
+                                                       (blk.txt, txt, ws["txt_n"], attn_txt, ws["mlp_txt"]))):
+            if x.shape[1] == 0:
+                continue
             mm = m[:, sidx]
             sp.to_out(att, residual=x, gate=mm[:, 2 * D:3 * D], out=x)
             fused.norm_modulate(x, shift=mm[:, 3 * D:4 * D], scale=mm[:, 4 * D:5 * D], eps=cfg.eps, out=xn)
@@ -245,10 +256,13 @@ class QwenImageTransformer2DModel(nn.Module):
         while isinstance(img_shapes[0], (list, tuple)):   # accept (f,h,w), [(f,h,w)], [[(f,h,w)]]
             img_shapes = img_shapes[0]
         frame, height, width = img_shapes
-        cos, sin = self.rope.cos_sin(frame, height, width, S_txt, dev)
+        P = self.sp.P if self.sp is not None else 1      # under SP the inputs are this rank's rows
+        cos, sin = self.rope.cos_sin(frame, height, width, S_txt * P, dev)
         kv_lens = None
-        if txt_seq_lens is not None and any(int(l) != S_txt for l in txt_seq_lens):
-            kv_lens = torch.tensor([S_img + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
+        if txt_seq_lens is not None and any(int(l) != S_txt * P for l in txt_seq_lens):
+            kv_lens = torch.tensor([S_img * P + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
+        if self.sp is not None:
+            self.sp.setup(B, S_img, S_txt, dev, self.dtype_)
         img, txt, temb, mods = self.embed(hidden_states, encoder_hidden_states, timestep)
         ws = self._workspace(B, S_img, S_txt, dev)
         run_blocks = self._run_blocks
@@ -277,10 +291,13 @@ class QwenImageTransformer2DModel(nn.Module):
         frame, height, width = img_shapes
         st = DenoiseLoopState()
         st.B, st.S_img, st.S_txt = B, S_img, S_txt
-        st.cos, st.sin = self.rope.cos_sin(frame, height, width, S_txt, dev)
+        P = self.sp.P if self.sp is not None else 1      # under SP: S_img / S_txt are this rank's rows
+        st.cos, st.sin = self.rope.cos_sin(frame, height, width, S_txt * P, dev)
         st.kv_lens = None
-        if txt_seq_lens is not None and any(int(l) != S_txt for l in txt_seq_lens):
-            st.kv_lens = torch.tensor([S_img + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
+        if txt_seq_lens is not None and any(int(l) != S_txt * P for l in txt_seq_lens):
+            st.kv_lens = torch.tensor([S_img * P + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
+        if self.sp is not None:
+            self.sp.setup(B, S_img, S_txt, dev, self.dtype_)
         txt = fused.norm_modulate(encoder_hidden_states.to(self.dtype_), weight=self.txt_norm_weight, rms=True,
                                   eps=cfg.eps)
         st.txt0 = self.txt_in(txt)

@@ -37,10 +37,15 @@ def attention_reference(q, k, v, scale=None, kv_lens=None, return_lse=False):
 
 
 def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, return_lse=False,
-              _v_desc_mode=0):
+              scatter=None):
     """Non-causal attention.  Returns ``out`` ([B, Sq, H, D], or the given buffer).
 
     ``out2``/``split``: rows >= split of every batch go to ``out2`` (row index s - split).
+
+    ``scatter = dict(n_peers, rows_per_rank, rows_per_rank2, o_ptrs, o2_ptrs, o_strides, o2_strides)``:
+    fused reverse all-to-all; row s < split is stored on rank s // rows_per_rank through the device
+    pointer ``o_ptrs[rank]`` (strides = (row, head, batch) in elements), rows >= split likewise with
+    the ``*2`` entries.  ``out`` / ``out2`` are then unused.
     """
     B, Sq, H, D = q.shape
     Skv, Hkv = k.shape[1], k.shape[2]
@@ -59,21 +64,33 @@ def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, r
     assert q.dtype == torch.bfloat16 and D == 128, "tcgen05 attention path: bf16, head_dim 128"
     for t in (q, k, v):
         assert t.stride(3) == 1
-    if out is None:
-        out = torch.empty(B, Sq, H, D, dtype=q.dtype, device=q.device)
-    assert out.stride(3) == 1 and (out2 is None or out2.stride(3) == 1)
+    sc = scatter
+    if sc is not None:
+        os_, o2s = sc["o_strides"], sc.get("o2_strides") or (0, 0, 0)
+        op = (ctypes.c_void_p * sc["n_peers"])(*sc["o_ptrs"])
+        o2p = (ctypes.c_void_p * sc["n_peers"])(*sc["o2_ptrs"]) if sc.get("o2_ptrs") else None
+        out_ptr, out2_ptr = ctypes.c_void_p(sc["o_ptrs"][0]), ctypes.c_void_p(sc["o2_ptrs"][0] if o2p else 0)
+        split = sc.get("split", split)
+    else:
+        if out is None:
+            out = torch.empty(B, Sq, H, D, dtype=q.dtype, device=q.device)
+        assert out.stride(3) == 1 and (out2 is None or out2.stride(3) == 1)
+        os_ = (out.stride(1), out.stride(2), out.stride(0))
+        o2s = (out2.stride(1), out2.stride(2), out2.stride(0)) if out2 is not None else (0, 0, 0)
+        op = o2p = None
+        out_ptr, out2_ptr = nv.ptr(out), nv.ptr(out2)
     lse = torch.empty(B, H, Sq, dtype=torch.float32, device=q.device) if return_lse else None
     if kv_lens is not None:
         assert kv_lens.dtype == torch.int32 and kv_lens.is_cuda
-    o2s = (out2.stride(1), out2.stride(2), out2.stride(0)) if out2 is not None else (0, 0, 0)
     st = nv.status_word(q.device)
     rc = nv.lib("attention_sm100").omni_attn_fwd(
         nv.ptr(q), c_long(q.stride(1)), c_long(q.stride(2)), c_long(q.stride(0)),
         nv.ptr(k), c_long(k.stride(1)), c_long(k.stride(2)), c_long(k.stride(0)),
         nv.ptr(v), c_long(v.stride(1)), c_long(v.stride(2)), c_long(v.stride(0)),
-        nv.ptr(out), c_long(out.stride(1)), c_long(out.stride(2)), c_long(out.stride(0)),
-        nv.ptr(out2), c_long(o2s[0]), c_long(o2s[1]), c_long(o2s[2]), c_int(split),
+        out_ptr, c_long(os_[0]), c_long(os_[1]), c_long(os_[2]),
+        out2_ptr, c_long(o2s[0]), c_long(o2s[1]), c_long(o2s[2]), c_int(split),
         nv.ptr(lse), c_int(B), c_int(H), c_int(Hkv), c_int(Sq), c_int(Skv), c_int(D), nv.ptr(kv_lens),
-        c_float(scale), c_int(_v_desc_mode), nv.ptr(st), nv.stream_ptr())
+        c_float(scale), c_int(sc["n_peers"] if sc else 0), c_int(sc["rows_per_rank"] if sc else 0),
+        c_int(sc.get("rows_per_rank2", 0) if sc else 0), op, o2p, nv.ptr(st), nv.stream_ptr())
     nv.check_rc(rc, "omni_attn_fwd")
     return (out, lse) if return_lse else out

@@ -153,8 +153,12 @@ def cfg_euler_step_reference(pos, neg, lat, guidance, dt, renorm):
     return lat + dt * v
 
 
-def cfg_euler_step_(pos, neg, lat, guidance: float, dt: float, renorm: bool = False, lat_lowp=None):
-    """lat (fp32, in place) += dt * guided velocity; optional bf16 copy in ``lat_lowp``."""
+def cfg_euler_step_(pos, neg, lat, guidance: float, dt: float, renorm: bool = False, lat_lowp=None,
+                    pos_ptr: int | None = None, neg_ptr: int | None = None):
+    """lat (fp32, in place) += dt * guided velocity; optional bf16 copy in ``lat_lowp``.
+
+    ``pos_ptr`` / ``neg_ptr``: raw device pointers (bf16, same shape as ``lat``) used instead of
+    the tensors; a pointer into a peer GPU's memory makes this the fused CFG exchange."""
     if not lat.is_cuda:
         lat.copy_(cfg_euler_step_reference(pos, neg, lat, guidance, dt, renorm))
         if lat_lowp is not None:
@@ -162,10 +166,14 @@ def cfg_euler_step_(pos, neg, lat, guidance: float, dt: float, renorm: bool = Fa
         return lat
     C = lat.shape[-1]
     rows = lat.numel() // C
-    assert lat.dtype == torch.float32 and lat.is_contiguous() and pos.is_contiguous() and pos.dtype == torch.bfloat16
-    assert neg is None or (neg.is_contiguous() and neg.dtype == torch.bfloat16)
+    assert lat.dtype == torch.float32 and lat.is_contiguous()
+    if pos_ptr is None:
+        assert pos.is_contiguous() and pos.dtype == torch.bfloat16
+        assert neg is None or (neg.is_contiguous() and neg.dtype == torch.bfloat16)
+    p_arg = nv.ptr(pos) if pos_ptr is None else ctypes.c_void_p(pos_ptr)
+    n_arg = nv.ptr(neg) if neg_ptr is None else ctypes.c_void_p(neg_ptr)
     rc = nv.lib("elementwise").omni_cfg_euler_step(
-        nv.ptr(pos), nv.ptr(neg), nv.ptr(lat), nv.ptr(lat_lowp), c_long(rows), c_int(C), c_float(guidance),
+        p_arg, n_arg, nv.ptr(lat), nv.ptr(lat_lowp), c_long(rows), c_int(C), c_float(guidance),
         c_float(dt), c_int(1 if renorm else 0), nv.stream_ptr())
     nv.check_rc(rc, "omni_cfg_euler_step")
     return lat

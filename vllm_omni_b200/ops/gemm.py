@@ -39,12 +39,16 @@ def linear_reference(x, w, bias=None, act=None, residual=None, gate=None):
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
            residual: torch.Tensor | None = None, gate: torch.Tensor | None = None,
            out: torch.Tensor | None = None, force_bn: int = 0,
-           out_rows_per_batch: int = 0, out_batch_stride: int = 0) -> torch.Tensor:
+           out_rows_per_batch: int = 0, out_batch_stride: int = 0, scatter=None) -> torch.Tensor:
     """y = residual + gate * act(x @ w.T + bias).
 
     ``out_rows_per_batch`` / ``out_batch_stride`` (elements): row r of the result is stored at
     ``out + (r // rpb) * batch_stride + (r % rpb) * out.stride(-2)``; used to write one stream's
     rows into a joint [B, S_txt + S_img, N] buffer (pass ``out`` as the [B, S_x, N] slice).
+
+    ``scatter = (P, G, ptrs, ld)``: fused all-to-all epilogue.  Column group g (G columns) goes to
+    rank g % P, into the buffer at device pointer ``ptrs[g % P]`` (row pitch ``ld`` elements) at
+    column (g // P) * G + col % G.  ``out`` is ignored (pass None).
 
     x: [..., K] bf16 (last dim contiguous), w: [N, K] bf16, bias: [N], residual: [..., N]
     (may be ``out``), gate: [B, N] view (last dim contiguous, any row stride) where the rows
@@ -65,9 +69,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
     M = x2.shape[0]
     if w.stride(-1) != 1:
         w = w.contiguous()
-    if out is None:
+    sc_P, sc_G, sc_arr = 0, 0, None
+    if scatter is not None:
+        sc_P, sc_G, ptrs, ldc = scatter
+        sc_arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        out = x                      # placeholder object; the kernel writes through the peer pointers
+    elif out is None:
         out = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
-    if out_rows_per_batch:
+    if scatter is not None:
+        pass
+    elif out_rows_per_batch:
         assert out.stride(-1) == 1
         ldc = out.stride(-2)
     else:
@@ -92,6 +103,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
         nv.ptr(out), ctypes.c_int(ldc), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
         nv.ptr(bias), nv.ptr(res2), ctypes.c_int(ldr), nv.ptr(gate), ctypes.c_int(gs), ctypes.c_int(rpb),
         ctypes.c_int(ACT[act]), ctypes.c_int(out_rows_per_batch), ctypes.c_long(out_batch_stride),
-        ctypes.c_int(force_bn), nv.ptr(st), nv.stream_ptr())
+        ctypes.c_int(sc_P), ctypes.c_int(sc_G), sc_arr, ctypes.c_int(force_bn), nv.ptr(st), nv.stream_ptr())
     nv.check_rc(rc, "omni_gemm_bf16")
-    return out
+    return None if scatter is not None else out

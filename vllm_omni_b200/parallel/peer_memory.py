@@ -1,0 +1,123 @@
+"""Symmetric peer-memory arenas for the fused compute+collective kernels.
+
+Every rank of a group allocates an arena of the same size (``cudaMalloc`` in
+csrc/peer_rt.cu), exports it as a CUDA IPC handle, and maps all peers' arenas, which makes a
+peer's memory addressable by ordinary loads and stores inside our kernels (NVLink / NVSwitch
+P2P).  Tensors are carved from the arena with a bump allocator, in the same order on every
+rank, so the i-th allocation sits at the same offset everywhere ("symmetric").  A flag page
+plus a device-resident epoch counter implement the bounded-wait barrier.
+
+The reference has no such layer: all of its cross-GPU traffic is NCCL calls issued between
+kernels (vllm_omni/diffusion/distributed/group_coordinator.py).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import _native as nv
+
+_ALIGN = 1024
+
+
+class _DevMem:
+    """Exposes a raw device pointer to torch through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int, owner=None):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+        self._owner = owner
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device: torch.device, owner=None) -> torch.Tensor:
+    n = 1
+    for s in shape:
+        n *= int(s)
+    nbytes = n * torch.empty(0, dtype=dtype).element_size()
+    raw = torch.as_tensor(_DevMem(ptr, max(nbytes, 1), owner), device=device)
+    return raw[:nbytes].view(dtype).view(*shape)
+
+
+class SymTensor:
+    """A symmetric allocation: the local tensor and the device pointer of its twin on every rank."""
+
+    def __init__(self, local: torch.Tensor, ptrs: list[int], offset: int):
+        self.local = local
+        self.ptrs = ptrs          # index = rank in group; ptrs[my_rank] == local.data_ptr()
+        self.offset = offset
+
+    def peer_ptrs(self, byte_offset: int = 0) -> list[int]:
+        return [p + byte_offset for p in self.ptrs]
+
+
+class PeerArena:
+    def __init__(self, group, nbytes: int, device: torch.device | None = None, timeout_ms: int = 1000):
+        """``group``: a GroupCoordinator (uses its CPU twin to exchange IPC handles)."""
+        self.group = group
+        self.rank, self.world = group.rank_in_group, group.world_size
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.timeout_ns = int(timeout_ms) * 1_000_000
+        self._lib = nv.lib("peer_rt")
+        self._flag_bytes = _ALIGN                      # world u64 flags + the epoch counter
+        total = self.nbytes + self._flag_bytes
+        base = ctypes.c_void_p()
+        nv.check_rc(self._lib.omni_peer_alloc(ctypes.c_size_t(total), ctypes.byref(base)), "omni_peer_alloc")
+        self._base = base.value
+        hsz = self._lib.omni_ipc_handle_size()
+        handle = (ctypes.c_ubyte * hsz)()
+        nv.check_rc(self._lib.omni_peer_export(ctypes.c_void_p(self._base), handle), "omni_peer_export")
+        handles = group.all_gather_object(bytes(handle))
+        self.bases: list[int] = []
+        self._opened: list[int] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.bases.append(self._base)
+                continue
+            buf = (ctypes.c_ubyte * hsz).from_buffer_copy(h)
+            p = ctypes.c_void_p()
+            nv.check_rc(self._lib.omni_peer_open(buf, ctypes.byref(p)), "omni_peer_open")
+            self.bases.append(p.value)
+            self._opened.append(p.value)
+        # flag page sits at the start of every arena; the epoch counter after the flags
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*self.bases)
+        self._epoch_ptr = self._base + 8 * 16
+        self._bump = self._flag_bytes
+        self._closed = False
+        group.barrier()
+
+    def alloc(self, shape, dtype=torch.bfloat16) -> SymTensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty(0, dtype=dtype).element_size()
+        off = self._bump
+        if off + nbytes > self.nbytes + self._flag_bytes:
+            raise MemoryError(f"peer arena exhausted: need {nbytes} B at offset {off}, arena {self.nbytes} B")
+        self._bump = (off + nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
+        local = tensor_from_ptr(self._base + off, shape, dtype, self.device, owner=self)
+        return SymTensor(local, [b + off for b in self.bases], off)
+
+    def barrier(self) -> None:
+        """Device-side barrier over the group on the current stream (bounded wait)."""
+        if self.world == 1:
+            return
+        st = nv.status_word(self.device)
+        rc = self._lib.omni_peer_barrier(self._flag_ptrs, ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                         ctypes.c_void_p(self._epoch_ptr), ctypes.c_ulonglong(self.timeout_ns),
+                                         nv.ptr(st), nv.stream_ptr())
+        nv.check_rc(rc, "omni_peer_barrier")
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        torch.cuda.synchronize(self.device)
+        try:
+            self.group.barrier()
+        except Exception:
+            pass
+        for p in self._opened:
+            self._lib.omni_peer_close(ctypes.c_void_p(p))
+        self._lib.omni_peer_free(ctypes.c_void_p(self._base))

@@ -1,0 +1,119 @@
+"""Ulysses sequence parallelism for joint (image + text) attention.
+
+Each rank owns S_img/P image rows and S_txt/P text rows of every sample (text is sharded
+like the image; the reference keeps it replicated and head-sliced,
+vllm_omni/diffusion/attention/parallel/ulysses.py:61-238, which costs P-fold redundant text
+compute).  Attention needs every row but only H/P heads per rank, i.e. a head<->sequence
+all-to-all before and after.
+
+``mode="fused"`` (GPU): no collective calls and no layout copies.
+  * the QKV GEMM epilogue stores each head group straight into its owner rank's joint
+    ``[B, S_img+S_txt, 3, H/P, Dh]`` buffer over NVLink (csrc/gemm_sm100.cu scatter epilogue);
+  * the attention epilogue stores each output row straight into the owner rank's
+    ``[B, S_loc, H, Dh]`` buffer at this rank's head offset (csrc/attention_sm100.cu);
+  * two bounded-wait device barriers per block order the exchanges (csrc/peer_rt.cu).
+``mode="nccl"``: the same data movement with ``all_to_all_single`` + permutes — the baseline
+the fused path is measured against, and the path CPU (Gloo) tests run.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import fused
+from ..ops.attention import attention
+from .comm import all_to_all_4d, all_to_all_5d
+
+
+class UlyssesJointAttention:
+    def __init__(self, group, num_heads: int, head_dim: int, mode: str | None = None):
+        self.group = group
+        self.P, self.rank = group.world_size, group.rank_in_group
+        if num_heads % self.P:
+            raise ValueError(f"num_heads ({num_heads}) must be divisible by the Ulysses degree ({self.P})")
+        self.H, self.Dh, self.Hp = num_heads, head_dim, num_heads // self.P
+        self.mode = mode or ("fused" if torch.cuda.is_available() else "nccl")
+        self.arena = None
+        self._key = None
+
+    # ------------------------------------------------------------------ buffers
+    def setup(self, B: int, Si_loc: int, St_loc: int, device, dtype):
+        key = (B, Si_loc, St_loc, str(device), dtype)
+        if self._key == key:
+            return
+        self._key = key
+        self.B, self.Si_loc, self.St_loc = B, Si_loc, St_loc
+        self.S_img, self.S_txt = Si_loc * self.P, St_loc * self.P
+        self.S_tot = self.S_img + self.S_txt
+        G = self.Hp * self.Dh
+        if self.mode == "fused":
+            from .peer_memory import PeerArena
+            if self.arena is not None:
+                self.arena.close()
+            es = torch.empty(0, dtype=dtype).element_size()
+            need = (B * self.S_tot * 3 * G + B * (Si_loc + St_loc) * self.H * self.Dh) * es + 8192
+            self.arena = PeerArena(self.group, need, device)
+            self.joint = self.arena.alloc((B, self.S_tot, 3 * G), dtype)
+            self.attn_img = self.arena.alloc((B, Si_loc, self.H * self.Dh), dtype)
+            self.attn_txt = self.arena.alloc((B, St_loc, self.H * self.Dh), dtype)
+            ld = 3 * G
+            self._img_scatter = (self.P, G, self.joint.peer_ptrs(self.rank * Si_loc * ld * es), ld)
+            self._txt_scatter = (self.P, G, self.joint.peer_ptrs((self.S_img + self.rank * St_loc) * ld * es), ld)
+            hoff = self.rank * G * es
+            HD = self.H * self.Dh
+            self._attn_scatter = dict(n_peers=self.P, rows_per_rank=Si_loc, rows_per_rank2=max(St_loc, 1),
+                                      split=self.S_img, o_ptrs=self.attn_img.peer_ptrs(hoff),
+                                      o2_ptrs=self.attn_txt.peer_ptrs(hoff), o_strides=(HD, self.Dh, Si_loc * HD),
+                                      o2_strides=(HD, self.Dh, St_loc * HD))
+            self.joint_local = self.joint.local
+        else:
+            e = lambda *s: torch.empty(*s, dtype=dtype, device=device)
+            self.joint_local = e(B, self.S_tot, 3 * G)
+            self.qkv_img = e(B, Si_loc, 3 * self.H * self.Dh)
+            self.qkv_txt = e(B, St_loc, 3 * self.H * self.Dh)
+
+    # ------------------------------------------------------------------ per block
+    def project_qkv(self, img_lin, xn_img, txt_lin, xn_txt):
+        """QKV projections of the local rows; afterwards ``joint_local`` holds q,k,v of ALL rows
+        for this rank's heads."""
+        G, B = self.Hp * self.Dh, self.B
+        if self.mode == "fused":
+            bs = self.S_tot * 3 * G
+            img_lin(xn_img, scatter=self._img_scatter, out_rows_per_batch=self.Si_loc, out_batch_stride=bs)
+            if self.St_loc:
+                txt_lin(xn_txt, scatter=self._txt_scatter, out_rows_per_batch=self.St_loc, out_batch_stride=bs)
+            self.arena.barrier()
+            return
+        grp = self.group.device_group
+        img_lin(xn_img, out=self.qkv_img)
+        q = all_to_all_5d(self.qkv_img.view(B, self.Si_loc, 3, self.H, self.Dh), 3, 1, grp)
+        self.joint_local[:, :self.S_img].copy_(q.reshape(B, self.S_img, 3 * G))
+        if self.St_loc:
+            txt_lin(xn_txt, out=self.qkv_txt)
+            t = all_to_all_5d(self.qkv_txt.view(B, self.St_loc, 3, self.H, self.Dh), 3, 1, grp)
+            self.joint_local[:, self.S_img:].copy_(t.reshape(B, self.S_txt, 3 * G))
+
+    def norm_rope(self, wq, wk, wq_txt, wk_txt, cos, sin, eps):
+        fused.qk_norm_rope_(self.joint_local, self.Hp, self.Hp, self.Dh, wq=wq, wk=wk, wq_alt=wq_txt, wk_alt=wk_txt,
+                            s_alt=self.S_img, cos=cos, sin=sin, interleaved=True, eps=eps)
+
+    def attend(self, kv_lens, ws):
+        """Joint attention over this rank's heads; returns (attn_img [B,Si_loc,H*Dh],
+        attn_txt [B,St_loc,H*Dh]) holding ALL heads of the local rows."""
+        B = self.B
+        q5 = self.joint_local.view(B, self.S_tot, 3, self.Hp, self.Dh)
+        if self.mode == "fused":
+            attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], kv_lens=kv_lens, scatter=self._attn_scatter)
+            self.arena.barrier()
+            return self.attn_img.local, self.attn_txt.local
+        o = attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], kv_lens=kv_lens)     # [B, S_tot, Hp, Dh]
+        grp = self.group.device_group
+        oi = all_to_all_4d(o[:, :self.S_img].contiguous(), 1, 2, grp).reshape(B, self.Si_loc, self.H * self.Dh)
+        ot = None
+        if self.St_loc:
+            ot = all_to_all_4d(o[:, self.S_img:].contiguous(), 1, 2, grp).reshape(B, self.St_loc, self.H * self.Dh)
+        return oi, ot
+
+    def close(self):
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None
