@@ -136,3 +136,48 @@ def test_cfg_euler_and_rel_l1(dev):
     rel = float(fused.rel_l1_reference(a, b))
     got = st.state.tolist()
     assert abs(got[1] - rel) < 1e-3 * rel and abs(got[0] - (2.0 * rel + 0.5)) < 1e-3 and got[2] == 1.0
+
+
+@pytest.mark.parametrize("Sq,Skv,off", [(300, 300, 0), (128, 700, 572), (513, 513, 0), (40, 1000, 960)])
+def test_attention_causal(dev, Sq, Skv, off):
+    from vllm_omni_b200.ops import attention as A
+    torch.manual_seed(8)
+    q = torch.randn(1, Sq, 8, 128, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(1, Skv, 2, 128, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(1, Skv, 2, 128, device=dev, dtype=torch.bfloat16)
+    o = A.attention(q, k, v, causal=True, q_offset=off)
+    ref = A.attention_reference(q, k, v, causal=True, q_offset=off)
+    _status_ok(dev)
+    assert (o.float() - ref.float()).abs().max().item() < 0.03
+
+
+@pytest.mark.parametrize("H,Hkv,splits", [(32, 4, 4), (8, 8, 1), (16, 4, 3)])
+def test_paged_decode(dev, H, Hkv, splits):
+    from vllm_omni_b200.ops import kv_cache as KC
+    from vllm_omni_b200.ops import attention as A
+    torch.manual_seed(9)
+    bs, nblk, D = 16, 64, 128
+    lens = [37, 200, 1, 129]
+    kc = torch.zeros(nblk, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    perm = torch.randperm(nblk).tolist()
+    tables, ks, vs = [], [], []
+    for L in lens:
+        nb = (L + bs - 1) // bs
+        ids = [perm.pop() for _ in range(nb)]
+        tables.append(ids)
+        k = torch.randn(L, Hkv, D, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(L, Hkv, D, device=dev, dtype=torch.bfloat16)
+        slots = torch.tensor([ids[t // bs] * bs + t % bs for t in range(L)], dtype=torch.int32, device=dev)
+        KC.kv_write(k, v, kc, vc, slots)
+        ks.append(k); vs.append(v)
+    maxb = max(len(t) for t in tables)
+    bt = torch.tensor([t + [0] * (maxb - len(t)) for t in tables], dtype=torch.int32, device=dev)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    q = torch.randn(len(lens), H, D, device=dev, dtype=torch.bfloat16)
+    out = KC.paged_decode(q, kc, vc, bt, sl, num_splits=splits)
+    for i, L in enumerate(lens):
+        ref = A.attention_reference(q[i:i + 1, None].reshape(1, 1, H, D), ks[i][None], vs[i][None])
+        assert (out[i].float() - ref[0, 0].float()).abs().max().item() < 0.03, i
+        gk, gv = KC.kv_gather(kc, vc, bt[i], L)
+        assert torch.equal(gk, ks[i]) and torch.equal(gv, vs[i])

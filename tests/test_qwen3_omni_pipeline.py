@@ -1,0 +1,86 @@
+"""Three-stage Qwen3-Omni-style pipeline (thinker -> talker -> code2wav) on CPU with the tiny
+geometry: text + audio features in, text tokens and a waveform out, through the Omni API and a
+stage-config YAML."""
+import textwrap
+
+import pytest
+import torch
+
+from vllm_omni_b200.entrypoints.omni import Omni
+from vllm_omni_b200.inputs import SamplingParams
+
+YAML = textwrap.dedent("""
+    async_chunk: false
+    stage_args:
+      - stage_id: 0
+        stage_type: llm
+        runtime: {devices: "0", max_batch_size: 4}
+        engine_args: {model_stage: thinker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
+                      engine_output_type: latent, device: cpu, num_gpu_blocks: 64, max_num_batched_tokens: 64,
+                      model_overrides: {tiny: true}}
+        final_output: true
+        final_output_type: text
+        default_sampling_params: {temperature: 0.0, max_tokens: 5}
+      - stage_id: 1
+        stage_type: llm
+        runtime: {devices: "0", max_batch_size: 4}
+        engine_args: {model_stage: talker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
+                      engine_output_type: latent, device: cpu, num_gpu_blocks: 64, model_overrides: {tiny: true}}
+        engine_input_source: [0]
+        custom_process_input_func: vllm_omni.model_executor.stage_input_processors.qwen3_omni.thinker2talker
+        default_sampling_params: {temperature: 0.0, max_tokens: 7, detokenize: false, stop_token_ids: [66]}
+      - stage_id: 2
+        stage_type: llm
+        runtime: {devices: "0", max_batch_size: 4}
+        engine_args: {model_stage: code2wav, model_arch: Qwen3OmniMoeForConditionalGeneration,
+                      worker_type: generation, engine_output_type: audio, device: cpu, model_overrides: {tiny: true}}
+        engine_input_source: [1]
+        custom_process_input_func: vllm_omni_b200.models.stage_input_processors.qwen3_omni.talker2code2wav
+        final_output: true
+        final_output_type: audio
+    """)
+
+
+@pytest.fixture(scope="module")
+def omni(tmp_path_factory):
+    p = tmp_path_factory.mktemp("cfg") / "tiny_qwen3_omni.yaml"
+    p.write_text(YAML)
+    o = Omni("qwen3-omni-tiny", stage_configs_path=str(p))
+    yield o
+    o.close()
+
+
+def _prompt(n_audio_frames=40):
+    mel = torch.randn(16, n_audio_frames, generator=torch.Generator().manual_seed(0))
+    ids = [506, 10, 11, 500, 12, 507, 506, 13]          # text, one audio placeholder, text
+    return {"prompt_token_ids": ids, "multi_modal_data": {"audio": [mel]}}
+
+
+def test_three_stage_text_and_audio(omni):
+    sps = [s.default_sampling_params() for s in omni.stage_list]
+    outs = omni.generate([_prompt(), _prompt(24)], sps)
+    by_type = {}
+    for o in outs:
+        by_type.setdefault(o.final_output_type, []).append(o)
+    assert len(by_type["text"]) == 2 and len(by_type["audio"]) == 2
+    t = by_type["text"][0]
+    assert t.stage_id == 0 and len(t.outputs[0].token_ids) == 5
+    a = by_type["audio"][0]
+    wav = a.multimodal_output["audio"]
+    # 7 codec frames (or fewer if the stop code came up) x total up-sampling 16
+    assert wav.dim() == 1 and wav.numel() % 16 == 0 and 16 <= wav.numel() <= 7 * 16
+    assert torch.isfinite(wav).all() and wav.abs().max() <= 1.0
+    s = omni.metrics.build_summary()
+    assert s["overall"]["e2e_requests"] >= 2 and len(s["stages"]) >= 6
+
+
+def test_thinker_expands_audio_placeholder(omni):
+    from vllm_omni_b200.entrypoints.stage_runtime import inproc_adapter
+    llm = inproc_adapter(0).llm
+    req = llm.add_request("probe", _prompt(40), SamplingParams(temperature=0.0, max_tokens=1))
+    n_audio = llm.model.audio_tower.output_length(40)
+    assert req.num_prompt_tokens == 7 + n_audio
+    assert req.prompt_embeds.shape == (7 + n_audio, 64)
+    pos = req.runtime_state["mrope_positions"]
+    assert pos.shape == (3, 7 + n_audio) and int(pos[0, -1]) == 7 + n_audio - 1
+    llm.abort_request(["probe"])

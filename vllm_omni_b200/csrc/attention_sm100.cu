@@ -1,6 +1,7 @@
 // K4: flash-attention forward for sm_100a on tcgen05 tensor cores with TMEM accumulators.
 //
-// Non-causal softmax(Q K^T * scale) V over bf16 inputs, head_dim 128, optional per-batch
+// softmax(Q K^T * scale) V over bf16 inputs (non-causal, or causal with a query offset for
+// chunked prefill), head_dim 128, optional per-batch
 // key lengths (padding mask), GQA, optional log-sum-exp output (used by the ring /
 // peer-KV merge).  Replaces the PyTorch SDPA call the reference makes on Blackwell
 // (vllm_omni/diffusion/attention/backends/sdpa.py:82; its FlashAttention backend is gated
@@ -58,7 +59,7 @@ __device__ __forceinline__ float ex2(float x) {
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnOut out, int Sq, int Skv, int H, int Hkv,
-                const int* __restrict__ kv_lens, float scale_log2, int* status) {
+                const int* __restrict__ kv_lens, float scale_log2, int causal, int q_offset, int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
   __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
@@ -74,7 +75,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t sK = smem_base + 2 * ATT_TILE_BYTES;    // 2 stages
   const uint32_t sV = smem_base + 4 * ATT_TILE_BYTES;    // 2 stages
   const int kv_len = kv_lens ? min(kv_lens[b], Skv) : Skv;
-  const int n_kv = (kv_len + ATT_BN - 1) / ATT_BN;
+  // causal: query row s sees keys [0, s + q_offset]; the CTA only visits tiles its last row sees
+  const int kv_cta = causal ? min(kv_len, qblk * 2 * ATT_BM + 2 * ATT_BM + q_offset) : kv_len;
+  const int n_kv = (kv_cta + ATT_BN - 1) / ATT_BN;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -198,7 +201,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int j = 0; j < n_kv; ++j) {
       mbar_wait(smem_u32(&s_full[t]), j & 1, &s_abort, status, ERR_WAIT_FULL);
       tc_fence_after_sync();
-      const int valid = kv_len - j * ATT_BN;  // keys of this tile that exist
+      const int row_limit = causal ? min(kv_len, srow + q_offset + 1) : kv_len;
+      const int valid = row_limit - j * ATT_BN;  // keys of this tile this row may see
       // pass 1: row maximum
       float mx = -INFINITY;
 #pragma unroll 1
@@ -342,7 +346,8 @@ extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, con
                              long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
                              void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
                              long o2_bs, int split, float* lse, int B, int H, int Hkv, int Sq, int Skv,
-                             int D, const int* kv_lens, float scale, int n_peers, int rows_per_rank,
+                             int D, const int* kv_lens, float scale, int causal, int q_offset, int n_peers,
+                             int rows_per_rank,
                              int rows_per_rank2, void* const* o_peers, void* const* o2_peers, int* status,
                              void* stream) {
   using namespace omni;
@@ -381,6 +386,6 @@ extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, con
   dim3 grid((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), H, B);
   const float scale_log2 = scale * 1.4426950408889634f;
   attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens,
-                                                                         scale_log2, status);
+                                                                         scale_log2, causal, q_offset, status);
   return (int)cudaGetLastError();
 }

@@ -78,7 +78,7 @@ template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  __nv_bfloat16* __restrict__ C, int ldc, int M, int N, int K, GemmEpilogue epi,
-                 int* status) {
+                 const int* __restrict__ tile_expert, int* status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
 
@@ -130,13 +130,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         int mb, nb;
         tile_coords(t, num_m, num_n, mb, nb);
+        // grouped (MoE) mode: every 128-row tile belongs to one expert; -1 = padding tile
+        const int ex = tile_expert ? tile_expert[mb] : 0;
+        if (ex < 0) continue;
         for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
           const uint32_t fb = smem_u32(&full_bar[stage]);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           mbar_expect_tx(fb, Cfg::STAGE_BYTES);
           tma_load_2d(sa, &tmA, fb, kb * BK, mb * BM);
-          tma_load_2d(sa + Cfg::A_BYTES, &tmB, fb, kb * BK, nb * BN);
+          tma_load_3d(sa + Cfg::A_BYTES, &tmB, fb, kb * BK, nb * BN, ex);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -150,6 +153,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        if (tile_expert) {
+          int mb, nb;
+          tile_coords(t, num_m, num_n, mb, nb);
+          if (tile_expert[mb] < 0) continue;
+        }
         mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, &s_abort, status, ERR_WAIT_TMEM_EMPTY);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
@@ -182,6 +190,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, num_m, num_n, mb, nb);
+      if (tile_expert && tile_expert[mb] < 0) continue;
       mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, &s_abort, status, ERR_WAIT_TMEM_FULL);
       tc_fence_after_sync();
       const int row = mb * BM + q * 32 + lane;
@@ -275,11 +284,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 template <int BN>
 static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, int ldc, int M,
                        int N, int K, int ldw, const GemmEpilogue& epi, int* status, int max_ctas,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int num_experts = 1, const int* tile_expert = nullptr) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmB;
-  int rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K,
-                        (uint64_t)ldw * 2, BN, BK);
+  // weights as [E, N, K]; a plain linear layer is E = 1
+  int rc = make_tmap_3d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)K, (uint64_t)N,
+                        (uint64_t)num_experts, (uint64_t)ldw * 2, (uint64_t)N * ldw * 2, BK, BN);
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
@@ -290,7 +300,7 @@ static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, 
   }
   const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
-  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, status);
+  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, tile_expert, status);
   return (int)cudaGetLastError();
 }
 
@@ -361,6 +371,34 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
     case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
     case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
     case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
+    default: return RC_BAD_ARG;
+  }
+}
+
+// Grouped (MoE expert) GEMM: A is the expert-major, 128-row-padded activation buffer [M, K];
+// W is [E, N, K] contiguous; tile_expert[m_tile] names the expert of every 128-row tile (-1 =
+// padding, skipped).  C[M, N] = act(A * W[e]^T).
+extern "C" int omni_gemm_bf16_grouped(const void* A, int lda, const void* W, int num_experts, void* C, int ldc,
+                                      int M, int N, int K, const int* tile_expert, int act, int force_bn,
+                                      int* status, void* stream) {
+  using namespace omni;
+  if (M <= 0 || N <= 0 || K <= 0) return RC_OK;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldc & 7) || (M % BM) || tile_expert == nullptr) return RC_BAD_ARG;
+  CUtensorMap tmA;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K,
+                        (uint64_t)lda * 2, BM, BK);
+  if (rc) return rc;
+  GemmEpilogue epi = {};
+  epi.rows_per_batch = 1;
+  epi.act = act;
+  const int ctas = sm_count();
+  const int bn = force_bn ? force_bn : pick_bn(M, N, ctas);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* c = static_cast<__nv_bfloat16*>(C);
+  switch (bn) {
+    case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert);
+    case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert);
+    case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert);
     default: return RC_BAD_ARG;
   }
 }

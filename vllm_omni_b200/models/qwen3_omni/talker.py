@@ -1,0 +1,191 @@
+"""Qwen3-Omni talker stage: a smaller MoE decoder that speaks codec frames.
+
+Inputs (from the thinker, through ``thinker2talker``): the thinker's token embeddings and
+layer-N hidden states for the whole sequence plus the tts bos/eos/pad embeddings.
+Prefill: multimodal positions are projected with ``hidden_projection``, text positions with
+``text_projection`` (vllm_omni/model_executor/models/qwen3_omni/qwen3_omni.py:586-917).
+Decode: every step emits one codec frame of ``num_code_groups`` codes: code 0 is sampled from
+the talker's codec head, codes 1..G-1 come from the code predictor, a small transformer run
+G-1 times on (talker hidden, embeddings of the codes so far)
+(qwen3_omni_moe_code_predictor_mtp.py:413-524).  The next input embedding is the sum of the
+frame's code embeddings plus the projected thinker embedding of the next text token (or the
+tts-pad embedding once the text is exhausted).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ...diffusion.layers.linear import FusedLinear
+from ...ops import fused
+from ...ops.attention import attention_reference
+from ...ops.sampler import RowParams, sample
+from ..base import StageModel
+from ..qwen_decoder import DecoderConfig, QwenDecoderModel
+from .config import CodePredictorConfig, Qwen3OmniConfig
+
+
+class ResizeMLP(nn.Module):
+    def __init__(self, din, dhid, dout, dtype, device):
+        super().__init__()
+        self.fc1 = FusedLinear(din, dhid, dtype=dtype, device=device)
+        self.fc2 = FusedLinear(dhid, dout, dtype=dtype, device=device)
+
+    def forward(self, x):
+        return self.fc2(self.fc1(x, act="silu"))
+
+
+class CodePredictor(nn.Module):
+    """G-1 sequential steps over a tiny context (<= G+1 tokens), no KV cache: at these sizes the
+    whole loop is launch-bound, so the step is written to be captured in a CUDA graph."""
+
+    def __init__(self, cfg: CodePredictorConfig, talker_hidden: int, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        dc = DecoderConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+                           num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
+                           num_key_value_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
+                           intermediate_size=cfg.intermediate_size)
+        self.core = QwenDecoderModel(dc, dtype, device, with_lm_head=False)
+        G = cfg.num_code_groups
+        self.in_proj = FusedLinear(talker_hidden, cfg.hidden_size, dtype=dtype, device=device) \
+            if talker_hidden != cfg.hidden_size else None
+        # one embedding table and one head per residual codebook 1..G-1
+        self.codec_embedding = nn.Parameter(torch.empty(G - 1, cfg.vocab_size, talker_hidden, dtype=dtype, device=device)
+                                            .normal_(0, 0.02), requires_grad=False)
+        self.lm_heads = nn.Parameter(torch.empty(G - 1, cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+                                     .normal_(0, 0.02), requires_grad=False)
+
+    def _forward_seq(self, x):
+        """x: [n, L, D] small dense causal forward (no cache)."""
+        from ..qwen_decoder import reference_forward  # noqa: F401  (same math, batched below)
+        core, cfg = self.core, self.core.cfg
+        n, L, D = x.shape
+        H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        pos = torch.arange(L, device=x.device)
+        cos, sin = core.rope.cos_sin_for(pos)
+        x = x.reshape(n * L, D).contiguous()
+        for layer in core.layers:
+            xn = fused.norm_modulate(x, weight=layer.input_layernorm, rms=True, eps=cfg.rms_norm_eps)
+            qkv = layer.qkv_proj(xn).view(n, L, -1)
+            fused.qk_norm_rope_(qkv, H, Hkv, Dh, wq=layer.q_norm, wk=layer.k_norm, cos=cos, sin=sin,
+                                interleaved=False, eps=cfg.rms_norm_eps)
+            q = qkv[..., :H * Dh].reshape(n, L, H, Dh)
+            k = qkv[..., H * Dh:(H + Hkv) * Dh].reshape(n, L, Hkv, Dh)
+            v = qkv[..., (H + Hkv) * Dh:].reshape(n, L, Hkv, Dh)
+            o = attention_reference(q, k, v, causal=True).reshape(n * L, H * Dh)
+            layer.o_proj(o.contiguous(), residual=x, out=x)
+            xn = fused.norm_modulate(x, weight=layer.post_attention_layernorm, rms=True, eps=cfg.rms_norm_eps)
+            layer.down(fused.silu_mul(layer.gate_up(xn)), residual=x, out=x)
+        return fused.norm_modulate(x, weight=core.norm, rms=True, eps=cfg.rms_norm_eps).view(n, L, D)
+
+    @torch.no_grad()
+    def generate(self, talker_hidden, code0_embed, temperature=0.0, seed=0, step=0):
+        """talker_hidden, code0_embed: [n, Dt].  Returns (codes [n, G-1] int64, summed embeddings
+        of codes 1..G-1 [n, Dt])."""
+        G = self.cfg.num_code_groups
+        n = talker_hidden.shape[0]
+        seq = torch.stack([talker_hidden, code0_embed], dim=1)               # [n, 2, Dt]
+        codes, summed = [], torch.zeros_like(code0_embed)
+        for g in range(G - 1):
+            xin = seq if self.in_proj is None else self.in_proj(seq.contiguous())
+            h = self._forward_seq(xin)[:, -1]                                # [n, D]
+            logits = F.linear(h.float(), self.lm_heads[g].float())
+            if temperature <= 0:
+                c = logits.argmax(-1)
+            else:
+                c, _ = sample(logits, [RowParams(temperature=temperature, top_k=50, seed=seed + 7919 * (g + 1),
+                                                 step=step) for _ in range(n)])
+                c = c.long()
+            e = self.codec_embedding[g][c]
+            codes.append(c)
+            summed = summed + e
+            seq = torch.cat([seq, e[:, None]], dim=1)
+        return torch.stack(codes, dim=1), summed
+
+
+class Qwen3OmniMoeTalker(StageModel):
+    engine_output_type = "latent"
+
+    def __init__(self, cfg: Qwen3OmniConfig, dtype=torch.bfloat16, device=None):
+        super().__init__(cfg.talker, dtype, device)
+        self.cfg = cfg
+        Dt, Dth = cfg.talker.hidden_size, cfg.thinker.hidden_size
+        self.decoder = QwenDecoderModel(cfg.talker, dtype, device, with_lm_head=False)
+        self.text_projection = ResizeMLP(Dth, Dth, Dt, dtype, device)
+        self.hidden_projection = ResizeMLP(Dth, Dth, Dt, dtype, device)
+        self.codec_head = FusedLinear(Dt, cfg.talker.vocab_size, bias=False, dtype=dtype, device=device)
+        self.code_predictor = CodePredictor(cfg.code_predictor, Dt, dtype, device)
+        self.num_code_groups = cfg.code_predictor.num_code_groups
+
+    def eos_token_id(self):
+        return self.cfg.codec_eos_id
+
+    # ---- request preprocessing (prefill embeddings)
+    @torch.no_grad()
+    def preprocess_request(self, req) -> None:
+        info = req.additional_information
+        cfg = self.cfg
+        dev = self.decoder.embed_tokens.device
+        if "thinker_embeddings" not in info:
+            return
+        emb = info["thinker_embeddings"].to(dev, self.dtype_)               # [L_total, Dth]
+        hid = info["thinker_hidden_states"].to(dev, self.dtype_)
+        seq = list(info.get("thinker_sequences") or [])
+        n_in = len(info.get("thinker_input_ids") or [])
+        mm_ids = {cfg.audio_token_id, cfg.image_token_id, cfg.video_token_id}
+        is_mm = torch.tensor([t in mm_ids for t in seq[:n_in]], dtype=torch.bool, device=dev)
+        # prompt part: multimodal rows use the layer-N hidden states, text rows the embeddings
+        proj_text = self.text_projection(emb[:n_in].contiguous())
+        proj_hid = self.hidden_projection(hid[:n_in].contiguous())
+        prompt = torch.where(is_mm[:, None], proj_hid, proj_text) if n_in else proj_text
+        pad = self.text_projection(info["tts_pad_embed"].to(dev, self.dtype_).reshape(1, -1))
+        bos = self.text_projection(info["tts_bos_embed"].to(dev, self.dtype_).reshape(1, -1))
+        codec = self.decoder.embed_tokens
+        head = torch.cat([prompt,
+                          pad + codec[cfg.codec_nothink_id % codec.shape[0]][None],
+                          bos + codec[cfg.codec_bos_id % codec.shape[0]][None]], dim=0)
+        req.prompt_embeds = head
+        req.prompt_token_ids = [0] * head.shape[0]
+        # text the talker still has to speak: projected embeddings of the thinker's generated tokens
+        gen = self.text_projection(emb[n_in:].contiguous()) if emb.shape[0] > n_in else emb.new_zeros(0, pad.shape[1])
+        eos = self.text_projection(info["tts_eos_embed"].to(dev, self.dtype_).reshape(1, -1))
+        req.runtime_state.update(text_steps=torch.cat([gen, eos], 0), tts_pad=pad, frames=[], next_embed=None)
+
+    def input_embeds_for(self, req, start, n):
+        if start < req.num_prompt_tokens:
+            return req.prompt_embeds[start:start + n]
+        ne = req.runtime_state.get("next_embed")
+        return ne if ne is not None else None
+
+    def compute_logits(self, hidden):
+        return self.codec_head(hidden)
+
+    @torch.no_grad()
+    def postprocess_sampled(self, reqs, ids, hidden):
+        """Complete each sampled code 0 to a full frame with the code predictor and prepare the
+        next step's input embedding."""
+        codec = self.decoder.embed_tokens
+        code0 = ids.long().clamp(0, codec.shape[0] - 1)
+        e0 = codec[code0]
+        temp = max((r.sampling_params.temperature for r in reqs), default=0.0)
+        seed = reqs[0].sampling_params.seed or 0
+        rest, summed = self.code_predictor.generate(hidden.to(self.dtype_), e0, temperature=temp, seed=seed,
+                                                    step=len(reqs[0].output_token_ids))
+        frames = torch.cat([code0[:, None], rest], dim=1)                     # [n, G]
+        for i, r in enumerate(reqs):
+            st = r.runtime_state
+            k = len(r.output_token_ids)                                      # index of this frame
+            ts = st.get("text_steps")
+            text = ts[k:k + 1] if ts is not None and k < ts.shape[0] else st.get("tts_pad")
+            nxt = e0[i:i + 1] + summed[i:i + 1]
+            st["next_embed"] = nxt + text if text is not None else nxt
+            r.multimodal_outputs.setdefault("codes", []).append(frames[i:i + 1])
+        return ids
+
+    def load_weights(self, weights):
+        ws = [(n[len("talker."):] if n.startswith("talker.") else n, w) for n, w in weights]
+        return self.decoder.load_weights(ws)

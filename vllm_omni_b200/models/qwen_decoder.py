@@ -1,0 +1,341 @@
+"""Decoder-only transformer (Qwen2/Qwen3 family, dense or MoE) on the sm_100a ops, used by
+the thinker and talker stages and as a text encoder.
+
+Per layer: RMSNorm -> fused QKV GEMM -> q/k RMSNorm + RoPE in place -> KV pages written ->
+attention (tcgen05 flash kernel for prefill segments, paged split-context kernel for decode
+tokens) -> output GEMM with the residual add in its epilogue -> RMSNorm -> SwiGLU MLP or
+MoE (grouped GEMM) with the residual add fused into the last kernel.
+
+The reference borrows all of this from vLLM (``Qwen3MoeModel``, FusedMoE, paged attention:
+vllm_omni/model_executor/models/qwen3_omni/qwen3_omni_moe_thinker.py); checkpoint names
+follow the HF layout (``model.layers.N.self_attn.q_proj`` ...) with q/k/v and gate/up stacked
+at load time.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+from torch import nn
+
+from ..diffusion.layers.linear import FusedLinear
+from ..ops import fused, kv_cache as KC
+from ..ops.attention import attention
+from ..ops.moe import MoEWorkspace, moe_forward
+
+
+@dataclass
+class DecoderConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 2048
+    num_hidden_layers: int = 48
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 4
+    head_dim: int = 128
+    intermediate_size: int = 6144
+    num_experts: int = 0                 # 0 = dense MLP
+    num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 768
+    norm_topk_prob: bool = True
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    qk_norm: bool = True
+    attention_bias: bool = False
+    mrope_section: tuple | None = None   # e.g. (24, 20, 20): temporal / height / width frequency split
+    mrope_interleaved: bool = False
+    max_position_embeddings: int = 65536
+    tie_word_embeddings: bool = False
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "DecoderConfig":
+        d = dict(d)
+        rs = d.get("rope_scaling") or {}
+        if "mrope_section" in rs and "mrope_section" not in d:
+            d["mrope_section"] = tuple(rs["mrope_section"])
+            d["mrope_interleaved"] = bool(rs.get("mrope_interleaved", rs.get("interleaved", False)))
+        if "head_dim" not in d and "hidden_size" in d and "num_attention_heads" in d:
+            d["head_dim"] = d["hidden_size"] // d["num_attention_heads"]
+        keys = set(cls.__dataclass_fields__)
+        return cls(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items() if k in keys})
+
+
+@dataclass
+class PrefillSeg:
+    start: int            # first row of this segment in the flattened batch
+    length: int           # new tokens in this step
+    context: int          # tokens already in the cache
+    block_table: torch.Tensor | None = None    # int32 [num_blocks_of_request]
+
+
+@dataclass
+class ModelBatch:
+    input_ids: torch.Tensor                    # [T]
+    positions: torch.Tensor                    # [T] or [3, T] (MRoPE)
+    slot_mapping: torch.Tensor                 # int32 [T]
+    prefills: list[PrefillSeg] = field(default_factory=list)
+    decode_rows: torch.Tensor | None = None    # int64 [n] rows of decode tokens
+    decode_block_tables: torch.Tensor | None = None
+    decode_seq_lens: torch.Tensor | None = None
+    input_embeds: torch.Tensor | None = None   # [T, D] replaces the embedding lookup where mask is set
+    embeds_mask: torch.Tensor | None = None    # bool [T]
+
+
+class RotaryTable:
+    def __init__(self, head_dim: int, theta: float, max_pos: int):
+        self.head_dim, self.theta, self.max_pos = head_dim, theta, max_pos
+        self.inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+        self._dev = {}
+
+    def cos_sin_for(self, positions: torch.Tensor, mrope_section=None, interleaved=False):
+        """Per-token tables [T, head_dim/2] (fp32).  positions: [T] or [3, T]."""
+        inv = self._dev.get(positions.device)
+        if inv is None:
+            inv = self.inv_freq.to(positions.device)
+            self._dev[positions.device] = inv
+        if positions.dim() == 1:
+            ang = positions.float()[:, None] * inv[None, :]
+        else:
+            ang3 = positions.float()[:, :, None] * inv[None, None, :]          # [3, T, Dh/2]
+            if interleaved:
+                # frequency i takes its position from axis (i % 3) inside the sectioned range
+                ang = ang3[0].clone()
+                for ax, off in ((1, 1), (2, 2)):
+                    n = mrope_section[ax] * 3
+                    ang[:, off:n:3] = ang3[ax][:, off:n:3]
+            else:
+                parts, o = [], 0
+                for ax, n in enumerate(mrope_section):
+                    parts.append(ang3[ax][:, o:o + n])
+                    o += n
+                ang = torch.cat(parts, dim=-1)
+        return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: DecoderConfig, dtype, device):
+        super().__init__()
+        D, H, Hkv, Dh = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        P = lambda *s: nn.Parameter(torch.ones(*s, dtype=dtype, device=device), requires_grad=False)
+        self.input_layernorm = P(D)
+        self.qkv_proj = FusedLinear(D, (H + 2 * Hkv) * Dh, bias=cfg.attention_bias, dtype=dtype, device=device)
+        self.q_norm = P(Dh) if cfg.qk_norm else None
+        self.k_norm = P(Dh) if cfg.qk_norm else None
+        self.o_proj = FusedLinear(H * Dh, D, bias=False, dtype=dtype, device=device)
+        self.post_attention_layernorm = P(D)
+        if cfg.num_experts:
+            E, F_ = cfg.num_experts, cfg.moe_intermediate_size
+            self.router = FusedLinear(D, E, bias=False, dtype=dtype, device=device)
+            self.w13 = nn.Parameter(torch.empty(E, 2 * F_, D, dtype=dtype, device=device).normal_(0, 0.02),
+                                    requires_grad=False)
+            self.w2 = nn.Parameter(torch.empty(E, D, F_, dtype=dtype, device=device).normal_(0, 0.02),
+                                   requires_grad=False)
+            self.moe_ws = MoEWorkspace()
+        else:
+            self.gate_up = FusedLinear(D, 2 * cfg.intermediate_size, bias=False, dtype=dtype, device=device)
+            self.down = FusedLinear(cfg.intermediate_size, D, bias=False, dtype=dtype, device=device)
+
+
+class QwenDecoderModel(nn.Module):
+    def __init__(self, cfg: DecoderConfig, dtype=torch.bfloat16, device=None, with_lm_head: bool = True):
+        super().__init__()
+        self.cfg, self.dtype_ = cfg, dtype
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+                                         .normal_(0, 0.02), requires_grad=False)
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device), requires_grad=False)
+        self.lm_head = None
+        if with_lm_head and not cfg.tie_word_embeddings:
+            self.lm_head = FusedLinear(cfg.hidden_size, cfg.vocab_size, bias=False, dtype=dtype, device=device)
+        self.rope = RotaryTable(cfg.head_dim, cfg.rope_theta, cfg.max_position_embeddings)
+        self.ep_group = None          # expert-parallel group: experts sharded, partial outputs summed
+        self.ep_range = (0, cfg.num_experts)
+
+    # ------------------------------------------------------------------ forward
+    def embed(self, batch: ModelBatch) -> torch.Tensor:
+        x = self.embed_tokens[batch.input_ids.long().clamp(0, self.cfg.vocab_size - 1)]
+        if batch.input_embeds is not None:
+            m = batch.embeds_mask
+            x = torch.where(m[:, None], batch.input_embeds.to(x.dtype), x) if m is not None else batch.input_embeds.to(x.dtype)
+        return x.contiguous()
+
+    def attention_block(self, layer: DecoderLayer, qkv: torch.Tensor, batch: ModelBatch, k_cache, v_cache, out):
+        cfg = self.cfg
+        H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        T = qkv.shape[0]
+        q = qkv[:, :H * Dh].view(T, H, Dh)
+        k = qkv[:, H * Dh:(H + Hkv) * Dh].view(T, Hkv, Dh)
+        v = qkv[:, (H + Hkv) * Dh:].view(T, Hkv, Dh)
+        if k_cache is not None:
+            KC.kv_write(k, v, k_cache, v_cache, batch.slot_mapping)
+        scale = 1.0 / math.sqrt(Dh)
+        o = out.view(T, H, Dh)
+        for seg in batch.prefills:
+            s, n = seg.start, seg.length
+            if seg.context == 0 or k_cache is None:
+                attention(q[None, s:s + n], k[None, s:s + n], v[None, s:s + n], scale=scale, causal=True,
+                          out=o[None, s:s + n])
+            else:
+                gk, gv = KC.kv_gather(k_cache, v_cache, seg.block_table, seg.context + n)
+                attention(q[None, s:s + n], gk[None], gv[None], scale=scale, causal=True, q_offset=seg.context,
+                          out=o[None, s:s + n])
+        if batch.decode_rows is not None and batch.decode_rows.numel():
+            rows = batch.decode_rows
+            qd = q[rows].contiguous()
+            od = KC.paged_decode(qd, k_cache, v_cache, batch.decode_block_tables, batch.decode_seq_lens, scale=scale)
+            o[rows] = od
+        return out
+
+    def forward(self, batch: ModelBatch, kv_caches=None, capture_layers=()):
+        """Returns (hidden [T, D] before the final norm applied -> after final norm, captured)."""
+        cfg = self.cfg
+        H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        x = self.embed(batch)
+        T = x.shape[0]
+        cos, sin = self.rope.cos_sin_for(batch.positions, cfg.mrope_section, cfg.mrope_interleaved)
+        captured = {}
+        if 0 in capture_layers:
+            captured[0] = x.clone()
+        xn = torch.empty_like(x)
+        attn = torch.empty(T, H * Dh, dtype=x.dtype, device=x.device)
+        for li, layer in enumerate(self.layers):
+            fused.norm_modulate(x, weight=layer.input_layernorm, rms=True, eps=cfg.rms_norm_eps, out=xn)
+            qkv = layer.qkv_proj(xn)
+            fused.qk_norm_rope_(qkv.view(1, T, -1), H, Hkv, Dh, wq=layer.q_norm, wk=layer.k_norm, cos=cos, sin=sin,
+                                interleaved=False, eps=cfg.rms_norm_eps)
+            kc, vc = kv_caches[li] if kv_caches is not None else (None, None)
+            self.attention_block(layer, qkv, batch, kc, vc, attn)
+            layer.o_proj(attn, residual=x, out=x)
+            fused.norm_modulate(x, weight=layer.post_attention_layernorm, rms=True, eps=cfg.rms_norm_eps, out=xn)
+            if cfg.num_experts:
+                logits = layer.router(xn)
+                e_lo, e_hi = self.ep_range
+                if self.ep_group is None or self.ep_group.world_size == 1:
+                    moe_forward(xn, logits, layer.w13, layer.w2, cfg.num_experts_per_tok, cfg.norm_topk_prob,
+                                ws=layer.moe_ws, residual=x, out=x)
+                else:
+                    part = moe_forward(xn, logits, layer.w13, layer.w2, cfg.num_experts_per_tok, cfg.norm_topk_prob,
+                                       e_lo=e_lo, e_hi=e_hi, ws=layer.moe_ws)
+                    self.ep_group.all_reduce(part)
+                    x.add_(part)
+            else:
+                h = fused.silu_mul(layer.gate_up(xn))
+                layer.down(h, residual=x, out=x)
+            if (li + 1) in capture_layers:
+                captured[li + 1] = x.clone()
+        hidden = fused.norm_modulate(x, weight=self.norm, rms=True, eps=cfg.rms_norm_eps)
+        return hidden, captured
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        if self.lm_head is not None:
+            return self.lm_head(hidden)
+        from ..ops.gemm import linear
+        return linear(hidden, self.embed_tokens)
+
+    # ------------------------------------------------------------------ weights
+    @torch.no_grad()
+    def load_weights(self, weights, prefix: str = "model.") -> set:
+        cfg = self.cfg
+        H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        F_ = cfg.moe_intermediate_size if cfg.num_experts else cfg.intermediate_size
+        loaded = set()
+        for name, w in weights:
+            n = name[len(prefix):] if name.startswith(prefix) else name
+            tgt, sl = None, None
+            if n == "embed_tokens.weight":
+                tgt = self.embed_tokens
+            elif n == "norm.weight":
+                tgt = self.norm
+            elif name in ("lm_head.weight", prefix + "lm_head.weight") and self.lm_head is not None:
+                tgt = self.lm_head.weight
+            elif n.startswith("layers."):
+                parts = n.split(".")
+                layer = self.layers[int(parts[1])]
+                rest = ".".join(parts[2:])
+                qkv_off = {"self_attn.q_proj": (0, H * Dh), "self_attn.k_proj": (H * Dh, (H + Hkv) * Dh),
+                           "self_attn.v_proj": ((H + Hkv) * Dh, (H + 2 * Hkv) * Dh)}
+                for k, (a, b) in qkv_off.items():
+                    if rest == k + ".weight":
+                        tgt, sl = layer.qkv_proj.weight, (a, b)
+                    elif rest == k + ".bias" and layer.qkv_proj.bias is not None:
+                        tgt, sl = layer.qkv_proj.bias, (a, b)
+                simple = {"input_layernorm.weight": layer.input_layernorm,
+                          "post_attention_layernorm.weight": layer.post_attention_layernorm,
+                          "self_attn.o_proj.weight": layer.o_proj.weight,
+                          "self_attn.q_norm.weight": layer.q_norm, "self_attn.k_norm.weight": layer.k_norm}
+                if rest in simple and simple[rest] is not None:
+                    tgt = simple[rest]
+                if cfg.num_experts:
+                    if rest == "mlp.gate.weight":
+                        tgt = layer.router.weight
+                    elif rest.startswith("mlp.experts."):
+                        e = int(parts[4])
+                        kind = parts[5]
+                        if kind == "gate_proj":
+                            tgt, sl = layer.w13[e], (0, F_)
+                        elif kind == "up_proj":
+                            tgt, sl = layer.w13[e], (F_, 2 * F_)
+                        elif kind == "down_proj":
+                            tgt = layer.w2[e]
+                else:
+                    if rest == "mlp.gate_proj.weight":
+                        tgt, sl = layer.gate_up.weight, (0, F_)
+                    elif rest == "mlp.up_proj.weight":
+                        tgt, sl = layer.gate_up.weight, (F_, 2 * F_)
+                    elif rest == "mlp.down_proj.weight":
+                        tgt = layer.down.weight
+            if tgt is None:
+                continue
+            dst = tgt if sl is None else tgt[sl[0]:sl[1]]
+            dst.copy_(w.to(dst.dtype).reshape(dst.shape))
+            loaded.add(name)
+        return loaded
+
+
+def reference_forward(model: QwenDecoderModel, input_ids: torch.Tensor, positions: torch.Tensor | None = None):
+    """Plain PyTorch fp32 forward of one full sequence (no cache): the engine's oracle."""
+    import torch.nn.functional as F
+    cfg = model.cfg
+    H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    T = input_ids.numel()
+    f = lambda t: t.float()
+    x = f(model.embed_tokens)[input_ids.long()]
+    pos = torch.arange(T, device=input_ids.device) if positions is None else positions
+    cos, sin = model.rope.cos_sin_for(pos, cfg.mrope_section, cfg.mrope_interleaved)
+    rms = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * f(w)
+    for layer in model.layers:
+        xn = rms(x, layer.input_layernorm)
+        qkv = F.linear(xn, f(layer.qkv_proj.weight), None if layer.qkv_proj.bias is None else f(layer.qkv_proj.bias))
+        q = qkv[:, :H * Dh].view(T, H, Dh)
+        k = qkv[:, H * Dh:(H + Hkv) * Dh].view(T, Hkv, Dh)
+        v = qkv[:, (H + Hkv) * Dh:].view(T, Hkv, Dh)
+        if layer.q_norm is not None:
+            q, k = rms(q, layer.q_norm), rms(k, layer.k_norm)
+        q = fused.apply_rope_reference(q, cos, sin, False)
+        k = fused.apply_rope_reference(k, cos, sin, False)
+        kk = k.repeat_interleave(H // Hkv, dim=1)
+        vv = v.repeat_interleave(H // Hkv, dim=1)
+        s = torch.einsum("qhd,khd->hqk", q, kk) / math.sqrt(Dh)
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool, device=s.device), 1)[None], float("-inf"))
+        o = torch.einsum("hqk,khd->qhd", s.softmax(-1), vv).reshape(T, H * Dh)
+        x = x + F.linear(o, f(layer.o_proj.weight))
+        xn = rms(x, layer.post_attention_layernorm)
+        if cfg.num_experts:
+            logits = F.linear(xn, f(layer.router.weight))
+            p = logits.softmax(-1)
+            w, ids = torch.topk(p, cfg.num_experts_per_tok, dim=-1)
+            if cfg.norm_topk_prob:
+                w = w / w.sum(-1, keepdim=True)
+            y = torch.zeros_like(x)
+            Fd = cfg.moe_intermediate_size
+            for t in range(T):
+                for j in range(cfg.num_experts_per_tok):
+                    e = int(ids[t, j])
+                    h = F.linear(xn[t], f(layer.w13[e]))
+                    y[t] += w[t, j] * F.linear(F.silu(h[:Fd]) * h[Fd:], f(layer.w2[e]))
+            x = x + y
+        else:
+            h = F.linear(xn, f(layer.gate_up.weight))
+            Fd = cfg.intermediate_size
+            x = x + F.linear(F.silu(h[:, :Fd]) * h[:, Fd:], f(layer.down.weight))
+    return rms(x, model.norm)

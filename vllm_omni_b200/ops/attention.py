@@ -18,7 +18,7 @@ from . import _native as nv
 c_int, c_long, c_float = ctypes.c_int, ctypes.c_long, ctypes.c_float
 
 
-def attention_reference(q, k, v, scale=None, kv_lens=None, return_lse=False):
+def attention_reference(q, k, v, scale=None, kv_lens=None, return_lse=False, causal=False, q_offset=0):
     """fp32 softmax(q k^T * scale) v.  q: [B,Sq,H,D], k/v: [B,Skv,Hkv,D]."""
     B, Sq, H, D = q.shape
     Hkv = k.shape[2]
@@ -30,6 +30,10 @@ def attention_reference(q, k, v, scale=None, kv_lens=None, return_lse=False):
     if kv_lens is not None:
         idx = torch.arange(k.shape[1], device=q.device)[None, None, None, :]
         s = s.masked_fill(idx >= kv_lens.to(q.device)[:, None, None, None], float("-inf"))
+    if causal:
+        qi = torch.arange(Sq, device=q.device)[:, None] + q_offset
+        ki = torch.arange(k.shape[1], device=q.device)[None, :]
+        s = s.masked_fill((ki > qi)[None, None], float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     o = torch.matmul(torch.softmax(s, dim=-1), vf).permute(0, 2, 1, 3)
     o = o.to(q.dtype)
@@ -37,7 +41,7 @@ def attention_reference(q, k, v, scale=None, kv_lens=None, return_lse=False):
 
 
 def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, return_lse=False,
-              scatter=None):
+              scatter=None, causal=False, q_offset=0):
     """Non-causal attention.  Returns ``out`` ([B, Sq, H, D], or the given buffer).
 
     ``out2``/``split``: rows >= split of every batch go to ``out2`` (row index s - split).
@@ -51,7 +55,7 @@ def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, r
     Skv, Hkv = k.shape[1], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if not q.is_cuda:
-        r = attention_reference(q, k, v, scale, kv_lens, return_lse)
+        r = attention_reference(q, k, v, scale, kv_lens, return_lse, causal, q_offset)
         o, lse = (r if return_lse else (r, None))
         if out2 is not None:
             out.copy_(o[:, :split])
@@ -90,7 +94,7 @@ def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, r
         out_ptr, c_long(os_[0]), c_long(os_[1]), c_long(os_[2]),
         out2_ptr, c_long(o2s[0]), c_long(o2s[1]), c_long(o2s[2]), c_int(split),
         nv.ptr(lse), c_int(B), c_int(H), c_int(Hkv), c_int(Sq), c_int(Skv), c_int(D), nv.ptr(kv_lens),
-        c_float(scale), c_int(sc["n_peers"] if sc else 0), c_int(sc["rows_per_rank"] if sc else 0),
+        c_float(scale), c_int(1 if causal else 0), c_int(q_offset), c_int(sc["n_peers"] if sc else 0), c_int(sc["rows_per_rank"] if sc else 0),
         c_int(sc.get("rows_per_rank2", 0) if sc else 0), op, o2p, nv.ptr(st), nv.stream_ptr())
     nv.check_rc(rc, "omni_attn_fwd")
     return (out, lse) if return_lse else out

@@ -1,0 +1,126 @@
+"""K10 — mixture-of-experts forward on the grouped tcgen05 GEMM (csrc/moe.cu, gemm_sm100.cu).
+
+``moe_forward`` = route (softmax, top-k, renorm) -> plan (expert segments padded to the
+128-row MMA tile) -> dispatch (gather rows expert-major) -> grouped GEMM w13 -> SwiGLU ->
+grouped GEMM w2 -> weighted combine.  With expert parallelism a rank passes its local expert
+range; pairs routed to other ranks contribute nothing locally and the caller sums the
+partial outputs across ranks.  ``moe_reference`` is the dense per-token restatement (the
+semantics of vllm_omni/model_executor/models/qwen3_omni/qwen3_moe.py).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _native as nv
+from . import fused
+
+c_int, c_long = ctypes.c_int, ctypes.c_long
+
+
+def moe_route_reference(logits, k, renorm=True):
+    p = torch.softmax(logits.float(), dim=-1)
+    w, ids = torch.topk(p, k, dim=-1)
+    if renorm:
+        w = w / w.sum(-1, keepdim=True)
+    return ids.to(torch.int32), w
+
+
+def moe_reference(x, router_w, w13, w2, k, renorm=True, e_lo=0, e_hi=None):
+    """x [T, D]; router_w [E, D]; w13 [E, 2F, D]; w2 [E, D, F]."""
+    E = w13.shape[0]
+    e_hi = E if e_hi is None else e_hi
+    logits = F.linear(x.float(), router_w.float())
+    ids, w = moe_route_reference(logits.to(x.dtype), k, renorm)
+    out = torch.zeros_like(x, dtype=torch.float32)
+    Fd = w2.shape[2]
+    for t in range(x.shape[0]):
+        for j in range(k):
+            e = int(ids[t, j])
+            if not (e_lo <= e < e_hi):
+                continue
+            h = F.linear(x[t].float(), w13[e].float())
+            h = F.silu(h[:Fd]) * h[Fd:]
+            out[t] += w[t, j] * F.linear(h.to(x.dtype).float(), w2[e].float())
+    return out.to(x.dtype)
+
+
+class MoEWorkspace:
+    def __init__(self):
+        self.key = None
+
+    def get(self, T, k, E, D, Fd, device, dtype):
+        key = (T, k, E, D, Fd, str(device), dtype)
+        if self.key != key:
+            self.key = key
+            n_pairs = T * k
+            self.max_rows = ((n_pairs + E * 127) + 127) // 128 * 128
+            self.max_tiles = self.max_rows // 128
+            i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=device)
+            self.ids, self.row_of_pair = i32(T, k), i32(n_pairs)
+            self.tile_expert, self.offsets, self.n_rows = i32(self.max_tiles), i32(E + 1), i32(1)
+            self.weights = torch.empty(T, k, dtype=torch.float32, device=device)
+            self.xp = torch.zeros(self.max_rows, D, dtype=dtype, device=device)
+            self.h13 = torch.empty(self.max_rows, 2 * Fd, dtype=dtype, device=device)
+            self.h = torch.empty(self.max_rows, Fd, dtype=dtype, device=device)
+            self.y = torch.empty(self.max_rows, D, dtype=dtype, device=device)
+        return self
+
+
+def moe_forward(x, router_logits, w13, w2, k, renorm=True, e_lo=0, e_hi=None, ws: MoEWorkspace | None = None,
+                residual=None, out=None):
+    """x [T, D] bf16, router_logits [T, E] bf16, w13 [E_local, 2F, D], w2 [E_local, D, F] (the
+    local experts [e_lo, e_hi) of E = router_logits.shape[1])."""
+    T, D = x.shape
+    E = router_logits.shape[1]
+    e_hi = E if e_hi is None else e_hi
+    Fd = w2.shape[2]
+    if not x.is_cuda:
+        ids, w = moe_route_reference(router_logits, k, renorm)
+        y = torch.zeros(T, D, dtype=torch.float32)
+        for t in range(T):
+            for j in range(k):
+                e = int(ids[t, j])
+                if e_lo <= e < e_hi:
+                    h = F.linear(x[t].float(), w13[e - e_lo].float())
+                    h = (F.silu(h[:Fd]) * h[Fd:]).to(x.dtype).float()
+                    y[t] += w[t, j] * F.linear(h, w2[e - e_lo].float())
+        if residual is not None:
+            y += residual.float()
+        y = y.to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    ws = (ws or MoEWorkspace()).get(T, k, E, D, Fd, x.device, x.dtype)
+    lib, st = nv.lib("moe"), nv.stream_ptr()
+    assert router_logits.dtype == torch.bfloat16 and router_logits.stride(1) == 1
+    nv.check_rc(lib.omni_moe_route(nv.ptr(router_logits), c_int(router_logits.stride(0)), c_int(T), c_int(E), c_int(k),
+                                   c_int(1 if renorm else 0), nv.ptr(ws.ids), nv.ptr(ws.weights), st), "omni_moe_route")
+    nv.check_rc(lib.omni_moe_plan(nv.ptr(ws.ids), c_int(T * k), c_int(E), c_int(e_lo), c_int(e_hi),
+                                  c_int(ws.max_tiles), nv.ptr(ws.row_of_pair), nv.ptr(ws.tile_expert),
+                                  nv.ptr(ws.offsets), nv.ptr(ws.n_rows), st), "omni_moe_plan")
+    nv.check_rc(lib.omni_moe_dispatch(nv.ptr(x), c_long(x.stride(0)), nv.ptr(ws.row_of_pair), c_int(T * k), c_int(k),
+                                      c_int(D), nv.ptr(ws.xp), st), "omni_moe_dispatch")
+    g = nv.lib("gemm_sm100")
+    status = nv.status_word(x.device)
+    # tile_expert holds GLOBAL expert ids; the local weight tensors start at e_lo
+    te = ws.tile_expert
+    if e_lo:
+        te = torch.where(te >= 0, te - e_lo, te)
+    El = w13.shape[0]
+    nv.check_rc(g.omni_gemm_bf16_grouped(nv.ptr(ws.xp), c_int(D), nv.ptr(w13), c_int(El), nv.ptr(ws.h13),
+                                         c_int(2 * Fd), c_int(ws.max_rows), c_int(2 * Fd), c_int(D), nv.ptr(te),
+                                         c_int(0), c_int(0), nv.ptr(status), st), "omni_gemm_bf16_grouped")
+    fused.silu_mul(ws.h13, out=ws.h)
+    nv.check_rc(g.omni_gemm_bf16_grouped(nv.ptr(ws.h), c_int(Fd), nv.ptr(w2), c_int(El), nv.ptr(ws.y), c_int(D),
+                                         c_int(ws.max_rows), c_int(D), c_int(Fd), nv.ptr(te), c_int(0), c_int(0),
+                                         nv.ptr(status), st), "omni_gemm_bf16_grouped")
+    if out is None:
+        out = torch.empty_like(x)
+    nv.check_rc(lib.omni_moe_combine(nv.ptr(ws.y), nv.ptr(ws.row_of_pair), nv.ptr(ws.weights), c_int(T), c_int(k),
+                                     c_int(D), nv.ptr(residual), c_long(residual.stride(0) if residual is not None else 0),
+                                     nv.ptr(out), c_long(out.stride(0)), st), "omni_moe_combine")
+    return out
