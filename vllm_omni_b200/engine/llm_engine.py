@@ -157,6 +157,18 @@ class LLMEngine:
         comp = CompletionOutput(index=0, text=text, token_ids=list(req.output_token_ids),
                                 finish_reason=FINISH_REASON.get(req.status) if fin else None,
                                 stop_reason=req.stop_reason)
+        stream_keys = getattr(self.model, "stream_output_keys", ())
+        if not fin and not self.generation and stream_keys:
+            # streaming: only what is new since the last report (e.g. codec frames for the vocoder)
+            sent = req.runtime_state.setdefault("_mm_sent", {})
+            mm = {}
+            for k in stream_keys:
+                parts = req.multimodal_outputs.get(k) or []
+                new_parts = parts[sent.get(k, 0):]
+                sent[k] = len(parts)
+                if new_parts:
+                    mm[k] = torch.cat(new_parts, dim=0)
+            comp.multimodal_output = mm
         if fin or self.generation:
             mm = {}
             for k, parts in req.multimodal_outputs.items():

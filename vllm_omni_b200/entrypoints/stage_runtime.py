@@ -130,15 +130,20 @@ class LLMStageAdapter(StageEngineAdapter):
             sp = SamplingParams(**sp)
         inputs = task["engine_inputs"]
         inputs = inputs[0] if isinstance(inputs, list) and len(inputs) == 1 else inputs
-        self._t0[task["request_id"]] = time.perf_counter()
-        self.llm.add_request(task["request_id"], inputs, sp)
+        rid = task["request_id"]
+        if task.get("chunk_index") is not None:      # several chunk sub-requests share one request id
+            rid = f"{rid}#c{task['chunk_index']}"
+        self._t0[rid] = time.perf_counter()
+        self.llm.add_request(rid, inputs, sp)
 
     def has_work(self):
         return self.llm.has_unfinished_requests()
 
     def abort(self, request_ids):
-        self.llm.abort_request(request_ids)
-        for r in request_ids:
+        ids = set(request_ids)
+        full = [k for k in self._t0 if k.split("#c")[0] in ids] + list(request_ids)
+        self.llm.abort_request(full)
+        for r in full:
             self._t0.pop(r, None)
 
     def step(self):
@@ -155,10 +160,13 @@ class LLMStageAdapter(StageEngineAdapter):
         for ro in outs:
             if not ro.finished and not self.stream:
                 continue
-            res = {"request_id": ro.request_id, "stage_id": self.stage_id, "engine_outputs": [ro],
+            base_id = ro.request_id.split("#c")[0]
+            full_id = ro.request_id
+            ro.request_id = base_id
+            res = {"request_id": base_id, "stage_id": self.stage_id, "engine_outputs": [ro],
                    "finished": ro.finished}
             if ro.finished:
-                dt = (time.perf_counter() - self._t0.pop(ro.request_id, time.perf_counter())) * 1e3
+                dt = (time.perf_counter() - self._t0.pop(full_id, time.perf_counter())) * 1e3
                 res["metrics"] = {"batch_id": 0, "batch_size": 1, "num_tokens_in": len(ro.prompt_token_ids or []),
                                   "num_tokens_out": sum(len(o.token_ids) for o in ro.outputs),
                                   "stage_gen_time_ms": dt}

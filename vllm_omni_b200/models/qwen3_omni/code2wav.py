@@ -141,6 +141,8 @@ class Qwen3OmniCode2Wav(StageModel):
         left = c.left_context if left_context is None else left_context
         T = codes.shape[-1]
         up = c.total_upsample
+        if T == 0:
+            return torch.zeros(codes.shape[0], 0, device=codes.device)
         outs, start = [], 0
         while start < T:
             end = min(T, start + chunk_size)

@@ -109,6 +109,7 @@ class CodePredictor(nn.Module):
 
 class Qwen3OmniMoeTalker(StageModel):
     engine_output_type = "latent"
+    stream_output_keys = ("codes",)      # new codec frames ride on every streaming output
 
     def __init__(self, cfg: Qwen3OmniConfig, dtype=torch.bfloat16, device=None):
         super().__init__(cfg.talker, dtype, device)
