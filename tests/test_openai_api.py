@@ -1,0 +1,123 @@
+"""HTTP surface with FastAPI's TestClient: schema validation with a mocked engine, and the real
+tiny engines (diffusion + three-stage omni) end to end."""
+import base64
+import io
+
+import pytest
+import torch
+from fastapi.testclient import TestClient
+
+from vllm_omni_b200.entrypoints.openai.api_server import build_app
+from vllm_omni_b200.outputs import OmniRequestOutput
+
+
+class FakeDiffusionEngine:
+    """Records what the server asked for and returns a 1-pixel image per requested output."""
+    stage_list = []
+
+    def __init__(self):
+        self.calls = []
+
+    async def check_health(self):
+        return None
+
+    async def generate(self, prompt, request_id=None, sampling_params_list=None, output_modalities=None):
+        from PIL import Image
+        sp = sampling_params_list[0]
+        self.calls.append((prompt, sp))
+        imgs = [Image.new("RGB", (sp.width, sp.height), (i, 0, 0)) for i in range(sp.num_outputs_per_prompt)]
+        yield OmniRequestOutput.from_diffusion(request_id, imgs, prompt)
+
+
+@pytest.fixture()
+def fake_client():
+    eng = FakeDiffusionEngine()
+    return TestClient(build_app(eng, "fake", kind="diffusion")), eng
+
+
+def test_image_generation_request_mapping(fake_client):
+    c, eng = fake_client
+    r = c.post("/v1/images/generations", json={"prompt": "a cat", "n": 2, "size": "64x32", "seed": 7,
+                                                "negative_prompt": "blurry", "num_inference_steps": 9,
+                                                "true_cfg_scale": 3.5})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    assert len(body["data"]) == 2 and body["size"] == "64x32"
+    from PIL import Image
+    im = Image.open(io.BytesIO(base64.b64decode(body["data"][1]["b64_json"])))
+    assert im.size == (64, 32)
+    prompt, sp = eng.calls[0]
+    assert prompt == {"prompt": "a cat", "negative_prompt": "blurry"}
+    assert (sp.width, sp.height, sp.seed, sp.num_inference_steps, sp.true_cfg_scale) == (64, 32, 7, 9, 3.5)
+
+
+@pytest.mark.parametrize("payload,code", [({"prompt": "x", "size": "abc"}, 400), ({"prompt": "x", "size": "100x100"}, 400),
+                                          ({"prompt": "x", "n": 0}, 422), ({"size": "64x64"}, 422),
+                                          ({"prompt": "x", "response_format": "url"}, 400),
+                                          ({"prompt": "x", "lora": {"name": "a"}}, 400)])
+def test_image_generation_validation(fake_client, payload, code):
+    c, _ = fake_client
+    assert c.post("/v1/images/generations", json=payload).status_code == code
+
+
+def test_models_health_and_chat_as_image(fake_client):
+    c, eng = fake_client
+    assert c.get("/health").status_code == 200
+    assert c.get("/v1/models").json()["data"][0]["id"] == "fake"
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "a red fox"}],
+                                             "extra_body": {"size": "32x32", "num_inference_steps": 3}})
+    assert r.status_code == 200, r.text
+    url = r.json()["choices"][0]["message"]["content"][0]["image_url"]["url"]
+    assert url.startswith("data:image/png;base64,")
+    assert eng.calls[-1][1].num_inference_steps == 3
+
+
+def test_image_edit_multipart(fake_client):
+    c, eng = fake_client
+    from PIL import Image
+    buf = io.BytesIO()
+    Image.new("RGB", (48, 32), (9, 9, 9)).save(buf, format="PNG")
+    r = c.post("/v1/images/edits", files={"image": ("a.png", buf.getvalue(), "image/png")},
+               data={"prompt": "make it blue", "n": "1"})
+    assert r.status_code == 200, r.text
+    prompt, sp = eng.calls[-1]
+    assert prompt["multi_modal_data"]["image"].size == (48, 32) and (sp.width, sp.height) == (48, 32)
+
+
+def test_real_tiny_diffusion_server():
+    from vllm_omni_b200.entrypoints.async_omni import AsyncOmni
+    eng = AsyncOmni("TinyMMDiTPipeline", dtype="float32", device="cpu")
+    try:
+        with TestClient(build_app(eng, "tiny", kind="diffusion")) as c:
+            r = c.post("/v1/images/generations", json={"prompt": "a boat", "size": "64x64", "num_inference_steps": 2,
+                                                        "seed": 1})
+            assert r.status_code == 200, r.text
+            assert len(base64.b64decode(r.json()["data"][0]["b64_json"])) > 100
+            assert "omni_e2e_requests 1" in c.get("/metrics").text
+    finally:
+        eng.close()
+
+
+def test_real_tiny_omni_chat_and_speech(tmp_path):
+    from test_async_omni import _engine
+    eng = _engine(tmp_path)
+    try:
+        with TestClient(build_app(eng, "tiny-omni", kind="omni")) as c:
+            r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}],
+                                                     "modalities": ["text", "audio"], "max_tokens": 4})
+            assert r.status_code == 200, r.text
+            msg = r.json()["choices"][0]["message"]
+            assert r.json()["usage"]["completion_tokens"] == 4
+            assert base64.b64decode(msg["audio"]["data"])[:4] == b"RIFF"
+            # streaming: SSE chunks with text deltas, then [DONE]
+            with c.stream("POST", "/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}],
+                                                                 "stream": True, "max_tokens": 3}) as s:
+                lines = [l for l in s.iter_lines() if l.startswith("data:")]
+            assert lines[-1].strip() == "data: [DONE]" and len(lines) >= 2
+            r = c.post("/v1/audio/speech", json={"input": "hello there", "voice": "Vivian", "max_new_tokens": 4})
+            assert r.status_code == 200 and r.content[:4] == b"RIFF"
+            assert c.post("/v1/audio/speech", json={"input": "x", "voice": "nobody"}).status_code == 400
+            assert c.post("/v1/audio/speech", json={"input": "x", "response_format": "mp3"}).status_code == 400
+            assert "Vivian" in c.get("/v1/audio/voices").json()["voices"]
+    finally:
+        eng.close()
