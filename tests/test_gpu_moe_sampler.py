@@ -1,0 +1,58 @@
+"""MoE (route / plan / dispatch / grouped GEMM / combine) and the sampler kernel vs PyTorch."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_moe_forward_matches_reference():
+    from vllm_omni_b200.ops.moe import moe_forward, moe_reference
+    from vllm_omni_b200.ops import gemm, _native as nv
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    T, D, E, Fd, k = 37, 256, 16, 128, 4
+    x = torch.randn(T, D, device=dev, dtype=torch.bfloat16)
+    rw = torch.randn(E, D, device=dev, dtype=torch.bfloat16) * 0.1
+    w13 = torch.randn(E, 2 * Fd, D, device=dev, dtype=torch.bfloat16) * 0.05
+    w2 = torch.randn(E, D, Fd, device=dev, dtype=torch.bfloat16) * 0.05
+    logits = gemm.linear(x, rw)
+    y = moe_forward(x, logits, w13, w2, k).float()
+    torch.cuda.synchronize()
+    assert int(nv.status_word(dev).item()) == 0
+    ref = moe_reference(x.cpu(), rw.cpu(), w13.cpu(), w2.cpu(), k).float()
+    assert (y.cpu() - ref).abs().max().item() < 0.05 * max(1.0, ref.abs().max().item())
+    # expert-parallel halves sum to the whole
+    a = moe_forward(x, logits, w13[:8].contiguous(), w2[:8].contiguous(), k, e_lo=0, e_hi=8).float()
+    b = moe_forward(x, logits, w13[8:].contiguous(), w2[8:].contiguous(), k, e_lo=8, e_hi=16).float()
+    assert ((a + b) - y).abs().max().item() < 0.05
+
+
+def test_sampler_greedy_topk_topp_and_masks():
+    from vllm_omni_b200.ops.sampler import RowParams, sample
+    dev = torch.device("cuda")
+    torch.manual_seed(1)
+    B, V = 6, 151936
+    logits = torch.randn(B, V, device=dev) * 3
+    rows = [RowParams(temperature=0.0),
+            RowParams(temperature=0.0, suppressed=[int(logits[1].argmax())]),
+            RowParams(temperature=0.0, allowed_range=(1000, 2000)),
+            RowParams(temperature=1.0, top_k=1, seed=3),
+            RowParams(temperature=0.8, top_k=50, top_p=0.9, seed=5, step=2),
+            RowParams(temperature=0.0, repetition_penalty=1e4, history=[int(logits[5].argmax())], num_prompt_tokens=0)]
+    ids, lp = sample(logits, rows)
+    ids = ids.tolist()
+    assert ids[0] == int(logits[0].argmax())
+    l1 = logits[1].clone(); l1[int(logits[1].argmax())] = float("-inf")
+    assert ids[1] == int(l1.argmax())
+    assert 1000 <= ids[2] < 2000 and ids[2] == 1000 + int(logits[2, 1000:2000].argmax())
+    assert ids[3] == int(logits[3].argmax())
+    top50 = set(torch.topk(logits[4], 50).indices.tolist())
+    assert ids[4] in top50
+    assert ids[5] != int(logits[5].argmax())            # the repeated token was pushed down
+    assert torch.isfinite(lp).all()
+    # sampling frequencies follow the distribution (top-k=4 -> 4 outcomes)
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0] + [-30.0] * 60], device=dev).repeat(2000, 1)
+    ids, _ = sample(small, [RowParams(temperature=1.0, top_k=4, seed=11, step=i) for i in range(2000)])
+    freq = torch.bincount(ids.long().cpu(), minlength=4)[:4].float() / 2000
+    ref = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0)
+    assert (freq - ref).abs().max().item() < 0.05

@@ -26,13 +26,17 @@ def _build(dtype, device, head_dim, heads):
     return m
 
 
-def _sp_worker(rank, world, backend, mode, dtype_name, head_dim, heads, tol):
+def _sp_worker(rank, world, backend, mode, dtype_name, head_dim, heads, tol, kind="ulysses"):
     from vllm_omni_b200.parallel import parallel_state as ps
+    from vllm_omni_b200.parallel.ring import RingJointAttention
     from vllm_omni_b200.parallel.ulysses import UlyssesJointAttention
     dtype = getattr(torch, dtype_name)
     device = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
     ps.init_distributed_environment(world, rank, local_rank=rank, backend=backend)
-    ps.initialize_model_parallel(sequence_parallel_size=world, ulysses_degree=world, backend=backend)
+    if kind == "ring":
+        ps.initialize_model_parallel(sequence_parallel_size=world, ring_degree=world, backend=backend)
+    else:
+        ps.initialize_model_parallel(sequence_parallel_size=world, ulysses_degree=world, backend=backend)
     m = _build(dtype, device, head_dim, heads)
     B, h, w, St = 2, 8, 8, 6 * world
     g = torch.Generator(device="cpu").manual_seed(2)
@@ -41,7 +45,10 @@ def _sp_worker(rank, world, backend, mode, dtype_name, head_dim, heads, tol):
     t = torch.tensor([0.6, 0.6], device=device)
     lens = [St, St - 3]
     ref = m(x, e, t, (1, h, w), txt_seq_lens=lens).float()
-    m.sp = UlyssesJointAttention(ps.get_sp_group().ulysses, heads, head_dim, mode=mode)
+    if kind == "ring":
+        m.sp = RingJointAttention(ps.get_sp_group().ring, heads, head_dim, mode=mode)
+    else:
+        m.sp = UlyssesJointAttention(ps.get_sp_group().ulysses, heads, head_dim, mode=mode)
     Si, Sl = h * w // world, St // world
     y = m(x[:, rank * Si:(rank + 1) * Si].contiguous(), e[:, rank * Sl:(rank + 1) * Sl].contiguous(), t, (1, h, w),
           txt_seq_lens=lens).float()
@@ -57,6 +64,17 @@ def _sp_worker(rank, world, backend, mode, dtype_name, head_dim, heads, tol):
 
 def test_ulysses_matches_single_rank_cpu_gloo():
     run_distributed(_sp_worker, 2, "gloo", args=("gloo", "nccl", "float32", 32, 4, 2e-4))
+
+
+def test_ring_matches_single_rank_cpu_gloo():
+    run_distributed(_sp_worker, 2, "gloo", args=("gloo", "nccl", "float32", 32, 4, 2e-4, "ring"))
+
+
+@pytest.mark.gpu
+def test_ring_peer_kv_matches_single_rank_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_distributed(_sp_worker, 2, "nccl", args=("nccl", "peer", "bfloat16", 128, 4, 0.06, "ring"))
 
 
 @pytest.mark.gpu

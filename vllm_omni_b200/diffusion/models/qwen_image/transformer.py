@@ -313,7 +313,9 @@ class QwenImageTransformer2DModel(nn.Module):
         st.mods, st.ss = e(1, L, 2, 6 * D), e(1, 2 * D)
         st.out = e(B, S_img, cfg.patch_size * cfg.patch_size * cfg.out_channels)
         st.graph = None
-        st.use_graph = bool(use_graph) and dev.type == "cuda" and self.block_hook is None
+        # library collectives (the NCCL baseline mode) are not captured: only our own kernels are
+        nccl_sp = self.sp is not None and getattr(self.sp, "mode", "") == "nccl"
+        st.use_graph = bool(use_graph) and dev.type == "cuda" and self.block_hook is None and not nccl_sp
         return st
 
     def _step_body(self, st: "DenoiseLoopState"):

@@ -1,0 +1,125 @@
+"""Ring / peer-KV attention for sequence parallelism (K5).
+
+Each rank owns S/P rows (image and text sharded alike) and ALL heads.  Attention over the full
+sequence = merge of P partial attentions, one per K/V shard:
+    out = out - sigmoid(lse_b - lse) * (out - out_b),   lse = lse - logsigmoid(lse - lse_b)
+(the update rule of vllm_omni/diffusion/attention/backends/ring/ring_utils.py:79-80).
+
+``mode="peer"`` (GPU): every rank publishes its K/V shard in symmetric peer memory once per
+layer; behind NVSwitch there is no ring to walk — each rank's attention kernel reads the
+shard of rank (r + step) mod P straight from that peer through TMA descriptors built on the
+peer pointer (plain, non-multicast loads), one kernel launch per shard, LSE-merged.  One
+bounded-wait barrier before (shards written) and one after (shards consumed) per layer.
+``mode="nccl"``: classic ring with batched isend/irecv of K and V (the baseline; also the CPU
+test path).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import fused
+from ..ops.attention import attention
+from .comm import RingComm
+
+
+def merge_attention(out, lse, out_b, lse_b):
+    """Numerically stable merge of two partial attentions.  out: [B,S,H,D] fp32, lse: [B,H,S]."""
+    if out is None:
+        return out_b.float(), lse_b
+    l, lb = lse.transpose(1, 2).unsqueeze(-1), lse_b.transpose(1, 2).unsqueeze(-1)     # [B,S,H,1]
+    new_out = out - torch.sigmoid(lb - l) * (out - out_b.float())
+    new_lse = lse - F.logsigmoid(lse - lse_b)
+    return new_out, new_lse
+
+
+class RingJointAttention:
+    def __init__(self, group, num_heads: int, head_dim: int, mode: str | None = None):
+        self.group = group
+        self.P, self.rank = group.world_size, group.rank_in_group
+        self.H, self.Dh = num_heads, head_dim
+        self.mode = mode or ("peer" if torch.cuda.is_available() else "nccl")
+        self.arena = None
+        self._key = None
+
+    def setup(self, B, Si_loc, St_loc, device, dtype):
+        key = (B, Si_loc, St_loc, str(device), dtype)
+        if self._key == key:
+            return
+        self._key = key
+        self.B, self.Si_loc, self.St_loc = B, Si_loc, St_loc
+        self.S_loc = Si_loc + St_loc
+        self.S_img, self.S_txt = Si_loc * self.P, St_loc * self.P
+        HD = self.H * self.Dh
+        if self.mode == "peer":
+            from .peer_memory import PeerArena
+            if self.arena is not None:
+                self.arena.close()
+            es = torch.empty(0, dtype=dtype).element_size()
+            self.arena = PeerArena(self.group, B * self.S_loc * 3 * HD * es + 8192, device)
+            self.qkv = self.arena.alloc((B, self.S_loc, 3 * HD), dtype)
+            self.qkv_local = self.qkv.local
+        else:
+            self.qkv_local = torch.empty(B, self.S_loc, 3 * HD, dtype=dtype, device=device)
+        self.attn = torch.empty(B, self.S_loc, HD, dtype=dtype, device=device)
+
+    # same interface as UlyssesJointAttention --------------------------------------------
+    def project_qkv(self, img_lin, xn_img, txt_lin, xn_txt):
+        HD, B = self.H * self.Dh, self.B
+        bs = self.S_loc * 3 * HD
+        img_lin(xn_img, out=self.qkv_local[:, :self.Si_loc], out_rows_per_batch=self.Si_loc, out_batch_stride=bs)
+        if self.St_loc:
+            txt_lin(xn_txt, out=self.qkv_local[:, self.Si_loc:], out_rows_per_batch=self.St_loc, out_batch_stride=bs)
+
+    def norm_rope(self, wq, wk, wq_txt, wk_txt, cos, sin, eps):
+        # local rows: image rows r*Si_loc.., text rows S_img + r*St_loc.. of the global table
+        r = self.rank
+        idx = torch.cat([torch.arange(r * self.Si_loc, (r + 1) * self.Si_loc),
+                         torch.arange(self.S_img + r * self.St_loc, self.S_img + (r + 1) * self.St_loc)]).to(cos.device)
+        fused.qk_norm_rope_(self.qkv_local, self.H, self.H, self.Dh, wq=wq, wk=wk, wq_alt=wq_txt, wk_alt=wk_txt,
+                            s_alt=self.Si_loc, cos=cos[idx].contiguous(), sin=sin[idx].contiguous(), interleaved=True,
+                            eps=eps)
+
+    def _shard_kv_lens(self, kv_lens, src_rank):
+        """Valid keys inside the shard of ``src_rank``: all image rows, text rows below the length."""
+        if kv_lens is None:
+            return None
+        txt_valid = (kv_lens - self.S_img - src_rank * self.St_loc).clamp(0, self.St_loc)
+        return (self.Si_loc + txt_valid).to(torch.int32)
+
+    def attend(self, kv_lens, ws):
+        B, HD = self.B, self.H * self.Dh
+        q5 = self.qkv_local.view(B, self.S_loc, 3, self.H, self.Dh)
+        q = q5[:, :, 0]
+        out = lse = None
+        if self.mode == "peer":
+            from .peer_memory import tensor_from_ptr
+            self.arena.barrier()                                  # every rank's K/V shard is in place
+            for step in range(self.P):
+                src = (self.rank + step) % self.P
+                kv = tensor_from_ptr(self.qkv.ptrs[src], (B, self.S_loc, 3, self.H, self.Dh), self.qkv_local.dtype,
+                                     self.qkv_local.device)
+                o_b, lse_b = attention(q, kv[:, :, 1], kv[:, :, 2], kv_lens=self._shard_kv_lens(kv_lens, src),
+                                       return_lse=True)
+                out, lse = merge_attention(out, lse, o_b, lse_b)
+            self.arena.barrier()                                  # shards may be overwritten by the next layer
+        else:
+            comm = RingComm(self.group.device_group)
+            k, v = q5[:, :, 1].contiguous(), q5[:, :, 2].contiguous()
+            for step in range(self.P):
+                src = (self.rank - step) % self.P
+                if step + 1 < self.P:
+                    nk, nv_ = comm.send_recv(k), comm.send_recv(v)
+                    comm.commit()
+                o_b, lse_b = attention(q, k, v, kv_lens=self._shard_kv_lens(kv_lens, src), return_lse=True)
+                out, lse = merge_attention(out, lse, o_b, lse_b)
+                if step + 1 < self.P:
+                    comm.wait()
+                    k, v = nk, nv_
+        self.attn.copy_(out.reshape(B, self.S_loc, HD))
+        return self.attn[:, :self.Si_loc], self.attn[:, self.Si_loc:]
+
+    def close(self):
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None
