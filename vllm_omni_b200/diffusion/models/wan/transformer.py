@@ -1,0 +1,223 @@
+"""Wan2.x-style video DiT on the fused sm_100a ops.
+
+Structure of ``WanTransformer3DModel`` (vllm_omni/diffusion/models/wan2_2/wan2_2_transformer.py:
+728-990): (1,2,2) patch embedding, text MLP, timestep MLP whose 6*D projection is added to a
+learned ``scale_shift_table`` per block, 40 blocks of [modulated LayerNorm -> self attention
+with RMSNorm over the full q/k width and 3-D RoPE -> gated residual; LayerNorm -> cross attention
+to the text tokens -> residual; modulated LayerNorm -> GELU FFN -> gated residual], modulated
+output norm and projection.  Sequence parallelism shards the video tokens; cross attention stays
+local because the text is replicated.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ....ops import fused
+from ....ops.attention import attention
+from ...layers.linear import FusedLinear
+from ..qwen_image.transformer import timestep_sinusoid
+
+
+@dataclass
+class WanTransformerConfig:
+    patch_size: tuple = (1, 2, 2)
+    num_attention_heads: int = 40
+    attention_head_dim: int = 128
+    in_channels: int = 16
+    out_channels: int = 16
+    text_dim: int = 4096
+    freq_dim: int = 256
+    ffn_dim: int = 13824
+    num_layers: int = 40
+    eps: float = 1e-6
+    rope_max_seq_len: int = 1024
+
+    @property
+    def inner_dim(self):
+        return self.num_attention_heads * self.attention_head_dim
+
+    @classmethod
+    def from_dict(cls, d):
+        keys = set(cls.__dataclass_fields__)
+        return cls(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items() if k in keys})
+
+
+def wan_rope_angles(f: int, h: int, w: int, head_dim: int, theta: float = 10000.0) -> torch.Tensor:
+    """[f*h*w, head_dim/2] angles: the frequency range is split (d - 2*(d//3), d//3, d//3) over
+    (frame, height, width)."""
+    d = head_dim
+    dh = dw = 2 * (d // 6)
+    dt = d - dh - dw
+
+    def ang(n, dim):
+        inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+        return torch.outer(torch.arange(n, dtype=torch.float32), inv)
+    a = torch.cat([ang(f, dt)[:, None, None, :].expand(f, h, w, -1), ang(h, dh)[None, :, None, :].expand(f, h, w, -1),
+                   ang(w, dw)[None, None, :, :].expand(f, h, w, -1)], dim=-1)
+    return a.reshape(f * h * w, d // 2)
+
+
+class WanBlock(nn.Module):
+    def __init__(self, cfg: WanTransformerConfig, dtype, device):
+        super().__init__()
+        D = cfg.inner_dim
+        P = lambda *s: nn.Parameter(torch.ones(*s, dtype=dtype, device=device), requires_grad=False)
+        self.scale_shift_table = nn.Parameter(torch.randn(6, D, dtype=dtype, device=device) / D ** 0.5,
+                                              requires_grad=False)
+        self.attn1_qkv = FusedLinear(D, 3 * D, dtype=dtype, device=device)
+        self.attn1_norm_q, self.attn1_norm_k = P(D), P(D)
+        self.attn1_out = FusedLinear(D, D, dtype=dtype, device=device)
+        self.norm2_w = P(D)
+        self.norm2_b = nn.Parameter(torch.zeros(D, dtype=dtype, device=device), requires_grad=False)
+        self.attn2_q = FusedLinear(D, D, dtype=dtype, device=device)
+        self.attn2_kv = FusedLinear(D, 2 * D, dtype=dtype, device=device)
+        self.attn2_norm_q, self.attn2_norm_k = P(D), P(D)
+        self.attn2_out = FusedLinear(D, D, dtype=dtype, device=device)
+        self.ffn_up = FusedLinear(D, cfg.ffn_dim, dtype=dtype, device=device)
+        self.ffn_down = FusedLinear(cfg.ffn_dim, D, dtype=dtype, device=device)
+
+
+class WanTransformer3DModel(nn.Module):
+    def __init__(self, cfg: WanTransformerConfig | None = None, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.cfg = cfg = cfg or WanTransformerConfig()
+        self.dtype_ = dtype
+        D = cfg.inner_dim
+        pt, ph, pw = cfg.patch_size
+        self.patch_embedding = FusedLinear(cfg.in_channels * pt * ph * pw, D, dtype=dtype, device=device)
+        self.text_1 = FusedLinear(cfg.text_dim, D, dtype=dtype, device=device)
+        self.text_2 = FusedLinear(D, D, dtype=dtype, device=device)
+        self.time_1 = FusedLinear(cfg.freq_dim, D, dtype=dtype, device=device)
+        self.time_2 = FusedLinear(D, D, dtype=dtype, device=device)
+        self.time_proj = FusedLinear(D, 6 * D, dtype=dtype, device=device)
+        self.blocks = nn.ModuleList([WanBlock(cfg, dtype, device) for _ in range(cfg.num_layers)])
+        self.out_table = nn.Parameter(torch.randn(2, D, dtype=dtype, device=device) / D ** 0.5, requires_grad=False)
+        self.proj_out = FusedLinear(D, cfg.out_channels * pt * ph * pw, dtype=dtype, device=device)
+        self.sp = None
+        self.block_hook = None
+        self._rope = {}
+
+    # -------------------------------------------------------------- patchify
+    def patchify(self, x):          # [B, C, T, H, W] -> [B, S, C*pt*ph*pw], grid
+        pt, ph, pw = self.cfg.patch_size
+        B, C, T, H, W = x.shape
+        g = (T // pt, H // ph, W // pw)
+        x = x.view(B, C, g[0], pt, g[1], ph, g[2], pw).permute(0, 2, 4, 6, 1, 3, 5, 7)
+        return x.reshape(B, g[0] * g[1] * g[2], C * pt * ph * pw), g
+
+    def unpatchify(self, y, g):     # inverse
+        pt, ph, pw = self.cfg.patch_size
+        B = y.shape[0]
+        C = self.cfg.out_channels
+        y = y.view(B, g[0], g[1], g[2], C, pt, ph, pw).permute(0, 4, 1, 5, 2, 6, 3, 7)
+        return y.reshape(B, C, g[0] * pt, g[1] * ph, g[2] * pw)
+
+    def rope(self, g, device):
+        key = (g, str(device))
+        if key not in self._rope:
+            a = wan_rope_angles(*g, self.cfg.attention_head_dim)
+            self._rope[key] = (a.cos().contiguous().to(device), a.sin().contiguous().to(device))
+        return self._rope[key]
+
+    # -------------------------------------------------------------- forward
+    def block_forward(self, blk: WanBlock, x, ctx, e6, cos, sin):
+        """x [B,S,D] in place; ctx [B,L,D] text; e6 [B,6,D] = temb projection."""
+        cfg = self.cfg
+        D, H, Dh = cfg.inner_dim, cfg.num_attention_heads, cfg.attention_head_dim
+        B, S, _ = x.shape
+        mod = (blk.scale_shift_table[None].float() + e6.float()).to(x.dtype).reshape(B, 6 * D)
+        xn = fused.norm_modulate(x, shift=mod[:, 0:D], scale=mod[:, D:2 * D], eps=cfg.eps)
+        qkv = blk.attn1_qkv(xn)                                              # [B,S,3D]
+        q = fused.norm_modulate(qkv[..., :D].contiguous(), weight=blk.attn1_norm_q, rms=True, eps=cfg.eps)
+        k = fused.norm_modulate(qkv[..., D:2 * D].contiguous(), weight=blk.attn1_norm_k, rms=True, eps=cfg.eps)
+        qk = torch.cat([q, k, qkv[..., 2 * D:]], dim=-1).contiguous()
+        fused.qk_norm_rope_(qk, H, H, Dh, cos=cos, sin=sin, interleaved=True, eps=cfg.eps)
+        q5 = qk.view(B, S, 3, H, Dh)
+        o = attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2]).reshape(B, S, D)
+        blk.attn1_out(o, residual=x, gate=mod[:, 2 * D:3 * D], out=x)
+        xn = fused.norm_modulate(x, weight=blk.norm2_w, bias=blk.norm2_b, eps=cfg.eps)
+        q = fused.norm_modulate(blk.attn2_q(xn), weight=blk.attn2_norm_q, rms=True, eps=cfg.eps)
+        kv = blk.attn2_kv(ctx)
+        L = ctx.shape[1]
+        k2 = fused.norm_modulate(kv[..., :D].contiguous(), weight=blk.attn2_norm_k, rms=True, eps=cfg.eps)
+        o = attention(q.view(B, S, H, Dh), k2.view(B, L, H, Dh), kv[..., D:].reshape(B, L, H, Dh)).reshape(B, S, D)
+        blk.attn2_out(o, residual=x, out=x)
+        xn = fused.norm_modulate(x, shift=mod[:, 3 * D:4 * D], scale=mod[:, 4 * D:5 * D], eps=cfg.eps)
+        blk.ffn_down(blk.ffn_up(xn, act="gelu_tanh"), residual=x, gate=mod[:, 5 * D:6 * D], out=x)
+        return x
+
+    def forward(self, hidden_states, timestep, encoder_hidden_states, **_):
+        """hidden_states [B, C, T, H, W]; timestep [B] (0..1000); encoder_hidden_states [B, L, text_dim]."""
+        cfg, D = self.cfg, self.cfg.inner_dim
+        tokens, g = self.patchify(hidden_states.to(self.dtype_))
+        B = tokens.shape[0]
+        x = self.patch_embedding(tokens.contiguous())
+        cos, sin = self.rope(g, x.device)
+        ctx = self.text_2(self.text_1(encoder_hidden_states.to(self.dtype_), act="gelu_tanh"))
+        temb = self.time_2(self.time_1(timestep_sinusoid(timestep, cfg.freq_dim, scale=1.0).to(self.dtype_), act="silu"))
+        e6 = self.time_proj(F.silu(temb)).view(B, 6, D)
+        if self.block_hook is not None:
+            x = self.block_hook(self, x, ctx, e6, cos, sin)
+        else:
+            for blk in self.blocks:
+                self.block_forward(blk, x, ctx, e6, cos, sin)
+        om = (self.out_table[None].float() + temb[:, None].float()).to(x.dtype)      # [B,2,D]: shift, scale
+        xn = fused.norm_modulate(x, shift=om[:, 0].contiguous(), scale=om[:, 1].contiguous(), eps=cfg.eps)
+        return self.unpatchify(self.proj_out(xn), g)
+
+    @torch.no_grad()
+    def load_weights(self, weights) -> set:
+        """diffusers ``WanTransformer3DModel`` names; q/k/v and k/v are stacked into the fused
+        projections."""
+        cfg, D = self.cfg, self.cfg.inner_dim
+        params = dict(self.named_parameters())
+        simple = {"condition_embedder.text_embedder.linear_1": "text_1", "condition_embedder.text_embedder.linear_2": "text_2",
+                  "condition_embedder.time_embedder.linear_1": "time_1", "condition_embedder.time_embedder.linear_2": "time_2",
+                  "condition_embedder.time_proj": "time_proj", "proj_out": "proj_out"}
+        loaded = set()
+        for name, w in weights:
+            tgt, sl = None, None
+            base, _, leaf = name.rpartition(".")
+            if base in simple:
+                tgt = f"{simple[base]}.{leaf}"
+            elif name == "patch_embedding.weight":
+                tgt, w = "patch_embedding.weight", w.reshape(w.shape[0], -1)
+            elif name == "patch_embedding.bias":
+                tgt = "patch_embedding.bias"
+            elif name == "scale_shift_table":
+                tgt, w = "out_table", w.reshape(2, D)
+            elif name.startswith("blocks."):
+                p = name.split(".")
+                i, rest = int(p[1]), ".".join(p[2:])
+                pre = f"blocks.{i}."
+                qkv = {"attn1.to_q": 0, "attn1.to_k": 1, "attn1.to_v": 2}
+                kv = {"attn2.to_k": 0, "attn2.to_v": 1}
+                b2, _, lf = rest.rpartition(".")
+                if b2 in qkv:
+                    tgt, sl = pre + f"attn1_qkv.{lf}", (qkv[b2] * D, (qkv[b2] + 1) * D)
+                elif b2 in kv:
+                    tgt, sl = pre + f"attn2_kv.{lf}", (kv[b2] * D, (kv[b2] + 1) * D)
+                else:
+                    m = {"attn1.to_out.0": "attn1_out", "attn2.to_q": "attn2_q", "attn2.to_out.0": "attn2_out",
+                         "ffn.net.0.proj": "ffn_up", "ffn.net.2": "ffn_down"}
+                    if b2 in m:
+                        tgt = pre + f"{m[b2]}.{lf}"
+                    elif rest == "scale_shift_table":
+                        tgt, w = pre + "scale_shift_table", w.reshape(6, D)
+                    elif rest in ("attn1.norm_q.weight", "attn1.norm_k.weight", "attn2.norm_q.weight", "attn2.norm_k.weight"):
+                        tgt = pre + rest.replace(".norm_", "_norm_").replace(".weight", "")
+                    elif rest == "norm2.weight":
+                        tgt = pre + "norm2_w"
+                    elif rest == "norm2.bias":
+                        tgt = pre + "norm2_b"
+            if tgt is None or tgt not in params:
+                continue
+            dst = params[tgt] if sl is None else params[tgt][sl[0]:sl[1]]
+            dst.copy_(w.to(dst.dtype).reshape(dst.shape))
+            loaded.add(name)
+        return loaded
