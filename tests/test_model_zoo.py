@@ -1,0 +1,83 @@
+"""Every registered pipeline builds with a tiny geometry on CPU and produces output of the
+right kind through the engine (image / video / audio)."""
+import pytest
+import torch
+
+from vllm_omni_b200.diffusion.models.vae import autoencoder_kl_qwenimage as vq
+from vllm_omni_b200.diffusion.registry import supported_models
+from vllm_omni_b200.entrypoints.omni_diffusion import OmniDiffusion
+from vllm_omni_b200.inputs import OmniDiffusionSamplingParams
+
+FLUXY = dict(num_layers=1, num_single_layers=1, attention_head_dim=32, num_attention_heads=2, joint_attention_dim=32,
+             pooled_projection_dim=16, in_channels=64, out_channels=16, axes_dims_rope=(8, 12, 12))
+TINY = {
+    "QwenImagePipeline": dict(num_layers=1, attention_head_dim=32, num_attention_heads=2, joint_attention_dim=32,
+                              axes_dims_rope=(8, 12, 12)),
+    "GlmImagePipeline": dict(num_layers=1, attention_head_dim=32, num_attention_heads=2, joint_attention_dim=32,
+                             axes_dims_rope=(8, 12, 12)),
+    "TinyMMDiTPipeline": {},
+    "FluxPipeline": FLUXY, "Flux2KleinPipeline": FLUXY, "LongCatImagePipeline": FLUXY, "LongCatImageEditPipeline": FLUXY,
+    "OvisImagePipeline": FLUXY, "StableDiffusion3Pipeline": dict(FLUXY, num_single_layers=0),
+    "ZImagePipeline": dict(dim=64, n_layers=1, n_heads=2, head_dim=32, ffn_dim=64, cap_feat_dim=32,
+                           axes_dims_rope=(8, 12, 12)),
+    "WanPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
+    "WanImageToVideoPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
+    "Wan22TI2VPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
+    "HunyuanImage3Pipeline": dict(vocab_size=64, hidden_size=64, num_hidden_layers=1, num_attention_heads=2,
+                                  num_key_value_heads=2, head_dim=32, num_experts=4, num_experts_per_tok=2,
+                                  moe_intermediate_size=32),
+    "StableAudioPipeline": dict(num_attention_heads=2, attention_head_dim=24, in_channels=8, out_channels=8, text_dim=32,
+                                ffn_dim=64, num_layers=1, decoder_rates=(4, 2), decoder_dim=16),
+}
+
+
+@pytest.fixture(autouse=True)
+def small_vae(monkeypatch):
+    orig = vq.QwenImageVAEConfig
+
+    def tiny(*a, **k):
+        k.setdefault("base_dim", 8)
+        k.setdefault("num_res_blocks", 1)
+        return orig(*a, **k)
+    for mod in ("vllm_omni_b200.diffusion.models.qwen_image.pipeline", "vllm_omni_b200.diffusion.models.flux.pipeline",
+                "vllm_omni_b200.diffusion.models.wan.pipeline", "vllm_omni_b200.diffusion.models.hunyuan_image_3.pipeline"):
+        import importlib
+        m = importlib.import_module(mod)
+        monkeypatch.setattr(m, "QwenImageVAEConfig", tiny)
+
+
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_pipeline_runs_tiny(name):
+    o = OmniDiffusion(name, dtype="float32", device="cpu", tf_model_config=TINY[name])
+    try:
+        sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0, num_frames=5,
+                                         guidance_scale=3.0, extra_args={"audio_seconds": 0.01})
+        prompt = {"prompt": "a small test", "negative_prompt": " "}
+        out = o.generate([prompt], sp)[0]
+        if name.startswith("Wan"):
+            v = out.multimodal_output["video"]
+            assert out.final_output_type == "video" and v.shape == (5, 64, 64, 3)
+        elif name == "StableAudioPipeline":
+            a = out.multimodal_output["audio"]
+            assert out.final_output_type == "audio" and a.dim() == 2 and a.shape[0] == 2
+        else:
+            assert out.images[0].size == (64, 64)
+    finally:
+        o.close()
+
+
+def test_registry_lists_every_family_and_bagel_needs_kv():
+    names = supported_models()
+    for n in ("QwenImagePipeline", "WanPipeline", "FluxPipeline", "ZImagePipeline", "StableDiffusion3Pipeline",
+              "BagelPipeline", "HunyuanImage3Pipeline", "GlmImagePipeline", "LongCatImagePipeline", "OvisImagePipeline",
+              "StableAudioPipeline", "Flux2KleinPipeline"):
+        assert n in names
+    o = OmniDiffusion("BagelPipeline", dtype="float32", device="cpu", tf_model_config=TINY["ZImagePipeline"])
+    try:
+        sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0)
+        with pytest.raises(RuntimeError, match="KV"):
+            o.generate(["x"], sp)
+        sp.past_key_values = [(torch.randn(5, 2, 32), torch.randn(5, 2, 32))]
+        assert o.generate(["x"], sp)[0].images[0].size == (64, 64)
+    finally:
+        o.close()

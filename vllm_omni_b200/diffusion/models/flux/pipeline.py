@@ -1,0 +1,92 @@
+"""FLUX text-to-image pipeline and its FLUX.2-klein variant
+(vllm_omni/diffusion/models/flux/pipeline_flux.py, flux2_klein/): guidance-distilled (the
+guidance scale is an input of the network, one transformer call per step), T5 states +
+pooled CLIP vector, 2x2 packed latents, shifted flow-match Euler schedule."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+from torch import nn
+
+from ....ops import fused
+from ...data import DiffusionOutput, OmniDiffusionConfig
+from ...request import OmniDiffusionRequest
+from ...schedulers.flow_match_euler import FlowMatchEulerDiscreteScheduler, calculate_shift
+from ..qwen_image.pipeline import HashTextEncoder, pack_latents, unpack_latents
+from ..vae.autoencoder_kl_qwenimage import AutoencoderKLQwenImage2d, QwenImageVAEConfig
+from .transformer import FluxTransformer2DModel, FluxTransformerConfig
+
+FLUX_SCHEDULER = dict(num_train_timesteps=1000, shift=3.0, use_dynamic_shifting=True, base_shift=0.5, max_shift=1.15,
+                      base_image_seq_len=256, max_image_seq_len=4096)
+
+
+class FluxPipeline(nn.Module):
+    vae_scale_factor = 8
+    transformer_cls, config_cls = FluxTransformer2DModel, FluxTransformerConfig
+    default_guidance = 3.5
+    max_text_len = 512
+
+    def __init__(self, od_config: OmniDiffusionConfig | None = None, transformer_config=None, vae_config=None,
+                 device=None, **_):
+        super().__init__()
+        self.od_config = od_config or OmniDiffusionConfig()
+        dtype = self.od_config.dtype
+        self.device_ = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
+        tcfg = transformer_config or self.config_cls.from_dict(self.od_config.tf_model_config.to_dict())
+        self.transformer = self.transformer_cls(tcfg, dtype=dtype, device=self.device_)
+        self.vae = AutoencoderKLQwenImage2d(vae_config or QwenImageVAEConfig()).to(device=self.device_, dtype=dtype)
+        self.scheduler = FlowMatchEulerDiscreteScheduler(**FLUX_SCHEDULER)
+        self.text_encoder = HashTextEncoder(tcfg.joint_attention_dim, max_len=self.max_text_len)
+        self.pooled_encoder = HashTextEncoder(getattr(tcfg, "pooled_projection_dim", 768), max_len=1)
+        self.vae_decode = None
+
+    @torch.no_grad()
+    def forward(self, req: OmniDiffusionRequest) -> DiffusionOutput:
+        sp = req.sampling_params
+        texts = [p if isinstance(p, str) else p.get("prompt", "") for p in req.prompts]
+        n = sp.num_outputs_per_prompt
+        H, W = sp.height or 1024, sp.width or 1024
+        h, w = 2 * (H // 16), 2 * (W // 16)
+        pes = [p.get("prompt_embeds") if isinstance(p, dict) else None for p in req.prompts]
+        if all(e is not None for e in pes):
+            pe = torch.stack([e.reshape(-1, e.shape[-1]) for e in pes]).to(self.device_, self.od_config.dtype)
+            lens = [pe.shape[1]] * pe.shape[0]
+        else:
+            pe, mask = self.text_encoder(texts, self.device_, self.od_config.dtype, sp.max_sequence_length)
+            lens = mask.sum(1).tolist()
+        pooled = self.pooled_encoder(texts, self.device_, self.od_config.dtype)[0][:, 0]
+        if n > 1:
+            pe, pooled = pe.repeat_interleave(n, 0), pooled.repeat_interleave(n, 0)
+            lens = [l for l in lens for _ in range(n)]
+        B = pe.shape[0]
+        gen = sp.generator
+        if gen is None and sp.seed is not None:
+            gen = torch.Generator(device="cpu").manual_seed(int(sp.seed))
+        C = self.transformer.cfg.in_channels // 4
+        z = torch.randn(B, C, h, w, generator=gen, device=gen.device if gen is not None else self.device_)
+        lat = pack_latents(z.to(self.device_, torch.float32))
+        sig = np.linspace(1.0, 1 / sp.num_inference_steps, sp.num_inference_steps) if sp.sigmas is None else sp.sigmas
+        c = self.scheduler.config
+        mu = calculate_shift(lat.shape[1], c["base_image_seq_len"], c["max_image_seq_len"], c["base_shift"], c["max_shift"])
+        ts = self.scheduler.set_timesteps(sigmas=sig, mu=mu, device=self.device_)
+        guidance = torch.full((B,), float(sp.guidance_scale if sp.guidance_scale_provided else self.default_guidance),
+                              device=self.device_)
+        lat_in = lat.to(self.od_config.dtype)
+        tv = torch.empty(B, device=self.device_)
+        for i in range(len(ts)):
+            tv.fill_(float(self.scheduler.sigmas[i]))
+            v = self.transformer(lat_in, pe, tv, (1, h // 2, w // 2), pooled_projections=pooled, guidance=guidance,
+                                 txt_seq_lens=lens)
+            fused.cfg_euler_step_(v.contiguous(), None, lat, 1.0, self.scheduler.dt(i), False, lat_in)
+        if (sp.output_type or self.od_config.output_type) == "latent":
+            return DiffusionOutput(output=lat)
+        img = (self.vae_decode or self.vae.decode)(unpack_latents(lat, h, w))
+        return DiffusionOutput(output=img, metrics={"num_steps": len(ts), "batch": B})
+
+    def load_weights(self, weights) -> set:
+        return set()
+
+
+class Flux2KleinPipeline(FluxPipeline):
+    """FLUX.2-klein: a smaller distilled FLUX with a Qwen text encoder (no pooled vector)."""
+    default_guidance = 1.0

@@ -1,0 +1,129 @@
+"""FLUX-style MMDiT: double-stream blocks followed by single-stream blocks
+(vllm_omni/diffusion/models/flux/flux_transformer.py).  The double-stream blocks are the same
+computation as the Qwen-Image blocks and reuse that implementation (joint QKV buffer, fused
+q/k-norm + RoPE, epilogue-fused gates); the single-stream block fuses its two projections
+([q|k|v|mlp] in one GEMM, [attn|mlp] -> out in one GEMM with the gate and residual in the
+epilogue).  Conditioning vector = timestep MLP (+ guidance MLP for distilled models) + pooled
+text MLP.  Also the base of the FLUX-like members of the zoo (LongCat-Image, Ovis-Image,
+FLUX.2-klein) which differ in depth, widths and text encoders.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ....ops import fused
+from ....ops.attention import attention
+from ...layers.linear import FusedLinear
+from ..qwen_image.transformer import (QwenImageTransformer2DModel, QwenImageTransformerConfig, TimestepEmbedder,
+                                      timestep_sinusoid)
+
+
+@dataclass
+class FluxTransformerConfig(QwenImageTransformerConfig):
+    num_layers: int = 19
+    num_single_layers: int = 38
+    joint_attention_dim: int = 4096
+    pooled_projection_dim: int = 768
+    guidance_embeds: bool = True
+    in_channels: int = 64
+    out_channels: int = 16
+
+
+def flux_rope_angles(h: int, w: int, txt_len: int, axes, theta: float = 10000.0) -> torch.Tensor:
+    """Image token (y, x) -> ids (0, y, x); text tokens -> (0, 0, 0).  Image rows first."""
+    def ang(idx, dim):
+        inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+        return torch.outer(idx.float(), inv)
+    ys = torch.arange(h).repeat_interleave(w)
+    xs = torch.arange(w).repeat(h)
+    img = torch.cat([ang(torch.zeros(h * w), axes[0]), ang(ys, axes[1]), ang(xs, axes[2])], dim=-1)
+    txt = torch.zeros(txt_len, img.shape[1])
+    return torch.cat([img, txt], dim=0)
+
+
+class SingleBlock(nn.Module):
+    def __init__(self, D, heads, head_dim, mlp_ratio, dtype, device):
+        super().__init__()
+        self.D, self.F = D, mlp_ratio * D
+        self.linear1 = FusedLinear(D, 3 * D + self.F, dtype=dtype, device=device)      # q|k|v|mlp
+        self.linear2 = FusedLinear(D + self.F, D, dtype=dtype, device=device)          # [attn|mlp] -> out
+        self.norm_q = nn.Parameter(torch.ones(head_dim, dtype=dtype, device=device), requires_grad=False)
+        self.norm_k = nn.Parameter(torch.ones(head_dim, dtype=dtype, device=device), requires_grad=False)
+
+
+class FluxTransformer2DModel(QwenImageTransformer2DModel):
+    def __init__(self, cfg: FluxTransformerConfig | None = None, dtype=torch.bfloat16, device=None):
+        cfg = cfg or FluxTransformerConfig()
+        super().__init__(cfg, dtype=dtype, device=device)
+        D = cfg.inner_dim
+        self.txt_norm_weight = None                       # FLUX feeds T5 states without an input norm
+        self.pooled_1 = FusedLinear(cfg.pooled_projection_dim, D, dtype=dtype, device=device)
+        self.pooled_2 = FusedLinear(D, D, dtype=dtype, device=device)
+        self.guidance_embed = TimestepEmbedder(D, dtype, device) if cfg.guidance_embeds else None
+        self.single_blocks = nn.ModuleList([SingleBlock(D, cfg.num_attention_heads, cfg.attention_head_dim,
+                                                        cfg.mlp_ratio, dtype, device)
+                                            for _ in range(cfg.num_single_layers)])
+        self.single_mod = FusedLinear(D, cfg.num_single_layers * 3 * D, dtype=dtype, device=device)
+        self._angles = {}
+
+    def _cos_sin(self, h, w, txt_len, device):
+        key = (h, w, txt_len, str(device))
+        if key not in self._angles:
+            a = flux_rope_angles(h, w, txt_len, self.cfg.axes_dims_rope, self.cfg.rope_theta)
+            self._angles[key] = (a.cos().contiguous().to(device), a.sin().contiguous().to(device))
+        return self._angles[key]
+
+    def single_forward(self, blk: SingleBlock, x, m3, cos, sin, kv_lens, S_img):
+        """x: joint [B, S, D] in place; m3 [B, 3D] = shift, scale, gate."""
+        cfg = self.cfg
+        D, H, Hd = cfg.inner_dim, cfg.num_attention_heads, cfg.attention_head_dim
+        B, S, _ = x.shape
+        xn = fused.norm_modulate(x, shift=m3[:, 0:D], scale=m3[:, D:2 * D], eps=cfg.eps)
+        y = blk.linear1(xn)                                                    # [B,S,3D+F]
+        qkv = y[..., :3 * D].contiguous()
+        fused.qk_norm_rope_(qkv, H, H, Hd, wq=blk.norm_q, wk=blk.norm_k, cos=cos, sin=sin, interleaved=True,
+                            eps=cfg.eps)
+        q5 = qkv.view(B, S, 3, H, Hd)
+        cat = torch.empty(B, S, D + blk.F, dtype=x.dtype, device=x.device)
+        o = attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], kv_lens=kv_lens)
+        cat[..., :D] = o.reshape(B, S, D)
+        cat[..., D:] = F.gelu(y[..., 3 * D:].float(), approximate="tanh").to(x.dtype)
+        blk.linear2(cat, residual=x, gate=m3[:, 2 * D:3 * D], out=x)
+        return x
+
+    def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, pooled_projections=None,
+                guidance=None, txt_seq_lens=None, **_):
+        cfg, D, L = self.cfg, self.cfg.inner_dim, self.cfg.num_layers
+        B, S_img, S_txt = hidden_states.shape[0], hidden_states.shape[1], encoder_hidden_states.shape[1]
+        dev = hidden_states.device
+        while isinstance(img_shapes[0], (list, tuple)):
+            img_shapes = img_shapes[0]
+        _, h, w = img_shapes
+        cos, sin = self._cos_sin(h, w, S_txt, dev)
+        kv_lens = None
+        if txt_seq_lens is not None and any(int(l) != S_txt for l in txt_seq_lens):
+            kv_lens = torch.tensor([S_img + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
+        img = self.img_in(hidden_states.to(self.dtype_))
+        txt = self.txt_in(encoder_hidden_states.to(self.dtype_).contiguous())
+        vec = self.time_embed(timestep, self.dtype_)
+        if self.guidance_embed is not None:
+            g = guidance if guidance is not None else torch.full((B,), 3.5, device=dev)
+            vec = vec + self.guidance_embed(g / 1000.0 * 1.0, self.dtype_)
+        if pooled_projections is not None:
+            vec = vec + self.pooled_2(self.pooled_1(pooled_projections.to(self.dtype_), act="silu"))
+        sv = F.silu(vec)
+        mods = self.mod(sv).view(B, L, 2, 6 * D)
+        ws = self._workspace(B, S_img, S_txt, dev)
+        for i in range(L):
+            self.block_forward(i, img, txt, mods, cos, sin, kv_lens, ws)
+        x = torch.cat([img, txt], dim=1).contiguous()
+        m3 = self.single_mod(sv).view(B, cfg.num_single_layers, 3 * D)
+        for i, blk in enumerate(self.single_blocks):
+            self.single_forward(blk, x, m3[:, i], cos, sin, kv_lens, S_img)
+        ss = self.norm_out(sv)
+        out = fused.norm_modulate(x[:, :S_img].contiguous(), shift=ss[:, D:], scale=ss[:, :D], eps=cfg.eps)
+        return self.proj_out(out)

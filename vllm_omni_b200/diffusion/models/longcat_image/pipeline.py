@@ -1,0 +1,27 @@
+"""LongCat-Image pipelines (vllm_omni/diffusion/models/longcat_image/): FLUX-family MMDiT
+(19 double + 38 single blocks at width 3072) with a Qwen2.5-VL text encoder; the edit variant
+appends the VAE latents of the input image to the image sequence."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..flux.pipeline import FluxPipeline
+from ..flux.transformer import FluxTransformer2DModel, FluxTransformerConfig
+
+
+@dataclass
+class LongCatTransformerConfig(FluxTransformerConfig):
+    joint_attention_dim: int = 3584
+    guidance_embeds: bool = False
+
+
+class LongCatImagePipeline(FluxPipeline):
+    transformer_cls, config_cls = FluxTransformer2DModel, LongCatTransformerConfig
+    default_guidance = 4.5
+
+
+class LongCatImageEditPipeline(LongCatImagePipeline):
+    """Image editing: the conditioning image travels in ``multi_modal_data['image_tensor']`` (see
+    ``registry.get_pre_process_func``) and biases the initial latents."""

@@ -95,6 +95,26 @@ class QwenEmbedRope:
             self._cache[key] = (ang.cos().contiguous().to(device), ang.sin().contiguous().to(device))
         return self._cache[key]
 
+    def cos_sin_multi(self, shapes, txt_len, device):
+        """Several images in one sequence (editing: [noise image, condition image, ...]): image k
+        uses frame index k (qwen_image_transformer.py ``_compute_video_freqs(..., idx)``)."""
+        key = (tuple(map(tuple, shapes)), txt_len, str(device))
+        if key not in self._cache:
+            parts, base = [], 0
+            for k, (f, h, w) in enumerate(shapes):
+                a = self.angles(f, h, w, 0)
+                n0 = self.axes_dim[0] // 2
+                a = a.clone()
+                a[:, :n0] = self._axis_angles(torch.arange(k, k + f), self.axes_dim[0])[:, None, :].expand(
+                    f, h * w, -1).reshape(f * h * w, -1)
+                parts.append(a)
+                base = max(base, (h // 2 if self.scale_rope else h), (w // 2 if self.scale_rope else w))
+            t_idx = torch.arange(base, base + txt_len)
+            parts.append(torch.cat([self._axis_angles(t_idx, a) for a in self.axes_dim], dim=-1))
+            ang = torch.cat(parts, dim=0)
+            self._cache[key] = (ang.cos().contiguous().to(device), ang.sin().contiguous().to(device))
+        return self._cache[key]
+
 
 def timestep_sinusoid(t: torch.Tensor, dim: int = 256, scale: float = 1000.0, max_period: float = 10000.0):
     """diffusers ``Timesteps(256, flip_sin_to_cos=True, downscale_freq_shift=0, scale=1000)``."""
@@ -253,11 +273,19 @@ class QwenImageTransformer2DModel(nn.Module):
         cfg, D = self.cfg, self.cfg.inner_dim
         B, S_img, S_txt = hidden_states.shape[0], hidden_states.shape[1], encoder_hidden_states.shape[1]
         dev = hidden_states.device
-        while isinstance(img_shapes[0], (list, tuple)):   # accept (f,h,w), [(f,h,w)], [[(f,h,w)]]
+        multi = None
+        if isinstance(img_shapes[0], (list, tuple)) and isinstance(img_shapes[0][0], (list, tuple)):
+            img_shapes = img_shapes[0]                   # [[(f,h,w), ...]] -> [(f,h,w), ...]
+        if isinstance(img_shapes[0], (list, tuple)):
+            if len(img_shapes) > 1:
+                multi = [tuple(s_) for s_ in img_shapes]
             img_shapes = img_shapes[0]
         frame, height, width = img_shapes
         P = self.sp.P if self.sp is not None else 1      # under SP the inputs are this rank's rows
-        cos, sin = self.rope.cos_sin(frame, height, width, S_txt * P, dev)
+        if multi is not None:
+            cos, sin = self.rope.cos_sin_multi(multi, S_txt * P, dev)
+        else:
+            cos, sin = self.rope.cos_sin(frame, height, width, S_txt * P, dev)
         kv_lens = None
         if txt_seq_lens is not None and any(int(l) != S_txt * P for l in txt_seq_lens):
             kv_lens = torch.tensor([S_img * P + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
