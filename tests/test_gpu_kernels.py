@@ -181,3 +181,24 @@ def test_paged_decode(dev, H, Hkv, splits):
         assert (out[i].float() - ref[0, 0].float()).abs().max().item() < 0.03, i
         gk, gv = KC.kv_gather(kc, vc, bt[i], L)
         assert torch.equal(gk, ks[i]) and torch.equal(gv, vs[i])
+
+
+@pytest.mark.parametrize("M,N,K,act", [(300, 384, 512, None), (1024, 3072, 1024, "gelu_tanh"), (64, 136, 256, None)])
+def test_fp8_block_scaled_gemm(dev, M, N, K, act):
+    from vllm_omni_b200.diffusion.quantization import fp8
+    torch.manual_seed(4)
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+    w8, sw = fp8.quantize_weight_blockwise(w)
+    y = fp8.fp8_linear(x, (w8, sw), bias=bias, act=act, residual=res)
+    _status_ok(dev)
+    # oracle 1: the same quantised operands, dequantised and multiplied in fp32
+    ref = fp8.fp8_linear_reference(x.cpu(), w8.cpu(), sw.cpu(), bias.cpu(), act, res.cpu())
+    err = (y.float().cpu() - ref).abs().max().item()
+    assert err < 0.02 * max(1.0, ref.abs().max().item()), err
+    # oracle 2: the unquantised product; e4m3 with 128-wide scales stays within a few percent
+    full = fp8._epi(x.float().cpu() @ w.float().cpu().t(), bias.cpu(), act, res.cpu(), None)
+    rel = (y.float().cpu() - full).norm() / full.norm()
+    assert rel < 0.05, rel

@@ -26,7 +26,8 @@ def _run_paged(m, ids, device, chunks, decode_from):
     caches = [(torch.zeros(nb, bs, cfg.num_key_value_heads, cfg.head_dim, dtype=m.dtype_, device=device),
                torch.zeros(nb, bs, cfg.num_key_value_heads, cfg.head_dim, dtype=m.dtype_, device=device))
               for _ in range(cfg.num_hidden_layers)]
-    table = torch.arange(3, 3 + 8, dtype=torch.int32, device=device)
+    table = torch.arange(3, 3 + (ids.numel() + bs - 1) // bs, dtype=torch.int32, device=device)
+    assert int(table[-1]) < nb
     slot = lambda t: int(table[t // bs]) * bs + t % bs
     outs, done = [], 0
     for n in chunks:

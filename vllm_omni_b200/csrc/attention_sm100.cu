@@ -28,7 +28,7 @@ namespace omni {
 constexpr int ATT_D = 128;
 constexpr int ATT_BM = 128;   // rows per query tile
 constexpr int ATT_BN = 128;   // keys per KV tile
-constexpr int ATT_THREADS = 384;
+constexpr int ATT_THREADS = 640;  // TMA, MMA, 2 idle warps, 2 x 8 softmax warps
 constexpr int ATT_TILE_BYTES = ATT_BM * ATT_D * 2;  // 32 KiB
 constexpr int ATT_HALF_BYTES = ATT_TILE_BYTES / 2;  // one 64-wide TMA box
 constexpr int ATT_SMEM = 2 * ATT_TILE_BYTES /*Q*/ + 2 * ATT_TILE_BYTES /*K*/ + 2 * ATT_TILE_BYTES /*V*/ + 1024;
@@ -56,6 +56,61 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Packed pairs of fp32 in one 64-bit register (add/mul/fma.f32x2 issue once for two values).
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t r, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x for a pair, on the FMA and integer pipes: n = round(x), r = x - n in [-0.5, 0.5],
+// 2^r by a degree-3 polynomial (relative error 7.5e-5, far inside bf16's 2^-9), and n added
+// into the exponent field.  x is clamped at -126 so the exponent cannot wrap.
+__device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  x2 = pack2(x0, x1);
+  const uint64_t fl = add2(x2, pack2(12582912.f, 12582912.f));          // 1.5 * 2^23: integer in the low bits
+  const uint64_t n = add2(fl, pack2(-12582912.f, -12582912.f));
+  const uint64_t r = fma2(n, pack2(-1.f, -1.f), x2);
+  uint64_t p = fma2(pack2(0.0551716685f, 0.0551716685f), r, pack2(0.2426111251f, 0.2426111251f));
+  p = fma2(p, r, pack2(0.6932609677f, 0.6932609677f));
+  p = fma2(p, r, pack2(0.9999280572f, 0.9999280572f));
+  float p0, p1, f0, f1;
+  unpack2(p, p0, p1);
+  unpack2(fl, f0, f1);
+  p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(f0) << 23));
+  p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(f1) << 23));
+  return pack2(p0, p1);
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnOut out, int Sq, int Skv, int H, int Hkv,
@@ -65,6 +120,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
+  __shared__ float s_xmax[2][2][2][ATT_BM];  // [parity][tile][half][row]: partial row max / sum
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -88,7 +144,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(smem_u32(&v_full[i]), 1);
       mbar_init(smem_u32(&v_empty[i]), 1);
       mbar_init(smem_u32(&s_full[i]), 1);
-      mbar_init(smem_u32(&p_full[i]), 128);
+      mbar_init(smem_u32(&p_full[i]), 256);
       mbar_init(smem_u32(&o_done[i]), 1);
     }
     fence_mbar_init();
@@ -154,7 +210,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // ATT_HALF_BYTES apart
           const uint32_t addr = sV + st * ATT_TILE_BYTES + k * 2048;
           const uint64_t bd = umma_desc_sw128(addr, ATT_HALF_BYTES, 1024);
-          mma_f16_ts(d, p + k * 8, bd, idesc_pv, (j | k) != 0);
+          // P of keys [0, 64) sits in columns [0, 32) of the S block, keys [64, 128) in [64, 96)
+          mma_f16_ts(d, p + (k >> 2) * 64 + (k & 3) * 8, bd, idesc_pv, (j | k) != 0);
         }
       };
       mbar_wait(smem_u32(&q_full), 0, &s_abort, status, ERR_WAIT_FULL);
@@ -189,47 +246,70 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------- softmax + epilogue
-    const int t = (warp - 4) >> 2;       // query tile of this warpgroup
-    const int q = warp & 3;              // TMEM lane quadrant
+    // Eight warps per query tile: warps with the same (warp % 4) own the same 32 TMEM lanes
+    // (rows); the first of the pair takes S columns [0, 64), the second [64, 128).  The pair
+    // exchanges its partial row maxima through shared memory and a 64-thread named barrier.
+    const int t = (warp - 4) >> 3;       // query tile of this warp
+    const int q = warp & 3;              // TMEM lane quadrant this warp may access
+    const int hf = ((warp - 4) >> 2) & 1;  // column half
     const int row_in_tile = q * 32 + lane;
     const int srow = qblk * 2 * ATT_BM + t * ATT_BM + row_in_tile;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t tS = tmem_base + lane_addr + t * 128;
-    const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
+    const uint32_t tS = tmem_base + lane_addr + t * 128 + hf * 64;   // P overwrites the first 32 of these
+    const uint32_t tO = tmem_base + lane_addr + 256 + t * 128 + hf * 64;
+    const int bar_id = 1 + t * 4 + q;
+    const uint64_t scale2 = pack2(scale_log2, scale_log2);
     float m = -INFINITY;  // running maximum in log2 units that P and l are relative to
-    float l = 0.f;
+    uint64_t l2a = 0ull, l2b = 0ull;     // four partial row sums (two packed pairs) over this half
     for (int j = 0; j < n_kv; ++j) {
       mbar_wait(smem_u32(&s_full[t]), j & 1, &s_abort, status, ERR_WAIT_FULL);
       tc_fence_after_sync();
       const int row_limit = causal ? min(kv_len, srow + q_offset + 1) : kv_len;
-      const int valid = row_limit - j * ATT_BN;  // keys of this tile this row may see
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
+      const int valid = row_limit - j * ATT_BN - hf * 64;  // keys of this half-tile this row may see
+      const bool masked = valid < 64;
+      // pass 1: row maximum over this warp's 64 columns, four independent chains
+      float mx;
+      {
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(tS, va);
+        tmem_ld_32x32(tS + 32, vb);
         tmem_wait_ld();
-        if (valid >= ATT_BN) {
+        if (__any_sync(0xffffffffu, masked)) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (c * 32 + e < valid) mx = fmaxf(mx, __uint_as_float(v[e]));
+          for (int e = 0; e < 32; ++e) {
+            if (e >= valid) va[e] = 0xff800000u;  // -inf
+            if (e + 32 >= valid) vb[e] = 0xff800000u;
+          }
         }
+        float m0 = __uint_as_float(va[0]), m1 = __uint_as_float(va[1]);
+        float m2 = __uint_as_float(vb[0]), m3 = __uint_as_float(vb[1]);
+#pragma unroll
+        for (int e = 2; e < 32; e += 4) {
+          m0 = max3(m0, __uint_as_float(va[e]), __uint_as_float(va[e + 1]));
+          m2 = max3(m2, __uint_as_float(vb[e]), __uint_as_float(vb[e + 1]));
+          if (e + 2 < 32) {
+            m1 = max3(m1, __uint_as_float(va[e + 2]), __uint_as_float(va[e + 3]));
+            m3 = max3(m3, __uint_as_float(vb[e + 2]), __uint_as_float(vb[e + 3]));
+          }
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       }
-      mx *= scale_log2;
+      s_xmax[j & 1][t][hf][row_in_tile] = mx;
+      named_bar_sync(bar_id, 64);
+      mx = fmaxf(mx, s_xmax[j & 1][t][hf ^ 1][row_in_tile]) * scale_log2;
       const float m_new = fmaxf(m, mx);
-      // lazy rescale, decided per warp because tcgen05.ld/st are warp-wide
+      // lazy rescale, decided per warp because tcgen05.ld/st are warp-wide (both warps of a pair
+      // see the same m and mx, so they decide alike)
       const bool grow = m_new > m + 8.0f;
       if (j == 0) {
         m = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
         const float alpha = ex2(m - m_new);
-        l *= alpha;
+        const uint64_t alpha2 = pack2(alpha, alpha);
+        l2a = mul2(l2a, alpha2);
+        l2b = mul2(l2b, alpha2);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(tO + c * 32, v);
           tmem_wait_ld();
@@ -240,31 +320,62 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_wait_st();
         m = m_new;
       }
-      // pass 2: P = exp2(S * scale - m), written as packed bf16 over the S columns
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_wait_ld();
+      // pass 2: P = exp2(S * scale - m) as packed bf16 over the first half of this warp's S
+      // columns.  One pair in four goes through a degree-3 polynomial on the FMA pipe instead
+      // of the MUFU unit, which is otherwise as busy as the tensor pipe at head_dim 128.
+      const float m_use = m == -INFINITY ? 0.f : m;
+      const uint64_t negm2 = pack2(-m_use, -m_use);
+      auto softmax_chunk = [&](uint32_t (&v)[32], int c) {
+        if (__any_sync(0xffffffffu, masked)) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c * 32 + e >= valid) v[e] = 0xff800000u;
+        }
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = ex2(fmaf(__uint_as_float(v[e]), scale_log2, -m));
-          float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), scale_log2, -m));
-          if (valid < ATT_BN) {
-            if (c * 32 + e >= valid) p0 = 0.f;
-            if (c * 32 + e + 1 >= valid) p1 = 0.f;
+          const uint64_t x2 = fma2(pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), scale2, negm2);
+          float p0, p1;
+          uint64_t p2;
+          if ((e & 6) == 6) {
+            p2 = exp2_poly2(x2);
+            unpack2(p2, p0, p1);
+          } else {
+            unpack2(x2, p0, p1);
+            p0 = ex2(p0);
+            p1 = ex2(p1);
+            p2 = pack2(p0, p1);
           }
-          l += p0 + p1;
+          if (e & 2) l2b = add2(l2b, p2); else l2a = add2(l2a, p2);
           pk[e >> 1] = pack_bf16(p0, p1);
         }
         tmem_st_32x16(tS + c * 16, pk);
+      };
+      {
+        // the second chunk's load is in flight while the first is processed
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(tS, va);
+        tmem_wait_ld();
+        tmem_ld_32x32(tS + 32, vb);
+        softmax_chunk(va, 0);
+        tmem_wait_ld(vb);
+        softmax_chunk(vb, 1);
       }
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&p_full[t]));
     }
-    // epilogue: O / l -> bf16
+    // epilogue: O / l -> bf16; the row sum is the total of both halves
+    float l;
+    {
+      float a0, a1, b0, b1;
+      unpack2(l2a, a0, a1);
+      unpack2(l2b, b0, b1);
+      l = (a0 + a1) + (b0 + b1);
+      s_xmax[n_kv & 1][t][hf][row_in_tile] = l;
+      named_bar_sync(bar_id, 64);
+      l += s_xmax[n_kv & 1][t][hf ^ 1][row_in_tile];
+    }
     if (n_kv > 0) {
       mbar_wait(smem_u32(&o_done[t]), 0, &s_abort, status, ERR_WAIT_PV);
       tc_fence_after_sync();
@@ -280,16 +391,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int owner = srow / out.rows_per_rank;
         orow = out.o_peers[owner] + (long)b * out.o_bs + (long)(srow - owner * out.rows_per_rank) * out.o_rs + (long)h * out.o_hs;
       }
-      if (out.lse) out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
     } else if (srow < Sq) {
       if (out.o2 && srow >= out.split)
         orow = out.o2 + (long)b * out.o2_bs + (long)(srow - out.split) * out.o2_rs + (long)h * out.o2_hs;
       else
         orow = out.o + (long)b * out.o_bs + (long)srow * out.o_rs + (long)h * out.o_hs;
-      if (out.lse) out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
+    if (srow < Sq && out.lse && hf == 0)
+      out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       uint32_t v[32];
       if (n_kv > 0) {
         tmem_ld_32x32(tO + c * 32, v);
@@ -306,7 +417,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
           o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
           o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
+          *reinterpret_cast<uint4*>(orow + hf * 64 + c * 32 + g * 8) = o;
         }
       }
     }

@@ -67,66 +67,111 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long q_rs, const __nv_b
                     const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_tables, int max_blocks,
                     const int* __restrict__ seq_lens, int block_size, int Hkv, float scale_log2,
                     float* __restrict__ part_o, float* __restrict__ part_ml, int num_splits) {
+  // Half a warp (16 lanes x 8 dims, one 16-byte load per lane) owns one token; a warp handles two
+  // tokens per load instruction and two such instructions are in flight per iteration, so 8 half-
+  // warps x 2 = 16 tokens of K and V are being fetched per CTA at any time.
   const int seq = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int l16 = lane & 15, sub = lane >> 4;
+  const int grp = warp * 2 + sub;                 // 0..7: token stream of this half-warp
+  constexpr int NG = PD_WARPS * 2;
   const int len = seq_lens[seq];
   const int per = (len + num_splits - 1) / num_splits;
   const int t0 = split * per, t1 = min(len, t0 + per);
   const int H = Hkv * G;
-  float qv[G][4];
+  float qv[G][8];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const uint2 u = *reinterpret_cast<const uint2*>(q + (size_t)seq * q_rs + (size_t)(hk * G + g) * PD_D + lane * 4);
-    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
-    qv[g][0] = a.x * scale_log2; qv[g][1] = a.y * scale_log2; qv[g][2] = b.x * scale_log2; qv[g][3] = b.y * scale_log2;
-  }
-  float m[G], l[G], acc[G][4];
+    const uint4 u = *reinterpret_cast<const uint4*>(q + (size_t)seq * q_rs + (size_t)(hk * G + g) * PD_D + l16 * 8);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-  for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16(w[j]);
+      qv[g][2 * j] = f.x * scale_log2;
+      qv[g][2 * j + 1] = f.y * scale_log2;
+    }
+  }
+  float m[G], l[G], acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  }
   const int* bt = block_tables + (size_t)seq * max_blocks;
   const size_t row = (size_t)Hkv * PD_D;
-  for (int t = t0 + warp; t < t1; t += PD_WARPS) {
-    const size_t s = ((size_t)bt[t / block_size] * block_size + (t % block_size)) * row + (size_t)hk * PD_D + lane * 4;
-    const uint2 ku = *reinterpret_cast<const uint2*>(kc + s);
-    const uint2 vu = *reinterpret_cast<const uint2*>(vc + s);
-    const float2 k0 = unpack_bf16(ku.x), k1 = unpack_bf16(ku.y);
-    const float2 v0 = unpack_bf16(vu.x), v1 = unpack_bf16(vu.y);
-    float sc[G];
+  // The trip count is the same for every thread of the CTA (the shuffles below name all 32
+  // lanes, so the two half-warps must not leave the loop at different times); tokens past the
+  // end of the split are loaded from a valid address and ignored.
+  for (int tb0 = t0; tb0 < t1; tb0 += 2 * NG) {
+    uint4 ku[2], vu[2];
+    bool ok[2];
 #pragma unroll
-    for (int g = 0; g < G; ++g) sc[g] = qv[g][0] * k0.x + qv[g][1] * k0.y + qv[g][2] * k1.x + qv[g][3] * k1.y;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-      for (int g = 0; g < G; ++g) sc[g] += __shfl_xor_sync(0xffffffffu, sc[g], o);
+    for (int u = 0; u < 2; ++u) {
+      const int t = tb0 + grp + u * NG;
+      ok[u] = t < t1;
+      const int tt = ok[u] ? t : t0;
+      const size_t s = ((size_t)bt[tt / block_size] * block_size + (tt % block_size)) * row + (size_t)hk * PD_D + l16 * 8;
+      ku[u] = *reinterpret_cast<const uint4*>(kc + s);
+      vu[u] = *reinterpret_cast<const uint4*>(vc + s);
     }
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float mn = fmaxf(m[g], sc[g]);
-      const float a = exp2f(m[g] - mn);
-      const float p = exp2f(sc[g] - mn);
-      l[g] = l[g] * a + p;
-      acc[g][0] = acc[g][0] * a + p * v0.x; acc[g][1] = acc[g][1] * a + p * v0.y;
-      acc[g][2] = acc[g][2] * a + p * v1.x; acc[g][3] = acc[g][3] * a + p * v1.y;
-      m[g] = mn;
+    for (int u = 0; u < 2; ++u) {
+      float kf[8], vf[8];
+      {
+        const uint32_t kw[4] = {ku[u].x, ku[u].y, ku[u].z, ku[u].w};
+        const uint32_t vw[4] = {vu[u].x, vu[u].y, vu[u].z, vu[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = unpack_bf16(kw[j]), b = unpack_bf16(vw[j]);
+          kf[2 * j] = a.x; kf[2 * j + 1] = a.y; vf[2 * j] = b.x; vf[2 * j + 1] = b.y;
+        }
+      }
+      float sc[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d = fmaf(qv[g][e], kf[e], d);
+        sc[g] = d;
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) sc[g] += __shfl_xor_sync(0xffffffffu, sc[g], o);
+      }
+      if (ok[u]) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float mn = fmaxf(m[g], sc[g]);
+          const float a = exp2f(m[g] - mn);
+          const float p = exp2f(sc[g] - mn);
+          l[g] = l[g] * a + p;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(acc[g][e], a, p * vf[e]);
+          m[g] = mn;
+        }
+      }
     }
   }
-  // merge the 4 warps through shared memory
-  __shared__ float s_m[PD_WARPS][G], s_l[PD_WARPS][G];
-  __shared__ float s_acc[PD_WARPS][G][PD_D];
+  // merge the 8 half-warp streams through shared memory
+  __shared__ float s_m[NG][G], s_l[NG][G];
+  __shared__ float s_acc[NG][G][PD_D];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
-    *reinterpret_cast<float4*>(&s_acc[warp][g][lane * 4]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    if (l16 == 0) { s_m[grp][g] = m[g]; s_l[grp][g] = l[g]; }
+    *reinterpret_cast<float4*>(&s_acc[grp][g][l16 * 8]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    *reinterpret_cast<float4*>(&s_acc[grp][g][l16 * 8 + 4]) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < G * PD_D; idx += blockDim.x) {
     const int g = idx / PD_D, d = idx % PD_D;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < PD_WARPS; ++w) mm = fmaxf(mm, s_m[w][g]);
+    for (int w = 0; w < NG; ++w) mm = fmaxf(mm, s_m[w][g]);
     float ll = 0.f, o = 0.f;
 #pragma unroll
-    for (int w = 0; w < PD_WARPS; ++w) {
+    for (int w = 0; w < NG; ++w) {
       const float a = s_m[w][g] == -INFINITY ? 0.f : exp2f(s_m[w][g] - mm);
       ll += s_l[w][g] * a;
       o += s_acc[w][g][d] * a;

@@ -66,7 +66,7 @@ def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, scale=None, num_sp
         return out
     if num_splits is None:
         # enough CTAs to fill the GPU: seqs x kv heads x splits >= ~2 waves of 148 SMs
-        num_splits = max(1, min(16, (296 + n * Hkv - 1) // (n * Hkv)))
+        num_splits = max(1, min(32, (148 * 8 + n * Hkv - 1) // (n * Hkv)))
     key = (q.device.index, n * H * num_splits)
     sc = _scratch.get(key)
     if sc is None:
