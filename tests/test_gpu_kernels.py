@@ -16,7 +16,7 @@ def _status_ok(dev):
     assert int(nv.status_word(dev).item()) == 0
 
 
-@pytest.mark.parametrize("bn", [0, 256, 192, 128])
+@pytest.mark.parametrize("bn", [0, 576, 448, 384, 256, 192, 128])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 264, 136), (1024, 3072, 1024)])
 def test_gemm_plain(dev, M, N, K, bn):
     from vllm_omni_b200.ops import gemm
@@ -27,6 +27,23 @@ def test_gemm_plain(dev, M, N, K, bn):
     ref = x.float() @ w.float().t()
     _status_ok(dev)
     assert (y - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3
+
+
+def test_gemm_pair_kernel_many_tiles(dev):
+    """CTA-pair kernel over more tiles than CTA pairs (both accumulators and the whole ring wrap),
+    ragged M and N, full epilogue."""
+    from vllm_omni_b200.ops import gemm
+    torch.manual_seed(2)
+    B, S, K, N = 2, 2003, 640, 2568
+    x = torch.randn(B, S, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+    res = torch.randn(B, S, N, device=dev, dtype=torch.bfloat16)
+    gate = torch.randn(B, N, device=dev, dtype=torch.bfloat16)
+    y = gemm.linear(x, w, bias, "gelu_tanh", res, gate, force_bn=gemm.PAIR_BN).float()
+    ref = gemm.linear_reference(x, w, bias, "gelu_tanh", res, gate).float()
+    _status_ok(dev)
+    assert (y - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-2
 
 
 @pytest.mark.parametrize("act", [None, "gelu_tanh", "silu"])

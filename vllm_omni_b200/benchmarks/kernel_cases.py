@@ -28,6 +28,7 @@ def main(argv=None):
     ap.add_argument("case")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--bn", type=int, default=0, help="GEMM tile override (512 = CTA-pair kernel)")
     a = ap.parse_args(argv)
     from vllm_omni_b200.ops import attention as A, fused, gemm, kv_cache as KC, _native as nv
     dev = torch.device("cuda")
@@ -40,7 +41,7 @@ def main(argv=None):
         w = torch.randn(N, K, device=dev, dtype=bf) * 0.02
         b = torch.zeros(N, device=dev, dtype=bf)
         out = torch.empty(M, N, device=dev, dtype=bf)
-        fn = lambda: gemm.linear(x, w, b, act="gelu_tanh" if a.case == "gemm_gelu" else None, out=out)
+        fn = lambda: gemm.linear(x, w, b, act="gelu_tanh" if a.case == "gemm_gelu" else None, out=out, force_bn=a.bn)
         flops = 2.0 * M * N * K
     elif a.case == "attn":
         B, S, H = 2, 4352, 24

@@ -74,6 +74,67 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
   nb = in_g / gm;
 }
 
+// Fused epilogue for 32 accumulator columns of one output row: bias, activation, gate, residual,
+// bf16 conversion and the (possibly batched or peer-scattered) 16-byte stores.
+__device__ __forceinline__ void epilogue_store32(const uint32_t (&v)[32], int row, int col0, int N,
+                                                 __nv_bfloat16* __restrict__ C, int ldc, const GemmEpilogue& epi,
+                                                 const __nv_bfloat16* gate_row) {
+  __nv_bfloat16* out;
+  __nv_bfloat16* cbase = C;
+  int dcol = col0;
+  if (epi.scatter_P > 1) {
+    const int g = col0 / epi.scatter_G;
+    cbase = epi.peer_out[g % epi.scatter_P];
+    dcol = (g / epi.scatter_P) * epi.scatter_G + (col0 - g * epi.scatter_G);
+  }
+  if (epi.c_rows_per_batch > 0) {
+    const int cb = row / epi.c_rows_per_batch;
+    out = cbase + (size_t)cb * epi.c_batch_stride + (size_t)(row - cb * epi.c_rows_per_batch) * ldc + dcol;
+  } else {
+    out = cbase + (size_t)row * ldc + dcol;
+  }
+  const __nv_bfloat16* res = epi.residual ? epi.residual + (size_t)row * epi.ldr + col0 : nullptr;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {  // 8 columns per 16-byte store
+    if (col0 + j * 8 < N) {
+      float x[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[j * 8 + e]);
+      if (epi.bias) {
+        uint4 b = *reinterpret_cast<const uint4*>(epi.bias + col0 + j * 8);
+        float2 b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y), b2 = unpack_bf16(b.z), b3 = unpack_bf16(b.w);
+        x[0] += b0.x; x[1] += b0.y; x[2] += b1.x; x[3] += b1.y;
+        x[4] += b2.x; x[5] += b2.y; x[6] += b3.x; x[7] += b3.y;
+      }
+      if (epi.act == ACT_GELU_TANH) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = gelu_tanh(x[e]);
+      } else if (epi.act == ACT_SILU) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = silu(x[e]);
+      }
+      if (gate_row) {
+        uint4 g = *reinterpret_cast<const uint4*>(gate_row + col0 + j * 8);
+        float2 g0 = unpack_bf16(g.x), g1 = unpack_bf16(g.y), g2 = unpack_bf16(g.z), g3 = unpack_bf16(g.w);
+        x[0] *= g0.x; x[1] *= g0.y; x[2] *= g1.x; x[3] *= g1.y;
+        x[4] *= g2.x; x[5] *= g2.y; x[6] *= g3.x; x[7] *= g3.y;
+      }
+      if (res) {
+        uint4 r = *reinterpret_cast<const uint4*>(res + j * 8);
+        float2 r0 = unpack_bf16(r.x), r1 = unpack_bf16(r.y), r2 = unpack_bf16(r.z), r3 = unpack_bf16(r.w);
+        x[0] += r0.x; x[1] += r0.y; x[2] += r1.x; x[3] += r1.y;
+        x[4] += r2.x; x[5] += r2.y; x[6] += r3.x; x[7] += r3.y;
+      }
+      uint4 o;
+      o.x = pack_bf16(x[0], x[1]);
+      o.y = pack_bf16(x[2], x[3]);
+      o.z = pack_bf16(x[4], x[5]);
+      o.w = pack_bf16(x[6], x[7]);
+      *reinterpret_cast<uint4*>(out + j * 8) = o;
+    }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -204,62 +265,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, v);
         tmem_wait_ld();
-        if (row_ok) {
-          __nv_bfloat16* out;
-          __nv_bfloat16* cbase = C;
-          int dcol = col0;
-          if (epi.scatter_P > 1) {
-            const int g = col0 / epi.scatter_G;
-            cbase = epi.peer_out[g % epi.scatter_P];
-            dcol = (g / epi.scatter_P) * epi.scatter_G + (col0 - g * epi.scatter_G);
-          }
-          if (epi.c_rows_per_batch > 0) {
-            const int cb = row / epi.c_rows_per_batch;
-            out = cbase + (size_t)cb * epi.c_batch_stride + (size_t)(row - cb * epi.c_rows_per_batch) * ldc + dcol;
-          } else {
-            out = cbase + (size_t)row * ldc + dcol;
-          }
-          const __nv_bfloat16* res = epi.residual ? epi.residual + (size_t)row * epi.ldr + col0 : nullptr;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {  // 8 columns per 16-byte store
-            if (col0 + j * 8 < N) {
-              float x[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[j * 8 + e]);
-              if (epi.bias) {
-                uint4 b = *reinterpret_cast<const uint4*>(epi.bias + col0 + j * 8);
-                float2 b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y), b2 = unpack_bf16(b.z), b3 = unpack_bf16(b.w);
-                x[0] += b0.x; x[1] += b0.y; x[2] += b1.x; x[3] += b1.y;
-                x[4] += b2.x; x[5] += b2.y; x[6] += b3.x; x[7] += b3.y;
-              }
-              if (epi.act == ACT_GELU_TANH) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) x[e] = gelu_tanh(x[e]);
-              } else if (epi.act == ACT_SILU) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) x[e] = silu(x[e]);
-              }
-              if (gate_row) {
-                uint4 g = *reinterpret_cast<const uint4*>(gate_row + col0 + j * 8);
-                float2 g0 = unpack_bf16(g.x), g1 = unpack_bf16(g.y), g2 = unpack_bf16(g.z), g3 = unpack_bf16(g.w);
-                x[0] *= g0.x; x[1] *= g0.y; x[2] *= g1.x; x[3] *= g1.y;
-                x[4] *= g2.x; x[5] *= g2.y; x[6] *= g3.x; x[7] *= g3.y;
-              }
-              if (res) {
-                uint4 r = *reinterpret_cast<const uint4*>(res + j * 8);
-                float2 r0 = unpack_bf16(r.x), r1 = unpack_bf16(r.y), r2 = unpack_bf16(r.z), r3 = unpack_bf16(r.w);
-                x[0] += r0.x; x[1] += r0.y; x[2] += r1.x; x[3] += r1.y;
-                x[4] += r2.x; x[5] += r2.y; x[6] += r3.x; x[7] += r3.y;
-              }
-              uint4 o;
-              o.x = pack_bf16(x[0], x[1]);
-              o.y = pack_bf16(x[2], x[3]);
-              o.z = pack_bf16(x[4], x[5]);
-              o.w = pack_bf16(x[6], x[7]);
-              *reinterpret_cast<uint4*>(out + j * 8) = o;
-            }
-          }
-        }
+        if (row_ok) epilogue_store32(v, row, col0, N, C, ldc, epi, gate_row);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -279,6 +285,232 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): two CTAs of a cluster compute one 256 x 256 output tile.
+// Each CTA stages its own 128 rows of A and HALF of the W tile (128 of the 256 output columns'
+// weights) per k-block, so a k-block costs 32 KB of L2 -> shared-memory traffic per SM instead
+// of 48 KB, and the ring holds 6 stages instead of 4.  The even CTA issues one M=256, N=256
+// tcgen05.mma per 16 K-elements that reads A and W from both CTAs' shared memory; each CTA's
+// TMEM receives the 128 accumulator rows it owns and its own epilogue warps drain them.
+//   full_bar   (even CTA)   bytes of BOTH CTAs' loads land on it (the odd CTA's TMA names it)
+//   empty_bar  (each CTA)   released by two tcgen05.commit of the even CTA, one per CTA
+//   tfull_bar  (each CTA)   accumulator ready, same two-commit scheme
+//   tempty_bar (even CTA)   16 arrivals: 8 epilogue warps of each CTA
+// No load in this kernel is a multicast; every CTA fetches exactly the bytes it alone needs.
+// The tile width TN is 256, 192 or 128 (picked to minimise waves x width, like the one-CTA kernel).
+template <int TN>
+struct PairCfg {
+  static constexpr int A_BYTES = BM * BK * 2;            // 16 KiB: this CTA's 128 rows of A
+  static constexpr int B_BYTES = (TN / 2) * BK * 2;      // this CTA's half of the W tile
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // a multiple of 1 KiB for every TN
+  static constexpr int STAGES = (TN == 256) ? 6 : (TN == 192 ? 7 : 8);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+};
+
+template <int TN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      __nv_bfloat16* __restrict__ C, int ldc, int M, int N, int K, GemmEpilogue epi, int* status) {
+  constexpr int P_TILE_N = TN;
+  constexpr int P_STAGES = PairCfg<TN>::STAGES;
+  constexpr int P_STAGE_BYTES = PairCfg<TN>::STAGE_BYTES;
+  constexpr int P_A_BYTES = PairCfg<TN>::A_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[P_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[P_STAGES];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();      // 0: issues the MMAs, 1: its partner
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  const int num_m = (M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (N + P_TILE_N - 1) / P_TILE_N;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < P_STAGES; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 1);
+      mbar_init(smem_u32(&empty_bar[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tempty_bar[i]), 16);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers are initialised before either touches the other's
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = pair; t < num_tiles; t += num_pairs) {
+        int mb, nb;
+        tile_coords(t, num_m, num_n, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
+          if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * P_STAGE_BYTES);
+          const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);
+          const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+          tma_load_2d_pair(sa, &tmA, fb, kb * BK, mb * 2 * BM + (int)rank * BM);
+          tma_load_2d_pair(sa + P_A_BYTES, &tmB, fb, kb * BK, nb * P_TILE_N + (int)rank * (P_TILE_N / 2));
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer (even CTA)
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(2 * BM, P_TILE_N, 1, 1, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = pair; t < num_tiles; t += num_pairs) {
+        mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, &s_abort, status, ERR_WAIT_TMEM_EMPTY);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(smem_u32(&full_bar[stage]), phase, &s_abort, status, ERR_WAIT_FULL);
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+          const uint64_t a_desc = umma_desc_kmajor_sw128(sa);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(sa + P_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) mma_f16_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 0));
+          tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        tc_commit_pair(mapa_shared(smem_u32(&tfull_bar[acc]), 0));
+        tc_commit_pair(mapa_shared(smem_u32(&tfull_bar[acc]), 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs)
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      int mb, nb;
+      tile_coords(t, num_m, num_n, mb, nb);
+      mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, &s_abort, status, ERR_WAIT_TMEM_FULL);
+      tc_fence_after_sync();
+      const int row = mb * 2 * BM + (int)rank * BM + q * 32 + lane;
+      const bool row_ok = row < M;
+      const __nv_bfloat16* gate_row = nullptr;
+      if (epi.gate && row_ok) gate_row = epi.gate + (size_t)(row / epi.rows_per_batch) * epi.gate_stride;
+#pragma unroll 1
+      for (int c = half * (P_TILE_N / 64); c < (half + 1) * (P_TILE_N / 64); ++c) {
+        const int col0 = nb * P_TILE_N + c * 32;
+        if (col0 >= N) break;
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256 + c * 32, v);
+        tmem_wait_ld();
+        if (row_ok) epilogue_store32(v, row, col0, N, C, ldc, epi, gate_row);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (s_abort) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  cluster_sync_all();   // neither CTA frees TMEM or exits while its partner may still signal it
+  if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+}
+
+static int g_pair_mode = 1;   // 0: never unless forced, 1: automatic for large problems
+
+template <int TN>
+static int launch_gemm_pair(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, int ldc, int M, int N, int K,
+                            int ldw, const GemmEpilogue& epi, int* status, int max_pairs, cudaStream_t stream) {
+  using Cfg = PairCfg<TN>;
+  CUtensorMap tmB;
+  int rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, TN / 2, BK);
+  if (rc) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + TN - 1) / TN);
+  const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
+  gemm_bf16_pair_kernel<TN><<<2 * pairs, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, status);
+  return (int)cudaGetLastError();
+}
+
+// how many CTA pairs can be resident at once (one CTA per SM, two SMs of one TPC per pair)
+static int max_resident_pairs() {
+  static int cached = 0;
+  if (cached) return cached;
+  int n = 0;
+  if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           PairCfg<256>::SMEM_BYTES) == cudaSuccess) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count() & ~1);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = PairCfg<256>::SMEM_BYTES;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel<256>, &cfg) != cudaSuccess) n = 0;
+  }
+  (void)cudaGetLastError();
+  if (n <= 0 || n > sm_count() / 2) n = sm_count() / 2;
+  cached = n;
+  return n;
+}
+
+static int pick_pair_tn(int M, int N, int pairs) {
+  const int cand[3] = {256, 192, 128};
+  int best = 256;
+  long best_cost = -1;
+  const int num_m = (M + 2 * BM - 1) / (2 * BM);
+  for (int i = 0; i < 3; ++i) {
+    const int tn = cand[i];
+    const long tiles = (long)num_m * ((N + tn - 1) / tn);
+    const long waves = (tiles + pairs - 1) / pairs;
+    const long cost = waves * tn * (tn == 128 ? 108 : (tn == 192 ? 102 : 100));
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = tn; }
+  }
+  return best;
 }
 
 template <int BN>
@@ -364,9 +596,22 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
     for (int i = 0; i < scatter_P; ++i) epi.peer_out[i] = static_cast<__nv_bfloat16*>(peer_out[i]);
   }
   const int ctas = sm_count();
-  const int bn = force_bn ? force_bn : pick_bn(M, N, ctas);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   __nv_bfloat16* c = static_cast<__nv_bfloat16*>(C);
+  // force_bn = 576 / 448 / 384 selects the CTA-pair kernel with a 256 / 192 / 128 wide tile on two
+  // SMs, 512 the pair kernel with the launcher's choice of width; in automatic mode the pair kernel takes every
+  // problem with at least one full wave of 256 x 256 tiles
+  const long pair_tiles = (long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+  if (force_bn >= 384 || (force_bn == 0 && g_pair_mode == 1 && pair_tiles >= ctas / 2)) {
+    const int pairs = max_resident_pairs();
+    const int tn = force_bn == 576 ? 256 : (force_bn == 448 ? 192 : (force_bn == 384 ? 128 : pick_pair_tn(M, N, pairs)));
+    switch (tn) {
+      case 256: return launch_gemm_pair<256>(tmA, W, c, ldc, M, N, K, ldw, epi, status, pairs, s);
+      case 192: return launch_gemm_pair<192>(tmA, W, c, ldc, M, N, K, ldw, epi, status, pairs, s);
+      default: return launch_gemm_pair<128>(tmA, W, c, ldc, M, N, K, ldw, epi, status, pairs, s);
+    }
+  }
+  const int bn = force_bn ? force_bn : pick_bn(M, N, ctas);
   switch (bn) {
     case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
     case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
@@ -374,6 +619,9 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
     default: return RC_BAD_ARG;
   }
 }
+
+// 0: the CTA-pair kernel runs only when forced (force_bn = 512); 1: automatic for large problems.
+extern "C" void omni_gemm_set_pair_mode(int mode) { omni::g_pair_mode = mode; }
 
 // Grouped (MoE expert) GEMM: A is the expert-major, 128-row-padded activation buffer [M, K];
 // W is [E, N, K] contiguous; tile_expert[m_tile] names the expert of every 128-row tile (-1 =

@@ -20,7 +20,7 @@ class NativeError(RuntimeError):
 
 
 # kernels launched per exported entry point (default 1); used for the launch counter
-_KERNELS_PER_CALL = {"omni_rel_l1": 2, "omni_rel_l1_parts": 0, "omni_paged_decode": 2}
+_KERNELS_PER_CALL = {"omni_rel_l1": 2, "omni_rel_l1_parts": 0, "omni_paged_decode": 2, "omni_gemm_set_pair_mode": 0}
 launch_count = 0
 
 

@@ -16,6 +16,14 @@ from . import _native as nv
 
 ACT = {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}
 
+PAIR_BN = 512   # force_bn value that selects the CTA-pair (cta_group::2, 256 x 256 tile) kernel
+
+
+def set_pair_mode(auto: bool) -> None:
+    """Let the launcher pick the CTA-pair kernel for problems with at least one full wave of
+    256 x 256 tiles (``auto=True``) or only when ``force_bn=PAIR_BN`` is passed."""
+    nv.lib("gemm_sm100").omni_gemm_set_pair_mode(ctypes.c_int(1 if auto else 0))
+
 
 def linear_reference(x, w, bias=None, act=None, residual=None, gate=None):
     """Plain PyTorch restatement (fp32 accumulate) used on CPU and as the test oracle.
