@@ -168,8 +168,9 @@ def test_attention_causal(dev, Sq, Skv, off):
     assert (o.float() - ref.float()).abs().max().item() < 0.03
 
 
+@pytest.mark.parametrize("impl", ["tc", "simt"])
 @pytest.mark.parametrize("H,Hkv,splits", [(32, 4, 4), (8, 8, 1), (16, 4, 3)])
-def test_paged_decode(dev, H, Hkv, splits):
+def test_paged_decode(dev, H, Hkv, splits, impl):
     from vllm_omni_b200.ops import kv_cache as KC
     from vllm_omni_b200.ops import attention as A
     torch.manual_seed(9)
@@ -192,7 +193,7 @@ def test_paged_decode(dev, H, Hkv, splits):
     bt = torch.tensor([t + [0] * (maxb - len(t)) for t in tables], dtype=torch.int32, device=dev)
     sl = torch.tensor(lens, dtype=torch.int32, device=dev)
     q = torch.randn(len(lens), H, D, device=dev, dtype=torch.bfloat16)
-    out = KC.paged_decode(q, kc, vc, bt, sl, num_splits=splits)
+    out = KC.paged_decode(q, kc, vc, bt, sl, num_splits=splits, impl=impl)
     for i, L in enumerate(lens):
         ref = A.attention_reference(q[i:i + 1, None].reshape(1, 1, H, D), ks[i][None], vs[i][None])
         assert (out[i].float() - ref[0, 0].float()).abs().max().item() < 0.03, i
@@ -219,3 +220,25 @@ def test_fp8_block_scaled_gemm(dev, M, N, K, act):
     full = fp8._epi(x.float().cpu() @ w.float().cpu().t(), bias.cpu(), act, res.cpu(), None)
     rel = (y.float().cpu() - full).norm() / full.norm()
     assert rel < 0.05, rel
+
+
+@pytest.mark.parametrize("T,L", [(150, 150), (140, 290), (1, 77), (300, 1000)])
+def test_paged_prefill_chunk(dev, T, L):
+    """Causal attention of the last T tokens of an L-token sequence straight from the pages."""
+    from vllm_omni_b200.ops import kv_cache as KC
+    from vllm_omni_b200.ops import attention as A
+    torch.manual_seed(11)
+    bs, nblk, H, Hkv, D = 16, 80, 8, 2, 128
+    kc = torch.zeros(nblk, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    ids = torch.randperm(nblk)[: (L + bs - 1) // bs].tolist()
+    k = torch.randn(L, Hkv, D, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(L, Hkv, D, device=dev, dtype=torch.bfloat16)
+    slots = torch.tensor([ids[t // bs] * bs + t % bs for t in range(L)], dtype=torch.int32, device=dev)
+    KC.kv_write(k, v, kc, vc, slots)
+    bt = torch.tensor(ids, dtype=torch.int32, device=dev)
+    q = torch.randn(T, H, D, device=dev, dtype=torch.bfloat16)
+    out = KC.paged_prefill(q, kc, vc, bt, L)
+    ref = A.attention_reference(q[None], k[None], v[None], causal=True, q_offset=L - T)[0]
+    _status_ok(dev)
+    assert (out.float() - ref.float()).abs().max().item() < 0.03

@@ -29,6 +29,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--bn", type=int, default=0, help="GEMM tile override (512 = CTA-pair kernel)")
+    ap.add_argument("--impl", default=None, help="decode: tc (tcgen05, default) or simt")
     a = ap.parse_args(argv)
     from vllm_omni_b200.ops import attention as A, fused, gemm, kv_cache as KC, _native as nv
     dev = torch.device("cuda")
@@ -70,7 +71,7 @@ def main(argv=None):
         bt = torch.arange(nb, dtype=torch.int32, device=dev).view(n, -1)
         sl = torch.full((n,), ctx, dtype=torch.int32, device=dev)
         q = torch.randn(n, H, 128, device=dev, dtype=bf)
-        fn = lambda: KC.paged_decode(q, kc, vc, bt, sl)
+        fn = lambda: KC.paged_decode(q, kc, vc, bt, sl, impl=a.impl)
         bytes_ = 2.0 * kc.numel() * 2
     else:
         raise SystemExit(f"unknown case {a.case}")

@@ -48,6 +48,20 @@ struct AttnOut {
   int rows_per_rank, rows_per_rank2;
   __nv_bfloat16* o_peers[16];
   __nv_bfloat16* o2_peers[16];
+  // Split-KV: with kv_splits > 1 CTA (qblk, split) covers a contiguous share of the KV tiles and
+  // stores the unnormalised fp32 O row, its reference exponent m (log2 units) and row sum l at
+  // index ((b * H + h) * Sq + row) * kv_splits + split; a merge kernel combines the shares.
+  int kv_splits;
+  float* part_o;    // [.., kv_splits, 128]
+  float* part_ml;   // [.., kv_splits, 2]
+};
+
+// Paged K/V: the tensor maps cover the page pool as [num_blocks * block_size, Hkv, 128] and token
+// t of batch row b lives in page block_table[b * bt_stride + t / block_size].
+struct AttnPaging {
+  const int* block_table;   // nullptr = contiguous K/V
+  int bt_stride;
+  int block_size;           // a multiple of 8 that divides 128
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -114,7 +128,8 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnOut out, int Sq, int Skv, int H, int Hkv,
-                const int* __restrict__ kv_lens, float scale_log2, int causal, int q_offset, int* status) {
+                const int* __restrict__ kv_lens, float scale_log2, int causal, int q_offset, AttnPaging pg,
+                int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
   __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
@@ -124,7 +139,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int qblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int splits = out.kv_splits > 1 ? out.kv_splits : 1;
+  const int qblk = blockIdx.x / splits, split = blockIdx.x - qblk * splits;
+  const int h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / (H / Hkv);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = smem_base;                         // 2 tiles
@@ -133,7 +150,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int kv_len = kv_lens ? min(kv_lens[b], Skv) : Skv;
   // causal: query row s sees keys [0, s + q_offset]; the CTA only visits tiles its last row sees
   const int kv_cta = causal ? min(kv_len, qblk * 2 * ATT_BM + 2 * ATT_BM + q_offset) : kv_len;
-  const int n_kv = (kv_cta + ATT_BN - 1) / ATT_BN;
+  const int n_kv_all = (kv_cta + ATT_BN - 1) / ATT_BN;
+  const int per_split = (n_kv_all + splits - 1) / splits;
+  const int j0 = min(n_kv_all, split * per_split);       // this CTA's KV tiles: [j0, j0 + n_kv)
+  const int n_kv = min(n_kv_all, j0 + per_split) - j0;
+  // query tiles in use: the second one is skipped when this block's rows end inside the first
+  const int n_qt = (Sq - qblk * 2 * ATT_BM > ATT_BM) ? 2 : 1;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -171,19 +193,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tma_load_4d(sQ + t * ATT_TILE_BYTES, &tmQ, qb, 0, s0, h, b);
         tma_load_4d(sQ + t * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmQ, qb, 64, s0, h, b);
       }
-      for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+      const int* bt = pg.block_table ? pg.block_table + (long)b * pg.bt_stride : nullptr;
+      const int last_page = bt ? max(0, (kv_len + pg.block_size - 1) / pg.block_size - 1) : 0;
+      const int pages_per_tile = bt ? ATT_BN / pg.block_size : 0;
+      const uint32_t page_bytes = bt ? (uint32_t)pg.block_size * 128u : 0u;   // per 64-wide half
+      for (int jj = 0; jj < n_kv; ++jj) {
+        const int j = j0 + jj;
+        const int st = jj & 1;
+        const uint32_t ph = (jj >> 1) & 1;
         mbar_wait(smem_u32(&k_empty[st]), ph ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
         const uint32_t kb = smem_u32(&k_full[st]);
         mbar_expect_tx(kb, ATT_TILE_BYTES);
-        tma_load_4d(sK + st * ATT_TILE_BYTES, &tmK, kb, 0, j * ATT_BN, hkv, b);
-        tma_load_4d(sK + st * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmK, kb, 64, j * ATT_BN, hkv, b);
+        if (bt) {
+          // one box of block_size rows per page; pages past the sequence's last one re-read the
+          // last page (finite data that the key mask discards)
+          for (int i = 0; i < pages_per_tile; ++i) {
+            const int page = bt[min(j * pages_per_tile + i, last_page)];
+            tma_load_4d(sK + st * ATT_TILE_BYTES + i * page_bytes, &tmK, kb, 0, page * pg.block_size, hkv, 0);
+            tma_load_4d(sK + st * ATT_TILE_BYTES + ATT_HALF_BYTES + i * page_bytes, &tmK, kb, 64, page * pg.block_size, hkv, 0);
+          }
+        } else {
+          tma_load_4d(sK + st * ATT_TILE_BYTES, &tmK, kb, 0, j * ATT_BN, hkv, b);
+          tma_load_4d(sK + st * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmK, kb, 64, j * ATT_BN, hkv, b);
+        }
         mbar_wait(smem_u32(&v_empty[st]), ph ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
         const uint32_t vb = smem_u32(&v_full[st]);
         mbar_expect_tx(vb, ATT_TILE_BYTES);
-        tma_load_4d(sV + st * ATT_TILE_BYTES, &tmV, vb, 0, j * ATT_BN, hkv, b);
-        tma_load_4d(sV + st * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmV, vb, 64, j * ATT_BN, hkv, b);
+        if (bt) {
+          for (int i = 0; i < pages_per_tile; ++i) {
+            const int page = bt[min(j * pages_per_tile + i, last_page)];
+            tma_load_4d(sV + st * ATT_TILE_BYTES + i * page_bytes, &tmV, vb, 0, page * pg.block_size, hkv, 0);
+            tma_load_4d(sV + st * ATT_TILE_BYTES + ATT_HALF_BYTES + i * page_bytes, &tmV, vb, 64, page * pg.block_size, hkv, 0);
+          }
+        } else {
+          tma_load_4d(sV + st * ATT_TILE_BYTES, &tmV, vb, 0, j * ATT_BN, hkv, b);
+          tma_load_4d(sV + st * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmV, vb, 64, j * ATT_BN, hkv, b);
+        }
       }
     }
   } else if (warp == 1) {
@@ -217,7 +262,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_wait(smem_u32(&q_full), 0, &s_abort, status, ERR_WAIT_FULL);
       mbar_wait(smem_u32(&k_full[0]), 0, &s_abort, status, ERR_WAIT_FULL);
       tc_fence_after_sync();
-      for (int t = 0; t < 2; ++t) {
+      for (int t = 0; t < n_qt; ++t) {
         issue_s(t, 0);
         tc_commit(smem_u32(&s_full[t]));
       }
@@ -229,7 +274,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int st1 = (j + 1) & 1;
         mbar_wait(smem_u32(&v_full[st]), ph, &s_abort, status, ERR_WAIT_FULL);
         if (more) mbar_wait(smem_u32(&k_full[st1]), ((j + 1) >> 1) & 1, &s_abort, status, ERR_WAIT_FULL);
-        for (int t = 0; t < 2; ++t) {
+        for (int t = 0; t < n_qt; ++t) {
           mbar_wait(smem_u32(&p_full[t]), j & 1, &s_abort, status, ERR_WAIT_SOFTMAX);
           tc_fence_after_sync();
           issue_pv(t, st, j);
@@ -261,11 +306,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint64_t scale2 = pack2(scale_log2, scale_log2);
     float m = -INFINITY;  // running maximum in log2 units that P and l are relative to
     uint64_t l2a = 0ull, l2b = 0ull;     // four partial row sums (two packed pairs) over this half
-    for (int j = 0; j < n_kv; ++j) {
+    // A tile that is not in use has no work at all; a warp whose 32 rows all lie past the last
+    // query row (decode: a handful of real rows per tile) only keeps the barrier protocol going.
+    // Its rows of S come from zero-filled Q rows, so the stale bits the P*V MMA reads as their P
+    // are zeros, and nothing of those rows is stored.
+    const bool tile_used = t < n_qt;
+    const bool rows_used = tile_used && (srow - lane) < Sq;
+    for (int j = 0; tile_used && j < n_kv; ++j) {
       mbar_wait(smem_u32(&s_full[t]), j & 1, &s_abort, status, ERR_WAIT_FULL);
+      if (!rows_used) {
+        mbar_arrive(smem_u32(&p_full[t]));
+        continue;
+      }
       tc_fence_after_sync();
       const int row_limit = causal ? min(kv_len, srow + q_offset + 1) : kv_len;
-      const int valid = row_limit - j * ATT_BN - hf * 64;  // keys of this half-tile this row may see
+      const int valid = row_limit - (j0 + j) * ATT_BN - hf * 64;  // keys of this half-tile this row may see
       const bool masked = valid < 64;
       // pass 1: row maximum over this warp's 64 columns, four independent chains
       float mx;
@@ -366,58 +421,87 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(smem_u32(&p_full[t]));
     }
     // epilogue: O / l -> bf16; the row sum is the total of both halves
-    float l;
-    {
-      float a0, a1, b0, b1;
-      unpack2(l2a, a0, a1);
-      unpack2(l2b, b0, b1);
-      l = (a0 + a1) + (b0 + b1);
-      s_xmax[n_kv & 1][t][hf][row_in_tile] = l;
-      named_bar_sync(bar_id, 64);
-      l += s_xmax[n_kv & 1][t][hf ^ 1][row_in_tile];
-    }
-    if (n_kv > 0) {
-      mbar_wait(smem_u32(&o_done[t]), 0, &s_abort, status, ERR_WAIT_PV);
-      tc_fence_after_sync();
-    }
-    const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-    __nv_bfloat16* orow = nullptr;
-    if (srow < Sq && out.n_peers > 1) {
-      if (srow >= out.split) {
-        const int t2 = srow - out.split;
-        const int owner = t2 / out.rows_per_rank2;
-        orow = out.o2_peers[owner] + (long)b * out.o2_bs + (long)(t2 - owner * out.rows_per_rank2) * out.o2_rs + (long)h * out.o2_hs;
-      } else {
-        const int owner = srow / out.rows_per_rank;
-        orow = out.o_peers[owner] + (long)b * out.o_bs + (long)(srow - owner * out.rows_per_rank) * out.o_rs + (long)h * out.o_hs;
+    if (rows_used) {
+      float l;
+      {
+        float a0, a1, b0, b1;
+        unpack2(l2a, a0, a1);
+        unpack2(l2b, b0, b1);
+        l = (a0 + a1) + (b0 + b1);
+        s_xmax[n_kv & 1][t][hf][row_in_tile] = l;
+        named_bar_sync(bar_id, 64);
+        l += s_xmax[n_kv & 1][t][hf ^ 1][row_in_tile];
       }
-    } else if (srow < Sq) {
-      if (out.o2 && srow >= out.split)
-        orow = out.o2 + (long)b * out.o2_bs + (long)(srow - out.split) * out.o2_rs + (long)h * out.o2_hs;
-      else
-        orow = out.o + (long)b * out.o_bs + (long)srow * out.o_rs + (long)h * out.o_hs;
-    }
-    if (srow < Sq && out.lse && hf == 0)
-      out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      uint32_t v[32];
       if (n_kv > 0) {
-        tmem_ld_32x32(tO + c * 32, v);
-        tmem_wait_ld();
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) v[e] = 0u;
+        mbar_wait(smem_u32(&o_done[t]), 0, &s_abort, status, ERR_WAIT_PV);
+        tc_fence_after_sync();
       }
-      if (orow) {
+      if (out.kv_splits > 1) {
+        // split-KV share: unnormalised O, reference exponent and row sum for the merge kernel
+        const long pidx = (((long)b * H + h) * Sq + srow) * out.kv_splits + split;
+        if (srow < Sq && hf == 0) {
+          out.part_ml[pidx * 2] = n_kv > 0 ? m : -INFINITY;
+          out.part_ml[pidx * 2 + 1] = l;
+        }
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          if (n_kv > 0) {
+            tmem_ld_32x32(tO + c * 32, v);
+            tmem_wait_ld();
+          } else {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 o;
-          o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
-          o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
-          o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
-          o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(orow + hf * 64 + c * 32 + g * 8) = o;
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          if (srow < Sq) {
+            float4* dst = reinterpret_cast<float4*>(out.part_o + pidx * ATT_D + hf * 64 + c * 32);
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              dst[g] = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
+                                   __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
+          }
+        }
+      } else {
+        const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+        __nv_bfloat16* orow = nullptr;
+        if (srow < Sq && out.n_peers > 1) {
+          if (srow >= out.split) {
+            const int t2 = srow - out.split;
+            const int owner = t2 / out.rows_per_rank2;
+            orow = out.o2_peers[owner] + (long)b * out.o2_bs + (long)(t2 - owner * out.rows_per_rank2) * out.o2_rs + (long)h * out.o2_hs;
+          } else {
+            const int owner = srow / out.rows_per_rank;
+            orow = out.o_peers[owner] + (long)b * out.o_bs + (long)(srow - owner * out.rows_per_rank) * out.o_rs + (long)h * out.o_hs;
+          }
+        } else if (srow < Sq) {
+          if (out.o2 && srow >= out.split)
+            orow = out.o2 + (long)b * out.o2_bs + (long)(srow - out.split) * out.o2_rs + (long)h * out.o2_hs;
+          else
+            orow = out.o + (long)b * out.o_bs + (long)srow * out.o_rs + (long)h * out.o_hs;
+        }
+        if (srow < Sq && out.lse && hf == 0)
+          out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          if (n_kv > 0) {
+            tmem_ld_32x32(tO + c * 32, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          if (orow) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+              o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+              o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+              o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + hf * 64 + c * 32 + g * 8) = o;
+            }
+          }
         }
       }
     }
@@ -433,18 +517,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-static int make_qkv_tmap(CUtensorMap* tm, const void* p, int S, int Hn, int B, long rs, long hs, long bs) {
+// out[b, row, h, :] = sum_s 2^(m_s - m*) O_s / sum_s 2^(m_s - m*) l_s over the split-KV shares
+__global__ void __launch_bounds__(ATT_D)
+attn_merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
+                         __nv_bfloat16* __restrict__ o, long o_bs, long o_rs, long o_hs, float* __restrict__ lse,
+                         int H, int Sq) {
+  const long r = blockIdx.x;            // (b * H + h) * Sq + row
+  const int d = threadIdx.x;
+  const int row = (int)(r % Sq);
+  const int h = (int)((r / Sq) % H);
+  const long b = r / ((long)Sq * H);
+  float mm = -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(r * splits + s) * 2]);
+  float ll = 0.f, acc = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(r * splits + s) * 2];
+    const float a = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+    ll += part_ml[(r * splits + s) * 2 + 1] * a;
+    acc += part_o[(r * splits + s) * ATT_D + d] * a;
+  }
+  o[b * o_bs + (long)row * o_rs + (long)h * o_hs + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+  if (lse && d == 0) lse[r] = ll > 0.f ? (mm + log2f(ll)) * 0.6931471805599453f : -INFINITY;
+}
+
+static int make_qkv_tmap(CUtensorMap* tm, const void* p, int S, int Hn, int B, long rs, long hs, long bs,
+                         int box_rows = ATT_BM) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return RC_NO_DRIVER;
   if ((reinterpret_cast<uintptr_t>(p) & 15) || (rs & 7) || (hs & 7) || (bs & 7)) return RC_BAD_ARG;
   cuuint64_t gdim[4] = {(cuuint64_t)ATT_D, (cuuint64_t)S, (cuuint64_t)Hn, (cuuint64_t)B};
   cuuint64_t gstr[3] = {(cuuint64_t)rs * 2, (cuuint64_t)hs * 2, (cuuint64_t)bs * 2};
-  cuuint32_t box[4] = {64, ATT_BM, 1, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(p), gdim, gstr, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? RC_OK : RC_TMAP;
+}
+
+static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnOut& out, int B, int H,
+                       int Hkv, int Sq, int Skv, const int* kv_lens, float scale, int causal, int q_offset,
+                       const AttnPaging& pg, int* status, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int splits = out.kv_splits > 1 ? out.kv_splits : 1;
+  dim3 grid(((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM)) * splits, H, B);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens, scale_log2,
+                                                           causal, q_offset, pg, status);
+  return (int)cudaGetLastError();
 }
 
 }  // namespace omni
@@ -472,12 +597,6 @@ extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, con
   if (rc) return rc;
   rc = make_qkv_tmap(&tv, v, Skv, Hkv, B, v_rs, v_hs, v_bs);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
   AttnOut out;
   out.o = (__nv_bfloat16*)o; out.o2 = (__nv_bfloat16*)o2;
   out.o_bs = o_bs; out.o_rs = o_rs; out.o_hs = o_hs;
@@ -494,9 +613,56 @@ extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, con
       out.o2_peers[i] = o2_peers ? (__nv_bfloat16*)o2_peers[i] : nullptr;
     }
   }
-  dim3 grid((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), H, B);
-  const float scale_log2 = scale * 1.4426950408889634f;
-  attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens,
-                                                                         scale_log2, causal, q_offset, status);
+  out.kv_splits = 1; out.part_o = nullptr; out.part_ml = nullptr;
+  AttnPaging pg = {nullptr, 0, 0};
+  return launch_attn(tq, tk, tv, out, B, H, Hkv, Sq, Skv, kv_lens, scale, causal, q_offset, pg, status,
+                     (cudaStream_t)stream);
+}
+
+// Attention over a paged KV cache.  k_pool / v_pool: [num_blocks, block_size, Hkv, 128] bf16;
+// block_table: int32 [B, bt_stride] page ids; kv_lens: int32 [B] tokens per row.  Queries are
+// addressed by strides exactly as in omni_attn_fwd, which covers both uses:
+//   chunked prefill   q [T, H, 128] of one sequence: B = 1, Sq = T, causal with
+//                     q_offset = kv_len - T
+//   GQA decode        one token per sequence: the G = H / Hkv heads that share a KV head are the
+//                     ROWS of a query tile (Sq = G, "heads" = Hkv, q_rs = 128, q_hs = G * 128,
+//                     q_bs = token pitch), so one MMA serves the whole group
+// kv_splits > 1 spreads the KV tiles of a row block over that many CTAs; part_o
+// (float [B*H*Sq*kv_splits*128]) and part_ml (float [B*H*Sq*kv_splits*2]) are scratch.
+extern "C" int omni_attn_fwd_paged(const void* q, long q_rs, long q_hs, long q_bs, const void* k_pool,
+                                   const void* v_pool, int num_blocks, int block_size, const int* block_table,
+                                   int bt_stride, void* o, long o_rs, long o_hs, long o_bs, float* lse, int B, int H,
+                                   int Hkv, int Sq, int max_kv, const int* kv_lens, float scale, int causal,
+                                   int q_offset, int kv_splits, float* part_o, float* part_ml, int* status,
+                                   void* stream) {
+  using namespace omni;
+  if (H <= 0 || Hkv <= 0 || (H % Hkv) || B <= 0 || block_table == nullptr || kv_lens == nullptr) return RC_BAD_ARG;
+  if (block_size < 8 || (block_size & 7) || (ATT_BN % block_size) || num_blocks <= 0) return RC_BAD_ARG;
+  if (Sq <= 0 || max_kv <= 0) return RC_OK;
+  if ((o_rs & 7) || (o_hs & 7) || (o_bs & 7)) return RC_BAD_ARG;
+  if (kv_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return RC_BAD_ARG;
+  CUtensorMap tq, tk, tv;
+  int rc = make_qkv_tmap(&tq, q, Sq, H, B, q_rs, q_hs, q_bs);
+  if (rc) return rc;
+  const long pool_rows = (long)num_blocks * block_size;
+  rc = make_qkv_tmap(&tk, k_pool, (int)pool_rows, Hkv, 1, (long)Hkv * ATT_D, ATT_D, pool_rows * Hkv * ATT_D, block_size);
+  if (rc) return rc;
+  rc = make_qkv_tmap(&tv, v_pool, (int)pool_rows, Hkv, 1, (long)Hkv * ATT_D, ATT_D, pool_rows * Hkv * ATT_D, block_size);
+  if (rc) return rc;
+  AttnOut out;
+  out.o = (__nv_bfloat16*)o; out.o2 = nullptr;
+  out.o_bs = o_bs; out.o_rs = o_rs; out.o_hs = o_hs;
+  out.o2_bs = 0; out.o2_rs = 0; out.o2_hs = 0;
+  out.split = Sq; out.lse = kv_splits > 1 ? nullptr : lse;
+  out.n_peers = 0; out.rows_per_rank = 1; out.rows_per_rank2 = 1;
+  for (int i = 0; i < 16; ++i) { out.o_peers[i] = nullptr; out.o2_peers[i] = nullptr; }
+  out.kv_splits = kv_splits > 1 ? kv_splits : 1;
+  out.part_o = part_o; out.part_ml = part_ml;
+  AttnPaging pg = {block_table, bt_stride, block_size};
+  cudaStream_t st = (cudaStream_t)stream;
+  rc = launch_attn(tq, tk, tv, out, B, H, Hkv, Sq, max_kv, kv_lens, scale, causal, q_offset, pg, status, st);
+  if (rc || kv_splits <= 1) return rc;
+  attn_merge_splits_kernel<<<(unsigned)((long)B * H * Sq), ATT_D, 0, st>>>(part_o, part_ml, kv_splits, (__nv_bfloat16*)o,
+                                                                         o_bs, o_rs, o_hs, lse, H, Sq);
   return (int)cudaGetLastError();
 }

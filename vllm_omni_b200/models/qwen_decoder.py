@@ -175,6 +175,10 @@ class QwenDecoderModel(nn.Module):
             if seg.context == 0 or k_cache is None:
                 attention(q[None, s:s + n], k[None, s:s + n], v[None, s:s + n], scale=scale, causal=True,
                           out=o[None, s:s + n])
+            elif q.is_cuda and KC.tma_pages_ok(k_cache.shape[1], Dh):
+                # chunked prefill straight from the pages (this chunk's K/V were written above)
+                KC.paged_prefill(q[s:s + n], k_cache, v_cache, seg.block_table, seg.context + n, scale=scale,
+                                 out=o[s:s + n])
             else:
                 gk, gv = KC.kv_gather(k_cache, v_cache, seg.block_table, seg.context + n)
                 attention(q[None, s:s + n], gk[None], gv[None], scale=scale, causal=True, q_offset=seg.context,
