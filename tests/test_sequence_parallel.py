@@ -83,3 +83,44 @@ def test_ulysses_matches_single_rank_gpu(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     run_distributed(_sp_worker, 2, "nccl", args=("nccl", mode, "bfloat16", 128, 4, 0.06))
+
+
+def _tp_worker(rank, world, backend, mode, dtype_name, head_dim, heads, tol):
+    """Tensor-parallel transformer (heads and MLP columns split over the ranks) == single rank."""
+    from vllm_omni_b200.parallel import parallel_state as ps
+    from vllm_omni_b200.parallel.tensor_parallel import shard_transformer
+    dtype = getattr(torch, dtype_name)
+    device = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+    ps.init_distributed_environment(world, rank, local_rank=rank, backend=backend)
+    ps.initialize_model_parallel(tensor_parallel_size=world, backend=backend)
+    m = _build(dtype, device, head_dim, heads)
+    B, h, w, St = 2, 8, 8, 12
+    g = torch.Generator(device="cpu").manual_seed(2)
+    x = torch.randn(B, h * w, 16, generator=g).to(device)
+    e = torch.randn(B, St, 64, generator=g).to(device)
+    t = torch.tensor([0.6, 0.6], device=device)
+    lens = [St, St - 3]
+    ref = m(x, e, t, (1, h, w), txt_seq_lens=lens).float()
+    shard_transformer(m, ps.get_tp_group(), mode)
+    m._ws.key = None                      # the workspace is sized for this rank's share from here on
+    y = m(x, e, t, (1, h, w), txt_seq_lens=lens).float()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+        from vllm_omni_b200.ops import _native as nv
+        assert int(nv.status_word(device).item()) == 0
+    err = (y - ref).abs().max().item()
+    assert err < tol * max(1.0, ref.abs().max().item()), f"rank {rank}: {err}"
+    m.tp_reducer.close()
+    ps.destroy_distributed_environment()
+
+
+def test_tensor_parallel_matches_single_rank_cpu_gloo():
+    run_distributed(_tp_worker, 2, "gloo", args=("gloo", "nccl", "float32", 32, 4, 2e-4))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_tensor_parallel_matches_single_rank_gpu(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_distributed(_tp_worker, 2, "nccl", args=("nccl", mode, "bfloat16", 128, 4, 0.06))

@@ -47,6 +47,10 @@ struct GemmEpilogue {
   // (NVLink-mapped) or local pointers that already include this rank's row offset.
   int scatter_P;
   int scatter_G;
+  // Fused reduce-scatter feed (tensor parallel): with scatter_rows > 0 output row r belongs to rank
+  // r / scatter_rows and is stored, as row r % scatter_rows, through peer_out[that rank] (each
+  // pointer already addresses the slot reserved for THIS rank's partial sums on the owner).
+  int scatter_rows;
   __nv_bfloat16* peer_out[16];
 };
 
@@ -87,7 +91,10 @@ __device__ __forceinline__ void epilogue_store32(const uint32_t (&v)[32], int ro
     cbase = epi.peer_out[g % epi.scatter_P];
     dcol = (g / epi.scatter_P) * epi.scatter_G + (col0 - g * epi.scatter_G);
   }
-  if (epi.c_rows_per_batch > 0) {
+  if (epi.scatter_rows > 0) {
+    const int owner = row / epi.scatter_rows;
+    out = epi.peer_out[owner] + (size_t)(row - owner * epi.scatter_rows) * ldc + dcol;
+  } else if (epi.c_rows_per_batch > 0) {
     const int cb = row / epi.c_rows_per_batch;
     out = cbase + (size_t)cb * epi.c_batch_stride + (size_t)(row - cb * epi.c_rows_per_batch) * ldc + dcol;
   } else {
@@ -565,7 +572,7 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
                               int M, int N, int K, const void* bias, const void* residual, int ldr,
                               const void* gate, int gate_stride, int rows_per_batch, int act,
                               int c_rows_per_batch, long c_batch_stride, int scatter_P, int scatter_G,
-                              void* const* peer_out, int force_bn, int* status, void* stream) {
+                              int scatter_rows, void* const* peer_out, int force_bn, int* status, void* stream) {
   using namespace omni;
   if (M <= 0 || N <= 0 || K <= 0) return RC_OK;
   if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7) || (ldr & 7) || (gate_stride & 7))
@@ -588,8 +595,15 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
   if (c_rows_per_batch > 0 && (c_batch_stride & 7)) return RC_BAD_ARG;
   epi.scatter_P = 0;
   epi.scatter_G = 0;
+  epi.scatter_rows = 0;
   for (int i = 0; i < 16; ++i) epi.peer_out[i] = nullptr;
-  if (scatter_P > 1) {
+  if (scatter_rows > 0) {
+    // row owners: ceil(M / scatter_rows) ranks, at most 16
+    const int owners = (M + scatter_rows - 1) / scatter_rows;
+    if (owners > 16 || peer_out == nullptr || scatter_P != owners) return RC_BAD_ARG;
+    epi.scatter_rows = scatter_rows;
+    for (int i = 0; i < owners; ++i) epi.peer_out[i] = static_cast<__nv_bfloat16*>(peer_out[i]);
+  } else if (scatter_P > 1) {
     if (scatter_P > 16 || scatter_G <= 0 || (scatter_G & 31) || peer_out == nullptr || (N % scatter_G)) return RC_BAD_ARG;
     epi.scatter_P = scatter_P;
     epi.scatter_G = scatter_G;

@@ -208,10 +208,14 @@ class QwenImageTransformer2DModel(nn.Module):
             cfg, D, dt = self.cfg, self.cfg.inner_dim, self.dtype_
             S = S_img + S_txt
             e = lambda *s: torch.empty(*s, dtype=dt, device=device)
+            # under tensor parallelism the head / MLP-column dimension is this rank's share
+            tp = getattr(self, "tp_heads", 0)
+            Dl = tp * cfg.attention_head_dim if tp else D
+            Fl = cfg.mlp_ratio * D * Dl // D
             self._ws = _Workspace(key, dict(
-                qkv=e(B, S, 3 * D), img_n=e(B, S_img, D), txt_n=e(B, S_txt, D),
-                attn_img=e(B, S_img, D), attn_txt=e(B, S_txt, D),
-                mlp_img=e(B, S_img, cfg.mlp_ratio * D), mlp_txt=e(B, S_txt, cfg.mlp_ratio * D)))
+                qkv=e(B, S, 3 * Dl), img_n=e(B, S_img, D), txt_n=e(B, S_txt, D),
+                attn_img=e(B, S_img, Dl), attn_txt=e(B, S_txt, Dl),
+                mlp_img=e(B, S_img, Fl), mlp_txt=e(B, S_txt, Fl)))
         return self._ws.bufs
 
     # -------------------------------------------------------------------- forward
@@ -233,21 +237,35 @@ class QwenImageTransformer2DModel(nn.Module):
             self.sp.norm_rope(blk.img.norm_q, blk.img.norm_k, blk.txt.norm_q, blk.txt.norm_k, cos, sin, cfg.eps)
             attn_img, attn_txt = self.sp.attend(kv_lens, ws)
         else:
+            # tensor parallel: this rank projects and attends its H / P heads; nothing else changes
+            tp = getattr(self, "tp_heads", 0)
+            Hl = tp or H
+            Dl = Hl * Hd
             qkv = ws["qkv"]
             for sp, xn, rows, off in ((blk.img, ws["img_n"], S_img, 0), (blk.txt, ws["txt_n"], S_txt, S_img)):
-                sp.to_qkv(xn, out=qkv[:, off:off + rows], out_rows_per_batch=rows, out_batch_stride=S * 3 * D)
-            fused.qk_norm_rope_(qkv, H, H, Hd, wq=blk.img.norm_q, wk=blk.img.norm_k, wq_alt=blk.txt.norm_q,
+                proj = sp.tp_attn.up if tp else sp.to_qkv
+                proj(xn, out=qkv[:, off:off + rows], out_rows_per_batch=rows, out_batch_stride=S * 3 * Dl)
+            fused.qk_norm_rope_(qkv, Hl, Hl, Hd, wq=blk.img.norm_q, wk=blk.img.norm_k, wq_alt=blk.txt.norm_q,
                                 wk_alt=blk.txt.norm_k, s_alt=S_img, cos=cos, sin=sin, interleaved=True, eps=cfg.eps)
-            q5 = qkv.view(B, S, 3, H, Hd)
+            q5 = qkv.view(B, S, 3, Hl, Hd)
             self.attn_impl(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], kv_lens=kv_lens,
-                           out=ws["attn_img"].view(B, S_img, H, Hd), out2=ws["attn_txt"].view(B, S_txt, H, Hd),
+                           out=ws["attn_img"].view(B, S_img, Hl, Hd), out2=ws["attn_txt"].view(B, S_txt, Hl, Hd),
                            split=S_img)
             attn_img, attn_txt = ws["attn_img"], ws["attn_txt"]
+        tp = getattr(self, "tp_heads", 0) if self.sp is None else 0
         for sidx, (sp, x, xn, att, hbuf) in enumerate(((blk.img, img, ws["img_n"], attn_img, ws["mlp_img"]),
                                                        (blk.txt, txt, ws["txt_n"], attn_txt, ws["mlp_txt"]))):
             if x.shape[1] == 0:
                 continue
             mm = m[:, sidx]
+            if tp:
+                # row-parallel halves: partial tiles go to their row owners from the GEMM epilogue,
+                # gate / residual are applied by the reduce kernel
+                sp.tp_attn.down(att, gate=mm[:, 2 * D:3 * D], residual=x, out=x)
+                fused.norm_modulate(x, shift=mm[:, 3 * D:4 * D], scale=mm[:, 4 * D:5 * D], eps=cfg.eps, out=xn)
+                sp.tp_mlp.up(xn, act="gelu_tanh", out=hbuf)
+                sp.tp_mlp.down(hbuf, gate=mm[:, 5 * D:6 * D], residual=x, out=x)
+                continue
             sp.to_out(att, residual=x, gate=mm[:, 2 * D:3 * D], out=x)
             fused.norm_modulate(x, shift=mm[:, 3 * D:4 * D], scale=mm[:, 4 * D:5 * D], eps=cfg.eps, out=xn)
             sp.mlp_up(xn, act="gelu_tanh", out=hbuf)

@@ -47,7 +47,7 @@ def linear_reference(x, w, bias=None, act=None, residual=None, gate=None):
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
            residual: torch.Tensor | None = None, gate: torch.Tensor | None = None,
            out: torch.Tensor | None = None, force_bn: int = 0,
-           out_rows_per_batch: int = 0, out_batch_stride: int = 0, scatter=None) -> torch.Tensor:
+           out_rows_per_batch: int = 0, out_batch_stride: int = 0, scatter=None, row_scatter=None) -> torch.Tensor:
     """y = residual + gate * act(x @ w.T + bias).
 
     ``out_rows_per_batch`` / ``out_batch_stride`` (elements): row r of the result is stored at
@@ -57,6 +57,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
     ``scatter = (P, G, ptrs, ld)``: fused all-to-all epilogue.  Column group g (G columns) goes to
     rank g % P, into the buffer at device pointer ``ptrs[g % P]`` (row pitch ``ld`` elements) at
     column (g // P) * G + col % G.  ``out`` is ignored (pass None).
+
+    ``row_scatter = (rows_per_owner, ptrs, ld)``: fused reduce-scatter feed.  Output row r goes to
+    rank r // rows_per_owner, as row r % rows_per_owner of the buffer at ``ptrs[that rank]`` (row
+    pitch ``ld``).  ``len(ptrs)`` must equal ceil(M / rows_per_owner).  ``out`` is ignored.
 
     x: [..., K] bf16 (last dim contiguous), w: [N, K] bf16, bias: [N], residual: [..., N]
     (may be ``out``), gate: [B, N] view (last dim contiguous, any row stride) where the rows
@@ -77,8 +81,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
     M = x2.shape[0]
     if w.stride(-1) != 1:
         w = w.contiguous()
-    sc_P, sc_G, sc_arr = 0, 0, None
-    if scatter is not None:
+    sc_P, sc_G, sc_rows, sc_arr = 0, 0, 0, None
+    if row_scatter is not None:
+        sc_rows, ptrs, ldc = row_scatter
+        sc_P = len(ptrs)
+        sc_arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        scatter = row_scatter
+        out = x
+    elif scatter is not None:
         sc_P, sc_G, ptrs, ldc = scatter
         sc_arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
         out = x                      # placeholder object; the kernel writes through the peer pointers
@@ -111,6 +121,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
         nv.ptr(out), ctypes.c_int(ldc), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
         nv.ptr(bias), nv.ptr(res2), ctypes.c_int(ldr), nv.ptr(gate), ctypes.c_int(gs), ctypes.c_int(rpb),
         ctypes.c_int(ACT[act]), ctypes.c_int(out_rows_per_batch), ctypes.c_long(out_batch_stride),
-        ctypes.c_int(sc_P), ctypes.c_int(sc_G), sc_arr, ctypes.c_int(force_bn), nv.ptr(st), nv.stream_ptr())
+        ctypes.c_int(sc_P), ctypes.c_int(sc_G), ctypes.c_int(sc_rows), sc_arr, ctypes.c_int(force_bn), nv.ptr(st),
+        nv.stream_ptr())
     nv.check_rc(rc, "omni_gemm_bf16")
     return None if scatter is not None else out

@@ -60,8 +60,12 @@ class GroupCoordinator:
         if self.world_size == 1:
             return [x] if separate_tensors else x
         x = x.contiguous()
-        out = torch.empty((self.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x, group=self.device_group)
+        if x.dim() == 0:
+            x = x.reshape(1)
+        # the flat (concatenated along dim 0) form is the one both NCCL and Gloo accept
+        flat = torch.empty((self.world_size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, x, group=self.device_group)
+        out = flat.view((self.world_size,) + tuple(x.shape))
         if separate_tensors:
             return list(out.unbind(0))
         if dim < 0:

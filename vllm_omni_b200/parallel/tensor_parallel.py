@@ -5,12 +5,12 @@ GEMM (attention out, MLP down) whose partial sums must be added across ranks.  T
 uses vLLM's ``ColumnParallelLinear`` / ``RowParallelLinear`` with an NCCL all-reduce after every
 row-parallel layer (vllm_omni/diffusion/distributed/parallel_state.py:769).
 
-Here the reduction is folded into the GEMM's output stage: every rank writes its partial tile
-into ITS slot of a symmetric peer buffer; after one bounded-wait barrier each rank reduces the
-rows it owns by reading all slots over NVLink (reduce-scatter), applies gate/residual on those
-rows, and broadcasts them with peer stores (all-gather) — two kernels and two barriers instead
-of GEMM + all-reduce + elementwise.  ``mode="nccl"`` keeps the all-reduce baseline (and is the
-CPU path).
+Here the reduce-scatter is folded into the GEMM: its epilogue stores every output tile through
+NVLink into the slot this rank owns on the rank that owns those rows (csrc/gemm_sm100.cu,
+``scatter_rows``), so the transfer overlaps the main loop tile by tile.  After one bounded-wait
+barrier each rank adds the P slots of its rows from LOCAL memory, applies bias / gate / residual
+and stores the finished rows to every rank (csrc/tp_reduce.cu), then a second barrier.
+``mode="nccl"`` keeps the all-reduce baseline (and is the CPU path).
 """
 from __future__ import annotations
 
@@ -39,72 +39,88 @@ def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 
 
 class RowParallelReduce:
-    """Sum of per-rank partial outputs, then gate * y + residual, identical on every rank."""
+    """Row-parallel linear layer: ``y = residual + gate * (sum_r x_r @ w_r.T + bias)`` where rank r
+    holds the r-th slice of the input features, identical on every rank afterwards.
+
+    ``mode="peer"``: the GEMM's epilogue stores each 128-row tile of its partial product straight
+    into the slot reserved for this rank on the rank that owns those rows (NVLink stores while
+    the main loop runs on the next tile), one bounded barrier, a reduce kernel that reads only
+    local memory and stores the finished rows to every rank, one barrier.
+    ``mode="nccl"`` is GEMM + all-reduce + eager epilogue (baseline, and the CPU path).
+    """
 
     def __init__(self, group, mode: str | None = None):
         self.group = group
         self.P, self.rank = group.world_size, group.rank_in_group
         self.mode = mode or ("peer" if torch.cuda.is_available() else "nccl")
-        self.arena = None
-        self._key = None
+        self._states: dict = {}      # (M, N, dtype, device) -> (arena, slots, result, rows per owner)
 
-    def _setup(self, y):
-        key = (tuple(y.shape), y.dtype, str(y.device))
-        if self._key == key:
-            return
-        self._key = key
-        from .peer_memory import PeerArena
-        if self.arena is not None:
-            self.arena.close()
-        nbytes = y.numel() * y.element_size()
-        self.arena = PeerArena(self.group, nbytes * (self.P + 1) + 16384, y.device)
-        self.slots = self.arena.alloc((self.P,) + tuple(y.shape), y.dtype)     # slot r written by rank r
-        self.result = self.arena.alloc(tuple(y.shape), y.dtype)
+    def _setup(self, M, N, dtype, device):
+        key = (M, N, dtype, str(device))
+        st = self._states.get(key)
+        if st is None:
+            from .peer_memory import PeerArena
+            P = self.P
+            per = (-(-M // P) + 7) // 8 * 8
+            esz = torch.empty(0, dtype=dtype).element_size()
+            arena = PeerArena(self.group, (P * per * N + M * N) * esz + 65536, device)
+            slots = arena.alloc((P, per, N), dtype)      # slot s: rank s's partial of MY rows
+            result = arena.alloc((M, N), dtype)
+            st = self._states[key] = (arena, slots, result, per)
+        self.arena, self.slots, self.result, self.per = st
 
-    def __call__(self, partial: torch.Tensor, bias=None, gate=None, residual=None, out=None):
-        if self.P == 1 or self.mode == "nccl" or not partial.is_cuda:
-            y = partial.float()
-            if self.P > 1:
-                y = y.contiguous()
-                self.group.all_reduce(y)
-            return _finish(y, bias, gate, residual, out, partial.dtype)
-        from .peer_memory import tensor_from_ptr
-        self._setup(partial)
-        P, r = self.P, self.rank
-        self.slots.local[r].copy_(partial)
+    def linear(self, layer: FusedLinear, x: torch.Tensor, bias=None, gate=None, residual=None, out=None):
+        """``layer`` holds this rank's [N, K/P] weight slice, ``x`` its [.., K/P] input slice."""
+        N = layer.out_features
+        if self.P == 1 or self.mode == "nccl" or not x.is_cuda:
+            partial = layer(x)
+            return self(partial, bias=bias, gate=gate, residual=residual, out=out)
+        import ctypes
+        from ..ops import _native as nv
+        from ..ops import gemm
+        x2 = x.reshape(-1, x.shape[-1])
+        M = x2.shape[0]
+        self._setup(M, N, x.dtype, x.device)
+        P, r, per = self.P, self.rank, self.per
+        esz = x.element_size()
+        owners = -(-M // per)
+        # my partial of owner o's rows lands in slot r of owner o
+        ptrs = [self.slots.ptrs[o] + r * per * N * esz for o in range(owners)]
+        gemm.linear(x2, layer.weight, None, row_scatter=(per, ptrs, N))
         self.arena.barrier()
-        rows = partial.shape[-2]
-        per = (rows + P - 1) // P
-        lo, hi = min(rows, r * per), min(rows, (r + 1) * per)
-        if hi > lo:
-            acc = None
-            for src in range(P):       # reduce-scatter: pull my rows of every rank's partial over NVLink
-                peer = tensor_from_ptr(self.slots.ptrs[src], (P,) + tuple(partial.shape), partial.dtype, partial.device)
-                part = peer[src][..., lo:hi, :].float()
-                acc = part if acc is None else acc + part
-            mine = _finish(acc, bias, _rows(gate, partial, lo, hi), _slice(residual, lo, hi), None, partial.dtype)
-            for dst in range(P):       # all-gather: push my finished rows to every rank
-                peer = tensor_from_ptr(self.result.ptrs[dst], tuple(partial.shape), partial.dtype, partial.device)
-                peer[..., lo:hi, :].copy_(mine)
+        lo, hi = min(M, r * per), min(M, (r + 1) * per)
+        rpb = 0
+        gs = 0
+        if gate is not None:
+            assert gate.dim() == 2 and gate.stride(1) == 1 and M % gate.shape[0] == 0
+            rpb = M // gate.shape[0]
+            gs = gate.stride(0) if gate.shape[0] > 1 else N
+        res2 = residual.reshape(-1, N) if residual is not None else None
+        arr = (ctypes.c_void_p * P)(*self.result.ptrs)
+        rc = nv.lib("tp_reduce").omni_tp_reduce_gather(
+            nv.ptr(self.slots.local), ctypes.c_int(P), ctypes.c_int(per), ctypes.c_int(N), ctypes.c_int(lo),
+            ctypes.c_int(hi - lo), nv.ptr(bias), nv.ptr(gate), ctypes.c_int(gs), ctypes.c_int(rpb), nv.ptr(res2),
+            ctypes.c_long(res2.stride(0) if res2 is not None else 0), arr, ctypes.c_long(N), nv.stream_ptr())
+        nv.check_rc(rc, "omni_tp_reduce_gather")
         self.arena.barrier()
-        res = self.result.local
+        res = self.result.local.view(*x.shape[:-1], N)
         if out is not None:
             out.copy_(res)
             return out
         return res.clone()
 
+    def __call__(self, partial: torch.Tensor, bias=None, gate=None, residual=None, out=None):
+        """All-reduce form: ``partial`` is this rank's full-size partial product."""
+        y = partial.float()
+        if self.P > 1:
+            y = y.contiguous()
+            self.group.all_reduce(y)
+        return _finish(y, bias, gate, residual, out, partial.dtype)
+
     def close(self):
-        if self.arena is not None:
-            self.arena.close()
-            self.arena = None
-
-
-def _slice(t, lo, hi):
-    return None if t is None else t[..., lo:hi, :]
-
-
-def _rows(gate, like, lo, hi):
-    return gate
+        for arena, *_ in self._states.values():
+            arena.close()
+        self._states.clear()
 
 
 def _finish(y, bias, gate, residual, out, dtype):
@@ -138,6 +154,14 @@ class TPLinearPair:
         self.second.weight.data = shard_cols(second.weight.data, r, P)
         self.second_bias = second.bias
         self.reduce = reducer or RowParallelReduce(group)
+
+    def up(self, x, **kw):
+        """Column-parallel half: this rank's slice of the output features."""
+        return self.first(x, **kw)
+
+    def down(self, h, gate=None, residual=None, out=None):
+        """Row-parallel half on this rank's slice ``h`` of the input features; full result."""
+        return self.reduce.linear(self.second, h, bias=self.second_bias, gate=gate, residual=residual, out=out)
 
 
 def shard_transformer(tr, group, mode: str | None = None) -> None:
