@@ -111,10 +111,20 @@ class ClockSampler:
                 "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def default_parallelism(n: int) -> str:
+    """The two CFG branches go to two halves of the GPUs (no per-layer traffic between them);
+    each half splits the sequence (fused Ulysses) when it has more than one GPU."""
+    if n == 1:
+        return "single"
+    if n == 2:
+        return "cfg2"
+    return f"cfg2xsp{n // 2}" if n % 2 == 0 else f"sp{n}"
+
+
 def parse_parallelism(spec: str | None, n: int) -> dict:
     if n == 1:
         return {}
-    spec = (spec or f"sp{n}").lower()
+    spec = (spec or default_parallelism(n)).lower()
     out = {"ulysses_degree": 1, "ring_degree": 1, "cfg_parallel_size": 1, "tensor_parallel_size": 1}
     for part in spec.split("x"):
         if part.startswith("cfg"):
@@ -243,7 +253,7 @@ def main():
                        "global_batch": B, "seq_len": (args.height // 16) * (args.width // 16) + L,
                        "image": f"{args.height}x{args.width}", "num_inference_steps": args.num_inference_steps,
                        "true_cfg_scale": args.cfg_scale,
-                       "parallelism": args.parallelism or (f"sp{args.gpus}" if args.gpus > 1 else "single"),
+                       "parallelism": args.parallelism or default_parallelism(args.gpus),
                        "l2": "inputs+weights (40 GB) exceed L2; no explicit flush",
                        "step_definition": "one full image: 50 denoise steps x (cond+uncond) + VAE decode"},
             "clocks": clocks, "gpu_launches": int(launches),
@@ -254,7 +264,17 @@ def main():
         print(json.dumps(rec), flush=True)
     omni.close()
     if world > 1 and dist.is_initialized():
-        dist.destroy_process_group()
+        # Sub-groups whose NCCL communicator was never used (the peer-memory paths exchange their
+        # handles over Gloo) can fail to shut down cleanly; the measurement is already printed, so
+        # leave together and skip the interpreter's teardown of the process groups.
+        torch.cuda.synchronize()
+        try:
+            dist.barrier()
+        except Exception:   # noqa: BLE001
+            pass
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 
