@@ -75,7 +75,8 @@ def load_omni_transfer_config(stage_configs: list, runtime_cfg: dict | None = No
              for k, v in (runtime_cfg.get("connectors") or {}).items()}
     edges: dict[tuple[int, int], ConnectorSpec] = {}
     for e in runtime_cfg.get("edges") or []:
-        edges[(int(e["from"]), int(e["to"]))] = named[e["connector"]]
+        if e.get("connector"):              # an edge may only carry window settings
+            edges[(int(e["from"]), int(e["to"]))] = named[e["connector"]]
     for sc in stage_configs:
         for src in sc.engine_input_source:
             key = (int(src), int(sc.stage_id))
