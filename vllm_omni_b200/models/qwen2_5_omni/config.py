@@ -1,0 +1,110 @@
+"""Configuration of the three Qwen2.5-Omni stages (thinker, talker, token2wav); defaults are
+the 7B model's shapes (vllm_omni/model_executor/models/qwen2_5_omni/qwen2_5_omni.py:58-140)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+from ..qwen3_omni.config import AudioEncoderConfig, VisionEncoderConfig
+from ..qwen_decoder import DecoderConfig
+
+
+@dataclass
+class DiTConfig:
+    """Flow-matching transformer: codec tokens -> mel spectrogram."""
+    hidden_size: int = 1024
+    num_hidden_layers: int = 22
+    num_attention_heads: int = 16
+    head_dim: int = 64
+    ff_mult: int = 2
+    mel_dim: int = 80
+    num_embeds: int = 8193              # codec vocabulary + 1 "dropped" id
+    emb_dim: int = 512
+    repeats: int = 2                    # mel frames per codec token
+    block_size: int = 24                # block-sparse attention: frames per block
+    look_ahead_blocks: int = 1
+    look_backward_blocks: int = 2
+    speaker_dim: int = 128              # conditioning vector (speaker / voice embedding)
+    num_steps: int = 10
+    guidance_scale: float = 0.5
+    sway_coefficient: float = -1.0
+
+
+@dataclass
+class BigVGANConfig:
+    mel_dim: int = 80
+    upsample_initial_channel: int = 1536
+    upsample_rates: tuple = (5, 3, 2, 2, 2, 2)
+    upsample_kernel_sizes: tuple = (11, 7, 4, 4, 4, 4)
+    resblock_kernel_sizes: tuple = (3, 7, 11)
+    resblock_dilation_sizes: tuple = ((1, 3, 5), (1, 3, 5), (1, 3, 5))
+    sample_rate: int = 24000
+
+    @property
+    def total_upsample(self) -> int:
+        n = 1
+        for r in self.upsample_rates:
+            n *= r
+        return n
+
+
+@dataclass
+class Qwen25OmniConfig:
+    thinker: DecoderConfig = field(default_factory=lambda: DecoderConfig(
+        vocab_size=152064, hidden_size=3584, num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4,
+        head_dim=128, intermediate_size=18944, qk_norm=False, attention_bias=True, rope_theta=1e6,
+        mrope_section=(16, 24, 24)))
+    talker: DecoderConfig = field(default_factory=lambda: DecoderConfig(
+        vocab_size=8448, hidden_size=896, num_hidden_layers=24, num_attention_heads=12, num_key_value_heads=4,
+        head_dim=128, intermediate_size=18944, qk_norm=False, attention_bias=True, rope_theta=1e6,
+        mrope_section=(16, 24, 24)))
+    audio: AudioEncoderConfig = field(default_factory=lambda: AudioEncoderConfig(output_dim=3584))
+    vision: VisionEncoderConfig = field(default_factory=lambda: VisionEncoderConfig(out_hidden_size=3584))
+    dit: DiTConfig = field(default_factory=DiTConfig)
+    bigvgan: BigVGANConfig = field(default_factory=BigVGANConfig)
+    audio_token_id: int = 151646
+    image_token_id: int = 151655
+    video_token_id: int = 151656
+    im_end_token_id: int = 151645
+    codec_pad_id: int = 8292
+    codec_bos_id: int = 8293
+    codec_eos_id: int = 8294
+
+    @classmethod
+    def tiny(cls) -> "Qwen25OmniConfig":
+        th = DecoderConfig(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=16, intermediate_size=96, qk_norm=False,
+                           attention_bias=True, mrope_section=(4, 2, 2))
+        tk = DecoderConfig(vocab_size=96, hidden_size=32, num_hidden_layers=2, num_attention_heads=2,
+                           num_key_value_heads=2, head_dim=16, intermediate_size=64, qk_norm=False,
+                           attention_bias=True, mrope_section=(4, 2, 2))
+        return cls(thinker=th, talker=tk,
+                   audio=AudioEncoderConfig(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=2,
+                                            encoder_ffn_dim=64, downsample_hidden_size=8, output_dim=64, n_window=8),
+                   vision=VisionEncoderConfig(depth=1, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=4,
+                                              temporal_patch_size=1, spatial_merge_size=2, out_hidden_size=64),
+                   dit=DiTConfig(hidden_size=32, num_hidden_layers=2, num_attention_heads=2, head_dim=16, mel_dim=8,
+                                 num_embeds=97, emb_dim=16, block_size=4, speaker_dim=8, num_steps=3),
+                   bigvgan=BigVGANConfig(mel_dim=8, upsample_initial_channel=16, upsample_rates=(2, 2),
+                                         upsample_kernel_sizes=(4, 4), resblock_kernel_sizes=(3,),
+                                         resblock_dilation_sizes=((1, 3),)),
+                   audio_token_id=500, image_token_id=501, video_token_id=502, im_end_token_id=507,
+                   codec_pad_id=92, codec_bos_id=93, codec_eos_id=94)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Qwen25OmniConfig":
+        c = cls()
+        th = d.get("thinker_config", {})
+        if th.get("text_config"):
+            c.thinker = DecoderConfig.from_dict({**th["text_config"], "qk_norm": False, "attention_bias": True})
+        tk = d.get("talker_config", {})
+        if tk:
+            c.talker = DecoderConfig.from_dict({**tk, "qk_norm": False, "attention_bias": True})
+        for k, src in (("audio_token_id", "audio_token_index"), ("image_token_id", "image_token_index"),
+                       ("video_token_id", "video_token_index")):
+            if src in th:
+                setattr(c, k, th[src])
+        for k, src in (("codec_pad_id", "tts_codec_pad_token_id"), ("codec_bos_id", "tts_codec_start_token_id"),
+                       ("codec_eos_id", "tts_codec_end_token_id")):
+            if src in tk:
+                setattr(c, k, tk[src])
+        return c
