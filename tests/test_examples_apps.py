@@ -1,0 +1,86 @@
+"""User-facing scripts: the ComfyUI-style nodes against a fake server transport, the offline
+throughput benchmark on the tiny pipeline, and that every example at least parses."""
+import ast
+import base64
+import io
+import pathlib
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def test_examples_and_benchmarks_parse():
+    files = list((ROOT / "examples").rglob("*.py")) + list((ROOT / "benchmarks").rglob("*.py")) + \
+        list((ROOT / "apps").rglob("*.py"))
+    assert len(files) >= 10
+    for f in files:
+        ast.parse(f.read_text(), filename=str(f))
+
+
+def test_comfy_nodes_round_trip(monkeypatch):
+    sys.path.insert(0, str(ROOT / "apps"))
+    try:
+        from comfyui_nodes import NODE_CLASS_MAPPINGS, nodes
+    finally:
+        sys.path.pop(0)
+    from PIL import Image
+    seen = {}
+
+    class Resp:
+        status_code = 200
+
+        def __init__(self, payload=None, content=b""):
+            self._p, self.content, self.text = payload, content, ""
+
+        def json(self):
+            return self._p
+
+    def fake_post(url, **kw):
+        seen[url.rsplit("/", 1)[-1]] = kw
+        if url.endswith("generations") or url.endswith("edits"):
+            buf = io.BytesIO()
+            Image.new("RGB", (8, 4), (255, 0, 0)).save(buf, format="PNG")
+            n = (kw.get("json") or {}).get("n", 1)
+            return Resp({"data": [{"b64_json": base64.b64encode(buf.getvalue()).decode()}] * n})
+        import struct
+        pcm = struct.pack("<4h", 0, 16384, -16384, 0)
+        wav = b"RIFF" + struct.pack("<I", 36 + len(pcm)) + b"WAVEfmt " + struct.pack("<IHHIIHH", 16, 1, 1, 24000, 48000, 2, 16) \
+            + b"data" + struct.pack("<I", len(pcm)) + pcm
+        if url.endswith("speech"):
+            return Resp(content=wav)
+        return Resp({"choices": [{"message": {"content": "hi", "audio": {"data": base64.b64encode(wav).decode()}}}]})
+
+    monkeypatch.setattr(nodes, "_post", fake_post)
+    img, = NODE_CLASS_MAPPINGS["OmniImageGenerate"]().run("http://s", "m", "p", 8, 4, 2, 4.0, 1, n=2)
+    assert tuple(img.shape) == (2, 4, 8, 3) and float(img[0, 0, 0, 0]) == 1.0
+    assert seen["generations"]["json"]["size"] == "8x4"
+    out, = NODE_CLASS_MAPPINGS["OmniImageEdit"]().run("http://s", "m", img[:1], "p", 2, 0)
+    assert tuple(out.shape) == (1, 4, 8, 3) and seen["edits"]["files"]["image"][2] == "image/png"
+    audio, = NODE_CLASS_MAPPINGS["OmniSpeech"]().run("http://s", "m", "hello", "default")
+    assert audio["sample_rate"] == 24000 and tuple(audio["waveform"].shape) == (1, 1, 4)
+    assert abs(float(audio["waveform"][0, 0, 1]) - 0.5) < 1e-4
+    text, audio = NODE_CLASS_MAPPINGS["OmniChat"]().run("http://s", "m", "hello", True, image=img[:1])
+    assert text == "hi" and tuple(audio["waveform"].shape) == (1, 1, 4)
+    assert seen["completions"]["json"]["messages"][0]["content"][1]["type"] == "image_url"
+
+
+def test_offline_throughput_benchmark_tiny():
+    sys.path.insert(0, str(ROOT / "benchmarks" / "qwen3_omni"))
+    try:
+        import offline_throughput
+    finally:
+        sys.path.pop(0)
+    rec = offline_throughput.main(["--tiny", "--num-prompts", "3", "--input-len", "6"])
+    assert rec["requests"] == 3 and rec["text_tokens_per_s"] > 0 and rec["audio_seconds_per_s"] > 0
+
+
+def test_ray_backend_reports_missing_dependency():
+    from vllm_omni_b200.distributed import ray_utils
+    assert ray_utils.stage_bundles([type("S", (), {"runtime": {"devices": "0,1"}})(),
+                                    type("S", (), {"runtime": {}})()]) == [{"GPU": 2.0, "CPU": 1.0}, {"GPU": 1.0, "CPU": 1.0}]
+    if not ray_utils.ray_available():
+        with pytest.raises(RuntimeError, match="ray"):
+            ray_utils.require_ray()
