@@ -124,3 +124,42 @@ def test_tensor_parallel_matches_single_rank_gpu(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     run_distributed(_tp_worker, 2, "nccl", args=("nccl", mode, "bfloat16", 128, 4, 0.06))
+
+
+def _hybrid_worker(rank, world, backend, mode, dtype_name, head_dim, heads, tol):
+    """Ulysses 2 x ring 2 on four ranks == single rank."""
+    from vllm_omni_b200.parallel import parallel_state as ps
+    from vllm_omni_b200.parallel.hybrid import HybridJointAttention
+    dtype = getattr(torch, dtype_name)
+    device = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+    ps.init_distributed_environment(world, rank, local_rank=rank, backend=backend)
+    ps.initialize_model_parallel(sequence_parallel_size=world, ulysses_degree=2, ring_degree=2, backend=backend)
+    m = _build(dtype, device, head_dim, heads)
+    B, h, w, St = 2, 8, 8, 6 * world
+    g = torch.Generator(device="cpu").manual_seed(2)
+    x = torch.randn(B, h * w, 16, generator=g).to(device)
+    e = torch.randn(B, St, 64, generator=g).to(device)
+    t = torch.tensor([0.6, 0.6], device=device)
+    lens = [St, St - 7]                    # the second sample's padding spans more than one ring chunk
+    ref = m(x, e, t, (1, h, w), txt_seq_lens=lens).float()
+    m.sp = HybridJointAttention(ps.get_sp_group(), heads, head_dim, mode=mode)
+    Si, Sl = h * w // world, St // world
+    y = m(x[:, rank * Si:(rank + 1) * Si].contiguous(), e[:, rank * Sl:(rank + 1) * Sl].contiguous(), t, (1, h, w),
+          txt_seq_lens=lens).float()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+    err = (y - ref[:, rank * Si:(rank + 1) * Si]).abs().max().item()
+    assert err < tol * max(1.0, ref.abs().max().item()), f"rank {rank}: {err}"
+    m.sp.close()
+    ps.destroy_distributed_environment()
+
+
+def test_hybrid_ulysses_ring_matches_single_rank_cpu_gloo():
+    run_distributed(_hybrid_worker, 4, "gloo", args=("gloo", "nccl", "float32", 32, 4, 2e-4))
+
+
+@pytest.mark.gpu
+def test_hybrid_ulysses_ring_matches_single_rank_gpu():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    run_distributed(_hybrid_worker, 4, "nccl", args=("nccl", "peer", "bfloat16", 128, 4, 0.06))

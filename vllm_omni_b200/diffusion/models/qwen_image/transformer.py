@@ -360,8 +360,10 @@ class QwenImageTransformer2DModel(nn.Module):
         st.out = e(B, S_img, cfg.patch_size * cfg.patch_size * cfg.out_channels)
         st.graph = None
         # library collectives (the NCCL baseline mode) are not captured: only our own kernels are
-        nccl_sp = self.sp is not None and getattr(self.sp, "mode", "") == "nccl"
-        st.use_graph = bool(use_graph) and dev.type == "cuda" and self.block_hook is None and not nccl_sp
+        # collectives issued by NCCL (and host-side index building) do not go into a CUDA graph
+        nccl_sp = self.sp is not None and not getattr(self.sp, "graph_safe", getattr(self.sp, "mode", "") == "fused")
+        st.use_graph = (bool(use_graph) and dev.type == "cuda" and self.block_hook is None and not nccl_sp
+                        and not getattr(self, "tp_heads", 0))
         return st
 
     def _step_body(self, st: "DenoiseLoopState"):

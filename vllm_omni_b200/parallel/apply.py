@@ -10,9 +10,11 @@ from . import parallel_state as ps
 def apply_parallelism(pipe, od_config) -> None:
     pc = od_config.parallel_config
     tr = getattr(pipe, "transformer", None)
-    if pc.ulysses_degree > 1 and tr is not None:
-        if pc.ring_degree > 1:
-            raise NotImplementedError("hybrid Ulysses x ring is configured through parallel.ring.RingJointAttention")
+    if pc.ulysses_degree > 1 and pc.ring_degree > 1 and tr is not None:
+        from .hybrid import HybridJointAttention
+        tr.sp = HybridJointAttention(ps.get_sp_group(), tr.cfg.num_attention_heads, tr.cfg.attention_head_dim,
+                                     mode=os.environ.get("OMNI_SP_MODE"))
+    elif pc.ulysses_degree > 1 and tr is not None:
         from .ulysses import UlyssesJointAttention
         mode = os.environ.get("OMNI_SP_MODE")            # "fused" (default on GPU) or "nccl" (baseline)
         tr.sp = UlyssesJointAttention(ps.get_sp_group().ulysses, tr.cfg.num_attention_heads,

@@ -1,0 +1,121 @@
+"""Hybrid Ulysses x ring sequence parallelism (P5).
+
+The SP group of U * R ranks is a grid: ``ulysses`` groups are the contiguous runs of U ranks (one
+ring chunk of the sequence each), ``ring`` groups connect the ranks with the same position in
+their run (vllm_omni/diffusion/distributed/parallel_state.py:477-621).  Rank (u, r) owns
+S / (U R) rows.  Per block:
+
+1. head <-> sequence all-to-all INSIDE the Ulysses group (the fused GEMM-epilogue scatter on
+   GPUs): the rank now holds q, k, v of ring chunk r (S / R rows) for its H / U heads;
+2. attention of that chunk's queries against the keys of EVERY ring chunk: the R ranks of the ring
+   group publish their K/V in symmetric memory and each rank's attention kernel reads chunk
+   (r + step) mod R from its peer through TMA descriptors on the peer pointer (plain loads);
+   partial results are merged with their log-sum-exp, as in ring attention;
+3. the reverse all-to-all inside the Ulysses group gives the local rows all heads again.
+
+``mode="nccl"`` does steps 1-3 with collectives and send/recv (baseline and CPU test path).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops.attention import attention
+from .comm import RingComm, all_to_all_4d
+from .ring import merge_attention
+from .ulysses import UlyssesJointAttention
+
+
+class HybridJointAttention:
+    graph_safe = False        # the reverse all-to-all is an NCCL call
+
+    def __init__(self, sp_group, num_heads: int, head_dim: int, mode: str | None = None):
+        self.group = sp_group
+        self.P, self.rank = sp_group.world_size, sp_group.rank_in_group
+        self.U, self.R = sp_group.ulysses_world_size, sp_group.ring_world_size
+        self.u, self.r = sp_group.ulysses_rank, sp_group.ring_rank
+        if self.rank != self.r * self.U + self.u:
+            raise ValueError("the SP group must be laid out with Ulysses ranks contiguous")
+        self.mode = mode or ("peer" if torch.cuda.is_available() else "nccl")
+        self.uly = UlyssesJointAttention(sp_group.ulysses, num_heads, head_dim,
+                                         mode="fused" if self.mode == "peer" else "nccl")
+        self.H, self.Dh, self.Hp = num_heads, head_dim, num_heads // self.U
+        self.arena = None
+        self._key = None
+
+    def setup(self, B, Si_loc, St_loc, device, dtype):
+        self.uly.setup(B, Si_loc, St_loc, device, dtype)
+        key = (B, Si_loc, St_loc, str(device), dtype)
+        if self._key == key:
+            return
+        self._key = key
+        self.B, self.Si_loc, self.St_loc = B, Si_loc, St_loc
+        self.Si_c, self.St_c = Si_loc * self.U, St_loc * self.U          # rows of one ring chunk
+        self.S_c = self.Si_c + self.St_c
+        self.S_img, self.S_txt = self.Si_c * self.R, self.St_c * self.R
+        if self.mode == "peer":
+            from .peer_memory import PeerArena
+            if self.arena is not None:
+                self.arena.close()
+            es = torch.empty(0, dtype=dtype).element_size()
+            self.arena = PeerArena(self.group.ring, B * self.S_c * 2 * self.Hp * self.Dh * es + 8192, device)
+            self.kv = self.arena.alloc((B, self.S_c, 2, self.Hp, self.Dh), dtype)
+
+    # same interface as UlyssesJointAttention -------------------------------------------
+    def project_qkv(self, img_lin, xn_img, txt_lin, xn_txt):
+        self.uly.project_qkv(img_lin, xn_img, txt_lin, xn_txt)
+
+    def norm_rope(self, wq, wk, wq_txt, wk_txt, cos, sin, eps):
+        # this chunk's rows of the global [all image rows, all text rows] position table
+        r = self.r
+        idx = torch.cat([torch.arange(r * self.Si_c, (r + 1) * self.Si_c),
+                         torch.arange(self.S_img + r * self.St_c, self.S_img + (r + 1) * self.St_c)]).to(cos.device)
+        self.uly.norm_rope(wq, wk, wq_txt, wk_txt, cos[idx].contiguous(), sin[idx].contiguous(), eps)
+
+    def _chunk_kv_lens(self, kv_lens, chunk):
+        if kv_lens is None:
+            return None
+        txt_valid = (kv_lens - self.S_img - chunk * self.St_c).clamp(0, self.St_c)
+        return (self.Si_c + txt_valid).to(torch.int32)
+
+    def attend(self, kv_lens, ws):
+        B = self.B
+        q5 = self.uly.joint_local.view(B, self.S_c, 3, self.Hp, self.Dh)
+        q = q5[:, :, 0]
+        out = lse = None
+        if self.mode == "peer":
+            from .peer_memory import tensor_from_ptr
+            self.kv.local.copy_(q5[:, :, 1:3])
+            self.arena.barrier()                                  # every chunk's K/V is published
+            for step in range(self.R):
+                src = (self.r + step) % self.R
+                kv = tensor_from_ptr(self.kv.ptrs[src], (B, self.S_c, 2, self.Hp, self.Dh), q.dtype, q.device)
+                o_b, lse_b = attention(q, kv[:, :, 0], kv[:, :, 1], kv_lens=self._chunk_kv_lens(kv_lens, src),
+                                       return_lse=True)
+                out, lse = merge_attention(out, lse, o_b, lse_b)
+            self.arena.barrier()                                  # published K/V may be overwritten
+        else:
+            comm = RingComm(self.group.ring.device_group)
+            k, v = q5[:, :, 1].contiguous(), q5[:, :, 2].contiguous()
+            for step in range(self.R):
+                src = (self.r - step) % self.R
+                if step + 1 < self.R:
+                    nk, nv_ = comm.send_recv(k), comm.send_recv(v)
+                    comm.commit()
+                o_b, lse_b = attention(q, k, v, kv_lens=self._chunk_kv_lens(kv_lens, src), return_lse=True)
+                out, lse = merge_attention(out, lse, o_b, lse_b)
+                if step + 1 < self.R:
+                    comm.wait()
+                    k, v = nk, nv_
+        o = out.to(q.dtype)                                       # [B, S_c, Hp, Dh]
+        grp = self.group.ulysses.device_group
+        oi = all_to_all_4d(o[:, :self.Si_c].contiguous(), 1, 2, grp).reshape(B, self.Si_loc, self.H * self.Dh)
+        ot = None
+        if self.St_loc:
+            ot = all_to_all_4d(o[:, self.Si_c:].contiguous(), 1, 2, grp).reshape(B, self.St_loc, self.H * self.Dh)
+        return oi, ot
+
+    def close(self):
+        self.uly.close()
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None
