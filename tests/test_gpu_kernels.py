@@ -242,3 +242,54 @@ def test_paged_prefill_chunk(dev, T, L):
     ref = A.attention_reference(q[None], k[None], v[None], causal=True, q_offset=L - T)[0]
     _status_ok(dev)
     assert (out.float() - ref.float()).abs().max().item() < 0.03
+
+
+@pytest.mark.parametrize("N,H,W,cin,cout,k", [(1, 16, 16, 16, 96, 3), (2, 13, 21, 96, 192, 3), (1, 40, 24, 384, 384, 3),
+                                            (1, 9, 7, 96, 8, 3), (2, 10, 33, 192, 96, 1)])
+def test_conv2d_nhwc_implicit_gemm(dev, N, H, W, cin, cout, k):
+    from vllm_omni_b200.ops import conv as C
+    torch.manual_seed(5)
+    w = torch.randn(cout, cin, k, k, device=dev) * (1.0 / (cin * k * k) ** 0.5)
+    b = torch.randn(cout, device=dev) * 0.1
+    wp, bp = C.pack_conv_weight(w, b)
+    x = torch.randn(N, H, W, cin, device=dev, dtype=torch.bfloat16)
+    res = torch.randn(N, H, W, wp.shape[0], device=dev, dtype=torch.bfloat16)
+    y = C.conv2d_nhwc(x, wp, bp, k, cin, act="silu", residual=res)
+    ref = C.conv2d_nhwc_reference(x, wp, bp, k, cin, act="silu", residual=res)
+    _status_ok(dev)
+    assert (y.float() - ref).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
+
+
+def test_vae_elementwise_nhwc(dev):
+    from vllm_omni_b200.ops import conv as C
+    torch.manual_seed(6)
+    x = torch.randn(2, 9, 11, 96, device=dev, dtype=torch.bfloat16) * 3
+    g = (torch.rand(96, device=dev) + 0.5).bfloat16()
+    for silu in (True, False):
+        y = C.rmsnorm_silu_nhwc(x, g, silu=silu)
+        ref = C.rmsnorm_silu_nhwc(x.cpu(), g.cpu(), silu=silu)
+        assert (y.cpu().float() - ref.float()).abs().max().item() < 0.03
+    assert torch.equal(C.upsample2x_nhwc(x).cpu(), C.upsample2x_nhwc(x.cpu()))
+    z = torch.randn(2, 5, 7, 6, device=dev)
+    assert torch.equal(C.nchw_to_nhwc(z).cpu(), C.nchw_to_nhwc(z.cpu()))
+    img = torch.randn(2, 6, 5, 8, device=dev, dtype=torch.bfloat16)
+    assert torch.equal(C.nhwc_to_image(img).cpu(), C.nhwc_to_image(img.cpu()))
+    d = (C.nhwc_to_image(img, uint8=True).cpu().int() - C.nhwc_to_image(img.cpu(), uint8=True).int()).abs().max()
+    assert int(d) <= 1
+
+
+def test_vae_decoder_nhwc_matches_torch(dev):
+    from vllm_omni_b200.diffusion.models.vae.autoencoder_kl_qwenimage import AutoencoderKLQwenImage2d, QwenImageVAEConfig
+    torch.manual_seed(7)
+    vae = AutoencoderKLQwenImage2d(QwenImageVAEConfig()).to(dev).bfloat16()
+    for p in vae.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, (1.0 / p[0].numel()) ** 0.5)
+    z = torch.randn(1, 16, 24, 20, device=dev)
+    vae.decoder_impl = "torch"
+    ref = vae.decode(z).float()
+    vae.decoder_impl = "nhwc"
+    out = vae.decode(z).float()
+    _status_ok(dev)
+    assert out.shape == ref.shape == (1, 3, 192, 160)
+    assert (out - ref).abs().mean().item() < 0.02 and (out - ref).abs().max().item() < 0.25

@@ -73,6 +73,14 @@ def main(argv=None):
         q = torch.randn(n, H, 128, device=dev, dtype=bf)
         fn = lambda: KC.paged_decode(q, kc, vc, bt, sl, impl=a.impl)
         bytes_ = 2.0 * kc.numel() * 2
+    elif a.case in ("vae", "vae_torch"):
+        # 1024 x 1024 image: latent 16 x 128 x 128 through the full decoder
+        from vllm_omni_b200.diffusion.models.vae.autoencoder_kl_qwenimage import AutoencoderKLQwenImage2d
+        vae = AutoencoderKLQwenImage2d().to(dev).bfloat16()
+        vae.decoder_impl = "torch" if a.case == "vae_torch" else "nhwc"
+        z = torch.randn(1, 16, 128, 128, device=dev)
+        fn = lambda: vae.decode(z)
+        bytes_ = 0.0
     else:
         raise SystemExit(f"unknown case {a.case}")
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)

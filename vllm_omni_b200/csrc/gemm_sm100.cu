@@ -54,6 +54,19 @@ struct GemmEpilogue {
   __nv_bfloat16* peer_out[16];
 };
 
+// Implicit-GEMM convolution (stride 1, "same" padding, NHWC bf16): the M dimension is the output
+// pixels, walked in patches of CONV_BH x CONV_BW = 128 pixels; K runs over taps x input-channel
+// blocks of 64.  The A tile of one (tap, channel block) is ONE 4-D TMA box
+// {64 channels, CONV_BW, CONV_BH, 1 image} of the input, shifted by the tap's offset; pixels
+// outside the image are filled with zeros by TMA, which is the padding.  taps == 0: plain GEMM.
+constexpr int CONV_BW = 16, CONV_BH = 8;
+struct ConvGeom {
+  int taps;        // 0 (GEMM), 1 (1x1) or 9 (3x3)
+  int H, W;        // output (= input) height and width
+  int tiles_x, tiles_y;
+  int cin_blocks;  // ceil(Cin / 64); the weight matrix is [Cout, taps * cin_blocks * 64]
+};
+
 template <int BN>
 struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -146,7 +159,7 @@ template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  __nv_bfloat16* __restrict__ C, int ldc, int M, int N, int K, GemmEpilogue epi,
-                 const int* __restrict__ tile_expert, int* status) {
+                 const int* __restrict__ tile_expert, ConvGeom conv, int* status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
 
@@ -206,7 +219,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t fb = smem_u32(&full_bar[stage]);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-          tma_load_2d(sa, &tmA, fb, kb * BK, mb * BM);
+          if (conv.taps) {
+            const int per_img = conv.tiles_x * conv.tiles_y;
+            const int img = mb / per_img, rem = mb - img * per_img;
+            const int y0 = (rem / conv.tiles_x) * CONV_BH, x0 = (rem % conv.tiles_x) * CONV_BW;
+            const int tap = kb / conv.cin_blocks, cb = kb - tap * conv.cin_blocks;
+            const int dy = conv.taps == 9 ? tap / 3 - 1 : 0, dx = conv.taps == 9 ? tap % 3 - 1 : 0;
+            tma_load_4d(sa, &tmA, fb, cb * BK, x0 + dx, y0 + dy, img);
+          } else {
+            tma_load_2d(sa, &tmA, fb, kb * BK, mb * BM);
+          }
           tma_load_3d(sa + Cfg::A_BYTES, &tmB, fb, kb * BK, nb * BN, ex);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -261,8 +283,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (tile_expert && tile_expert[mb] < 0) continue;
       mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, &s_abort, status, ERR_WAIT_TMEM_FULL);
       tc_fence_after_sync();
-      const int row = mb * BM + q * 32 + lane;
-      const bool row_ok = row < M;
+      int row = mb * BM + q * 32 + lane;
+      bool row_ok = row < M;
+      if (conv.taps) {
+        // row of the tile -> pixel of the patch -> row of the [N*H*W, Cout] output
+        const int per_img = conv.tiles_x * conv.tiles_y;
+        const int img = mb / per_img, rem = mb - img * per_img;
+        const int r = q * 32 + lane;
+        const int y = (rem / conv.tiles_x) * CONV_BH + r / CONV_BW, x = (rem % conv.tiles_x) * CONV_BW + r % CONV_BW;
+        row_ok = y < conv.H && x < conv.W;
+        row = (img * conv.H + y) * conv.W + x;
+      }
       const __nv_bfloat16* gate_row = nullptr;
       if (epi.gate && row_ok) gate_row = epi.gate + (size_t)(row / epi.rows_per_batch) * epi.gate_stride;
 #pragma unroll 1
@@ -523,7 +554,8 @@ static int pick_pair_tn(int M, int N, int pairs) {
 template <int BN>
 static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, int ldc, int M,
                        int N, int K, int ldw, const GemmEpilogue& epi, int* status, int max_ctas,
-                       cudaStream_t stream, int num_experts = 1, const int* tile_expert = nullptr) {
+                       cudaStream_t stream, int num_experts = 1, const int* tile_expert = nullptr,
+                       const ConvGeom* conv = nullptr) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmB;
   // weights as [E, N, K]; a plain linear layer is E = 1
@@ -539,7 +571,9 @@ static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, 
   }
   const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
-  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, tile_expert, status);
+  ConvGeom geom = {};
+  if (conv) geom = *conv;
+  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, tile_expert, geom, status);
   return (int)cudaGetLastError();
 }
 
@@ -662,5 +696,55 @@ extern "C" int omni_gemm_bf16_grouped(const void* A, int lda, const void* W, int
     case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert);
     case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert);
     default: return RC_BAD_ARG;
+  }
+}
+
+
+// Convolution, stride 1, zero "same" padding, NHWC bf16:  y[n,h,w,:] = act(sum_taps x[n,h+dy,w+dx,:] W_tap^T + bias)
+// (+ residual).  x: [Nimg, H, W, Cin] with pixel pitch ldx (elements, >= Cin, multiple of 8);
+// w: [Cout, taps * cin_pad] with cin_pad = ceil(Cin / 64) * 64, tap-major (tap = ky * 3 + kx for 3x3),
+// zero in the padding columns; y / residual: [Nimg*H*W, ldy / ldr].  ksize is 1 or 3.
+extern "C" int omni_conv2d_nhwc_bf16(const void* x, long ldx, const void* w, void* y, int ldy, int Nimg, int H, int W,
+                                     int Cin, int Cout, int ksize, const void* bias, const void* residual, int ldr,
+                                     int act, int* status, void* stream) {
+  using namespace omni;
+  if (Nimg <= 0 || H <= 0 || W <= 0 || Cin <= 0 || Cout <= 0) return RC_OK;
+  if ((ksize != 1 && ksize != 3) || (Cout & 7) || (ldx & 7) || (ldy & 7) || (ldr & 7)) return RC_BAD_ARG;
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return RC_NO_DRIVER;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return RC_BAD_ARG;
+  ConvGeom g;
+  g.taps = ksize * ksize;
+  g.H = H; g.W = W;
+  g.tiles_x = (W + CONV_BW - 1) / CONV_BW;
+  g.tiles_y = (H + CONV_BH - 1) / CONV_BH;
+  g.cin_blocks = (Cin + BK - 1) / BK;
+  CUtensorMap tmA;
+  {
+    cuuint64_t gdim[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)Nimg};
+    cuuint64_t gstr[3] = {(cuuint64_t)ldx * 2, (cuuint64_t)ldx * 2 * W, (cuuint64_t)ldx * 2 * W * H};
+    cuuint32_t box[4] = {BK, CONV_BW, CONV_BH, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(x), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return RC_TMAP;
+  }
+  GemmEpilogue epi = {};
+  epi.bias = static_cast<const __nv_bfloat16*>(bias);
+  epi.residual = static_cast<const __nv_bfloat16*>(residual);
+  epi.ldr = ldr;
+  epi.rows_per_batch = 1;
+  epi.act = act;
+  const int K = g.taps * g.cin_blocks * BK;
+  const int M = Nimg * g.tiles_x * g.tiles_y * BM;       // rows as the tile scheduler counts them
+  const int ctas = sm_count();
+  const int bn = pick_bn(M, Cout, ctas);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* c = static_cast<__nv_bfloat16*>(y);
+  switch (bn) {
+    case 256: return launch_gemm<256>(tmA, w, c, ldy, M, Cout, K, K, epi, status, ctas, s, 1, nullptr, &g);
+    case 192: return launch_gemm<192>(tmA, w, c, ldy, M, Cout, K, K, epi, status, ctas, s, 1, nullptr, &g);
+    default: return launch_gemm<128>(tmA, w, c, ldy, M, Cout, K, K, epi, status, ctas, s, 1, nullptr, &g);
   }
 }

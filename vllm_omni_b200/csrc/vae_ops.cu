@@ -1,0 +1,156 @@
+// K12 (element-wise part): the VAE decoder's non-convolution kernels on channels-last (NHWC) bf16
+// activations.  The convolutions themselves run as implicit GEMMs on the tcgen05 kernel
+// (gemm_sm100.cu, omni_conv2d_nhwc_bf16).
+//
+//   omni_rmsnorm_silu_nhwc   y = silu( x / sqrt(mean_c x^2) * gamma )      per pixel, fused
+//   omni_upsample2x_nhwc     nearest-neighbour 2x up-sampling
+//   omni_nchw_to_nhwc        fp32/bf16 [N,C,H,W] -> bf16 [N,H,W,Cpad] (zero padded channels)
+//   omni_nhwc_to_image       bf16 [N,H,W,ld] -> uint8 [N,H,W,3] ((x * 0.5 + 0.5) clamped, * 255, rounded)
+//                            or fp32 [N,3,H,W] in [-1, 1]
+//
+// The reference decodes through diffusers' AutoencoderKL* modules, i.e. cuDNN convolutions with
+// separate eager norm / activation / interpolate / permute / clamp kernels
+// (vllm_omni/diffusion/models/qwen_image/autoencoder_kl_qwenimage.py).
+#include "host_util.h"
+#include "ptx_sm100.cuh"
+
+namespace omni {
+
+// one warp per pixel; C % 8 == 0, C <= 1024
+__global__ void __launch_bounds__(256)
+rmsnorm_silu_nhwc_kernel(const __nv_bfloat16* __restrict__ x, long ldx, const __nv_bfloat16* __restrict__ gamma,
+                         __nv_bfloat16* __restrict__ y, long ldy, long pixels, int C, int apply_silu) {
+  const long p = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (p >= pixels) return;
+  const int chunks = C >> 3;
+  float v[4][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = lane + i * 32;
+    if (c < chunks) {
+      const uint4 u = *reinterpret_cast<const uint4*>(x + p * ldx + c * 8);
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = b.x; v[i][3] = b.y; v[i][4] = cc.x; v[i][5] = cc.y; v[i][6] = d.x; v[i][7] = d.y;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = rsqrtf(fmaxf(ss / (float)C, 1e-24f));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = lane + i * 32;
+    if (c < chunks) {
+      const uint4 g = *reinterpret_cast<const uint4*>(gamma + c * 8);
+      const float2 a = unpack_bf16(g.x), b = unpack_bf16(g.y), cc = unpack_bf16(g.z), d = unpack_bf16(g.w);
+      const float gm[8] = {a.x, a.y, b.x, b.y, cc.x, cc.y, d.x, d.y};
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float t = v[i][e] * inv * gm[e];
+        o[e] = apply_silu ? silu(t) : t;
+      }
+      uint4 w;
+      w.x = pack_bf16(o[0], o[1]); w.y = pack_bf16(o[2], o[3]); w.z = pack_bf16(o[4], o[5]); w.w = pack_bf16(o[6], o[7]);
+      *reinterpret_cast<uint4*>(y + p * ldy + c * 8) = w;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+upsample2x_nhwc_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int N, int H, int W, int C) {
+  const int chunks = C >> 3;
+  const long total = (long)N * (2 * H) * (2 * W) * chunks;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % chunks);
+    long p = i / chunks;
+    const int ox = (int)(p % (2 * W)); p /= 2 * W;
+    const int oy = (int)(p % (2 * H));
+    const int n = (int)(p / (2 * H));
+    const size_t src = (((size_t)n * H + (oy >> 1)) * W + (ox >> 1)) * C + c * 8;
+    *reinterpret_cast<uint4*>(y + (i / chunks) * C + c * 8) = *reinterpret_cast<const uint4*>(x + src);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ y, int N, int C, int H, int W, int Cpad) {
+  const long total = (long)N * H * W * Cpad;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % Cpad);
+    const long p = i / Cpad;                 // n * H * W + h * W + w
+    const long hw = p % ((long)H * W);
+    const long n = p / ((long)H * W);
+    y[i] = c < C ? __float2bfloat16((float)x[(n * C + c) * (long)H * W + hw]) : __float2bfloat16(0.f);
+  }
+}
+
+// mode 0: uint8 [N,H,W,3]; mode 1: fp32 [N,3,H,W] clamped to [-1, 1]
+__global__ void __launch_bounds__(256)
+nhwc_to_image_kernel(const __nv_bfloat16* __restrict__ x, long ldx, void* __restrict__ out, long pixels, long HW, int mode) {
+  for (long p = (long)blockIdx.x * blockDim.x + threadIdx.x; p < pixels; p += (long)gridDim.x * blockDim.x) {
+    float v[3];
+#pragma unroll
+    for (int c = 0; c < 3; ++c) v[c] = fminf(fmaxf(__bfloat162float(x[p * ldx + c]), -1.f), 1.f);
+    if (mode == 0) {
+      uint8_t* o = static_cast<uint8_t*>(out) + p * 3;
+#pragma unroll
+      for (int c = 0; c < 3; ++c) o[c] = (uint8_t)__float2int_rn((v[c] * 0.5f + 0.5f) * 255.f);
+    } else {
+      float* o = static_cast<float*>(out);
+      const long n = p / HW, hw = p % HW;
+#pragma unroll
+      for (int c = 0; c < 3; ++c) o[(n * 3 + c) * HW + hw] = v[c];
+    }
+  }
+}
+
+static unsigned grid_for(long total) {
+  long b = (total + 255) / 256;
+  if (b > 148L * 16) b = 148L * 16;
+  return (unsigned)(b < 1 ? 1 : b);
+}
+
+}  // namespace omni
+
+using namespace omni;
+
+extern "C" int omni_rmsnorm_silu_nhwc(const void* x, long ldx, const void* gamma, void* y, long ldy, long pixels, int C,
+                                      int apply_silu, void* stream) {
+  if (pixels <= 0) return RC_OK;
+  if ((C & 7) || C > 1024 || (ldx & 7) || (ldy & 7)) return RC_BAD_ARG;
+  rmsnorm_silu_nhwc_kernel<<<(unsigned)((pixels + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)y, ldy, pixels, C, apply_silu);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int omni_upsample2x_nhwc(const void* x, void* y, int N, int H, int W, int C, void* stream) {
+  if (N <= 0 || H <= 0 || W <= 0) return RC_OK;
+  if (C & 7) return RC_BAD_ARG;
+  upsample2x_nhwc_kernel<<<grid_for((long)N * 4 * H * W * (C >> 3)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, H, W, C);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int omni_nchw_to_nhwc(const void* x, int is_fp32, void* y, int N, int C, int H, int W, int Cpad, void* stream) {
+  if (N <= 0) return RC_OK;
+  if (Cpad < C) return RC_BAD_ARG;
+  const unsigned g = grid_for((long)N * H * W * Cpad);
+  if (is_fp32)
+    nchw_to_nhwc_kernel<float><<<g, 256, 0, (cudaStream_t)stream>>>((const float*)x, (__nv_bfloat16*)y, N, C, H, W, Cpad);
+  else
+    nchw_to_nhwc_kernel<__nv_bfloat16><<<g, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, C, H, W, Cpad);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int omni_nhwc_to_image(const void* x, long ldx, void* out, int N, int H, int W, int mode, void* stream) {
+  if (N <= 0) return RC_OK;
+  if (ldx < 3 || (mode != 0 && mode != 1)) return RC_BAD_ARG;
+  const long pixels = (long)N * H * W;
+  nhwc_to_image_kernel<<<grid_for(pixels), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, out, pixels,
+                                                                         (long)H * W, mode);
+  return (int)cudaGetLastError();
+}

@@ -11,6 +11,7 @@ Layout: channels_last bf16 so the convolutions run as implicit GEMMs on tensor c
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -165,6 +166,8 @@ class AutoencoderKLQwenImage2d(nn.Module):
         self.use_tiling = False
         self.tile_latent = 64
         self.tile_overlap = 8
+        self.decoder_impl = os.environ.get("OMNI_VAE_IMPL", "nhwc")      # "nhwc" (own kernels) | "torch" (cuDNN)
+        self._nhwc = None                                               # repacked weights, built on first use
 
     @property
     def dtype(self):
@@ -184,9 +187,16 @@ class AutoencoderKLQwenImage2d(nn.Module):
     def decode(self, z):
         """z: [B, z_dim, h, w] normalised latents -> [B, 3, 8h, 8w] in [-1, 1]."""
         z = self.denormalize(z.float()).to(self.dtype)
+        tiled = self.use_tiling and max(z.shape[-2:]) > self.tile_latent
+        if z.is_cuda and self.dtype == torch.bfloat16 and not tiled and self.decoder_impl != "torch":
+            # channels-last decoder on the implicit-GEMM convolution kernels
+            if self._nhwc is None:
+                from .nhwc_decoder import NHWCDecoder
+                self._nhwc = NHWCDecoder(self.decoder, self.post_quant_conv, torch.bfloat16)
+            return self._nhwc(z)
         if z.is_cuda:
             z = z.contiguous(memory_format=torch.channels_last)
-        if self.use_tiling and max(z.shape[-2:]) > self.tile_latent:
+        if tiled:
             return self._tiled_decode(z)
         return self.decoder(self.post_quant_conv(z)).clamp_(-1, 1)
 
@@ -212,6 +222,7 @@ class AutoencoderKLQwenImage2d(nn.Module):
     @torch.no_grad()
     def load_weights(self, weights) -> set:
         """Accepts diffusers ``AutoencoderKLQwenImage`` names; 5-D kernels are sliced to 2-D."""
+        self._nhwc = None
         own = dict(self.named_parameters())
         loaded = set()
         for name, w in weights:
