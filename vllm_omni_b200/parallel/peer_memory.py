@@ -13,11 +13,13 @@ kernels (vllm_omni/diffusion/distributed/group_coordinator.py).
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from ..ops import _native as nv
 
+_CANARY_BYTE = 0xA5
 _ALIGN = 1024
 
 
@@ -57,7 +59,12 @@ class PeerArena:
         self.group = group
         self.rank, self.world = group.rank_in_group, group.world_size
         self.device = device or torch.device("cuda", torch.cuda.current_device())
-        self.nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
+        # OMNI_PEER_CANARY=1 (debug / tests): a guard block filled with a pattern follows every
+        # allocation and is verified on the host by check_canaries() / close(), so a kernel that
+        # stores past the end of a peer buffer is caught without any device-side trap
+        self._canary = os.environ.get("OMNI_PEER_CANARY") == "1"
+        self._guards: list[int] = []
+        self.nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN + (64 * _ALIGN if self._canary else 0)
         self.timeout_ns = int(timeout_ms) * 1_000_000
         self._lib = nv.lib("peer_rt")
         self._flag_bytes = _ALIGN                      # world u64 flags + the epoch counter
@@ -96,8 +103,22 @@ class PeerArena:
         if off + nbytes > self.nbytes + self._flag_bytes:
             raise MemoryError(f"peer arena exhausted: need {nbytes} B at offset {off}, arena {self.nbytes} B")
         self._bump = (off + nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
+        if self._canary and self._bump + _ALIGN <= self.nbytes + self._flag_bytes:
+            g = self._bump
+            tensor_from_ptr(self._base + g, (_ALIGN,), torch.uint8, self.device, owner=self).fill_(_CANARY_BYTE)
+            self._guards.append(g)
+            self._bump += _ALIGN
         local = tensor_from_ptr(self._base + off, shape, dtype, self.device, owner=self)
         return SymTensor(local, [b + off for b in self.bases], off)
+
+    def check_canaries(self) -> list[int]:
+        """Offsets of guard blocks (this rank's arena) that no longer hold the pattern."""
+        bad = []
+        for g in self._guards:
+            t = tensor_from_ptr(self._base + g, (_ALIGN,), torch.uint8, self.device, owner=self)
+            if not bool((t == _CANARY_BYTE).all().item()):
+                bad.append(g)
+        return bad
 
     def barrier(self) -> None:
         """Device-side barrier over the group on the current stream (bounded wait)."""
@@ -118,6 +139,9 @@ class PeerArena:
             self.group.barrier()
         except Exception:
             pass
+        bad = self.check_canaries() if self._canary else []
         for p in self._opened:
             self._lib.omni_peer_close(ctypes.c_void_p(p))
         self._lib.omni_peer_free(ctypes.c_void_p(self._base))
+        if bad:
+            raise RuntimeError(f"peer arena guard blocks overwritten at offsets {bad} (rank {self.rank})")
