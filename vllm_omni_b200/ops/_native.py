@@ -22,6 +22,31 @@ class NativeError(RuntimeError):
 # kernels launched per exported entry point (default 1); used for the launch counter
 _KERNELS_PER_CALL = {"omni_rel_l1": 2, "omni_rel_l1_parts": 0, "omni_paged_decode": 2, "omni_gemm_set_pair_mode": 0}
 launch_count = 0
+_timing: list | None = None      # (entry point, start event, stop event) while kernel timing is on
+
+
+def enable_kernel_timing(on: bool = True) -> None:
+    """Bracket every native launch with CUDA events; read the result with ``kernel_timing_summary``."""
+    global _timing
+    _timing = [] if on else None
+
+
+def kernel_timing_summary(reset: bool = True) -> dict[str, dict]:
+    """Per entry point: launches, total and mean device time in ms (synchronises the device)."""
+    global _timing
+    out: dict[str, dict] = {}
+    if not _timing:
+        return out
+    torch.cuda.synchronize()
+    for name, e0, e1 in _timing:
+        d = out.setdefault(name, {"launches": 0, "total_ms": 0.0})
+        d["launches"] += 1
+        d["total_ms"] += e0.elapsed_time(e1)
+    for d in out.values():
+        d["mean_us"] = 1000.0 * d["total_ms"] / max(1, d["launches"])
+    if reset:
+        _timing = []
+    return out
 
 
 class _CountingLib:
@@ -37,9 +62,18 @@ class _CountingLib:
             raw = getattr(self._cdll, name)
             n = _KERNELS_PER_CALL.get(name, 1)
 
-            def fn(*args, _raw=raw, _n=n):
+            def fn(*args, _raw=raw, _n=n, _name=name):
                 global launch_count
                 launch_count += _n
+                if _timing is not None and _n:
+                    # device timers around the launch (CUDA events on the launching stream); only
+                    # meaningful outside CUDA-graph capture
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    rc = _raw(*args)
+                    e1.record()
+                    _timing.append((_name, e0, e1))
+                    return rc
                 return _raw(*args)
 
             self._fns[name] = fn
