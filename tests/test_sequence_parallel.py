@@ -163,3 +163,33 @@ def test_hybrid_ulysses_ring_matches_single_rank_gpu():
     if torch.cuda.device_count() < 4:
         pytest.skip("needs 4 GPUs")
     run_distributed(_hybrid_worker, 4, "nccl", args=("nccl", "peer", "bfloat16", 128, 4, 0.06))
+
+
+def _wan_sp_worker(rank, world, backend, uly, ring):
+    """Wan-style video DiT with the token rows sharded over Ulysses x ring == single rank,
+    including a sequence length that is not a multiple of the SP degree (padding + key mask)."""
+    from vllm_omni_b200.diffusion.models.wan.transformer import WanTransformer3DModel, WanTransformerConfig
+    from vllm_omni_b200.parallel import parallel_state as ps
+    from vllm_omni_b200.parallel.sp_attention import SequenceParallelAttention
+    ps.init_distributed_environment(world, rank, local_rank=rank, backend=backend)
+    ps.initialize_model_parallel(sequence_parallel_size=world, ulysses_degree=uly, ring_degree=ring, backend=backend)
+    cfg = WanTransformerConfig(num_layers=2, num_attention_heads=4, attention_head_dim=24, ffn_dim=128, text_dim=32,
+                               freq_dim=32, in_channels=4, out_channels=4)
+    torch.manual_seed(0)
+    m = WanTransformer3DModel(cfg, dtype=torch.float32, device="cpu")
+    g = torch.Generator().manual_seed(3)
+    for T, H, W in ((2, 8, 8), (3, 6, 10)):            # 32 tokens (divisible) and 45 tokens (padded)
+        x = torch.randn(1, 4, T, H, W, generator=g)
+        e = torch.randn(1, 7, 32, generator=g)
+        t = torch.tensor([500.0])
+        m.sp = None
+        ref = m(x, t, e)
+        m.sp = SequenceParallelAttention(ps.get_sp_group(), 4, 24, mode="nccl")
+        y = m(x, t, e)
+        assert torch.allclose(y, ref, atol=3e-4, rtol=1e-3), (T, H, W, (y - ref).abs().max().item())
+    ps.destroy_distributed_environment()
+
+
+@pytest.mark.parametrize("uly,ring", [(2, 1), (1, 2), (2, 2)])
+def test_wan_sequence_parallel_cpu_gloo(uly, ring):
+    run_distributed(_wan_sp_worker, uly * ring, "gloo", args=("gloo", uly, ring))

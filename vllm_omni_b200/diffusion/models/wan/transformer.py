@@ -98,7 +98,9 @@ class WanTransformer3DModel(nn.Module):
         self.blocks = nn.ModuleList([WanBlock(cfg, dtype, device) for _ in range(cfg.num_layers)])
         self.out_table = nn.Parameter(torch.randn(2, D, dtype=dtype, device=device) / D ** 0.5, requires_grad=False)
         self.proj_out = FusedLinear(D, cfg.out_channels * pt * ph * pw, dtype=dtype, device=device)
-        self.sp = None
+        self.sp = None                   # SequenceParallelAttention when the sequence is sharded
+        self.sp_style = "attention"
+        self._sp_valid_len = None
         self.block_hook = None
         self._rope = {}
 
@@ -138,7 +140,11 @@ class WanTransformer3DModel(nn.Module):
         qk = torch.cat([q, k, qkv[..., 2 * D:]], dim=-1).contiguous()
         fused.qk_norm_rope_(qk, H, H, Dh, cos=cos, sin=sin, interleaved=True, eps=cfg.eps)
         q5 = qk.view(B, S, 3, H, Dh)
-        o = attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2]).reshape(B, S, D)
+        if self.sp is not None:
+            # sequence parallel: x holds this rank's rows; only self-attention sees the other ranks
+            o = self.sp(q5, valid_len=self._sp_valid_len).reshape(B, S, D)
+        else:
+            o = attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2]).reshape(B, S, D)
         blk.attn1_out(o, residual=x, gate=mod[:, 2 * D:3 * D], out=x)
         xn = fused.norm_modulate(x, weight=blk.norm2_w, bias=blk.norm2_b, eps=cfg.eps)
         q = fused.norm_modulate(blk.attn2_q(xn), weight=blk.attn2_norm_q, rms=True, eps=cfg.eps)
@@ -158,6 +164,15 @@ class WanTransformer3DModel(nn.Module):
         B = tokens.shape[0]
         x = self.patch_embedding(tokens.contiguous())
         cos, sin = self.rope(g, x.device)
+        S_full = x.shape[1]
+        if self.sp is not None:
+            # keep S / P rows (zero rows pad S up to a multiple of P and are masked as keys)
+            x, _ = self.sp.shard_rows(x, dim=1)
+            rows = self.sp.local_rows(S_full)
+            pad = x.shape[1] - cos[rows].shape[0]
+            cos = torch.cat([cos[rows], cos.new_ones(pad, cos.shape[1])]) if pad else cos[rows].contiguous()
+            sin = torch.cat([sin[rows], sin.new_zeros(pad, sin.shape[1])]) if pad else sin[rows].contiguous()
+            self._sp_valid_len = S_full if S_full % self.sp.P else None
         ctx = self.text_2(self.text_1(encoder_hidden_states.to(self.dtype_), act="gelu_tanh"))
         temb = self.time_2(self.time_1(timestep_sinusoid(timestep, cfg.freq_dim, scale=1.0).to(self.dtype_), act="silu"))
         e6 = self.time_proj(F.silu(temb)).view(B, 6, D)
@@ -168,7 +183,10 @@ class WanTransformer3DModel(nn.Module):
                 self.block_forward(blk, x, ctx, e6, cos, sin)
         om = (self.out_table[None].float() + temb[:, None].float()).to(x.dtype)      # [B,2,D]: shift, scale
         xn = fused.norm_modulate(x, shift=om[:, 0].contiguous(), scale=om[:, 1].contiguous(), eps=cfg.eps)
-        return self.unpatchify(self.proj_out(xn), g)
+        y = self.proj_out(xn)
+        if self.sp is not None:
+            y = self.sp.gather_rows(y, S_full, dim=1)
+        return self.unpatchify(y.contiguous(), g)
 
     @torch.no_grad()
     def load_weights(self, weights) -> set:

@@ -10,7 +10,14 @@ from . import parallel_state as ps
 def apply_parallelism(pipe, od_config) -> None:
     pc = od_config.parallel_config
     tr = getattr(pipe, "transformer", None)
-    if pc.ulysses_degree > 1 and pc.ring_degree > 1 and tr is not None:
+    if tr is not None and getattr(tr, "sp_style", "joint") == "attention" and pc.ulysses_degree * pc.ring_degree > 1:
+        # single-stream models shard rows themselves and only need a sequence-parallel attention
+        from .sp_attention import SequenceParallelAttention
+        for t in (tr, getattr(pipe, "transformer_2", None)):
+            if t is not None:
+                t.sp = SequenceParallelAttention(ps.get_sp_group(), t.cfg.num_attention_heads, t.cfg.attention_head_dim,
+                                                 mode=os.environ.get("OMNI_SP_MODE"))
+    elif pc.ulysses_degree > 1 and pc.ring_degree > 1 and tr is not None:
         from .hybrid import HybridJointAttention
         tr.sp = HybridJointAttention(ps.get_sp_group(), tr.cfg.num_attention_heads, tr.cfg.attention_head_dim,
                                      mode=os.environ.get("OMNI_SP_MODE"))

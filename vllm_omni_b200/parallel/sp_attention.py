@@ -1,0 +1,130 @@
+"""Sequence-parallel self-attention for single-stream DiTs (Wan, Z-Image, FLUX single blocks ...).
+
+The model keeps S / P rows of every sample on each rank; everything except self-attention is
+row-local.  ``SequenceParallelAttention`` takes the local ``[B, S_loc, 3, H, Dh]`` q/k/v (already
+normalised and rotated with the rows' own positions) and returns the local ``[B, S_loc, H, Dh]``
+attention output over the FULL sequence:
+
+* Ulysses degree U: head <-> sequence all-to-all inside the Ulysses group before and after;
+* ring degree R: the chunk's queries against every ring chunk's K/V — peer-KV reads through TMA
+  descriptors on the peer pointer (``mode="peer"``) or send/recv (``mode="nccl"``) — merged by
+  log-sum-exp;
+* both: the hybrid grid of vllm_omni/diffusion/distributed/parallel_state.py:477-621.
+
+``valid_len`` masks padding rows at the end of the global sequence (a model pads S up to a multiple
+of P), the role of ``auto_pad`` in the reference's ``_sp_plan`` (sp_plan.py).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops.attention import attention
+from .comm import RingComm, all_to_all_4d, all_to_all_5d
+from .ring import merge_attention
+
+
+class SequenceParallelAttention:
+    graph_safe = False
+
+    def __init__(self, sp_group, num_heads: int, head_dim: int, mode: str | None = None):
+        self.group = sp_group
+        self.P, self.rank = sp_group.world_size, sp_group.rank_in_group
+        self.U, self.R = sp_group.ulysses_world_size, sp_group.ring_world_size
+        self.u, self.r = sp_group.ulysses_rank, sp_group.ring_rank
+        if num_heads % self.U:
+            raise ValueError(f"num_heads ({num_heads}) must be divisible by the Ulysses degree ({self.U})")
+        self.H, self.Dh = num_heads, head_dim
+        self.mode = mode or ("peer" if torch.cuda.is_available() else "nccl")
+        self.arena = None
+        self._key = None
+
+    # rows ------------------------------------------------------------------------------
+    def shard_rows(self, x: torch.Tensor, dim: int = 1):
+        """Pad ``dim`` to a multiple of P with zeros and keep this rank's slice.  Returns
+        (local slice, original length)."""
+        S = x.shape[dim]
+        pad = (-S) % self.P
+        if pad:
+            shape = list(x.shape)
+            shape[dim] = pad
+            x = torch.cat([x, x.new_zeros(shape)], dim=dim)
+        per = x.shape[dim] // self.P
+        return x.narrow(dim, self.rank * per, per).contiguous(), S
+
+    def gather_rows(self, x: torch.Tensor, orig_len: int, dim: int = 1):
+        return self.group.all_gather(x.contiguous(), dim=dim).narrow(dim, 0, orig_len)
+
+    def local_rows(self, total_len: int) -> slice:
+        per = (total_len + self.P - 1) // self.P
+        return slice(self.rank * per, (self.rank + 1) * per)
+
+    # attention -------------------------------------------------------------------------
+    def _chunk_lens(self, valid_len, chunk, S_c, B, device):
+        if valid_len is None:
+            return None
+        n = max(0, min(S_c, int(valid_len) - chunk * S_c))
+        return torch.full((B,), n, dtype=torch.int32, device=device)
+
+    def _setup_arena(self, shape, dtype, device):
+        key = (tuple(shape), dtype, str(device))
+        if self._key == key:
+            return
+        self._key = key
+        from .peer_memory import PeerArena
+        if self.arena is not None:
+            self.arena.close()
+        n = 1
+        for s in shape:
+            n *= s
+        self.arena = PeerArena(self.group.ring, n * torch.empty(0, dtype=dtype).element_size() + 8192, device)
+        self.kv = self.arena.alloc(shape, dtype)
+
+    def __call__(self, q5: torch.Tensor, valid_len: int | None = None, scale: float | None = None) -> torch.Tensor:
+        B, S_loc = q5.shape[0], q5.shape[1]
+        if self.U > 1:
+            q5 = all_to_all_5d(q5.contiguous(), 3, 1, self.group.ulysses.device_group)    # [B, S_c, 3, H/U, Dh]
+        S_c = q5.shape[1]
+        q, k, v = q5[:, :, 0], q5[:, :, 1], q5[:, :, 2]
+        dev = q5.device
+        if self.R == 1:
+            o = attention(q, k, v, kv_lens=self._chunk_lens(valid_len, 0, S_c, B, dev), scale=scale)
+        else:
+            if valid_len is not None and int(valid_len) <= (self.R - 1) * S_c:
+                raise ValueError("padding may not cover a whole ring chunk")
+            out = lse = None
+            if self.mode == "peer" and q5.is_cuda:
+                from .peer_memory import tensor_from_ptr
+                shape = (B, S_c, 2, q5.shape[3], self.Dh)
+                self._setup_arena(shape, q5.dtype, dev)
+                self.kv.local.copy_(q5[:, :, 1:3])
+                self.arena.barrier()
+                for step in range(self.R):
+                    src = (self.r + step) % self.R
+                    kv = tensor_from_ptr(self.kv.ptrs[src], shape, q5.dtype, dev)
+                    o_b, lse_b = attention(q, kv[:, :, 0], kv[:, :, 1], scale=scale, return_lse=True,
+                                           kv_lens=self._chunk_lens(valid_len, src, S_c, B, dev))
+                    out, lse = merge_attention(out, lse, o_b, lse_b)
+                self.arena.barrier()
+            else:
+                comm = RingComm(self.group.ring.device_group)
+                k, v = k.contiguous(), v.contiguous()
+                for step in range(self.R):
+                    src = (self.r - step) % self.R
+                    if step + 1 < self.R:
+                        nk, nv_ = comm.send_recv(k), comm.send_recv(v)
+                        comm.commit()
+                    o_b, lse_b = attention(q, k, v, scale=scale, return_lse=True,
+                                           kv_lens=self._chunk_lens(valid_len, src, S_c, B, dev))
+                    out, lse = merge_attention(out, lse, o_b, lse_b)
+                    if step + 1 < self.R:
+                        comm.wait()
+                        k, v = nk, nv_
+            o = out.to(q5.dtype)
+        if self.U > 1:
+            o = all_to_all_4d(o.contiguous(), 1, 2, self.group.ulysses.device_group)      # [B, S_loc, H, Dh]
+        return o
+
+    def close(self):
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None
