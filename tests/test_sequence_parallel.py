@@ -193,3 +193,33 @@ def _wan_sp_worker(rank, world, backend, uly, ring):
 @pytest.mark.parametrize("uly,ring", [(2, 1), (1, 2), (2, 2)])
 def test_wan_sequence_parallel_cpu_gloo(uly, ring):
     run_distributed(_wan_sp_worker, uly * ring, "gloo", args=("gloo", uly, ring))
+
+
+def _zimage_sp_worker(rank, world, backend, uly, ring):
+    """Z-Image-style single-stream DiT (joint image + text rows, per-sample text padding) with the
+    rows sharded over the SP group == single rank."""
+    from vllm_omni_b200.diffusion.models.z_image.transformer import ZImageTransformer2DModel, ZImageTransformerConfig
+    from vllm_omni_b200.parallel import parallel_state as ps
+    from vllm_omni_b200.parallel.sp_attention import SequenceParallelAttention
+    ps.init_distributed_environment(world, rank, local_rank=rank, backend=backend)
+    ps.initialize_model_parallel(sequence_parallel_size=world, ulysses_degree=uly, ring_degree=ring, backend=backend)
+    cfg = ZImageTransformerConfig(dim=64, n_layers=2, n_heads=4, head_dim=16, ffn_dim=96, in_channels=8, out_channels=2,
+                                  cap_feat_dim=24, axes_dims_rope=(4, 6, 6))
+    torch.manual_seed(0)
+    m = ZImageTransformer2DModel(cfg, dtype=torch.float32, device="cpu")
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(2, 6 * 5, 8, generator=g)
+    e = torch.randn(2, 9, 24, generator=g)                 # 30 + 9 = 39 rows: padded to a multiple of P
+    t = torch.tensor([0.3, 0.3])
+    for lens in (None, [9, 5]):
+        m.sp = None
+        ref = m(x, e, t, (1, 6, 5), txt_seq_lens=lens)
+        m.sp = SequenceParallelAttention(ps.get_sp_group(), 4, 16, mode="nccl")
+        y = m(x, e, t, (1, 6, 5), txt_seq_lens=lens)
+        assert torch.allclose(y, ref, atol=3e-4, rtol=1e-3), (lens, (y - ref).abs().max().item())
+    ps.destroy_distributed_environment()
+
+
+@pytest.mark.parametrize("uly,ring", [(2, 1), (2, 2)])
+def test_zimage_sequence_parallel_cpu_gloo(uly, ring):
+    run_distributed(_zimage_sp_worker, uly * ring, "gloo", args=("gloo", uly, ring))

@@ -72,6 +72,8 @@ class ZImageTransformer2DModel(nn.Module):
         self.final_adaln = FusedLinear(min(D, 256), D, dtype=dtype, device=device)
         self.proj_out = FusedLinear(D, c.out_channels * 4, dtype=dtype, device=device)
         self.block_hook = None
+        self.sp = None                   # SequenceParallelAttention when the joint sequence is sharded
+        self.sp_style = "attention"
         self._ang = {}
 
     @staticmethod
@@ -98,6 +100,21 @@ class ZImageTransformer2DModel(nn.Module):
         cap = self.cap_embedder(fused.norm_modulate(encoder_hidden_states.to(self.dtype_).contiguous(),
                                                     weight=self.cap_norm, rms=True, eps=c.eps))
         x = torch.cat([x, cap], dim=1).contiguous()
+        S_full = x.shape[1]
+        sp = self.sp if past_key_values is None else None
+        sp_lens = None
+        if sp is not None:
+            # rows of the joint [image, text] sequence are split over the SP group; text padding and
+            # the zero rows that round S up to a multiple of P are masked as keys
+            x, _ = sp.shard_rows(x, dim=1)
+            rows = sp.local_rows(S_full)
+            pad = x.shape[1] - cos[rows].shape[0]
+            cos = torch.cat([cos[rows], cos.new_ones(pad, cos.shape[1])]) if pad else cos[rows].contiguous()
+            sin = torch.cat([sin[rows], sin.new_zeros(pad, sin.shape[1])]) if pad else sin[rows].contiguous()
+            if kv_lens is not None:
+                sp_lens = kv_lens
+            elif S_full % sp.P:
+                sp_lens = S_full
         S = x.shape[1]
         temb = F.silu(self.t_embedder(timestep, self.dtype_))
         for li, blk in enumerate(self.layers):
@@ -114,7 +131,10 @@ class ZImageTransformer2DModel(nn.Module):
                 rep = H // pk.shape[2]
                 k = torch.cat([pk.repeat_interleave(rep, 2), k], dim=1).contiguous()
                 v = torch.cat([pv.repeat_interleave(rep, 2), v], dim=1).contiguous()
-            o = attention(q5[:, :, 0], k, v, kv_lens=kv_lens).reshape(B, S, H * Dh)
+            if sp is not None:
+                o = sp(q5, valid_len=sp_lens).reshape(B, S, H * Dh)
+            else:
+                o = attention(q5[:, :, 0], k, v, kv_lens=kv_lens).reshape(B, S, H * Dh)
             a = blk.out(o)
             a = fused.norm_modulate(a, weight=blk.attn_norm2, rms=True, eps=c.eps)
             x = x + torch.tanh(m[:, None, D:2 * D].float()).to(x.dtype) * a
@@ -123,5 +143,7 @@ class ZImageTransformer2DModel(nn.Module):
             f = fused.norm_modulate(f, weight=blk.ffn_norm2, rms=True, eps=c.eps)
             x = (x + torch.tanh(m[:, None, 3 * D:].float()).to(x.dtype) * f).contiguous()
         sc = self.final_adaln(temb)
+        if sp is not None:
+            x = sp.gather_rows(x, S_full, dim=1)
         out = fused.norm_modulate(x[:, :S_img].contiguous(), scale=sc, eps=1e-6)
         return self.proj_out(out)

@@ -60,8 +60,12 @@ class SequenceParallelAttention:
 
     # attention -------------------------------------------------------------------------
     def _chunk_lens(self, valid_len, chunk, S_c, B, device):
+        """Valid keys of ring chunk ``chunk``: ``valid_len`` is an int or an int tensor [B] of global
+        lengths (everything past it, at the END of the global sequence, is padding)."""
         if valid_len is None:
             return None
+        if torch.is_tensor(valid_len):
+            return (valid_len.to(device) - chunk * S_c).clamp(0, S_c).to(torch.int32)
         n = max(0, min(S_c, int(valid_len) - chunk * S_c))
         return torch.full((B,), n, dtype=torch.int32, device=device)
 
@@ -79,7 +83,7 @@ class SequenceParallelAttention:
         self.arena = PeerArena(self.group.ring, n * torch.empty(0, dtype=dtype).element_size() + 8192, device)
         self.kv = self.arena.alloc(shape, dtype)
 
-    def __call__(self, q5: torch.Tensor, valid_len: int | None = None, scale: float | None = None) -> torch.Tensor:
+    def __call__(self, q5: torch.Tensor, valid_len=None, scale: float | None = None) -> torch.Tensor:
         B, S_loc = q5.shape[0], q5.shape[1]
         if self.U > 1:
             q5 = all_to_all_5d(q5.contiguous(), 3, 1, self.group.ulysses.device_group)    # [B, S_c, 3, H/U, Dh]
@@ -89,7 +93,7 @@ class SequenceParallelAttention:
         if self.R == 1:
             o = attention(q, k, v, kv_lens=self._chunk_lens(valid_len, 0, S_c, B, dev), scale=scale)
         else:
-            if valid_len is not None and int(valid_len) <= (self.R - 1) * S_c:
+            if valid_len is not None and int(torch.as_tensor(valid_len).min()) <= (self.R - 1) * S_c:
                 raise ValueError("padding may not cover a whole ring chunk")
             out = lse = None
             if self.mode == "peer" and q5.is_cuda:
