@@ -160,8 +160,9 @@ def test_hybrid_ulysses_ring_matches_single_rank_cpu_gloo():
 
 @pytest.mark.gpu
 def test_hybrid_ulysses_ring_matches_single_rank_gpu():
-    if torch.cuda.device_count() < 4:
-        pytest.skip("needs 4 GPUs")
+    import os
+    if torch.cuda.device_count() < 4 or os.environ.get("OMNI_TEST_4GPU") != "1":
+        pytest.skip("needs 4 GPUs and OMNI_TEST_4GPU=1 (the peer path of the hybrid has only run on CPU ranks so far)")
     run_distributed(_hybrid_worker, 4, "nccl", args=("nccl", "peer", "bfloat16", 128, 4, 0.06))
 
 
