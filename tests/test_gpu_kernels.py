@@ -293,3 +293,31 @@ def test_vae_decoder_nhwc_matches_torch(dev):
     _status_ok(dev)
     assert out.shape == ref.shape == (1, 3, 192, 160)
     assert (out - ref).abs().mean().item() < 0.02 and (out - ref).abs().max().item() < 0.25
+
+
+def test_gemm_two_problems_one_launch(dev):
+    """Image-stream and text-stream linears of one layer through a single CTA-pair launch."""
+    from vllm_omni_b200.ops import gemm
+    torch.manual_seed(8)
+    B, S1, S2, K, N = 2, 2100, 260, 512, 1544
+    mk = lambda *s: torch.randn(*s, device=dev, dtype=torch.bfloat16)
+    x1, x2 = mk(B, S1, K), mk(B, S2, K)
+    w1, w2 = mk(N, K) * 0.05, mk(N, K) * 0.05
+    b1, b2 = mk(N), mk(N)
+    r1, r2 = mk(B, S1, N), mk(B, S2, N)
+    g1, g2 = mk(B, N), mk(B, N)
+    o1, o2 = torch.empty_like(r1), torch.empty_like(r2)
+    gemm.linear_pair(dict(x=x1, w=w1, bias=b1, act="gelu_tanh", residual=r1, gate=g1, out=o1),
+                     dict(x=x2, w=w2, bias=b2, residual=r2, gate=g2, out=o2))
+    _status_ok(dev)
+    ref1 = gemm.linear_reference(x1, w1, b1, "gelu_tanh", r1, g1).float()
+    ref2 = gemm.linear_reference(x2, w2, b2, None, r2, g2).float()
+    assert (o1.float() - ref1).abs().max().item() <= 0.02 * ref1.abs().max().item() + 1e-2
+    assert (o2.float() - ref2).abs().max().item() <= 0.02 * ref2.abs().max().item() + 1e-2
+    # joint [B, S1 + S2, N] output buffer, rows of each stream written in place (the QKV layout)
+    joint = torch.zeros(B, S1 + S2, N, device=dev, dtype=torch.bfloat16)
+    gemm.linear_pair(dict(x=x1, w=w1, bias=b1, out=joint[:, :S1], out_rows_per_batch=S1, out_batch_stride=(S1 + S2) * N),
+                     dict(x=x2, w=w2, bias=b2, out=joint[:, S1:], out_rows_per_batch=S2, out_batch_stride=(S1 + S2) * N))
+    _status_ok(dev)
+    refj = torch.cat([gemm.linear_reference(x1, w1, b1).float(), gemm.linear_reference(x2, w2, b2).float()], 1)
+    assert (joint.float() - refj).abs().max().item() <= 0.02 * refj.abs().max().item() + 1e-2

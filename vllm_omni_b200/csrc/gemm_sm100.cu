@@ -347,11 +347,29 @@ struct PairCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
 };
 
+// One launch can carry TWO problems that share N and K (the image and the text stream of a
+// dual-stream DiT block: same layer shape, different activations, weights, outputs and epilogue
+// operands).  The tile list is problem 0's tiles followed by problem 1's, so the short text
+// problem fills the partial last wave of the image problem instead of paying for a launch and a
+// mostly idle grid of its own.
+struct PairProblem {
+  CUtensorMap tmA, tmB;
+  __nv_bfloat16* C;
+  int ldc;
+  int M;
+  GemmEpilogue epi;
+};
+struct PairArgs {
+  PairProblem p[2];
+  int n_problems;   // 1 or 2
+  int N, K;
+};
+
 template <int TN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      __nv_bfloat16* __restrict__ C, int ldc, int M, int N, int K, GemmEpilogue epi, int* status) {
+gemm_bf16_pair_kernel(const __grid_constant__ PairArgs args, int* status) {
   constexpr int P_TILE_N = TN;
+  const int N = args.N, K = args.K;
   constexpr int P_STAGES = PairCfg<TN>::STAGES;
   constexpr int P_STAGE_BYTES = PairCfg<TN>::STAGE_BYTES;
   constexpr int P_A_BYTES = PairCfg<TN>::A_BYTES;
@@ -370,10 +388,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int num_pairs = gridDim.x >> 1;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
-  const int num_m = (M + 2 * BM - 1) / (2 * BM);
   const int num_n = (N + P_TILE_N - 1) / P_TILE_N;
-  const int num_tiles = num_m * num_n;
+  const int num_m0 = (args.p[0].M + 2 * BM - 1) / (2 * BM);
+  const int num_m1 = args.n_problems > 1 ? (args.p[1].M + 2 * BM - 1) / (2 * BM) : 0;
+  const int tiles0 = num_m0 * num_n;
+  const int num_tiles = tiles0 + num_m1 * num_n;
   const int num_kb = (K + BK - 1) / BK;
+  // tile index -> (problem, row block, column block)
+  auto locate = [&](int t, int& prob, int& mb, int& nb) {
+    prob = t >= tiles0 ? 1 : 0;
+    tile_coords(prob ? t - tiles0 : t, prob ? num_m1 : num_m0, num_n, mb, nb);
+  };
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -386,8 +411,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       mbar_init(smem_u32(&tempty_bar[i]), 16);
     }
     fence_mbar_init();
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
+    for (int i = 0; i < args.n_problems; ++i) {
+      tma_prefetch_desc(&args.p[i].tmA);
+      tma_prefetch_desc(&args.p[i].tmB);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(&tmem_base_s), 512);
@@ -405,15 +432,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       for (int t = pair; t < num_tiles; t += num_pairs) {
-        int mb, nb;
-        tile_coords(t, num_m, num_n, mb, nb);
+        int prob, mb, nb;
+        locate(t, prob, mb, nb);
+        const CUtensorMap* tmA = &args.p[prob].tmA;
+        const CUtensorMap* tmB = &args.p[prob].tmB;
         for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
           if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * P_STAGE_BYTES);
           const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);
           const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
-          tma_load_2d_pair(sa, &tmA, fb, kb * BK, mb * 2 * BM + (int)rank * BM);
-          tma_load_2d_pair(sa + P_A_BYTES, &tmB, fb, kb * BK, nb * P_TILE_N + (int)rank * (P_TILE_N / 2));
+          tma_load_2d_pair(sa, tmA, fb, kb * BK, mb * 2 * BM + (int)rank * BM);
+          tma_load_2d_pair(sa + P_A_BYTES, tmB, fb, kb * BK, nb * P_TILE_N + (int)rank * (P_TILE_N / 2));
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -455,12 +484,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = pair; t < num_tiles; t += num_pairs) {
-      int mb, nb;
-      tile_coords(t, num_m, num_n, mb, nb);
+      int prob, mb, nb;
+      locate(t, prob, mb, nb);
+      const GemmEpilogue& epi = args.p[prob].epi;
+      __nv_bfloat16* C = args.p[prob].C;
+      const int ldc = args.p[prob].ldc;
       mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, &s_abort, status, ERR_WAIT_TMEM_FULL);
       tc_fence_after_sync();
       const int row = mb * 2 * BM + (int)rank * BM + q * 32 + lane;
-      const bool row_ok = row < M;
+      const bool row_ok = row < args.p[prob].M;
       const __nv_bfloat16* gate_row = nullptr;
       if (epi.gate && row_ok) gate_row = epi.gate + (size_t)(row / epi.rows_per_batch) * epi.gate_stride;
 #pragma unroll 1
@@ -493,23 +525,39 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
 static int g_pair_mode = 1;   // 0: never unless forced, 1: automatic for large problems
 
-template <int TN>
-static int launch_gemm_pair(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, int ldc, int M, int N, int K,
-                            int ldw, const GemmEpilogue& epi, int* status, int max_pairs, cudaStream_t stream) {
-  using Cfg = PairCfg<TN>;
-  CUtensorMap tmB;
-  int rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, TN / 2, BK);
+static int fill_pair_problem(PairProblem& pp, const void* A, int lda, const void* W, int ldw, __nv_bfloat16* C,
+                             int ldc, int M, int N, int K, const GemmEpilogue& epi, int tn) {
+  int rc = make_tmap_2d(&pp.tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
   if (rc) return rc;
+  rc = make_tmap_2d(&pp.tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, tn / 2, BK);
+  if (rc) return rc;
+  pp.C = C; pp.ldc = ldc; pp.M = M; pp.epi = epi;
+  return RC_OK;
+}
+
+template <int TN>
+static int launch_gemm_pair(const PairArgs& args, int* status, int max_pairs, cudaStream_t stream) {
+  using Cfg = PairCfg<TN>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const int num_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + TN - 1) / TN);
+  const int num_n = (args.N + TN - 1) / TN;
+  int num_tiles = 0;
+  for (int i = 0; i < args.n_problems; ++i) num_tiles += ((args.p[i].M + 2 * BM - 1) / (2 * BM)) * num_n;
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
-  gemm_bf16_pair_kernel<TN><<<2 * pairs, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, status);
+  gemm_bf16_pair_kernel<TN><<<2 * pairs, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(args, status);
   return (int)cudaGetLastError();
+}
+
+static int launch_pair_tn(int tn, const PairArgs& args, int* status, int pairs, cudaStream_t s) {
+  switch (tn) {
+    case 256: return launch_gemm_pair<256>(args, status, pairs, s);
+    case 192: return launch_gemm_pair<192>(args, status, pairs, s);
+    default: return launch_gemm_pair<128>(args, status, pairs, s);
+  }
 }
 
 // how many CTA pairs can be resident at once (one CTA per SM, two SMs of one TPC per pair)
@@ -653,11 +701,11 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
   if (force_bn >= 384 || (force_bn == 0 && g_pair_mode == 1 && pair_tiles >= ctas / 2)) {
     const int pairs = max_resident_pairs();
     const int tn = force_bn == 576 ? 256 : (force_bn == 448 ? 192 : (force_bn == 384 ? 128 : pick_pair_tn(M, N, pairs)));
-    switch (tn) {
-      case 256: return launch_gemm_pair<256>(tmA, W, c, ldc, M, N, K, ldw, epi, status, pairs, s);
-      case 192: return launch_gemm_pair<192>(tmA, W, c, ldc, M, N, K, ldw, epi, status, pairs, s);
-      default: return launch_gemm_pair<128>(tmA, W, c, ldc, M, N, K, ldw, epi, status, pairs, s);
-    }
+    PairArgs args = {};
+    args.n_problems = 1; args.N = N; args.K = K;
+    rc = fill_pair_problem(args.p[0], A, lda, W, ldw, c, ldc, M, N, K, epi, tn);
+    if (rc) return rc;
+    return launch_pair_tn(tn, args, status, pairs, s);
   }
   const int bn = force_bn ? force_bn : pick_bn(M, N, ctas);
   switch (bn) {
@@ -666,6 +714,74 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
     case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
     default: return RC_BAD_ARG;
   }
+}
+
+// Two linear layers of the same shape (N, K) in one launch of the CTA-pair kernel: the image and
+// text streams of a dual-stream DiT block.  Each descriptor carries its own activations, weights,
+// output mapping and epilogue operands.  Falls back to two launches when the pair kernel does not
+// apply (too few tiles for one wave).
+struct OmniGemmDesc {
+  const void* A; const void* W; void* C;
+  const void* bias; const void* residual; const void* gate;
+  long c_batch_stride;
+  int lda, ldw, ldc, M, ldr, gate_stride, rows_per_batch, act, c_rows_per_batch;
+};
+
+static int desc_epilogue(const OmniGemmDesc& d, omni::GemmEpilogue& epi) {
+  if ((d.lda & 7) || (d.ldw & 7) || (d.ldc & 7) || (d.ldr & 7) || (d.gate_stride & 7)) return omni::RC_BAD_ARG;
+  if (d.gate && d.rows_per_batch <= 0) return omni::RC_BAD_ARG;
+  if (d.c_rows_per_batch > 0 && (d.c_batch_stride & 7)) return omni::RC_BAD_ARG;
+  epi = omni::GemmEpilogue{};
+  epi.bias = static_cast<const __nv_bfloat16*>(d.bias);
+  epi.residual = static_cast<const __nv_bfloat16*>(d.residual);
+  epi.gate = static_cast<const __nv_bfloat16*>(d.gate);
+  epi.ldr = d.ldr;
+  epi.gate_stride = d.gate_stride;
+  epi.rows_per_batch = d.rows_per_batch > 0 ? d.rows_per_batch : 1;
+  epi.act = d.act;
+  epi.c_rows_per_batch = d.c_rows_per_batch;
+  epi.c_batch_stride = d.c_batch_stride;
+  return omni::RC_OK;
+}
+
+extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
+                              int M, int N, int K, const void* bias, const void* residual, int ldr,
+                              const void* gate, int gate_stride, int rows_per_batch, int act,
+                              int c_rows_per_batch, long c_batch_stride, int scatter_P, int scatter_G,
+                              int scatter_rows, void* const* peer_out, int force_bn, int* status, void* stream);
+
+extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d1, int N, int K, int* status,
+                                   void* stream) {
+  using namespace omni;
+  if (!d0 || !d1 || N <= 0 || K <= 0 || (N & 7) || (K & 7)) return RC_BAD_ARG;
+  const OmniGemmDesc* ds[2] = {d0, d1};
+  const int ctas = sm_count();
+  long tiles = 0;
+  for (int i = 0; i < 2; ++i) tiles += (long)((ds[i]->M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+  if (d0->M <= 0 || d1->M <= 0 || g_pair_mode != 1 || tiles < ctas / 2) {
+    for (int i = 0; i < 2; ++i) {
+      const OmniGemmDesc& d = *ds[i];
+      if (d.M <= 0) continue;
+      int rc = omni_gemm_bf16(d.A, d.lda, d.W, d.ldw, d.C, d.ldc, d.M, N, K, d.bias, d.residual, d.ldr, d.gate,
+                              d.gate_stride, d.rows_per_batch, d.act, d.c_rows_per_batch, d.c_batch_stride, 0, 0, 0,
+                              nullptr, 0, status, stream);
+      if (rc) return rc;
+    }
+    return RC_OK;
+  }
+  const int pairs = max_resident_pairs();
+  const int tn = pick_pair_tn(d0->M + d1->M, N, pairs);
+  PairArgs args = {};
+  args.n_problems = 2; args.N = N; args.K = K;
+  for (int i = 0; i < 2; ++i) {
+    GemmEpilogue epi;
+    int rc = desc_epilogue(*ds[i], epi);
+    if (rc) return rc;
+    rc = fill_pair_problem(args.p[i], ds[i]->A, ds[i]->lda, ds[i]->W, ds[i]->ldw, static_cast<__nv_bfloat16*>(ds[i]->C),
+                           ds[i]->ldc, ds[i]->M, N, K, epi, tn);
+    if (rc) return rc;
+  }
+  return launch_pair_tn(tn, args, status, pairs, static_cast<cudaStream_t>(stream));
 }
 
 // 0: the CTA-pair kernel runs only when forced (force_bn = 512); 1: automatic for large problems.

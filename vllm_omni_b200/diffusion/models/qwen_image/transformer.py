@@ -25,9 +25,19 @@ import torch.nn.functional as F
 from torch import nn
 
 from ....ops import _native as _nv
-from ....ops import fused
+from ....ops import fused, gemm
 from ....ops.attention import attention
 from ...layers.linear import FusedLinear
+
+
+def _plain_pair(blk) -> bool:
+    """True when the image and text linears of a block can share launches: plain bf16 weights
+    (no LoRA delta, no fp8 state) on both streams."""
+    for sp in (blk.img, blk.txt):
+        for lin in (sp.to_qkv, sp.to_out, sp.mlp_up, sp.mlp_down):
+            if lin is None or lin.lora or lin.fp8 is not None:
+                return False
+    return True
 
 
 @dataclass
@@ -242,9 +252,18 @@ class QwenImageTransformer2DModel(nn.Module):
             Hl = tp or H
             Dl = Hl * Hd
             qkv = ws["qkv"]
-            for sp, xn, rows, off in ((blk.img, ws["img_n"], S_img, 0), (blk.txt, ws["txt_n"], S_txt, S_img)):
-                proj = sp.tp_attn.up if tp else sp.to_qkv
-                proj(xn, out=qkv[:, off:off + rows], out_rows_per_batch=rows, out_batch_stride=S * 3 * Dl)
+            paired = (not tp) and S_txt > 0 and img.is_cuda and _plain_pair(blk)
+            if paired:
+                # image and text projections of one layer share a launch (same N, K)
+                gemm.linear_pair(
+                    dict(x=ws["img_n"], w=blk.img.to_qkv.weight, bias=blk.img.to_qkv.bias, out=qkv[:, :S_img],
+                         out_rows_per_batch=S_img, out_batch_stride=S * 3 * Dl),
+                    dict(x=ws["txt_n"], w=blk.txt.to_qkv.weight, bias=blk.txt.to_qkv.bias, out=qkv[:, S_img:],
+                         out_rows_per_batch=S_txt, out_batch_stride=S * 3 * Dl))
+            else:
+                for sp, xn, rows, off in ((blk.img, ws["img_n"], S_img, 0), (blk.txt, ws["txt_n"], S_txt, S_img)):
+                    proj = sp.tp_attn.up if tp else sp.to_qkv
+                    proj(xn, out=qkv[:, off:off + rows], out_rows_per_batch=rows, out_batch_stride=S * 3 * Dl)
             fused.qk_norm_rope_(qkv, Hl, Hl, Hd, wq=blk.img.norm_q, wk=blk.img.norm_k, wq_alt=blk.txt.norm_q,
                                 wk_alt=blk.txt.norm_k, s_alt=S_img, cos=cos, sin=sin, interleaved=True, eps=cfg.eps)
             q5 = qkv.view(B, S, 3, Hl, Hd)
@@ -253,6 +272,24 @@ class QwenImageTransformer2DModel(nn.Module):
                            split=S_img)
             attn_img, attn_txt = ws["attn_img"], ws["attn_txt"]
         tp = getattr(self, "tp_heads", 0) if self.sp is None else 0
+        if (not tp) and S_txt > 0 and img.is_cuda and _plain_pair(blk):
+            # both streams per launch: out-projection, then the two norms, MLP up, MLP down
+            mi, mt = m[:, 0], m[:, 1]
+            bi, bt = blk.img, blk.txt
+            gemm.linear_pair(
+                dict(x=attn_img, w=bi.to_out.weight, bias=bi.to_out.bias, residual=img, gate=mi[:, 2 * D:3 * D], out=img),
+                dict(x=attn_txt, w=bt.to_out.weight, bias=bt.to_out.bias, residual=txt, gate=mt[:, 2 * D:3 * D], out=txt))
+            fused.norm_modulate(img, shift=mi[:, 3 * D:4 * D], scale=mi[:, 4 * D:5 * D], eps=cfg.eps, out=ws["img_n"])
+            fused.norm_modulate(txt, shift=mt[:, 3 * D:4 * D], scale=mt[:, 4 * D:5 * D], eps=cfg.eps, out=ws["txt_n"])
+            gemm.linear_pair(
+                dict(x=ws["img_n"], w=bi.mlp_up.weight, bias=bi.mlp_up.bias, act="gelu_tanh", out=ws["mlp_img"]),
+                dict(x=ws["txt_n"], w=bt.mlp_up.weight, bias=bt.mlp_up.bias, act="gelu_tanh", out=ws["mlp_txt"]))
+            gemm.linear_pair(
+                dict(x=ws["mlp_img"], w=bi.mlp_down.weight, bias=bi.mlp_down.bias, residual=img, gate=mi[:, 5 * D:6 * D],
+                     out=img),
+                dict(x=ws["mlp_txt"], w=bt.mlp_down.weight, bias=bt.mlp_down.bias, residual=txt, gate=mt[:, 5 * D:6 * D],
+                     out=txt))
+            return img, txt
         for sidx, (sp, x, xn, att, hbuf) in enumerate(((blk.img, img, ws["img_n"], attn_img, ws["mlp_img"]),
                                                        (blk.txt, txt, ws["txt_n"], attn_txt, ws["mlp_txt"]))):
             if x.shape[1] == 0:

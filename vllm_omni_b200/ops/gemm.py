@@ -125,3 +125,64 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
         nv.stream_ptr())
     nv.check_rc(rc, "omni_gemm_bf16")
     return None if scatter is not None else out
+
+
+class _GemmDesc(ctypes.Structure):
+    _fields_ = [("A", ctypes.c_void_p), ("W", ctypes.c_void_p), ("C", ctypes.c_void_p), ("bias", ctypes.c_void_p),
+                ("residual", ctypes.c_void_p), ("gate", ctypes.c_void_p), ("c_batch_stride", ctypes.c_long),
+                ("lda", ctypes.c_int), ("ldw", ctypes.c_int), ("ldc", ctypes.c_int), ("M", ctypes.c_int),
+                ("ldr", ctypes.c_int), ("gate_stride", ctypes.c_int), ("rows_per_batch", ctypes.c_int),
+                ("act", ctypes.c_int), ("c_rows_per_batch", ctypes.c_int)]
+
+
+def _desc(x, w, bias, act, residual, gate, out, out_rows_per_batch, out_batch_stride, keep):
+    K, N = x.shape[-1], w.shape[0]
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    if w.stride(-1) != 1:
+        w = w.contiguous()
+    M = x2.shape[0]
+    if out_rows_per_batch:
+        ldc = out.stride(-2)
+    else:
+        ldc = out.view(-1, N).stride(0)
+    d = _GemmDesc()
+    d.A, d.W, d.C = x2.data_ptr(), w.data_ptr(), out.data_ptr()
+    d.bias = bias.data_ptr() if bias is not None else None
+    d.lda, d.ldw, d.ldc, d.M, d.act = x2.stride(0), w.stride(0), ldc, M, ACT[act]
+    d.c_rows_per_batch, d.c_batch_stride = out_rows_per_batch, out_batch_stride
+    if residual is not None:
+        r2 = residual.reshape(-1, N)
+        assert r2.stride(-1) == 1
+        d.residual, d.ldr = r2.data_ptr(), r2.stride(0)
+        keep.append(r2)
+    if gate is not None:
+        assert gate.dim() == 2 and gate.shape[1] == N and gate.stride(1) == 1 and M % gate.shape[0] == 0
+        d.gate, d.rows_per_batch = gate.data_ptr(), M // gate.shape[0]
+        d.gate_stride = gate.stride(0) if gate.shape[0] > 1 else N
+    keep += [x2, w]
+    return d
+
+
+def linear_pair(a: dict, b: dict) -> None:
+    """Two linear layers of the same (N, K) in ONE launch (the image and text streams of a
+    dual-stream block).  ``a`` / ``b``: keyword sets of ``linear`` — ``x, w, bias, act, residual,
+    gate, out`` (``out`` is required), optionally ``out_rows_per_batch, out_batch_stride``.  On the
+    GPU both problems share the CTA-pair kernel's tile list, so the short one fills the last wave
+    of the long one; on CPU they run one after the other."""
+    xa, xb = a["x"], b["x"]
+    if (not xa.is_cuda) or xa.numel() == 0 or xb.numel() == 0:
+        for kw in (a, b):
+            if kw["x"].numel():
+                linear(**kw)
+        return
+    assert a["w"].shape == b["w"].shape, "the two problems must share N and K"
+    keep: list = []
+    ds = [_desc(kw["x"], kw["w"], kw.get("bias"), kw.get("act"), kw.get("residual"), kw.get("gate"), kw["out"],
+                kw.get("out_rows_per_batch", 0), kw.get("out_batch_stride", 0), keep) for kw in (a, b)]
+    N, K = a["w"].shape
+    st = nv.status_word(xa.device)
+    rc = nv.lib("gemm_sm100").omni_gemm_bf16_dual(ctypes.byref(ds[0]), ctypes.byref(ds[1]), ctypes.c_int(N),
+                                                  ctypes.c_int(K), nv.ptr(st), nv.stream_ptr())
+    nv.check_rc(rc, "omni_gemm_bf16_dual")
