@@ -1,25 +1,32 @@
-// K4: flash-attention forward for sm_100a on tcgen05 tensor cores with TMEM accumulators.
+// K4 / K11: flash-attention forward for sm_100a on tcgen05 tensor cores with TMEM accumulators.
 //
 // softmax(Q K^T * scale) V over bf16 inputs (non-causal, or causal with a query offset for
-// chunked prefill), head_dim 128, optional per-batch
-// key lengths (padding mask), GQA, optional log-sum-exp output (used by the ring /
-// peer-KV merge).  Replaces the PyTorch SDPA call the reference makes on Blackwell
+// chunked prefill), head_dim 128, optional per-batch key lengths (padding mask), GQA, optional
+// log-sum-exp output (used by the ring / peer-KV merge), K/V either contiguous or in a paged cache
+// addressed through a block table, optional split of the KV range over several CTAs with a
+// merge kernel.  Replaces the PyTorch SDPA call the reference makes on Blackwell
 // (vllm_omni/diffusion/attention/backends/sdpa.py:82; its FlashAttention backend is gated
-// off for compute capability >= 10, vllm_omni/platforms/cuda/platform.py:44-51).
+// off for compute capability >= 10, vllm_omni/platforms/cuda/platform.py:44-51) and the paged
+// attention it takes from vLLM for the AR stages (vllm_omni/worker/gpu_model_runner.py:37).
 //
-// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles.
-//   warp 0       TMA producer: Q once, then K and V tiles through two 2-deep rings
-//   warp 1       MMA issuer (one elected thread):
-//                  S_t = Q_t K_j^T      (SS form, both operands K-major in shared memory)
-//                  O_t += P_t V_j       (TS form: P_t read from TMEM, V_j MN-major in smem)
-//   warps 4-7    softmax of tile 0,  warps 8-11 softmax of tile 1: one row per thread;
-//                tcgen05.ld of S, running max, exp2, bf16 P written back with tcgen05.st
-//                over the S columns it came from, then the final O / l epilogue
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases the
-// first 64 columns of S_t.  O is rescaled lazily: only when a row maximum grows by more
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles (one tile when the
+// rows end inside the first; decode maps the heads of a GQA group onto the rows of a tile).
+//   warp 0        TMA producer: Q once, then K and V tiles through two 2-deep rings; with a paged
+//                 cache one box per page, page ids read from the block table
+//   warp 1        MMA issuer (one elected thread):
+//                   S_t = Q_t K_j^T      (SS form, both operands K-major in shared memory)
+//                   O_t += P_t V_j       (TS form: P_t read from TMEM, V_j MN-major in smem)
+//   warps 4-11    softmax of tile 0, warps 12-19 softmax of tile 1.  Two warps share each group
+//                 of 32 rows (TMEM lanes) and take 64 S columns each: tcgen05.ld of S, row maximum
+//                 exchanged through shared memory, exp2 in packed fp32 (a quarter of the
+//                 exponentials on an FMA-pipe polynomial), bf16 P written back with tcgen05.st
+//                 over S columns already read, then the final O / l epilogue (local stores,
+//                 peer stores for the fused Ulysses exchange, or fp32 partials for split-KV)
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t sits in columns
+// [0,32) and [64,96) of S_t.  O is rescaled lazily: only when a row maximum grows by more
 // than 2^8, so the steady state never touches O outside the MMAs.
 // The MMA stream is software-pipelined (PV_t(j) is followed at once by S_t(j+1)) so that
-// the tensor pipe works on one tile while the other tile's softmax runs.
+// the tensor pipe works on one tile while the other tile's softmax runs.  Every wait is bounded.
 #include "host_util.h"
 #include "ptx_sm100.cuh"
 

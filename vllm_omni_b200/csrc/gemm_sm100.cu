@@ -2,19 +2,32 @@
 //
 //   C[M,N] (bf16) = epilogue( A[M,K] (bf16, row-major) * W[N,K]^T (bf16, row-major) )
 //
-// i.e. the nn.Linear contraction with both operands K-major.  One CTA per SM walks a
-// strided list of 128 x BN output tiles.  Roles:
+// i.e. the nn.Linear contraction with both operands K-major.  Two kernels share one epilogue:
+//
+// gemm_bf16_kernel<BN>       one CTA per SM walks a strided list of 128 x BN output tiles
+//                            (BN = 128 / 192 / 256).  Also runs the grouped (MoE expert) GEMM, where
+//                            every 128-row tile names its expert, and the implicit-GEMM convolution,
+//                            where the A tile of a (tap, channel block) is a shifted 4-D TMA box.
+// gemm_bf16_pair_kernel<TN>  two CTAs of a cluster (cta_group::2) compute one 256 x TN tile; each
+//                            stages its own 128 rows of A and half of the W tile, the even CTA issues
+//                            the M=256 MMAs.  Used whenever the problem fills a wave of such tiles;
+//                            one launch can carry two problems of the same (N, K).
+//
+// Roles inside a CTA (both kernels):
 //   warp 0    TMA producer: cp.async.bulk.tensor loads of the A / W k-blocks (128-byte
-//             swizzle) into a STAGES-deep shared-memory ring, completion on mbarriers
-//   warp 1    MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) with
+//             swizzle) into a multi-stage shared-memory ring, completion on mbarriers
+//   warp 1    MMA issuer: one elected thread issues tcgen05.mma (K=16 per instruction) with
 //             the fp32 accumulator in tensor memory; tcgen05.commit hands ring slots back
 //             to the producer and finished accumulators to the epilogue
 //   warps 2-9 epilogue: two warps per TMEM lane quadrant, each draining half of the tile's
 //             columns: tcgen05.ld of the accumulator (one row per thread, 32 columns per
-//             instruction), fused bias / GELU-tanh / SiLU / gate*x + residual, bf16 stores
+//             instruction), fused bias / GELU-tanh / SiLU / gate*x + residual, bf16 stores to
+//             local memory or, for the fused collectives, straight into peers' buffers
+//             (column groups: Ulysses head scatter; row blocks: tensor-parallel reduce-scatter)
 // Two accumulators live in TMEM so the epilogue of tile i overlaps the main loop of
 // tile i+1.  All mbarrier waits are bounded (see ptx_sm100.cuh); a timeout is reported
-// through *status and the kernel still terminates and frees its TMEM.
+// through *status and the kernel still terminates and frees its TMEM.  No TMA load in this
+// file is a multicast.
 //
 // Replaces the cuBLAS calls behind the reference's vLLM linear layers
 // (vllm_omni/diffusion/models/qwen_image/qwen_image_transformer.py:427-560).
