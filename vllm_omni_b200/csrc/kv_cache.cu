@@ -7,7 +7,8 @@
 //   omni_kv_gather     pages -> contiguous [T, Hkv, D] (context for chunked prefill; KV
 //                      hand-off to another stage: the destination may be peer memory)
 //   omni_paged_decode  one query token per sequence against its paged KV, GQA, split over
-//                      the context with a second pass that merges the partial results
+//                      the context with a second pass that merges the partial results (CUDA-core
+//                      fallback; the tensor-core paged attention lives in attention_sm100.cu)
 //
 // The reference reaches vLLM's FlashAttention / FlashInfer backends for these
 // (vllm_omni/worker/gpu_model_runner.py:37) and extracts KV for hand-off with eager index +
@@ -53,12 +54,13 @@ kv_gather_kernel(const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __re
 }
 
 // --------------------------------------------------------------------- paged decode
-// grid = (num_seqs, Hkv, num_splits), 128 threads (4 warps).  The CTA serves the G = H/Hkv
-// query heads that share one KV head.  Each warp walks tokens of its split with stride 4;
-// within a warp, lane l owns dims [4l, 4l+4) of D = 128 (8-byte loads).  Scores of the G heads
-// are reduced with butterfly shuffles, then an online softmax keeps (m, l, acc[4]) per head.
+// CUDA-core fallback for page shapes the tcgen05 path (attention_sm100.cu, omni_attn_fwd_paged)
+// does not take.  grid = (num_seqs, Hkv, num_splits), 128 threads.  The CTA serves the
+// G = H/Hkv query heads that share one KV head.  Half a warp owns one token (16 lanes x 8 dims,
+// one 16-byte load per lane); scores of the G heads are reduced with butterfly shuffles inside the
+// half-warp, then an online softmax keeps (m, l, acc[8]) per head; the 8 half-warp streams are
+// merged through shared memory and the splits by a second kernel.
 constexpr int PD_D = 128;
-constexpr int PD_MAXG = 8;
 constexpr int PD_WARPS = 4;
 
 template <int G>
