@@ -62,8 +62,10 @@ class LLMEngine:
         per_block = 2 * dec.num_hidden_layers * block_size * dec.num_key_value_heads * dec.head_dim * \
             torch.empty(0, dtype=self.dtype).element_size()
         if self.device.type == "cuda":
+            from ..utils.gpu_memory import kv_cache_budget
             free, total = torch.cuda.mem_get_info(self.device)
-            budget = max(0, free - int(total * (1.0 - util)))
+            # per-process accounting: stages that share this GPU may be initialising concurrently
+            budget = kv_cache_budget(total, free, util, self.device.index or 0)
         else:
             budget = 256 << 20
         want = (max_model_len // block_size + 1) * max_num_seqs
