@@ -77,3 +77,45 @@ def test_decoder_paged_matches_reference_gpu(moe):
         assert torch.isfinite(got).all()
     else:
         assert row_err.max().item() < tol, row_err.max().item()
+
+
+def _ep_worker(rank, world, backend, mode, dtype_name, head_dim, tol):
+    """MoE decoder with the experts split over the ranks == all experts on one rank."""
+    from vllm_omni_b200.parallel import parallel_state as ps
+    dtype = getattr(torch, dtype_name)
+    device = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+    ps.init_distributed_environment(world, rank, local_rank=rank, backend=backend)
+    ps.initialize_model_parallel(tensor_parallel_size=world, backend=backend)     # the TP group doubles as EP group
+    m = _model(dtype, device, True, head_dim=head_dim)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 512, (150 if device.type == "cuda" else 40,), generator=g).to(device)
+    ref = reference_forward(m, ids).float()
+    m.enable_expert_parallel(ps.get_tp_group(), mode)
+    assert m.layers[0].w13.shape[0] == 8 // world
+    n = ids.numel()
+    got = _run_paged(m, ids, device, chunks=[n // 2, n - n // 2 - 6], decode_from=n - 6).float()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+        from vllm_omni_b200.ops import _native as nv
+        assert int(nv.status_word(device).item()) == 0
+        row_err = (got - ref).abs().amax(-1)
+        assert row_err.median().item() < tol * max(1.0, ref.abs().max().item()), row_err.median().item()
+        assert torch.isfinite(got).all()
+    else:
+        assert torch.allclose(got, ref, atol=tol, rtol=1e-3), (got - ref).abs().max()
+    m.ep_reduce.close()
+    ps.destroy_distributed_environment()
+
+
+def test_expert_parallel_matches_single_rank_cpu_gloo():
+    from dist_utils import run_distributed
+    run_distributed(_ep_worker, 2, "gloo", args=("gloo", "nccl", "float32", 32, 3e-4))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_expert_parallel_matches_single_rank_gpu(mode):
+    from dist_utils import run_distributed
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_distributed(_ep_worker, 2, "nccl", args=("nccl", mode, "bfloat16", 128, 0.08))

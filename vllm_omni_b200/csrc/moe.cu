@@ -165,9 +165,57 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ 
   }
 }
 
+// Expert-parallel combine: the weighted sum of THIS rank's experts for token t is a partial result;
+// it is stored straight into the slot this rank owns on the rank that owns token t's row block
+// (peer_out[t / rows_per_owner], local row t % rows_per_owner, pitch D), so the cross-rank sum needs
+// no separate all-reduce of a [T, D] tensor: a local reduce kernel finishes it (tp_reduce.cu).
+struct MoePeers {
+  __nv_bfloat16* out[16];
+};
+__global__ void __launch_bounds__(256)
+moe_combine_scatter_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ row_of_pair,
+                           const float* __restrict__ weights, int T, int k, int D, int rows_per_owner, MoePeers peers) {
+  const int chunks = D >> 3;
+  const long total = (long)T * chunks;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / chunks);
+    const int c = (int)(i % chunks) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const int r = row_of_pair[(size_t)t * k + j];
+      if (r < 0) continue;
+      const float w = weights[(size_t)t * k + j];
+      const uint4 u = *reinterpret_cast<const uint4*>(y + (size_t)r * D + c);
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * b.x; acc[3] += w * b.y;
+      acc[4] += w * cc.x; acc[5] += w * cc.y; acc[6] += w * d.x; acc[7] += w * d.y;
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    const int owner = t / rows_per_owner;
+    *reinterpret_cast<uint4*>(peers.out[owner] + (size_t)(t - owner * rows_per_owner) * D + c) = o;
+  }
+}
+
 }  // namespace omni
 
 using namespace omni;
+
+extern "C" int omni_moe_combine_scatter(const void* y, const int* row_of_pair, const float* weights, int T, int k, int D,
+                                        int rows_per_owner, void* const* peer_out, void* stream) {
+  if (T <= 0) return RC_OK;
+  if ((D & 7) || rows_per_owner <= 0 || peer_out == nullptr) return RC_BAD_ARG;
+  const int owners = (T + rows_per_owner - 1) / rows_per_owner;
+  if (owners > 16) return RC_BAD_ARG;
+  MoePeers peers;
+  for (int i = 0; i < 16; ++i) peers.out[i] = i < owners ? static_cast<__nv_bfloat16*>(peer_out[i]) : nullptr;
+  long blocks = ((long)T * (D >> 3) + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  moe_combine_scatter_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)y, row_of_pair, weights, T, k, D, rows_per_owner, peers);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int omni_moe_route(const void* logits, int ld, int T, int E, int k, int renorm, int* ids, float* weights,
                               void* stream) {

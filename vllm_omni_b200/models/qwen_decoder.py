@@ -150,6 +150,29 @@ class QwenDecoderModel(nn.Module):
         self.rope = RotaryTable(cfg.head_dim, cfg.rope_theta, cfg.max_position_embeddings)
         self.ep_group = None          # expert-parallel group: experts sharded, partial outputs summed
         self.ep_range = (0, cfg.num_experts)
+        self.ep_reduce = None         # RowParallelReduce over the EP group (peer-memory sum of the partials)
+
+    @torch.no_grad()
+    def enable_expert_parallel(self, group, mode: str | None = None) -> None:
+        """Keep experts [r E/P, (r+1) E/P) on rank r of ``group``.  Tokens are replicated across the
+        group (attention is not sharded here), so dispatch is local; the partial sums of the local
+        experts are added across ranks either by the combine kernel storing them straight into the
+        row owners' peer memory followed by a local reduce (``mode="peer"``) or by an all-reduce
+        (``mode="nccl"``, the baseline and the CPU path)."""
+        cfg = self.cfg
+        P, r = group.world_size, group.rank_in_group
+        if not cfg.num_experts or P == 1:
+            return
+        if cfg.num_experts % P:
+            raise ValueError(f"num_experts ({cfg.num_experts}) must be divisible by the expert-parallel size ({P})")
+        per = cfg.num_experts // P
+        lo, hi = r * per, (r + 1) * per
+        for layer in self.layers:
+            layer.w13 = nn.Parameter(layer.w13.data[lo:hi].clone(), requires_grad=False)
+            layer.w2 = nn.Parameter(layer.w2.data[lo:hi].clone(), requires_grad=False)
+        from ..parallel.tensor_parallel import RowParallelReduce
+        self.ep_group, self.ep_range = group, (lo, hi)
+        self.ep_reduce = RowParallelReduce(group, mode)
 
     # ------------------------------------------------------------------ forward
     def embed(self, batch: ModelBatch) -> torch.Tensor:
@@ -217,6 +240,16 @@ class QwenDecoderModel(nn.Module):
                 if self.ep_group is None or self.ep_group.world_size == 1:
                     moe_forward(xn, logits, layer.w13, layer.w2, cfg.num_experts_per_tok, cfg.norm_topk_prob,
                                 ws=layer.moe_ws, residual=x, out=x)
+                elif self.ep_reduce is not None and self.ep_reduce.mode == "peer" and x.is_cuda:
+                    # combine stores each token's partial sum into its row owner's peer slot; the
+                    # owners reduce locally, add the residual and push the rows to every rank
+                    cap = max(64, 1 << (T - 1).bit_length())
+                    res = self.ep_reduce.reduce_from(
+                        lambda per, ptrs: moe_forward(xn, logits, layer.w13, layer.w2, cfg.num_experts_per_tok,
+                                                      cfg.norm_topk_prob, e_lo=e_lo, e_hi=e_hi, ws=layer.moe_ws,
+                                                      scatter=(per, ptrs)),
+                        T, cfg.hidden_size, x.dtype, x.device, residual=x, capacity=cap)
+                    x.copy_(res)
                 else:
                     part = moe_forward(xn, logits, layer.w13, layer.w2, cfg.num_experts_per_tok, cfg.norm_topk_prob,
                                        e_lo=e_lo, e_hi=e_hi, ws=layer.moe_ws)

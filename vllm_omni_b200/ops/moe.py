@@ -70,9 +70,14 @@ class MoEWorkspace:
 
 
 def moe_forward(x, router_logits, w13, w2, k, renorm=True, e_lo=0, e_hi=None, ws: MoEWorkspace | None = None,
-                residual=None, out=None):
+                residual=None, out=None, scatter=None):
     """x [T, D] bf16, router_logits [T, E] bf16, w13 [E_local, 2F, D], w2 [E_local, D, F] (the
-    local experts [e_lo, e_hi) of E = router_logits.shape[1])."""
+    local experts [e_lo, e_hi) of E = router_logits.shape[1]).
+
+    ``scatter = (rows_per_owner, ptrs)`` (GPU, expert parallel): instead of returning the partial
+    sum of the local experts, store token t's partial into ``ptrs[t // rows_per_owner]`` (peer
+    memory of the rank that owns that block of rows) at local row ``t % rows_per_owner``; the
+    cross-rank sum is finished by ``parallel.tensor_parallel.RowParallelReduce.reduce_from``."""
     T, D = x.shape
     E = router_logits.shape[1]
     e_hi = E if e_hi is None else e_hi
@@ -118,6 +123,12 @@ def moe_forward(x, router_logits, w13, w2, k, renorm=True, e_lo=0, e_hi=None, ws
     nv.check_rc(g.omni_gemm_bf16_grouped(nv.ptr(ws.h), c_int(Fd), nv.ptr(w2), c_int(El), nv.ptr(ws.y), c_int(D),
                                          c_int(ws.max_rows), c_int(D), c_int(Fd), nv.ptr(te), c_int(0), c_int(0),
                                          nv.ptr(status), st), "omni_gemm_bf16_grouped")
+    if scatter is not None:
+        per, ptrs = scatter
+        arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        nv.check_rc(lib.omni_moe_combine_scatter(nv.ptr(ws.y), nv.ptr(ws.row_of_pair), nv.ptr(ws.weights), c_int(T), c_int(k),
+                                                 c_int(D), c_int(per), arr, st), "omni_moe_combine_scatter")
+        return None
     if out is None:
         out = torch.empty_like(x)
     nv.check_rc(lib.omni_moe_combine(nv.ptr(ws.y), nv.ptr(ws.row_of_pair), nv.ptr(ws.weights), c_int(T), c_int(k),

@@ -75,18 +75,34 @@ class RowParallelReduce:
         if self.P == 1 or self.mode == "nccl" or not x.is_cuda:
             partial = layer(x)
             return self(partial, bias=bias, gate=gate, residual=residual, out=out)
-        import ctypes
-        from ..ops import _native as nv
         from ..ops import gemm
         x2 = x.reshape(-1, x.shape[-1])
-        M = x2.shape[0]
-        self._setup(M, N, x.dtype, x.device)
+        res = self.reduce_from(lambda per, ptrs: gemm.linear(x2, layer.weight, None, row_scatter=(per, ptrs, N)),
+                               x2.shape[0], N, x.dtype, x.device, bias=bias, gate=gate, residual=residual)
+        res = res.view(*x.shape[:-1], N)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res.clone()
+
+    def reduce_from(self, produce, M: int, N: int, dtype, device, bias=None, gate=None, residual=None,
+                    capacity: int | None = None):
+        """Sum over the ranks of an [M, N] partial result that ``produce(rows_per_owner, ptrs)``
+        writes straight into peer memory: row r goes to ``ptrs[r // rows_per_owner]`` at local row
+        ``r % rows_per_owner`` (pitch N).  Returns the [M, N] view of the reduced result (with bias,
+        gate and residual applied) that every rank holds after the second barrier; it is valid
+        until the next call with the same shape.  ``capacity`` >= M sizes the buffers (and fixes the
+        rows-per-owner split) for callers whose M changes from call to call, so that one arena per
+        capacity bucket serves them all."""
+        import ctypes
+        from ..ops import _native as nv
+        self._setup(capacity or M, N, dtype, device)
         P, r, per = self.P, self.rank, self.per
-        esz = x.element_size()
+        esz = torch.empty(0, dtype=dtype).element_size()
         owners = -(-M // per)
         # my partial of owner o's rows lands in slot r of owner o
         ptrs = [self.slots.ptrs[o] + r * per * N * esz for o in range(owners)]
-        gemm.linear(x2, layer.weight, None, row_scatter=(per, ptrs, N))
+        produce(per, ptrs)
         self.arena.barrier()
         lo, hi = min(M, r * per), min(M, (r + 1) * per)
         rpb = 0
@@ -103,11 +119,7 @@ class RowParallelReduce:
             ctypes.c_long(res2.stride(0) if res2 is not None else 0), arr, ctypes.c_long(N), nv.stream_ptr())
         nv.check_rc(rc, "omni_tp_reduce_gather")
         self.arena.barrier()
-        res = self.result.local.view(*x.shape[:-1], N)
-        if out is not None:
-            out.copy_(res)
-            return out
-        return res.clone()
+        return self.result.local[:M]
 
     def __call__(self, partial: torch.Tensor, bias=None, gate=None, residual=None, out=None):
         """All-reduce form: ``partial`` is this rank's full-size partial product."""
