@@ -1,0 +1,143 @@
+"""Qwen3-Omni three-stage pipeline under load, in process (no HTTP): Poisson arrivals under a
+concurrency cap through ``AsyncOmni``; reports end-to-end text tokens/s, p50/p90/p99 time to first
+token, time to first audio packet and the audio real-time factor — the second headline metric
+(e2e tok/s + p50 TTFT at 64 concurrent requests).
+
+    # full-size architecture with random weights, all three stages on GPU 0
+    python benchmarks/qwen3_omni/serving_latency.py --device cuda --num-prompts 128 --max-concurrency 64 \
+        --request-rate 8 --input-len 256 --max-tokens 128
+    # CPU smoke run with the tiny geometry
+    python benchmarks/qwen3_omni/serving_latency.py --tiny --num-prompts 6 --max-concurrency 3
+
+Inputs are synthetic token ids; weights are random-init, so every request runs to ``max_tokens``
+(``ignore_eos``), which fixes the work per request."""
+import argparse
+import asyncio
+import json
+import os
+import random
+import sys
+import tempfile
+import time
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
+
+YAML = """
+async_chunk: ASYNC_CHUNK
+stage_args:
+  - stage_id: 0
+    stage_type: llm
+    runtime: {devices: "0", max_batch_size: MAXB}
+    engine_args: {model_stage: thinker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
+                  engine_output_type: latent, device: DEVICE, max_num_batched_tokens: 8192, gpu_memory_utilization: 0.55,
+                  load_format: dummy, model_overrides: OVERRIDES}
+    final_output: true
+    final_output_type: text
+    default_sampling_params: {temperature: 0.0, max_tokens: MAXTOK, ignore_eos: true, detokenize: false}
+  - stage_id: 1
+    stage_type: llm
+    runtime: {devices: "0", max_batch_size: MAXB}
+    engine_args: {model_stage: talker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
+                  engine_output_type: latent, device: DEVICE, gpu_memory_utilization: 0.75, load_format: dummy,
+                  model_overrides: OVERRIDES}
+    engine_input_source: [0]
+    custom_process_input_func: vllm_omni_b200.models.stage_input_processors.qwen3_omni.thinker2talker
+    default_sampling_params: {temperature: 0.9, top_k: 50, max_tokens: CODEC, seed: 1, ignore_eos: true,
+                              stop_token_ids: [], detokenize: false}
+  - stage_id: 2
+    stage_type: llm
+    runtime: {devices: "0", max_batch_size: MAXB}
+    engine_args: {model_stage: code2wav, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: generation,
+                  engine_output_type: audio, device: DEVICE, load_format: dummy, model_overrides: OVERRIDES}
+    engine_input_source: [1]
+    custom_process_input_func: vllm_omni_b200.models.stage_input_processors.qwen3_omni.talker2code2wav
+    final_output: true
+    final_output_type: audio
+"""
+
+
+def _pct(xs, q):
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(round(q / 100 * (len(xs) - 1))))] if xs else None
+
+
+async def _run(a, path):
+    from vllm_omni_b200.entrypoints.async_omni import AsyncOmni
+    eng = AsyncOmni("qwen3-omni-bench", stage_configs_path=path)
+    rng = random.Random(a.seed)
+    vocab = 400 if a.tiny else 150000
+    prompts = [{"prompt_token_ids": [rng.randrange(10, vocab) for _ in range(a.input_len)]} for _ in range(a.num_prompts)]
+    sem = asyncio.Semaphore(a.max_concurrency)
+    recs = []
+
+    async def one(i, p):
+        async with sem:
+            t0 = time.perf_counter()
+            r = {"ttft": None, "ttfp": None, "tokens": 0, "audio_s": 0.0}
+            async for o in eng.generate(p, request_id=f"bench-{i}"):
+                now = time.perf_counter()
+                if o.final_output_type == "text" and o.outputs:
+                    n = len(o.outputs[0].token_ids)
+                    if n and r["ttft"] is None:
+                        r["ttft"] = now - t0
+                    r["tokens"] = max(r["tokens"], n)
+                elif o.final_output_type == "audio":
+                    mm = o.multimodal_output or {}
+                    if "audio" in mm:
+                        if r["ttfp"] is None:
+                            r["ttfp"] = now - t0
+                        r["audio_s"] += mm["audio"].numel() / float(mm.get("sample_rate", 24000))
+            r["latency"] = time.perf_counter() - t0
+            recs.append(r)
+
+    t0 = time.perf_counter()
+    tasks = []
+    for i, p in enumerate(prompts):
+        tasks.append(asyncio.create_task(one(i, p)))
+        if a.request_rate > 0:
+            await asyncio.sleep(rng.expovariate(a.request_rate))
+    await asyncio.gather(*tasks)
+    wall = time.perf_counter() - t0
+    eng.close()
+    toks = sum(r["tokens"] for r in recs)
+    out = {"metric": "qwen3_omni_e2e_tok_s", "requests": len(recs), "wall_s": round(wall, 3),
+           "e2e_text_tokens_per_s": round(toks / wall, 2), "requests_per_s": round(len(recs) / wall, 3),
+           "audio_seconds_per_s": round(sum(r["audio_s"] for r in recs) / wall, 3),
+           "ttft_s": {f"p{q}": _pct([r["ttft"] for r in recs if r["ttft"] is not None], q) for q in (50, 90, 99)},
+           "audio_ttfp_s": {f"p{q}": _pct([r["ttfp"] for r in recs if r["ttfp"] is not None], q) for q in (50, 90, 99)},
+           "e2el_s": {f"p{q}": _pct([r["latency"] for r in recs], q) for q in (50, 90, 99)},
+           "config": {"tiny": a.tiny, "input_len": a.input_len, "max_tokens": a.max_tokens, "codec_frames": a.codec_frames,
+                      "max_concurrency": a.max_concurrency, "request_rate": a.request_rate, "async_chunk": a.async_chunk,
+                      "data": "synthetic token ids; random-init weights"}}
+    print(json.dumps(out))
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--device", default="cpu")
+    ap.add_argument("--num-prompts", type=int, default=64)
+    ap.add_argument("--max-concurrency", type=int, default=64)
+    ap.add_argument("--request-rate", type=float, default=0.0, help="Poisson arrivals per second (0 = all at once)")
+    ap.add_argument("--input-len", type=int, default=128)
+    ap.add_argument("--max-tokens", type=int, default=64)
+    ap.add_argument("--codec-frames", type=int, default=64)
+    ap.add_argument("--async-chunk", action="store_true")
+    ap.add_argument("--thinker-layers", type=int, default=None)
+    ap.add_argument("--seed", type=int, default=0)
+    a = ap.parse_args(argv)
+    ov = {"tiny": True} if a.tiny else {}
+    if a.thinker_layers:
+        ov["thinker_layers"] = a.thinker_layers
+    y = (YAML.replace("ASYNC_CHUNK", "true" if a.async_chunk else "false").replace("DEVICE", a.device)
+         .replace("MAXB", str(a.max_concurrency)).replace("MAXTOK", str(a.max_tokens)).replace("CODEC", str(a.codec_frames))
+         .replace("OVERRIDES", json.dumps(ov)))
+    f = tempfile.NamedTemporaryFile("w", suffix=".yaml", delete=False)
+    f.write(y)
+    f.close()
+    return asyncio.run(_run(a, f.name))
+
+
+if __name__ == "__main__":
+    main()

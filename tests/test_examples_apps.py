@@ -84,3 +84,15 @@ def test_ray_backend_reports_missing_dependency():
     if not ray_utils.ray_available():
         with pytest.raises(RuntimeError, match="ray"):
             ray_utils.require_ray()
+
+
+def test_serving_latency_benchmark_tiny():
+    sys.path.insert(0, str(ROOT / "benchmarks" / "qwen3_omni"))
+    try:
+        import serving_latency
+    finally:
+        sys.path.pop(0)
+    rec = serving_latency.main(["--tiny", "--num-prompts", "4", "--max-concurrency", "2", "--input-len", "8",
+                                "--max-tokens", "5", "--codec-frames", "6", "--request-rate", "50"])
+    assert rec["requests"] == 4 and rec["e2e_text_tokens_per_s"] > 0
+    assert rec["ttft_s"]["p50"] is not None and rec["audio_ttfp_s"]["p50"] >= rec["ttft_s"]["p50"]
