@@ -82,26 +82,24 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
     if w.stride(-1) != 1:
         w = w.contiguous()
     sc_P, sc_G, sc_rows, sc_arr = 0, 0, 0, None
+    to_peers = scatter is not None or row_scatter is not None
     if row_scatter is not None:
         sc_rows, ptrs, ldc = row_scatter
         sc_P = len(ptrs)
-        sc_arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
-        scatter = row_scatter
-        out = x
     elif scatter is not None:
         sc_P, sc_G, ptrs, ldc = scatter
+    if to_peers:
         sc_arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
-        out = x                      # placeholder object; the kernel writes through the peer pointers
-    elif out is None:
-        out = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
-    if scatter is not None:
-        pass
-    elif out_rows_per_batch:
-        assert out.stride(-1) == 1
-        ldc = out.stride(-2)
+        c_ptr = nv.ptr(x2)                   # placeholder: the kernel writes through the peer pointers only
     else:
-        out2 = out.view(-1, N)
-        ldc = out2.stride(0)
+        if out is None:
+            out = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
+        if out_rows_per_batch:
+            assert out.stride(-1) == 1
+            ldc = out.stride(-2)
+        else:
+            ldc = out.view(-1, N).stride(0)
+        c_ptr = nv.ptr(out)
     res2 = None
     ldr = 0
     if residual is not None:
@@ -118,13 +116,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
     st = nv.status_word(x.device)
     rc = nv.lib("gemm_sm100").omni_gemm_bf16(
         nv.ptr(x2), ctypes.c_int(x2.stride(0)), nv.ptr(w), ctypes.c_int(w.stride(0)),
-        nv.ptr(out), ctypes.c_int(ldc), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        c_ptr, ctypes.c_int(ldc), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
         nv.ptr(bias), nv.ptr(res2), ctypes.c_int(ldr), nv.ptr(gate), ctypes.c_int(gs), ctypes.c_int(rpb),
         ctypes.c_int(ACT[act]), ctypes.c_int(out_rows_per_batch), ctypes.c_long(out_batch_stride),
         ctypes.c_int(sc_P), ctypes.c_int(sc_G), ctypes.c_int(sc_rows), sc_arr, ctypes.c_int(force_bn), nv.ptr(st),
         nv.stream_ptr())
     nv.check_rc(rc, "omni_gemm_bf16")
-    return None if scatter is not None else out
+    return None if to_peers else out
 
 
 class _GemmDesc(ctypes.Structure):
