@@ -61,5 +61,16 @@ def build_all(force: bool = False, verbose: bool = True) -> list[str]:
     return msgs
 
 
+def build_one(name: str, force: bool = False) -> str:
+    """Build a single library by source stem (e.g. ``"rt_host"``): the host-only pieces compile in a
+    second with g++ and are needed by CPU-side code paths too."""
+    LIB.mkdir(exist_ok=True)
+    for ext in (".cu", ".cpp"):
+        src = CSRC / f"{name}{ext}"
+        if src.exists():
+            return _compile(src, force)
+    raise FileNotFoundError(f"no source for library {name!r} under {CSRC}")
+
+
 if __name__ == "__main__":
     build_all(force="--force" in sys.argv)

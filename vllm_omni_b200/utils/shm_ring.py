@@ -14,6 +14,9 @@ from ..ops import _native as nv
 
 
 def _lib():
+    from ..build import build_one, lib_path
+    if not lib_path("rt_host").exists():        # host-only C++: build on first use where the tree is fresh
+        build_one("rt_host")
     lib = nv.lib("rt_host")._cdll
     if not getattr(lib, "_ring_typed", False):
         lib.omni_ring_open.restype = ctypes.c_void_p
