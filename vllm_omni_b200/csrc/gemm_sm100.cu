@@ -738,6 +738,8 @@ struct OmniGemmDesc {
   const void* bias; const void* residual; const void* gate;
   long c_batch_stride;
   int lda, ldw, ldc, M, ldr, gate_stride, rows_per_batch, act, c_rows_per_batch;
+  int scatter_P, scatter_G;      // > 1: column groups of scatter_G go to peer_out[g % scatter_P] (see GemmEpilogue)
+  void* peer_out[16];
 };
 
 static int desc_epilogue(const OmniGemmDesc& d, omni::GemmEpilogue& epi) {
@@ -754,6 +756,12 @@ static int desc_epilogue(const OmniGemmDesc& d, omni::GemmEpilogue& epi) {
   epi.act = d.act;
   epi.c_rows_per_batch = d.c_rows_per_batch;
   epi.c_batch_stride = d.c_batch_stride;
+  if (d.scatter_P > 1) {
+    if (d.scatter_P > 16 || d.scatter_G <= 0 || (d.scatter_G & 31)) return omni::RC_BAD_ARG;
+    epi.scatter_P = d.scatter_P;
+    epi.scatter_G = d.scatter_G;
+    for (int i = 0; i < d.scatter_P; ++i) epi.peer_out[i] = static_cast<__nv_bfloat16*>(d.peer_out[i]);
+  }
   return omni::RC_OK;
 }
 
@@ -763,21 +771,23 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
                               int c_rows_per_batch, long c_batch_stride, int scatter_P, int scatter_G,
                               int scatter_rows, void* const* peer_out, int force_bn, int* status, void* stream);
 
-extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d1, int N, int K, int* status,
-                                   void* stream) {
+extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d1, int N, int K, int force_pair,
+                                   int* status, void* stream) {
   using namespace omni;
   if (!d0 || !d1 || N <= 0 || K <= 0 || (N & 7) || (K & 7)) return RC_BAD_ARG;
   const OmniGemmDesc* ds[2] = {d0, d1};
   const int ctas = sm_count();
   long tiles = 0;
   for (int i = 0; i < 2; ++i) tiles += (long)((ds[i]->M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-  if (d0->M <= 0 || d1->M <= 0 || g_pair_mode != 1 || tiles < ctas / 2) {
+  if (d0->M <= 0 || d1->M <= 0 || (!force_pair && (g_pair_mode != 1 || tiles < ctas / 2))) {
     for (int i = 0; i < 2; ++i) {
       const OmniGemmDesc& d = *ds[i];
       if (d.M <= 0) continue;
+      if (d.scatter_P > 1 && (N % d.scatter_G)) return RC_BAD_ARG;
       int rc = omni_gemm_bf16(d.A, d.lda, d.W, d.ldw, d.C, d.ldc, d.M, N, K, d.bias, d.residual, d.ldr, d.gate,
-                              d.gate_stride, d.rows_per_batch, d.act, d.c_rows_per_batch, d.c_batch_stride, 0, 0, 0,
-                              nullptr, 0, status, stream);
+                              d.gate_stride, d.rows_per_batch, d.act, d.c_rows_per_batch, d.c_batch_stride,
+                              d.scatter_P > 1 ? d.scatter_P : 0, d.scatter_P > 1 ? d.scatter_G : 0, 0,
+                              d.scatter_P > 1 ? d.peer_out : nullptr, 0, status, stream);
       if (rc) return rc;
     }
     return RC_OK;
@@ -790,6 +800,7 @@ extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d
     GemmEpilogue epi;
     int rc = desc_epilogue(*ds[i], epi);
     if (rc) return rc;
+    if (epi.scatter_P > 1 && (N % epi.scatter_G)) return RC_BAD_ARG;
     rc = fill_pair_problem(args.p[i], ds[i]->A, ds[i]->lda, ds[i]->W, ds[i]->ldw, static_cast<__nv_bfloat16*>(ds[i]->C),
                            ds[i]->ldc, ds[i]->M, N, K, epi, tn);
     if (rc) return rc;

@@ -8,6 +8,7 @@ reference's vLLM ``ColumnParallelLinear`` / ``RowParallelLinear`` / ``QKVParalle
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.nn.functional as F
@@ -130,10 +131,11 @@ class _GemmDesc(ctypes.Structure):
                 ("residual", ctypes.c_void_p), ("gate", ctypes.c_void_p), ("c_batch_stride", ctypes.c_long),
                 ("lda", ctypes.c_int), ("ldw", ctypes.c_int), ("ldc", ctypes.c_int), ("M", ctypes.c_int),
                 ("ldr", ctypes.c_int), ("gate_stride", ctypes.c_int), ("rows_per_batch", ctypes.c_int),
-                ("act", ctypes.c_int), ("c_rows_per_batch", ctypes.c_int)]
+                ("act", ctypes.c_int), ("c_rows_per_batch", ctypes.c_int), ("scatter_P", ctypes.c_int),
+                ("scatter_G", ctypes.c_int), ("peer_out", ctypes.c_void_p * 16)]
 
 
-def _desc(x, w, bias, act, residual, gate, out, out_rows_per_batch, out_batch_stride, keep):
+def _desc(x, w, bias, act, residual, gate, out, out_rows_per_batch, out_batch_stride, keep, scatter=None):
     K, N = x.shape[-1], w.shape[0]
     x2 = x.reshape(-1, K)
     if x2.stride(-1) != 1:
@@ -141,12 +143,17 @@ def _desc(x, w, bias, act, residual, gate, out, out_rows_per_batch, out_batch_st
     if w.stride(-1) != 1:
         w = w.contiguous()
     M = x2.shape[0]
-    if out_rows_per_batch:
-        ldc = out.stride(-2)
-    else:
-        ldc = out.view(-1, N).stride(0)
     d = _GemmDesc()
-    d.A, d.W, d.C = x2.data_ptr(), w.data_ptr(), out.data_ptr()
+    if scatter is not None:                  # column groups go to peers; no local output
+        P, G, ptrs, ldc = scatter
+        d.scatter_P, d.scatter_G = P, G
+        for i, pp in enumerate(ptrs):
+            d.peer_out[i] = pp
+        c_ptr = x2.data_ptr()                # placeholder, never written
+    else:
+        ldc = out.stride(-2) if out_rows_per_batch else out.view(-1, N).stride(0)
+        c_ptr = out.data_ptr()
+    d.A, d.W, d.C = x2.data_ptr(), w.data_ptr(), c_ptr
     d.bias = bias.data_ptr() if bias is not None else None
     d.lda, d.ldw, d.ldc, d.M, d.act = x2.stride(0), w.stride(0), ldc, M, ACT[act]
     d.c_rows_per_batch, d.c_batch_stride = out_rows_per_batch, out_batch_stride
@@ -163,10 +170,11 @@ def _desc(x, w, bias, act, residual, gate, out, out_rows_per_batch, out_batch_st
     return d
 
 
-def linear_pair(a: dict, b: dict) -> None:
+def linear_pair(a: dict, b: dict, force_pair: bool | None = None) -> None:
     """Two linear layers of the same (N, K) in ONE launch (the image and text streams of a
     dual-stream block).  ``a`` / ``b``: keyword sets of ``linear`` — ``x, w, bias, act, residual,
-    gate, out`` (``out`` is required), optionally ``out_rows_per_batch, out_batch_stride``.  On the
+    gate, out`` (``out`` is required unless ``scatter`` is given), optionally ``out_rows_per_batch,
+    out_batch_stride, scatter``.  On the
     GPU both problems share the CTA-pair kernel's tile list, so the short one fills the last wave
     of the long one; on CPU they run one after the other."""
     xa, xb = a["x"], b["x"]
@@ -177,10 +185,13 @@ def linear_pair(a: dict, b: dict) -> None:
         return
     assert a["w"].shape == b["w"].shape, "the two problems must share N and K"
     keep: list = []
-    ds = [_desc(kw["x"], kw["w"], kw.get("bias"), kw.get("act"), kw.get("residual"), kw.get("gate"), kw["out"],
-                kw.get("out_rows_per_batch", 0), kw.get("out_batch_stride", 0), keep) for kw in (a, b)]
+    ds = [_desc(kw["x"], kw["w"], kw.get("bias"), kw.get("act"), kw.get("residual"), kw.get("gate"), kw.get("out"),
+                kw.get("out_rows_per_batch", 0), kw.get("out_batch_stride", 0), keep, kw.get("scatter")) for kw in (a, b)]
     N, K = a["w"].shape
+    if force_pair is None:                   # tests force the CTA-pair kernel at sizes below one wave
+        force_pair = os.environ.get("OMNI_GEMM_DUAL_FORCE") == "1"
     st = nv.status_word(xa.device)
     rc = nv.lib("gemm_sm100").omni_gemm_bf16_dual(ctypes.byref(ds[0]), ctypes.byref(ds[1]), ctypes.c_int(N),
-                                                  ctypes.c_int(K), nv.ptr(st), nv.stream_ptr())
+                                                  ctypes.c_int(K), ctypes.c_int(1 if force_pair else 0), nv.ptr(st),
+                                                  nv.stream_ptr())
     nv.check_rc(rc, "omni_gemm_bf16_dual")

@@ -17,6 +17,8 @@ the fused path is measured against, and the path CPU (Gloo) tests run.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import fused
@@ -32,6 +34,9 @@ class UlyssesJointAttention:
             raise ValueError(f"num_heads ({num_heads}) must be divisible by the Ulysses degree ({self.P})")
         self.H, self.Dh, self.Hp = num_heads, head_dim, num_heads // self.P
         self.mode = mode or ("fused" if torch.cuda.is_available() else "nccl")
+        # one launch for the image and text QKV projections: opt-in (OMNI_SP_PAIR_QKV=1) until it has been
+        # timed on GPUs
+        self.pair_streams = os.environ.get("OMNI_SP_PAIR_QKV", "0") == "1"
         self.arena = None
         self._key = None
 
@@ -78,9 +83,19 @@ class UlyssesJointAttention:
         G, B = self.Hp * self.Dh, self.B
         if self.mode == "fused":
             bs = self.S_tot * 3 * G
-            img_lin(xn_img, scatter=self._img_scatter, out_rows_per_batch=self.Si_loc, out_batch_stride=bs)
-            if self.St_loc:
-                txt_lin(xn_txt, scatter=self._txt_scatter, out_rows_per_batch=self.St_loc, out_batch_stride=bs)
+            plain = all(l.fp8 is None and not l.lora for l in (img_lin, txt_lin))
+            if self.St_loc and plain and self.pair_streams:
+                # image and text projection in one launch; each carries its own scatter pointers
+                from ..ops import gemm
+                gemm.linear_pair(
+                    dict(x=xn_img, w=img_lin.weight, bias=img_lin.bias, scatter=self._img_scatter,
+                         out_rows_per_batch=self.Si_loc, out_batch_stride=bs),
+                    dict(x=xn_txt, w=txt_lin.weight, bias=txt_lin.bias, scatter=self._txt_scatter,
+                         out_rows_per_batch=self.St_loc, out_batch_stride=bs))
+            else:
+                img_lin(xn_img, scatter=self._img_scatter, out_rows_per_batch=self.Si_loc, out_batch_stride=bs)
+                if self.St_loc:
+                    txt_lin(xn_txt, scatter=self._txt_scatter, out_rows_per_batch=self.St_loc, out_batch_stride=bs)
             self.arena.barrier()
             return
         grp = self.group.device_group
