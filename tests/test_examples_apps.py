@@ -96,3 +96,81 @@ def test_serving_latency_benchmark_tiny():
                                 "--max-tokens", "5", "--codec-frames", "6", "--request-rate", "50"])
     assert rec["requests"] == 4 and rec["e2e_text_tokens_per_s"] > 0
     assert rec["ttft_s"]["p50"] is not None and rec["audio_ttfp_s"]["p50"] >= rec["ttft_s"]["p50"]
+
+
+def test_ray_backend_with_a_fake_ray(monkeypatch, tmp_path):
+    """The Ray worker backend end to end against a stand-in ``ray`` module whose actors are threads:
+    placement group per stage, one actor per stage running the worker loop over "Ray" queues."""
+    import queue
+    import sys as _sys
+    import threading
+    import types
+
+    ray = types.ModuleType("ray")
+    state = {"actors": 0, "bundles": None, "killed": 0}
+    ray.is_initialized = lambda: True
+    ray.init = lambda **kw: None
+    ray.get = lambda x: x
+    ray.kill = lambda a: state.__setitem__("killed", state["killed"] + 1)
+
+    def remote(cls):
+        class Factory:
+            @staticmethod
+            def options(**kw):
+                class Maker:
+                    @staticmethod
+                    def remote():
+                        state["actors"] += 1
+                        inst = cls()
+
+                        class Handle:
+                            class run:                                       # noqa: N801
+                                @staticmethod
+                                def remote(fn, a, kw):
+                                    t = threading.Thread(target=fn, args=a, kwargs=kw, daemon=True)
+                                    t.start()
+                                    return t
+                        Handle.inst = inst
+                        return Handle
+                return Maker
+        return Factory
+    ray.remote = remote
+    util = types.ModuleType("ray.util")
+    pgm = types.ModuleType("ray.util.placement_group")
+
+    def placement_group(bundles, strategy="PACK"):
+        state["bundles"] = bundles
+        return types.SimpleNamespace(bundle_specs=bundles, ready=lambda: True)
+    pgm.placement_group = placement_group
+    qm = types.ModuleType("ray.util.queue")
+
+    class Q(queue.Queue):
+        def __init__(self, maxsize=0):
+            super().__init__(maxsize)
+    qm.Queue = Q
+    sm = types.ModuleType("ray.util.scheduling_strategies")
+    sm.PlacementGroupSchedulingStrategy = lambda **kw: kw
+    for name, mod in (("ray", ray), ("ray.util", util), ("ray.util.placement_group", pgm), ("ray.util.queue", qm),
+                      ("ray.util.scheduling_strategies", sm)):
+        monkeypatch.setitem(_sys.modules, name, mod)
+
+    from vllm_omni_b200.entrypoints.omni import Omni
+    from vllm_omni_b200.inputs import SamplingParams
+    y = tmp_path / "tts.yaml"
+    y.write_text("""
+stage_args:
+  - stage_id: 0
+    stage_type: llm
+    runtime: {devices: "0", max_batch_size: 2}
+    engine_args: {model_stage: qwen3_tts, model_arch: Qwen3TTSForConditionalGeneration, worker_type: generation,
+                  engine_output_type: audio, device: cpu, model_overrides: {tiny: true}}
+    final_output: true
+    final_output_type: audio
+""")
+    omni = Omni("qwen3-tts-tiny", stage_configs_path=str(y), worker_backend="ray")
+    try:
+        outs = omni.generate([{"prompt_token_ids": [5, 6, 7]}], [SamplingParams(temperature=0.0, max_tokens=4, seed=1)])
+        assert outs and outs[0].final_output_type == "audio" and outs[0].multimodal_output["audio"].numel() > 0
+        assert state["actors"] == 1 and state["bundles"] == [{"GPU": 1.0, "CPU": 1.0}]
+    finally:
+        omni.close()

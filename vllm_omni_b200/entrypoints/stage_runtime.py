@@ -272,10 +272,34 @@ def _stage_worker(cfg: StageConfig, model: str, in_q, out_q, batch_timeout_s: fl
 
 
 # =============================================================================== stage
+class _RayWorkerHandle:
+    """The slice of the Process API that ``OmniStage`` uses, over a Ray actor."""
+
+    def __init__(self, actor):
+        self.actor = actor
+        self._dead = False
+
+    def start(self):
+        pass
+
+    def is_alive(self) -> bool:
+        return not self._dead
+
+    def join(self, timeout=None):
+        pass
+
+    def terminate(self):
+        from ..distributed import ray_utils
+        ray_utils.kill_ray_actor(self.actor)
+        self._dead = True
+
+
 class OmniStage:
     def __init__(self, cfg: StageConfig, model: str | None, batch_timeout_s: float = 0.01,
-                 stage_init_timeout: float = 300.0):
+                 stage_init_timeout: float = 300.0, worker_backend: str = "mp", placement_group=None):
         self.cfg = cfg
+        self.worker_backend = worker_backend
+        self._placement_group = placement_group
         self.stage_id = cfg.stage_id
         self.stage_type = cfg.stage_type
         self.model = model
@@ -298,6 +322,16 @@ class OmniStage:
 
     # ------------------------------------------------------------------ lifecycle
     def init_stage_worker(self):
+        if self.worker_backend == "ray":
+            # one actor per stage, pinned to its placement-group bundle, running the same worker loop
+            # over Ray queues (vllm_omni/distributed/ray_utils/utils.py:28-181)
+            from ..distributed import ray_utils
+            self.in_process = False
+            self._in_q, self._out_q = ray_utils.make_queue(), ray_utils.make_queue()
+            actor, _ = ray_utils.start_ray_actor(_stage_worker, self._placement_group, self.stage_id, self.cfg, self.model,
+                                                 self._in_q, self._out_q, self.batch_timeout_s, False)
+            self._worker = _RayWorkerHandle(actor)
+            return
         if self.in_process:
             self._in_q, self._out_q = queue.Queue(), queue.Queue()
             self._worker = threading.Thread(target=_stage_worker, name=f"omni-stage-{self.stage_id}", daemon=True,
@@ -419,9 +453,10 @@ def build_stages(model, stage_configs_path, kwargs: dict, stage_init_timeout=300
                  worker_backend="mp", batch_timeout=10):
     """Returns (stages, connectors, pipeline_config).  ``batch_timeout`` is in milliseconds."""
     from ..connectors.factory import initialize_orchestrator_connectors
+    placement_group = None
     if worker_backend == "ray":
-        from ..distributed.ray_utils import require_ray
-        require_ray()
+        from ..distributed import ray_utils
+        ray_utils.initialize_ray_cluster()
     path = stage_configs_path or resolve_model_config_path(model)
     if path is not None:
         base = {k: v for k, v in kwargs.items() if k in ("dtype", "seed", "device", "load_format")}
@@ -431,8 +466,12 @@ def build_stages(model, stage_configs_path, kwargs: dict, stage_init_timeout=300
         pcfg = load_stage_configs_from_dict({"stage_args": []})
         pcfg.stages = [StageConfig.from_dict(_default_diffusion_stage(dict(kwargs)))]
     inject_omni_kv_config(pcfg.stages)
+    if worker_backend == "ray":
+        placement_group = ray_utils.create_placement_group(pcfg.stages)
+        shm_threshold_bytes = ray_utils.SHM_THRESHOLD_UNDER_RAY     # payloads ride on the Ray queues
     connectors = initialize_orchestrator_connectors(pcfg.stages, pcfg.runtime, shm_threshold_bytes=shm_threshold_bytes)
-    stages = [OmniStage(sc, model, batch_timeout_s=batch_timeout / 1000.0, stage_init_timeout=stage_init_timeout)
+    stages = [OmniStage(sc, model, batch_timeout_s=batch_timeout / 1000.0, stage_init_timeout=stage_init_timeout,
+                        worker_backend=worker_backend, placement_group=placement_group)
               for sc in pcfg.stages]
     for s in stages:
         s.init_stage_worker()
