@@ -79,8 +79,10 @@ class UniProcExecutor(DiffusionExecutor):
 class MultiprocDiffusionExecutor(DiffusionExecutor):
     HEARTBEAT_STALL_S = 120.0
 
-    def __init__(self, od_config, init_timeout: float = 600.0):
+    def __init__(self, od_config, init_timeout: float = 600.0, heartbeat_stall_s: float | None = None):
         super().__init__(od_config)
+        self.heartbeat_stall_s = float(heartbeat_stall_s if heartbeat_stall_s is not None
+                                       else os.environ.get("OMNI_WORKER_STALL_S", self.HEARTBEAT_STALL_S))
         ctx = mp.get_context("spawn")
         n = od_config.parallel_config.world_size
         self.res_q = ctx.Queue()
@@ -115,7 +117,7 @@ class MultiprocDiffusionExecutor(DiffusionExecutor):
             self.cmd_qs[r].put(msg)
         deadline = None if timeout is None else time.monotonic() + timeout
         last_beats = [hb.value for hb in self.heartbeats]
-        last_change = time.monotonic()
+        last_moved = [time.monotonic()] * len(last_beats)
         while True:
             try:
                 res = self.res_q.get(timeout=0.2)
@@ -130,7 +132,14 @@ class MultiprocDiffusionExecutor(DiffusionExecutor):
                 raise WorkerDeadError(f"diffusion worker(s) {dead} died during {method}")
             beats = [hb.value for hb in self.heartbeats]
             if beats != last_beats:
-                last_beats, last_change = beats, time.monotonic()
+                moved = [r for r, (a, b) in enumerate(zip(beats, last_beats)) if a != b]
+                for r in moved:
+                    last_moved[r] = time.monotonic()
+                last_beats = beats
+            frozen = [r for r, t in enumerate(last_moved) if time.monotonic() - t > self.heartbeat_stall_s]
+            if frozen:
+                raise WorkerDeadError(f"diffusion worker(s) {frozen} stopped responding (no heartbeat for "
+                                      f"{self.heartbeat_stall_s:.1f}s) during {method}")
             if deadline is not None and time.monotonic() > deadline:
                 raise TimeoutError(f"collective_rpc({method}) timed out after {timeout}s")
 

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import importlib
 import os
+import threading
 import time
 import traceback
 from typing import Any
@@ -204,15 +205,22 @@ def worker_main(local_rank: int, rank: int, od_config: OmniDiffusionConfig, cmd_
         return
     finally:
         ready_conn.close()
+    # liveness: a side thread bumps the shared counter a few times per second whatever the main
+    # thread is doing, so the engine can tell a long-running generation (counter moves) from a
+    # frozen process (counter stands still)
+    stop_beat = threading.Event()
+
+    def _beat():
+        while not stop_beat.wait(0.2):
+            with heartbeat.get_lock():
+                heartbeat.value += 1
+
+    threading.Thread(target=_beat, name="omni-worker-heartbeat", daemon=True).start()
     while True:
         try:
             msg = cmd_q.get(timeout=0.5)
         except Exception:
-            with heartbeat.get_lock():
-                heartbeat.value += 1
             continue
-        with heartbeat.get_lock():
-            heartbeat.value += 1
         if msg.get("type") == "shutdown":
             break
         method, args, kwargs = msg["method"], msg.get("args", ()), msg.get("kwargs", {})
@@ -225,4 +233,5 @@ def worker_main(local_rank: int, rank: int, od_config: OmniDiffusionConfig, cmd_
             out, err = None, f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
         if rank == msg.get("output_rank", 0) or msg.get("reply_all"):
             res_q.put({"id": msg["id"], "rank": rank, "result": out, "error": err})
+    stop_beat.set()
     w.shutdown()
