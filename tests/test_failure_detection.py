@@ -59,3 +59,60 @@ def test_rpc_time_limit(executor):
     os.kill(executor.procs[0].pid, signal.SIGCONT)
     # the late reply of the timed-out call must not be taken for the next call's answer
     assert executor.collective_rpc("check_health", timeout=30) is True
+
+
+TTS_PROC_YAML = """
+stage_args:
+  - stage_id: 0
+    stage_type: llm
+    runtime: {devices: "0", max_batch_size: 2, process: true}
+    engine_args: {model_stage: qwen3_tts, model_arch: Qwen3TTSForConditionalGeneration, worker_type: generation,
+                  engine_output_type: audio, device: cpu, model_overrides: {tiny: true}}
+    final_output: true
+    final_output_type: audio
+"""
+
+
+def test_dead_stage_fails_inflight_requests_and_is_restarted(tmp_path):
+    """A stage process is killed while a request is inside it: the request fails with a typed error,
+    the stage is started again and the next request is served."""
+    import asyncio
+
+    from vllm_omni_b200.entrypoints.async_omni import AsyncOmni
+    from vllm_omni_b200.entrypoints.orchestrator import StageError
+    from vllm_omni_b200.inputs import SamplingParams
+    y = tmp_path / "tts_proc.yaml"
+    y.write_text(TTS_PROC_YAML)
+
+    async def run():
+        eng = AsyncOmni("qwen3-tts-tiny", stage_configs_path=str(y), auto_restart_stages=True)
+        try:
+            sp = [SamplingParams(temperature=0.0, max_tokens=4, seed=1)]
+            outs = [o async for o in eng.generate({"prompt_token_ids": [5, 6, 7]}, sampling_params_list=sp)]
+            assert outs and outs[-1].final_output_type == "audio"
+            first_pid = eng.stage_list[0]._worker.pid
+
+            async def doomed():
+                got = []
+                with pytest.raises(StageError, match="died"):
+                    async for o in eng.generate({"prompt_token_ids": [8, 9]}, request_id="doomed",
+                                                sampling_params_list=[SamplingParams(temperature=0.0, max_tokens=60, seed=1)]):
+                        got.append(o)
+                return got
+
+            task = asyncio.create_task(doomed())
+            await asyncio.sleep(0.05)
+            os.kill(first_pid, signal.SIGKILL)
+            await asyncio.wait_for(task, 60)
+            # the router restarts the stage; wait until the new worker is in place
+            for _ in range(600):
+                if eng.stage_list[0]._worker.pid != first_pid and eng.stage_list[0].check_health():
+                    break
+                await asyncio.sleep(0.1)
+            assert eng.stage_list[0]._worker.pid != first_pid and not eng.errored
+            outs = [o async for o in eng.generate({"prompt_token_ids": [5, 6, 7]}, sampling_params_list=sp)]
+            assert outs and outs[-1].multimodal_output["audio"].numel() > 0
+        finally:
+            eng.close()
+
+    asyncio.run(run())

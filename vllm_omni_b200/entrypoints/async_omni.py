@@ -47,6 +47,10 @@ class _ReqState:
 
 class AsyncOmni(OmniBase):
     def __init__(self, model: str | None = None, **kwargs):
+        # auto_restart_stages: when a stage worker dies, fail the requests in flight with a typed
+        # error, start a fresh worker for that stage and keep serving (instead of declaring the whole
+        # engine dead)
+        self.auto_restart = bool(kwargs.pop("auto_restart_stages", False))
         super().__init__(model, **kwargs)
         self.async_chunk = bool(self.stage_configs.async_chunk)
         self._states: dict[str, _ReqState] = {}
@@ -184,16 +188,33 @@ class AsyncOmni(OmniBase):
                         self._post(st, e)
                         self._post(st, _DONE)
             if not progressed:
-                for s in self.stage_list:
+                for s in list(self.stage_list):
                     if not s.check_health() and not self._stop.is_set():
-                        self._errored = f"stage {s.stage_id} worker died"
+                        why = f"stage {s.stage_id} worker died"
                         with self._lock:
+                            lost = list(self._states)
                             for st in self._states.values():
-                                self._post(st, RuntimeError(self._errored))
+                                self._post(st, StageError(s.stage_id, st.rid, why, ""))
                                 self._post(st, _DONE)
                             self._states.clear()
+                        if self.auto_restart:
+                            for other in self.stage_list:          # drop what the lost requests left behind
+                                if other is not s and other.check_health() and lost:
+                                    other.abort(lost)
+                            try:
+                                self.restart_stage(s.stage_id)
+                                self._rewire()
+                                continue
+                            except Exception as e:   # noqa: BLE001
+                                why = f"{why}; restart failed: {e}"
+                        self._errored = why
                         return
                 time.sleep(0.0005)
+
+    def _rewire(self) -> None:
+        """Consumer lists hold stage objects: rebuild them after a stage was replaced."""
+        self.consumers = {s.stage_id: [d for d in self.stage_list if s.stage_id in d.engine_input_source]
+                          for s in self.stage_list}
 
     def _route(self, stage, res: dict) -> None:
         if res.get("type") in ("profile", "stage_stopped", "stage_ready"):

@@ -55,6 +55,26 @@ class OmniBase:
     def check_health(self) -> bool:
         return all(s.check_health() for s in self.stage_list)
 
+    def restart_stage(self, stage_id: int, timeout: float | None = None) -> None:
+        """Replace a stage whose worker died (or hangs) by a fresh one with the same configuration:
+        the old worker is stopped or terminated, a new worker loads the model again and the stage
+        object is swapped in place, so stage ids, edges and connectors stay valid.  Requests that were
+        inside the old worker are lost; the caller fails them (see ``AsyncOmni``)."""
+        from .stage_runtime import OmniStage
+        old = self.stage_list[stage_id]
+        try:
+            old.stop_stage_worker(join_timeout=1.0)
+        except Exception:   # noqa: BLE001
+            logger.exception("stopping stage %s before its restart failed", stage_id)
+        new = OmniStage(old.cfg, old.model, batch_timeout_s=old.batch_timeout_s, stage_init_timeout=old.stage_init_timeout,
+                        worker_backend=old.worker_backend, placement_group=getattr(old, "_placement_group", None))
+        new.init_stage_worker()
+        if not new.wait_ready(timeout):
+            new.stop_stage_worker()
+            raise RuntimeError(f"stage {stage_id} did not come back within its start-up limit")
+        self.stage_list[stage_id] = new
+        logger.warning("stage %s restarted", stage_id)
+
     def close(self):
         if self._closed:
             return
