@@ -50,7 +50,16 @@ class DecoderConfig:
     @classmethod
     def from_dict(cls, d: dict) -> "DecoderConfig":
         d = dict(d)
-        rs = d.get("rope_scaling") or {}
+        # newer HF configs nest the rotary settings under "rope_parameters" and call the expert
+        # count "num_local_experts"; checkpoints on disk carry either generation of names
+        rp = d.get("rope_parameters") or {}
+        if "rope_theta" in rp and d.get("rope_theta") is None:
+            d["rope_theta"] = float(rp["rope_theta"])
+        if d.get("rope_theta") is None:
+            d.pop("rope_theta", None)
+        if not d.get("num_experts") and d.get("num_local_experts"):
+            d["num_experts"] = d["num_local_experts"]
+        rs = d.get("rope_scaling") or rp
         if "mrope_section" in rs and "mrope_section" not in d:
             d["mrope_section"] = tuple(rs["mrope_section"])
             d["mrope_interleaved"] = bool(rs.get("mrope_interleaved", rs.get("interleaved", False)))
@@ -305,6 +314,10 @@ class QwenDecoderModel(nn.Module):
                 if cfg.num_experts:
                     if rest == "mlp.gate.weight":
                         tgt = layer.router.weight
+                    elif rest == "mlp.experts.gate_up_proj":        # experts stacked: [E, 2F, D]
+                        tgt = layer.w13
+                    elif rest == "mlp.experts.down_proj":           # [E, D, F]
+                        tgt = layer.w2
                     elif rest.startswith("mlp.experts."):
                         e = int(parts[4])
                         kind = parts[5]
