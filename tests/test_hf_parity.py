@@ -73,3 +73,77 @@ def test_per_expert_checkpoint_names():
     assert b.load_weights(flat.items()) == set(flat)
     for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
         assert torch.equal(p, q), n
+
+
+# ---------------------------------------------------------------------------- Qwen3-Omni stages
+def _init(hf, std=0.05, also=()):
+    for n, p in hf.named_parameters():
+        if p.dim() > 1 or any(k in n for k in also):
+            torch.nn.init.normal_(p, 0, std)
+    return hf.float().eval()
+
+
+def test_qwen3_omni_talker_stage_against_hf():
+    """MoE decoder with the shared expert and interleaved MRoPE, resize MLPs, codec head and code
+    predictor, all loaded from the ``talker.*`` names of a Hugging Face state dict."""
+    M = pytest.importorskip("transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe")
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeTalkerConfig
+    from vllm_omni_b200.models.qwen3_omni.config import Qwen3OmniConfig
+    from vllm_omni_b200.models.qwen3_omni.talker import Qwen3OmniMoeTalker
+    torch.manual_seed(0)
+    text = dict(vocab_size=96, hidden_size=48, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=16, moe_intermediate_size=32, shared_expert_intermediate_size=24,
+                num_experts=4, num_experts_per_tok=2, norm_topk_prob=True, max_position_embeddings=512,
+                rope_parameters=dict(rope_theta=1e6, rope_type="default", mrope_section=[4, 2, 2], mrope_interleaved=True))
+    cp = dict(vocab_size=64, hidden_size=48, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, num_code_groups=4, max_position_embeddings=64)
+    hc = Qwen3OmniMoeTalkerConfig(text_config=text, code_predictor_config=cp, thinker_hidden_size=64, num_code_groups=4,
+                                  accept_hidden_layer=2, spatial_merge_size=2)
+    hf = _init(M.Qwen3OmniMoeTalkerForConditionalGeneration(hc))
+    cfg = Qwen3OmniConfig.from_hf({"talker_config": hc.to_dict(), "thinker_config": {}})
+    cfg.thinker = Qwen3OmniConfig.tiny().thinker            # width 64 = thinker_hidden_size above
+    assert cfg.talker.shared_expert_intermediate_size == 24 and cfg.code_predictor.num_code_groups == 4
+    tk = Qwen3OmniMoeTalker(cfg, torch.float32, "cpu")
+    sd = {"talker." + k: v for k, v in hf.state_dict().items()}
+    assert tk.load_weights(sd.items()) == set(sd)
+    T = 11
+    x = torch.randn(T, 48)
+    pos = torch.stack([torch.arange(T), torch.arange(T) // 2, torch.arange(T) // 3])
+    with torch.no_grad():
+        ref = hf.model(inputs_embeds=x[None], position_ids=pos[:, None]).last_hidden_state[0]
+        b = ModelBatch(torch.zeros(T, dtype=torch.long), pos, torch.full((T,), -1, dtype=torch.int32),
+                       [PrefillSeg(0, T, 0, None)], input_embeds=x)
+        h, _ = tk.decoder(b, None)
+        assert (h - ref).abs().max().item() < 1e-4
+        assert (tk.compute_logits(h) - hf.codec_head(ref)).abs().max().item() < 1e-4
+        y = torch.randn(5, 64)
+        assert (tk.text_projection(y) - hf.text_projection(y)).abs().max().item() < 1e-5
+        assert (tk.hidden_projection(y) - hf.hidden_projection(y)).abs().max().item() < 1e-5
+        s = torch.randn(2, 3, 48)                       # talker hidden, code 0, code 1 -> logits of code 2
+        r = hf.code_predictor(inputs_embeds=s)
+        mine = torch.nn.functional.linear(tk.code_predictor._forward_seq(s), tk.code_predictor.lm_heads[1])
+        assert (mine - r.logits).abs().max().item() < 1e-4
+
+
+def test_qwen3_omni_code2wav_against_hf():
+    M = pytest.importorskip("transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe")
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeCode2WavConfig
+    from vllm_omni_b200.models.qwen3_omni.code2wav import Qwen3OmniCode2Wav
+    from vllm_omni_b200.models.qwen3_omni.config import Qwen3OmniConfig
+    torch.manual_seed(0)
+    hc = Qwen3OmniMoeCode2WavConfig(codebook_size=64, hidden_size=32, num_attention_heads=2, num_key_value_heads=2,
+                                    sliding_window=5, intermediate_size=64, num_hidden_layers=2, num_quantizers=4,
+                                    upsample_rates=[4, 2], upsampling_ratios=[2], decoder_dim=32, max_position_embeddings=512)
+    hf = _init(M.Qwen3OmniMoeCode2Wav(hc), 0.08, also=("alpha", "beta", "gamma", "scale", "bias"))
+    cfg = Qwen3OmniConfig.from_hf({"code2wav_config": hc.to_dict()})
+    m = Qwen3OmniCode2Wav(cfg, torch.float32, "cpu")
+    sd = {"code2wav." + k: v for k, v in hf.state_dict().items()}
+    assert m.load_weights(sd.items()) == set(sd)
+    codes = torch.randint(0, 64, (2, 4, 13))
+    with torch.no_grad():
+        ref, out = hf(codes)[:, 0], m.decode(codes)
+        assert ref.shape == out.shape and 0.05 < ref.abs().max().item() < 0.99        # not saturated by the clamp
+        assert (ref - out).abs().max().item() < 1e-5
+        r2 = hf.chunked_decode(codes, chunk_size=5, left_context_size=2)[:, 0]
+        o2 = m.chunked_decode(codes, 5, 2)
+        assert r2.shape == o2.shape and (r2 - o2).abs().max().item() < 1e-5

@@ -29,7 +29,7 @@ def test_tts_stage_produces_waveform(tmp_path):
         outs = omni.generate([prompt], [SamplingParams(temperature=0.0, max_tokens=8, seed=1)])
         assert len(outs) == 1 and outs[0].final_output_type == "audio"
         wav = outs[0].multimodal_output["audio"]
-        assert wav.dim() == 1 and wav.numel() % 16 == 0 and 0 < wav.numel() <= 8 * 16
+        assert wav.dim() == 1 and 0 < wav.numel() <= 8 * 16
         assert torch.isfinite(wav).all() and wav.abs().max() <= 1.0
     finally:
         omni.close()

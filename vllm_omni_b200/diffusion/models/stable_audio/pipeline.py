@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from ....models.qwen3_omni.code2wav import UpBlock
+from ....models.qwen3_omni.code2wav import DecoderBlock as UpBlock
 from ...data import DiffusionOutput, OmniDiffusionConfig
 from ...schedulers.flow_match_euler import FlowMatchEulerDiscreteScheduler
 from ..qwen_image.pipeline import HashTextEncoder

@@ -1,24 +1,32 @@
 """Qwen3-Omni code2wav stage: codec frames [T, G] -> 24 kHz waveform.
 
-Sum of per-codebook embeddings -> a few sliding-window transformer layers -> transposed-conv
-up-sampling stack with SnakeBeta activations (total factor = prod(upsample_rates) *
-prod(upsampling_ratios)).  Long sequences are decoded in chunks of ``chunk_size`` frames with
-``left_context`` frames of overlap whose samples are discarded
-(vllm_omni/model_executor/models/qwen3_omni/qwen3_omni_code2wav.py, chunked_decode).
-A one-shot ("generation") stage: no sampling, no KV cache.
+Mean of the per-codebook embeddings (one table, codebook g at offset g * codebook_size) ->
+sliding-window causal transformer with RoPE and layer scale -> (transposed conv, ConvNeXt block)
+per ``upsampling_ratios`` -> causal conv -> one block per ``upsample_rates`` (SnakeBeta, transposed
+conv, three dilated residual units) -> SnakeBeta -> causal conv to one channel, clamped to
+[-1, 1].  Long sequences are decoded in chunks of ``chunk_size`` frames with ``left_context``
+frames of overlap whose samples are discarded
+(vllm_omni/model_executor/models/qwen3_omni/qwen3_omni_code2wav.py:35-255).  The module tree
+and parameter names follow the Hugging Face checkpoint (``code2wav.*``), except that q/k/v and
+gate/up are stacked at load time.  A one-shot ("generation") stage: no sampling, no KV cache.
 """
 from __future__ import annotations
+
+import math
 
 import torch
 import torch.nn.functional as F
 from torch import nn
 
-from ...ops.attention import attention_reference
+from ...diffusion.layers.linear import FusedLinear
+from ...ops import fused
 from ..base import StageModel
 from .config import Code2WavConfig, Qwen3OmniConfig
 
 
 class SnakeBeta(nn.Module):
+    """x + sin^2(x e^alpha) / e^beta, per channel."""
+
     def __init__(self, ch, dtype, device):
         super().__init__()
         self.alpha = nn.Parameter(torch.zeros(ch, dtype=dtype, device=device), requires_grad=False)
@@ -31,66 +39,133 @@ class SnakeBeta(nn.Module):
         return (xf + (1.0 / (b + 1e-9)) * torch.sin(xf * a).pow(2)).to(x.dtype)
 
 
+class CausalConv1d(nn.Module):
+    """Left-padded convolution: output t sees inputs <= t (parameters ``conv.weight/bias``)."""
+
+    def __init__(self, cin, cout, k, dilation=1, stride=1, groups=1, dtype=None, device=None):
+        super().__init__()
+        self.conv = nn.Conv1d(cin, cout, k, stride=stride, dilation=dilation, groups=groups, dtype=dtype, device=device)
+        self.k_eff, self.stride = (k - 1) * dilation + 1, stride
+        self.pad = self.k_eff - stride
+
+    def forward(self, x):
+        L = x.shape[-1]
+        frames = math.ceil((L - self.k_eff + self.pad) / self.stride + 1)
+        extra = (frames - 1) * self.stride + (self.k_eff - self.pad) - L
+        return self.conv(F.pad(x, (self.pad, extra)))
+
+
+class CausalTransConv1d(nn.Module):
+    """Transposed convolution with (kernel - stride) samples cut from both ends."""
+
+    def __init__(self, cin, cout, k, stride, dtype=None, device=None):
+        super().__init__()
+        self.conv = nn.ConvTranspose1d(cin, cout, k, stride=stride, dtype=dtype, device=device)
+        self.trim = k - stride
+
+    def forward(self, x):
+        y = self.conv(x)
+        return y[..., self.trim: y.shape[-1] - self.trim].contiguous()
+
+
+class ConvNeXtBlock(nn.Module):
+    def __init__(self, dim, dtype, device):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device)
+        self.dwconv = CausalConv1d(dim, dim, 7, groups=dim, **kw)
+        self.norm = nn.LayerNorm(dim, eps=1e-6, **kw)
+        self.pwconv1 = FusedLinear(dim, 4 * dim, **kw)
+        self.pwconv2 = FusedLinear(4 * dim, dim, **kw)
+        self.gamma = nn.Parameter(torch.full((dim,), 1e-6, **kw), requires_grad=False)
+
+    def forward(self, x):           # [B, C, T]
+        h = self.norm(self.dwconv(x).transpose(1, 2))
+        h = self.pwconv2(F.gelu(self.pwconv1(h.contiguous())))
+        return x + (self.gamma * h).transpose(1, 2)
+
+
 class ResUnit(nn.Module):
     def __init__(self, ch, dilation, dtype, device):
         super().__init__()
         kw = dict(dtype=dtype, device=device)
         self.act1, self.act2 = SnakeBeta(ch, dtype, device), SnakeBeta(ch, dtype, device)
-        self.conv1 = nn.Conv1d(ch, ch, 7, dilation=dilation, padding=0, **kw)
-        self.conv2 = nn.Conv1d(ch, ch, 1, **kw)
-        self.pad = 6 * dilation
+        self.conv1 = CausalConv1d(ch, ch, 7, dilation=dilation, **kw)
+        self.conv2 = CausalConv1d(ch, ch, 1, **kw)
 
     def forward(self, x):
-        h = self.conv1(F.pad(self.act1(x), (self.pad, 0)))          # causal
-        return x + self.conv2(self.act2(h))
+        return x + self.conv2(self.act2(self.conv1(self.act1(x))))
 
 
-class UpBlock(nn.Module):
+class DecoderBlock(nn.Module):
+    """``block.0`` SnakeBeta, ``block.1`` transposed conv (x rate), ``block.2-4`` residual units."""
+
     def __init__(self, cin, cout, rate, dtype, device):
         super().__init__()
-        kw = dict(dtype=dtype, device=device)
-        self.act = SnakeBeta(cin, dtype, device)
-        self.up = nn.ConvTranspose1d(cin, cout, 2 * rate, stride=rate, **kw)
-        self.rate = rate
-        self.res = nn.ModuleList([ResUnit(cout, d, dtype, device) for d in (1, 3, 9)])
+        self.block = nn.ModuleList([SnakeBeta(cin, dtype, device),
+                                    CausalTransConv1d(cin, cout, 2 * rate, rate, dtype=dtype, device=device)] +
+                                   [ResUnit(cout, d, dtype, device) for d in (1, 3, 9)])
 
     def forward(self, x):
-        y = self.up(self.act(x))
-        y = y[..., :x.shape[-1] * self.rate]                          # causal trim
-        for r in self.res:
-            y = r(y)
-        return y
+        for b in self.block:
+            x = b(x)
+        return x
 
 
-class WindowBlock(nn.Module):
+class WindowLayer(nn.Module):
+    """Pre-norm transformer layer: causal attention inside a sliding window, RoPE, SwiGLU MLP, both
+    residual branches scaled per channel (layer scale)."""
+
     def __init__(self, cfg: Code2WavConfig, dtype, device):
         super().__init__()
         kw = dict(dtype=dtype, device=device)
-        D = cfg.hidden_size
-        self.heads, self.window = cfg.num_attention_heads, cfg.sliding_window
-        self.n1 = nn.Parameter(torch.ones(D, **kw), requires_grad=False)
-        self.n2 = nn.Parameter(torch.ones(D, **kw), requires_grad=False)
-        self.qkv = nn.Linear(D, 3 * D, bias=False, **kw)
-        self.o = nn.Linear(D, D, bias=False, **kw)
-        self.gate_up = nn.Linear(D, 2 * cfg.intermediate_size, bias=False, **kw)
-        self.down = nn.Linear(cfg.intermediate_size, D, bias=False, **kw)
+        D, H, Hkv = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads
+        self.H, self.Hkv, self.Dh, self.window, self.eps = H, Hkv, cfg.head_dim or D // H, cfg.sliding_window, cfg.rms_norm_eps
+        P = lambda v: nn.Parameter(torch.full((D,), v, **kw), requires_grad=False)
+        self.input_layernorm, self.post_attention_layernorm = P(1.0), P(1.0)
+        self.attn_scale, self.mlp_scale = P(cfg.layer_scale_initial_scale), P(cfg.layer_scale_initial_scale)
+        self.qkv = FusedLinear(D, (H + 2 * Hkv) * self.Dh, bias=cfg.attention_bias, **kw)
+        self.o = FusedLinear(H * self.Dh, D, bias=cfg.attention_bias, **kw)
+        self.gate_up = FusedLinear(D, 2 * cfg.intermediate_size, bias=False, **kw)
+        self.down = FusedLinear(cfg.intermediate_size, D, bias=False, **kw)
 
-    @staticmethod
-    def _rms(x, w):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).to(x.dtype)
-
-    def forward(self, x):           # [B, T, D]
+    def forward(self, x, cos, sin, mask):           # x [B, T, D]
         B, T, D = x.shape
-        qkv = self.qkv(self._rms(x, self.n1)).view(B, T, 3, self.heads, D // self.heads)
-        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        H, Hkv, Dh = self.H, self.Hkv, self.Dh
+        h = fused.norm_modulate(x, weight=self.input_layernorm, rms=True, eps=self.eps)
+        qkv = self.qkv(h)
+        if qkv.is_cuda and Dh not in (64, 128):
+            qkv = fused.qk_norm_rope_reference(qkv, H, Hkv, Dh, None, None, None, None, 1 << 30, cos, sin, False, self.eps)
+        else:
+            fused.qk_norm_rope_(qkv, H, Hkv, Dh, cos=cos, sin=sin, interleaved=False, eps=self.eps)
+        q = qkv[..., :H * Dh].view(B, T, H, Dh).transpose(1, 2)
+        k = qkv[..., H * Dh:(H + Hkv) * Dh].view(B, T, Hkv, Dh).transpose(1, 2)
+        v = qkv[..., (H + Hkv) * Dh:].view(B, T, Hkv, Dh).transpose(1, 2)
+        if Hkv != H:
+            k, v = k.repeat_interleave(H // Hkv, dim=1), v.repeat_interleave(H // Hkv, dim=1)
+        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask).transpose(1, 2).reshape(B, T, H * Dh)
+        x = x + self.attn_scale * self.o(o.contiguous())
+        h = fused.norm_modulate(x.contiguous(), weight=self.post_attention_layernorm, rms=True, eps=self.eps)
+        return x + self.mlp_scale * self.down(fused.silu_mul(self.gate_up(h)))
+
+
+class PreTransformer(nn.Module):
+    def __init__(self, cfg: Code2WavConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.layers = nn.ModuleList([WindowLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device), requires_grad=False)
+        Dh = cfg.head_dim or cfg.hidden_size // cfg.num_attention_heads
+        self.inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, Dh, 2, dtype=torch.float32) / Dh))
+
+    def forward(self, x):
+        T = x.shape[1]
         i = torch.arange(T, device=x.device)
-        mask = (i[None, :] <= i[:, None]) & (i[:, None] - i[None, :] < self.window)
-        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask).transpose(1, 2).reshape(B, T, D)
-        x = x + self.o(o)
-        h = self.gate_up(self._rms(x, self.n2))
-        F_ = h.shape[-1] // 2
-        return x + self.down(F.silu(h[..., :F_]) * h[..., F_:])
+        ang = i.float()[:, None] * self.inv_freq.to(x.device)[None]
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        mask = (i[None, :] <= i[:, None]) & (i[:, None] - i[None, :] < self.cfg.sliding_window)
+        for layer in self.layers:
+            x = layer(x, cos, sin, mask)
+        return fused.norm_modulate(x.contiguous(), weight=self.norm, rms=True, eps=self.cfg.rms_norm_eps)
 
 
 class Qwen3OmniCode2Wav(StageModel):
@@ -101,38 +176,35 @@ class Qwen3OmniCode2Wav(StageModel):
         super().__init__(None, dtype, device)
         c = self.c = cfg.code2wav
         kw = dict(dtype=dtype, device=device)
-        self.code_embedding = nn.Parameter(torch.empty(c.num_quantizers, c.codebook_size, c.hidden_size, **kw)
-                                           .normal_(0, 0.02), requires_grad=False)
-        self.pre = nn.ModuleList([WindowBlock(c, dtype, device) for _ in range(c.num_hidden_layers)])
-        self.pre_up = nn.ModuleList()
-        ch = c.hidden_size
-        for r in c.upsampling_ratios:
-            self.pre_up.append(nn.ConvTranspose1d(ch, ch, r, stride=r, **kw))
-        self.conv_in = nn.Conv1d(ch, c.decoder_dim, 7, padding=0, **kw)
-        ups, cin = [], c.decoder_dim
-        for r in c.upsample_rates:
-            ups.append(UpBlock(cin, max(cin // 2, 8), r, dtype, device))
-            cin = max(cin // 2, 8)
-        self.ups = nn.ModuleList(ups)
-        self.act_out = SnakeBeta(cin, dtype, device)
-        self.conv_out = nn.Conv1d(cin, 1, 7, padding=0, **kw)
+        D = c.hidden_size
+        self.code_embedding = nn.Parameter(torch.empty(c.num_quantizers * c.codebook_size, D, **kw).normal_(0, 0.02),
+                                           requires_grad=False)
+        self.pre_transformer = PreTransformer(c, dtype, device)
+        self.upsample = nn.ModuleList([nn.ModuleList([CausalTransConv1d(D, D, r, r, **kw), ConvNeXtBlock(D, dtype, device)])
+                                       for r in c.upsampling_ratios])
+        dec = [CausalConv1d(D, c.decoder_dim, 7, **kw)]
+        for i, r in enumerate(c.upsample_rates):
+            dec.append(DecoderBlock(c.decoder_dim // 2 ** i, c.decoder_dim // 2 ** (i + 1), r, dtype, device))
+        out = c.decoder_dim // 2 ** len(c.upsample_rates)
+        dec += [SnakeBeta(out, dtype, device), CausalConv1d(out, 1, 7, **kw)]
+        self.decoder = nn.ModuleList(dec)
 
     @torch.no_grad()
     def decode(self, codes: torch.Tensor) -> torch.Tensor:
-        """codes: [B, G, T] int64 -> waveform [B, T * total_upsample] in [-1, 1]."""
+        """codes: [B, G, T] int64 -> waveform [B, ~T * total_upsample] in [-1, 1] (every transposed
+        convolution of the decoder drops ``rate`` samples at each end)."""
         c = self.c
         B, G, T = codes.shape
-        x = sum(self.code_embedding[g][codes[:, g].clamp(0, c.codebook_size - 1)] for g in range(G))   # [B, T, D]
-        for blk in self.pre:
+        if G != c.num_quantizers:
+            raise ValueError(f"expected {c.num_quantizers} codebooks per frame, got {G}")
+        off = torch.arange(G, device=codes.device)[None, :, None] * c.codebook_size
+        x = self.code_embedding[codes.clamp(0, c.codebook_size - 1) + off].float().mean(1).to(self.code_embedding.dtype)
+        x = self.pre_transformer(x.contiguous()).transpose(1, 2)
+        for up, nxt in self.upsample:
+            x = nxt(up(x))
+        for blk in self.decoder:
             x = blk(x)
-        x = x.transpose(1, 2)
-        for up in self.pre_up:
-            x = up(x)
-        x = self.conv_in(F.pad(x, (6, 0)))
-        for up in self.ups:
-            x = up(x)
-        x = self.conv_out(F.pad(self.act_out(x), (6, 0)))
-        return torch.tanh(x.float())[:, 0]
+        return x.float().clamp(-1.0, 1.0)[:, 0]
 
     @torch.no_grad()
     def chunked_decode(self, codes: torch.Tensor, chunk_size=None, left_context=None) -> torch.Tensor:
@@ -150,7 +222,7 @@ class Qwen3OmniCode2Wav(StageModel):
             wav = self.decode(codes[..., start - ctx:end])
             outs.append(wav[..., ctx * up:])
             start = end
-        return torch.cat(outs, dim=-1)
+        return torch.cat(outs, dim=-1)[..., :T * up]
 
     def generate_for(self, req, start, n):
         info = req.additional_information
@@ -167,3 +239,48 @@ class Qwen3OmniCode2Wav(StageModel):
         if ctx:
             wav = wav[..., ctx * self.c.total_upsample:]
         return {"audio": wav[0].float(), "sample_rate": self.c.sample_rate}
+
+    # ------------------------------------------------------------------ weights
+    @torch.no_grad()
+    def load_weights(self, weights) -> set:
+        """Checkpoint names under ``code2wav.``; other stages' tensors are ignored."""
+        params = dict(self.named_parameters())
+        loaded = set()
+        for full, w in weights:
+            if full.startswith(("thinker.", "talker.")):
+                continue
+            n = full[len("code2wav."):] if full.startswith("code2wav.") else full
+            tgt, sl = None, None
+            p = n.split(".")
+            if n.startswith("pre_transformer.layers."):
+                layer = self.pre_transformer.layers[int(p[2])]
+                rest = ".".join(p[3:])
+                H, Hkv, Dh, Fi = layer.H, layer.Hkv, layer.Dh, self.c.intermediate_size
+                qo = {"q_proj": (0, H * Dh), "k_proj": (H * Dh, (H + Hkv) * Dh), "v_proj": ((H + Hkv) * Dh, (H + 2 * Hkv) * Dh)}
+                if p[3] == "self_attn" and p[4] in qo:
+                    tgt, sl = getattr(layer.qkv, p[5]), qo[p[4]]
+                elif p[3] == "self_attn" and p[4] == "o_proj":
+                    tgt = getattr(layer.o, p[5])
+                elif rest == "mlp.gate_proj.weight":
+                    tgt, sl = layer.gate_up.weight, (0, Fi)
+                elif rest == "mlp.up_proj.weight":
+                    tgt, sl = layer.gate_up.weight, (Fi, 2 * Fi)
+                elif rest == "mlp.down_proj.weight":
+                    tgt = layer.down.weight
+                else:
+                    tgt = {"input_layernorm.weight": layer.input_layernorm,
+                           "post_attention_layernorm.weight": layer.post_attention_layernorm,
+                           "self_attn_layer_scale.scale": layer.attn_scale,
+                           "mlp_layer_scale.scale": layer.mlp_scale}.get(rest)
+            elif n == "pre_transformer.norm.weight":
+                tgt = self.pre_transformer.norm
+            elif n == "code_embedding.weight":
+                tgt = self.code_embedding
+            else:
+                tgt = params.get(n)
+            if tgt is None:
+                continue
+            dst = tgt if sl is None else tgt[sl[0]:sl[1]]
+            dst.copy_(w.to(dst.dtype).reshape(dst.shape))
+            loaded.add(full)
+        return loaded

@@ -44,6 +44,8 @@ class CodePredictorConfig:
     intermediate_size: int = 3072
     vocab_size: int = 2048
     num_code_groups: int = 16
+    rope_theta: float = 1e6
+    rms_norm_eps: float = 1e-6
 
 
 @dataclass
@@ -56,6 +58,11 @@ class Code2WavConfig:
     num_key_value_heads: int = 16
     intermediate_size: int = 3072
     sliding_window: int = 72
+    head_dim: int | None = None        # None: hidden_size / num_attention_heads
+    attention_bias: bool = False
+    layer_scale_initial_scale: float = 0.01
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
     decoder_dim: int = 1536
     upsample_rates: tuple = (8, 5, 4, 3)
     upsampling_ratios: tuple = (2, 2)
@@ -79,7 +86,8 @@ class Qwen3OmniConfig:
         mrope_section=(24, 20, 20), mrope_interleaved=True))
     talker: DecoderConfig = field(default_factory=lambda: DecoderConfig(
         vocab_size=3072, hidden_size=1024, num_hidden_layers=20, num_attention_heads=16, num_key_value_heads=2,
-        head_dim=128, num_experts=128, num_experts_per_tok=6, moe_intermediate_size=384, rope_theta=1e6,
+        head_dim=128, intermediate_size=2048, num_experts=128, num_experts_per_tok=6, moe_intermediate_size=384,
+        shared_expert_intermediate_size=768, rope_theta=1e6,
         mrope_section=(24, 20, 20), mrope_interleaved=True))
     audio: AudioEncoderConfig = field(default_factory=AudioEncoderConfig)
     vision: VisionEncoderConfig = field(default_factory=VisionEncoderConfig)
@@ -105,8 +113,9 @@ class Qwen3OmniConfig:
                            num_key_value_heads=2, head_dim=16, num_experts=4, num_experts_per_tok=2,
                            moe_intermediate_size=32, mrope_section=(4, 2, 2), mrope_interleaved=True)
         tk = DecoderConfig(vocab_size=96, hidden_size=48, num_hidden_layers=2, num_attention_heads=4,
-                           num_key_value_heads=2, head_dim=16, num_experts=4, num_experts_per_tok=2,
-                           moe_intermediate_size=32, mrope_section=(4, 2, 2), mrope_interleaved=True)
+                           num_key_value_heads=2, head_dim=16, intermediate_size=64, num_experts=4,
+                           num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=24,
+                           mrope_section=(4, 2, 2), mrope_interleaved=True)
         return cls(thinker=th, talker=tk,
                    audio=AudioEncoderConfig(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=2,
                                             encoder_ffn_dim=64, downsample_hidden_size=8, output_dim=64, n_window=8),
@@ -132,6 +141,24 @@ class Qwen3OmniConfig:
         tk = d.get("talker_config", {})
         if tk.get("text_config"):
             c.talker = DecoderConfig.from_dict(tk["text_config"])
+        cp = tk.get("code_predictor_config")
+        if cp:
+            keys = set(CodePredictorConfig.__dataclass_fields__)
+            cp = dict(cp)
+            if cp.get("rope_theta") is None:
+                cp["rope_theta"] = float((cp.get("rope_parameters") or {}).get("rope_theta", 1e6))
+            c.code_predictor = CodePredictorConfig(**{k: v for k, v in cp.items() if k in keys})
+        cw = d.get("code2wav_config")
+        if cw:
+            keys = set(Code2WavConfig.__dataclass_fields__)
+            cw = dict(cw)
+            if cw.get("rope_theta") is None:
+                cw["rope_theta"] = float((cw.get("rope_parameters") or {}).get("rope_theta", 10000.0))
+            c.code2wav = Code2WavConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in cw.items() if k in keys})
+        for src, dst in (("codec_eos_token_id", "codec_eos_id"), ("codec_bos_id", "codec_bos_id"),
+                         ("codec_pad_id", "codec_pad_id"), ("codec_nothink_id", "codec_nothink_id")):
+            if src in tk:
+                setattr(c, dst, tk[src])
         for k in ("audio_token_id", "image_token_id", "video_token_id"):
             if k in th:
                 setattr(c, k, th[k])

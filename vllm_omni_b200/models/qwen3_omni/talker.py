@@ -29,6 +29,8 @@ from .config import CodePredictorConfig, Qwen3OmniConfig
 
 
 class ResizeMLP(nn.Module):
+    """thinker width -> talker width: Linear, SiLU, Linear (checkpoint names ``linear_fc1/2``)."""
+
     def __init__(self, din, dhid, dout, dtype, device):
         super().__init__()
         self.fc1 = FusedLinear(din, dhid, dtype=dtype, device=device)
@@ -36,6 +38,16 @@ class ResizeMLP(nn.Module):
 
     def forward(self, x):
         return self.fc2(self.fc1(x, act="silu"))
+
+    def load_weights(self, weights) -> set:
+        tgt = {"linear_fc1.weight": self.fc1.weight, "linear_fc1.bias": self.fc1.bias,
+               "linear_fc2.weight": self.fc2.weight, "linear_fc2.bias": self.fc2.bias}
+        loaded = set()
+        for n, w in weights:
+            if n in tgt:
+                tgt[n].copy_(w.to(tgt[n].dtype))
+                loaded.add(n)
+        return loaded
 
 
 class CodePredictor(nn.Module):
@@ -48,7 +60,8 @@ class CodePredictor(nn.Module):
         dc = DecoderConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
                            num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
                            num_key_value_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
-                           intermediate_size=cfg.intermediate_size)
+                           intermediate_size=cfg.intermediate_size, rope_theta=cfg.rope_theta,
+                           rms_norm_eps=cfg.rms_norm_eps)
         self.core = QwenDecoderModel(dc, dtype, device, with_lm_head=False)
         G = cfg.num_code_groups
         self.in_proj = FusedLinear(talker_hidden, cfg.hidden_size, dtype=dtype, device=device) \
@@ -58,6 +71,26 @@ class CodePredictor(nn.Module):
                                             .normal_(0, 0.02), requires_grad=False)
         self.lm_heads = nn.Parameter(torch.empty(G - 1, cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
                                      .normal_(0, 0.02), requires_grad=False)
+
+    @torch.no_grad()
+    def load_weights(self, weights) -> set:
+        """Names relative to ``talker.code_predictor.``: ``model.layers.*`` / ``model.norm.weight``,
+        ``model.codec_embedding.G.weight`` and ``lm_head.G.weight`` for residual codebooks G."""
+        loaded, core = set(), []
+        for n, w in weights:
+            p = n.split(".")
+            if n.startswith("model.codec_embedding.") and p[-1] == "weight":
+                self.codec_embedding[int(p[2])].copy_(w.to(self.codec_embedding.dtype))
+                loaded.add(n)
+            elif n.startswith("lm_head.") and p[-1] == "weight":
+                self.lm_heads[int(p[1])].copy_(w.to(self.lm_heads.dtype))
+                loaded.add(n)
+            elif n.startswith("in_proj.") and self.in_proj is not None:
+                getattr(self.in_proj, p[1]).copy_(w.to(self.in_proj.weight.dtype))
+                loaded.add(n)
+            else:
+                core.append((n, w))
+        return loaded | self.core.load_weights(core)
 
     def _forward_seq(self, x):
         """x: [n, L, D] small dense causal forward (no cache)."""
@@ -116,8 +149,9 @@ class Qwen3OmniMoeTalker(StageModel):
         self.cfg = cfg
         Dt, Dth = cfg.talker.hidden_size, cfg.thinker.hidden_size
         self.decoder = QwenDecoderModel(cfg.talker, dtype, device, with_lm_head=False)
-        self.text_projection = ResizeMLP(Dth, Dth, Dt, dtype, device)
-        self.hidden_projection = ResizeMLP(Dth, Dth, Dt, dtype, device)
+        Dr = cfg.talker.intermediate_size            # width of the resize MLPs' hidden layer
+        self.text_projection = ResizeMLP(Dth, Dr, Dt, dtype, device)
+        self.hidden_projection = ResizeMLP(Dth, Dr, Dt, dtype, device)
         self.codec_head = FusedLinear(Dt, cfg.talker.vocab_size, bias=False, dtype=dtype, device=device)
         self.code_predictor = CodePredictor(cfg.code_predictor, Dt, dtype, device)
         self.num_code_groups = cfg.code_predictor.num_code_groups
@@ -187,6 +221,30 @@ class Qwen3OmniMoeTalker(StageModel):
             r.multimodal_outputs.setdefault("codes", []).append(frames[i:i + 1])
         return ids
 
+    @torch.no_grad()
     def load_weights(self, weights):
-        ws = [(n[len("talker."):] if n.startswith("talker.") else n, w) for n, w in weights]
-        return self.decoder.load_weights(ws)
+        """Checkpoint names under ``talker.``: ``model.*`` (decoder, ``model.codec_embedding`` is its
+        embedding table), ``text_projection.*``, ``hidden_projection.*``, ``codec_head.weight``,
+        ``code_predictor.*``.  Names of other stages are ignored."""
+        groups = {"model.": [], "text_projection.": [], "hidden_projection.": [], "code_predictor.": []}
+        loaded = set()
+        for n, w in weights:
+            if n.startswith(("thinker.", "code2wav.")):
+                continue
+            full = n
+            n = n[len("talker."):] if n.startswith("talker.") else n
+            if n == "codec_head.weight":
+                self.codec_head.weight.copy_(w.to(self.codec_head.weight.dtype))
+                loaded.add(full)
+                continue
+            for pre, lst in groups.items():
+                if n.startswith(pre):
+                    lst.append((n if pre == "model." else n[len(pre):], w, full))
+                    break
+        subs = {"model.": self.decoder, "text_projection.": self.text_projection,
+                "hidden_projection.": self.hidden_projection, "code_predictor.": self.code_predictor}
+        for pre, lst in groups.items():
+            names = {n: full for n, _, full in lst}
+            got = subs[pre].load_weights([(n, w) for n, w, _ in lst])
+            loaded |= {names[n] for n in got}
+        return loaded

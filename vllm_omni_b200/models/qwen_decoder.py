@@ -37,6 +37,7 @@ class DecoderConfig:
     num_experts: int = 0                 # 0 = dense MLP
     num_experts_per_tok: int = 8
     moe_intermediate_size: int = 768
+    shared_expert_intermediate_size: int = 0   # > 0: a dense SwiGLU expert every token takes, sigmoid-gated
     norm_topk_prob: bool = True
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1e6
@@ -140,6 +141,12 @@ class DecoderLayer(nn.Module):
             self.w2 = nn.Parameter(torch.empty(E, D, F_, dtype=dtype, device=device).normal_(0, 0.02),
                                    requires_grad=False)
             self.moe_ws = MoEWorkspace()
+            Fs = cfg.shared_expert_intermediate_size
+            if Fs:
+                self.shared_gate_up = FusedLinear(D, 2 * Fs, bias=False, dtype=dtype, device=device)
+                self.shared_down = FusedLinear(Fs, D, bias=False, dtype=dtype, device=device)
+                self.shared_expert_gate = nn.Parameter(torch.empty(1, D, dtype=dtype, device=device).normal_(0, 0.02),
+                                                       requires_grad=False)
         else:
             self.gate_up = FusedLinear(D, 2 * cfg.intermediate_size, bias=False, dtype=dtype, device=device)
             self.down = FusedLinear(cfg.intermediate_size, D, bias=False, dtype=dtype, device=device)
@@ -246,6 +253,11 @@ class QwenDecoderModel(nn.Module):
             if cfg.num_experts:
                 logits = layer.router(xn)
                 e_lo, e_hi = self.ep_range
+                shared = None
+                if cfg.shared_expert_intermediate_size:
+                    # replicated under expert parallelism: added once, after the routed experts
+                    g = torch.sigmoid(xn.float() @ layer.shared_expert_gate.float().t())
+                    shared = layer.shared_down(fused.silu_mul(layer.shared_gate_up(xn))).float().mul_(g)
                 if self.ep_group is None or self.ep_group.world_size == 1:
                     moe_forward(xn, logits, layer.w13, layer.w2, cfg.num_experts_per_tok, cfg.norm_topk_prob,
                                 ws=layer.moe_ws, residual=x, out=x)
@@ -264,6 +276,8 @@ class QwenDecoderModel(nn.Module):
                                        e_lo=e_lo, e_hi=e_hi, ws=layer.moe_ws)
                     self.ep_group.all_reduce(part)
                     x.add_(part)
+                if shared is not None:
+                    x.add_(shared.to(x.dtype))
             else:
                 h = fused.silu_mul(layer.gate_up(xn))
                 layer.down(h, residual=x, out=x)
@@ -288,7 +302,7 @@ class QwenDecoderModel(nn.Module):
         for name, w in weights:
             n = name[len(prefix):] if name.startswith(prefix) else name
             tgt, sl = None, None
-            if n == "embed_tokens.weight":
+            if n in ("embed_tokens.weight", "codec_embedding.weight"):   # the talker calls its table codec_embedding
                 tgt = self.embed_tokens
             elif n == "norm.weight":
                 tgt = self.norm
@@ -318,6 +332,16 @@ class QwenDecoderModel(nn.Module):
                         tgt = layer.w13
                     elif rest == "mlp.experts.down_proj":           # [E, D, F]
                         tgt = layer.w2
+                    elif cfg.shared_expert_intermediate_size and rest.startswith("mlp.shared_expert"):
+                        Fs = cfg.shared_expert_intermediate_size
+                        if rest == "mlp.shared_expert.gate_proj.weight":
+                            tgt, sl = layer.shared_gate_up.weight, (0, Fs)
+                        elif rest == "mlp.shared_expert.up_proj.weight":
+                            tgt, sl = layer.shared_gate_up.weight, (Fs, 2 * Fs)
+                        elif rest == "mlp.shared_expert.down_proj.weight":
+                            tgt = layer.shared_down.weight
+                        elif rest == "mlp.shared_expert_gate.weight":
+                            tgt = layer.shared_expert_gate
                     elif rest.startswith("mlp.experts."):
                         e = int(parts[4])
                         kind = parts[5]
@@ -383,6 +407,11 @@ def reference_forward(model: QwenDecoderModel, input_ids: torch.Tensor, position
                     e = int(ids[t, j])
                     h = F.linear(xn[t], f(layer.w13[e]))
                     y[t] += w[t, j] * F.linear(F.silu(h[:Fd]) * h[Fd:], f(layer.w2[e]))
+            if cfg.shared_expert_intermediate_size:
+                Fs = cfg.shared_expert_intermediate_size
+                h = F.linear(xn, f(layer.shared_gate_up.weight))
+                y = y + torch.sigmoid(F.linear(xn, f(layer.shared_expert_gate))) * \
+                    F.linear(F.silu(h[:, :Fs]) * h[:, Fs:], f(layer.shared_down.weight))
             x = x + y
         else:
             h = F.linear(xn, f(layer.gate_up.weight))
