@@ -147,3 +147,117 @@ def test_qwen3_omni_code2wav_against_hf():
         r2 = hf.chunked_decode(codes, chunk_size=5, left_context_size=2)[:, 0]
         o2 = m.chunked_decode(codes, 5, 2)
         assert r2.shape == o2.shape and (r2 - o2).abs().max().item() < 1e-5
+
+
+def _init_all(hf):
+    for n, p in hf.named_parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, 0, 0.05)
+        else:
+            torch.nn.init.normal_(p, 0.5 if ("norm" in n or "ln" in n) else 0.0, 0.1)
+    return hf.float().eval()
+
+
+def test_qwen3_omni_audio_tower_against_hf():
+    """Chunked conv stem, per-chunk positions and block-diagonal windows.  The eager attention path
+    of the HF module drops ``cu_seqlens``; its own block-diagonal mask is handed to the layers so
+    that the oracle has the windowed semantics of its variable-length attention path."""
+    M = pytest.importorskip("transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe")
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeAudioEncoderConfig
+    from vllm_omni_b200.models.qwen3_omni.config import Qwen3OmniConfig
+    from vllm_omni_b200.models.qwen3_omni.encoders import AudioEncoder
+    torch.manual_seed(0)
+    ac = Qwen3OmniMoeAudioEncoderConfig(num_mel_bins=16, d_model=32, encoder_layers=2, encoder_attention_heads=2,
+                                        encoder_ffn_dim=64, downsample_hidden_size=8, output_dim=24, n_window=50,
+                                        n_window_infer=200, max_source_positions=64, conv_chunksize=500)
+    hf = _init_all(M.Qwen3OmniMoeAudioEncoder(ac))
+    cfg = Qwen3OmniConfig.from_hf({"thinker_config": {"audio_config": ac.to_dict()}})
+    enc = AudioEncoder(cfg.audio, torch.float32, "cpu")
+    sd = hf.state_dict()
+    assert enc.load_weights(sd.items()) == set(sd)
+
+    def windowed(mel, T):
+        origs = [layer.forward for layer in hf.layers]
+        for layer, orig in zip(hf.layers, origs):
+            layer.forward = lambda hs, cu, attention_mask=None, _o=orig, **kw: _o(
+                hs, cu, attention_mask=hf._prepare_attention_mask(hs, cu), **kw)
+        try:
+            return hf(mel, feature_lens=torch.tensor([T])).last_hidden_state
+        finally:
+            for layer, orig in zip(hf.layers, origs):
+                layer.forward = orig
+
+    for T in (530, 100, 37, 300):          # several chunks + short tail, one full chunk, one short chunk, exact chunks
+        mel = torch.randn(16, T)
+        with torch.no_grad():
+            ref, out = windowed(mel, T), enc(mel)
+        assert out.shape == ref.shape and out.shape[0] == enc.output_length(T)
+        assert (ref - out).abs().max().item() < 1e-5, T
+
+
+def test_qwen3_omni_vision_tower_against_hf():
+    M = pytest.importorskip("transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe")
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeVisionEncoderConfig
+    from vllm_omni_b200.models.qwen3_omni.config import Qwen3OmniConfig
+    from vllm_omni_b200.models.qwen3_omni.encoders import VisionEncoder
+    torch.manual_seed(0)
+    vc = Qwen3OmniMoeVisionEncoderConfig(depth=3, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=4,
+                                         temporal_patch_size=2, spatial_merge_size=2, in_channels=3, out_hidden_size=24,
+                                         num_position_embeddings=16, deepstack_visual_indexes=[0, 2])
+    hf = _init_all(M.Qwen3OmniMoeVisionEncoder(vc))
+    cfg = Qwen3OmniConfig.from_hf({"thinker_config": {"vision_config": vc.to_dict()}})
+    enc = VisionEncoder(cfg.vision, torch.float32, "cpu")
+    sd = hf.state_dict()
+    assert enc.load_weights(sd.items()) == set(sd)
+    gt, gh, gw = 2, 6, 4
+    patches = torch.randn(gt * gh * gw, 3 * 2 * 4 * 4)
+    with torch.no_grad():
+        r = hf(patches, grid_thw=torch.tensor([[gt, gh, gw]]))
+        out, grid, deep = enc.forward_patches(patches, (gt, gh, gw))
+    assert grid == (2, 3, 2) and (r.pooler_output - out).abs().max().item() < 1e-5
+    assert len(deep) == 2
+    for a, b in zip(r.deepstack_features, deep):
+        assert (a - b).abs().max().item() < 1e-5
+    # pixel entry point: frames [T, C, H, W] are cut into the same patch order
+    px = torch.randn(4, 3, 24, 16)
+    tp, p, m = 2, 4, 2
+    x = px.reshape(2, tp, 3, 3, m, p, 2, m, p).permute(0, 3, 6, 4, 7, 2, 1, 5, 8).reshape(2 * 6 * 4, -1)
+    with torch.no_grad():
+        o1, g1, _ = enc(px)
+        o2 = hf(x, grid_thw=torch.tensor([[2, 6, 4]])).pooler_output
+    assert g1 == (2, 3, 2) and (o1 - o2).abs().max().item() < 1e-5
+
+
+def test_qwen3_omni_thinker_text_with_deepstack_against_hf():
+    M = pytest.importorskip("transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe")
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeTextConfig
+    torch.manual_seed(0)
+    tc = Qwen3OmniMoeTextConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=3,
+                                num_attention_heads=4, num_key_value_heads=2, head_dim=16, moe_intermediate_size=32,
+                                num_experts=4, num_experts_per_tok=2, norm_topk_prob=True, max_position_embeddings=512,
+                                decoder_sparse_step=1, mlp_only_layers=[],
+                                rope_parameters=dict(rope_theta=1e6, rope_type="default", mrope_section=[4, 2, 2],
+                                                     mrope_interleaved=True))
+    hf = _init(M.Qwen3OmniMoeThinkerTextModel(tc))
+    cfg = DecoderConfig.from_dict(tc.to_dict())
+    assert cfg.mrope_section == (4, 2, 2) and cfg.mrope_interleaved and cfg.num_experts == 4
+    m = QwenDecoderModel(cfg, torch.float32, "cpu", with_lm_head=False)
+    sd = {"model." + k: v for k, v in hf.state_dict().items()}
+    assert m.load_weights(sd.items()) == set(sd)
+    T = 14
+    ids = torch.randint(0, 128, (T,))
+    pos = torch.stack([torch.arange(T), torch.arange(T) // 2, (torch.arange(T) * 2) % 5])
+    vis = torch.zeros(T, dtype=torch.bool)
+    vis[3:9] = True
+    feats = [torch.randn(6, 64) for _ in range(2)]
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None], position_ids=pos[:, None], visual_pos_masks=vis[None],
+                 deepstack_visual_embeds=feats).last_hidden_state[0]
+        dense = []
+        for f in feats:
+            d = torch.zeros(T, 64)
+            d[vis] = f
+            dense.append(d)
+        b = ModelBatch(ids, pos, torch.full((T,), -1, dtype=torch.int32), [PrefillSeg(0, T, 0, None)])
+        out, _ = m(b, None, deepstack=dense)
+    assert (out - ref).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())

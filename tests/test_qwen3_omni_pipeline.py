@@ -84,3 +84,48 @@ def test_thinker_expands_audio_placeholder(omni):
     pos = req.runtime_state["mrope_positions"]
     assert pos.shape == (3, 7 + n_audio) and int(pos[0, -1]) == 7 + n_audio - 1
     llm.abort_request(["probe"])
+
+
+def test_thinker_image_deepstack_reaches_the_decoder(omni):
+    """An image placeholder expands to the merged patch count; the vision tower's deep-stack features
+    are added after the first decoder layer(s) on exactly the image rows, also when the prompt is
+    prefilled in two chunks."""
+    from types import SimpleNamespace
+    from vllm_omni_b200.entrypoints.stage_runtime import inproc_adapter
+    from vllm_omni_b200.models.qwen_decoder import ModelBatch, PrefillSeg
+    llm = inproc_adapter(0).llm
+    th = llm.model
+    img = torch.randn(3, 16, 16, generator=torch.Generator().manual_seed(1))     # 4x4 patches -> 2x2 merged tokens
+    ids = [506, 10, 501, 11, 507]
+    req = llm.add_request("img", {"prompt_token_ids": ids, "multi_modal_data": {"image": [img]}},
+                          SamplingParams(temperature=0.0, max_tokens=1))
+    try:
+        assert req.num_prompt_tokens == 4 + 4
+        rows, vals = req.runtime_state["deepstack"]
+        assert rows.tolist() == [2, 3, 4, 5] and len(vals) == 1 and vals[0].shape == (4, 64)
+        T = req.num_prompt_tokens
+        pos = req.runtime_state["mrope_positions"]
+
+        def run(chunks):
+            outs, start = [], 0
+            for n in chunks:
+                b = ModelBatch(torch.tensor(req.prompt_token_ids[start:start + n]), pos[:, start:start + n],
+                               torch.full((n,), -1, dtype=torch.int32), [PrefillSeg(0, n, 0, None)],
+                               input_embeds=req.prompt_embeds[start:start + n],
+                               embeds_mask=torch.ones(n, dtype=torch.bool))
+                sched = SimpleNamespace(scheduled=[SimpleNamespace(request=req, start=start, num_new_tokens=n, is_prefill=True)])
+                outs.append(th._deepstack(b, sched))
+                start += n
+            return outs
+        whole = run([T])[0][0]
+        assert torch.equal(whole[2:6], vals[0]) and whole[:2].abs().sum() == 0 and whole[6:].abs().sum() == 0
+        a, b = run([3, T - 3])
+        assert torch.equal(torch.cat([a[0], b[0]]), whole)
+        # the features change the hidden states of the image rows (and, through attention, later rows)
+        b0 = ModelBatch(torch.tensor(req.prompt_token_ids), pos, torch.full((T,), -1, dtype=torch.int32),
+                        [PrefillSeg(0, T, 0, None)], input_embeds=req.prompt_embeds, embeds_mask=torch.ones(T, dtype=torch.bool))
+        h0, _ = th.decoder(b0, None)
+        h1, _ = th.decoder(b0, None, deepstack=[whole])
+        assert torch.equal(h0[:2], h1[:2]) and (h0[2:] - h1[2:]).abs().max() > 0
+    finally:
+        llm.abort_request(["img"])

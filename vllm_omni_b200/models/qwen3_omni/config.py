@@ -18,7 +18,9 @@ class AudioEncoderConfig:
     encoder_ffn_dim: int = 5120
     downsample_hidden_size: int = 480
     output_dim: int = 2048
-    n_window: int = 50                 # frames per attention window after the conv stem (x2)
+    n_window: int = 50                 # a chunk of the conv stem is 2 * n_window mel frames
+    n_window_infer: int = 400          # mel frames covered by one attention window
+    activation_function: str = "gelu"
 
 
 @dataclass
@@ -32,6 +34,9 @@ class VisionEncoderConfig:
     spatial_merge_size: int = 2
     in_channels: int = 3
     out_hidden_size: int = 2048
+    num_position_embeddings: int = 2304            # learned G x G position grid, G = 48
+    deepstack_visual_indexes: tuple = (8, 16, 24)  # blocks whose output also feeds decoder layers 0, 1, 2
+    hidden_act: str = "gelu_pytorch_tanh"
 
 
 @dataclass
@@ -118,9 +123,11 @@ class Qwen3OmniConfig:
                            mrope_section=(4, 2, 2), mrope_interleaved=True)
         return cls(thinker=th, talker=tk,
                    audio=AudioEncoderConfig(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=2,
-                                            encoder_ffn_dim=64, downsample_hidden_size=8, output_dim=64, n_window=8),
+                                            encoder_ffn_dim=64, downsample_hidden_size=8, output_dim=64, n_window=8,
+                                            n_window_infer=32),
                    vision=VisionEncoderConfig(depth=1, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=4,
-                                              temporal_patch_size=1, spatial_merge_size=2, out_hidden_size=64),
+                                              temporal_patch_size=1, spatial_merge_size=2, out_hidden_size=64,
+                                              num_position_embeddings=16, deepstack_visual_indexes=(0,)),
                    code_predictor=CodePredictorConfig(hidden_size=48, num_hidden_layers=1, num_attention_heads=4,
                                                       num_key_value_heads=2, head_dim=16, intermediate_size=64,
                                                       vocab_size=64, num_code_groups=4),
@@ -159,6 +166,11 @@ class Qwen3OmniConfig:
                          ("codec_pad_id", "codec_pad_id"), ("codec_nothink_id", "codec_nothink_id")):
             if src in tk:
                 setattr(c, dst, tk[src])
+        for key, klass, attr in (("audio_config", AudioEncoderConfig, "audio"), ("vision_config", VisionEncoderConfig, "vision")):
+            sub = th.get(key)
+            if sub:
+                keys = set(klass.__dataclass_fields__)
+                setattr(c, attr, klass(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in sub.items() if k in keys}))
         for k in ("audio_token_id", "image_token_id", "video_token_id"):
             if k in th:
                 setattr(c, k, th[k])

@@ -38,6 +38,7 @@ class Qwen3OmniMoeThinker(StageModel):
         mm = req.multi_modal_data or {}
         ids = list(req.prompt_token_ids)
         feats: dict[int, list[torch.Tensor]] = {}
+        deep_of: dict[int, list] = {}            # id(feature tensor) -> deep-stack features of that image / video
         image_grids, video_grids = [], []
         dev = self.decoder.embed_tokens.device
         for a in _as_list(mm.get("audio")):
@@ -46,12 +47,14 @@ class Qwen3OmniMoeThinker(StageModel):
         for im in _as_list(mm.get("image")):
             px = torch.as_tensor(im).to(dev)
             px = px[None] if px.dim() == 3 else px
-            f, g = self.visual(px)
+            f, g, deep = self.visual(px)
             feats.setdefault(cfg.image_token_id, []).append(f)
+            deep_of[id(f)] = deep
             image_grids.append(g)
         for vd in _as_list(mm.get("video")):
-            f, g = self.visual(torch.as_tensor(vd).to(dev))
+            f, g, deep = self.visual(torch.as_tensor(vd).to(dev))
             feats.setdefault(cfg.video_token_id, []).append(f)
+            deep_of[id(f)] = deep
             video_grids.append(g)
         if feats:
             # expand each single placeholder token to the feature length, build the overlay
@@ -77,9 +80,13 @@ class Qwen3OmniMoeThinker(StageModel):
             emb = torch.empty(len(new_ids), D, dtype=self.dtype_, device=dev)
             r = 0
             tok_rows, tok_ids = [], []
+            ds_rows, ds_vals = [], []
             for kind, v in chunks:
                 if kind == "feat":
                     emb[r:r + v.shape[0]] = v.to(self.dtype_)
+                    if deep_of.get(id(v)):
+                        ds_rows.append(torch.arange(r, r + v.shape[0], device=dev))
+                        ds_vals.append(deep_of[id(v)])
                     r += v.shape[0]
                 else:
                     tok_rows.append(r)
@@ -90,6 +97,11 @@ class Qwen3OmniMoeThinker(StageModel):
                     torch.tensor(tok_ids, device=dev).clamp(0, cfg.thinker.vocab_size - 1)]
             req.prompt_token_ids = new_ids
             req.prompt_embeds = emb
+            if ds_rows:
+                # prompt rows of the visual tokens and, per deep-stack level, their additive features
+                levels = len(ds_vals[0])
+                req.runtime_state["deepstack"] = (torch.cat(ds_rows), [torch.cat([d[l] for d in ds_vals]).to(self.dtype_)
+                                                                       for l in range(levels)])
         pos, _ = get_input_positions(req.prompt_token_ids, cfg.image_token_id, cfg.video_token_id, cfg.audio_token_id,
                                      image_grids, video_grids)
         req.runtime_state["mrope_positions"] = pos
@@ -104,7 +116,24 @@ class Qwen3OmniMoeThinker(StageModel):
         return torch.stack(cols, dim=1)
 
     def forward_batch(self, batch, kv_caches, sched):
-        return self.decoder(batch, kv_caches, capture_layers=self.capture)
+        return self.decoder(batch, kv_caches, capture_layers=self.capture, deepstack=self._deepstack(batch, sched))
+
+    def _deepstack(self, batch, sched):
+        """Dense [T, D] additive tensors for this step's rows, one per deep-stack level."""
+        out, row = None, 0
+        for s in getattr(sched, "scheduled", ()):
+            ds = s.request.runtime_state.get("deepstack")
+            if ds is not None and s.is_prefill:
+                rows, vals = ds
+                sel = (rows >= s.start) & (rows < s.start + s.num_new_tokens)
+                if bool(sel.any()):
+                    if out is None:
+                        T, D = batch.input_ids.shape[0], self.cfg.thinker.hidden_size
+                        out = [torch.zeros(T, D, dtype=self.dtype_, device=rows.device) for _ in vals]
+                    for l, v in enumerate(vals):
+                        out[l][rows[sel] - s.start + row] = v[sel]
+            row += s.num_new_tokens
+        return out
 
     def collect_outputs(self, sched, batch, hidden, captured) -> None:
         """Append this step's rows of the captured layers to every scheduled request."""
@@ -123,10 +152,26 @@ class Qwen3OmniMoeThinker(StageModel):
                 r.multimodal_outputs["tts_pad_embed"] = [e[c.tts_pad_token_id % e.shape[0]][None]]
             row += n
 
+    @torch.no_grad()
     def load_weights(self, weights):
-        ws = list(weights)
-        loaded = self.decoder.load_weights(((n[len("thinker."):] if n.startswith("thinker.") else n, w) for n, w in ws))
-        return {("thinker." + n if not n.startswith("thinker.") else n) for n in loaded}
+        """Checkpoint names under ``thinker.``: ``model.*`` / ``lm_head.weight`` (decoder),
+        ``audio_tower.*``, ``visual.*``.  Names of other stages are ignored."""
+        dec, aud, vis = [], [], []
+        for n, w in weights:
+            if n.startswith(("talker.", "code2wav.")):
+                continue
+            m = n[len("thinker."):] if n.startswith("thinker.") else n
+            if m.startswith("audio_tower."):
+                aud.append((m[len("audio_tower."):], w, n))
+            elif m.startswith("visual."):
+                vis.append((m[len("visual."):], w, n))
+            else:
+                dec.append((m, w, n))
+        loaded = set()
+        for sub, lst in ((self.decoder, dec), (self.audio_tower, aud), (self.visual, vis)):
+            full = {m: n for m, _, n in lst}
+            loaded |= {full[m] for m in sub.load_weights([(m, w) for m, w, _ in lst])}
+        return loaded
 
 
 def _as_list(x):

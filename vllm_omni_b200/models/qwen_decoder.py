@@ -229,8 +229,10 @@ class QwenDecoderModel(nn.Module):
             o[rows] = od
         return out
 
-    def forward(self, batch: ModelBatch, kv_caches=None, capture_layers=()):
-        """Returns (hidden [T, D] before the final norm applied -> after final norm, captured)."""
+    def forward(self, batch: ModelBatch, kv_caches=None, capture_layers=(), deepstack=None):
+        """Returns (hidden [T, D] after the final norm, captured layer outputs).  ``deepstack``: list
+        of [T, D] tensors; entry i is added to the output of layer i (visual features of the
+        vision tower's intermediate blocks, zero on the other rows)."""
         cfg = self.cfg
         H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         x = self.embed(batch)
@@ -281,6 +283,8 @@ class QwenDecoderModel(nn.Module):
             else:
                 h = fused.silu_mul(layer.gate_up(xn))
                 layer.down(h, residual=x, out=x)
+            if deepstack is not None and li < len(deepstack):
+                x.add_(deepstack[li].to(x.dtype))
             if (li + 1) in capture_layers:
                 captured[li + 1] = x.clone()
         hidden = fused.norm_modulate(x, weight=self.norm, rms=True, eps=cfg.rms_norm_eps)
