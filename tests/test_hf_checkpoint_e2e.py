@@ -116,3 +116,19 @@ def test_pipeline_serves_hf_checkpoint(checkpoint):
         g = hf.thinker.generate(input_ids=torch.tensor([ids]), attention_mask=torch.ones(1, len(ids), dtype=torch.long),
                                 max_new_tokens=6, do_sample=False)
     assert mine == g[0, len(ids):].tolist()
+
+
+def test_mrope_positions_match_hf_rope_index(checkpoint):
+    """Text, an image (1x4x6 patches), an audio clip and a video (2x4x4 patches, 2 s per temporal
+    grid step) in one prompt: the (t, h, w) position triples equal ``get_rope_index``."""
+    from vllm_omni_b200.models.mrope import get_input_positions
+    hf, _ = checkpoint
+    th = hf.thinker
+    th.config.vision_start_token_id, th.config.audio_start_token_id, th.config.position_id_per_seconds = 508, 510, 25
+    ids = [506, 10, 508] + [501] * 6 + [509, 11, 510] + [500] * 5 + [511, 12, 508] + [502] * 8 + [509, 13, 14]
+    inp = torch.tensor([ids])
+    ref, delta = th.get_rope_index(inp, image_grid_thw=torch.tensor([[1, 4, 6]]), video_grid_thw=torch.tensor([[2, 4, 4]]),
+                                   attention_mask=torch.ones_like(inp), use_audio_in_video=False,
+                                   audio_seqlens=torch.tensor([5]), second_per_grids=torch.tensor([2.0]))
+    mine, d = get_input_positions(ids, 501, 502, 500, [(1, 2, 3)], [(2, 2, 2)], seconds_per_grid_t=2.0)
+    assert torch.equal(ref[:, 0].long(), mine) and int(delta) == d

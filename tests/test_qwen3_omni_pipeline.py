@@ -52,7 +52,7 @@ def omni(tmp_path_factory):
 
 def _prompt(n_audio_frames=40):
     mel = torch.randn(16, n_audio_frames, generator=torch.Generator().manual_seed(0))
-    ids = [506, 10, 11, 500, 12, 507, 506, 13]          # text, one audio placeholder, text
+    ids = [506, 509, 11, 500, 12, 507, 506, 510, 13]    # user turn with one audio placeholder, assistant header
     return {"prompt_token_ids": ids, "multi_modal_data": {"audio": [mel]}}
 
 
@@ -79,10 +79,10 @@ def test_thinker_expands_audio_placeholder(omni):
     llm = inproc_adapter(0).llm
     req = llm.add_request("probe", _prompt(40), SamplingParams(temperature=0.0, max_tokens=1))
     n_audio = llm.model.audio_tower.output_length(40)
-    assert req.num_prompt_tokens == 7 + n_audio
-    assert req.prompt_embeds.shape == (7 + n_audio, 64)
+    assert req.num_prompt_tokens == 8 + n_audio
+    assert req.prompt_embeds.shape == (8 + n_audio, 64)
     pos = req.runtime_state["mrope_positions"]
-    assert pos.shape == (3, 7 + n_audio) and int(pos[0, -1]) == 7 + n_audio - 1
+    assert pos.shape == (3, 8 + n_audio) and int(pos[0, -1]) == 8 + n_audio - 1
     llm.abort_request(["probe"])
 
 
@@ -129,3 +129,42 @@ def test_thinker_image_deepstack_reaches_the_decoder(omni):
         assert torch.equal(h0[:2], h1[:2]) and (h0[2:] - h1[2:]).abs().max() > 0
     finally:
         llm.abort_request(["img"])
+
+
+def test_talker_prompt_follows_chatml_turns():
+    """System turn dropped, user turn row per token (audio row from the hidden states), assistant turn
+    = 3 header rows + 4 x pad + bos + first reply token with the codec control tokens added on the
+    last six rows; the other reply tokens and tts-eos wait for the decode steps."""
+    from types import SimpleNamespace
+    from vllm_omni_b200.models.qwen3_omni.config import Qwen3OmniConfig
+    from vllm_omni_b200.models.qwen3_omni.talker import Qwen3OmniMoeTalker
+    torch.manual_seed(0)
+    cfg = Qwen3OmniConfig.tiny()
+    tk = Qwen3OmniMoeTalker(cfg, torch.float32, "cpu")
+    prompt = [506, 508, 20, 507, 506, 509, 21, 500, 22, 507, 506, 510, 30]
+    gen = [40, 41, 42]
+    L = len(prompt) + len(gen)
+    emb, hid = torch.randn(L, 64), torch.randn(L, 64)
+    e3 = {k: torch.randn(1, 64) for k in ("tts_bos_embed", "tts_eos_embed", "tts_pad_embed")}
+    req = SimpleNamespace(additional_information=dict(thinker_embeddings=emb, thinker_hidden_states=hid,
+                                                      thinker_sequences=prompt + gen, thinker_input_ids=prompt,
+                                                      voice_type="Chelsie", **e3),
+                          runtime_state={}, prompt_embeds=None, prompt_token_ids=None)
+    tk.preprocess_request(req)
+    head = req.prompt_embeds
+    tp, hp, codec = tk.text_projection, tk.hidden_projection, tk.decoder.embed_tokens
+    pad, bos, eos = tp(e3["tts_pad_embed"]), tp(e3["tts_bos_embed"]), tp(e3["tts_eos_embed"])
+    assert head.shape == (6 + 9, 48) and len(req.prompt_token_ids) == 15
+    user = tp(emb[4:10])
+    user[3] = hp(hid[7:8])[0]
+    assert torch.allclose(head[:6], user, atol=1e-6)
+    a = head[6:]
+    assert torch.allclose(a[:3], tp(emb[10:13]), atol=1e-6)
+    ctrl = [cfg.codec_nothink_id, cfg.codec_think_bos_id, cfg.codec_think_eos_id, cfg.speaker_ids["chelsie"]]
+    for i, c in enumerate(ctrl):
+        assert torch.allclose(a[3 + i], pad[0] + codec[c], atol=1e-6)
+    assert torch.allclose(a[7], bos[0] + codec[cfg.codec_pad_id], atol=1e-6)
+    assert torch.allclose(a[8], tp(emb[13:14])[0] + codec[cfg.codec_bos_id], atol=1e-6)
+    trailing = req.runtime_state["text_steps"]
+    assert torch.allclose(trailing, torch.cat([tp(emb[14:16]), eos]), atol=1e-6)
+    assert tk.speaker_token("nobody") == cfg.speaker_ids["ethan"]        # unknown voice -> the first listed voice

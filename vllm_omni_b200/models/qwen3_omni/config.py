@@ -111,6 +111,13 @@ class Qwen3OmniConfig:
     codec_eos_id: int = 2150
     codec_pad_id: int = 2148
     codec_nothink_id: int = 2155
+    codec_think_bos_id: int = 2156
+    codec_think_eos_id: int = 2157
+    system_token_id: int = 8948         # role tokens that follow <|im_start|>
+    user_token_id: int = 872
+    assistant_token_id: int = 77091
+    audio_start_token_id: int = 151669  # stands in for the speaker token when the checkpoint lists no voices
+    speaker_ids: dict = field(default_factory=dict)      # voice name (lower case) -> codec token id
 
     @classmethod
     def tiny(cls) -> "Qwen3OmniConfig":
@@ -137,7 +144,9 @@ class Qwen3OmniConfig:
                                            chunk_size=12, left_context=3),
                    accept_hidden_layer=2, audio_token_id=500, image_token_id=501, video_token_id=502,
                    tts_bos_token_id=503, tts_eos_token_id=504, tts_pad_token_id=505, im_start_token_id=506,
-                   im_end_token_id=507, codec_bos_id=65, codec_eos_id=66, codec_pad_id=64, codec_nothink_id=67)
+                   im_end_token_id=507, codec_bos_id=65, codec_eos_id=66, codec_pad_id=64, codec_nothink_id=67,
+                   codec_think_bos_id=68, codec_think_eos_id=69, system_token_id=508, user_token_id=509,
+                   assistant_token_id=510, audio_start_token_id=71, speaker_ids={"ethan": 70, "chelsie": 72})
 
     @classmethod
     def from_hf(cls, d: dict) -> "Qwen3OmniConfig":
@@ -162,7 +171,10 @@ class Qwen3OmniConfig:
             if cw.get("rope_theta") is None:
                 cw["rope_theta"] = float((cw.get("rope_parameters") or {}).get("rope_theta", 10000.0))
             c.code2wav = Code2WavConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in cw.items() if k in keys})
-        for src, dst in (("codec_eos_token_id", "codec_eos_id"), ("codec_bos_id", "codec_bos_id"),
+        if isinstance(tk.get("speaker_id"), dict):
+            c.speaker_ids = {str(k).lower(): int(v) for k, v in tk["speaker_id"].items()}
+        for src, dst in (("codec_think_bos_id", "codec_think_bos_id"), ("codec_think_eos_id", "codec_think_eos_id"),
+                         ("audio_start_token_id", "audio_start_token_id"), ("codec_eos_token_id", "codec_eos_id"), ("codec_bos_id", "codec_bos_id"),
                          ("codec_pad_id", "codec_pad_id"), ("codec_nothink_id", "codec_nothink_id")):
             if src in tk:
                 setattr(c, dst, tk[src])
@@ -174,7 +186,8 @@ class Qwen3OmniConfig:
         for k in ("audio_token_id", "image_token_id", "video_token_id"):
             if k in th:
                 setattr(c, k, th[k])
-        for k in ("tts_bos_token_id", "tts_eos_token_id", "tts_pad_token_id", "im_start_token_id", "im_end_token_id"):
+        for k in ("tts_bos_token_id", "tts_eos_token_id", "tts_pad_token_id", "im_start_token_id", "im_end_token_id",
+                  "system_token_id", "user_token_id", "assistant_token_id"):
             if k in d:
                 setattr(c, k, d[k])
         if "accept_hidden_layer" in tk:

@@ -160,8 +160,25 @@ class Qwen3OmniMoeTalker(StageModel):
         return self.cfg.codec_eos_id
 
     # ---- request preprocessing (prefill embeddings)
+    def speaker_token(self, voice: str | None) -> int:
+        ids = self.cfg.speaker_ids
+        if not ids:
+            return self.cfg.audio_start_token_id
+        return ids.get((voice or "").lower(), next(iter(ids.values())))
+
     @torch.no_grad()
     def preprocess_request(self, req) -> None:
+        """Builds the talker prompt from the thinker's ChatML sequence
+        (vllm_omni/model_executor/models/qwen3_omni/qwen3_omni.py:778-1005).  The sequence is cut at
+        every ``<|im_start|>`` of the thinker prompt; system turns and earlier assistant turns are
+        dropped; user turns contribute one row per token (multimodal rows: projected layer-N hidden
+        state, text rows: projected embedding); the last assistant turn becomes nine rows,
+
+            text side   h0 h1 h2 pad pad pad pad bos t0      (h = header tokens, t0 = first reply token)
+            codec side   0  0  0 nothink think_bos think_eos speaker codec_pad codec_bos
+
+        added row by row.  The remaining reply tokens followed by tts-eos are fed one per decode
+        step on top of the previous frame's code embeddings, tts-pad afterwards."""
         info = req.additional_information
         cfg = self.cfg
         dev = self.decoder.embed_tokens.device
@@ -169,26 +186,64 @@ class Qwen3OmniMoeTalker(StageModel):
             return
         emb = info["thinker_embeddings"].to(dev, self.dtype_)               # [L_total, Dth]
         hid = info["thinker_hidden_states"].to(dev, self.dtype_)
-        seq = list(info.get("thinker_sequences") or [])
-        n_in = len(info.get("thinker_input_ids") or [])
+        prompt_ids = list(info.get("thinker_input_ids") or [])
+        seq = list(info.get("thinker_sequences") or prompt_ids)
+        L = min(emb.shape[0], max(len(seq), len(prompt_ids)))
+        n_in = min(len(prompt_ids), L)
         mm_ids = {cfg.audio_token_id, cfg.image_token_id, cfg.video_token_id}
-        is_mm = torch.tensor([t in mm_ids for t in seq[:n_in]], dtype=torch.bool, device=dev)
-        # prompt part: multimodal rows use the layer-N hidden states, text rows the embeddings
-        proj_text = self.text_projection(emb[:n_in].contiguous())
-        proj_hid = self.hidden_projection(hid[:n_in].contiguous())
-        prompt = torch.where(is_mm[:, None], proj_hid, proj_text) if n_in else proj_text
-        pad = self.text_projection(info["tts_pad_embed"].to(dev, self.dtype_).reshape(1, -1))
-        bos = self.text_projection(info["tts_bos_embed"].to(dev, self.dtype_).reshape(1, -1))
+        is_mm = torch.tensor([t in mm_ids for t in seq[:L]] + [False] * (L - len(seq[:L])), dtype=torch.bool, device=dev)
+        proj = lambda name: self.text_projection(info[name].to(dev, self.dtype_).reshape(1, -1))
+        pad, bos, eos = proj("tts_pad_embed"), proj("tts_bos_embed"), proj("tts_eos_embed")
         codec = self.decoder.embed_tokens
-        head = torch.cat([prompt,
-                          pad + codec[cfg.codec_nothink_id % codec.shape[0]][None],
-                          bos + codec[cfg.codec_bos_id % codec.shape[0]][None]], dim=0)
+        special = torch.tensor([cfg.codec_nothink_id, cfg.codec_think_bos_id, cfg.codec_think_eos_id,
+                                self.speaker_token(info.get("voice_type") or info.get("voice")), cfg.codec_pad_id,
+                                cfg.codec_bos_id], device=dev) % codec.shape[0]
+        codec_rows = codec[special]                                          # [6, Dt]
+
+        def user_part(a, b):
+            if b <= a:
+                return emb.new_zeros(0, pad.shape[1])
+            text = self.text_projection(emb[a:b].contiguous())
+            m = is_mm[a:b]
+            if bool(m.any()):
+                text = torch.where(m[:, None], self.hidden_projection(hid[a:b].contiguous()), text)
+            return text
+
+        def assistant_part(a, header):
+            """a: first row of the turn; header: number of ChatML header rows (3, or 0 without ChatML)."""
+            h = self.text_projection(emb[a:L].contiguous()) if L > a else emb.new_zeros(0, pad.shape[1])
+            first = h[header:header + 1] if h.shape[0] > header else torch.zeros_like(pad)
+            text = torch.cat([h[:header], pad.expand(4, -1), bos, first], dim=0)
+            text[header:] += codec_rows
+            trailing = torch.cat([h[header + 1:], eos], dim=0) if h.shape[0] > header + 1 else torch.zeros_like(eos)
+            return text, trailing
+
+        starts = [i for i, t in enumerate(prompt_ids[:n_in]) if t == cfg.im_start_token_id] + [L]
+        parts, trailing = [], None
+        if len(starts) > 1 and starts[0] > 0:
+            parts.append(user_part(0, starts[0]))                            # tokens before the first turn
+        for i in range(len(starts) - 1):
+            a, b = starts[i], starts[i + 1]
+            role = prompt_ids[a + 1] if a + 1 < n_in else None
+            last = i == len(starts) - 2
+            if role == cfg.system_token_id or (role == cfg.assistant_token_id and not last):
+                continue
+            if role == cfg.assistant_token_id:
+                text, trailing = assistant_part(a, 3)
+                parts.append(text)
+            else:
+                parts.append(user_part(a, min(b, n_in) if last else b))
+        if trailing is None:
+            # no ChatML assistant header in the prompt: the whole prompt is context, the reply starts
+            # with the first generated token
+            if len(starts) == 1:
+                parts.append(user_part(0, n_in))
+            text, trailing = assistant_part(n_in, 0)
+            parts.append(text)
+        head = torch.cat(parts, dim=0).contiguous()
         req.prompt_embeds = head
         req.prompt_token_ids = [0] * head.shape[0]
-        # text the talker still has to speak: projected embeddings of the thinker's generated tokens
-        gen = self.text_projection(emb[n_in:].contiguous()) if emb.shape[0] > n_in else emb.new_zeros(0, pad.shape[1])
-        eos = self.text_projection(info["tts_eos_embed"].to(dev, self.dtype_).reshape(1, -1))
-        req.runtime_state.update(text_steps=torch.cat([gen, eos], 0), tts_pad=pad, frames=[], next_embed=None)
+        req.runtime_state.update(text_steps=trailing, tts_pad=pad, frames=[], next_embed=None)
 
     def input_embeds_for(self, req, start, n):
         if start < req.num_prompt_tokens:
