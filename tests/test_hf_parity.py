@@ -261,3 +261,39 @@ def test_qwen3_omni_thinker_text_with_deepstack_against_hf():
         b = ModelBatch(ids, pos, torch.full((T,), -1, dtype=torch.int32), [PrefillSeg(0, T, 0, None)])
         out, _ = m(b, None, deepstack=dense)
     assert (out - ref).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())
+
+
+def test_qwen_image_prompt_encoder_against_hf_qwen2_5_vl():
+    """Packed (padding-free) prompt encoding equals the HF model's last hidden states behind the
+    34-token template head, for prompts of different lengths."""
+    from vllm_omni_b200.diffusion.models.qwen_image.text_encoder import QwenVLTextEncoder, text_config_from_hf
+    from vllm_omni_b200.engine.tokenizer import ByteTokenizer
+    torch.manual_seed(0)
+    hc = transformers.Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=2048,
+                         rope_parameters=dict(rope_theta=1e6, rope_type="default", mrope_section=[2, 3, 3])),
+        vision_config=dict(depth=1, hidden_size=32, intermediate_size=64, num_heads=2, out_hidden_size=64, patch_size=4,
+                           fullatt_block_indexes=[0]))
+    hf = transformers.Qwen2_5_VLForConditionalGeneration(hc).float().eval()
+    enc = QwenVLTextEncoder(text_config_from_hf(hc.to_dict()), ByteTokenizer(), torch.float32, "cpu")
+    sd = hf.state_dict()
+    want = {k for k in sd if "visual" not in k and not k.startswith("lm_head")}
+    assert enc.load_weights(sd.items()) == want
+    prompts = ["a cat on a mat", "a much longer prompt about a dog that sits under the old tree"]
+    states, mask = enc(prompts)
+    tok = ByteTokenizer()
+    seqs = [tok.encode(enc.template.format(p)) for p in prompts]
+    L = max(len(s) for s in seqs)
+    ids, am = torch.zeros(2, L, dtype=torch.long), torch.zeros(2, L, dtype=torch.long)
+    for i, s in enumerate(seqs):
+        ids[i, :len(s)], am[i, :len(s)] = torch.tensor(s), 1
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=am, output_hidden_states=True).hidden_states[-1]
+    assert states.shape == (2, L - 34, 64)
+    for i, s in enumerate(seqs):
+        n = len(s) - 34
+        assert int(mask[i].sum()) == n and states[i, n:].abs().sum() == 0
+        assert (states[i, :n] - ref[i, 34:len(s)]).abs().max().item() < 1e-4
+    short, _ = enc(prompts, max_sequence_length=50)
+    assert short.shape[1] == 50 and torch.equal(short, states[:, :50])

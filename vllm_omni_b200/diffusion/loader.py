@@ -84,6 +84,8 @@ class DiffusersPipelineLoader:
             if fmt != "dummy":
                 logger.warning("model path %r is not a local directory; keeping random weights", cfg.model)
         else:
+            if hasattr(pipe, "attach_text_encoder") and pipe.attach_text_encoder(cfg.model):
+                logger.info("prompt encoder: text_encoder/ of %s", cfg.model)
             loaded = pipe.load_weights(self.weights(cfg.model))
             logger.info("loaded %d checkpoint tensors from %s", len(loaded), cfg.model)
         if cfg.quantization:

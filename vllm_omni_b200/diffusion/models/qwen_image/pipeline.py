@@ -262,12 +262,27 @@ class QwenImagePipeline(nn.Module):
     def load_weights(self, weights) -> set:
         """``weights``: iterable of (name, tensor) with diffusers sub-folder prefixes
         ``transformer.`` / ``vae.``."""
-        tw, vw = [], []
+        tw, vw, ew = [], [], []
         for n, w in weights:
             if n.startswith("transformer."):
                 tw.append((n[len("transformer."):], w))
             elif n.startswith("vae."):
                 vw.append((n[len("vae."):], w))
+            elif n.startswith("text_encoder."):
+                ew.append((n[len("text_encoder."):], w))
         loaded = {"transformer." + n for n in self.transformer.load_weights(tw)}
         loaded |= {"vae." + n for n in self.vae.load_weights(vw)}
+        if ew and hasattr(self.text_encoder, "load_weights"):
+            loaded |= {"text_encoder." + n for n in self.text_encoder.load_weights(ew)}
         return loaded
+
+    def attach_text_encoder(self, model_path: str) -> bool:
+        """Replace the stand-in prompt encoder by the checkpoint's Qwen2.5-VL language model when the
+        pipeline directory carries ``text_encoder/`` and ``tokenizer/``."""
+        import os
+        if not (os.path.isfile(os.path.join(model_path, "text_encoder", "config.json")) and
+                os.path.isdir(os.path.join(model_path, "tokenizer"))):
+            return False
+        from .text_encoder import QwenVLTextEncoder
+        self.text_encoder = QwenVLTextEncoder.from_pretrained(model_path, self.od_config.dtype, self.device_)
+        return True
