@@ -31,6 +31,9 @@ TINY = {
 }
 
 
+SMALL_KL = dict(block_out_channels=(8, 16, 16, 16), layers_per_block=1, norm_num_groups=4)   # read by the KL-VAE families
+
+
 @pytest.fixture(autouse=True)
 def small_vae(monkeypatch):
     orig = vq.QwenImageVAEConfig
@@ -39,7 +42,7 @@ def small_vae(monkeypatch):
         k.setdefault("base_dim", 8)
         k.setdefault("num_res_blocks", 1)
         return orig(*a, **k)
-    for mod in ("vllm_omni_b200.diffusion.models.qwen_image.pipeline", "vllm_omni_b200.diffusion.models.flux.pipeline",
+    for mod in ("vllm_omni_b200.diffusion.models.qwen_image.pipeline",
                 "vllm_omni_b200.diffusion.models.wan.pipeline", "vllm_omni_b200.diffusion.models.hunyuan_image_3.pipeline"):
         import importlib
         m = importlib.import_module(mod)
@@ -48,7 +51,7 @@ def small_vae(monkeypatch):
 
 @pytest.mark.parametrize("name", sorted(TINY))
 def test_pipeline_runs_tiny(name):
-    o = OmniDiffusion(name, dtype="float32", device="cpu", tf_model_config=TINY[name])
+    o = OmniDiffusion(name, dtype="float32", device="cpu", tf_model_config=TINY[name], vae_config=SMALL_KL)
     try:
         sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0, num_frames=5,
                                          guidance_scale=3.0, extra_args={"audio_seconds": 0.01})

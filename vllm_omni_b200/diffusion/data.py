@@ -145,6 +145,7 @@ class OmniDiffusionConfig:
     host: str | None = None
     port: int | None = None
     model_paths: dict[str, str] = field(default_factory=dict)
+    vae_config: dict[str, Any] = field(default_factory=dict)   # vae/config.json of the checkpoint (or overrides)
     override_transformer_cls_name: str | None = None
     boundary_ratio: float | None = None
     flow_shift: float | None = None

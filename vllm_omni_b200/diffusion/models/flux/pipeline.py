@@ -13,7 +13,7 @@ from ...data import DiffusionOutput, OmniDiffusionConfig
 from ...request import OmniDiffusionRequest
 from ...schedulers.flow_match_euler import FlowMatchEulerDiscreteScheduler, calculate_shift
 from ..qwen_image.pipeline import HashTextEncoder, pack_latents, unpack_latents
-from ..vae.autoencoder_kl_qwenimage import AutoencoderKLQwenImage2d, QwenImageVAEConfig
+from ..vae import build_vae
 from .transformer import FluxTransformer2DModel, FluxTransformerConfig
 
 FLUX_SCHEDULER = dict(num_train_timesteps=1000, shift=3.0, use_dynamic_shifting=True, base_shift=0.5, max_shift=1.15,
@@ -34,7 +34,8 @@ class FluxPipeline(nn.Module):
         self.device_ = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
         tcfg = transformer_config or self.config_cls.from_dict(self.od_config.tf_model_config.to_dict())
         self.transformer = self.transformer_cls(tcfg, dtype=dtype, device=self.device_)
-        self.vae = AutoencoderKLQwenImage2d(vae_config or QwenImageVAEConfig()).to(device=self.device_, dtype=dtype)
+        self.vae = build_vae(vae_config or self.od_config.vae_config, "kl").to(device=self.device_, dtype=dtype)
+        self.vae.use_tiling = self.od_config.vae_use_tiling
         self.scheduler = FlowMatchEulerDiscreteScheduler(**FLUX_SCHEDULER)
         self.text_encoder = HashTextEncoder(tcfg.joint_attention_dim, max_len=self.max_text_len)
         self.pooled_encoder = HashTextEncoder(getattr(tcfg, "pooled_projection_dim", 768), max_len=1)
@@ -84,7 +85,17 @@ class FluxPipeline(nn.Module):
         return DiffusionOutput(output=img, metrics={"num_steps": len(ts), "batch": B})
 
     def load_weights(self, weights) -> set:
-        return set()
+        """diffusers sub-folder prefixes ``transformer.`` / ``vae.``."""
+        tw, vw = [], []
+        for n, w in weights:
+            if n.startswith("transformer."):
+                tw.append((n[len("transformer."):], w))
+            elif n.startswith("vae."):
+                vw.append((n[len("vae."):], w))
+        loaded = {"transformer." + n for n in self.transformer.load_weights(tw)}
+        if vw and hasattr(self.vae, "load_weights"):
+            loaded |= {"vae." + n for n in self.vae.load_weights(vw)}
+        return loaded
 
 
 class Flux2KleinPipeline(FluxPipeline):

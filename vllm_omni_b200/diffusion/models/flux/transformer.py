@@ -77,6 +77,35 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
             self._angles[key] = (a.cos().contiguous().to(device), a.sin().contiguous().to(device))
         return self._angles[key]
 
+    def checkpoint_name_map(self) -> dict:
+        """diffusers ``FluxTransformer2DModel`` parameter name -> (our parameter name, row slice)."""
+        cfg, D = self.cfg, self.cfg.inner_dim
+        ren = (("img_in.", "x_embedder."), ("txt_in.", "context_embedder."), (".img_mod.1.", ".norm1.linear."),
+               (".txt_mod.1.", ".norm1_context.linear."), (".img_mlp.", ".ff."), (".txt_mlp.", ".ff_context."))
+        m = {}
+        for k, v in super().checkpoint_name_map().items():
+            if k.startswith("txt_norm"):
+                continue
+            for a, b in ren:
+                k = k.replace(a, b) if a[0] == "." else (b + k[len(a):] if k.startswith(a) else k)
+            m[k] = v
+        for wb in ("weight", "bias"):
+            for j in (1, 2):
+                m[f"time_text_embed.text_embedder.linear_{j}.{wb}"] = (f"pooled_{j}.{wb}", None)
+                if self.guidance_embed is not None:
+                    m[f"time_text_embed.guidance_embedder.linear_{j}.{wb}"] = (f"guidance_embed.linear_{j}.{wb}", None)
+            for i in range(cfg.num_single_layers):
+                p, o = f"single_transformer_blocks.{i}.", f"single_blocks.{i}."
+                m[p + f"norm.linear.{wb}"] = (f"single_mod.{wb}", (i * 3 * D, (i + 1) * 3 * D))
+                for k, n in enumerate(("to_q", "to_k", "to_v")):
+                    m[p + f"attn.{n}.{wb}"] = (o + f"linear1.{wb}", (k * D, (k + 1) * D))
+                m[p + f"proj_mlp.{wb}"] = (o + f"linear1.{wb}", (3 * D, 3 * D + cfg.mlp_ratio * D))
+                m[p + f"proj_out.{wb}"] = (o + f"linear2.{wb}", None)
+        for i in range(cfg.num_single_layers):
+            m[f"single_transformer_blocks.{i}.attn.norm_q.weight"] = (f"single_blocks.{i}.norm_q", None)
+            m[f"single_transformer_blocks.{i}.attn.norm_k.weight"] = (f"single_blocks.{i}.norm_k", None)
+        return m
+
     def single_forward(self, blk: SingleBlock, x, m3, cos, sin, kv_lens, S_img):
         """x: joint [B, S, D] in place; m3 [B, 3D] = shift, scale, gate."""
         cfg = self.cfg
@@ -112,7 +141,7 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
         vec = self.time_embed(timestep, self.dtype_)
         if self.guidance_embed is not None:
             g = guidance if guidance is not None else torch.full((B,), 3.5, device=dev)
-            vec = vec + self.guidance_embed(g / 1000.0 * 1.0, self.dtype_)
+            vec = vec + self.guidance_embed(g, self.dtype_)          # the embedder scales by 1000 itself
         if pooled_projections is not None:
             vec = vec + self.pooled_2(self.pooled_1(pooled_projections.to(self.dtype_), act="silu"))
         sv = F.silu(vec)

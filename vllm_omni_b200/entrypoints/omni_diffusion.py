@@ -48,6 +48,9 @@ def build_diffusion_config(model: str | None = None, od_config: OmniDiffusionCon
             tc = read_component_config(m, "transformer")
             if tc and not cfg.tf_model_config.params:
                 cfg.tf_model_config = TransformerConfig.from_dict(tc)
+            vc = read_component_config(m, "vae")
+            if vc and not cfg.vae_config:
+                cfg.vae_config = vc
         elif m in _DIFFUSION_MODELS:
             cfg.model_class_name = m
             cfg.diffusion_load_format = "dummy"
