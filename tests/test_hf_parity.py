@@ -297,3 +297,21 @@ def test_qwen_image_prompt_encoder_against_hf_qwen2_5_vl():
         assert (states[i, :n] - ref[i, 34:len(s)]).abs().max().item() < 1e-4
     short, _ = enc(prompts, max_sequence_length=50)
     assert short.shape[1] == 50 and torch.equal(short, states[:, :50])
+
+
+def test_z_image_caption_encoder_takes_second_to_last_layer():
+    from vllm_omni_b200.diffusion.models.z_image.text_encoder import QwenCaptionEncoder
+    from vllm_omni_b200.engine.tokenizer import ByteTokenizer
+    torch.manual_seed(0)
+    hf = transformers.Qwen3ForCausalLM(transformers.Qwen3Config(**{**BASE, "vocab_size": 300, "num_hidden_layers": 3}, head_dim=32)).float().eval()
+    enc = QwenCaptionEncoder(DecoderConfig.from_dict(hf.config.to_dict()), ByteTokenizer(), torch.float32, "cpu")
+    sd = hf.state_dict()
+    assert enc.load_weights(sd.items()) == {k for k in sd if not k.startswith("lm_head")}
+    prompts = ["a lighthouse at dusk", "fog"]
+    states, mask = enc(prompts)
+    for i, p in enumerate(prompts):
+        ids = torch.tensor([enc._ids(p)])
+        with torch.no_grad():
+            ref = hf(input_ids=ids, output_hidden_states=True).hidden_states[-2][0]
+        n = ids.shape[1]
+        assert int(mask[i].sum()) == n and (states[i, :n] - ref).abs().max().item() < 1e-4

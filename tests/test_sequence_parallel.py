@@ -204,15 +204,15 @@ def _zimage_sp_worker(rank, world, backend, uly, ring):
     from vllm_omni_b200.parallel.sp_attention import SequenceParallelAttention
     ps.init_distributed_environment(world, rank, local_rank=rank, backend=backend)
     ps.initialize_model_parallel(sequence_parallel_size=world, ulysses_degree=uly, ring_degree=ring, backend=backend)
-    cfg = ZImageTransformerConfig(dim=64, n_layers=2, n_heads=4, head_dim=16, ffn_dim=96, in_channels=8, out_channels=2,
-                                  cap_feat_dim=24, axes_dims_rope=(4, 6, 6))
+    cfg = ZImageTransformerConfig(dim=64, n_layers=2, n_refiner_layers=1, n_heads=4, n_kv_heads=4, in_channels=2,
+                                  cap_feat_dim=24, axes_dims=(4, 6, 6), axes_lens=(128, 16, 16))
     torch.manual_seed(0)
     m = ZImageTransformer2DModel(cfg, dtype=torch.float32, device="cpu")
     g = torch.Generator().manual_seed(4)
     x = torch.randn(2, 6 * 5, 8, generator=g)
-    e = torch.randn(2, 9, 24, generator=g)                 # 30 + 9 = 39 rows: padded to a multiple of P
+    e = torch.randn(2, 40, 24, generator=g)                # captions of 40 and 5 tokens -> 64 and 32 rows with pad tokens
     t = torch.tensor([0.3, 0.3])
-    for lens in (None, [9, 5]):
+    for lens in (None, [40, 5]):
         m.sp = None
         ref = m(x, e, t, (1, 6, 5), txt_seq_lens=lens)
         m.sp = SequenceParallelAttention(ps.get_sp_group(), 4, 16, mode="nccl")
