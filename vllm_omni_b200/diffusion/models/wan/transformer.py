@@ -203,6 +203,10 @@ class WanTransformer3DModel(nn.Module):
             base, _, leaf = name.rpartition(".")
             if base in simple:
                 tgt = f"{simple[base]}.{leaf}"
+                if base == "proj_out":
+                    # the checkpoint emits a patch as (pt, ph, pw, c); ``unpatchify`` reads (c, pt, ph, pw)
+                    C = cfg.out_channels
+                    w = w.reshape(w.shape[0] // C, C, *w.shape[1:]).transpose(0, 1).reshape(w.shape)
             elif name == "patch_embedding.weight":
                 tgt, w = "patch_embedding.weight", w.reshape(w.shape[0], -1)
             elif name == "patch_embedding.bias":
