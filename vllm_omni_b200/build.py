@@ -43,7 +43,9 @@ def _compile(src: Path, force: bool) -> str:
         nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
         cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(out), str(src)]
     else:
-        cmd = [os.environ.get("CXX", "g++"), *CXX_FLAGS, "-I", str(CSRC), "-o", str(out), str(src), "-lrt"]
+        cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")     # NVTX v3 headers
+        inc = ["-I", cuda_inc] if os.path.isdir(cuda_inc) else []
+        cmd = [os.environ.get("CXX", "g++"), *CXX_FLAGS, "-I", str(CSRC), *inc, "-o", str(out), str(src), "-lrt", "-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"build failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")

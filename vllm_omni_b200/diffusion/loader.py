@@ -48,18 +48,30 @@ def _shard_files(folder: str) -> list[str]:
     return sorted(os.path.join(folder, f) for f in os.listdir(folder) if f.endswith(".safetensors"))
 
 
-def safetensors_weights_iterator(files: list[str], prefix: str = "", num_threads: int = 4) -> Iterator:
-    """Yields (prefix + name, tensor).  Shards are opened by a small thread pool so that disk
-    reads of the next shard overlap the copies of the current one."""
-    from ..utils.safetensors_reader import open_safetensors
+def safetensors_weights_iterator(files: list[str], prefix: str = "", num_threads: int = 8) -> Iterator:
+    """Yields (prefix + name, tensor).  Each shard is read by the C++ reader: its tensors are copied
+    out of the mapping by ``num_threads`` workers into one host buffer, which overlaps the page
+    faults of a cold file; the next shard is read while the current one is consumed.
+    ``OMNI_LOADER=mmap`` yields zero-copy views of the mapping instead (one page fault at a time)."""
+    from ..utils.safetensors_reader import NativeSafetensorsFile, open_safetensors
 
     def load(path):
-        return open_safetensors(path)
+        if os.environ.get("OMNI_LOADER", "native") != "mmap":
+            try:
+                f = NativeSafetensorsFile(path, threads=num_threads)
+                try:
+                    return f.read(pin=False)
+                finally:
+                    f.close()
+            except (OSError, RuntimeError) as e:          # library not buildable here: fall back
+                logger.warning("native safetensors reader unavailable (%s); using the mmap reader", e)
+        st = open_safetensors(path)
+        return {name: st.get_tensor(name) for name in st.keys()}
 
-    with ThreadPoolExecutor(max_workers=max(1, num_threads)) as ex:
-        for st in ex.map(load, files):
-            for name in st.keys():
-                yield prefix + name, st.get_tensor(name)
+    with ThreadPoolExecutor(max_workers=2) as ex:
+        for tensors in ex.map(load, files):
+            for name, t in tensors.items():
+                yield prefix + name, t
 
 
 class DiffusersPipelineLoader:

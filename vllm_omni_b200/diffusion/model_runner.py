@@ -6,6 +6,8 @@ import time
 
 import torch
 
+from ..utils.safetensors_reader import NvtxRange
+
 from ..logger import init_logger
 from .data import DiffusionOutput, OmniDiffusionConfig
 from .forward_context import set_forward_context
@@ -54,7 +56,7 @@ class DiffusionModelRunner:
         if self.cache_backend is not None:
             self.cache_backend.refresh(self.pipeline, sp.num_inference_steps)
         with set_forward_context(od_config=self.od_config, num_steps=sp.num_inference_steps):
-            with torch.profiler.record_function("pipeline_forward"):
+            with torch.profiler.record_function("pipeline_forward"), NvtxRange("pipeline_forward"):
                 try:
                     return self.pipeline.forward(req)
                 except Exception as e:   # surfaced to the engine as a typed error result

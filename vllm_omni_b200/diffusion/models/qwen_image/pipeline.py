@@ -23,6 +23,7 @@ from ....ops import fused
 from ...data import DiffusionOutput, OmniDiffusionConfig
 from ...request import OmniDiffusionRequest
 from ...schedulers.flow_match_euler import FlowMatchEulerDiscreteScheduler, calculate_shift
+from ....utils.safetensors_reader import NvtxRange
 from ..vae.autoencoder_kl_qwenimage import AutoencoderKLQwenImage2d, QwenImageVAEConfig
 from .transformer import QwenImageTransformer2DModel, QwenImageTransformerConfig
 
@@ -161,6 +162,7 @@ class QwenImagePipeline(nn.Module):
         if nb > B:
             lat_in[B:].copy_(lat_in[:B])
         for i in range(len(timesteps)):
+            nvtx = NvtxRange("denoise_step").__enter__()
             v = self.transformer.forward_step(st, i)
             dt = self.scheduler.dt(i)
             if cfg_par:
@@ -172,6 +174,7 @@ class QwenImagePipeline(nn.Module):
                 fused.cfg_euler_step_(v, None, latents, 1.0, dt, False, lat_in)
             if step_callback is not None:
                 step_callback(i, latents)
+            nvtx.__exit__(None, None, None)
         if sp is not None:
             parts = sp.group.all_gather(latents, dim=1)       # once per image, before the VAE
             full_latents.copy_(parts)
