@@ -91,3 +91,60 @@ def test_chunk_adapter_state_machine():
     assert cons.poll(req)
     assert req.prompt_token_ids == [5, 6, 7] and req.prompt_embeds.shape == (3, 4) and not req.expects_more_chunks
     assert not cons.poll(req)
+
+
+def test_fault_injection_connector_drives_the_error_paths():
+    """Scheduled host-side faults around a shared-memory connector: a dropped put is reported to the
+    sender, a corrupted payload trips the receiver's checksum, a lost payload makes the adapter time
+    out with a typed error, and an unfaulted transfer (with an injected delay) still arrives."""
+    from vllm_omni_b200.connectors.adapter import try_recv_via_connector, try_send_via_connector
+    c = OmniConnectorFactory.create({"name": "FaultInjectionConnector", "extra": {
+        "inner": {"name": "SharedMemoryConnector", "extra": {"shm_threshold_bytes": 64, "get_retries": 2,
+                                                             "get_retry_interval_s": 0.01}},
+        # one schedule entry per connector call: put a, put b, get b, put c, get c, put d, get d
+        "schedule": ["drop_put", "corrupt", None, None, None, None, "lose_get"], "delay_ms": 2}})
+    data = {"h": torch.arange(64, dtype=torch.float32), "note": "x"}
+    task = {}
+    assert not try_send_via_connector(c, 0, 1, "a", data, task) and "connector_meta" not in task       # drop_put
+    task = {}
+    assert try_send_via_connector(c, 0, 1, "b", data, task)                                            # corrupt
+    with pytest.raises(ValueError, match="checksum"):
+        try_recv_via_connector(c, task)
+    task = {}
+    t0 = time.perf_counter()
+    assert try_send_via_connector(c, 0, 1, "c", data, task)                                            # clean, delayed
+    got = try_recv_via_connector(c, task)
+    assert torch.equal(got["h"], data["h"]) and time.perf_counter() - t0 >= 0.004
+    task = {}
+    assert try_send_via_connector(c, 0, 1, "d", data, task)                                            # lost before the get
+    with pytest.raises(TimeoutError, match="never arrived"):
+        try_recv_via_connector(c, task)
+    assert [f for f, _ in c.injected] == ["drop_put", "corrupt", "lose_get"]
+    assert c.health()["injected_faults"] == 3
+    c.cleanup_all()
+
+
+def test_fault_rates_are_reproducible_and_kv_transfer_survives_drops():
+    mk = lambda: OmniConnectorFactory.create({"name": "FaultInjectionConnector", "extra": {
+        "inner": "InProcConnector", "rates": {"drop_put": 0.5}, "seed": 7}})
+    a, b = mk(), mk()
+    ra = [a.put(0, 1, f"k{i}", {"v": i})[0] for i in range(20)]
+    rb = [b.put(0, 1, f"k{i}", {"v": i})[0] for i in range(20)]
+    assert ra == rb and 3 < sum(ra) < 17
+    # the KV sender retries with back-off until a put gets through
+    conn = OmniConnectorFactory.create({"name": "FaultInjectionConnector", "extra": {
+        "inner": "InProcConnector", "schedule": ["drop_put", "drop_put", None]}})
+    send = OmniKVTransferManager.from_config({"stage_id": 0, "to_stages": [1], "need_send_cache": True,
+                                              "send_retries": 4, "send_backoff_s": 0.001}, conn)
+    req = Request("r1", [1, 2, 3], SamplingParams())
+    assert send.handle_finished_requests_kv_transfer([req], _Runner()) == ["r1"] and send.stats["sent"] == 1
+    assert [f for f, _ in conn.injected] == ["drop_put", "drop_put"]
+
+
+def test_talker_prompt_length_follows_the_chat_turns():
+    from vllm_omni_b200.connectors.adapter import compute_talker_prompt_ids_length as n
+    IM, SYS, USR, AST = 151644, 8948, 872, 77091
+    ids = [IM, SYS, 1, 2, 3, IM, USR, 4, 5, 6, 7, IM, AST, 8]
+    assert n(ids) == 6 + 9                         # the user turn's six tokens + the nine-row assistant head
+    assert n([IM, USR, 1, IM, AST, 2, 3, IM, USR, 4, 5, IM, AST, 6]) == 3 + 4 + 9      # the earlier assistant turn is dropped
+    assert n([1, 2, 3]) == 0

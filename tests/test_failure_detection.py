@@ -116,3 +116,56 @@ def test_dead_stage_fails_inflight_requests_and_is_restarted(tmp_path):
             eng.close()
 
     asyncio.run(run())
+
+
+FAULTY_EDGE_YAML = """
+async_chunk: false
+stage_args:
+  - stage_id: 0
+    stage_type: llm
+    runtime: {devices: "0", max_batch_size: 4}
+    engine_args: {model_stage: thinker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
+                  engine_output_type: latent, device: cpu, num_gpu_blocks: 64, max_num_batched_tokens: 64,
+                  model_overrides: {tiny: true}}
+    final_output: true
+    final_output_type: text
+    default_sampling_params: {temperature: 0.0, max_tokens: 4}
+  - stage_id: 1
+    stage_type: llm
+    runtime: {devices: "0", max_batch_size: 4, process: true}
+    engine_args: {model_stage: talker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
+                  engine_output_type: latent, device: cpu, num_gpu_blocks: 64, model_overrides: {tiny: true}}
+    engine_input_source: [0]
+    custom_process_input_func: vllm_omni_b200.models.stage_input_processors.qwen3_omni.thinker2talker
+    final_output: true
+    final_output_type: latent
+    default_sampling_params: {temperature: 0.0, max_tokens: 3, detokenize: false, stop_token_ids: [66]}
+runtime:
+  connectors:
+    flaky:
+      name: FaultInjectionConnector
+      extra:
+        inner: {name: SharedMemoryConnector, extra: {shm_threshold_bytes: 64, get_retries: 2, get_retry_interval_s: 0.01}}
+        schedule: [corrupt]
+  edges:
+    - {from: 0, to: 1, connector: flaky}
+"""
+
+
+def test_corrupted_stage_payload_fails_one_request_and_the_pipeline_keeps_serving(tmp_path):
+    """The thinker -> talker edge of a process-separated pipeline corrupts the first payload: that
+    request ends with a checksum error from the receiving stage, the next one goes through."""
+    from vllm_omni_b200.entrypoints.omni import Omni
+    y = tmp_path / "faulty_edge.yaml"
+    y.write_text(FAULTY_EDGE_YAML)
+    o = Omni("qwen3-omni-tiny", stage_configs_path=str(y))
+    try:
+        prompt = {"prompt_token_ids": [506, 509, 11, 12, 507, 506, 510, 13]}
+        from vllm_omni_b200.entrypoints.orchestrator import StageError
+        with pytest.raises(StageError, match="checksum"):
+            o.generate([prompt])
+        second = o.generate([prompt])
+        assert not [x.error for x in second if x.error]
+        assert any(x.stage_id == 1 for x in second)
+    finally:
+        o.close()

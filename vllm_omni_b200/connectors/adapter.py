@@ -44,18 +44,21 @@ def try_recv_via_connector(connector, task: dict, metrics=None):
     return data
 
 
-def compute_talker_prompt_ids_length(thinker_input_ids: list[int], thinker_output_len: int,
-                                     im_start_id: int = 151644, system_id: int = 8948) -> int:
-    """Length of the talker prompt for a thinker sequence: the talker consumes the assistant
-    turn (everything after the last ``<|im_start|>``) plus the generated tokens, with system
-    turns dropped (adapter.py:176)."""
-    starts = [i for i, t in enumerate(thinker_input_ids) if t == im_start_id]
-    keep = 0
-    for j, s in enumerate(starts):
-        e = starts[j + 1] if j + 1 < len(starts) else len(thinker_input_ids)
-        if s + 1 < len(thinker_input_ids) and thinker_input_ids[s + 1] == system_id:
+def compute_talker_prompt_ids_length(prompt_ids: list[int], im_start_id: int = 151644, system_id: int = 8948,
+                                     user_id: int = 872, assistant_id: int = 77091) -> int:
+    """Length of the talker prompt built from a thinker sequence (adapter.py:176-206): the sequence is
+    cut at every ``<|im_start|>``; system turns are dropped, every user turn contributes its tokens,
+    and the last assistant turn contributes nine rows (3 header tokens, 4 x tts-pad, tts-bos, the
+    first reply token).  Earlier assistant turns are dropped."""
+    starts = [i for i, t in enumerate(prompt_ids) if t == im_start_id] + [len(prompt_ids)]
+    user_len = assistant_len = 0
+    for j in range(len(starts) - 1):
+        s, e = starts[j], starts[j + 1]
+        role = prompt_ids[s + 1] if s + 1 < len(prompt_ids) else None
+        if role == system_id:
             continue
-        keep += e - s
-    if not starts:
-        keep = len(thinker_input_ids)
-    return keep + thinker_output_len
+        if role == user_id:
+            user_len += e - s
+        elif role == assistant_id and j == len(starts) - 2:
+            assistant_len += 9
+    return user_len + assistant_len

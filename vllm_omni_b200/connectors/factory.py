@@ -29,7 +29,9 @@ class OmniConnectorFactory:
             spec = ConnectorSpec(spec.get("name", "SharedMemoryConnector"), dict(spec.get("extra", {})))
         if spec.name not in cls._registry:
             raise ValueError(f"unknown connector {spec.name!r}; registered: {sorted(cls._registry)}")
-        return cls._registry[spec.name](spec.extra)
+        c = cls._registry[spec.name](spec.extra)
+        c.spec = {"name": spec.name, "extra": dict(spec.extra)}      # lets the receiving process open its own end
+        return c
 
 
 def _shm(cfg):
@@ -57,6 +59,12 @@ def _yuanrong(cfg):
     return YuanrongConnector(cfg)
 
 
+def _faulty(cfg):
+    from .fault_injection import FaultInjectingConnector
+    return FaultInjectingConnector(cfg)
+
+
+OmniConnectorFactory.register("FaultInjectionConnector", _faulty)
 OmniConnectorFactory.register("SharedMemoryConnector", _shm)
 OmniConnectorFactory.register("InProcConnector", _inproc)
 OmniConnectorFactory.register("DeviceConnector", _device)

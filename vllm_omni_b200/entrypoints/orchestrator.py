@@ -45,6 +45,10 @@ def send_downstream(omni, src_stage, dst_stage, request_id: str, prompt, samplin
     if connector is not None and not dst_stage.in_process:
         sent = try_send_via_connector(connector, src_stage.stage_id, dst_stage.stage_id, request_id, inputs, task,
                                       omni.metrics)
+        if sent:
+            # the receiving process opens its own end of the edge from this description
+            spec = getattr(connector, "spec", None)
+            task["connector_meta"]["spec"] = spec or {"name": type(connector).__name__, "extra": dict(connector.config)}
     if not sent:
         task["engine_inputs"] = inputs
     dst_stage.submit(task)

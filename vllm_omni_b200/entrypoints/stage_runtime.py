@@ -199,6 +199,26 @@ def inproc_adapter(stage_id: int) -> StageEngineAdapter:
     return _INPROC_ADAPTERS[stage_id]
 
 
+def _resolve_payload(task: dict, cache: dict) -> None:
+    """Pull ``task['engine_inputs']`` through the edge connector when the orchestrator sent only a
+    descriptor (process-separated stages).  Raises on a missing or corrupted payload; the worker turns
+    that into an error result for this request."""
+    cm = task.get("connector_meta")
+    if cm is None or "engine_inputs" in task:
+        return
+    from ..connectors.adapter import try_recv_via_connector
+    from ..connectors.factory import OmniConnectorFactory
+    edge = (cm["from_stage"], cm["to_stage"])
+    if edge not in cache:
+        spec = cm.get("spec") or {"name": "SharedMemoryConnector"}
+        if spec.get("name") == "FaultInjectionConnector":
+            # faults are injected where the payload is produced; this end only has to read it
+            spec = (spec.get("extra") or {}).get("inner") or {"name": "SharedMemoryConnector"}
+            spec = {"name": spec} if isinstance(spec, str) else spec
+        cache[edge] = OmniConnectorFactory.create(spec)
+    try_recv_via_connector(cache[edge], task)
+
+
 # ========================================================================= worker loop
 def _stage_worker(cfg: StageConfig, model: str, in_q, out_q, batch_timeout_s: float, in_process: bool):
     """Body of a stage (thread or process)."""
@@ -217,6 +237,7 @@ def _stage_worker(cfg: StageConfig, model: str, in_q, out_q, batch_timeout_s: fl
     out_q.put({"type": "stage_ready", "stage_id": sid})
     paused = False
     held: list[dict] = []
+    edge_connectors: dict = {}          # (from_stage, to_stage) -> this process's end of the edge connector
     while True:
         idle = not adapter.has_work()
         try:
@@ -237,6 +258,7 @@ def _stage_worker(cfg: StageConfig, model: str, in_q, out_q, batch_timeout_s: fl
                     held.append(task)
                 else:
                     try:
+                        _resolve_payload(task, edge_connectors)
                         adapter.add_task(task)
                     except Exception as e:
                         out_q.put({"request_id": task.get("request_id"), "stage_id": sid,
