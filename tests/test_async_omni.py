@@ -12,8 +12,8 @@ from test_qwen3_omni_pipeline import YAML, _prompt
 def _engine(tmp_path, async_chunk=False, talker_tokens=7):
     y = YAML.replace("async_chunk: false", f"async_chunk: {'true' if async_chunk else 'false'}")
     y = y.replace("max_tokens: 7", f"max_tokens: {talker_tokens}")
-    if async_chunk:      # random weights may emit the stop code early; this test wants a long utterance
-        y = y.replace("stop_token_ids: [66]", "stop_token_ids: [], ignore_eos: true")
+    # random weights may emit the stop code early; these tests want the whole utterance
+    y = y.replace("stop_token_ids: [66]", "stop_token_ids: [], ignore_eos: true")
     p = tmp_path / "cfg.yaml"
     p.write_text(y)
     return AsyncOmni("qwen3-omni-tiny", stage_configs_path=str(p))

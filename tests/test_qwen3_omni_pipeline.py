@@ -58,6 +58,7 @@ def _prompt(n_audio_frames=40):
 
 def test_three_stage_text_and_audio(omni):
     sps = [s.default_sampling_params() for s in omni.stage_list]
+    sps[1].stop_token_ids, sps[1].ignore_eos = [], True     # random weights may pick the stop code first: speak all 7 frames
     outs = omni.generate([_prompt(), _prompt(24)], sps)
     by_type = {}
     for o in outs:
@@ -168,3 +169,23 @@ def test_talker_prompt_follows_chatml_turns():
     trailing = req.runtime_state["text_steps"]
     assert torch.allclose(trailing, torch.cat([tp(emb[14:16]), eos]), atol=1e-6)
     assert tk.speaker_token("nobody") == cfg.speaker_ids["ethan"]        # unknown voice -> the first listed voice
+
+
+def test_every_stage_in_its_own_process_matches_the_in_process_pipeline(omni, tmp_path):
+    """``runtime.process: true`` on all three stages: payloads cross the edges through shared-memory
+    connectors, and text tokens and waveform equal the single-process run."""
+    y = tmp_path / "procs.yaml"
+    y.write_text(YAML.replace("max_batch_size: 4}", "max_batch_size: 4, process: true}"))
+    sps = [s.default_sampling_params() for s in omni.stage_list]
+    sps[1].stop_token_ids, sps[1].ignore_eos = [], True
+    ref = omni.generate([_prompt(40)], sps)
+    o = Omni("qwen3-omni-tiny", stage_configs_path=str(y))
+    try:
+        assert all(not s.in_process for s in o.stage_list)
+        out = o.generate([_prompt(40)], sps)
+    finally:
+        o.close()
+    pick = lambda outs, kind: [x for x in outs if x.final_output_type == kind][0]
+    assert list(pick(out, "text").request_output.outputs[0].token_ids) == list(pick(ref, "text").request_output.outputs[0].token_ids)
+    a, b = pick(out, "audio").multimodal_output["audio"], pick(ref, "audio").multimodal_output["audio"]
+    assert a.shape == b.shape and torch.allclose(a, b, atol=1e-6)

@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import json
 import os
+import threading
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -19,6 +20,7 @@ from ..logger import init_logger
 from ..models.registry import build_stage_model
 
 logger = init_logger(__name__)
+_BUILD_LOCK = threading.Lock()
 
 
 @dataclass
@@ -81,8 +83,11 @@ class OmniLLM:
             with open(os.path.join(model, "config.json")) as f:
                 hf_cfg = json.load(f)
         arch = a.model_arch or (hf_cfg.get("architectures") or ["Qwen3ForCausalLM"])[0]
-        torch.manual_seed(a.seed + 1000 * stage_id)
-        self.model = build_stage_model(arch, a.model_stage, hf_cfg, dtype, device, **a.model_overrides)
+        # stages that share a process are built on a thread pool and share torch's global generator:
+        # seeding and random initialisation must not interleave, or the weights depend on thread timing
+        with _BUILD_LOCK:
+            torch.manual_seed(a.seed + 1000 * stage_id)
+            self.model = build_stage_model(arch, a.model_stage, hf_cfg, dtype, device, **a.model_overrides)
         if model and os.path.isdir(model) and a.load_format not in ("dummy",):
             from ..diffusion.loader import _shard_files, safetensors_weights_iterator
             files = _shard_files(model)
