@@ -315,3 +315,81 @@ def test_z_image_caption_encoder_takes_second_to_last_layer():
             ref = hf(input_ids=ids, output_hidden_states=True).hidden_states[-2][0]
         n = ids.shape[1]
         assert int(mask[i].sum()) == n and (states[i, :n] - ref).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("grid", [(1, 8, 12), (2, 6, 10), (1, 4, 4)])
+def test_qwen2_5_vl_vision_tower_against_hf(grid):
+    """Window attention (ragged windows at the right / bottom edge), full-attention blocks, 2-D rotary
+    embedding, window re-ordering and its inverse, SwiGLU blocks, patch merger."""
+    from vllm_omni_b200.models.qwen2_5_vl_vision import Qwen25VisionConfig, Qwen25VisionTower
+    torch.manual_seed(0)
+    hc = transformers.Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=64, hidden_size=64, intermediate_size=96, num_hidden_layers=1, num_attention_heads=4,
+                         num_key_value_heads=2),
+        vision_config=dict(depth=3, hidden_size=32, intermediate_size=48, num_heads=2, out_hidden_size=64, patch_size=4,
+                           window_size=24, fullatt_block_indexes=[1]))
+    hf = _init_all(transformers.Qwen2_5_VLForConditionalGeneration(hc)).model.visual
+    tower = Qwen25VisionTower(Qwen25VisionConfig.from_dict(hc.vision_config.to_dict()), torch.float32, "cpu")
+    sd = hf.state_dict()
+    assert tower.load_weights(sd.items()) == set(sd)
+    gt, gh, gw = grid
+    patches = torch.randn(gt * gh * gw, 3 * 2 * 4 * 4)
+    with torch.no_grad():
+        ref = hf(patches, grid_thw=torch.tensor([[gt, gh, gw]])).pooler_output
+        out, g = tower.forward_patches(patches, grid)
+    assert g == (gt, gh // 2, gw // 2) and out.shape == ref.shape
+    assert (out - ref).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())
+
+
+class _SlotTokenizer:
+    """Bytes as ids, plus single ids for the three vision markers."""
+    MARK = {"<|vision_start|>": 290, "<|image_pad|>": 291, "<|vision_end|>": 292}
+
+    def encode(self, text, add_special_tokens=False):
+        import re
+        out = []
+        for part in re.split("(" + "|".join(re.escape(k) for k in self.MARK) + ")", text):
+            out.extend([self.MARK[part]] if part in self.MARK else list(part.encode()))
+        return out
+
+
+def test_qwen_image_edit_prompt_encoder_with_an_image_against_hf():
+    """Instruction + condition image through the vision tower and the language model with (t, h, w)
+    rotary positions: the states behind the template head equal the HF model's."""
+    from vllm_omni_b200.diffusion.models.qwen_image.text_encoder import QwenVLTextEncoder, text_config_from_hf
+    from vllm_omni_b200.models.qwen2_5_vl_vision import Qwen25VisionConfig
+    torch.manual_seed(0)
+    hc = transformers.Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=2048,
+                         rope_parameters=dict(rope_theta=1e6, rope_type="default", mrope_section=[2, 3, 3])),
+        vision_config=dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, out_hidden_size=64, patch_size=4,
+                           window_size=16, fullatt_block_indexes=[1]),
+        image_token_id=291, vision_start_token_id=290, vision_end_token_id=292, video_token_id=293)
+    hf = _init_all(transformers.Qwen2_5_VLForConditionalGeneration(hc))
+    enc = QwenVLTextEncoder(text_config_from_hf(hc.to_dict()), _SlotTokenizer(), torch.float32, "cpu",
+                            vision_config=Qwen25VisionConfig.from_dict(hc.vision_config.to_dict()), image_token_id=291)
+    assert enc.cfg.mrope_section == (2, 3, 3)
+    sd = hf.state_dict()
+    assert enc.load_weights(sd.items()) == {k for k in sd if not k.startswith("lm_head")}
+    grid = (1, 6, 4)                                            # 24 patches -> 6 merged tokens
+    patches = torch.randn(24, 3 * 2 * 4 * 4)
+    template, drop = "<|im_start|>user\n{}<|im_end|>\n<|im_start|>assistant\n", 5
+    states, mask = enc.encode_with_images(["make it blue"], [[]], template=template, drop_tokens=drop,
+                                          patches=[[(patches, grid)]])
+    tok = _SlotTokenizer()
+    ids = tok.encode(template.format("<|vision_start|><|image_pad|><|vision_end|>make it blue"))
+    i = ids.index(291)
+    ids = ids[:i] + [291] * 6 + ids[i + 1:]
+    inp = torch.tensor([ids])
+    with torch.no_grad():
+        # positions: (t, h, w) of the original Qwen2.5-VL rule (an image keeps t = its start index), the one
+        # the Qwen3-Omni test checks against ``get_rope_index``; this release's Qwen2.5-VL helper scales t
+        from vllm_omni_b200.models.mrope import get_input_positions
+        pos, _ = get_input_positions(ids, 291, -1, -2, [(1, 3, 2)], [])
+        ref = hf(input_ids=inp, attention_mask=torch.ones_like(inp), pixel_values=patches,
+                 image_grid_thw=torch.tensor([list(grid)]), position_ids=pos[:, None],
+                 output_hidden_states=True).hidden_states[-1][0]
+    n = len(ids) - drop
+    assert states.shape == (1, n, 64) and int(mask.sum()) == n
+    assert (states[0] - ref[drop:]).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())

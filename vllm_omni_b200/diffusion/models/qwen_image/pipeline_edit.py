@@ -20,12 +20,47 @@ from .pipeline import QwenImagePipeline, pack_latents, unpack_latents
 
 class QwenImageEditPipeline(QwenImagePipeline):
     max_condition_images = 1
+    vl_image_area = 1024 * 1024        # the condition image is shown to the prompt encoder at about this many pixels
+    picture_prefix = False             # Edit-Plus numbers its images: "Picture 1: <image>Picture 2: <image>..."
 
     def __init__(self, od_config=None, transformer_config=None, vae_config=None, device=None, **kw):
         super().__init__(od_config, transformer_config, vae_config, device)
         enc = AutoencoderKLQwenImage2d(self.vae.cfg, with_encoder=True)
         self.vae.encoder = enc.encoder.to(self.device_, self.od_config.dtype)
         self.vae.quant_conv = enc.quant_conv.to(self.device_, self.od_config.dtype)
+
+    def attach_text_encoder(self, model_path: str) -> bool:
+        """Edit pipelines need the vision tower of the Qwen2.5-VL prompt encoder as well."""
+        import os
+        if not (os.path.isfile(os.path.join(model_path, "text_encoder", "config.json")) and
+                os.path.isdir(os.path.join(model_path, "tokenizer"))):
+            return False
+        from .text_encoder import QwenVLTextEncoder
+        self.text_encoder = QwenVLTextEncoder.from_pretrained(model_path, self.od_config.dtype, self.device_, with_vision=True)
+        return True
+
+    def encode_edit_prompt(self, texts, images, max_sequence_length=None):
+        """Instruction + condition images through the vision-language prompt encoder; the stand-in
+        encoder of random-weight runs sees the text only."""
+        enc = self.text_encoder
+        if getattr(enc, "visual", None) is None or not any(images):
+            return self.encode_prompt(texts, max_sequence_length=max_sequence_length)
+        from .text_encoder import IMAGE_SLOT
+        import math
+        import torch.nn.functional as F
+        shown, prompts = [], []
+        for text, ims in zip(texts, images):
+            row = []
+            for im in ims:
+                r = im.shape[-1] / im.shape[-2]
+                W = round(math.sqrt(self.vl_image_area * r) / 32) * 32
+                H = round(W / r / 32) * 32
+                row.append(F.interpolate(im[None].float(), size=(max(32, H), max(32, W)), mode="bicubic", align_corners=False,
+                                         antialias=True)[0].clamp(0, 1))
+            shown.append(row)
+            slots = "".join((f"Picture {i + 1}: " if self.picture_prefix else "") + IMAGE_SLOT for i in range(len(row)))
+            prompts.append(slots + text)
+        return enc.encode_with_images(prompts, shown, self.device_, self.od_config.dtype, max_sequence_length=max_sequence_length)
 
     def _condition_latents(self, prompt, h, w):
         mm = (prompt.get("multi_modal_data") or {}) if isinstance(prompt, dict) else {}
@@ -51,11 +86,13 @@ class QwenImageEditPipeline(QwenImagePipeline):
             return super().forward(req)
         text = p.get("prompt", "") if isinstance(p, dict) else p
         neg = p.get("negative_prompt") if isinstance(p, dict) else None
-        pe, pm = self.encode_prompt([text], max_sequence_length=sp.max_sequence_length)
+        mm = (p.get("multi_modal_data") or {}) if isinstance(p, dict) else {}
+        shown = [list((mm.get("image_tensor") or [])[: self.max_condition_images])]
+        pe, pm = self.encode_edit_prompt([text], shown, sp.max_sequence_length)
         true_cfg = sp.true_cfg_scale if sp.true_cfg_scale is not None else (sp.guidance_scale or 1.0)
         do_cfg = true_cfg > 1 and neg is not None
         if do_cfg:
-            ne, nm = self.encode_prompt([neg])
+            ne, nm = self.encode_edit_prompt([neg], shown, sp.max_sequence_length)
             L = max(pe.shape[1], ne.shape[1])
             enc = torch.zeros(2, L, pe.shape[2], dtype=pe.dtype, device=pe.device)
             enc[0, :pe.shape[1]], enc[1, :ne.shape[1]] = pe[0], ne[0]
@@ -86,6 +123,8 @@ class QwenImageEditPipeline(QwenImagePipeline):
 
 class QwenImageEditPlusPipeline(QwenImageEditPipeline):
     max_condition_images = 3
+    vl_image_area = 384 * 384
+    picture_prefix = True
 
 
 class QwenImageLayeredPipeline(QwenImageEditPipeline):

@@ -4,7 +4,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-from ..qwen3_omni.config import AudioEncoderConfig, VisionEncoderConfig
+from ..qwen2_5_vl_vision import Qwen25VisionConfig
+from ..qwen3_omni.config import AudioEncoderConfig
 from ..qwen_decoder import DecoderConfig
 
 
@@ -58,7 +59,7 @@ class Qwen25OmniConfig:
         head_dim=128, intermediate_size=18944, qk_norm=False, attention_bias=True, rope_theta=1e6,
         mrope_section=(16, 24, 24)))
     audio: AudioEncoderConfig = field(default_factory=lambda: AudioEncoderConfig(output_dim=3584))
-    vision: VisionEncoderConfig = field(default_factory=lambda: VisionEncoderConfig(out_hidden_size=3584))
+    vision: Qwen25VisionConfig = field(default_factory=Qwen25VisionConfig)
     dit: DiTConfig = field(default_factory=DiTConfig)
     bigvgan: BigVGANConfig = field(default_factory=BigVGANConfig)
     audio_token_id: int = 151646
@@ -80,8 +81,9 @@ class Qwen25OmniConfig:
         return cls(thinker=th, talker=tk,
                    audio=AudioEncoderConfig(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=2,
                                             encoder_ffn_dim=64, downsample_hidden_size=8, output_dim=64, n_window=8),
-                   vision=VisionEncoderConfig(depth=1, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=4,
-                                              temporal_patch_size=1, spatial_merge_size=2, out_hidden_size=64),
+                   vision=Qwen25VisionConfig(depth=2, hidden_size=32, num_heads=2, intermediate_size=48, patch_size=4,
+                                             temporal_patch_size=1, spatial_merge_size=2, out_hidden_size=64,
+                                             window_size=16, fullatt_block_indexes=(1,)),
                    dit=DiTConfig(hidden_size=32, num_hidden_layers=2, num_attention_heads=2, head_dim=16, mel_dim=8,
                                  num_embeds=97, emb_dim=16, block_size=4, speaker_dim=8, num_steps=3),
                    bigvgan=BigVGANConfig(mel_dim=8, upsample_initial_channel=16, upsample_rates=(2, 2),
@@ -96,6 +98,8 @@ class Qwen25OmniConfig:
         th = d.get("thinker_config", {})
         if th.get("text_config"):
             c.thinker = DecoderConfig.from_dict({**th["text_config"], "qk_norm": False, "attention_bias": True})
+        if th.get("vision_config"):
+            c.vision = Qwen25VisionConfig.from_dict(th["vision_config"])
         tk = d.get("talker_config", {})
         if tk:
             c.talker = DecoderConfig.from_dict({**tk, "qk_norm": False, "attention_bias": True})

@@ -7,7 +7,8 @@ import torch
 
 from ..qwen3_omni.thinker import Qwen3OmniMoeThinker
 from ..qwen_decoder import QwenDecoderModel
-from ..qwen3_omni.encoders import AudioEncoder, VisionEncoder
+from ..qwen2_5_vl_vision import Qwen25VisionTower
+from ..qwen3_omni.encoders import AudioEncoder
 from ..base import StageModel
 from .config import Qwen25OmniConfig
 
@@ -22,7 +23,7 @@ class Qwen25OmniThinker(Qwen3OmniMoeThinker):
         self.cfg = cfg
         self.decoder = QwenDecoderModel(cfg.thinker, dtype, device)
         self.audio_tower = AudioEncoder(cfg.audio, dtype, device)
-        self.visual = VisionEncoder(cfg.vision, dtype, device)
+        self.visual = Qwen25VisionTower(cfg.vision, dtype, device)      # window-attention ViT of Qwen2.5-VL
         self.capture = ()
 
     def forward_batch(self, batch, kv_caches, sched):
