@@ -393,3 +393,56 @@ def test_qwen_image_edit_prompt_encoder_with_an_image_against_hf():
     n = len(ids) - drop
     assert states.shape == (1, n, 64) and int(mask.sum()) == n
     assert (states[0] - ref[drop:]).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())
+
+
+def test_qwen2_5_omni_audio_tower_against_hf():
+    M = pytest.importorskip("transformers.models.qwen2_5_omni.modeling_qwen2_5_omni")
+    from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import Qwen2_5OmniAudioEncoderConfig
+    from vllm_omni_b200.models.qwen2_5_omni.audio import Qwen25AudioConfig, Qwen25AudioEncoder
+    torch.manual_seed(0)
+    ac = Qwen2_5OmniAudioEncoderConfig(num_mel_bins=16, d_model=32, encoder_layers=2, encoder_attention_heads=2,
+                                       encoder_ffn_dim=64, output_dim=24, n_window=10, max_source_positions=64)
+    hf = _init_all(M.Qwen2_5OmniAudioEncoder(ac))
+    enc = Qwen25AudioEncoder(Qwen25AudioConfig.from_dict(ac.to_dict()), torch.float32, "cpu")
+    sd = hf.state_dict()
+    assert enc.load_weights(sd.items()) == set(sd)
+    for T in (53, 20, 7, 40):              # chunks of 20 frames: ragged tail, one chunk, short chunk, exact
+        mel = torch.randn(16, T)
+        full, tail = divmod(T, 20)
+        after = full * 10 + ((tail - 1) // 2 + 1 if tail else 0)
+        with torch.no_grad():
+            ref = hf(mel, feature_lens=torch.tensor([T]), aftercnn_lens=torch.tensor([after])).last_hidden_state
+            out = enc(mel)
+        assert out.shape == ref.shape and out.shape[0] == enc.output_length(T), T
+        assert (ref - out).abs().max().item() < 1e-5, T
+
+
+def test_qwen2_5_omni_talker_against_hf():
+    """Codec embedding table in the thinker width, ``thinker_to_talker_proj``, dense Qwen2 decoder with
+    MRoPE, codec head — loaded from the ``talker.*`` names."""
+    M = pytest.importorskip("transformers.models.qwen2_5_omni.modeling_qwen2_5_omni")
+    from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import Qwen2_5OmniTalkerConfig
+    from vllm_omni_b200.models.qwen2_5_omni.config import Qwen25OmniConfig
+    from vllm_omni_b200.models.qwen2_5_omni.talker import Qwen25OmniTalker
+    torch.manual_seed(0)
+    tc = Qwen2_5OmniTalkerConfig(vocab_size=96, embedding_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                                 num_attention_heads=2, num_key_value_heads=2, head_dim=16, max_position_embeddings=256,
+                                 rope_parameters=dict(rope_theta=1e6, rope_type="default", mrope_section=[2, 3, 3]),
+                                 tts_codec_start_token_id=93, tts_codec_end_token_id=94, tts_codec_pad_token_id=92)
+    hf = _init_all(M.Qwen2_5OmniTalkerForConditionalGeneration(tc))
+    cfg = Qwen25OmniConfig.from_hf({"talker_config": tc.to_dict(), "thinker_config": {}})
+    assert cfg.talker_embedding_size == 64 and cfg.talker.mrope_section == (2, 3, 3) and cfg.codec_bos_id == 93
+    tk = Qwen25OmniTalker(cfg, torch.float32, "cpu")
+    sd = {"talker." + k: v for k, v in hf.state_dict().items()}
+    assert tk.load_weights(sd.items()) == set(sd)
+    T = 9
+    x = torch.randn(T, 64)
+    pos = torch.stack([torch.arange(T), torch.arange(T) // 2, torch.arange(T) // 3])
+    with torch.no_grad():
+        ref = hf(inputs_embeds=x[None].clone(), position_ids=pos[:, None]).logits[0]
+        b = ModelBatch(torch.zeros(T, dtype=torch.long), pos, torch.full((T,), -1, dtype=torch.int32),
+                       [PrefillSeg(0, T, 0, None)], input_embeds=tk.thinker_to_talker_proj(x))
+        h, _ = tk.decoder(b, None)
+        out = tk.codec_head(h)
+    assert (out - ref).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())
+    assert torch.isinf(tk.compute_logits(h)[:, 93]).all()            # the start marker cannot be sampled

@@ -5,7 +5,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 from ..qwen2_5_vl_vision import Qwen25VisionConfig
-from ..qwen3_omni.config import AudioEncoderConfig
+from .audio import Qwen25AudioConfig
 from ..qwen_decoder import DecoderConfig
 
 
@@ -58,7 +58,8 @@ class Qwen25OmniConfig:
         vocab_size=8448, hidden_size=896, num_hidden_layers=24, num_attention_heads=12, num_key_value_heads=4,
         head_dim=128, intermediate_size=18944, qk_norm=False, attention_bias=True, rope_theta=1e6,
         mrope_section=(16, 24, 24)))
-    audio: AudioEncoderConfig = field(default_factory=lambda: AudioEncoderConfig(output_dim=3584))
+    audio: Qwen25AudioConfig = field(default_factory=Qwen25AudioConfig)
+    talker_embedding_size: int = 3584     # width of the talker's codec embedding table (= thinker width)
     vision: Qwen25VisionConfig = field(default_factory=Qwen25VisionConfig)
     dit: DiTConfig = field(default_factory=DiTConfig)
     bigvgan: BigVGANConfig = field(default_factory=BigVGANConfig)
@@ -69,6 +70,9 @@ class Qwen25OmniConfig:
     codec_pad_id: int = 8292
     codec_bos_id: int = 8293
     codec_eos_id: int = 8294
+    tts_text_bos_id: int = 151860       # thinker-vocabulary tokens whose embeddings frame the spoken text
+    tts_text_eos_id: int = 151861
+    tts_text_pad_id: int = 151859
 
     @classmethod
     def tiny(cls) -> "Qwen25OmniConfig":
@@ -79,8 +83,9 @@ class Qwen25OmniConfig:
                            num_key_value_heads=2, head_dim=16, intermediate_size=64, qk_norm=False,
                            attention_bias=True, mrope_section=(4, 2, 2))
         return cls(thinker=th, talker=tk,
-                   audio=AudioEncoderConfig(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=2,
-                                            encoder_ffn_dim=64, downsample_hidden_size=8, output_dim=64, n_window=8),
+                   audio=Qwen25AudioConfig(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=2,
+                                           encoder_ffn_dim=64, output_dim=64, n_window=8),
+                   talker_embedding_size=64,
                    vision=Qwen25VisionConfig(depth=2, hidden_size=32, num_heads=2, intermediate_size=48, patch_size=4,
                                              temporal_patch_size=1, spatial_merge_size=2, out_hidden_size=64,
                                              window_size=16, fullatt_block_indexes=(1,)),
@@ -90,7 +95,8 @@ class Qwen25OmniConfig:
                                          upsample_kernel_sizes=(4, 4), resblock_kernel_sizes=(3,),
                                          resblock_dilation_sizes=((1, 3),)),
                    audio_token_id=500, image_token_id=501, video_token_id=502, im_end_token_id=507,
-                   codec_pad_id=92, codec_bos_id=93, codec_eos_id=94)
+                   codec_pad_id=92, codec_bos_id=93, codec_eos_id=94, tts_text_bos_id=503, tts_text_eos_id=504,
+                   tts_text_pad_id=505)
 
     @classmethod
     def from_hf(cls, d: dict) -> "Qwen25OmniConfig":
@@ -98,17 +104,21 @@ class Qwen25OmniConfig:
         th = d.get("thinker_config", {})
         if th.get("text_config"):
             c.thinker = DecoderConfig.from_dict({**th["text_config"], "qk_norm": False, "attention_bias": True})
+        if th.get("audio_config"):
+            c.audio = Qwen25AudioConfig.from_dict(th["audio_config"])
         if th.get("vision_config"):
             c.vision = Qwen25VisionConfig.from_dict(th["vision_config"])
         tk = d.get("talker_config", {})
         if tk:
             c.talker = DecoderConfig.from_dict({**tk, "qk_norm": False, "attention_bias": True})
+            c.talker_embedding_size = int(tk.get("embedding_size", c.thinker.hidden_size))
         for k, src in (("audio_token_id", "audio_token_index"), ("image_token_id", "image_token_index"),
                        ("video_token_id", "video_token_index")):
             if src in th:
                 setattr(c, k, th[src])
         for k, src in (("codec_pad_id", "tts_codec_pad_token_id"), ("codec_bos_id", "tts_codec_start_token_id"),
-                       ("codec_eos_id", "tts_codec_end_token_id")):
+                       ("codec_eos_id", "tts_codec_end_token_id"), ("tts_text_bos_id", "tts_text_start_token_id"),
+                       ("tts_text_eos_id", "tts_text_end_token_id"), ("tts_text_pad_id", "tts_text_pad_token_id")):
             if src in tk:
                 setattr(c, k, tk[src])
         return c

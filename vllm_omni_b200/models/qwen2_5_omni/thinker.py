@@ -8,7 +8,7 @@ import torch
 from ..qwen3_omni.thinker import Qwen3OmniMoeThinker
 from ..qwen_decoder import QwenDecoderModel
 from ..qwen2_5_vl_vision import Qwen25VisionTower
-from ..qwen3_omni.encoders import AudioEncoder
+from .audio import Qwen25AudioEncoder
 from ..base import StageModel
 from .config import Qwen25OmniConfig
 
@@ -22,16 +22,29 @@ class Qwen25OmniThinker(Qwen3OmniMoeThinker):
         StageModel.__init__(self, cfg.thinker, dtype, device)
         self.cfg = cfg
         self.decoder = QwenDecoderModel(cfg.thinker, dtype, device)
-        self.audio_tower = AudioEncoder(cfg.audio, dtype, device)
+        self.audio_tower = Qwen25AudioEncoder(cfg.audio, dtype, device)
         self.visual = Qwen25VisionTower(cfg.vision, dtype, device)      # window-attention ViT of Qwen2.5-VL
-        self.capture = ()
+        self.capture = (0,)
 
     def forward_batch(self, batch, kv_caches, sched):
-        return self.decoder(batch, kv_caches)
+        return self.decoder(batch, kv_caches, capture_layers=self.capture)
 
     def collect_outputs(self, sched, batch, hidden, captured) -> None:
+        """Per token the talker gets (final hidden state + input embedding); the embeddings of audio /
+        image / video placeholder rows count as zero (transformers' Qwen2.5-Omni ``generate``)."""
+        cfg = self.cfg
+        emb = captured[0]
+        ids = batch.input_ids
+        mm = (ids == cfg.audio_token_id) | (ids == cfg.image_token_id) | (ids == cfg.video_token_id)
+        state = hidden + torch.where(mm[:, None], torch.zeros_like(emb), emb)
         row = 0
         for s in sched.scheduled:
             n = s.num_new_tokens
-            s.request.multimodal_outputs.setdefault("latent", []).append(hidden[row:row + n])
+            r = s.request
+            r.multimodal_outputs.setdefault("latent", []).append(state[row:row + n])
+            if "tts_bos_embed" not in r.multimodal_outputs:
+                e = self.decoder.embed_tokens
+                for key, tid in (("tts_bos_embed", cfg.tts_text_bos_id), ("tts_eos_embed", cfg.tts_text_eos_id),
+                                 ("tts_pad_embed", cfg.tts_text_pad_id)):
+                    r.multimodal_outputs[key] = [e[tid % e.shape[0]][None]]
             row += n

@@ -25,9 +25,11 @@ def thinker2talker(stage_list, engine_input_source, prompt=None, requires_multim
         o = ro.outputs[0]
         latent = o.multimodal_output["latent"].detach()
         n_in = len(ro.prompt_token_ids)
+        mmo = o.multimodal_output
         info = {
             "thinker_result": latent[n_in:],
             "prompt_embeds": latent[:n_in],
+            **{k: mmo[k].detach() for k in ("tts_bos_embed", "tts_eos_embed", "tts_pad_embed") if k in mmo},
             "prompt_token_ids": list(ro.prompt_token_ids),
             "thinker_output_token_ids": list(o.token_ids),
         }
