@@ -446,3 +446,52 @@ def test_qwen2_5_omni_talker_against_hf():
         out = tk.codec_head(h)
     assert (out - ref).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())
     assert torch.isinf(tk.compute_logits(h)[:, 93]).all()            # the start marker cannot be sampled
+
+
+def test_qwen2_5_omni_token2wav_against_hf():
+    """DiT (ECAPA speaker encoder, first-head rotary, block-local attention, guided velocity), the
+    sampled mel spectrogram and the BigVGAN waveform, from the ``token2wav.*`` names."""
+    M = pytest.importorskip("transformers.models.qwen2_5_omni.modeling_qwen2_5_omni")
+    from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import (Qwen2_5OmniBigVGANConfig, Qwen2_5OmniDiTConfig,
+                                                                            Qwen2_5OmniToken2WavConfig)
+    from vllm_omni_b200.models.qwen2_5_omni.config import Qwen25OmniConfig
+    from vllm_omni_b200.models.qwen2_5_omni.token2wav import Qwen25OmniToken2Wav
+    torch.manual_seed(0)
+    dc = dict(hidden_size=32, num_hidden_layers=3, num_attention_heads=2, ff_mult=2, emb_dim=16, head_dim=16, block_size=4,
+              look_ahead_layers=[1], look_backward_layers=[0, 2], repeats=2, num_embeds=97, mel_dim=8, dropout=0.0,
+              enc_emb_dim=8, enc_dim=8, enc_channels=[8, 8, 8, 8, 24], enc_kernel_sizes=[5, 3, 3, 3, 1], enc_dilations=[1, 2, 3, 4, 1],
+              enc_attention_channels=4, enc_res2net_scale=2, enc_se_channels=4, max_position_embeddings=512)
+    bc = dict(mel_dim=8, upsample_initial_channel=16, resblock_kernel_sizes=[3, 5], resblock_dilation_sizes=[[1, 3, 5], [1, 3, 5]],
+              upsample_rates=[2, 2], upsample_kernel_sizes=[4, 4])
+    hc = Qwen2_5OmniToken2WavConfig(dit_config=dc, bigvgan_config=bc)
+    hf = M.Qwen2_5OmniToken2WavModel(hc)
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, 0, 0.15 if p.dim() > 1 else 0.05)
+    hf = hf.float().eval()
+    cfg = Qwen25OmniConfig.from_hf({"token2wav_config": hc.to_dict(), "thinker_config": {}})
+    assert cfg.dit.look_backward_layers == (0, 2) and cfg.bigvgan.resblock_dilation_sizes == ((1, 3, 5), (1, 3, 5))
+    m = Qwen25OmniToken2Wav(cfg, torch.float32, "cpu")
+    sd = {"token2wav." + k: v for k, v in hf.state_dict().items()}
+    assert m.load_weights(sd.items()) == set(sd)
+    B, Tc = 1, 10
+    codes = torch.randint(1, 90, (B, Tc))
+    xvec, ref = torch.randn(B, 8), torch.randn(B, 11, 8)
+    x = torch.randn(B, 2 * Tc, 8)
+    xv = xvec.unsqueeze(1).repeat(1, 2 * Tc, 1)
+    with torch.no_grad():
+        a = hf.code2wav_dit_model(hidden_states=x, condition_vector=ref, speaker_embedding=xv, quantized_code=codes,
+                                  time_step=torch.tensor(0.37), apply_cfg=True)
+        b = m.dit(x, ref, xv, codes, torch.tensor(0.37), apply_cfg=True)
+        assert a.shape == b.shape == (2, 2 * Tc, 8) and (a - b).abs().max().item() < 1e-4 * max(1.0, a.abs().max().item())
+        # the whole sampler from the same noise
+        torch.manual_seed(5)
+        mel_ref = hf.code2wav_dit_model.sample(xvec, ref, codes, num_steps=4, guidance_scale=0.5, sway_coefficient=-1.0)
+        torch.manual_seed(5)
+        noise = torch.randn(B, 2 * Tc, 8)
+        mel = m.dit.sample(codes, xvec, ref, num_steps=4, guidance_scale=0.5, sway=-1.0, noise=noise)
+        assert mel.shape == mel_ref.shape == (B, 8, 2 * Tc)
+        assert (mel - mel_ref).abs().max().item() < 1e-3 * max(1.0, mel_ref.abs().max().item())
+        wav_ref = hf.code2wav_bigvgan_model(mel_ref)
+        wav = m.vocoder(mel_ref)[0]
+        assert wav.shape == wav_ref.shape == (2 * Tc * 4,) and (wav - wav_ref).abs().max().item() < 1e-4
+        assert 0.01 < wav_ref.abs().max().item()

@@ -73,11 +73,25 @@ def test_rk4_and_time_grid():
     assert bool((t[1:-1] < torch.linspace(0, 1, 10)[1:-1]).all())
 
 
-def test_dit_band_mask_limits_context():
+def test_dit_block_locality():
+    """Every layer sees its own block of frames; the listed layers also the previous / next block."""
     from vllm_omni_b200.models.qwen2_5_omni.config import Qwen25OmniConfig
     from vllm_omni_b200.models.qwen2_5_omni.token2wav import Token2WavDiT
     c = Qwen25OmniConfig.tiny().dit
-    m = Token2WavDiT(c, torch.float32, "cpu")
-    mask = m._band_mask(40, "cpu")
-    assert bool(mask[0, 0]) and bool(mask[0, 2 * c.block_size - 1]) and not bool(mask[0, 2 * c.block_size])
-    assert bool(mask[39, 39 - 2 * c.block_size]) and not bool(mask[39, 39 - 4 * c.block_size])
+    m = Token2WavDiT(c)
+    d = m.block_diff(40, "cpu")
+    bs = c.block_size
+    assert int(d[0, bs - 1]) == 0 and int(d[0, bs]) == 1 and int(d[2 * bs, 0]) == -2
+    assert [(l.look_ahead, l.look_backward) for l in m.transformer_blocks] == [(0, 1), (1, 0), (0, 1)]
+    # a change in block 3 reaches block 0 through at most the backward-looking layers: not at all here
+    torch.manual_seed(0)
+    for p in m.parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, 0, 0.2)
+    x, ref, xv = torch.randn(1, 40, c.mel_dim), torch.randn(1, 9, c.mel_dim), torch.randn(1, 40, c.enc_emb_dim)
+    codes = torch.randint(1, 90, (1, 20))
+    y0 = m(x, ref, xv, codes, torch.tensor(0.3), apply_cfg=False)
+    x2 = x.clone()
+    x2[:, 3 * bs:] += 1.0
+    y1 = m(x2, ref, xv, codes, torch.tensor(0.3), apply_cfg=False)
+    assert torch.allclose(y0[:, :bs], y1[:, :bs], atol=1e-6) and not torch.allclose(y0[:, 3 * bs:], y1[:, 3 * bs:])

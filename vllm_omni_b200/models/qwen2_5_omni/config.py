@@ -21,13 +21,30 @@ class DiTConfig:
     num_embeds: int = 8193              # codec vocabulary + 1 "dropped" id
     emb_dim: int = 512
     repeats: int = 2                    # mel frames per codec token
-    block_size: int = 24                # block-sparse attention: frames per block
-    look_ahead_blocks: int = 1
-    look_backward_blocks: int = 2
-    speaker_dim: int = 128              # conditioning vector (speaker / voice embedding)
+    block_size: int = 24                # attention is restricted to neighbouring blocks of this many frames
+    look_ahead_layers: tuple = (10,)    # layers that also see the next block
+    look_backward_layers: tuple = (0, 20)   # layers that also see the previous block
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 32768
+    enc_emb_dim: int = 192              # speaker x-vector width
+    enc_dim: int = 128                  # output of the reference-mel speaker encoder
+    enc_channels: tuple = (256, 256, 256, 256, 768)
+    enc_kernel_sizes: tuple = (5, 3, 3, 3, 1)
+    enc_dilations: tuple = (1, 2, 3, 4, 1)
+    enc_attention_channels: int = 64
+    enc_res2net_scale: int = 2
+    enc_se_channels: int = 64
     num_steps: int = 10
     guidance_scale: float = 0.5
     sway_coefficient: float = -1.0
+
+    @classmethod
+    def from_dict(cls, d):
+        d = dict(d)
+        if d.get("rope_theta") is None:
+            d["rope_theta"] = float((d.get("rope_parameters") or {}).get("rope_theta", 10000.0))
+        keys = set(cls.__dataclass_fields__)
+        return cls(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items() if k in keys})
 
 
 @dataclass
@@ -46,6 +63,12 @@ class BigVGANConfig:
         for r in self.upsample_rates:
             n *= r
         return n
+
+    @classmethod
+    def from_dict(cls, d):
+        keys = set(cls.__dataclass_fields__)
+        tup = lambda v: tuple(tup(x) for x in v) if isinstance(v, (list, tuple)) else v
+        return cls(**{k: tup(v) for k, v in d.items() if k in keys})
 
 
 @dataclass
@@ -89,8 +112,11 @@ class Qwen25OmniConfig:
                    vision=Qwen25VisionConfig(depth=2, hidden_size=32, num_heads=2, intermediate_size=48, patch_size=4,
                                              temporal_patch_size=1, spatial_merge_size=2, out_hidden_size=64,
                                              window_size=16, fullatt_block_indexes=(1,)),
-                   dit=DiTConfig(hidden_size=32, num_hidden_layers=2, num_attention_heads=2, head_dim=16, mel_dim=8,
-                                 num_embeds=97, emb_dim=16, block_size=4, speaker_dim=8, num_steps=3),
+                   dit=DiTConfig(hidden_size=32, num_hidden_layers=3, num_attention_heads=2, head_dim=16, mel_dim=8,
+                                 num_embeds=97, emb_dim=16, block_size=4, look_ahead_layers=(1,), look_backward_layers=(0, 2),
+                                 enc_emb_dim=8, enc_dim=8, enc_channels=(8, 8, 8, 8, 24), enc_kernel_sizes=(5, 3, 3, 3, 1),
+                                 enc_dilations=(1, 2, 3, 4, 1), enc_attention_channels=4, enc_res2net_scale=2,
+                                 enc_se_channels=4, num_steps=3),
                    bigvgan=BigVGANConfig(mel_dim=8, upsample_initial_channel=16, upsample_rates=(2, 2),
                                          upsample_kernel_sizes=(4, 4), resblock_kernel_sizes=(3,),
                                          resblock_dilation_sizes=((1, 3),)),
@@ -112,6 +138,11 @@ class Qwen25OmniConfig:
         if tk:
             c.talker = DecoderConfig.from_dict({**tk, "qk_norm": False, "attention_bias": True})
             c.talker_embedding_size = int(tk.get("embedding_size", c.thinker.hidden_size))
+        tw = d.get("token2wav_config", {})
+        if tw.get("dit_config"):
+            c.dit = DiTConfig.from_dict(tw["dit_config"])
+        if tw.get("bigvgan_config"):
+            c.bigvgan = BigVGANConfig.from_dict(tw["bigvgan_config"])
         for k, src in (("audio_token_id", "audio_token_index"), ("image_token_id", "image_token_index"),
                        ("video_token_id", "video_token_index")):
             if src in th:
