@@ -112,6 +112,9 @@ def test_pipeline_serves_hf_checkpoint(checkpoint):
         o.close()
     hf.thinker.config.vision_start_token_id = 508          # read by the HF position-id helper, unused for text
     hf.thinker.config.position_id_per_seconds = 25
+    for k, v in (("vision_start_token_id", 508), ("audio_start_token_id", 510), ("position_id_per_seconds", 25)):
+        if not hasattr(hf.thinker.config, k):              # read by the HF position-id helper, unused for text
+            setattr(hf.thinker.config, k, v)
     with torch.no_grad():
         g = hf.thinker.generate(input_ids=torch.tensor([ids]), attention_mask=torch.ones(1, len(ids), dtype=torch.long),
                                 max_new_tokens=6, do_sample=False)
@@ -132,3 +135,73 @@ def test_mrope_positions_match_hf_rope_index(checkpoint):
                                    audio_seqlens=torch.tensor([5]), second_per_grids=torch.tensor([2.0]))
     mine, d = get_input_positions(ids, 501, 502, 500, [(1, 2, 3)], [(2, 2, 2)], seconds_per_grid_t=2.0)
     assert torch.equal(ref[:, 0].long(), mine) and int(delta) == d
+
+
+# ---------------------------------------------------------------------------- Qwen2.5-Omni
+Q25_YAML = YAML.replace("Qwen3OmniMoeForConditionalGeneration", "Qwen2_5OmniForConditionalGeneration") \
+    .replace("vllm_omni_b200.models.stage_input_processors.qwen3_omni.thinker2talker",
+             "vllm_omni_b200.models.stage_input_processors.qwen2_5_omni.thinker2talker") \
+    .replace("vllm_omni_b200.models.stage_input_processors.qwen3_omni.talker2code2wav",
+             "vllm_omni_b200.models.stage_input_processors.qwen2_5_omni.talker2code2wav") \
+    .replace("stop_token_ids: [66]", "stop_token_ids: [94]")
+
+
+def test_qwen2_5_omni_hf_checkpoint_through_the_pipeline(tmp_path):
+    """``save_pretrained`` of a tiny Qwen2.5-Omni: the three stages load ``thinker.* / talker.* /
+    token2wav.*``, the greedy thinker tokens equal transformers', and a waveform comes out."""
+    from transformers.models.qwen2_5_omni import modeling_qwen2_5_omni as M
+    from transformers.models.qwen2_5_omni.configuration_qwen2_5_omni import Qwen2_5OmniConfig
+    from vllm_omni_b200.entrypoints.stage_runtime import inproc_adapter
+    torch.manual_seed(0)
+    rope = dict(rope_theta=1e6, rope_type="default", mrope_section=[2, 3, 3])
+    thinker = dict(
+        audio_config=dict(num_mel_bins=16, d_model=32, encoder_layers=1, encoder_attention_heads=2, encoder_ffn_dim=64,
+                          output_dim=64, n_window=10, max_source_positions=64),
+        vision_config=dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, out_hidden_size=64, patch_size=4,
+                           window_size=16, fullatt_block_indexes=[1]),
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=512, rope_parameters=rope),
+        audio_token_index=500, image_token_index=501, video_token_index=502)
+    talker = dict(vocab_size=96, embedding_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                  num_attention_heads=2, num_key_value_heads=2, head_dim=16, max_position_embeddings=256, rope_parameters=rope,
+                  tts_codec_start_token_id=93, tts_codec_end_token_id=94, tts_codec_pad_token_id=92, tts_codec_mask_token_id=95,
+                  tts_text_start_token_id=503, tts_text_end_token_id=504, tts_text_pad_token_id=505)
+    t2w = dict(dit_config=dict(hidden_size=32, num_hidden_layers=2, num_attention_heads=2, ff_mult=2, emb_dim=16, head_dim=16,
+                               block_size=4, look_ahead_layers=[1], look_backward_layers=[0], repeats=2, num_embeds=97, mel_dim=8,
+                               dropout=0.0, enc_emb_dim=8, enc_dim=8, enc_channels=[8, 8, 8, 8, 24],
+                               enc_kernel_sizes=[5, 3, 3, 3, 1], enc_dilations=[1, 2, 3, 4, 1], enc_attention_channels=4,
+                               enc_res2net_scale=2, enc_se_channels=4, max_position_embeddings=512),
+               bigvgan_config=dict(mel_dim=8, upsample_initial_channel=16, resblock_kernel_sizes=[3], resblock_dilation_sizes=[[1, 3, 5]],
+                                   upsample_rates=[2, 2], upsample_kernel_sizes=[4, 4]))
+    hf = M.Qwen2_5OmniForConditionalGeneration(Qwen2_5OmniConfig(thinker_config=thinker, talker_config=talker,
+                                                                 token2wav_config=t2w, enable_audio_output=True))
+    for _, p in hf.named_parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, 0, 0.05)
+    hf = hf.float().eval()
+    hf.save_pretrained(str(tmp_path))
+    (tmp_path / "stages.yaml").write_text(Q25_YAML)
+    ids = [506, 10, 11, 12, 507, 506, 13]
+    o = Omni(str(tmp_path), stage_configs_path=str(tmp_path / "stages.yaml"))
+    try:
+        outs = o.generate([{"prompt_token_ids": ids}])
+        mine = list([x for x in outs if x.final_output_type == "text"][0].request_output.outputs[0].token_ids)
+        audio = [x for x in outs if x.final_output_type == "audio"][0]
+        assert audio.multimodal_output["audio"].dim() == 1
+        sd = hf.state_dict()
+        th, tk, tw = (inproc_adapter(i).llm.model for i in range(3))
+        assert torch.equal(th.audio_tower.proj.weight, sd["thinker.audio_tower.proj.weight"])
+        assert torch.equal(th.visual.merge2.weight, sd["thinker.visual.merger.mlp.2.weight"])
+        assert torch.equal(tk.codec_embedding, sd["talker.model.embed_tokens.weight"])
+        assert torch.equal(tw.dit.proj_out.weight, sd["token2wav.code2wav_dit_model.proj_out.weight"])
+        assert torch.equal(tw.vocoder.conv_post.weight, sd["token2wav.code2wav_bigvgan_model.conv_post.weight"])
+        assert tk.cfg.codec_eos_id == 94 and tk.cfg.tts_text_bos_id == 503
+    finally:
+        o.close()
+    for k, v in (("vision_start_token_id", 508), ("audio_start_token_id", 510), ("position_id_per_seconds", 25)):
+        if not hasattr(hf.thinker.config, k):              # read by the HF position-id helper, unused for text
+            setattr(hf.thinker.config, k, v)
+    with torch.no_grad():
+        g = hf.thinker.generate(input_ids=torch.tensor([ids]), attention_mask=torch.ones(1, len(ids), dtype=torch.long),
+                                max_new_tokens=6, do_sample=False)
+    assert mine == g[0, len(ids):].tolist()

@@ -129,7 +129,9 @@ class Qwen25OmniConfig:
         c = cls()
         th = d.get("thinker_config", {})
         if th.get("text_config"):
-            c.thinker = DecoderConfig.from_dict({**th["text_config"], "qk_norm": False, "attention_bias": True})
+            # the thinker checkpoint always carries its own ``lm_head.weight``, whatever the tie flag says
+            c.thinker = DecoderConfig.from_dict({**th["text_config"], "qk_norm": False, "attention_bias": True,
+                                                 "tie_word_embeddings": False})
         if th.get("audio_config"):
             c.audio = Qwen25AudioConfig.from_dict(th["audio_config"])
         if th.get("vision_config"):
