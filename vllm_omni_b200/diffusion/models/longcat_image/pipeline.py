@@ -3,22 +3,14 @@
 appends the VAE latents of the input image to the image sequence."""
 from __future__ import annotations
 
-from dataclasses import dataclass
-
 import torch
 
 from ..flux.pipeline import FluxPipeline
-from ..flux.transformer import FluxTransformer2DModel, FluxTransformerConfig
-
-
-@dataclass
-class LongCatTransformerConfig(FluxTransformerConfig):
-    joint_attention_dim: int = 3584
-    guidance_embeds: bool = False
+from .transformer import LongCatImageTransformer2DModel, LongCatTransformerConfig
 
 
 class LongCatImagePipeline(FluxPipeline):
-    transformer_cls, config_cls = FluxTransformer2DModel, LongCatTransformerConfig
+    transformer_cls, config_cls = LongCatImageTransformer2DModel, LongCatTransformerConfig
     default_guidance = 4.5
 
 

@@ -272,7 +272,8 @@ class QwenImageTransformer2DModel(nn.Module):
                            split=S_img)
             attn_img, attn_txt = ws["attn_img"], ws["attn_txt"]
         tp = getattr(self, "tp_heads", 0) if self.sp is None else 0
-        if (not tp) and S_txt > 0 and img.is_cuda and _plain_pair(blk):
+        swiglu = getattr(cfg, "mlp_act", "gelu_tanh") == "swiglu"        # FLUX-family variants with gated MLPs
+        if (not tp) and S_txt > 0 and img.is_cuda and _plain_pair(blk) and not swiglu:
             # both streams per launch: out-projection, then the two norms, MLP up, MLP down
             mi, mt = m[:, 0], m[:, 1]
             bi, bt = blk.img, blk.txt
@@ -305,6 +306,9 @@ class QwenImageTransformer2DModel(nn.Module):
                 continue
             sp.to_out(att, residual=x, gate=mm[:, 2 * D:3 * D], out=x)
             fused.norm_modulate(x, shift=mm[:, 3 * D:4 * D], scale=mm[:, 4 * D:5 * D], eps=cfg.eps, out=xn)
+            if swiglu:
+                sp.mlp_down(fused.silu_mul(sp.mlp_up(xn)), residual=x, gate=mm[:, 5 * D:6 * D], out=x)
+                continue
             sp.mlp_up(xn, act="gelu_tanh", out=hbuf)
             sp.mlp_down(hbuf, residual=x, gate=mm[:, 5 * D:6 * D], out=x)
         return img, txt
