@@ -13,6 +13,8 @@ request, outputs returned as multimodal tensors, no sampling
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..models.qwen_decoder import ModelBatch, PrefillSeg
@@ -30,6 +32,14 @@ class ARModelRunner:
                                        device=device),
                            torch.zeros(num_blocks, block_size, dec.num_key_value_heads, dec.head_dim, dtype=dtype,
                                        device=device)) for _ in range(dec.num_hidden_layers)]
+        # decode-only steps replay a captured graph per batch-size bucket (``OMNI_AR_CUDA_GRAPH=1``); contexts
+        # longer than ``OMNI_AR_GRAPH_MAX_TOKENS`` (default 4096) and mixed prefill/decode steps run eagerly
+        self.graph_runner = None
+        if os.environ.get("OMNI_AR_CUDA_GRAPH", "0") == "1" and hasattr(model, "decoder"):
+            from .graph_runner import DecodeGraphRunner
+            max_tokens = int(os.environ.get("OMNI_AR_GRAPH_MAX_TOKENS", "4096"))
+            self.graph_runner = DecodeGraphRunner(model.decoder, self.kv_caches, max(1, max_tokens // block_size),
+                                                  capture_layers=getattr(model, "capture", ()))
 
     # ------------------------------------------------------------------ batch assembly
     def _build_batch(self, sched: SchedulerOutput, kv_mgr):
@@ -96,7 +106,10 @@ class ARModelRunner:
         if sched.empty:
             return {}, []
         batch, sample_rows, sample_reqs = self._build_batch(sched, kv_mgr)
-        hidden, captured = self.model.forward_batch(batch, self.kv_caches, sched)
+        if self.graph_runner is not None and self.graph_runner.supports(batch):
+            hidden, captured = self.graph_runner.run(batch)
+        else:
+            hidden, captured = self.model.forward_batch(batch, self.kv_caches, sched)
         sampled: dict[str, int] = {}
         if sample_rows:
             rows_t = torch.tensor(sample_rows, dtype=torch.long, device=self.device)
