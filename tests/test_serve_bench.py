@@ -70,3 +70,48 @@ def test_image_bench_over_http():
     finally:
         server.should_exit = True
         th.join(timeout=5)
+
+
+def test_perf_gate_passes_and_fails_on_baselines(tmp_path):
+    """The regression gate against a live (fake-engine) server: every request must complete and the
+    gated metrics must stay under their baselines."""
+    uvicorn = pytest.importorskip("uvicorn")
+    import importlib.util
+    import json
+    import os
+    from test_openai_api import FakeDiffusionEngine
+    from vllm_omni_b200.entrypoints.openai.api_server import build_app
+    spec = importlib.util.spec_from_file_location(
+        "perf_gate", os.path.join(os.path.dirname(__file__), "..", "benchmarks", "perf", "run_benchmark.py"))
+    gate = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gate)
+    app = build_app(FakeDiffusionEngine(), "fake", kind="diffusion")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    try:
+        for _ in range(100):
+            if server.started:
+                break
+            time.sleep(0.05)
+        entry = {"name": "img", "kind": "image", "model": "fake",
+                 "sweeps": [{"num_prompts": 3, "max_concurrency": 2, "size": "32x32", "num_inference_steps": 2}]}
+        tests = tmp_path / "t.json"
+        tests.write_text(json.dumps([dict(entry, baseline={"mean_e2el_ms": 60000})]))
+        out = tmp_path / "r.json"
+        assert gate.main(["--tests", str(tests), "--base-url", f"http://127.0.0.1:{port}", "--out", str(out)]) == 0
+        rep = json.loads(out.read_text())
+        assert rep[0]["summary"]["completed"] == 3 and rep[0]["violations"] == []
+        tests.write_text(json.dumps([dict(entry, baseline={"mean_e2el_ms": 1e-6})]))
+        assert gate.main(["--tests", str(tests), "--base-url", f"http://127.0.0.1:{port}"]) == 1
+    finally:
+        server.should_exit = True
+        th.join(timeout=5)
+    # the shipped gate file is well formed
+    shipped = json.load(open(os.path.join(os.path.dirname(__file__), "..", "benchmarks", "perf", "tests.json")))
+    assert all(set(e["baseline"]) <= set(gate.METRICS) and e["sweeps"] for e in shipped)
+    assert gate.check({"completed": 2, "ttft_s": {"mean": 0.5}}, {"mean_ttft_ms": 400}, 3) == [
+        "completed 2 of 3 requests", "mean_ttft_ms = 500.000 exceeds the baseline 400"]
