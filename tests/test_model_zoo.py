@@ -13,8 +13,8 @@ FLUXY = dict(num_layers=1, num_single_layers=1, attention_head_dim=32, num_atten
 TINY = {
     "QwenImagePipeline": dict(num_layers=1, attention_head_dim=32, num_attention_heads=2, joint_attention_dim=32,
                               axes_dims_rope=(8, 12, 12)),
-    "GlmImagePipeline": dict(num_layers=1, attention_head_dim=32, num_attention_heads=2, joint_attention_dim=32,
-                             axes_dims_rope=(8, 12, 12)),
+    "GlmImagePipeline": dict(num_layers=1, attention_head_dim=32, num_attention_heads=2, time_embed_dim=32, condition_dim=16,
+                             prior_vq_quantizer_codebook_size=64, text_embed_dim=24, in_channels=16, out_channels=16),
     "TinyMMDiTPipeline": {},
     "FluxPipeline": FLUXY, "Flux2KleinPipeline": FLUXY, "LongCatImagePipeline": FLUXY, "LongCatImageEditPipeline": FLUXY,
     "OvisImagePipeline": FLUXY, "StableDiffusion3Pipeline": dict(FLUXY, num_single_layers=0),
