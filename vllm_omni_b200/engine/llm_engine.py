@@ -35,6 +35,8 @@ class LLMEngine:
             "cuda" if torch.cuda.is_available() else "cpu")
         self.dtype = dtype
         self.tokenizer = tokenizer or get_tokenizer(None)
+        if hasattr(model, "text_tokenizer"):             # models that tokenize request fields themselves (TTS instructions)
+            model.text_tokenizer = self.tokenizer
         self.stage_id = stage_id
         self.engine_output_type = engine_output_type or getattr(model, "engine_output_type", "text")
         self.generation = bool(getattr(model, "is_generation_model", False))

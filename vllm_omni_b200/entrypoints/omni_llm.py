@@ -82,6 +82,7 @@ class OmniLLM:
         if model and os.path.isdir(model) and os.path.exists(os.path.join(model, "config.json")):
             with open(os.path.join(model, "config.json")) as f:
                 hf_cfg = json.load(f)
+            hf_cfg.setdefault("_model_dir", model)          # for models that keep sub-configs in sub-folders
         arch = a.model_arch or (hf_cfg.get("architectures") or ["Qwen3ForCausalLM"])[0]
         # stages that share a process are built on a thread pool and share torch's global generator:
         # seeding and random initialisation must not interleave, or the weights depend on thread timing
@@ -93,6 +94,8 @@ class OmniLLM:
             files = _shard_files(model)
             if files and hasattr(self.model, "load_weights"):
                 n = len(self.model.load_weights(safetensors_weights_iterator(files)))
+                if hasattr(self.model, "load_auxiliary"):          # weights kept beside the main checkpoint
+                    n += self.model.load_auxiliary(model)
                 logger.info("stage %d (%s): loaded %d tensors", stage_id, a.model_stage, n)
         self.model.eval()
         chunk_adapter = kv_mgr = None

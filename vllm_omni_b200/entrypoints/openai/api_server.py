@@ -217,9 +217,13 @@ def build_app(engine, model_name: str = "omni", kind: str = "omni", default_stag
         return VideoGenerationResponse(data=data)
 
     # ------------------------------------------------------------------ speech
+    def _known_voices():
+        from ..utils import voices_of_checkpoint
+        return (getattr(engine, "voices", None) or voices_of_checkpoint(getattr(engine, "model", None)) or DEFAULT_VOICES)
+
     @app.get("/v1/audio/voices")
     async def voices():
-        return {"voices": getattr(engine, "voices", None) or DEFAULT_VOICES}
+        return {"voices": _known_voices()}
 
     @app.post("/v1/audio/speech")
     async def speech(req: OpenAICreateSpeechRequest):
@@ -227,12 +231,19 @@ def build_app(engine, model_name: str = "omni", kind: str = "omni", default_stag
             return _err(400, "input must not be empty")
         if req.response_format not in ("wav", "pcm"):
             return _err(400, f"response_format {req.response_format!r} is not available in this build; use wav or pcm")
-        voice = req.voice or DEFAULT_VOICES[0]
-        known = getattr(engine, "voices", None) or DEFAULT_VOICES
-        if voice not in known:
-            return _err(400, f"unknown voice {voice!r}; available: {known}")
-        info = {"voice": voice, "instructions": req.instructions, "language": req.language,
-                "task_type": req.task_type or "CustomVoice", "ref_text": req.ref_text}
+        task = req.task_type or ("Base" if req.ref_audio else "CustomVoice")
+        known = _known_voices()
+        voice = req.voice
+        if task == "CustomVoice":                        # a named voice; the other tasks describe or clone one
+            voice = voice or known[0]
+            if voice.lower() not in {k.lower() for k in known}:
+                return _err(400, f"unknown voice {voice!r}; available: {known}")
+        elif task == "Base" and not (req.ref_audio or voice):
+            return _err(400, "voice cloning (task_type Base) needs ref_audio (a WAV file as base64 or a data: URL)")
+        elif task == "VoiceDesign" and not req.instructions:
+            return _err(400, "voice design (task_type VoiceDesign) needs instructions that describe the voice")
+        info = {"voice": voice, "instructions": req.instructions, "language": req.language, "task_type": task,
+                "ref_text": req.ref_text, "ref_audio": req.ref_audio, "x_vector_only_mode": req.x_vector_only_mode}
         prompt = {"prompt": req.input, "additional_information": {k: v for k, v in info.items() if v is not None}}
         sps = None
         if req.max_new_tokens:

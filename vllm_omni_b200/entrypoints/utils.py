@@ -146,3 +146,17 @@ def inject_omni_kv_config(stage_cfgs: list[StageConfig]) -> None:
             kv.setdefault("to_stages", [s.stage_id for s in stage_cfgs if sc.stage_id in s.engine_input_source])
         if kv.get("need_recv_cache"):
             kv.setdefault("from_stage", sc.engine_input_source[0] if sc.engine_input_source else None)
+
+
+def voices_of_checkpoint(model: str | None) -> list[str]:
+    """Named voices of a speech checkpoint: the keys of ``talker_config.spk_id`` (Qwen3-TTS) or
+    ``talker_config.speaker_id`` (Qwen3-Omni) in its ``config.json``; [] when there is none."""
+    if not model or not os.path.isdir(model):
+        return []
+    try:
+        with open(os.path.join(model, "config.json")) as f:
+            tk = json.load(f).get("talker_config") or {}
+    except (OSError, ValueError):
+        return []
+    table = tk.get("spk_id") or tk.get("speaker_id") or {}
+    return list(table) if isinstance(table, dict) else []

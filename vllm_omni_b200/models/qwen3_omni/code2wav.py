@@ -56,16 +56,18 @@ class CausalConv1d(nn.Module):
 
 
 class CausalTransConv1d(nn.Module):
-    """Transposed convolution with (kernel - stride) samples cut from both ends."""
+    """Transposed convolution with (kernel - stride) samples cut from both ends (Qwen3-Omni code2wav)
+    or, with ``trim_left=False``, from the right end only (the Qwen3-TTS 12 Hz tokenizer decoder)."""
 
-    def __init__(self, cin, cout, k, stride, dtype=None, device=None):
+    def __init__(self, cin, cout, k, stride, dtype=None, device=None, trim_left=True):
         super().__init__()
         self.conv = nn.ConvTranspose1d(cin, cout, k, stride=stride, dtype=dtype, device=device)
         self.trim = k - stride
+        self.left = self.trim if trim_left else 0
 
     def forward(self, x):
         y = self.conv(x)
-        return y[..., self.trim: y.shape[-1] - self.trim].contiguous()
+        return y[..., self.left: y.shape[-1] - self.trim].contiguous()
 
 
 class ConvNeXtBlock(nn.Module):
@@ -99,10 +101,11 @@ class ResUnit(nn.Module):
 class DecoderBlock(nn.Module):
     """``block.0`` SnakeBeta, ``block.1`` transposed conv (x rate), ``block.2-4`` residual units."""
 
-    def __init__(self, cin, cout, rate, dtype, device):
+    def __init__(self, cin, cout, rate, dtype, device, trim_left=True):
         super().__init__()
         self.block = nn.ModuleList([SnakeBeta(cin, dtype, device),
-                                    CausalTransConv1d(cin, cout, 2 * rate, rate, dtype=dtype, device=device)] +
+                                    CausalTransConv1d(cin, cout, 2 * rate, rate, dtype=dtype, device=device,
+                                                      trim_left=trim_left)] +
                                    [ResUnit(cout, d, dtype, device) for d in (1, 3, 9)])
 
     def forward(self, x):
@@ -166,6 +169,34 @@ class PreTransformer(nn.Module):
         for layer in self.layers:
             x = layer(x, cos, sin, mask)
         return fused.norm_modulate(x.contiguous(), weight=self.norm, rms=True, eps=self.cfg.rms_norm_eps)
+
+
+def pre_transformer_target(pt: "PreTransformer", n: str):
+    """Checkpoint name ``pre_transformer.*`` -> (parameter, row slice or None) of the fused layout."""
+    c = pt.cfg
+    p = n.split(".")
+    if n == "pre_transformer.norm.weight":
+        return pt.norm, None
+    if not n.startswith("pre_transformer.layers."):
+        return None, None
+    layer = pt.layers[int(p[2])]
+    rest = ".".join(p[3:])
+    H, Hkv, Dh, Fi = layer.H, layer.Hkv, layer.Dh, c.intermediate_size
+    qo = {"q_proj": (0, H * Dh), "k_proj": (H * Dh, (H + Hkv) * Dh), "v_proj": ((H + Hkv) * Dh, (H + 2 * Hkv) * Dh)}
+    if p[3] == "self_attn" and p[4] in qo:
+        return getattr(layer.qkv, p[5]), qo[p[4]]
+    if p[3] == "self_attn" and p[4] == "o_proj":
+        return getattr(layer.o, p[5]), None
+    if rest == "mlp.gate_proj.weight":
+        return layer.gate_up.weight, (0, Fi)
+    if rest == "mlp.up_proj.weight":
+        return layer.gate_up.weight, (Fi, 2 * Fi)
+    if rest == "mlp.down_proj.weight":
+        return layer.down.weight, None
+    return {"input_layernorm.weight": layer.input_layernorm,
+            "post_attention_layernorm.weight": layer.post_attention_layernorm,
+            "self_attn_layer_scale.scale": layer.attn_scale,
+            "mlp_layer_scale.scale": layer.mlp_scale}.get(rest), None
 
 
 class Qwen3OmniCode2Wav(StageModel):
@@ -252,28 +283,8 @@ class Qwen3OmniCode2Wav(StageModel):
             n = full[len("code2wav."):] if full.startswith("code2wav.") else full
             tgt, sl = None, None
             p = n.split(".")
-            if n.startswith("pre_transformer.layers."):
-                layer = self.pre_transformer.layers[int(p[2])]
-                rest = ".".join(p[3:])
-                H, Hkv, Dh, Fi = layer.H, layer.Hkv, layer.Dh, self.c.intermediate_size
-                qo = {"q_proj": (0, H * Dh), "k_proj": (H * Dh, (H + Hkv) * Dh), "v_proj": ((H + Hkv) * Dh, (H + 2 * Hkv) * Dh)}
-                if p[3] == "self_attn" and p[4] in qo:
-                    tgt, sl = getattr(layer.qkv, p[5]), qo[p[4]]
-                elif p[3] == "self_attn" and p[4] == "o_proj":
-                    tgt = getattr(layer.o, p[5])
-                elif rest == "mlp.gate_proj.weight":
-                    tgt, sl = layer.gate_up.weight, (0, Fi)
-                elif rest == "mlp.up_proj.weight":
-                    tgt, sl = layer.gate_up.weight, (Fi, 2 * Fi)
-                elif rest == "mlp.down_proj.weight":
-                    tgt = layer.down.weight
-                else:
-                    tgt = {"input_layernorm.weight": layer.input_layernorm,
-                           "post_attention_layernorm.weight": layer.post_attention_layernorm,
-                           "self_attn_layer_scale.scale": layer.attn_scale,
-                           "mlp_layer_scale.scale": layer.mlp_scale}.get(rest)
-            elif n == "pre_transformer.norm.weight":
-                tgt = self.pre_transformer.norm
+            if n.startswith("pre_transformer."):
+                tgt, sl = pre_transformer_target(self.pre_transformer, n)
             elif n == "code_embedding.weight":
                 tgt = self.code_embedding
             else:

@@ -75,7 +75,8 @@ class CodePredictor(nn.Module):
     @torch.no_grad()
     def load_weights(self, weights) -> set:
         """Names relative to ``talker.code_predictor.``: ``model.layers.*`` / ``model.norm.weight``,
-        ``model.codec_embedding.G.weight`` and ``lm_head.G.weight`` for residual codebooks G."""
+        ``model.codec_embedding.G.weight`` and ``lm_head.G.weight`` for residual codebooks G; Qwen3-TTS adds
+        ``small_to_mtp_projection`` (talker width -> predictor width) when the two widths differ."""
         loaded, core = set(), []
         for n, w in weights:
             p = n.split(".")
@@ -85,7 +86,7 @@ class CodePredictor(nn.Module):
             elif n.startswith("lm_head.") and p[-1] == "weight":
                 self.lm_heads[int(p[1])].copy_(w.to(self.lm_heads.dtype))
                 loaded.add(n)
-            elif n.startswith("in_proj.") and self.in_proj is not None:
+            elif n.startswith(("in_proj.", "small_to_mtp_projection.")) and self.in_proj is not None:
                 getattr(self.in_proj, p[1]).copy_(w.to(self.in_proj.weight.dtype))
                 loaded.add(n)
             else:
