@@ -75,7 +75,8 @@ def safetensors_weights_iterator(files: list[str], prefix: str = "", num_threads
 
 
 class DiffusersPipelineLoader:
-    COMPONENTS = ("transformer", "transformer_2", "vae", "text_encoder", "text_encoder_2")
+    COMPONENTS = ("transformer", "transformer_2", "vae", "text_encoder", "text_encoder_2", "text_encoder_3",
+                  "projection_model")
 
     def __init__(self, od_config: OmniDiffusionConfig):
         self.od_config = od_config

@@ -84,17 +84,50 @@ class FluxPipeline(nn.Module):
         img = (self.vae_decode or self.vae.decode)(unpack_latents(lat, h, w))
         return DiffusionOutput(output=img, metrics={"num_steps": len(ts), "batch": B})
 
+    # sub-folder of the checkpoint -> attribute that holds its encoder (CLIP: pooled vector, T5: states)
+    encoder_slots = {"text_encoder": "pooled_encoder", "text_encoder_2": "text_encoder"}
+
+    def attach_text_encoder(self, model_path: str) -> bool:
+        """``text_encoder/`` (CLIP, pooled vector) and ``text_encoder_2/`` (T5 states) with their
+        tokenizers replace the seeded stand-ins when the checkpoint has them."""
+        import os
+        from ..text_encoders.clip import CLIPPromptEncoder
+        from ..text_encoders.t5 import T5PromptEncoder
+        import json
+
+        def has(enc, tok, kind):                     # the sub-folder holds an encoder of that family, with a tokenizer
+            path = os.path.join(model_path, enc, "config.json")
+            if not (os.path.isfile(path) and os.path.isdir(os.path.join(model_path, tok))):
+                return False
+            with open(path) as f:
+                d = json.load(f)
+            return kind in (d.get("model_type") or "") or any(kind in a.lower() for a in d.get("architectures") or [])
+        got = False
+        if has("text_encoder", "tokenizer", "clip"):
+            self.pooled_encoder = CLIPPromptEncoder.from_pretrained(model_path, "text_encoder", "tokenizer",
+                                                                    self.od_config.dtype, self.device_)
+            got = True
+        if has("text_encoder_2", "tokenizer_2", "t5"):
+            self.text_encoder = T5PromptEncoder.from_pretrained(model_path, "text_encoder_2", "tokenizer_2",
+                                                                self.od_config.dtype, self.device_, max_len=self.max_text_len)
+            got = True
+        return got
+
     def load_weights(self, weights) -> set:
-        """diffusers sub-folder prefixes ``transformer.`` / ``vae.``."""
-        tw, vw = [], []
+        """diffusers sub-folder prefixes ``transformer.`` / ``vae.`` / ``text_encoder*.``."""
+        groups: dict[str, list] = {"transformer": [], "vae": []}
+        groups.update({k: [] for k in self.encoder_slots})
         for n, w in weights:
-            if n.startswith("transformer."):
-                tw.append((n[len("transformer."):], w))
-            elif n.startswith("vae."):
-                vw.append((n[len("vae."):], w))
-        loaded = {"transformer." + n for n in self.transformer.load_weights(tw)}
-        if vw and hasattr(self.vae, "load_weights"):
-            loaded |= {"vae." + n for n in self.vae.load_weights(vw)}
+            comp, _, rest = n.partition(".")
+            if comp in groups:
+                groups[comp].append((rest, w))
+        loaded = {"transformer." + n for n in self.transformer.load_weights(groups["transformer"])}
+        if groups["vae"] and hasattr(self.vae, "load_weights"):
+            loaded |= {"vae." + n for n in self.vae.load_weights(groups["vae"])}
+        for comp, attr in self.encoder_slots.items():
+            enc = getattr(self, attr, None)
+            if groups[comp] and hasattr(enc, "load_weights"):
+                loaded |= {comp + "." + n for n in enc.load_weights(groups[comp])}
         return loaded
 
 

@@ -14,6 +14,45 @@ from ..qwen_image.pipeline import pack_latents, unpack_latents
 from .transformer import SD3Transformer2DModel, SD3TransformerConfig
 
 
+class SD3PromptEncoder:
+    """SD3 conditioning from its three encoders: the penultimate states of CLIP-L and CLIP-G side by
+    side, zero-padded to the T5 width and followed by the T5 states along the sequence; the pooled
+    vector is the two projected CLIP end-of-text vectors side by side.  A missing T5 (the checkpoint
+    may ship without it) contributes zero states, as in diffusers."""
+
+    def __init__(self, clip_l, clip_g, t5, joint_dim: int, t5_len: int = 256):
+        self.clip_l, self.clip_g, self.t5, self.joint_dim, self.t5_len = clip_l, clip_g, t5, joint_dim, t5_len
+        self._key, self._val = None, None
+
+    def _encode(self, texts, device, dtype, max_len):
+        key = (tuple(texts), str(device), dtype, max_len)
+        if key != self._key:
+            _, pool_l, pen_l = self.clip_l.encode(texts, device)
+            _, pool_g, pen_g = self.clip_g.encode(texts, device)
+            clip = torch.cat([pen_l, pen_g], dim=-1)
+            clip = torch.nn.functional.pad(clip, (0, self.joint_dim - clip.shape[-1]))
+            L = min(int(max_len or self.t5_len), self.t5_len)
+            if self.t5 is not None:
+                t5, _ = self.t5(texts, device, None, L)
+            else:
+                t5 = clip.new_zeros(clip.shape[0], L, self.joint_dim)
+            self._key = key
+            self._val = (torch.cat([clip, t5.to(clip.dtype)], dim=1).to(dtype), torch.cat([pool_l, pool_g], dim=-1).to(dtype))
+        return self._val
+
+    def __call__(self, texts, device, dtype=None, max_len=None):
+        pe, _ = self._encode(list(texts), device, dtype, max_len)
+        return pe, torch.ones(pe.shape[:2], dtype=torch.long, device=pe.device)
+
+    def pooled(self, texts, device, dtype=None, max_len=None):
+        pooled = self._encode(list(texts), device, dtype, max_len)[1]
+        return pooled[:, None], None
+
+    def load_component(self, comp: str, weights) -> set:
+        enc = {"text_encoder": self.clip_l, "text_encoder_2": self.clip_g, "text_encoder_3": self.t5}.get(comp)
+        return enc.load_weights(weights) if enc is not None else set()
+
+
 class StableDiffusion3Pipeline(FluxPipeline):
     transformer_cls, config_cls = SD3Transformer2DModel, SD3TransformerConfig
     default_guidance = 7.0
@@ -25,6 +64,40 @@ class StableDiffusion3Pipeline(FluxPipeline):
         vc.setdefault("shift_factor", 0.0609)
         super().__init__(od_config, transformer_config, vc, device)
         self.scheduler = FlowMatchEulerDiscreteScheduler(shift=3.0)
+
+    def attach_text_encoder(self, model_path: str) -> bool:
+        """``text_encoder/`` + ``text_encoder_2/`` (CLIP-L and CLIP-G with projection) and, when present,
+        ``text_encoder_3/`` (T5) with ``tokenizer*/`` replace the seeded stand-ins."""
+        import os
+        from ..text_encoders.clip import CLIPPromptEncoder
+        from ..text_encoders.t5 import T5PromptEncoder
+        has = lambda enc, tok: (os.path.isfile(os.path.join(model_path, enc, "config.json")) and
+                                os.path.isdir(os.path.join(model_path, tok)))
+        if not (has("text_encoder", "tokenizer") and has("text_encoder_2", "tokenizer_2")):
+            return False
+        dt, dev = self.od_config.dtype, self.device_
+        clip_l = CLIPPromptEncoder.from_pretrained(model_path, "text_encoder", "tokenizer", dt, dev, with_projection=True)
+        clip_g = CLIPPromptEncoder.from_pretrained(model_path, "text_encoder_2", "tokenizer_2", dt, dev, with_projection=True)
+        t5 = T5PromptEncoder.from_pretrained(model_path, "text_encoder_3", "tokenizer_3", dt, dev, max_len=256) \
+            if has("text_encoder_3", "tokenizer_3") else None
+        enc = SD3PromptEncoder(clip_l, clip_g, t5, self.transformer.cfg.joint_attention_dim)
+        self.text_encoder, self.pooled_encoder = enc, enc.pooled
+        return True
+
+    def load_weights(self, weights) -> set:
+        rest, enc = [], {"text_encoder": [], "text_encoder_2": [], "text_encoder_3": []}
+        for n, w in weights:
+            comp, _, tail = n.partition(".")
+            if comp in enc:
+                enc[comp].append((tail, w))
+            else:
+                rest.append((n, w))
+        loaded = super().load_weights(rest)
+        if isinstance(self.text_encoder, SD3PromptEncoder):
+            for comp, ws in enc.items():
+                if ws:
+                    loaded |= {comp + "." + n for n in self.text_encoder.load_component(comp, ws)}
+        return loaded
 
     @torch.no_grad()
     def forward(self, req) -> DiffusionOutput:
