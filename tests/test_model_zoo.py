@@ -27,8 +27,9 @@ TINY = {
     "HunyuanImage3Pipeline": dict(vocab_size=64, hidden_size=64, num_hidden_layers=1, num_attention_heads=2,
                                   num_key_value_heads=2, head_dim=32, num_experts=4, num_experts_per_tok=2,
                                   moe_intermediate_size=32),
-    "StableAudioPipeline": dict(num_attention_heads=2, attention_head_dim=24, in_channels=8, out_channels=8, text_dim=32,
-                                ffn_dim=64, num_layers=1, decoder_rates=(4, 2), decoder_dim=16),
+    "StableAudioPipeline": dict(num_attention_heads=2, attention_head_dim=16, num_key_value_attention_heads=1, in_channels=8,
+                                out_channels=8, cross_attention_dim=24, cross_attention_input_dim=24, global_states_input_dim=48,
+                                time_proj_dim=16, num_layers=1, sample_size=6),
 }
 
 
@@ -52,10 +53,12 @@ def small_vae(monkeypatch):
 
 @pytest.mark.parametrize("name", sorted(n for n in TINY if n != "BagelPipeline"))
 def test_pipeline_runs_tiny(name):
-    o = OmniDiffusion(name, dtype="float32", device="cpu", tf_model_config=TINY[name], vae_config=SMALL_KL)
+    vae = SMALL_KL if name != "StableAudioPipeline" else dict(decoder_channels=8, channel_multiples=(1, 2),
+                                                                downsampling_ratios=(2, 4), sampling_rate=800)
+    o = OmniDiffusion(name, dtype="float32", device="cpu", tf_model_config=TINY[name], vae_config=vae)
     try:
         sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0, num_frames=5,
-                                         guidance_scale=3.0, extra_args={"audio_seconds": 0.01})
+                                         guidance_scale=3.0, extra_args={"audio_seconds": 0.05})
         prompt = {"prompt": "a small test", "negative_prompt": " "}
         out = o.generate([prompt], sp)[0]
         if name.startswith("Wan"):
@@ -63,7 +66,7 @@ def test_pipeline_runs_tiny(name):
             assert out.final_output_type == "video" and v.shape == (5, 64, 64, 3)
         elif name == "StableAudioPipeline":
             a = out.multimodal_output["audio"]
-            assert out.final_output_type == "audio" and a.dim() == 2 and a.shape[0] == 2
+            assert out.final_output_type == "audio" and a.shape == (2, 40) and out.multimodal_output["sample_rate"] == 800
         else:
             assert out.images[0].size == (64, 64)
     finally:

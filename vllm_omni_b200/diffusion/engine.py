@@ -79,8 +79,10 @@ class DiffusionEngine:
         for i, prompt in enumerate(request.prompts):
             chunk = outs[i * n_out:(i + 1) * n_out]
             if supports_audio_output(name):
-                results.append(OmniRequestOutput.from_diffusion(ids[i], [], prompt, metrics, output.trajectory_latents,
-                                                                {"audio": chunk[0] if len(chunk) == 1 else chunk},
+                mm = {"audio": chunk[0] if len(chunk) == 1 else chunk}
+                if "sample_rate" in metrics:
+                    mm["sample_rate"] = int(metrics["sample_rate"])
+                results.append(OmniRequestOutput.from_diffusion(ids[i], [], prompt, metrics, output.trajectory_latents, mm,
                                                                 "audio"))
             elif supports_video_output(name):
                 results.append(OmniRequestOutput.from_diffusion(ids[i], [], prompt, metrics, output.trajectory_latents,
