@@ -16,7 +16,7 @@ TINY = {
     "GlmImagePipeline": dict(num_layers=1, attention_head_dim=32, num_attention_heads=2, time_embed_dim=32, condition_dim=16,
                              prior_vq_quantizer_codebook_size=64, text_embed_dim=24, in_channels=16, out_channels=16),
     "TinyMMDiTPipeline": {},
-    "FluxPipeline": FLUXY, "Flux2KleinPipeline": FLUXY, "LongCatImagePipeline": FLUXY, "LongCatImageEditPipeline": FLUXY,
+    "FluxPipeline": FLUXY, "Flux2KleinPipeline": dict(FLUXY, out_channels=None, axes_dims_rope=(8, 8, 8, 8), timestep_guidance_channels=32), "LongCatImagePipeline": FLUXY, "LongCatImageEditPipeline": FLUXY,
     "OvisImagePipeline": FLUXY, "StableDiffusion3Pipeline": dict(FLUXY, num_single_layers=0),
     "ZImagePipeline": dict(dim=64, n_layers=1, n_refiner_layers=1, n_heads=2, n_kv_heads=2, cap_feat_dim=32,
                            axes_dims=(8, 12, 12), axes_lens=(128, 32, 32)),

@@ -1,5 +1,5 @@
-"""FLUX text-to-image pipeline and its FLUX.2-klein variant
-(vllm_omni/diffusion/models/flux/pipeline_flux.py, flux2_klein/): guidance-distilled (the
+"""FLUX text-to-image pipeline
+(vllm_omni/diffusion/models/flux/pipeline_flux.py): guidance-distilled (the
 guidance scale is an input of the network, one transformer call per step), T5 states +
 pooled CLIP vector, 2x2 packed latents, shifted flow-match Euler schedule."""
 from __future__ import annotations
@@ -129,8 +129,3 @@ class FluxPipeline(nn.Module):
             if groups[comp] and hasattr(enc, "load_weights"):
                 loaded |= {comp + "." + n for n in enc.load_weights(groups[comp])}
         return loaded
-
-
-class Flux2KleinPipeline(FluxPipeline):
-    """FLUX.2-klein: a smaller distilled FLUX with a Qwen text encoder (no pooled vector)."""
-    default_guidance = 1.0

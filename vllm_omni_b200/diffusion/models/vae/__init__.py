@@ -8,7 +8,7 @@ def build_vae(vae_config: dict | None, family: str = "qwen", with_encoder: bool 
     FLUX / SD3 / Z-Image checkpoints)."""
     vc = dict(vae_config or {})
     name = vc.get("_class_name")
-    if name == "AutoencoderKL" or (name is None and family == "kl"):
+    if name in ("AutoencoderKL", "AutoencoderKLFlux2") or (name is None and family == "kl"):
         from .autoencoder_kl import AutoencoderKL, AutoencoderKLConfig
         return AutoencoderKL(AutoencoderKLConfig.from_dict(vc), with_encoder=with_encoder)
     from .autoencoder_kl_qwenimage import AutoencoderKLQwenImage2d, QwenImageVAEConfig

@@ -22,7 +22,7 @@ _DIFFUSION_MODELS: dict[str, tuple[str, str]] = {
     "WanImageToVideoPipeline": ("wan.pipeline", "WanImageToVideoPipeline"),
     "Wan22TI2VPipeline": ("wan.pipeline", "WanTI2VPipeline"),
     "FluxPipeline": ("flux.pipeline", "FluxPipeline"),
-    "Flux2KleinPipeline": ("flux.pipeline", "Flux2KleinPipeline"),
+    "Flux2KleinPipeline": ("flux2.pipeline", "Flux2KleinPipeline"),
     "ZImagePipeline": ("z_image.pipeline", "ZImagePipeline"),
     "StableDiffusion3Pipeline": ("sd3.pipeline", "StableDiffusion3Pipeline"),
     "LongCatImagePipeline": ("longcat_image.pipeline", "LongCatImagePipeline"),
