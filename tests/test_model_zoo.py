@@ -20,7 +20,9 @@ TINY = {
     "OvisImagePipeline": FLUXY, "StableDiffusion3Pipeline": dict(FLUXY, num_single_layers=0),
     "ZImagePipeline": dict(dim=64, n_layers=1, n_refiner_layers=1, n_heads=2, n_kv_heads=2, cap_feat_dim=32,
                            axes_dims=(8, 12, 12), axes_lens=(128, 32, 32)),
-    "BagelPipeline": dict(dim=64, n_layers=1, n_heads=2, head_dim=32, ffn_dim=64, cap_feat_dim=32, axes_dims_rope=(8, 12, 12)),
+    "BagelPipeline": dict(vocab_size=300, hidden_size=64, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1,
+                          intermediate_size=64, max_latent_size=8, z_channels=16, start_of_image=290, end_of_image=291,
+                          bos_token_id=288, eos_token_id=289),
     "WanPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
     "WanImageToVideoPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
     "Wan22TI2VPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
@@ -51,7 +53,7 @@ def small_vae(monkeypatch):
         monkeypatch.setattr(m, "QwenImageVAEConfig", tiny)
 
 
-@pytest.mark.parametrize("name", sorted(n for n in TINY if n != "BagelPipeline"))
+@pytest.mark.parametrize("name", sorted(TINY))
 def test_pipeline_runs_tiny(name):
     vae = SMALL_KL if name != "StableAudioPipeline" else dict(decoder_channels=8, channel_multiples=(1, 2),
                                                                 downsampling_ratios=(2, 4), sampling_rate=800)
@@ -73,7 +75,7 @@ def test_pipeline_runs_tiny(name):
         o.close()
 
 
-def test_registry_lists_every_family_and_bagel_needs_kv():
+def test_registry_lists_every_family_and_bagel_takes_injected_kv():
     names = supported_models()
     for n in ("QwenImagePipeline", "WanPipeline", "FluxPipeline", "ZImagePipeline", "StableDiffusion3Pipeline",
               "BagelPipeline", "HunyuanImage3Pipeline", "GlmImagePipeline", "LongCatImagePipeline", "OvisImagePipeline",
@@ -82,9 +84,7 @@ def test_registry_lists_every_family_and_bagel_needs_kv():
     o = OmniDiffusion("BagelPipeline", dtype="float32", device="cpu", tf_model_config=TINY["BagelPipeline"], vae_config=SMALL_KL)
     try:
         sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0)
-        with pytest.raises(RuntimeError, match="KV"):
-            o.generate(["x"], sp)
-        sp.past_key_values = [(torch.randn(5, 2, 32), torch.randn(5, 2, 32))]
+        sp.past_key_values = [(torch.randn(5, 1, 32), torch.randn(5, 1, 32))]          # the prompt context of an AR stage
         assert o.generate(["x"], sp)[0].images[0].size == (64, 64)
     finally:
         o.close()

@@ -172,6 +172,34 @@ class Encoder(nn.Module):
 
 
 _OLD_ATTN = {"query": "to_q", "key": "to_k", "value": "to_v", "proj_attn": "to_out.0"}
+_BFL_ATTN = {"q": "to_q", "k": "to_k", "v": "to_v", "proj_out": "to_out.0", "norm": "group_norm"}
+
+
+def bfl_to_diffusers_name(name: str, num_blocks: int) -> str:
+    """Names of the original FLUX autoencoder file (``ae.safetensors``, also what BAGEL ships:
+    ``decoder.up.3.block.0.norm1``, ``decoder.mid.attn_1.q``, ``encoder.down.0.downsample.conv``) -> the
+    diffusers names this module uses.  The original numbers its up stages from the output side."""
+    p = name.split(".")
+    if len(p) < 3 or p[0] not in ("encoder", "decoder"):
+        return name
+    side, rest = p[0], p[1:]
+    if rest[0] == "norm_out":
+        return ".".join([side, "conv_norm_out"] + rest[1:])
+    if rest[0] == "mid":
+        if rest[1] in ("block_1", "block_2"):
+            tail = ["conv_shortcut" if t == "nin_shortcut" else t for t in rest[2:]]
+            return ".".join([side, "mid_block", "resnets", "0" if rest[1] == "block_1" else "1"] + tail)
+        if rest[1] == "attn_1":
+            return ".".join([side, "mid_block", "attentions", "0", _BFL_ATTN.get(rest[2], rest[2])] + rest[3:])
+    if rest[0] in ("up", "down") and len(rest) > 3:
+        i = int(rest[1])
+        blk = ("up_blocks", str(num_blocks - 1 - i)) if rest[0] == "up" else ("down_blocks", str(i))
+        if rest[2] == "block":
+            tail = ["conv_shortcut" if t == "nin_shortcut" else t for t in rest[4:]]
+            return ".".join([side, *blk, "resnets", rest[3]] + tail)
+        if rest[2] in ("upsample", "downsample"):
+            return ".".join([side, *blk, "upsamplers" if rest[2] == "upsample" else "downsamplers", "0"] + rest[3:])
+    return name
 
 
 class AutoencoderKL(nn.Module):
@@ -254,6 +282,8 @@ class AutoencoderKL(nn.Module):
             n = name
             for old, new in _OLD_ATTN.items():
                 n = n.replace(f".attentions.0.{old}.", f".attentions.0.{new}.")
+            if n not in own:
+                n = bfl_to_diffusers_name(name, len(self.cfg.block_out_channels))
             if n not in own:
                 continue
             p = own[n]
