@@ -201,3 +201,26 @@ def test_bagel_stage_text_to_image_and_injected_context():
     img = pipe(OmniDiffusionRequest(prompts=["a cube"], sampling_params=OmniDiffusionSamplingParams(height=32, width=32, num_inference_steps=2, seed=2,
                                                                                                    output_type="pt"), request_ids=["r"])).output
     assert img.shape[-2:] == (32, 32)
+
+
+def test_ar_stage_cache_equals_the_generation_stage_prefill(pair):
+    """The AR stage (understanding weights of the same checkpoint, ``llm_config`` geometry) fills a paged
+    KV cache whose rows equal what the generation stage would prefill itself: the context it hands over
+    is exactly the one the denoiser expects."""
+    from vllm_omni_b200.models.local_decode import LocalDecodeSession
+    from vllm_omni_b200.models.text import build_text_model
+    sd, m = pair
+    c = CFG
+    hf = {"architectures": ["BagelForConditionalGeneration"],
+          "llm_config": dict(vocab_size=c.vocab_size, hidden_size=c.hidden_size, num_hidden_layers=c.num_hidden_layers,
+                             num_attention_heads=c.num_attention_heads, num_key_value_heads=c.num_key_value_heads,
+                             intermediate_size=c.intermediate_size, rope_theta=c.rope_theta, rms_norm_eps=c.rms_norm_eps)}
+    ar = build_text_model("thinker", hf, torch.float32, "cpu")
+    loaded = ar.load_weights(sd.items())
+    assert "model.layers.0.self_attn.q_norm.weight" in loaded and not any("moe_gen" in n for n in loaded)
+    ids = torch.tensor([c.bos_token_id, 5, 9, 11, 3, c.eos_token_id])
+    sess = LocalDecodeSession(ar.decoder, 32)
+    sess.prefill(ids=ids)
+    ctx = m.prefill_text(ids)
+    for (kp, vp), (k, v) in zip(sess.caches, ctx):
+        assert (kp.flatten(0, 1)[:6] - k).abs().max().item() < 1e-5 and (vp.flatten(0, 1)[:6] - v).abs().max().item() < 1e-5

@@ -67,4 +67,7 @@ class TextDecoderModel(StageModel):
         self.decoder = QwenDecoderModel(cfg, dtype, device)
 
     def load_weights(self, weights):
-        return self.decoder.load_weights(weights)
+        pre = "language_model."                          # multimodal checkpoints nest the LM under this prefix
+        strip = lambda n: n[len(pre):] if n.startswith(pre) else n
+        loaded = self.decoder.load_weights((strip(n), w) for n, w in weights)
+        return loaded

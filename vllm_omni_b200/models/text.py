@@ -1,4 +1,6 @@
-"""Plain causal-LM stages (Qwen2 / Qwen3 / Qwen3-MoE text models)."""
+"""Plain causal-LM stages (Qwen2 / Qwen3 / Qwen3-MoE text models) and the understanding half of BAGEL:
+its checkpoint nests a Qwen2 config with per-head q/k norms under ``llm_config`` and names the weights
+``language_model.model.*`` (the ``*_moe_gen`` twins belong to the image-generation stage and are skipped)."""
 from __future__ import annotations
 
 from .base import TextDecoderModel
@@ -7,6 +9,10 @@ from .qwen_decoder import DecoderConfig
 
 def build_text_model(model_stage, hf_config: dict, dtype, device, **kw):
     cfg = hf_config.get("text_config", hf_config)
+    if hf_config.get("llm_config"):                       # BAGEL
+        cfg = dict(hf_config["llm_config"])
+        cfg.setdefault("qk_norm", True)
+        cfg.setdefault("attention_bias", True)
     dc = DecoderConfig.from_dict(cfg) if cfg else DecoderConfig()
     if "num_experts" not in cfg:
         dc.num_experts = 0
