@@ -441,7 +441,15 @@ def tts_folder(tmp_path_factory):
             q.copy_(torch.randn_like(q) * (0.08 if q.dim() > 1 else 0.1))
     (tmp_path / "speech_tokenizer").mkdir()
     dcd = {k: (list(v) if isinstance(v, tuple) else v) for k, v in dc.__dict__.items()}
-    (tmp_path / "speech_tokenizer" / "config.json").write_text(json.dumps({"model_type": "qwen3_tts_tokenizer_12hz", "decoder_config": dcd}))
+    import transformers.models.mimi.modeling_mimi as MM
+    mc = MM.MimiConfig(num_filters=4, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2, head_dim=8,
+                       intermediate_size=32, sliding_window=6, codebook_size=dc.codebook_size, codebook_dim=8,
+                       vector_quantization_hidden_dimension=8, num_quantizers=6, num_semantic_quantizers=1,
+                       upsampling_ratios=[4, 3, 2, 2], frame_rate=250.0, sampling_rate=24000, upsample_groups=16)
+    mimi = MM.MimiModel(mc).float().eval()
+    (tmp_path / "speech_tokenizer" / "config.json").write_text(json.dumps({
+        "model_type": "qwen3_tts_tokenizer_12hz", "decoder_config": dcd, "encoder_config": mc.to_dict(),
+        "encoder_valid_num_quantizers": dc.num_quantizers}))
     G, bins, cd = dc.num_quantizers, dc.codebook_size, dc.codebook_dim
     tsd = {"decoder." + k: v.detach().clone().contiguous() for k, v in _decoder_checkpoint_names(dec).items()}
     table = torch.zeros(G, bins, cd)
@@ -453,13 +461,13 @@ def tts_folder(tmp_path_factory):
             tsd[f"decoder.quantizer.{grp}.vq.layers.{li}._codebook.embedding_sum"] = s
             tsd[f"decoder.quantizer.{grp}.vq.layers.{li}._codebook.cluster_usage"] = u
             table[g] = (s / u[:, None]) @ proj[:, :, 0].t()
-    tsd["encoder.placeholder"] = torch.zeros(1)             # the encoder half of the file is ignored
+    tsd.update({"encoder." + k: v.detach().clone().contiguous() for k, v in mimi.state_dict().items()})
     save_file(tsd, str(tmp_path / "speech_tokenizer" / "model.safetensors"))
     with torch.no_grad():
         dec.code_table.copy_(table.view(G * bins, cd))
     (tmp_path / "stages.yaml").write_text(TTS_YAML)
 
-    return tmp_path, cfg, oracle, dec, sd
+    return tmp_path, cfg, oracle, dec, sd, mimi
 
 
 def test_checkpoint_folder_through_the_pipeline(tts_folder):
@@ -468,7 +476,7 @@ def test_checkpoint_folder_through_the_pipeline(tts_folder):
     from vllm_omni_b200.entrypoints.omni import Omni
     from vllm_omni_b200.entrypoints.stage_runtime import inproc_adapter
     from vllm_omni_b200.inputs import SamplingParams
-    tmp_path, cfg, oracle, dec, sd = tts_folder
+    tmp_path, cfg, oracle, dec, sd, mimi = tts_folder
     dc = cfg.tokenizer_decoder
     ids = _wrapped(cfg, TEXT)
     with torch.no_grad():
@@ -491,6 +499,14 @@ def test_checkpoint_folder_through_the_pipeline(tts_folder):
                                                                    "x_vector_only_mode": True}}
         outs = o.generate([p2], [SamplingParams(temperature=0.0, max_tokens=4, seed=1)])
         assert outs[0].multimodal_output["audio"].numel() == outs[0].multimodal_output["codes"].shape[0] * dc.total_upsample
+        # in-context cloning: the clip's frames come from the tokenizer's own encoder (= transformers' Mimi on the same weights)
+        voice = live.create_voice_clone_prompt(torch.tensor(clip), 24000, ref_ids=[41, 42])
+        want_code = mimi.encode(torch.tensor(clip)[None, None], num_quantizers=dc.num_quantizers).audio_codes[0].t()
+        assert voice["icl_mode"] and torch.equal(voice["ref_code"], want_code[: voice["ref_code"].shape[0]])
+        p3 = {"prompt_token_ids": TEXT, "additional_information": {"task_type": "Base", "ref_audio": clip, "ref_sr": 24000,
+                                                                   "ref_token_ids": [41, 42]}}
+        outs = o.generate([p3], [SamplingParams(temperature=0.0, max_tokens=3, seed=1)])
+        assert outs[0].multimodal_output["codes"].shape[1] == dc.num_quantizers and outs[0].multimodal_output["audio"].numel() > 0
     finally:
         o.close()
 
@@ -523,3 +539,39 @@ def test_speech_endpoint_on_a_tts_checkpoint(tts_folder):
             assert c.post("/v1/audio/speech", json={"input": "x", "task_type": "VoiceDesign"}).status_code == 400
     finally:
         eng.close()
+
+
+def test_tokenizer_encoder_against_hf_mimi():
+    """The 12 Hz tokenizer's encoder is transformers' Mimi analysis path: same frames from the same
+    state dict (SEANet stack, sliding-window transformer, stride-2 downsampling, split quantizer)."""
+    M = pytest.importorskip("transformers.models.mimi.modeling_mimi")
+    from vllm_omni_b200.models.qwen3_tts.tokenizer_12hz_encoder import MimiEncoderConfig, Qwen3TTSTokenizerEncoder
+    torch.manual_seed(0)
+    hc = M.MimiConfig(num_filters=4, hidden_size=32, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=2, head_dim=16,
+                      intermediate_size=64, sliding_window=6, codebook_size=32, codebook_dim=8, vector_quantization_hidden_dimension=8,
+                      num_quantizers=6, num_semantic_quantizers=1, upsampling_ratios=[4, 3, 2, 2], frame_rate=250.0, sampling_rate=24000,
+                      upsample_groups=32)
+    hf = M.MimiModel(hc).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            p.copy_(torch.randn_like(p) * (0.2 if p.dim() > 1 else 0.1) + (1.0 if "layernorm" in n and n.endswith("weight") else 0.0))
+        for n, b in hf.named_buffers():
+            if n.endswith("embed_sum"):
+                b.copy_(torch.randn_like(b))
+            elif n.endswith("cluster_usage"):
+                b.copy_(torch.rand_like(b) + 0.5)
+    cfg = MimiEncoderConfig.from_dict(hc.to_dict())
+    assert cfg.encodec_frame_rate == 500.0
+    m = Qwen3TTSTokenizerEncoder(cfg, valid_quantizers=4, device="cpu")
+    sd = {k: v for k, v in hf.state_dict().items()
+          if k.startswith(("encoder.", "encoder_transformer.", "downsample.", "quantizer.")) and "output_proj" not in k and "initialized" not in k}
+    loaded = m.load_weights(sd.items())
+    assert loaded == set(sd), sorted(set(sd) - loaded)[:5]
+    wav = torch.randn(1, 1, 1000) * 0.3
+    with torch.no_grad():
+        ref_emb = hf.downsample(hf.encoder_transformer(hf.encoder(wav).transpose(1, 2))[0].transpose(1, 2))
+        emb = m.features(wav[:, 0])
+        assert ref_emb.shape == emb.shape and (ref_emb - emb).abs().max().item() < 1e-4 * max(1.0, ref_emb.abs().max().item())
+        ref = hf.encode(wav, num_quantizers=4).audio_codes[0]                # [K, T']
+        got = m.encode(wav[0, 0])
+    assert got.shape == (ref.shape[1], 4) and torch.equal(got, ref.t())

@@ -158,6 +158,7 @@ class Qwen3TTSModel(StageModel):
         self.code_predictor = CodePredictor(cfg.code_predictor, Dt, dtype, device)
         self.speaker_encoder = Qwen3TTSSpeakerEncoder(cfg.speaker_encoder, device) if cfg.speaker_encoder else None
         self.decoder = Qwen3TTSTokenizerDecoder(cfg.tokenizer_decoder, dtype, device)     # speech tokenizer decoder
+        self.tokenizer_encoder = None                   # speech tokenizer encoder, built when the checkpoint ships one
         self.voices: dict[str, dict] = {}               # registered cloned voices
         self.text_tokenizer = None                      # set by the engine; turns instruction / transcript strings into ids
         self._session = None
@@ -358,11 +359,17 @@ class Qwen3TTSModel(StageModel):
     def create_voice_clone_prompt(self, ref_audio: torch.Tensor, sr: int, ref_ids=None, ref_code=None,
                                   x_vector_only_mode: bool = False, name: str | None = None) -> dict:
         """Reference clip -> {"ref_spk_embedding", "ref_code", "x_vector_only_mode", "icl_mode", "ref_ids"}.
-        In-context mode needs the clip's codec frames ``ref_code`` [T, G] (from the speech tokenizer's
-        encoder) and its transcript ``ref_ids``; without frames only the x-vector is used."""
+        In-context mode needs the clip's codec frames ``ref_code`` [T, G] — given, or computed by the
+        speech tokenizer's encoder when the checkpoint ships it — and its transcript ``ref_ids``; without
+        frames only the x-vector is used."""
         if self.speaker_encoder is None:
             raise ValueError("this checkpoint has no speaker encoder: voice cloning needs the 'base' model type")
-        xvec = self.speaker_encoder.embed_audio(torch.as_tensor(ref_audio, dtype=torch.float32), sr)
+        ref_audio = torch.as_tensor(ref_audio, dtype=torch.float32)
+        xvec = self.speaker_encoder.embed_audio(ref_audio, sr)
+        if ref_code is None and not x_vector_only_mode and self.tokenizer_encoder is not None:
+            from .speaker import resample_sinc
+            clip = resample_sinc(ref_audio.reshape(1, -1), int(sr), self.tokenizer_encoder.cfg.sampling_rate)[0]
+            ref_code = self.tokenizer_encoder.encode(clip)
         icl = (not x_vector_only_mode) and ref_code is not None
         if icl and not ref_ids:
             raise ValueError("in-context voice cloning needs the reference transcript (ref_ids)")
@@ -451,17 +458,27 @@ class Qwen3TTSModel(StageModel):
             return 0
         from ...diffusion.loader import _shard_files, safetensors_weights_iterator
         cfg_path = os.path.join(folder, "config.json")
+        tok_cfg = {}
         if os.path.exists(cfg_path):
             with open(cfg_path) as f:
-                dc = TokenizerDecoderConfig.from_dict((json.load(f).get("decoder_config") or {}))
+                tok_cfg = json.load(f)
+            dc = TokenizerDecoderConfig.from_dict(tok_cfg.get("decoder_config") or {})
             if dc != self.cfg.tokenizer_decoder:
                 self.cfg.tokenizer_decoder = dc
                 self.decoder = Qwen3TTSTokenizerDecoder(dc, self.dtype_, self.text_embedding.device)
         files = _shard_files(folder)
         if not files:
             return 0
-        it = ((n[len("decoder."):], w) for n, w in safetensors_weights_iterator(files) if n.startswith("decoder."))
-        return len(self.decoder.load_weights(it))
+        ws = list(safetensors_weights_iterator(files))
+        n = len(self.decoder.load_weights((k[len("decoder."):], w) for k, w in ws if k.startswith("decoder.")))
+        enc = [(k[len("encoder."):], w) for k, w in ws if k.startswith("encoder.")]
+        if self.speaker_encoder is not None and tok_cfg.get("encoder_config") and len(enc) > 1:
+            from .tokenizer_12hz_encoder import MimiEncoderConfig, Qwen3TTSTokenizerEncoder
+            self.tokenizer_encoder = Qwen3TTSTokenizerEncoder(MimiEncoderConfig.from_dict(tok_cfg["encoder_config"]),
+                                                              int(tok_cfg.get("encoder_valid_num_quantizers", 16)),
+                                                              self.text_embedding.device)
+            n += len(self.tokenizer_encoder.load_weights(enc))
+        return n
 
 
 def load_reference_audio(ref, sr=None):
