@@ -229,8 +229,8 @@ def build_app(engine, model_name: str = "omni", kind: str = "omni", default_stag
     async def speech(req: OpenAICreateSpeechRequest):
         if not req.input or not req.input.strip():
             return _err(400, "input must not be empty")
-        if req.response_format not in ("wav", "pcm"):
-            return _err(400, f"response_format {req.response_format!r} is not available in this build; use wav or pcm")
+        if req.response_format not in ("wav", "pcm", "flac"):
+            return _err(400, f"response_format {req.response_format!r} is not available in this build; use wav, pcm or flac")
         task = req.task_type or ("Base" if req.ref_audio else "CustomVoice")
         known = _known_voices()
         voice = req.voice

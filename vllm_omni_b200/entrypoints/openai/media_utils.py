@@ -54,13 +54,113 @@ def pcm_bytes(audio) -> bytes:
     return (np.clip(a.reshape(-1), -1.0, 1.0) * 32767.0).astype("<i2").tobytes()
 
 
+# ---------------------------------------------------------------------------------------------- FLAC
+_CRC8 = [0] * 256
+_CRC16 = [0] * 256
+for _i in range(256):
+    _c8, _c16 = _i, _i << 8
+    for _ in range(8):
+        _c8 = ((_c8 << 1) ^ 0x07) & 0xFF if _c8 & 0x80 else (_c8 << 1) & 0xFF
+        _c16 = ((_c16 << 1) ^ 0x8005) & 0xFFFF if _c16 & 0x8000 else (_c16 << 1) & 0xFFFF
+    _CRC8[_i], _CRC16[_i] = _c8, _c16
+_FLAC_RATES = {88200: 1, 176400: 2, 192000: 3, 8000: 4, 16000: 5, 22050: 6, 24000: 7, 32000: 8, 44100: 9, 48000: 10, 96000: 11}
+
+
+def _bits(value: int, n: int) -> np.ndarray:
+    return np.array([(value >> (n - 1 - i)) & 1 for i in range(n)], dtype=np.uint8)
+
+
+def _utf8_number(v: int) -> list:
+    """The variable-length frame number of a FLAC frame header (UTF-8's byte layout, up to 36 bits)."""
+    if v < 0x80:
+        return [v]
+    for nbytes, lead_bits in ((2, 5), (3, 4), (4, 3), (5, 2), (6, 1), (7, 0)):
+        if v < (1 << (lead_bits + 6 * (nbytes - 1))):
+            tail = []
+            for _ in range(nbytes - 1):
+                tail.append(0x80 | (v & 0x3F))
+                v >>= 6
+            return [((0xFF << (8 - nbytes)) & 0xFF) | v] + tail[::-1]
+    raise ValueError("frame number too large")
+
+
+def _rice_bits(res: np.ndarray, k: int) -> np.ndarray:
+    """Rice code of signed residuals with parameter k: zig-zag, quotient in unary (zeros then a one), k-bit remainder."""
+    u = np.where(res >= 0, res << 1, ((-res) << 1) - 1).astype(np.int64)
+    q = u >> k
+    length = q + 1 + k
+    start = np.concatenate([[0], np.cumsum(length)[:-1]])
+    out = np.zeros(int(length.sum()), dtype=np.uint8)
+    out[start + q] = 1
+    for j in range(k):
+        out[start + q + 1 + j] = (u >> (k - 1 - j)) & 1
+    return out
+
+
+def flac_bytes(audio, sample_rate: int = 24000, block: int = 4096) -> bytes:
+    """float waveform in [-1, 1], [T] or [C, T] with C <= 2 -> a 16-bit FLAC stream: fixed block size,
+    per channel the best of the fixed predictors of order 0..2 with one Rice partition (lossless for the
+    16-bit samples; STREAMINFO carries their MD5)."""
+    import hashlib
+    a = audio.detach().float().cpu().numpy() if isinstance(audio, torch.Tensor) else np.asarray(audio, dtype=np.float32)
+    a = a.reshape(1, -1) if a.ndim == 1 else a
+    C, T = a.shape
+    if C > 2:
+        raise ValueError("FLAC output supports mono or stereo")
+    pcm = (np.clip(a, -1.0, 1.0) * 32767.0).astype(np.int64)
+    md5 = hashlib.md5(pcm.T.astype("<i2").tobytes()).digest()
+    frames, sizes = [], []
+    for fi, s in enumerate(range(0, max(T, 1), block)):
+        x = pcm[:, s:s + block]
+        n = x.shape[1]
+        if n == 0:
+            break
+        hdr = [0xFF, 0xF8, (7 << 4) | _FLAC_RATES.get(sample_rate, 0), ((C - 1) << 4) | (4 << 1)]
+        hdr += _utf8_number(fi)
+        hdr += [((n - 1) >> 8) & 0xFF, (n - 1) & 0xFF]      # 16-bit block size - 1 (block-size code 0111)
+        c8 = 0
+        for b in hdr:
+            c8 = _CRC8[c8 ^ b]
+        hdr.append(c8)
+        bits = [np.unpackbits(np.array(hdr, dtype=np.uint8))]
+        for ch in range(C):
+            v = x[ch]
+            best = None
+            for order in range(min(3, n)):
+                r = v[order:] if order == 0 else (v[1:] - v[:-1] if order == 1 else v[2:] - 2 * v[1:-1] + v[:-2])
+                mean = float(np.abs(r).mean()) if r.size else 0.0
+                k = min(14, max(0, int(np.ceil(np.log2(mean + 1e-9))) if mean > 1 else 0))
+                cost = int(((np.where(r >= 0, r << 1, ((-r) << 1) - 1) >> k) + 1 + k).sum()) if r.size else 0
+                if best is None or cost < best[0]:
+                    best = (cost, order, k, r)
+            _, order, k, r = best
+            sub = [_bits((0b001000 | order) << 1, 8)]
+            sub += [_bits(int(w) & 0xFFFF, 16) for w in v[:order]]
+            sub += [_bits(0, 2), _bits(0, 4), _bits(k, 4), _rice_bits(r, k)]
+            bits += sub
+        allbits = np.concatenate(bits)
+        if allbits.size % 8:
+            allbits = np.concatenate([allbits, np.zeros(8 - allbits.size % 8, dtype=np.uint8)])
+        body = np.packbits(allbits).tobytes()
+        c16 = 0
+        for b in body:
+            c16 = ((c16 << 8) & 0xFFFF) ^ _CRC16[(c16 >> 8) ^ b]
+        frames.append(body + struct.pack(">H", c16))
+        sizes.append(len(frames[-1]))
+    info = _bits(block, 16).tolist() + _bits(block, 16).tolist() + _bits(min(sizes) if sizes else 0, 24).tolist() + \
+        _bits(max(sizes) if sizes else 0, 24).tolist() + _bits(sample_rate, 20).tolist() + _bits(C - 1, 3).tolist() + \
+        _bits(15, 5).tolist() + _bits(T, 36).tolist()
+    streaminfo = np.packbits(np.array(info, dtype=np.uint8)).tobytes() + md5
+    return b"fLaC" + bytes([0x80]) + struct.pack(">I", len(streaminfo))[1:] + streaminfo + b"".join(frames)
+
+
 AUDIO_MEDIA_TYPES = {"wav": "audio/wav", "pcm": "audio/pcm", "flac": "audio/flac", "mp3": "audio/mpeg",
                      "aac": "audio/aac", "opus": "audio/ogg"}
 
 
 def encode_audio(audio, sample_rate: int, fmt: str = "wav", speed: float = 1.0) -> tuple[bytes, str]:
-    """wav and pcm are encoded here; compressed formats need an encoder library that this
-    image does not ship, so they are refused with a clear message."""
+    """wav, pcm and flac are encoded here; the lossy formats (mp3, aac, opus) need an encoder library
+    that this image does not ship, so they are refused with a clear message."""
     if speed and abs(speed - 1.0) > 1e-6:
         a = audio if isinstance(audio, torch.Tensor) else torch.as_tensor(np.asarray(audio))
         n = max(1, int(round(a.numel() / speed)))
@@ -70,7 +170,9 @@ def encode_audio(audio, sample_rate: int, fmt: str = "wav", speed: float = 1.0) 
         return wav_bytes(audio, sample_rate), AUDIO_MEDIA_TYPES["wav"]
     if fmt == "pcm":
         return pcm_bytes(audio), AUDIO_MEDIA_TYPES["pcm"]
-    raise ValueError(f"response_format {fmt!r} needs an audio encoder that is not installed; use wav or pcm")
+    if fmt == "flac":
+        return flac_bytes(audio, sample_rate), AUDIO_MEDIA_TYPES["flac"]
+    raise ValueError(f"response_format {fmt!r} needs an audio encoder that is not installed; use wav, pcm or flac")
 
 
 def frames_to_gif_bytes(frames: np.ndarray, fps: int = 16) -> bytes:
