@@ -43,3 +43,56 @@ def test_dbcache_thresholds_and_taylorseer():
                                                          "max_continuous_cached_steps": 2, "enable_taylorseer": True})
     assert 2 <= fast[1]["skipped_steps"] <= 5 and fast[1]["block_skip_ratio"] > 0
     assert torch.isfinite(_latent(fast)).all()
+
+
+# ----------------------------------------------------------------------------- the other model families
+def _zoo(name, **kw):
+    from test_model_zoo import SMALL_KL, TINY
+    import importlib
+    import vllm_omni_b200.diffusion.models.vae.autoencoder_kl_qwenimage as vq
+    orig = vq.QwenImageVAEConfig
+    mods = [importlib.import_module(m) for m in ("vllm_omni_b200.diffusion.models.qwen_image.pipeline",
+                                                 "vllm_omni_b200.diffusion.models.wan.pipeline")]
+    tiny = lambda *a, **k: orig(*a, **{**dict(base_dim=8, num_res_blocks=1), **k})
+    for m in mods:
+        m.QwenImageVAEConfig = tiny
+    tf = dict(TINY[name])
+    for k in ("num_layers", "num_single_layers", "n_layers", "num_hidden_layers"):
+        if k in tf:
+            tf[k] = 3                                         # enough blocks for first / middle / last groups
+    try:
+        o = OmniDiffusion(name, dtype="float32", device="cpu", tf_model_config=tf, vae_config=SMALL_KL, output_type="latent", **kw)
+        try:
+            sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=6, seed=0, num_frames=5, guidance_scale=3.0,
+                                             output_type="latent")
+            out = o.generate([{"prompt": "a small test", "negative_prompt": " "}], sp)[0]
+            runner = o.engine.executor.worker.model_runner
+            stats = runner.cache_backend.summary() if runner.cache_backend else None
+            lat = out.latents if out.latents is not None else (out.images[0] if out.images else out.multimodal_output.get("video"))
+            return torch.as_tensor(lat).float(), stats
+        finally:
+            o.close()
+    finally:
+        for m in mods:
+            m.QwenImageVAEConfig = orig
+
+
+import pytest
+
+
+@pytest.mark.parametrize("name", ["FluxPipeline", "StableDiffusion3Pipeline", "Flux2KleinPipeline", "ZImagePipeline", "WanPipeline",
+                                  "BagelPipeline", "LongCatImagePipeline", "OvisImagePipeline"])
+def test_cache_backends_on_every_family_with_a_block_stack(name):
+    """Thresholds of zero reproduce the uncached sample exactly; permissive thresholds skip work.  Pipelines
+    that evaluate the guidance branches in separate calls (FLUX.2-klein, BAGEL) keep one state per branch."""
+    base, _ = _zoo(name)
+    tea0, s = _zoo(name, cache_backend="tea_cache", cache_config={"rel_l1_thresh": 0.0, "coefficients": [0, 0, 0, 1.0, 0]})
+    assert s["skipped_steps"] == 0 and s["steps"] >= 5 and torch.allclose(base, tea0, atol=1e-5)
+    tea, s = _zoo(name, cache_backend="tea_cache", cache_config={"rel_l1_thresh": 1e9, "coefficients": [0, 0, 0, 1.0, 0]})
+    assert s["skipped_steps"] >= 2 and torch.isfinite(tea).all()
+    db0, s = _zoo(name, cache_backend="cache_dit", cache_config={"residual_diff_threshold": 0.0, "max_warmup_steps": 0})
+    assert s["skipped_steps"] == 0 and torch.allclose(base, db0, atol=1e-5)
+    db, s = _zoo(name, cache_backend="cache_dit", cache_config={"residual_diff_threshold": 1e9, "max_warmup_steps": 1,
+                                                                "max_continuous_cached_steps": 2, "enable_taylorseer": True,
+                                                                "Fn_compute_blocks": 1, "Bn_compute_blocks": 1})
+    assert s["skipped_steps"] >= 1 and s["block_skip_ratio"] > 0 and torch.isfinite(db).all()

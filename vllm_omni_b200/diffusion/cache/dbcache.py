@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from ...ops import fused
-from .base import CacheBackend
+from .base import BlockStack, CacheBackend
 
 SCM_POLICIES = {   # 1 = compute, 0 = may use the cache; the pattern repeats over the steps
     "slow": [1, 1, 0, 1, 1, 0], "medium": [1, 0, 1, 0], "fast": [1, 0, 0, 1, 0, 0], "ultra": [1, 0, 0, 0],
@@ -49,6 +49,7 @@ class TaylorSeer:
 
 class DBCacheBackend(CacheBackend):
     name = "cache_dit"
+    _branch_attrs = ("step", "cached_steps", "cont", "prev_fn_res", "mid_res", "seers", "state")
 
     def __init__(self, config):
         super().__init__(config)
@@ -70,9 +71,9 @@ class DBCacheBackend(CacheBackend):
         self.cont = 0
         self.prev_fn_res = None
         self.mid_res = None
-        self.seer_img = TaylorSeer(self.order)
-        self.seer_txt = TaylorSeer(self.order)
+        self.seers: list = []
         self.state = None
+        self._remember_fresh_state()
 
     def _may_cache(self) -> bool:
         if self.step < self.warmup:
@@ -87,43 +88,53 @@ class DBCacheBackend(CacheBackend):
                 return False
         return True
 
-    def _hook(self, model, run_blocks, img, txt, mods, cos, sin, kv_lens, ws, temb):
-        L = model.cfg.num_layers
+    def on_stack(self, stack: BlockStack) -> tuple:
+        self._switch_branch(stack.branch)
+        L, states = stack.num_blocks, stack.states
         Fn, Bn = min(self.Fn, L), min(self.Bn, max(0, L - self.Fn))
-        img_in = img.clone()
-        run_blocks(img, txt, mods, cos, sin, kv_lens, ws, 0, Fn)
-        fn_res = img - img_in
+        first_in = states[0].clone()
+        states = stack.run(states, 0, Fn)
+        fn_res = states[0] - first_in
         use_cache = False
-        if self.prev_fn_res is not None and self.mid_res is not None and self._may_cache():
+        if self.prev_fn_res is not None and self.mid_res is not None and self._may_cache() \
+                and self.prev_fn_res.shape == fn_res.shape:
             if self.state is None:
-                self.state = fused.RelL1State(img.device, None, self.thresh)
+                self.state = fused.RelL1State(fn_res.device, None, self.thresh)
             self.state.reset()
             fused.rel_l1_update(fn_res.contiguous(), self.prev_fn_res, self.state)
             use_cache = bool(self.state.state[2].item() > 0.5)
         if use_cache:
-            if self.use_taylor and self.seer_img.derivs:
-                img.add_(self.seer_img.predict(self.step))
-                txt.add_(self.seer_txt.predict(self.step))
+            if self.use_taylor and self.seers and self.seers[0].derivs:
+                states = tuple(s.add_(seer.predict(self.step)) for s, seer in zip(states, self.seers))
             else:
-                img.add_(self.mid_res[0])
-                txt.add_(self.mid_res[1])
+                states = tuple(s.add_(r) for s, r in zip(states, self.mid_res))
             self.cached_steps += 1
             self.cont += 1
             self.stats["skipped_steps"] += 1
             self.stats["skipped_blocks"] += L - Fn - Bn
             self.stats["computed_blocks"] += Fn + Bn
         else:
-            i0, t0 = img.clone(), txt.clone()
-            run_blocks(img, txt, mods, cos, sin, kv_lens, ws, Fn, L - Bn)
-            self.mid_res = (img - i0, txt - t0)
+            before = tuple(s.clone() for s in states)
+            states = stack.run(states, Fn, L - Bn)
+            self.mid_res = tuple(o - b for o, b in zip(states, before))
             self.prev_fn_res = fn_res.contiguous()
             if self.use_taylor:
-                self.seer_img.update(self.mid_res[0], self.step)
-                self.seer_txt.update(self.mid_res[1], self.step)
+                if len(self.seers) != len(states):
+                    self.seers = [TaylorSeer(self.order) for _ in states]
+                for seer, r in zip(self.seers, self.mid_res):
+                    seer.update(r, self.step)
             self.cont = 0
             self.stats["computed_blocks"] += L
         if Bn:
-            run_blocks(img, txt, mods, cos, sin, kv_lens, ws, L - Bn, L)
+            states = stack.run(states, L - Bn, L)
         self.step += 1
         self.stats["steps"] += 1
-        return img, txt
+        return states
+
+    def _hook(self, model, run_blocks, img, txt, mods, cos, sin, kv_lens, ws, temb):
+        """Qwen-Image entry: blocks run in place on the two streams."""
+        def run(states, a, b):
+            if b > a:
+                run_blocks(img, txt, mods, cos, sin, kv_lens, ws, a, b)
+            return (img, txt)
+        return self.on_stack(BlockStack(model.cfg.num_layers, (img, txt), None, run))

@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from ...ops import fused
-from .base import CacheBackend
+from .base import BlockStack, CacheBackend
 
 MODEL_COEFFICIENTS = {
     "FluxTransformer2DModel": [4.98651651e02, -2.83781631e02, 5.58554382e01, -3.82021401e00, 2.64230861e-01],
@@ -28,6 +28,7 @@ MODEL_COEFFICIENTS = {
 
 class TeaCacheBackend(CacheBackend):
     name = "tea_cache"
+    _branch_attrs = ("step", "state", "prev_mod", "residual")
 
     def __init__(self, config):
         super().__init__(config)
@@ -43,6 +44,7 @@ class TeaCacheBackend(CacheBackend):
         super().enable(pipeline)
         if self.coefficients is None:
             name = type(self.transformer).__name__
+            name = {"BagelMoT": "Bagel"}.get(name, name)
             self.coefficients = MODEL_COEFFICIENTS.get(name, MODEL_COEFFICIENTS["QwenImageTransformer2DModel"])
         if len(self.coefficients) != 5:
             raise ValueError(f"coefficients must contain exactly 5 elements, got {len(self.coefficients)}")
@@ -54,30 +56,39 @@ class TeaCacheBackend(CacheBackend):
         self.state = None
         self.prev_mod = None
         self.residual = None
+        self._remember_fresh_state()
 
-    def _hook(self, model, run_blocks, img, txt, mods, cos, sin, kv_lens, ws, temb):
-        D = model.cfg.inner_dim
-        m0 = mods[:, 0, 0]
-        cur = fused.norm_modulate(img, shift=m0[:, 0:D], scale=m0[:, D:2 * D], eps=model.cfg.eps)
+    def on_stack(self, stack: BlockStack) -> tuple:
+        self._switch_branch(stack.branch)
+        cur = stack.probe.contiguous()
+        states, L = stack.states, stack.num_blocks
         if self.state is None:
-            self.state = fused.RelL1State(img.device, self.coefficients, self.thresh)
+            self.state = fused.RelL1State(cur.device, self.coefficients, self.thresh)
         first_or_last = self.step == 0 or (self.num_steps and self.step == self.num_steps - 1)
         skip = False
-        if self.prev_mod is not None and self.residual is not None:
+        if self.prev_mod is not None and self.residual is not None and self.prev_mod.shape == cur.shape:
             fused.rel_l1_update(cur, self.prev_mod, self.state, force_compute=bool(first_or_last))
             skip = bool(self.state.state[2].item() > 0.5)       # the one host read-back of this step
         self.prev_mod = cur
         self.step += 1
         self.stats["steps"] += 1
-        L = model.cfg.num_layers
         if skip:
-            img.add_(self.residual[0])
-            txt.add_(self.residual[1])
             self.stats["skipped_steps"] += 1
             self.stats["skipped_blocks"] += L
-            return img, txt
-        img0, txt0 = img.clone(), txt.clone()
-        run_blocks(img, txt, mods, cos, sin, kv_lens, ws)
-        self.residual = (img - img0, txt - txt0)
+            return tuple(s.add_(r) for s, r in zip(states, self.residual))
+        before = tuple(s.clone() for s in states)
+        out = stack.run(states, 0, L)
+        self.residual = tuple(o - b for o, b in zip(out, before))
         self.stats["computed_blocks"] += L
-        return img, txt
+        return out
+
+    def _hook(self, model, run_blocks, img, txt, mods, cos, sin, kv_lens, ws, temb):
+        """Qwen-Image entry: the probe is the image stream under block 0's modulation; blocks run in place."""
+        D = model.cfg.inner_dim
+        m0 = mods[:, 0, 0]
+        cur = fused.norm_modulate(img, shift=m0[:, 0:D], scale=m0[:, D:2 * D], eps=model.cfg.eps)
+
+        def run(states, a, b):
+            run_blocks(img, txt, mods, cos, sin, kv_lens, ws, a, b)
+            return (img, txt)
+        return self.on_stack(BlockStack(model.cfg.num_layers, (img, txt), cur, run))

@@ -138,6 +138,7 @@ class BagelMoT(nn.Module):
         self.vae2llm, self.llm2vae = FusedLinear(c.patch_latent_dim, D, **kw), FusedLinear(D, c.patch_latent_dim, **kw)
         self.latent_pos_embed = nn.Parameter(sincos_2d_table(D, c.max_latent_size).to(**kw), requires_grad=False)
         self.inv_freq = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, dtype=torch.float32) / c.head_dim))
+        self.stack_hook = None            # cache backends: called per velocity evaluation with a BlockStack over the layers
 
     # ------------------------------------------------------------------ helpers
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
@@ -206,9 +207,30 @@ class BagelMoT(nn.Module):
             x = s.down(fused.silu_mul(s.gate_up(h)), residual=x)
         return out
 
+    def _gen_layer(self, li, x, N, cos, sin, past):
+        """One layer in generation mode: latent rows [0, N) on the generation weights, marker rows on the understanding weights."""
+        c = self.cfg
+        eps = c.rms_norm_eps
+        B, S = x.shape[0], x.shape[1]
+        layer = self.layers[li]
+        g, u = layer.gen, layer.und
+        hv = fused.norm_modulate(x[:, :N].contiguous(), weight=g.input_layernorm, rms=True, eps=eps)
+        ht = fused.norm_modulate(x[:, N:].contiguous(), weight=u.input_layernorm, rms=True, eps=eps)
+        qkv = torch.cat([g.qkv(hv), u.qkv(ht)], dim=1).contiguous()
+        qkv = self._norm_rope(qkv, cos, sin, g.q_norm, g.k_norm, u.q_norm, u.k_norm, N)
+        q, k, v = self._qkv_heads(qkv)
+        o = self._attend(q, k, v, past, li, causal=False).reshape(B, S, -1)
+        xv = g.o(o[:, :N].contiguous(), residual=x[:, :N].contiguous())
+        xt = u.o(o[:, N:].contiguous(), residual=x[:, N:].contiguous())
+        hv = fused.norm_modulate(xv, weight=g.post_attention_layernorm, rms=True, eps=eps)
+        ht = fused.norm_modulate(xt, weight=u.post_attention_layernorm, rms=True, eps=eps)
+        xv = g.down(fused.silu_mul(g.gate_up(hv)), residual=xv)
+        xt = u.down(fused.silu_mul(u.gate_up(ht)), residual=xt)
+        return torch.cat([xv, xt], dim=1)
+
     # ------------------------------------------------------------------ generation mode: one velocity evaluation
     @torch.no_grad()
-    def flow(self, x_t: torch.Tensor, t: torch.Tensor, grid, past=None, position: int = 0) -> torch.Tensor:
+    def flow(self, x_t: torch.Tensor, t: torch.Tensor, grid, past=None, position: int = 0, branch: int = 0) -> torch.Tensor:
         """x_t [B, N, patch_latent_dim] (N = h * w latent tokens), t [B] in [0, 1], grid (h, w), context
         ``past`` of length ``position`` rows (or any length, with the image placed at rotary position
         ``position``) -> velocity [B, N, patch_latent_dim]."""
@@ -225,21 +247,16 @@ class BagelMoT(nn.Module):
         x = torch.cat([lat, marks[None].expand(B, -1, -1)], dim=1).contiguous()            # [B, N + 2, D]
         S = N + 2
         cos, sin = self._cos_sin(torch.full((S,), int(position), device=dev))
-        for li, layer in enumerate(self.layers):
-            g, u = layer.gen, layer.und
-            hv = fused.norm_modulate(x[:, :N].contiguous(), weight=g.input_layernorm, rms=True, eps=eps)
-            ht = fused.norm_modulate(x[:, N:].contiguous(), weight=u.input_layernorm, rms=True, eps=eps)
-            qkv = torch.cat([g.qkv(hv), u.qkv(ht)], dim=1).contiguous()
-            qkv = self._norm_rope(qkv, cos, sin, g.q_norm, g.k_norm, u.q_norm, u.k_norm, N)
-            q, k, v = self._qkv_heads(qkv)
-            o = self._attend(q, k, v, past, li, causal=False).reshape(B, S, -1)
-            xv = g.o(o[:, :N].contiguous(), residual=x[:, :N].contiguous())
-            xt = u.o(o[:, N:].contiguous(), residual=x[:, N:].contiguous())
-            hv = fused.norm_modulate(xv, weight=g.post_attention_layernorm, rms=True, eps=eps)
-            ht = fused.norm_modulate(xt, weight=u.post_attention_layernorm, rms=True, eps=eps)
-            xv = g.down(fused.silu_mul(g.gate_up(hv)), residual=xv)
-            xt = u.down(fused.silu_mul(u.gate_up(ht)), residual=xt)
-            x = torch.cat([xv, xt], dim=1)
+        def run(states, a, b):
+            x = states[0]
+            for li in range(a, b):
+                x = self._gen_layer(li, x, N, cos, sin, past)
+            return (x,)
+        if self.stack_hook is not None:
+            from ...cache.base import BlockStack
+            (x,) = self.stack_hook(BlockStack(len(self.layers), (x,), x[:, :N], run, branch=branch))
+        else:
+            (x,) = run((x,), 0, len(self.layers))
         out = fused.norm_modulate(x[:, :N].contiguous(), weight=self.norm_moe_gen, rms=True, eps=eps)
         return self.llm2vae(out)
 

@@ -159,7 +159,7 @@ class BagelPipeline(nn.Module):
             t = ts[i]
             v = tf.flow(x, t.reshape(1), (h, w), ctx, pos).float()
             if text_scale > 1.0 and interval[0] < float(t) <= interval[1]:
-                vn = tf.flow(x, t.reshape(1), (h, w), neg_ctx, neg_pos).float()
+                vn = tf.flow(x, t.reshape(1), (h, w), neg_ctx, neg_pos, branch=1).float()
                 v = guided_velocity(v, vn, None, text_scale, 1.0, renorm_min, renorm_type)
             x = x - v * (ts[i] - ts[i + 1])
         p = c.latent_patch_size

@@ -69,6 +69,8 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
                                             for _ in range(cfg.num_single_layers)])
         self.single_mod = FusedLinear(D, cfg.num_single_layers * 3 * D, dtype=dtype, device=device)
         self._angles = {}
+        self.stack_hook = None            # cache backends: called once per step with a BlockStack over double + single blocks
+        self.block_hook = None            # (the Qwen-Image in-place entry is not used by this forward)
 
     def _cos_sin(self, h, w, txt_len, device):
         key = (h, w, txt_len, str(device))
@@ -147,12 +149,27 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
         sv = F.silu(vec)
         mods = self.mod(sv).view(B, L, 2, 6 * D)
         ws = self._workspace(B, S_img, S_txt, dev)
-        for i in range(L):
-            self.block_forward(i, img, txt, mods, cos, sin, kv_lens, ws)
-        x = torch.cat([img, txt], dim=1).contiguous()
         m3 = self.single_mod(sv).view(B, cfg.num_single_layers, 3 * D)
-        for i, blk in enumerate(self.single_blocks):
-            self.single_forward(blk, x, m3[:, i], cos, sin, kv_lens, S_img)
+        Ls = cfg.num_single_layers
+
+        def run(states, a, b):
+            """Blocks a..b-1 of [double blocks | single blocks] on the (image, text) streams."""
+            im, tx = states
+            for i in range(a, min(b, L)):
+                self.block_forward(i, im, tx, mods, cos, sin, kv_lens, ws)
+            if b > L and max(a, L) < b:
+                x = torch.cat([im, tx], dim=1).contiguous()
+                for j in range(max(a, L) - L, b - L):
+                    self.single_forward(self.single_blocks[j], x, m3[:, j], cos, sin, kv_lens, S_img)
+                im, tx = x[:, :S_img].contiguous(), x[:, S_img:].contiguous()
+            return (im, tx)
+        if self.stack_hook is not None:
+            from ...cache.base import BlockStack
+            m0 = mods[:, 0, 0]
+            probe = fused.norm_modulate(img, shift=m0[:, 0:D], scale=m0[:, D:2 * D], eps=cfg.eps)
+            img, txt = self.stack_hook(BlockStack(L + Ls, (img, txt), probe, run))
+        else:
+            img, txt = run((img, txt), 0, L + Ls)
         ss = self.norm_out(sv)
-        out = fused.norm_modulate(x[:, :S_img].contiguous(), shift=ss[:, D:], scale=ss[:, :D], eps=cfg.eps)
+        out = fused.norm_modulate(img.contiguous(), shift=ss[:, D:], scale=ss[:, :D], eps=cfg.eps)
         return self.proj_out(out)

@@ -179,7 +179,7 @@ class Flux2KleinPipeline(nn.Module):
             tv.fill_(float(self.scheduler.sigmas[i]))
             x = lat_in if ref is None else torch.cat([lat_in, ref], dim=1)
             v = tf(x, pe, tv, ids_img, ids_txt)[:, :S]
-            vn = tf(x, ne, tv, ids_img, ids_txt)[:, :S] if do_cfg else None
+            vn = tf(x, ne, tv, ids_img, ids_txt, branch=1)[:, :S] if do_cfg else None
             fused.cfg_euler_step_(v.contiguous(), vn.contiguous() if vn is not None else None, lat, scale if do_cfg else 1.0,
                                   self.scheduler.dt(i), False, lat_in)
         z = lat.transpose(1, 2).reshape(B, C, h, w)

@@ -142,6 +142,7 @@ class Flux2Transformer2DModel(nn.Module):
         self.norm_out = FusedLinear(D, 2 * D, **kw)
         self.proj_out = FusedLinear(D, c.patch_size * c.patch_size * self.out_channels, **kw)
         self._angles: dict = {}
+        self.stack_hook = None            # cache backends: called once per step with a BlockStack over double + single blocks
 
     # ------------------------------------------------------------------ rotary tables
     def cos_sin(self, img_ids: torch.Tensor, txt_ids: torch.Tensor, device):
@@ -198,7 +199,8 @@ class Flux2Transformer2DModel(nn.Module):
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
-    def forward(self, hidden_states, encoder_hidden_states, timestep, img_ids, txt_ids, guidance=None, txt_seq_lens=None, **_):
+    def forward(self, hidden_states, encoder_hidden_states, timestep, img_ids, txt_ids, guidance=None, txt_seq_lens=None,
+                branch: int = 0, **_):
         """hidden_states [B, S_img, C], encoder_hidden_states [B, S_txt, J], timestep [B] in [0, 1],
         img_ids [S_img, 4], txt_ids [S_txt, 4] -> [B, S_img, patch^2 * out_channels]."""
         c = self.cfg
@@ -221,13 +223,26 @@ class Flux2Transformer2DModel(nn.Module):
         mi, mt, ms = self.mod_img(sv), self.mod_txt(sv), self.mod_single(sv)
         img = self.x_embedder(hidden_states.to(dt).contiguous())
         txt = self.context_embedder(encoder_hidden_states.to(dt).contiguous())
-        for blk in self.blocks:
-            img, txt = self._double(blk, img, txt, mi, mt, cos, sin, kv_lens)
-        x = torch.cat([img, txt], dim=1).contiguous()
-        for blk in self.single_blocks:
-            x = self._single(blk, x, ms, cos, sin, kv_lens)
+        L, Ls = len(self.blocks), len(self.single_blocks)
+
+        def run(states, a, b):
+            im, tx = states
+            for i in range(a, min(b, L)):
+                im, tx = self._double(self.blocks[i], im, tx, mi, mt, cos, sin, kv_lens)
+            if b > L and max(a, L) < b:
+                x = torch.cat([im, tx], dim=1).contiguous()
+                for j in range(max(a, L) - L, b - L):
+                    x = self._single(self.single_blocks[j], x, ms, cos, sin, kv_lens)
+                im, tx = x[:, :Si].contiguous(), x[:, Si:].contiguous()
+            return (im, tx)
+        if self.stack_hook is not None:
+            from ...cache.base import BlockStack
+            probe = fused.norm_modulate(img, shift=mi[:, 0:D], scale=mi[:, D:2 * D], eps=c.eps)
+            img, txt = self.stack_hook(BlockStack(L + Ls, (img, txt), probe, run, branch=branch))
+        else:
+            img, txt = run((img, txt), 0, L + Ls)
         ss = self.norm_out(sv)                                   # scale | shift
-        out = fused.norm_modulate(x[:, :Si].contiguous(), shift=ss[:, D:], scale=ss[:, :D], eps=c.eps)
+        out = fused.norm_modulate(img.contiguous(), shift=ss[:, D:], scale=ss[:, :D], eps=c.eps)
         return self.proj_out(out)
 
     # ------------------------------------------------------------------ weights

@@ -97,8 +97,17 @@ class SD3Transformer2DModel(FluxTransformer2DModel):
         sv = F.silu(vec)
         mods = self.mod(sv).view(B, L, 2, 6 * D)
         ws = self._workspace(B, S_img, S_txt, dev)
-        for i in range(L):
-            self.block_forward(i, img, txt, mods, None, None, kv_lens, ws)       # no rotary embedding
+        def run(states, a, b):
+            for i in range(a, b):
+                self.block_forward(i, img, txt, mods, None, None, kv_lens, ws)   # in place; no rotary embedding
+            return (img, txt)
+        if self.stack_hook is not None:
+            from ...cache.base import BlockStack
+            m0 = mods[:, 0, 0]
+            probe = fused.norm_modulate(img, shift=m0[:, 0:D], scale=m0[:, D:2 * D], eps=cfg.eps)
+            self.stack_hook(BlockStack(L, (img, txt), probe, run))
+        else:
+            run((img, txt), 0, L)
         ss = self.norm_out(sv)
         out = fused.norm_modulate(img, shift=ss[:, D:], scale=ss[:, :D], eps=cfg.eps)
         return self.proj_out(out)

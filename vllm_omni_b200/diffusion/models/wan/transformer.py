@@ -101,7 +101,7 @@ class WanTransformer3DModel(nn.Module):
         self.sp = None                   # SequenceParallelAttention when the sequence is sharded
         self.sp_style = "attention"
         self._sp_valid_len = None
-        self.block_hook = None
+        self.stack_hook = None            # cache backends: called once per step with a BlockStack over the blocks
         self._rope = {}
 
     # -------------------------------------------------------------- patchify
@@ -176,11 +176,16 @@ class WanTransformer3DModel(nn.Module):
         ctx = self.text_2(self.text_1(encoder_hidden_states.to(self.dtype_), act="gelu_tanh"))
         temb = self.time_2(self.time_1(timestep_sinusoid(timestep, cfg.freq_dim, scale=1.0).to(self.dtype_), act="silu"))
         e6 = self.time_proj(F.silu(temb)).view(B, 6, D)
-        if self.block_hook is not None:
-            x = self.block_hook(self, x, ctx, e6, cos, sin)
+        def run(states, a, b):
+            for blk in self.blocks[a:b]:
+                self.block_forward(blk, states[0], ctx, e6, cos, sin)        # in place
+            return states
+        if self.stack_hook is not None:
+            from ...cache.base import BlockStack
+            probe = fused.norm_modulate(x, shift=e6[:, 0].contiguous(), scale=e6[:, 1].contiguous(), eps=cfg.eps)
+            (x,) = self.stack_hook(BlockStack(len(self.blocks), (x,), probe, run))
         else:
-            for blk in self.blocks:
-                self.block_forward(blk, x, ctx, e6, cos, sin)
+            run((x,), 0, len(self.blocks))
         om = (self.out_table[None].float() + temb[:, None].float()).to(x.dtype)      # [B,2,D]: shift, scale
         xn = fused.norm_modulate(x, shift=om[:, 0].contiguous(), scale=om[:, 1].contiguous(), eps=cfg.eps)
         y = self.proj_out(xn)

@@ -114,7 +114,8 @@ class ZImageTransformer2DModel(nn.Module):
         self.layers = nn.ModuleList([ZBlock(c, True, dtype, device) for _ in range(c.n_layers)])
         self.final_adaln = FusedLinear(A, D, **kw)
         self.proj_out = FusedLinear(D, c.patch_dim, **kw)
-        self.block_hook = None
+        self.block_hook = None            # observer: called as (layer index, states) after every main layer
+        self.stack_hook = None            # cache backends: called once per step with a BlockStack over the main layers
         self.sp = None                   # SequenceParallelAttention when the unified sequence is sharded
         self.sp_style = "attention"
         self._tables = None
@@ -251,10 +252,18 @@ class ZImageTransformer2DModel(nn.Module):
                 upos = torch.cat([upos, upos.new_zeros(B, pad)], dim=1)
             upos = upos.contiguous()
             sp_lens = kv_lens if kv_lens is not None else (S_full if S_full % sp.P else None)
-        for li, blk in enumerate(self.layers):
-            u = self._block(blk, u, temb, uc, us, upos, kv_lens, sp, sp_lens)
-            if self.block_hook is not None:
-                self.block_hook(li, u)
+        def run(states, a, b):
+            x = states[0]
+            for li in range(a, b):
+                x = self._block(self.layers[li], x, temb, uc, us, upos, kv_lens, sp, sp_lens)
+                if self.block_hook is not None:
+                    self.block_hook(li, x)
+            return (x,)
+        if self.stack_hook is not None:
+            from ...cache.base import BlockStack
+            (u,) = self.stack_hook(BlockStack(len(self.layers), (u,), u, run))
+        else:
+            (u,) = run((u,), 0, len(self.layers))
         if sp is not None:
             u = sp.gather_rows(u, S_full, dim=1)
         sc = self.final_adaln(F.silu(temb))
