@@ -37,3 +37,23 @@ def test_parallel_config_matches_single_process(baseline, kw):
     assert img.shape == baseline.shape
     d = (img - baseline).abs()
     assert d.mean().item() < 2e-4 and d.max().item() < 2e-3, (d.mean().item(), d.max().item())
+
+
+def test_flux2_klein_cfg_parallel_matches_single_process():
+    """FLUX.2-klein under classifier-free guidance: one guidance branch per rank equals both on one rank."""
+    tf = dict(in_channels=64, num_layers=1, num_single_layers=1, attention_head_dim=32, num_attention_heads=2,
+              joint_attention_dim=32, timestep_guidance_channels=32, axes_dims_rope=(8, 8, 8, 8), guidance_embeds=False)
+    vae = dict(block_out_channels=(8, 16, 16, 16), layers_per_block=1, norm_num_groups=4)
+
+    def run(par):
+        omni = Omni("Flux2KleinPipeline", dtype="float32", device="cpu", tf_model_config=tf, vae_config=vae,
+                    diffusion_load_format="dummy", parallel_config=par, output_type="latent")
+        try:
+            sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=3, guidance_scale=4.0, seed=0,
+                                             output_type="latent", max_sequence_length=8)
+            out = omni.generate(["a cube"], sp)[0]
+            return torch.as_tensor(out.latents if out.latents is not None else out.images[0]).float()
+        finally:
+            omni.close()
+    a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(cfg_parallel_size=2))
+    assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4

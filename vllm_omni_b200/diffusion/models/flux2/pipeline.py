@@ -80,6 +80,7 @@ class Flux2KleinPipeline(nn.Module):
         self.scheduler = FlowMatchEulerDiscreteScheduler(**KLEIN_SCHEDULER)
         self.text_encoder = HashTextEncoder(tcfg.joint_attention_dim, max_len=self.max_text_len)
         self.vae_decode = None
+        self.cfg_exchange = None        # set by CFG-parallel: rank 0 runs the prompt branch, rank 1 the empty-prompt branch
 
     def attach_text_encoder(self, model_path: str) -> bool:
         if not (os.path.isfile(os.path.join(model_path, "text_encoder", "config.json")) and
@@ -178,6 +179,11 @@ class Flux2KleinPipeline(nn.Module):
         for i in range(len(ts)):
             tv.fill_(float(self.scheduler.sigmas[i]))
             x = lat_in if ref is None else torch.cat([lat_in, ref], dim=1)
+            if do_cfg and self.cfg_exchange is not None:     # one branch per rank, velocities exchanged inside the step kernel
+                mine = ne if self.cfg_exchange.is_negative_rank else pe
+                v = tf(x, mine, tv, ids_img, ids_txt)[:, :S].contiguous()
+                self.cfg_exchange.step(v, lat, scale, self.scheduler.dt(i), False, lat_in)
+                continue
             v = tf(x, pe, tv, ids_img, ids_txt)[:, :S]
             vn = tf(x, ne, tv, ids_img, ids_txt, branch=1)[:, :S] if do_cfg else None
             fused.cfg_euler_step_(v.contiguous(), vn.contiguous() if vn is not None else None, lat, scale if do_cfg else 1.0,
