@@ -57,3 +57,28 @@ def test_flux2_klein_cfg_parallel_matches_single_process():
             omni.close()
     a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(cfg_parallel_size=2))
     assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("name", ["LongCatImagePipeline", "OvisImagePipeline", "StableDiffusion3Pipeline"])
+def test_true_cfg_families_match_under_cfg_parallel(name):
+    """LongCat-Image (guided velocity clamped per token) and Ovis-Image run true guidance against the negative
+    prompt; with one branch per rank the latents equal the single-process run, and guidance changes them."""
+    tf = dict(num_layers=1, num_single_layers=1, attention_head_dim=32, num_attention_heads=2, joint_attention_dim=32,
+              pooled_projection_dim=16, in_channels=64, out_channels=16, axes_dims_rope=(8, 12, 12))
+    if name == "StableDiffusion3Pipeline":
+        tf = dict(tf, num_single_layers=0, num_layers=2)
+    vae = dict(block_out_channels=(8, 16, 16, 16), layers_per_block=1, norm_num_groups=4)
+
+    def run(par, scale):
+        omni = Omni(name, dtype="float32", device="cpu", tf_model_config=tf, vae_config=vae, diffusion_load_format="dummy",
+                    parallel_config=par, output_type="latent")
+        try:
+            sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=3, guidance_scale=scale, seed=0,
+                                             output_type="latent", max_sequence_length=8)
+            out = omni.generate([{"prompt": "a cube", "negative_prompt": "blurry"}], sp)[0]
+            return torch.as_tensor(out.latents if out.latents is not None else out.images[0]).float()
+        finally:
+            omni.close()
+    a, b = run(DiffusionParallelConfig(), 4.0), run(DiffusionParallelConfig(cfg_parallel_size=2), 4.0)
+    assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4
+    assert (a - run(DiffusionParallelConfig(), 1.0)).abs().max().item() > 1e-6

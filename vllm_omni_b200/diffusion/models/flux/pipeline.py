@@ -25,6 +25,10 @@ class FluxPipeline(nn.Module):
     transformer_cls, config_cls = FluxTransformer2DModel, FluxTransformerConfig
     default_guidance = 3.5
     max_text_len = 512
+    # FLUX.1 is guidance-distilled (the scale is an input of the network).  The FLUX-family members without a
+    # guidance embedding (LongCat-Image, Ovis-Image) run true classifier-free guidance against a negative prompt:
+    true_cfg = False
+    cfg_renorm_clamp = False            # rescale the guided velocity per token to at most the conditional one's norm
 
     def __init__(self, od_config: OmniDiffusionConfig | None = None, transformer_config=None, vae_config=None,
                  device=None, **_):
@@ -40,6 +44,13 @@ class FluxPipeline(nn.Module):
         self.text_encoder = HashTextEncoder(tcfg.joint_attention_dim, max_len=self.max_text_len)
         self.pooled_encoder = HashTextEncoder(getattr(tcfg, "pooled_projection_dim", 768), max_len=1)
         self.vae_decode = None
+        self.cfg_exchange = None        # set by CFG-parallel
+
+    def _guided(self, v, vn, scale, renorm_min=0.0):
+        out = vn.float() + scale * (v.float() - vn.float())
+        if self.cfg_renorm_clamp:
+            out = out * (v.float().norm(dim=-1, keepdim=True) / (out.norm(dim=-1, keepdim=True) + 1e-8)).clamp(min=renorm_min, max=1.0)
+        return out
 
     @torch.no_grad()
     def forward(self, req: OmniDiffusionRequest) -> DiffusionOutput:
@@ -56,9 +67,18 @@ class FluxPipeline(nn.Module):
             pe, mask = self.text_encoder(texts, self.device_, self.od_config.dtype, sp.max_sequence_length)
             lens = mask.sum(1).tolist()
         pooled = self.pooled_encoder(texts, self.device_, self.od_config.dtype)[0][:, 0]
+        scale = float(sp.guidance_scale if sp.guidance_scale_provided else self.default_guidance)
+        do_cfg = self.true_cfg and scale > 1.0
+        ne = nlens = None
+        if do_cfg:
+            negs = [(p.get("negative_prompt") if isinstance(p, dict) else None) or "" for p in req.prompts]
+            ne, nmask = self.text_encoder(negs, self.device_, self.od_config.dtype, sp.max_sequence_length)
+            nlens = nmask.sum(1).tolist()
         if n > 1:
             pe, pooled = pe.repeat_interleave(n, 0), pooled.repeat_interleave(n, 0)
             lens = [l for l in lens for _ in range(n)]
+            if do_cfg:
+                ne, nlens = ne.repeat_interleave(n, 0), [l for l in nlens for _ in range(n)]
         B = pe.shape[0]
         gen = sp.generator
         if gen is None and sp.seed is not None:
@@ -70,15 +90,30 @@ class FluxPipeline(nn.Module):
         c = self.scheduler.config
         mu = calculate_shift(lat.shape[1], c["base_image_seq_len"], c["max_image_seq_len"], c["base_shift"], c["max_shift"])
         ts = self.scheduler.set_timesteps(sigmas=sig, mu=mu, device=self.device_)
-        guidance = torch.full((B,), float(sp.guidance_scale if sp.guidance_scale_provided else self.default_guidance),
-                              device=self.device_)
+        guidance = torch.full((B,), scale, device=self.device_)
         lat_in = lat.to(self.od_config.dtype)
         tv = torch.empty(B, device=self.device_)
         for i in range(len(ts)):
             tv.fill_(float(self.scheduler.sigmas[i]))
-            v = self.transformer(lat_in, pe, tv, (1, h // 2, w // 2), pooled_projections=pooled, guidance=guidance,
-                                 txt_seq_lens=lens)
-            fused.cfg_euler_step_(v.contiguous(), None, lat, 1.0, self.scheduler.dt(i), False, lat_in)
+            call = lambda enc, ln, branch=0: self.transformer(lat_in, enc, tv, (1, h // 2, w // 2), pooled_projections=pooled,
+                                                              guidance=guidance, txt_seq_lens=ln, branch=branch)
+            dt = self.scheduler.dt(i)
+            if do_cfg and self.cfg_exchange is not None:     # one guidance branch per rank
+                mine = call(ne, nlens) if self.cfg_exchange.is_negative_rank else call(pe, lens)
+                if self.cfg_renorm_clamp:
+                    both = self.cfg_exchange.group.all_gather(mine.contiguous(), separate_tensors=True)
+                    fused.cfg_euler_step_(self._guided(both[0], both[1], scale).to(mine.dtype).contiguous(), None, lat, 1.0, dt,
+                                          False, lat_in)
+                else:
+                    self.cfg_exchange.step(mine.contiguous(), lat, scale, dt, False, lat_in)
+            elif do_cfg:
+                v, vn = call(pe, lens), call(ne, nlens, 1)
+                if self.cfg_renorm_clamp:
+                    fused.cfg_euler_step_(self._guided(v, vn, scale).to(v.dtype).contiguous(), None, lat, 1.0, dt, False, lat_in)
+                else:
+                    fused.cfg_euler_step_(v.contiguous(), vn.contiguous(), lat, scale, dt, False, lat_in)
+            else:
+                fused.cfg_euler_step_(call(pe, lens).contiguous(), None, lat, 1.0, dt, False, lat_in)
         if (sp.output_type or self.od_config.output_type) == "latent":
             return DiffusionOutput(output=lat)
         img = (self.vae_decode or self.vae.decode)(unpack_latents(lat, h, w))

@@ -127,7 +127,7 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
         return x
 
     def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, pooled_projections=None,
-                guidance=None, txt_seq_lens=None, **_):
+                guidance=None, txt_seq_lens=None, branch: int = 0, **_):
         cfg, D, L = self.cfg, self.cfg.inner_dim, self.cfg.num_layers
         B, S_img, S_txt = hidden_states.shape[0], hidden_states.shape[1], encoder_hidden_states.shape[1]
         dev = hidden_states.device
@@ -167,7 +167,7 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
             from ...cache.base import BlockStack
             m0 = mods[:, 0, 0]
             probe = fused.norm_modulate(img, shift=m0[:, 0:D], scale=m0[:, D:2 * D], eps=cfg.eps)
-            img, txt = self.stack_hook(BlockStack(L + Ls, (img, txt), probe, run))
+            img, txt = self.stack_hook(BlockStack(L + Ls, (img, txt), probe, run, branch=branch))
         else:
             img, txt = run((img, txt), 0, L + Ls)
         ss = self.norm_out(sv)

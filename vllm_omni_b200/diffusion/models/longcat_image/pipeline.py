@@ -12,6 +12,7 @@ from .transformer import LongCatImageTransformer2DModel, LongCatTransformerConfi
 class LongCatImagePipeline(FluxPipeline):
     transformer_cls, config_cls = LongCatImageTransformer2DModel, LongCatTransformerConfig
     default_guidance = 4.5
+    true_cfg, cfg_renorm_clamp = True, True     # guidance against the negative prompt, guided velocity clamped per token
 
 
 class LongCatImageEditPipeline(LongCatImagePipeline):

@@ -52,9 +52,9 @@ class LongCatImageTransformer2DModel(FluxTransformer2DModel):
             self._angles[key] = (a.cos().contiguous().to(device), a.sin().contiguous().to(device))
         return self._angles[key]
 
-    def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, txt_seq_lens=None, **_):
+    def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, txt_seq_lens=None, branch: int = 0, **_):
         return super().forward(hidden_states, encoder_hidden_states, timestep, img_shapes, pooled_projections=None,
-                               guidance=None, txt_seq_lens=txt_seq_lens)
+                               guidance=None, txt_seq_lens=txt_seq_lens, branch=branch)
 
     def checkpoint_name_map(self) -> dict:
         m = {}

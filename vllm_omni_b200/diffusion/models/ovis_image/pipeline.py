@@ -9,3 +9,4 @@ from .transformer import OvisImageTransformer2DModel, OvisTransformerConfig
 class OvisImagePipeline(FluxPipeline):
     transformer_cls, config_cls = OvisImageTransformer2DModel, OvisTransformerConfig
     default_guidance = 5.0
+    true_cfg = True                             # guidance against the negative prompt

@@ -67,11 +67,11 @@ class OvisImageTransformer2DModel(FluxTransformer2DModel):
         blk.linear2(cat, residual=x, gate=m3[:, 2 * D:3 * D], out=x)
         return x
 
-    def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, txt_seq_lens=None, **_):
+    def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, txt_seq_lens=None, branch: int = 0, **_):
         enc = fused.norm_modulate(encoder_hidden_states.to(self.dtype_).contiguous(), weight=self.txt_norm_weight, rms=True,
                                   eps=1e-6)
         return super().forward(hidden_states, enc, timestep, img_shapes, pooled_projections=None, guidance=None,
-                               txt_seq_lens=txt_seq_lens)
+                               txt_seq_lens=txt_seq_lens, branch=branch)
 
     # ------------------------------------------------------------------ weights
     def checkpoint_name_map(self) -> dict:

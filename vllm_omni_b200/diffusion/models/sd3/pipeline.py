@@ -113,26 +113,33 @@ class StableDiffusion3Pipeline(FluxPipeline):
         pooled = self.pooled_encoder(texts, self.device_, dt_model)[0][:, 0]
         lens = mask.sum(1).tolist()
         B = pe.shape[0]
+        cfg_par = do_cfg and self.cfg_exchange is not None       # one guidance branch per rank instead of a doubled batch
         if do_cfg:
             ne, nmask = self.text_encoder(negs, self.device_, dt_model, sp.max_sequence_length)
             npooled = self.pooled_encoder(negs, self.device_, dt_model)[0][:, 0]
-            L = max(pe.shape[1], ne.shape[1])
-            both = pe.new_zeros(2 * B, L, pe.shape[2])
-            both[:B, :pe.shape[1]], both[B:, :ne.shape[1]] = pe, ne
-            pe, pooled, lens = both, torch.cat([pooled, npooled]), lens + nmask.sum(1).tolist()
+            if cfg_par:
+                if self.cfg_exchange.is_negative_rank:
+                    pe, pooled, lens = ne, npooled, nmask.sum(1).tolist()
+            else:
+                L = max(pe.shape[1], ne.shape[1])
+                both = pe.new_zeros(2 * B, L, pe.shape[2])
+                both[:B, :pe.shape[1]], both[B:, :ne.shape[1]] = pe, ne
+                pe, pooled, lens = both, torch.cat([pooled, npooled]), lens + nmask.sum(1).tolist()
         gen = sp.generator or (torch.Generator(device="cpu").manual_seed(int(sp.seed)) if sp.seed is not None else None)
         C = self.transformer.cfg.in_channels // 4
         z = torch.randn(B, C, h, w, generator=gen, device=gen.device if gen is not None else self.device_)
         lat = pack_latents(z.to(self.device_, torch.float32))
         ts = self.scheduler.set_timesteps(sp.num_inference_steps, device=self.device_)
         lat_in = lat.to(dt_model)
-        nb = 2 * B if do_cfg else B
+        nb = 2 * B if (do_cfg and not cfg_par) else B
         tv = torch.empty(nb, device=self.device_)
         for i in range(len(ts)):
             tv.fill_(float(self.scheduler.sigmas[i]))
-            x = lat_in.repeat(2, 1, 1) if do_cfg else lat_in
+            x = lat_in.repeat(2, 1, 1) if (do_cfg and not cfg_par) else lat_in
             v = self.transformer(x, pe, tv, (1, h // 2, w // 2), pooled_projections=pooled, txt_seq_lens=lens)
-            if do_cfg:
+            if cfg_par:
+                self.cfg_exchange.step(v.contiguous(), lat, scale, self.scheduler.dt(i), False, lat_in)
+            elif do_cfg:
                 fused.cfg_euler_step_(v[:B].contiguous(), v[B:].contiguous(), lat, scale, self.scheduler.dt(i), False, lat_in)
             else:
                 fused.cfg_euler_step_(v.contiguous(), None, lat, 1.0, self.scheduler.dt(i), False, lat_in)
