@@ -82,3 +82,22 @@ def test_true_cfg_families_match_under_cfg_parallel(name):
     a, b = run(DiffusionParallelConfig(), 4.0), run(DiffusionParallelConfig(cfg_parallel_size=2), 4.0)
     assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4
     assert (a - run(DiffusionParallelConfig(), 1.0)).abs().max().item() > 1e-6
+
+
+def test_wan_cfg_parallel_matches_single_process():
+    """Wan text-to-video: the UniPC step runs on both ranks from the gathered branch velocities."""
+    tf = dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1)
+
+    def run(par):
+        omni = Omni("WanPipeline", dtype="float32", device="cpu", tf_model_config=tf, vae_config=dict(base_dim=8, num_res_blocks=1),
+                    diffusion_load_format="dummy", parallel_config=par, output_type="latent")
+        try:
+            sp = OmniDiffusionSamplingParams(height=32, width=32, num_frames=5, num_inference_steps=3, guidance_scale=4.0, seed=0,
+                                             output_type="latent")
+            out = omni.generate([{"prompt": "a cube", "negative_prompt": "blurry"}], sp)[0]
+            lat = out.latents if out.latents is not None else out.multimodal_output.get("video")
+            return torch.as_tensor(lat).float()
+        finally:
+            omni.close()
+    a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(cfg_parallel_size=2))
+    assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4

@@ -42,6 +42,27 @@ def test_t5_encoder_against_hf(ff):
         assert (ref - out)[mask.bool()].abs().max().item() < 2e-5 * max(1.0, ref.abs().max().item())
 
 
+def test_umt5_encoder_against_hf():
+    """Wan's text encoder: T5 with one relative-position table per block."""
+    torch.manual_seed(0)
+    hc = transformers.UMT5Config(vocab_size=200, d_model=48, d_kv=8, d_ff=96, num_layers=3, num_heads=4,
+                                 relative_attention_num_buckets=8, relative_attention_max_distance=20, feed_forward_proj="gated-gelu")
+    hf = _init(transformers.UMT5EncoderModel(hc))
+    cfg = T5Config.from_dict(hc.to_dict())
+    assert cfg.per_layer_bias and cfg.gated
+    m = T5Encoder(cfg, torch.float32, "cpu")
+    sd = hf.state_dict()
+    assert m.load_weights(sd.items()) == set(sd)
+    assert not torch.equal(m.rel_bias[0], m.rel_bias[2])
+    ids = torch.randint(0, 200, (2, 21))
+    mask = torch.ones(2, 21, dtype=torch.long)
+    mask[0, 13:] = 0
+    with torch.no_grad():
+        ref = hf(ids, attention_mask=mask).last_hidden_state
+        out = m(ids, mask)
+    assert (ref - out)[mask.bool()].abs().max().item() < 2e-5 * max(1.0, ref.abs().max().item())
+
+
 def test_relative_position_buckets_cover_both_signs():
     rel = torch.arange(-40, 41)
     b = relative_position_bucket(rel, 8, 20)
@@ -194,3 +215,31 @@ def test_sd3_folder_builds_the_joint_conditioning(tmp_path):
                                      guidance_scale=4.0)
     out = pipe(OmniDiffusionRequest(prompts=[{"prompt": texts[0], "negative_prompt": "blurry"}], sampling_params=sp, request_ids=["r"]))
     assert torch.isfinite(out.output).all()
+
+
+def test_wan_folder_attaches_umt5(tmp_path):
+    import json
+    pytest.importorskip("tokenizers")
+    from vllm_omni_b200.diffusion.loader import DiffusersPipelineLoader
+    from vllm_omni_b200.diffusion.models.text_encoders.t5 import T5PromptEncoder
+    from vllm_omni_b200.entrypoints.omni_diffusion import build_diffusion_config
+    torch.manual_seed(0)
+    d = tmp_path
+    (d / "model_index.json").write_text(json.dumps({"_class_name": "WanPipeline"}))
+    (d / "transformer").mkdir()
+    (d / "transformer" / "config.json").write_text(json.dumps(dict(_class_name="WanTransformer3DModel", num_attention_heads=2,
+                                                                   attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1)))
+    hc = transformers.UMT5Config(vocab_size=40, d_model=32, d_kv=8, d_ff=64, num_layers=2, num_heads=2,
+                                 relative_attention_num_buckets=8, relative_attention_max_distance=16, feed_forward_proj="gated-gelu")
+    hf = _init(transformers.UMT5EncoderModel(hc))
+    hf.save_pretrained(str(d / "text_encoder"))
+    _tokenizer_dir(d / "tokenizer", 512)
+    cfg = build_diffusion_config(str(d), dtype="float32", vae_config=dict(base_dim=8, num_res_blocks=1), output_type="latent")
+    pipe = DiffusersPipelineLoader(cfg).load_model("cpu")
+    assert isinstance(pipe.text_encoder, T5PromptEncoder) and pipe.text_encoder.model.cfg.per_layer_bias
+    tok = transformers.AutoTokenizer.from_pretrained(str(d / "tokenizer"))
+    enc = tok(["a red cube on the table"], padding="max_length", max_length=512, truncation=True, return_tensors="pt")
+    with torch.no_grad():
+        ref = hf(enc.input_ids, attention_mask=enc.attention_mask).last_hidden_state * enc.attention_mask[..., None]
+        got = pipe._embeds(["a red cube on the table"], "prompt_embeds")
+    assert got.shape == ref.shape and (got - ref).abs().max().item() < 2e-5 * max(1.0, ref.abs().max().item())

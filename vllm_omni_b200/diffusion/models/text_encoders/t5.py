@@ -1,9 +1,10 @@
-"""T5 encoder as a prompt encoder (FLUX and SD3 use T5-v1.1-XXL, Stable Audio T5-base; the
+"""T5 / UMT5 encoder as a prompt encoder (FLUX and SD3 use T5-v1.1-XXL, Stable Audio T5-base, Wan UMT5-XXL; the
 reference instantiates ``transformers.T5EncoderModel`` inside its pipelines, e.g.
 vllm_omni/diffusion/models/flux/pipeline_flux.py, stable_audio/pipeline_stable_audio.py).
 
 Pre-norm blocks with scale-only RMS norms; attention WITHOUT the 1/sqrt(d) factor and with a learned
-additive bias per (head, bucketed relative position) that block 0 owns and every block reuses; a
+additive bias per (head, bucketed relative position) that block 0 owns and every block reuses (UMT5: every
+block has its own table); a
 feed-forward that is either ReLU (``wi``/``wo``) or gated GELU (``wi_0``/``wi_1``/``wo``).  The bias
 table is looked up once per sequence length and cached.  The attention core is torch's fused SDPA with
 that bias as the additive mask: the encoder runs once per request, outside the denoising loop.
@@ -39,9 +40,13 @@ class T5Config:
     relative_attention_max_distance: int = 128
     layer_norm_epsilon: float = 1e-6
     feed_forward_proj: str = "gated-gelu"          # "relu" | "gated-gelu"
+    per_layer_bias: bool = False                   # UMT5 (Wan's encoder): every block owns a relative-position bias table
 
     @classmethod
     def from_dict(cls, d: dict) -> "T5Config":
+        d = dict(d)
+        if d.get("model_type") == "umt5" or any("UMT5" in a for a in d.get("architectures") or []):
+            d.setdefault("per_layer_bias", True)
         keys = set(cls.__dataclass_fields__)
         return cls(**{k: v for k, v in d.items() if k in keys})
 
@@ -99,7 +104,8 @@ class T5Encoder(nn.Module):
         self.cfg = c = cfg
         kw = dict(dtype=dtype, device=device)
         self.embed = nn.Parameter(torch.empty(c.vocab_size, c.d_model, **kw).normal_(0, 1.0), requires_grad=False)
-        self.rel_bias = nn.Parameter(torch.zeros(c.relative_attention_num_buckets, c.num_heads, **kw), requires_grad=False)
+        self.rel_bias = nn.Parameter(torch.zeros(c.num_layers if c.per_layer_bias else 1, c.relative_attention_num_buckets,
+                                                 c.num_heads, **kw), requires_grad=False)
         self.blocks = nn.ModuleList([T5Block(c, dtype, device) for _ in range(c.num_layers)])
         self.final_norm = nn.Parameter(torch.ones(c.d_model, **kw), requires_grad=False)
         self._bias_cache: dict[int, torch.Tensor] = {}
@@ -110,7 +116,7 @@ class T5Encoder(nn.Module):
             pos = torch.arange(L, device=self.rel_bias.device)
             bucket = relative_position_bucket(pos[None, :] - pos[:, None], self.cfg.relative_attention_num_buckets,
                                               self.cfg.relative_attention_max_distance)
-            b = self.rel_bias.float()[bucket].permute(2, 0, 1)[None].contiguous()        # [1, H, L, L]
+            b = self.rel_bias.float()[:, bucket].permute(0, 3, 1, 2)[:, None].contiguous()   # [tables, 1, H, L, L]
             self._bias_cache = {L: b}
         return b
 
@@ -122,9 +128,9 @@ class T5Encoder(nn.Module):
         bias = self.position_bias(L)
         if attention_mask is not None:
             neg = torch.finfo(torch.float32).min
-            bias = bias + (1.0 - attention_mask[:, None, None, :].float()) * neg
-        for blk in self.blocks:
-            x = blk(x, bias)
+            bias = bias + ((1.0 - attention_mask[:, None, None, :].float()) * neg)[None]
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, bias[i if self.cfg.per_layer_bias else 0])
         return fused.norm_modulate(x.contiguous(), weight=self.final_norm, rms=True, eps=self.cfg.layer_norm_epsilon)
 
     @torch.no_grad()
@@ -148,7 +154,7 @@ class T5Encoder(nn.Module):
                 elif rest == "layer.0.SelfAttention.o.weight":
                     tgt = blk.o.weight
                 elif rest == "layer.0.SelfAttention.relative_attention_bias.weight":
-                    tgt = self.rel_bias
+                    tgt = self.rel_bias[int(p[2]) if c.per_layer_bias else 0]
                     self._bias_cache = {}
                 elif rest == "layer.0.layer_norm.weight":
                     tgt = blk.norm1

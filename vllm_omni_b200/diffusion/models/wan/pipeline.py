@@ -41,6 +41,19 @@ class WanPipeline(nn.Module):
         self.scheduler = FlowUniPCMultistepScheduler(shift=self.od_config.flow_shift or 5.0)
         self.text_encoder = HashTextEncoder(tcfg.text_dim, max_len=512)
         self.vae_decode = None
+        self.cfg_exchange = None        # set by CFG-parallel: rank 0 runs the prompt branch, rank 1 the negative one
+
+    def attach_text_encoder(self, model_path: str) -> bool:
+        """``text_encoder/`` (UMT5) + ``tokenizer/``: states of padded positions are zeroed, as the reference does
+        (vllm_omni/diffusion/models/wan2_2/pipeline_wan2_2.py, ``_get_t5_prompt_embeds``)."""
+        import os
+        if not (os.path.isfile(os.path.join(model_path, "text_encoder", "config.json")) and
+                os.path.isdir(os.path.join(model_path, "tokenizer"))):
+            return False
+        from ..text_encoders.t5 import T5PromptEncoder
+        self.text_encoder = T5PromptEncoder.from_pretrained(model_path, "text_encoder", "tokenizer", self.od_config.dtype,
+                                                            self.device_, max_len=512, zero_padding=True)
+        return True
 
     def _embeds(self, prompts, key, negs=False):
         es = [p.get(key) if isinstance(p, dict) else None for p in prompts]
@@ -80,17 +93,24 @@ class WanPipeline(nn.Module):
         boundary = None
         if self.transformer_2 is not None:
             boundary = (sp.boundary_ratio or self.od_config.boundary_ratio) * 1000.0
-        enc = torch.cat([pe, ne], 0) if do_cfg else pe
+        cfg_par = do_cfg and self.cfg_exchange is not None
+        if cfg_par:
+            enc = ne if self.cfg_exchange.is_negative_rank else pe
+        else:
+            enc = torch.cat([pe, ne], 0) if do_cfg else pe
         for i, t in enumerate(ts):
             model = self.transformer if (boundary is None or float(t) >= boundary) else self.transformer_2
             x = lat.to(self.od_config.dtype)
             if cond is not None:
                 x = torch.cat([x, cond], dim=1)
-            xin = torch.cat([x, x], 0) if do_cfg else x
+            xin = torch.cat([x, x], 0) if (do_cfg and not cfg_par) else x
             tv = t.expand(xin.shape[0])
             v = model(xin, tv, enc).float()
             if do_cfg:
-                vc, vu = v[:B], v[B:]
+                if cfg_par:                              # both ranks take both branches and step their own copy identically
+                    vc, vu = self.cfg_exchange.group.all_gather(v.contiguous(), separate_tensors=True)
+                else:
+                    vc, vu = v[:B], v[B:]
                 g = guidance if (boundary is None or float(t) >= boundary) else (sp.guidance_scale_2 or guidance)
                 v = vu + g * (vc - vu)
             lat = self.scheduler.step(v, t, lat)
@@ -103,13 +123,17 @@ class WanPipeline(nn.Module):
         return None
 
     def load_weights(self, weights) -> set:
-        tw, t2 = [], []
+        tw, t2, te = [], [], []
         for n, w in weights:
             if n.startswith("transformer_2."):
                 t2.append((n[len("transformer_2."):], w))
             elif n.startswith("transformer."):
                 tw.append((n[len("transformer."):], w))
+            elif n.startswith("text_encoder."):
+                te.append((n[len("text_encoder."):], w))
         loaded = {"transformer." + n for n in self.transformer.load_weights(tw)}
+        if te and hasattr(self.text_encoder, "load_weights"):
+            loaded |= {"text_encoder." + n for n in self.text_encoder.load_weights(te)}
         if self.transformer_2 is not None:
             loaded |= {"transformer_2." + n for n in self.transformer_2.load_weights(t2)}
         return loaded
