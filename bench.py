@@ -41,24 +41,18 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=60, help="60 = the 20B config; anything else is a smoke run")
     ap.add_argument("--parallelism", default=None, help="e.g. sp8, cfg2xsp4, tp8 (default: sp{N})")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ref-eager", action="store_true", help="reference arm: skip its regional torch.compile")
     return ap.parse_args()
 
 
 def reference_arm(args):
-    """The reference cannot be imported offline: say why and exit 0."""
-    why = None
-    try:
-        sys.path.insert(0, os.path.join(REPO, "baseline", "_ref"))
-        import vllm_omni  # noqa: F401
-    except Exception as e:  # noqa: BLE001
-        why = (f"reference installs with --no-deps but `import vllm_omni` fails offline ({type(e).__name__}: {e}); "
-               "aenum, omegaconf, diffusers and cache_dit are not in the wheelhouse and it pins vllm 0.16")
-    if why is None:
-        why = ("reference imports, but its Qwen-Image pipeline needs diffusers (absent offline) for the scheduler, "
-               "VAE and image processor")
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:400]}))
-    return 0
+    """Runs the unmodified reference (installed under ``baseline/_ref``) on the same metric and
+    config; ``baseline/reference_arm.py`` says which of its files run.  The reference's layouts:
+    N=1 single, N=2 CFG-parallel, N>=4 CFG-parallel x Ulysses N/2 (its `cfg_parallel_size` and
+    `ulysses_degree` options) unless ``--parallelism`` names another."""
+    from baseline import reference_arm as ra
+    par = parse_parallelism(args.parallelism, args.gpus)
+    return ra.main(args, par, ClockSampler)
 
 
 class ClockSampler:

@@ -138,6 +138,9 @@ class LLMEngine:
             done = self.kv_transfer_manager.handle_finished_requests_kv_transfer(
                 [self._reqs[r] for r in sched.kv_transfer_ids if r in self._reqs], self.runner)
             self.scheduler.update_from_output(type(sched)(), {}, done)
+        elif sched.kv_transfer_ids:
+            # a hand-off criterion without a transfer manager: nothing will ever extract the KV
+            self.scheduler.update_from_output(type(sched)(), {}, list(sched.kv_transfer_ids))
         now = time.time()
         for req in touched:
             if req.first_token_time is None:

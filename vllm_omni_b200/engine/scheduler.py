@@ -93,33 +93,34 @@ class OmniARScheduler:
         self._poll_chunks()
         out = SchedulerOutput()
         budget = self.max_num_batched_tokens
-        # 1. running requests: decode (or continue a chunked prefill)
+        # 1. running requests: decode, continue a chunked prefill, or recompute after a preemption.
+        #    What a request still has to feed is every token it owns (prompt + generated) whose KV is
+        #    not in the cache; a token is sampled only by the step that feeds the last of them.
         preempted: list[Request] = []
+        scheduled_ids: set[str] = set()
         for req in list(self.running):
             if budget <= 0:
                 break
-            remaining_prompt = req.num_prompt_tokens - req.num_computed_tokens
-            if remaining_prompt > 0:
-                n = min(remaining_prompt, budget)
-                is_prefill = True
-                samples = (n == remaining_prompt) and not req.expects_more_chunks
-            elif req.expects_more_chunks:
-                continue                      # prompt so far consumed; wait for the next chunk
-            else:
-                n, is_prefill, samples = 1, False, True
-                if req.num_computed_tokens >= req.num_tokens:     # nothing new to feed
-                    continue
+            if req.status != RequestStatus.RUNNING:
+                continue                      # preempted earlier in this very step
+            remaining = req.num_tokens - req.num_computed_tokens
+            if remaining <= 0:
+                continue                      # everything consumed; waiting for the next chunk
+            n = min(remaining, budget)
+            is_prefill = not (remaining == 1 and req.output_token_ids)
+            samples = (n == remaining) and not req.expects_more_chunks
             while not self.kv.allocate_slots(req, n):
-                victim = self._pick_victim(exclude=req)
+                victim = self._pick_victim(exclude=req, scheduled=scheduled_ids)
                 if victim is None:
                     break
                 self._preempt(victim)
                 preempted.append(victim)
             else:
                 out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, is_prefill, samples))
+                scheduled_ids.add(req.request_id)
                 budget -= n
                 continue
-            # could not allocate even after preempting everyone else: preempt this one
+            # no pages even after preempting every request that is not part of this step
             self._preempt(req)
             preempted.append(req)
         # 2. admit waiting requests
@@ -131,35 +132,38 @@ class OmniARScheduler:
                 if all(r.status == RequestStatus.WAITING_FOR_CHUNK for r in self.waiting):
                     break
                 continue
-            remaining_prompt = req.num_prompt_tokens - req.num_computed_tokens
-            n = min(max(remaining_prompt, 1), budget)
+            remaining = req.num_tokens - req.num_computed_tokens
+            n = min(max(remaining, 1), budget)
             if not self.kv.allocate_slots(req, n):
                 break
             self.waiting.popleft()
             req.status = RequestStatus.RUNNING
             self.running.append(req)
-            samples = (n >= remaining_prompt) and not req.expects_more_chunks
+            samples = (n >= remaining) and not req.expects_more_chunks
             out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, True, samples))
             budget -= n
         out.total_tokens = self.max_num_batched_tokens - budget
         out.finished_ids, self.finished_since_last = self.finished_since_last, []
         return out
 
-    def _pick_victim(self, exclude: Request) -> Request | None:
+    def _pick_victim(self, exclude: Request, scheduled: set[str] = frozenset()) -> Request | None:
+        """Latest-admitted running request that holds pages and is not part of the current step."""
         for r in reversed(self.running):
-            if r is not exclude and r.block_ids:
+            if r is not exclude and r.block_ids and r.request_id not in scheduled \
+                    and r.status == RequestStatus.RUNNING:
                 return r
         return None
 
     def _preempt(self, req: Request) -> None:
-        """Recompute-style preemption: drop the pages, keep the tokens, back to the queue head."""
+        """Recompute-style preemption: drop the pages, keep the tokens, back to the queue head.
+        The generated tokens stay in ``output_token_ids``; on re-admission they are fed again
+        together with the prompt (``num_tokens - num_computed_tokens``)."""
         self.kv.free(req)
         req.num_computed_tokens = 0
-        req.status = RequestStatus.PREEMPTED
         if req in self.running:
             self.running.remove(req)
-        # generated tokens become part of what has to be recomputed
-        self.waiting.appendleft(req)
+        if req not in self.waiting:
+            self.waiting.appendleft(req)
         req.status = RequestStatus.WAITING
 
     # ------------------------------------------------------------------ after the step
@@ -192,6 +196,10 @@ class OmniARScheduler:
             if req is not None:
                 req.kv_transfer_done = True
                 self.kv.free(req)
+                continue
+            live = self.requests.get(rid)       # still running: its pages go when it finishes
+            if live is not None:
+                live.kv_transfer_done = True
         for req in [r for r in self.running if r.is_finished()]:
             self._release(req)
         return touched
