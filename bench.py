@@ -198,6 +198,39 @@ def main():
         sp.generator = torch.Generator(device=dev).manual_seed(0)
         return pipe.forward(OmniDiffusionRequest(prompts, sp, ["bench"] * B))
 
+    # ---- N > 1: the parallel layout against the same image computed by rank 0 alone (same weights,
+    #      same seed, the full-depth model, 4 denoising steps).  The GPU test box of a driver may
+    #      have one GPU only, so this is where the fused exchange kernels are checked at scale.
+    check = None
+    if world > 1 and not par.get("tensor_parallel_size", 1) > 1:
+        def short_image():
+            prompts = [{"prompt": "", "negative_prompt": " ", "prompt_embeds": pos_d[i],
+                        "negative_prompt_embeds": neg_d[i]} for i in range(B)]
+            sp = make_sp("pt")
+            sp.num_inference_steps = 4
+            sp.generator = torch.Generator(device=dev).manual_seed(0)
+            return pipe.forward(OmniDiffusionRequest(prompts, sp, ["check"] * B))
+        par_img = short_image().output.float()
+        barrier()
+        if rank == 0:
+            tr = pipe.transformer
+            saved = (tr.sp, pipe.cfg_exchange)
+            tr.sp, pipe.cfg_exchange = None, None
+            try:
+                one_img = short_image().output.float()
+            finally:
+                tr.sp, pipe.cfg_exchange = saved
+            diff = float((par_img - one_img).abs().max())
+            span = float(one_img.max() - one_img.min())
+            check = {"max_abs_diff_vs_single": round(diff, 5), "tolerance": 0.03, "image_value_span": round(span, 4),
+                     "what": "decoded image, 4 steps, full-depth model, N-GPU layout vs rank 0 alone"}
+        barrier()
+        flag = torch.tensor([0 if check is None or check["max_abs_diff_vs_single"] <= check["tolerance"] else 1],
+                            device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag):
+            raise SystemExit(f"parallel image differs from the single-GPU image: {check}")
+
     for _ in range(args.warmup):
         out = device_image()
     barrier()
@@ -252,6 +285,8 @@ def main():
                        "step_definition": "one full image: 50 denoise steps x (cond+uncond) + VAE decode"},
             "clocks": clocks, "gpu_launches": int(launches),
         }
+        if check is not None:
+            rec["correctness"] = check
         if e2e_ms is not None:
             rec["e2e"] = {"value": round(e2e_max / 1e3 / B, 4), "unit": "s/img", "h2d_bytes_per_step": h2d,
                           "d2h_bytes_per_step": d2h}

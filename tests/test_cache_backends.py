@@ -96,3 +96,34 @@ def test_cache_backends_on_every_family_with_a_block_stack(name):
                                                                 "max_continuous_cached_steps": 2, "enable_taylorseer": True,
                                                                 "Fn_compute_blocks": 1, "Bn_compute_blocks": 1})
     assert s["skipped_steps"] >= 1 and s["block_skip_ratio"] > 0 and torch.isfinite(db).all()
+
+
+def test_teacache_accumulates_absolute_rescaled_distance_like_the_reference_loop():
+    """Coefficients whose polynomial is negative at small rel (the Qwen-Image set ends in -2.0e-02):
+    the accumulator adds |poly(rel)| as the reference hook does (teacache/hook.py:225), so the skip
+    sequence equals a straight restatement of that loop."""
+    import numpy as np
+    from vllm_omni_b200.ops.fused import RelL1State, rel_l1_update
+    coef = [-4.50000000e+02, 2.80000000e+02, -4.50000000e+01, 3.20000000e+00, -2.00000000e-02]
+    thresh = 0.06
+    torch.manual_seed(0)
+    base = torch.randn(4, 64, 32)
+    rels = [0.001, 0.002, 0.004, 0.05, 0.003, 0.001, 0.08, 0.002, 0.002, 0.002, 0.03]
+    st = RelL1State("cpu", coef, thresh)
+    acc, want, got = 0.0, [], []
+    poly = np.poly1d(coef)
+    prev = base
+    for r in rels:
+        cur = prev + r * prev.abs().mean() / 0.7979 * torch.randn_like(prev)      # E|N(0,1)| = 0.7979
+        rel = float(((cur - prev).abs().mean() / (prev.abs().mean() + 1e-8)))
+        acc += abs(float(poly(rel)))
+        if acc < thresh:
+            want.append(1)
+        else:
+            want.append(0)
+            acc = 0.0
+        rel_l1_update(cur, prev, st)
+        got.append(int(st.state[2]))
+        prev = cur
+    assert got == want
+    assert 0 < sum(want) < len(want)

@@ -29,6 +29,7 @@
 // the tensor pipe works on one tile while the other tile's softmax runs.  Every wait is bounded.
 #include "host_util.h"
 #include "ptx_sm100.cuh"
+#include "peer_signal.cuh"
 
 namespace omni {
 
@@ -136,7 +137,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnOut out, int Sq, int Skv, int H, int Hkv,
                 const int* __restrict__ kv_lens, float scale_log2, int causal, int q_offset, AttnPaging pg,
-                int* status) {
+                PeerSignal sig, int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
   __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
@@ -488,6 +489,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         if (srow < Sq && out.lse && hf == 0)
           out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        if (out.n_peers > 1) {
+          // Fused exchange: rows go to their owner ranks over NVLink.  A store from the thread that
+          // owns the row would put 32 separate 16-byte writes on the link per instruction, so the
+          // warp's 32 rows x 64 columns pass through shared memory (the Q tile of this query tile is
+          // no longer read once o_done has fired) and leave as whole 128-byte row segments: 8 lanes
+          // per row, 4 rows per store instruction.
+          const uint32_t stg = sQ + t * ATT_TILE_BYTES + (q * 2 + hf) * 4096;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32];
+            if (n_kv > 0) {
+              tmem_ld_32x32(tO + c * 32, v);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v[e] = 0u;
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+              o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+              o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+              o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+              const int k = c * 4 + g;
+              st_shared_v4(stg + lane * 128 + ((k ^ (lane & 7)) << 4), o);
+            }
+          }
+          __syncwarp();
+          const int k = lane & 7;
+          const int row_base = qblk * 2 * ATT_BM + t * ATT_BM + q * 32;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3);
+            const int sr = row_base + r;
+            if (sr < Sq) {
+              __nv_bfloat16* dst;
+              if (sr >= out.split) {
+                const int t2 = sr - out.split;
+                const int owner = t2 / out.rows_per_rank2;
+                dst = out.o2_peers[owner] + (long)b * out.o2_bs + (long)(t2 - owner * out.rows_per_rank2) * out.o2_rs + (long)h * out.o2_hs;
+              } else {
+                const int owner = sr / out.rows_per_rank;
+                dst = out.o_peers[owner] + (long)b * out.o_bs + (long)(sr - owner * out.rows_per_rank) * out.o_rs + (long)h * out.o_hs;
+              }
+              const uint4 val = ld_shared_v4(stg + r * 128 + ((k ^ (r & 7)) << 4));
+              *reinterpret_cast<uint4*>(dst + hf * 64 + k * 8) = val;
+            }
+          }
+        } else {
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
@@ -510,12 +561,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
           }
         }
+        }
       }
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  // every peer store of this CTA was issued before the barrier above
+  if (threadIdx.x == 0) peer_signal_cta_done(sig, gridDim.x * gridDim.y * gridDim.z);
   if (s_abort) {
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) {
@@ -564,7 +618,7 @@ static int make_qkv_tmap(CUtensorMap* tm, const void* p, int S, int Hn, int B, l
 
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnOut& out, int B, int H,
                        int Hkv, int Sq, int Skv, const int* kv_lens, float scale, int causal, int q_offset,
-                       const AttnPaging& pg, int* status, cudaStream_t stream) {
+                       const AttnPaging& pg, int* status, cudaStream_t stream, const OmniSync* sync = nullptr) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
@@ -574,8 +628,11 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   const int splits = out.kv_splits > 1 ? out.kv_splits : 1;
   dim3 grid(((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM)) * splits, H, B);
   const float scale_log2 = scale * 1.4426950408889634f;
+  PeerSignal sig;
+  PeerWait unused;
+  unpack_sync(sync, sig, unused);
   attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens, scale_log2,
-                                                           causal, q_offset, pg, status);
+                                                           causal, q_offset, pg, sig, status);
   return (int)cudaGetLastError();
 }
 
@@ -585,14 +642,16 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
 // *_bs between batches; head_dim (128) is contiguous.  o2/split route query rows >= split
 // of every batch to a second tensor (used to hand text and image rows to their own
 // projections).  kv_lens: optional int32[B] valid key counts.  lse: optional fp32 [B,H,Sq].
-extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, const void* k, long k_rs,
-                             long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
-                             void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
-                             long o2_bs, int split, float* lse, int B, int H, int Hkv, int Sq, int Skv,
-                             int D, const int* kv_lens, float scale, int causal, int q_offset, int n_peers,
-                             int rows_per_rank,
-                             int rows_per_rank2, void* const* o_peers, void* const* o2_peers, int* status,
-                             void* stream) {
+// `sync` (may be null): the arrival this launch reports to the group once its peer stores are out
+// (see peer_signal.cuh); only the signalling half is used.
+extern "C" int omni_attn_fwd_sync(const void* q, long q_rs, long q_hs, long q_bs, const void* k, long k_rs,
+                                  long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
+                                  void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
+                                  long o2_bs, int split, float* lse, int B, int H, int Hkv, int Sq, int Skv,
+                                  int D, const int* kv_lens, float scale, int causal, int q_offset, int n_peers,
+                                  int rows_per_rank,
+                                  int rows_per_rank2, void* const* o_peers, void* const* o2_peers,
+                                  const omni::OmniSync* sync, int* status, void* stream) {
   using namespace omni;
   if (D != ATT_D || H <= 0 || Hkv <= 0 || (H % Hkv) || B <= 0) return RC_BAD_ARG;
   if (Sq <= 0) return RC_OK;
@@ -623,7 +682,20 @@ extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, con
   out.kv_splits = 1; out.part_o = nullptr; out.part_ml = nullptr;
   AttnPaging pg = {nullptr, 0, 0};
   return launch_attn(tq, tk, tv, out, B, H, Hkv, Sq, Skv, kv_lens, scale, causal, q_offset, pg, status,
-                     (cudaStream_t)stream);
+                     (cudaStream_t)stream, sync);
+}
+
+extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, const void* k, long k_rs,
+                             long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
+                             void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
+                             long o2_bs, int split, float* lse, int B, int H, int Hkv, int Sq, int Skv,
+                             int D, const int* kv_lens, float scale, int causal, int q_offset, int n_peers,
+                             int rows_per_rank,
+                             int rows_per_rank2, void* const* o_peers, void* const* o2_peers, int* status,
+                             void* stream) {
+  return omni_attn_fwd_sync(q, q_rs, q_hs, q_bs, k, k_rs, k_hs, k_bs, v, v_rs, v_hs, v_bs, o, o_rs, o_hs, o_bs, o2,
+                            o2_rs, o2_hs, o2_bs, split, lse, B, H, Hkv, Sq, Skv, D, kv_lens, scale, causal, q_offset,
+                            n_peers, rows_per_rank, rows_per_rank2, o_peers, o2_peers, nullptr, status, stream);
 }
 
 // Attention over a paged KV cache.  k_pool / v_pool: [num_blocks, block_size, Hkv, 128] bf16;

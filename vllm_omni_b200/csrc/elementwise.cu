@@ -20,6 +20,7 @@
 //                       (reference: vllm_omni/diffusion/cache/teacache/hook.py:185-232)
 #include "host_util.h"
 #include "ptx_sm100.cuh"
+#include "peer_signal.cuh"
 
 namespace omni {
 
@@ -185,8 +186,17 @@ qk_norm_rope128_kernel(__nv_bfloat16* __restrict__ qkv, long rows, int S, int H,
                        const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
                        const __nv_bfloat16* __restrict__ wq_alt, const __nv_bfloat16* __restrict__ wk_alt,
                        int s_alt, const float* __restrict__ cosb, const float* __restrict__ sinb,
-                       int interleaved, float eps, const int* __restrict__ positions) {
+                       int interleaved, float eps, const int* __restrict__ positions, PeerWait wt, int* status) {
   constexpr int D = 128;
+  if (wt.counter) {
+    // fused exchange: the rows come from the peers' QKV GEMM epilogues; wait for their arrivals
+    // here instead of in a barrier kernel of its own
+    if (threadIdx.x == 0) {
+      peer_wait_arrivals(wt, nullptr, status);
+      peer_wait_cta_exit(wt, gridDim.x);      // only this thread reads the epoch word
+    }
+    __syncthreads();
+  }
   const long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -454,7 +464,9 @@ rel_l1_finish_kernel(const float* __restrict__ scratch, int nparts, float* __res
         r = coef[0];
         for (int i = 1; i < ncoef; ++i) r = r * rel + coef[i];
       }
-      float acc = state[0] + r;
+      // the reference accumulates |rescale(rel)| (teacache/hook.py:225): a polynomial that dips below
+      // zero at small rel must not pull the accumulator down
+      float acc = state[0] + fabsf(r);
       float skip = 0.f;
       if (!force_compute && acc < thresh) skip = 1.f; else acc = 0.f;
       state[0] = acc;
@@ -496,12 +508,18 @@ extern "C" int omni_norm_modulate(const void* x, void* y, int rows, int D, int l
   return (int)cudaGetLastError();
 }
 
-extern "C" int omni_qk_norm_rope(void* qkv, int B, int S, int H, int Hkv, int D, int ld, const void* wq,
-                                 const void* wk, const void* wq_alt, const void* wk_alt, int s_alt,
-                                 const float* cosb, const float* sinb, int interleaved, float eps,
-                                 const int* positions, void* stream) {
+// `sync` (may be null, head_dim 128 only): arrivals from the peers' QKV epilogues that the kernel
+// waits for before it touches the buffer (see peer_signal.cuh); `status` receives a timeout code.
+extern "C" int omni_qk_norm_rope_sync(void* qkv, int B, int S, int H, int Hkv, int D, int ld, const void* wq,
+                                      const void* wk, const void* wq_alt, const void* wk_alt, int s_alt,
+                                      const float* cosb, const float* sinb, int interleaved, float eps,
+                                      const int* positions, const OmniSync* sync, int* status, void* stream) {
   const long total = (long)B * S * (H + Hkv);
-  if (total <= 0) return RC_OK;
+  if (total <= 0) return sync ? RC_BAD_ARG : RC_OK;
+  PeerSignal unused;
+  PeerWait wt;
+  unpack_sync(sync, unused, wt);
+  if (wt.counter && !(D == 128 && (ld & 7) == 0 && (wq != nullptr) == (wk != nullptr))) return RC_BAD_ARG;
   const int wpb = 8;
   const unsigned grid = (unsigned)((total + wpb - 1) / wpb);
   auto q = (__nv_bfloat16*)qkv;
@@ -512,7 +530,7 @@ extern "C" int omni_qk_norm_rope(void* qkv, int B, int S, int H, int Hkv, int D,
     const long rows = (long)B * S;
     (void)have_w;
     qk_norm_rope128_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
-        q, rows, S, H, Hkv, ld, a, b, c, d, s_alt, cosb, sinb, interleaved, eps, positions);
+        q, rows, S, H, Hkv, ld, a, b, c, d, s_alt, cosb, sinb, interleaved, eps, positions, wt, status);
   } else if (D == 128)
     qk_norm_rope_kernel<128><<<grid, wpb * 32, 0, (cudaStream_t)stream>>>(q, B, S, H, Hkv, ld, a, b, c, d, s_alt, cosb, sinb, interleaved, eps, positions);
   else if (D == 64)
@@ -520,6 +538,14 @@ extern "C" int omni_qk_norm_rope(void* qkv, int B, int S, int H, int Hkv, int D,
   else
     return RC_BAD_ARG;
   return (int)cudaGetLastError();
+}
+
+extern "C" int omni_qk_norm_rope(void* qkv, int B, int S, int H, int Hkv, int D, int ld, const void* wq,
+                                 const void* wk, const void* wq_alt, const void* wk_alt, int s_alt,
+                                 const float* cosb, const float* sinb, int interleaved, float eps,
+                                 const int* positions, void* stream) {
+  return omni_qk_norm_rope_sync(qkv, B, S, H, Hkv, D, ld, wq, wk, wq_alt, wk_alt, s_alt, cosb, sinb, interleaved, eps,
+                                positions, nullptr, nullptr, stream);
 }
 
 extern "C" int omni_cfg_euler_step(const void* pos, const void* neg, float* lat, void* lat_bf16, long rows,
@@ -554,7 +580,8 @@ extern "C" int omni_rel_l1_parts(long n) {
 extern "C" int omni_rel_l1(const void* a, const void* b, long n, float* scratch, float* state,
                            const float* coef, int ncoef, float thresh, int force_compute,
                            float* sums_out, void* stream) {
-  if (n <= 0 || (n & 7)) return RC_BAD_ARG;
+  if (n <= 0 || (n & 7) || a == nullptr || b == nullptr || scratch == nullptr) return RC_BAD_ARG;
+  if (ncoef < 0 || (state != nullptr && ncoef > 0 && coef == nullptr)) return RC_BAD_ARG;
   const int parts = omni_rel_l1_parts(n);
   rel_l1_partial_kernel<<<parts, RL_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, n >> 3, scratch);
   rel_l1_finish_kernel<<<1, RL_THREADS, 0, (cudaStream_t)stream>>>(scratch, parts, state, coef, ncoef, thresh, force_compute, sums_out);
@@ -582,7 +609,7 @@ extern "C" long omni_rel_l1_noalloc_max_elems(void) { return RL_NOALLOC_MAX_ELEM
 extern "C" const char* omni_rel_l1_noalloc_strerror(int rc) {
   switch (rc) {
     case 0: return "ok";
-    case RC_BAD_ARG: return "bad argument: n must be a positive multiple of 8 and the pointers non-null";
+    case RC_BAD_ARG: return "bad argument: n must be a positive multiple of 8, the pointers non-null, ncoef >= 0 and coef non-null when state and ncoef are given";
     case RC_TOO_LARGE: return "n exceeds omni_rel_l1_noalloc_max_elems() (2^28 elements per operand)";
     default: return rc > 0 ? "CUDA runtime error (the value is the cudaError_t)" : "unknown error";
   }
@@ -593,6 +620,7 @@ extern "C" int omni_rel_l1_noalloc(const void* a, const void* b, long n, float* 
                                    void* stream) {
   if (a == nullptr || b == nullptr || n <= 0 || (n & 7)) return RC_BAD_ARG;
   if (sums_out == nullptr && state == nullptr) return RC_BAD_ARG;
+  if (ncoef < 0 || (state != nullptr && ncoef > 0 && coef == nullptr)) return RC_BAD_ARG;
   if (n > RL_NOALLOC_MAX_ELEMS) return RC_TOO_LARGE;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -617,6 +645,8 @@ extern "C" int omni_rel_l1_noalloc(const void* a, const void* b, long n, float* 
   // so nothing left over from an earlier call is ever read and nothing needs clearing.
   rel_l1_partial_kernel<<<parts, RL_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, n >> 3, scratch);
+  e = cudaGetLastError();                 // report a failed first launch, not only the second
+  if (e != cudaSuccess) return (int)e;
   rel_l1_finish_kernel<<<1, RL_THREADS, 0, (cudaStream_t)stream>>>(scratch, parts, state, coef, ncoef, thresh,
                                                                    force_compute, sums_out);
   return (int)cudaGetLastError();

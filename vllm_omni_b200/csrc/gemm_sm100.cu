@@ -33,6 +33,7 @@
 // (vllm_omni/diffusion/models/qwen_image/qwen_image_transformer.py:427-560).
 #include "host_util.h"
 #include "ptx_sm100.cuh"
+#include "peer_signal.cuh"
 
 namespace omni {
 
@@ -85,10 +86,11 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : 6);
   static constexpr int ACC_STRIDE = (BN > 128) ? 256 : 128;
   static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
+  // ring + the epilogue warps' staging blocks for peer stores + alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * 32 * 128 + 1024;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
@@ -104,12 +106,10 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
   nb = in_g / gm;
 }
 
-// Fused epilogue for 32 accumulator columns of one output row: bias, activation, gate, residual,
-// bf16 conversion and the (possibly batched or peer-scattered) 16-byte stores.
-__device__ __forceinline__ void epilogue_store32(const uint32_t (&v)[32], int row, int col0, int N,
-                                                 __nv_bfloat16* __restrict__ C, int ldc, const GemmEpilogue& epi,
-                                                 const __nv_bfloat16* gate_row) {
-  __nv_bfloat16* out;
+// Where output element (row, col0) lands: plain row-major, batched rows, or a peer's buffer for
+// the fused collectives (column groups: Ulysses head scatter; row blocks: reduce-scatter feed).
+__device__ __forceinline__ __nv_bfloat16* epilogue_dest(int row, int col0, __nv_bfloat16* __restrict__ C, int ldc,
+                                                        const GemmEpilogue& epi) {
   __nv_bfloat16* cbase = C;
   int dcol = col0;
   if (epi.scatter_P > 1) {
@@ -119,16 +119,24 @@ __device__ __forceinline__ void epilogue_store32(const uint32_t (&v)[32], int ro
   }
   if (epi.scatter_rows > 0) {
     const int owner = row / epi.scatter_rows;
-    out = epi.peer_out[owner] + (size_t)(row - owner * epi.scatter_rows) * ldc + dcol;
-  } else if (epi.c_rows_per_batch > 0) {
-    const int cb = row / epi.c_rows_per_batch;
-    out = cbase + (size_t)cb * epi.c_batch_stride + (size_t)(row - cb * epi.c_rows_per_batch) * ldc + dcol;
-  } else {
-    out = cbase + (size_t)row * ldc + dcol;
+    return epi.peer_out[owner] + (size_t)(row - owner * epi.scatter_rows) * ldc + dcol;
   }
+  if (epi.c_rows_per_batch > 0) {
+    const int cb = row / epi.c_rows_per_batch;
+    return cbase + (size_t)cb * epi.c_batch_stride + (size_t)(row - cb * epi.c_rows_per_batch) * ldc + dcol;
+  }
+  return cbase + (size_t)row * ldc + dcol;
+}
+
+// Fused epilogue math for 32 accumulator columns of one output row: bias, activation, gate,
+// residual, bf16 conversion.  o[j] holds columns [col0 + 8j, col0 + 8j + 8); groups at or past N
+// are left untouched.
+__device__ __forceinline__ void epilogue_math32(const uint32_t (&v)[32], int row, int col0, int N,
+                                                const GemmEpilogue& epi, const __nv_bfloat16* gate_row,
+                                                uint4* __restrict__ o) {
   const __nv_bfloat16* res = epi.residual ? epi.residual + (size_t)row * epi.ldr + col0 : nullptr;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {  // 8 columns per 16-byte store
+  for (int j = 0; j < 4; ++j) {  // 8 columns per 16-byte group
     if (col0 + j * 8 < N) {
       float x[8];
 #pragma unroll
@@ -158,21 +166,61 @@ __device__ __forceinline__ void epilogue_store32(const uint32_t (&v)[32], int ro
         x[0] += r0.x; x[1] += r0.y; x[2] += r1.x; x[3] += r1.y;
         x[4] += r2.x; x[5] += r2.y; x[6] += r3.x; x[7] += r3.y;
       }
-      uint4 o;
-      o.x = pack_bf16(x[0], x[1]);
-      o.y = pack_bf16(x[2], x[3]);
-      o.z = pack_bf16(x[4], x[5]);
-      o.w = pack_bf16(x[6], x[7]);
-      *reinterpret_cast<uint4*>(out + j * 8) = o;
+      o[j].x = pack_bf16(x[0], x[1]);
+      o[j].y = pack_bf16(x[2], x[3]);
+      o[j].z = pack_bf16(x[4], x[5]);
+      o[j].w = pack_bf16(x[6], x[7]);
     }
   }
+}
+
+// Direct store of one row's 32 columns from the thread that owns the row (local outputs: L2
+// merges the 16-byte pieces of a line).
+__device__ __forceinline__ void epilogue_store32(const uint32_t (&v)[32], int row, int col0, int N,
+                                                 __nv_bfloat16* __restrict__ C, int ldc, const GemmEpilogue& epi,
+                                                 const __nv_bfloat16* gate_row) {
+  uint4 o[4];
+  epilogue_math32(v, row, col0, N, epi, gate_row, o);
+  __nv_bfloat16* out = epilogue_dest(row, col0, C, ldc, epi);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (col0 + j * 8 < N) *reinterpret_cast<uint4*>(out + j * 8) = o[j];
+}
+
+// Peer stores (fused collectives) go through a per-warp staging block in shared memory so that
+// the warp writes whole 128-byte row segments: a store from the row-owning thread would put 32
+// separate 16-byte writes on NVLink per instruction, which is request-bound far below link speed.
+//   write phase: lane = row, `ngroups` (4 or 8) 16-byte groups, group index XOR-swizzled by the row
+//   read  phase: 8 lanes per row, 4 rows per instruction -> 4 x 128 contiguous bytes per store
+constexpr int EPI_STAGE_BYTES = 32 * 128;          // per epilogue warp: 32 rows x 64 bf16 columns
+constexpr int EPI_STAGE_TOTAL = 8 * EPI_STAGE_BYTES;
+
+__device__ __forceinline__ void epilogue_store_staged(uint32_t stg, const uint4* __restrict__ o, int ngroups, int lane,
+                                                      int row0, int M, int col0, int N, __nv_bfloat16* __restrict__ C,
+                                                      int ldc, const GemmEpilogue& epi) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    if (k < ngroups) st_shared_v4(stg + lane * 128 + ((k ^ (lane & 7)) << 4), o[k]);
+  __syncwarp();
+  const int k = lane & 7;
+  const int col = col0 + k * 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const int row = row0 + r;
+    if (k < ngroups && row < M && col < N) {
+      const uint4 val = ld_shared_v4(stg + r * 128 + ((k ^ (r & 7)) << 4));
+      *reinterpret_cast<uint4*>(epilogue_dest(row, col, C, ldc, epi)) = val;
+    }
+  }
+  __syncwarp();
 }
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  __nv_bfloat16* __restrict__ C, int ldc, int M, int N, int K, GemmEpilogue epi,
-                 const int* __restrict__ tile_expert, ConvGeom conv, int* status) {
+                 const int* __restrict__ tile_expert, ConvGeom conv, PeerSignal sig, PeerWait wt, int* status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
 
@@ -221,6 +269,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
+      peer_wait_arrivals(wt, &s_abort, status);   // A may hold rows that peers write (fused exchange)
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         int mb, nb;
         tile_coords(t, num_m, num_n, mb, nb);
@@ -288,6 +337,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;         // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     constexpr int CH_PER_WARP = BN / 64;
+    const bool peer_stores = (epi.scatter_P > 1 || epi.scatter_rows > 0) && conv.taps == 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -309,14 +359,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const __nv_bfloat16* gate_row = nullptr;
       if (epi.gate && row_ok) gate_row = epi.gate + (size_t)(row / epi.rows_per_batch) * epi.gate_stride;
+      if (peer_stores) {
+        // fused collectives: 64 columns at a time through the staging block
+        const uint32_t stg = smem_base + STAGES * Cfg::STAGE_BYTES + (warp - 2) * EPI_STAGE_BYTES;
 #pragma unroll 1
-      for (int c = half * CH_PER_WARP; c < (half + 1) * CH_PER_WARP; ++c) {
-        const int col0 = nb * BN + c * 32;
-        if (col0 >= N) break;
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, v);
-        tmem_wait_ld();
-        if (row_ok) epilogue_store32(v, row, col0, N, C, ldc, epi, gate_row);
+        for (int c = half * CH_PER_WARP; c < (half + 1) * CH_PER_WARP; c += 2) {
+          const int col0 = nb * BN + c * 32;
+          if (col0 >= N) break;
+          const int nsub = min(2, (half + 1) * CH_PER_WARP - c);
+          uint4 o[8];
+          for (int sidx = 0; sidx < nsub; ++sidx) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * Cfg::ACC_STRIDE + (c + sidx) * 32, v);
+            tmem_wait_ld();
+            if (row_ok) epilogue_math32(v, row, col0 + sidx * 32, N, epi, gate_row, o + sidx * 4);
+          }
+          epilogue_store_staged(stg, o, nsub * 4, lane, mb * BM + q * 32, M, col0, N, C, ldc, epi);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = half * CH_PER_WARP; c < (half + 1) * CH_PER_WARP; ++c) {
+          const int col0 = nb * BN + c * 32;
+          if (col0 >= N) break;
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, v);
+          tmem_wait_ld();
+          if (row_ok) epilogue_store32(v, row, col0, N, C, ldc, epi, gate_row);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -328,6 +397,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) {
+    // every peer store of this CTA was issued before the barrier above
+    peer_signal_cta_done(sig, gridDim.x);
+    peer_wait_cta_exit(wt, gridDim.x);
+  }
   if (s_abort) {
     // give copies and MMAs that may still be in flight time to land before TMEM and
     // shared memory are handed back
@@ -356,8 +430,9 @@ struct PairCfg {
   static constexpr int A_BYTES = BM * BK * 2;            // 16 KiB: this CTA's 128 rows of A
   static constexpr int B_BYTES = (TN / 2) * BK * 2;      // this CTA's half of the W tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // a multiple of 1 KiB for every TN
-  static constexpr int STAGES = (TN == 256) ? 6 : (TN == 192 ? 7 : 8);
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr int STAGES = (TN == 256) ? 6 : (TN == 192 ? 6 : 7);
+  // ring + the epilogue warps' staging blocks for peer stores + alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * 32 * 128 + 1024;
 };
 
 // One launch can carry TWO problems that share N and K (the image and the text stream of a
@@ -376,6 +451,8 @@ struct PairArgs {
   PairProblem p[2];
   int n_problems;   // 1 or 2
   int N, K;
+  PeerSignal sig;   // arrivals this launch reports to the group once its peer stores are out
+  PeerWait wt;      // arrivals this launch needs before it reads its A operands
 };
 
 template <int TN>
@@ -444,6 +521,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ PairArgs args, int* status) {
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
+      peer_wait_arrivals(args.wt, &s_abort, status);   // A may hold rows that peers write (fused exchange)
       for (int t = pair; t < num_tiles; t += num_pairs) {
         int prob, mb, nb;
         locate(t, prob, mb, nb);
@@ -508,14 +586,34 @@ gemm_bf16_pair_kernel(const __grid_constant__ PairArgs args, int* status) {
       const bool row_ok = row < args.p[prob].M;
       const __nv_bfloat16* gate_row = nullptr;
       if (epi.gate && row_ok) gate_row = epi.gate + (size_t)(row / epi.rows_per_batch) * epi.gate_stride;
+      if (epi.scatter_P > 1 || epi.scatter_rows > 0) {
+        // fused collectives: 64 columns at a time through the staging block
+        const uint32_t stg = smem_base + P_STAGES * P_STAGE_BYTES + (warp - 2) * EPI_STAGE_BYTES;
+        const int M = args.p[prob].M;
 #pragma unroll 1
-      for (int c = half * (P_TILE_N / 64); c < (half + 1) * (P_TILE_N / 64); ++c) {
-        const int col0 = nb * P_TILE_N + c * 32;
-        if (col0 >= N) break;
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256 + c * 32, v);
-        tmem_wait_ld();
-        if (row_ok) epilogue_store32(v, row, col0, N, C, ldc, epi, gate_row);
+        for (int c = half * (P_TILE_N / 64); c < (half + 1) * (P_TILE_N / 64); c += 2) {
+          const int col0 = nb * P_TILE_N + c * 32;
+          if (col0 >= N) break;
+          const int nsub = min(2, (half + 1) * (P_TILE_N / 64) - c);
+          uint4 o[8];
+          for (int sidx = 0; sidx < nsub; ++sidx) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256 + (c + sidx) * 32, v);
+            tmem_wait_ld();
+            if (row_ok) epilogue_math32(v, row, col0 + sidx * 32, N, epi, gate_row, o + sidx * 4);
+          }
+          epilogue_store_staged(stg, o, nsub * 4, lane, mb * 2 * BM + (int)rank * BM + q * 32, M, col0, N, C, ldc, epi);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = half * (P_TILE_N / 64); c < (half + 1) * (P_TILE_N / 64); ++c) {
+          const int col0 = nb * P_TILE_N + c * 32;
+          if (col0 >= N) break;
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256 + c * 32, v);
+          tmem_wait_ld();
+          if (row_ok) epilogue_store32(v, row, col0, N, C, ldc, epi, gate_row);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -527,6 +625,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ PairArgs args, int* status) {
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) {
+    peer_signal_cta_done(args.sig, gridDim.x);
+    peer_wait_cta_exit(args.wt, gridDim.x);
+  }
   if (s_abort) {
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) {
@@ -616,7 +718,7 @@ template <int BN>
 static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, int ldc, int M,
                        int N, int K, int ldw, const GemmEpilogue& epi, int* status, int max_ctas,
                        cudaStream_t stream, int num_experts = 1, const int* tile_expert = nullptr,
-                       const ConvGeom* conv = nullptr) {
+                       const ConvGeom* conv = nullptr, const OmniSync* sync = nullptr) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmB;
   // weights as [E, N, K]; a plain linear layer is E = 1
@@ -634,7 +736,10 @@ static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, 
   int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
   ConvGeom geom = {};
   if (conv) geom = *conv;
-  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, tile_expert, geom, status);
+  PeerSignal sig;
+  PeerWait wt;
+  unpack_sync(sync, sig, wt);
+  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, tile_expert, geom, sig, wt, status);
   return (int)cudaGetLastError();
 }
 
@@ -663,13 +768,16 @@ static int pick_bn(int M, int N, int ctas) {
 // C ABI.  All pointers are device pointers; `status` is a device int32 that receives the
 // first timeout code (0 = none).  Strides are in elements.  force_bn = 0 lets the launcher
 // choose the tile width.
-extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
-                              int M, int N, int K, const void* bias, const void* residual, int ldr,
-                              const void* gate, int gate_stride, int rows_per_batch, int act,
-                              int c_rows_per_batch, long c_batch_stride, int scatter_P, int scatter_G,
-                              int scatter_rows, void* const* peer_out, int force_bn, int* status, void* stream) {
+// `sync` (may be null): arrivals this launch waits for before reading A, and / or reports to the
+// group after its peer stores (see peer_signal.cuh).
+extern "C" int omni_gemm_bf16_sync(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
+                                   int M, int N, int K, const void* bias, const void* residual, int ldr,
+                                   const void* gate, int gate_stride, int rows_per_batch, int act,
+                                   int c_rows_per_batch, long c_batch_stride, int scatter_P, int scatter_G,
+                                   int scatter_rows, void* const* peer_out, int force_bn, const omni::OmniSync* sync,
+                                   int* status, void* stream) {
   using namespace omni;
-  if (M <= 0 || N <= 0 || K <= 0) return RC_OK;
+  if (M <= 0 || N <= 0 || K <= 0) return sync ? RC_BAD_ARG : RC_OK;
   if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7) || (ldc & 7) || (ldr & 7) || (gate_stride & 7))
     return RC_BAD_ARG;
   if (gate && rows_per_batch <= 0) return RC_BAD_ARG;
@@ -716,17 +824,28 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
     const int tn = force_bn == 576 ? 256 : (force_bn == 448 ? 192 : (force_bn == 384 ? 128 : pick_pair_tn(M, N, pairs)));
     PairArgs args = {};
     args.n_problems = 1; args.N = N; args.K = K;
+    unpack_sync(sync, args.sig, args.wt);
     rc = fill_pair_problem(args.p[0], A, lda, W, ldw, c, ldc, M, N, K, epi, tn);
     if (rc) return rc;
     return launch_pair_tn(tn, args, status, pairs, s);
   }
   const int bn = force_bn ? force_bn : pick_bn(M, N, ctas);
   switch (bn) {
-    case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
-    case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
-    case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s);
+    case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s, 1, nullptr, nullptr, sync);
+    case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s, 1, nullptr, nullptr, sync);
+    case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s, 1, nullptr, nullptr, sync);
     default: return RC_BAD_ARG;
   }
+}
+
+extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
+                              int M, int N, int K, const void* bias, const void* residual, int ldr,
+                              const void* gate, int gate_stride, int rows_per_batch, int act,
+                              int c_rows_per_batch, long c_batch_stride, int scatter_P, int scatter_G,
+                              int scatter_rows, void* const* peer_out, int force_bn, int* status, void* stream) {
+  return omni_gemm_bf16_sync(A, lda, W, ldw, C, ldc, M, N, K, bias, residual, ldr, gate, gate_stride, rows_per_batch,
+                             act, c_rows_per_batch, c_batch_stride, scatter_P, scatter_G, scatter_rows, peer_out,
+                             force_bn, nullptr, status, stream);
 }
 
 // Two linear layers of the same shape (N, K) in one launch of the CTA-pair kernel: the image and
@@ -765,14 +884,10 @@ static int desc_epilogue(const OmniGemmDesc& d, omni::GemmEpilogue& epi) {
   return omni::RC_OK;
 }
 
-extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
-                              int M, int N, int K, const void* bias, const void* residual, int ldr,
-                              const void* gate, int gate_stride, int rows_per_batch, int act,
-                              int c_rows_per_batch, long c_batch_stride, int scatter_P, int scatter_G,
-                              int scatter_rows, void* const* peer_out, int force_bn, int* status, void* stream);
-
-extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d1, int N, int K, int force_pair,
-                                   int* status, void* stream) {
+// With `sync`: the wait goes to the first launch and the arrivals are reported by the last one, so
+// the group sees exactly one report per call whichever path (one paired launch, or two) is taken.
+extern "C" int omni_gemm_bf16_dual_sync(const OmniGemmDesc* d0, const OmniGemmDesc* d1, int N, int K, int force_pair,
+                                        const omni::OmniSync* sync, int* status, void* stream) {
   using namespace omni;
   if (!d0 || !d1 || N <= 0 || K <= 0 || (N & 7) || (K & 7)) return RC_BAD_ARG;
   const OmniGemmDesc* ds[2] = {d0, d1};
@@ -780,14 +895,26 @@ extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d
   long tiles = 0;
   for (int i = 0; i < 2; ++i) tiles += (long)((ds[i]->M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
   if (d0->M <= 0 || d1->M <= 0 || (!force_pair && (g_pair_mode != 1 || tiles < ctas / 2))) {
+    const int first = d0->M > 0 ? 0 : 1, last = d1->M > 0 ? 1 : 0;
     for (int i = 0; i < 2; ++i) {
       const OmniGemmDesc& d = *ds[i];
       if (d.M <= 0) continue;
       if (d.scatter_P > 1 && (N % d.scatter_G)) return RC_BAD_ARG;
-      int rc = omni_gemm_bf16(d.A, d.lda, d.W, d.ldw, d.C, d.ldc, d.M, N, K, d.bias, d.residual, d.ldr, d.gate,
-                              d.gate_stride, d.rows_per_batch, d.act, d.c_rows_per_batch, d.c_batch_stride,
-                              d.scatter_P > 1 ? d.scatter_P : 0, d.scatter_P > 1 ? d.scatter_G : 0, 0,
-                              d.scatter_P > 1 ? d.peer_out : nullptr, 0, status, stream);
+      OmniSync part = {};
+      if (sync) {
+        if (i == first) {
+          part.wait_counter = sync->wait_counter; part.wait_epoch = sync->wait_epoch;
+          part.wait_per_use = sync->wait_per_use; part.wait_timeout_ns = sync->wait_timeout_ns;
+        }
+        if (i == last) {
+          part.signal_n = sync->signal_n; part.signal_done = sync->signal_done;
+          for (int j = 0; j < SIGNAL_MAX_PEERS; ++j) part.signal_counters[j] = sync->signal_counters[j];
+        }
+      }
+      int rc = omni_gemm_bf16_sync(d.A, d.lda, d.W, d.ldw, d.C, d.ldc, d.M, N, K, d.bias, d.residual, d.ldr, d.gate,
+                                   d.gate_stride, d.rows_per_batch, d.act, d.c_rows_per_batch, d.c_batch_stride,
+                                   d.scatter_P > 1 ? d.scatter_P : 0, d.scatter_P > 1 ? d.scatter_G : 0, 0,
+                                   d.scatter_P > 1 ? d.peer_out : nullptr, 0, sync ? &part : nullptr, status, stream);
       if (rc) return rc;
     }
     return RC_OK;
@@ -796,6 +923,7 @@ extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d
   const int tn = pick_pair_tn(d0->M + d1->M, N, pairs);
   PairArgs args = {};
   args.n_problems = 2; args.N = N; args.K = K;
+  unpack_sync(sync, args.sig, args.wt);
   for (int i = 0; i < 2; ++i) {
     GemmEpilogue epi;
     int rc = desc_epilogue(*ds[i], epi);
@@ -806,6 +934,11 @@ extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d
     if (rc) return rc;
   }
   return launch_pair_tn(tn, args, status, pairs, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d1, int N, int K, int force_pair,
+                                   int* status, void* stream) {
+  return omni_gemm_bf16_dual_sync(d0, d1, N, K, force_pair, nullptr, status, stream);
 }
 
 // 0: the CTA-pair kernel runs only when forced (force_bn = 512); 1: automatic for large problems.

@@ -161,13 +161,21 @@ sample_kernel(const T* __restrict__ logits, long ld, int V, const SampleRow* __r
     cut = fmaxf(cut, lo);
   }
   if (p.top_p < 1.f) {
-    float lo = mx - 60.f, hi = mx;   // mass(w >= lo) >= top_p
+    // top-p is measured on the distribution that survived min-p and top-k (vLLM applies top-k first
+    // and top-p on the renormalised survivors), not on the full one
+    float surv = sum;
+    if (cut > -INFINITY) {
+      surv = 0.f;
+      for (int i = threadIdx.x; i < V; i += SP_THREADS) surv += w[i] >= cut ? __expf(w[i] - mx) : 0.f;
+      surv = block_reduce_sum(surv, sh);
+    }
+    float lo = mx - 60.f, hi = mx;   // mass(w >= lo) >= top_p * surviving mass
     for (int it = 0; it < 26; ++it) {
       const float mid = 0.5f * (lo + hi);
       float c = 0.f;
       for (int i = threadIdx.x; i < V; i += SP_THREADS) c += (w[i] >= mid && w[i] >= cut) ? __expf(w[i] - mx) : 0.f;
       c = block_reduce_sum(c, sh);
-      if (c >= p.top_p * sum) lo = mid; else hi = mid;
+      if (c >= p.top_p * surv) lo = mid; else hi = mid;
     }
     cut = fmaxf(cut, lo);
   }

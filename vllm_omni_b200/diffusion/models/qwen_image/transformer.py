@@ -243,6 +243,7 @@ class QwenImageTransformer2DModel(nn.Module):
         if self.sp is not None:
             # sequence parallel: img/txt hold this rank's rows; the exchange happens in the
             # GEMM / attention epilogues (fused) or in all-to-all calls (nccl baseline)
+            self.sp.block_plain = _plain_pair(blk)
             self.sp.project_qkv(blk.img.to_qkv, ws["img_n"], blk.txt.to_qkv, ws["txt_n"])
             self.sp.norm_rope(blk.img.norm_q, blk.img.norm_k, blk.txt.norm_q, blk.txt.norm_k, cos, sin, cfg.eps)
             attn_img, attn_txt = self.sp.attend(kv_lens, ws)
@@ -272,6 +273,9 @@ class QwenImageTransformer2DModel(nn.Module):
                            split=S_img)
             attn_img, attn_txt = ws["attn_img"], ws["attn_txt"]
         tp = getattr(self, "tp_heads", 0) if self.sp is None else 0
+        # fused sequence parallelism: the attention rows arrive from the peers; the first GEMM that
+        # reads them waits for the arrivals inside the kernel
+        out_wait = self.sp.take_out_wait() if self.sp is not None and hasattr(self.sp, "take_out_wait") else None
         swiglu = getattr(cfg, "mlp_act", "gelu_tanh") == "swiglu"        # FLUX-family variants with gated MLPs
         if (not tp) and S_txt > 0 and img.is_cuda and _plain_pair(blk) and not swiglu:
             # both streams per launch: out-projection, then the two norms, MLP up, MLP down
@@ -279,7 +283,8 @@ class QwenImageTransformer2DModel(nn.Module):
             bi, bt = blk.img, blk.txt
             gemm.linear_pair(
                 dict(x=attn_img, w=bi.to_out.weight, bias=bi.to_out.bias, residual=img, gate=mi[:, 2 * D:3 * D], out=img),
-                dict(x=attn_txt, w=bt.to_out.weight, bias=bt.to_out.bias, residual=txt, gate=mt[:, 2 * D:3 * D], out=txt))
+                dict(x=attn_txt, w=bt.to_out.weight, bias=bt.to_out.bias, residual=txt, gate=mt[:, 2 * D:3 * D], out=txt),
+                sync=out_wait)
             fused.norm_modulate(img, shift=mi[:, 3 * D:4 * D], scale=mi[:, 4 * D:5 * D], eps=cfg.eps, out=ws["img_n"])
             fused.norm_modulate(txt, shift=mt[:, 3 * D:4 * D], scale=mt[:, 4 * D:5 * D], eps=cfg.eps, out=ws["txt_n"])
             gemm.linear_pair(
@@ -304,7 +309,11 @@ class QwenImageTransformer2DModel(nn.Module):
                 sp.tp_mlp.up(xn, act="gelu_tanh", out=hbuf)
                 sp.tp_mlp.down(hbuf, gate=mm[:, 5 * D:6 * D], residual=x, out=x)
                 continue
-            sp.to_out(att, residual=x, gate=mm[:, 2 * D:3 * D], out=x)
+            if out_wait is not None:
+                sp.to_out(att, residual=x, gate=mm[:, 2 * D:3 * D], out=x, sync=out_wait)
+                out_wait = None
+            else:
+                sp.to_out(att, residual=x, gate=mm[:, 2 * D:3 * D], out=x)
             fused.norm_modulate(x, shift=mm[:, 3 * D:4 * D], scale=mm[:, 4 * D:5 * D], eps=cfg.eps, out=xn)
             if swiglu:
                 sp.mlp_down(fused.silu_mul(sp.mlp_up(xn)), residual=x, gate=mm[:, 5 * D:6 * D], out=x)

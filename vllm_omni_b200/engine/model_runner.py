@@ -14,6 +14,7 @@ request, outputs returned as multimodal tensors, no sampling
 from __future__ import annotations
 
 import os
+import zlib
 
 import torch
 
@@ -28,10 +29,12 @@ class ARModelRunner:
         self.model, self.device, self.dtype = model, device, dtype
         self.block_size = block_size
         dec = model.decoder_config
-        self.kv_caches = [(torch.zeros(num_blocks, block_size, dec.num_key_value_heads, dec.head_dim, dtype=dtype,
-                                       device=device),
-                           torch.zeros(num_blocks, block_size, dec.num_key_value_heads, dec.head_dim, dtype=dtype,
-                                       device=device)) for _ in range(dec.num_hidden_layers)]
+        # under tensor parallelism a rank keeps the pages of its own KV heads only
+        kvh = getattr(getattr(model, "decoder", None), "kv_heads_local", dec.num_key_value_heads)
+        self.kv_caches = [(torch.zeros(num_blocks, block_size, kvh, dec.head_dim, dtype=dtype, device=device),
+                           torch.zeros(num_blocks, block_size, kvh, dec.head_dim, dtype=dtype, device=device))
+                          for _ in range(dec.num_hidden_layers)]
+        self.tp_group = None        # set by OmniLLM: sampled ids of every step come from rank 0
         # decode-only steps replay a captured graph per batch-size bucket (``OMNI_AR_CUDA_GRAPH=1``); contexts
         # longer than ``OMNI_AR_GRAPH_MAX_TOKENS`` (default 4096) and mixed prefill/decode steps run eagerly
         self.graph_runner = None
@@ -118,6 +121,9 @@ class ARModelRunner:
             params = [self._row_params(r) for r in sample_reqs]
             ids, _ = sample(logits, params)
             ids = self.model.postprocess_sampled(sample_reqs, ids, h)
+            if self.tp_group is not None and self.tp_group.world_size > 1:
+                # one request stream on every rank: a rounding difference must not split it
+                ids = self.tp_group.broadcast(ids.contiguous(), src=0)
             for r, t in zip(sample_reqs, ids.tolist()):
                 sampled[r.request_id] = int(t)
         self.model.collect_outputs(sched, batch, hidden, captured)
@@ -125,7 +131,8 @@ class ARModelRunner:
 
     def _row_params(self, r) -> RowParams:
         sp = r.sampling_params
-        seed = sp.seed if sp.seed is not None else (hash(r.request_id) & 0x7FFFFFFF)
+        # a process-independent default seed (Python's str hash is salted per process)
+        seed = sp.seed if sp.seed is not None else (zlib.crc32(r.request_id.encode()) & 0x7FFFFFFF)
         allowed = sp.extra_args.get("allowed_token_range") if sp.extra_args else None
         return RowParams(sp.temperature, sp.top_p, sp.min_p, sp.top_k, sp.repetition_penalty, sp.presence_penalty,
                          sp.frequency_penalty, seed, len(r.output_token_ids), r.all_token_ids, r.num_prompt_tokens,

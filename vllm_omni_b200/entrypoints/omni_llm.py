@@ -72,9 +72,21 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.
 
 class OmniLLM:
     def __init__(self, model: str | None = None, stage_id: int = 0, **kwargs):
+        # tensor-parallel followers are started by rank 0 with these three (engine/tp_worker.py)
+        tp_rank = int(kwargs.pop("_tp_rank", 0))
+        tp_port = kwargs.pop("_tp_port", None)
+        tp_dev = kwargs.pop("_tp_device_index", None)
+        self._spawn_kwargs = dict(kwargs, stage_id=stage_id)
         self.args = a = OmniEngineArgs.from_kwargs(model=model, stage_id=stage_id, **kwargs)
         dtype = _DTYPES[a.dtype] if isinstance(a.dtype, str) else a.dtype
         use_cuda = torch.cuda.is_available() and a.device != "cpu"
+        tp = int(a.tensor_parallel_size or 1)
+        self.tp_size, self.tp_rank, self.tp_control, self._tp_procs = tp, tp_rank, None, []
+        tp_group = None
+        if tp > 1:
+            tp_group = self._join_tp_group(model, tp, tp_rank, tp_port, tp_dev, use_cuda)
+        elif a.enable_expert_parallel:
+            logger.info("stage %d: enable_expert_parallel has no effect with tensor_parallel_size=1", stage_id)
         device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
         if not use_cuda and dtype == torch.bfloat16:
             dtype = torch.float32
@@ -98,7 +110,18 @@ class OmniLLM:
                     n += self.model.load_auxiliary(model)
                 logger.info("stage %d (%s): loaded %d tensors", stage_id, a.model_stage, n)
         self.model.eval()
+        if tp_group is not None:
+            dec = getattr(self.model, "decoder", None)
+            if dec is None or not hasattr(dec, "enable_tensor_parallel"):
+                raise NotImplementedError(f"stage model {type(self.model).__name__} ({a.model_stage}) has no "
+                                          "tensor-parallel decoder; set tensor_parallel_size: 1 for this stage")
+            if a.async_chunk and stage_id > 0:
+                raise NotImplementedError("a tensor-parallel stage cannot take its input as a chunk stream yet")
+            dec.enable_tensor_parallel(tp_group, mode=os.environ.get("OMNI_TP_MODE"),
+                                       expert_parallel=bool(a.enable_expert_parallel))
         chunk_adapter = kv_mgr = None
+        if tp_rank > 0:
+            a.async_chunk, a.omni_kv_config = False, {}       # connectors live on rank 0 only
         if a.async_chunk and a.stage_connector_spec:
             from ..connectors.chunk_transfer_adapter import OmniChunkTransferAdapter
             chunk_adapter = OmniChunkTransferAdapter.from_spec(a.stage_connector_spec, stage_id, a.model_stage)
@@ -112,23 +135,81 @@ class OmniLLM:
                                 max_num_batched_tokens=a.max_num_batched_tokens, max_model_len=a.max_model_len,
                                 kv_transfer_criteria=crit, chunk_adapter=chunk_adapter, kv_transfer_manager=kv_mgr,
                                 stage_id=stage_id, engine_output_type=a.engine_output_type)
+        if tp_group is not None and hasattr(self.engine.runner, "tp_group"):
+            self.engine.runner.tp_group = tp_group
         self._profiler = None
+
+    # ------------------------------------------------------------------ tensor parallel group
+    def _join_tp_group(self, model, tp, tp_rank, tp_port, tp_dev, use_cuda):
+        """Rank 0 starts ranks 1..tp-1 (one process per GPU of this stage) and all join one group."""
+        import torch.distributed as dist
+        from ..engine import tp_worker
+        if use_cuda and torch.cuda.device_count() < tp:
+            raise ValueError(f"tensor_parallel_size={tp} but this stage sees {torch.cuda.device_count()} GPU(s); "
+                             "list them under runtime.devices")
+        if tp_rank == 0:
+            if dist.is_initialized():
+                raise NotImplementedError("tensor_parallel_size > 1 needs a process of its own for the stage "
+                                          "(runtime.process: true): this process already has a process group")
+            tp_port = tp_worker.free_port()
+            devs = list(range(tp)) if use_cuda else [0] * tp
+            self._tp_procs, readies, self._tp_errq = tp_worker.spawn_followers(tp, tp_port, model, self._spawn_kwargs, devs)
+            tp_dev = devs[0]
+        group = tp_worker.init_tp_process(tp_rank, tp, tp_port, use_cuda, tp_dev if tp_dev is not None else 0)
+        self.tp_control = tp_worker.TPControl(group)
+        return group
 
     # engine passthrough -------------------------------------------------
     def add_request(self, request_id, prompt, sampling_params: SamplingParams | None = None):
-        return self.engine.add_request(request_id, prompt, sampling_params)
+        req = self.engine.add_request(request_id, prompt, sampling_params)
+        if self.tp_control is not None and self.tp_rank == 0:
+            self.tp_control.pending_add.append((request_id, prompt, sampling_params))
+        return req
 
     def step(self):
+        if self.tp_control is not None and self.tp_rank == 0:
+            if not self.engine.has_unfinished_requests() and not self.tp_control.pending_add \
+                    and not self.tp_control.pending_abort:
+                return []                     # nothing to run: do not wake the followers
+            self._check_followers()
+            self.tp_control.leader_step_message()
         return self.engine.step()
+
+    def _check_followers(self):
+        for p in self._tp_procs:
+            if not p.is_alive():
+                why = ""
+                try:
+                    why = self._tp_errq.get_nowait()
+                except Exception:   # noqa: BLE001
+                    pass
+                raise RuntimeError(f"tensor-parallel worker {p.name} died (exit code {p.exitcode}) {why}")
 
     def has_unfinished_requests(self):
         return self.engine.has_unfinished_requests()
 
     def abort_request(self, request_ids):
+        if isinstance(request_ids, str):
+            request_ids = [request_ids]
         self.engine.abort_request(request_ids)
+        if self.tp_control is not None and self.tp_rank == 0:
+            self.tp_control.pending_abort.extend(request_ids)
 
     def generate(self, prompts, sampling_params=None):
-        return self.engine.generate(prompts, sampling_params)
+        """Blocking convenience wrapper: run the given prompts to completion."""
+        import time
+        if isinstance(prompts, (str, dict)):
+            prompts = [prompts]
+        sps = sampling_params if isinstance(sampling_params, (list, tuple)) else [sampling_params] * len(prompts)
+        ids = [f"gen-{i}-{time.monotonic_ns()}" for i in range(len(prompts))]
+        for rid, p, sp in zip(ids, prompts, sps):
+            self.add_request(rid, p, sp)
+        final = {}
+        while len(final) < len(ids):
+            for o in self.step():
+                if o.finished and o.request_id in ids:
+                    final[o.request_id] = o
+        return [final[i] for i in ids]
 
     def start_profile(self, trace_dir=None):
         from ..diffusion.profiler import TorchProfiler
@@ -142,4 +223,10 @@ class OmniLLM:
         return p
 
     def shutdown(self):
-        pass
+        if self.tp_control is not None and self.tp_rank == 0 and self._tp_procs:
+            self.tp_control.leader_shutdown()
+            for p in self._tp_procs:
+                p.join(timeout=10)
+                if p.is_alive():
+                    p.terminate()
+            self._tp_procs = []

@@ -167,6 +167,89 @@ class QwenDecoderModel(nn.Module):
         self.ep_group = None          # expert-parallel group: experts sharded, partial outputs summed
         self.ep_range = (0, cfg.num_experts)
         self.ep_reduce = None         # RowParallelReduce over the EP group (peer-memory sum of the partials)
+        self.tp_group = None          # tensor-parallel group: heads and MLP columns sharded
+        self.tp_reduce = None
+        self.local_heads = (cfg.num_attention_heads, cfg.num_key_value_heads)   # (q, kv) heads on this rank
+
+    @property
+    def kv_heads_local(self) -> int:
+        """KV heads whose pages this rank keeps (all of them without tensor parallelism)."""
+        return self.local_heads[1]
+
+    @torch.no_grad()
+    def enable_tensor_parallel(self, group, mode: str | None = None, expert_parallel: bool = False) -> None:
+        """Shard the decoder over ``group`` (the reference takes this from vLLM's
+        ``ColumnParallelLinear`` / ``RowParallelLinear`` / ``FusedMoE`` under ``tensor_parallel_size``,
+        vllm_omni/model_executor/stage_configs/qwen3_omni_moe.yaml:27):
+
+        * attention: rank r keeps q heads [r H/P, (r+1) H/P) and the KV heads they read (a KV head is
+          replicated when there are fewer KV heads than ranks); ``o_proj`` becomes row-parallel;
+        * dense MLP: gate/up column-parallel, down row-parallel;
+        * MoE: ``expert_parallel=True`` keeps whole experts per rank, otherwise every expert's FFN
+          dimension is sliced; either way each rank produces a partial sum of the MoE output;
+        * embeddings, norms, router, shared expert and the LM head stay replicated.
+
+        Row-parallel outputs are summed by ``RowParallelReduce`` (GEMM epilogue stores to the row
+        owners + local reduce on the GPU, all-reduce on CPU / ``mode="nccl"``)."""
+        from ..parallel.tensor_parallel import RowParallelReduce, shard_cols
+        cfg = self.cfg
+        P, r = group.world_size, group.rank_in_group
+        if P == 1:
+            return
+        H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        if H % P:
+            raise ValueError(f"num_attention_heads ({H}) must be divisible by tensor_parallel_size ({P})")
+        Hl = H // P
+        if Hkv % P == 0:
+            kv_lo, Hkvl = r * (Hkv // P), Hkv // P
+        elif P % Hkv == 0:
+            kv_lo, Hkvl = r // (P // Hkv), 1              # several ranks share one KV head
+        else:
+            raise ValueError(f"num_key_value_heads ({Hkv}) and tensor_parallel_size ({P}) must divide one another")
+        self.tp_group = group
+        self.tp_reduce = RowParallelReduce(group, mode)
+        self.local_heads = (Hl, Hkvl)
+        qs = slice(r * Hl * Dh, (r + 1) * Hl * Dh)
+        ks = slice(H * Dh + kv_lo * Dh, H * Dh + (kv_lo + Hkvl) * Dh)
+        vs = slice((H + Hkv) * Dh + kv_lo * Dh, (H + Hkv) * Dh + (kv_lo + Hkvl) * Dh)
+
+        def relinear(old: FusedLinear, w: torch.Tensor, b: torch.Tensor | None) -> FusedLinear:
+            new = FusedLinear(w.shape[1], w.shape[0], bias=b is not None, dtype=w.dtype, device="meta")
+            new.weight = nn.Parameter(w.contiguous(), requires_grad=False)
+            if b is not None:
+                new.bias = nn.Parameter(b.contiguous(), requires_grad=False)
+            return new
+
+        for layer in self.layers:
+            w = layer.qkv_proj.weight.data
+            b = layer.qkv_proj.bias.data if layer.qkv_proj.bias is not None else None
+            layer.qkv_proj = relinear(layer.qkv_proj, torch.cat([w[qs], w[ks], w[vs]], 0),
+                                      None if b is None else torch.cat([b[qs], b[ks], b[vs]], 0))
+            layer.o_proj = relinear(layer.o_proj, layer.o_proj.weight.data[:, qs], None)
+            if not cfg.num_experts:
+                F_ = cfg.intermediate_size
+                if F_ % P:
+                    raise ValueError(f"intermediate_size ({F_}) must be divisible by tensor_parallel_size ({P})")
+                Fl = F_ // P
+                gu = layer.gate_up.weight.data
+                layer.gate_up = relinear(layer.gate_up, torch.cat([gu[r * Fl:(r + 1) * Fl],
+                                                                   gu[F_ + r * Fl:F_ + (r + 1) * Fl]], 0), None)
+                layer.down = relinear(layer.down, shard_cols(layer.down.weight.data, r, P), None)
+            elif not expert_parallel:
+                F_ = cfg.moe_intermediate_size
+                if F_ % (P * 8):
+                    raise ValueError(f"moe_intermediate_size ({F_}) must be divisible by 8 x tensor_parallel_size")
+                Fl = F_ // P
+                w13 = layer.w13.data
+                layer.w13 = nn.Parameter(torch.cat([w13[:, r * Fl:(r + 1) * Fl], w13[:, F_ + r * Fl:F_ + (r + 1) * Fl]],
+                                                   1).contiguous(), requires_grad=False)
+                layer.w2 = nn.Parameter(layer.w2.data[:, :, r * Fl:(r + 1) * Fl].contiguous(), requires_grad=False)
+        if cfg.num_experts:
+            if expert_parallel:
+                self.enable_expert_parallel(group, mode)
+            else:
+                # FFN-sliced experts: every rank runs all experts on its slice; same partial-sum path
+                self.ep_group, self.ep_range, self.ep_reduce = group, (0, cfg.num_experts), self.tp_reduce
 
     @torch.no_grad()
     def enable_expert_parallel(self, group, mode: str | None = None) -> None:
@@ -200,7 +283,7 @@ class QwenDecoderModel(nn.Module):
 
     def attention_block(self, layer: DecoderLayer, qkv: torch.Tensor, batch: ModelBatch, k_cache, v_cache, out):
         cfg = self.cfg
-        H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        (H, Hkv), Dh = self.local_heads, cfg.head_dim
         T = qkv.shape[0]
         q = qkv[:, :H * Dh].view(T, H, Dh)
         k = qkv[:, H * Dh:(H + Hkv) * Dh].view(T, Hkv, Dh)
@@ -234,7 +317,7 @@ class QwenDecoderModel(nn.Module):
         of [T, D] tensors; entry i is added to the output of layer i (visual features of the
         vision tower's intermediate blocks, zero on the other rows)."""
         cfg = self.cfg
-        H, Hkv, Dh = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        (H, Hkv), Dh = self.local_heads, cfg.head_dim        # this rank's heads under tensor parallelism
         x = self.embed(batch)
         T = x.shape[0]
         cos, sin = self.rope.cos_sin_for(batch.positions, cfg.mrope_section, cfg.mrope_interleaved)
@@ -243,6 +326,7 @@ class QwenDecoderModel(nn.Module):
             captured[0] = x.clone()
         xn = torch.empty_like(x)
         attn = torch.empty(T, H * Dh, dtype=x.dtype, device=x.device)
+        tp_cap = max(64, 1 << (T - 1).bit_length())          # peer-buffer bucket of the row-parallel reduces
         for li, layer in enumerate(self.layers):
             fused.norm_modulate(x, weight=layer.input_layernorm, rms=True, eps=cfg.rms_norm_eps, out=xn)
             qkv = layer.qkv_proj(xn)
@@ -250,7 +334,10 @@ class QwenDecoderModel(nn.Module):
                                 interleaved=False, eps=cfg.rms_norm_eps)
             kc, vc = kv_caches[li] if kv_caches is not None else (None, None)
             self.attention_block(layer, qkv, batch, kc, vc, attn)
-            layer.o_proj(attn, residual=x, out=x)
+            if self.tp_reduce is not None:
+                self.tp_reduce.linear(layer.o_proj, attn, residual=x, out=x, capacity=tp_cap)   # sum over ranks
+            else:
+                layer.o_proj(attn, residual=x, out=x)
             fused.norm_modulate(x, weight=layer.post_attention_layernorm, rms=True, eps=cfg.rms_norm_eps, out=xn)
             if cfg.num_experts:
                 logits = layer.router(xn)
@@ -282,7 +369,10 @@ class QwenDecoderModel(nn.Module):
                     x.add_(shared.to(x.dtype))
             else:
                 h = fused.silu_mul(layer.gate_up(xn))
-                layer.down(h, residual=x, out=x)
+                if self.tp_reduce is not None:
+                    self.tp_reduce.linear(layer.down, h, residual=x, out=x, capacity=tp_cap)
+                else:
+                    layer.down(h, residual=x, out=x)
             if deepstack is not None and li < len(deepstack):
                 x.add_(deepstack[li].to(x.dtype))
             if (li + 1) in capture_layers:

@@ -41,7 +41,7 @@ def attention_reference(q, k, v, scale=None, kv_lens=None, return_lse=False, cau
 
 
 def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, return_lse=False,
-              scatter=None, causal=False, q_offset=0):
+              scatter=None, causal=False, q_offset=0, sync=None):
     """Non-causal attention.  Returns ``out`` ([B, Sq, H, D], or the given buffer).
 
     ``out2``/``split``: rows >= split of every batch go to ``out2`` (row index s - split).
@@ -50,6 +50,9 @@ def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, r
     fused reverse all-to-all; row s < split is stored on rank s // rows_per_rank through the device
     pointer ``o_ptrs[rank]`` (strides = (row, head, batch) in elements), rows >= split likewise with
     the ``*2`` entries.  ``out`` / ``out2`` are then unused.
+
+    ``sync``: an ``OmniSync`` (parallel/peer_memory.py) whose signalling half tells the group that
+    this launch's peer stores are out, so the consumer kernel waits for them itself.
     """
     B, Sq, H, D = q.shape
     Skv, Hkv = k.shape[1], k.shape[2]
@@ -87,7 +90,7 @@ def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, r
     if kv_lens is not None:
         assert kv_lens.dtype == torch.int32 and kv_lens.is_cuda
     st = nv.status_word(q.device)
-    rc = nv.lib("attention_sm100").omni_attn_fwd(
+    rc = nv.lib("attention_sm100").omni_attn_fwd_sync(
         nv.ptr(q), c_long(q.stride(1)), c_long(q.stride(2)), c_long(q.stride(0)),
         nv.ptr(k), c_long(k.stride(1)), c_long(k.stride(2)), c_long(k.stride(0)),
         nv.ptr(v), c_long(v.stride(1)), c_long(v.stride(2)), c_long(v.stride(0)),
@@ -95,6 +98,7 @@ def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, r
         out2_ptr, c_long(o2s[0]), c_long(o2s[1]), c_long(o2s[2]), c_int(split),
         nv.ptr(lse), c_int(B), c_int(H), c_int(Hkv), c_int(Sq), c_int(Skv), c_int(D), nv.ptr(kv_lens),
         c_float(scale), c_int(1 if causal else 0), c_int(q_offset), c_int(sc["n_peers"] if sc else 0), c_int(sc["rows_per_rank"] if sc else 0),
-        c_int(sc.get("rows_per_rank2", 0) if sc else 0), op, o2p, nv.ptr(st), nv.stream_ptr())
+        c_int(sc.get("rows_per_rank2", 0) if sc else 0), op, o2p,
+        ctypes.byref(sync) if sync is not None else None, nv.ptr(st), nv.stream_ptr())
     nv.check_rc(rc, "omni_attn_fwd")
     return (out, lse) if return_lse else out

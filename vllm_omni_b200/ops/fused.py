@@ -117,11 +117,12 @@ def qk_norm_rope_reference(qkv, H, Hkv, D, wq, wk, wq_alt, wk_alt, s_alt, cos, s
 
 
 def qk_norm_rope_(qkv, H, Hkv, D, wq=None, wk=None, wq_alt=None, wk_alt=None, s_alt=1 << 30, cos=None, sin=None,
-                  interleaved=True, eps=1e-6, positions=None):
+                  interleaved=True, eps=1e-6, positions=None, sync=None):
     """In place on a packed qkv buffer [B, S, (H + 2*Hkv) * D]: q,k <- rope(rmsnorm(q,k)).
 
     Rows s >= s_alt use the norm weights ``wq_alt`` / ``wk_alt`` (the text rows that follow
-    the image rows of a joint sequence)."""
+    the image rows of a joint sequence).  ``sync``: an ``OmniSync`` whose waiting half names the
+    arrivals (peers' QKV epilogues) the kernel waits for before it touches the buffer."""
     if not qkv.is_cuda:
         qkv.copy_(qk_norm_rope_reference(qkv, H, Hkv, D, wq, wk, wq_alt, wk_alt, s_alt, cos, sin, interleaved, eps, positions))
         return qkv
@@ -132,10 +133,11 @@ def qk_norm_rope_(qkv, H, Hkv, D, wq=None, wk=None, wq_alt=None, wk_alt=None, s_
         assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape[-1] == D // 2
     if positions is not None:
         assert positions.dtype == torch.int32 and positions.is_contiguous()
-    rc = nv.lib("elementwise").omni_qk_norm_rope(
+    rc = nv.lib("elementwise").omni_qk_norm_rope_sync(
         nv.ptr(qkv), c_int(B), c_int(S), c_int(H), c_int(Hkv), c_int(D), c_int(ld), nv.ptr(wq), nv.ptr(wk),
         nv.ptr(wq_alt), nv.ptr(wk_alt), c_int(min(s_alt, 1 << 30)), nv.ptr(cos), nv.ptr(sin), c_int(1 if interleaved else 0),
-        c_float(eps), nv.ptr(positions), nv.stream_ptr())
+        c_float(eps), nv.ptr(positions), ctypes.byref(sync) if sync is not None else None,
+        nv.ptr(nv.status_word(qkv.device)), nv.stream_ptr())
     nv.check_rc(rc, "omni_qk_norm_rope")
     return qkv
 
@@ -233,7 +235,7 @@ def rel_l1_update(a, b, st: RelL1State, force_compute: bool = False):
             r = 0.0
             for c in st.coef.tolist():
                 r = r * rel + c
-        acc = float(st.state[0]) + r
+        acc = float(st.state[0]) + abs(r)        # |rescale(rel)|, as the reference accumulates it
         skip = 0.0
         if (not force_compute) and acc < st.thresh:
             skip = 1.0

@@ -48,7 +48,8 @@ def linear_reference(x, w, bias=None, act=None, residual=None, gate=None):
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
            residual: torch.Tensor | None = None, gate: torch.Tensor | None = None,
            out: torch.Tensor | None = None, force_bn: int = 0,
-           out_rows_per_batch: int = 0, out_batch_stride: int = 0, scatter=None, row_scatter=None) -> torch.Tensor:
+           out_rows_per_batch: int = 0, out_batch_stride: int = 0, scatter=None, row_scatter=None,
+           sync=None) -> torch.Tensor:
     """y = residual + gate * act(x @ w.T + bias).
 
     ``out_rows_per_batch`` / ``out_batch_stride`` (elements): row r of the result is stored at
@@ -62,6 +63,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
     ``row_scatter = (rows_per_owner, ptrs, ld)``: fused reduce-scatter feed.  Output row r goes to
     rank r // rows_per_owner, as row r % rows_per_owner of the buffer at ``ptrs[that rank]`` (row
     pitch ``ld``).  ``len(ptrs)`` must equal ceil(M / rows_per_owner).  ``out`` is ignored.
+
+    ``sync``: an ``OmniSync`` (parallel/peer_memory.py): arrivals the launch waits for before it reads
+    ``x`` (rows that peers write) and / or reports to the group after its own peer stores.
 
     x: [..., K] bf16 (last dim contiguous), w: [N, K] bf16, bias: [N], residual: [..., N]
     (may be ``out``), gate: [B, N] view (last dim contiguous, any row stride) where the rows
@@ -115,13 +119,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
         rpb = M // gate.shape[0]
         gs = gate.stride(0) if gate.shape[0] > 1 else N
     st = nv.status_word(x.device)
-    rc = nv.lib("gemm_sm100").omni_gemm_bf16(
+    rc = nv.lib("gemm_sm100").omni_gemm_bf16_sync(
         nv.ptr(x2), ctypes.c_int(x2.stride(0)), nv.ptr(w), ctypes.c_int(w.stride(0)),
         c_ptr, ctypes.c_int(ldc), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
         nv.ptr(bias), nv.ptr(res2), ctypes.c_int(ldr), nv.ptr(gate), ctypes.c_int(gs), ctypes.c_int(rpb),
         ctypes.c_int(ACT[act]), ctypes.c_int(out_rows_per_batch), ctypes.c_long(out_batch_stride),
-        ctypes.c_int(sc_P), ctypes.c_int(sc_G), ctypes.c_int(sc_rows), sc_arr, ctypes.c_int(force_bn), nv.ptr(st),
-        nv.stream_ptr())
+        ctypes.c_int(sc_P), ctypes.c_int(sc_G), ctypes.c_int(sc_rows), sc_arr, ctypes.c_int(force_bn),
+        ctypes.byref(sync) if sync is not None else None, nv.ptr(st), nv.stream_ptr())
     nv.check_rc(rc, "omni_gemm_bf16")
     return None if to_peers else out
 
@@ -170,13 +174,14 @@ def _desc(x, w, bias, act, residual, gate, out, out_rows_per_batch, out_batch_st
     return d
 
 
-def linear_pair(a: dict, b: dict, force_pair: bool | None = None) -> None:
+def linear_pair(a: dict, b: dict, force_pair: bool | None = None, sync=None) -> None:
     """Two linear layers of the same (N, K) in ONE launch (the image and text streams of a
     dual-stream block).  ``a`` / ``b``: keyword sets of ``linear`` — ``x, w, bias, act, residual,
     gate, out`` (``out`` is required unless ``scatter`` is given), optionally ``out_rows_per_batch,
     out_batch_stride, scatter``.  On the
     GPU both problems share the CTA-pair kernel's tile list, so the short one fills the last wave
-    of the long one; on CPU they run one after the other."""
+    of the long one; on CPU they run one after the other.  ``sync`` as in ``linear``: one wait before
+    and one report after the pair, whichever way it is launched."""
     xa, xb = a["x"], b["x"]
     if (not xa.is_cuda) or xa.numel() == 0 or xb.numel() == 0:
         for kw in (a, b):
@@ -191,7 +196,8 @@ def linear_pair(a: dict, b: dict, force_pair: bool | None = None) -> None:
     if force_pair is None:                   # tests force the CTA-pair kernel at sizes below one wave
         force_pair = os.environ.get("OMNI_GEMM_DUAL_FORCE") == "1"
     st = nv.status_word(xa.device)
-    rc = nv.lib("gemm_sm100").omni_gemm_bf16_dual(ctypes.byref(ds[0]), ctypes.byref(ds[1]), ctypes.c_int(N),
-                                                  ctypes.c_int(K), ctypes.c_int(1 if force_pair else 0), nv.ptr(st),
-                                                  nv.stream_ptr())
+    rc = nv.lib("gemm_sm100").omni_gemm_bf16_dual_sync(ctypes.byref(ds[0]), ctypes.byref(ds[1]), ctypes.c_int(N),
+                                                       ctypes.c_int(K), ctypes.c_int(1 if force_pair else 0),
+                                                       ctypes.byref(sync) if sync is not None else None, nv.ptr(st),
+                                                       nv.stream_ptr())
     nv.check_rc(rc, "omni_gemm_bf16_dual")

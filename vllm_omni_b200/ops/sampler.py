@@ -89,7 +89,7 @@ def sample_reference(logits: torch.Tensor, rows: list[RowParams]):
             pr = torch.where(keep, torch.exp(w - mx), torch.zeros(()))
             srt, order = torch.sort(pr, descending=True)
             cum = torch.cumsum(srt, 0)
-            n = int((cum < p.top_p * torch.exp(w - mx).sum()).sum()) + 1
+            n = int((cum < p.top_p * pr.sum()).sum()) + 1       # mass of what survived min-p / top-k
             k2 = torch.zeros(V, dtype=torch.bool)
             k2[order[:n]] = True
             keep &= k2

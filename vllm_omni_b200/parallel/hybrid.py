@@ -38,6 +38,7 @@ class HybridJointAttention:
         self.mode = mode or ("peer" if torch.cuda.is_available() else "nccl")
         self.uly = UlyssesJointAttention(sp_group.ulysses, num_heads, head_dim,
                                          mode="fused" if self.mode == "peer" else "nccl")
+        self.uly.use_flags = False       # this class orders its exchanges with barriers and NCCL calls
         self.H, self.Dh, self.Hp = num_heads, head_dim, num_heads // self.U
         self.arena = None
         self._key = None

@@ -53,6 +53,70 @@ class SymTensor:
         return [p + byte_offset for p in self.ptrs]
 
 
+class OmniSync(ctypes.Structure):
+    """C mirror of ``OmniSync`` in csrc/peer_signal.cuh: what a launch reports to the group after its
+    peer stores (``signal_*``) and what it waits for before reading peer-written data (``wait_*``)."""
+    _fields_ = [("signal_counters", ctypes.c_void_p * 16), ("signal_done", ctypes.c_void_p),
+                ("signal_n", ctypes.c_int), ("wait_counter", ctypes.c_void_p), ("wait_epoch", ctypes.c_void_p),
+                ("wait_per_use", ctypes.c_ulonglong), ("wait_timeout_ns", ctypes.c_ulonglong)]
+
+
+class SignalChannel:
+    """One direction of a fused exchange: producers on every rank report an arrival per launch,
+    the consumer kernel on every rank waits for ``per_use`` arrivals (producer launches x ranks).
+
+    ``counter`` lives in the arena (peers add to it); ``done`` (producer CTA count) and ``epoch``
+    (consumer uses completed, CTA exit count) are local device words, so a captured CUDA graph
+    replays correctly: nothing in the launch arguments changes from use to use."""
+
+    def __init__(self, arena: "PeerArena | None", producer_launches: int = 1, device=None, timeout_ms: int = 1000):
+        """``arena=None``: a single-rank channel on ``device`` (one GPU; used by tests and by groups of
+        one), whose counter is an ordinary device tensor."""
+        self.arena = arena
+        if arena is not None:
+            self.counter = arena.alloc((16,), torch.int64)      # [0] is the arrival counter; the rest pads a line
+            world, device, timeout_ns = arena.world, arena.device, arena.timeout_ns
+        else:
+            t = torch.zeros(16, dtype=torch.int64, device=device)
+            self.counter = SymTensor(t, [t.data_ptr()], 0)
+            world, timeout_ns = 1, int(timeout_ms) * 1_000_000
+        self.counter.local.zero_()
+        self.done = torch.zeros(4, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(2, dtype=torch.int64, device=device)
+        self.per_use = producer_launches * world
+        self._signal = OmniSync()
+        for r, p in enumerate(self.counter.ptrs):
+            self._signal.signal_counters[r] = p
+        self._signal.signal_done = self.done.data_ptr()
+        self._signal.signal_n = world
+        self._wait = OmniSync()
+        self._wait.wait_counter = self.counter.local.data_ptr()
+        self._wait.wait_epoch = self.epoch.data_ptr()
+        self._wait.wait_per_use = self.per_use
+        self._wait.wait_timeout_ns = timeout_ns
+
+    def signal(self) -> OmniSync:
+        """For the producer launch (reports one arrival to every rank when its stores are out)."""
+        return self._signal
+
+    def wait(self) -> OmniSync:
+        """For the consumer launch (waits for this use's arrivals before reading)."""
+        return self._wait
+
+    @staticmethod
+    def combine(wait_from: "SignalChannel | None", signal_to: "SignalChannel | None") -> OmniSync | None:
+        """A launch that consumes one exchange and produces the next."""
+        if wait_from is None and signal_to is None:
+            return None
+        s = OmniSync()
+        if signal_to is not None:
+            ctypes.memmove(ctypes.byref(s), ctypes.byref(signal_to._signal), ctypes.sizeof(OmniSync))
+        if wait_from is not None:
+            s.wait_counter, s.wait_epoch = wait_from._wait.wait_counter, wait_from._wait.wait_epoch
+            s.wait_per_use, s.wait_timeout_ns = wait_from._wait.wait_per_use, wait_from._wait.wait_timeout_ns
+        return s
+
+
 class PeerArena:
     def __init__(self, group, nbytes: int, device: torch.device | None = None, timeout_ms: int = 1000):
         """``group``: a GroupCoordinator (uses its CPU twin to exchange IPC handles)."""

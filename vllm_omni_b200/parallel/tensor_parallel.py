@@ -69,8 +69,11 @@ class RowParallelReduce:
             st = self._states[key] = (arena, slots, result, per)
         self.arena, self.slots, self.result, self.per = st
 
-    def linear(self, layer: FusedLinear, x: torch.Tensor, bias=None, gate=None, residual=None, out=None):
-        """``layer`` holds this rank's [N, K/P] weight slice, ``x`` its [.., K/P] input slice."""
+    def linear(self, layer: FusedLinear, x: torch.Tensor, bias=None, gate=None, residual=None, out=None,
+               capacity: int | None = None):
+        """``layer`` holds this rank's [N, K/P] weight slice, ``x`` its [.., K/P] input slice.
+        ``capacity`` (>= rows of x): size the peer buffers for this many rows, so that callers whose
+        row count changes from call to call (AR decode) reuse one arena per capacity bucket."""
         N = layer.out_features
         if self.P == 1 or self.mode == "nccl" or not x.is_cuda:
             partial = layer(x)
@@ -78,7 +81,8 @@ class RowParallelReduce:
         from ..ops import gemm
         x2 = x.reshape(-1, x.shape[-1])
         res = self.reduce_from(lambda per, ptrs: gemm.linear(x2, layer.weight, None, row_scatter=(per, ptrs, N)),
-                               x2.shape[0], N, x.dtype, x.device, bias=bias, gate=gate, residual=residual)
+                               x2.shape[0], N, x.dtype, x.device, bias=bias, gate=gate, residual=residual,
+                               capacity=capacity)
         res = res.view(*x.shape[:-1], N)
         if out is not None:
             out.copy_(res)
