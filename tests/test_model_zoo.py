@@ -62,6 +62,9 @@ def test_pipeline_runs_tiny(name):
         sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0, num_frames=5,
                                          guidance_scale=3.0, extra_args={"audio_seconds": 0.05})
         prompt = {"prompt": "a small test", "negative_prompt": " "}
+        if name == "LongCatImageEditPipeline":             # an editing pipeline needs its input image
+            from PIL import Image
+            prompt["multi_modal_data"] = {"image": Image.new("RGB", (64, 64), (90, 120, 30))}
         out = o.generate([prompt], sp)[0]
         if name.startswith("Wan"):
             v = out.multimodal_output["video"]
@@ -86,5 +89,35 @@ def test_registry_lists_every_family_and_bagel_takes_injected_kv():
         sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0)
         sp.past_key_values = [(torch.randn(5, 1, 32), torch.randn(5, 1, 32))]          # the prompt context of an AR stage
         assert o.generate(["x"], sp)[0].images[0].size == (64, 64)
+    finally:
+        o.close()
+
+
+def test_longcat_edit_appends_the_condition_image_as_a_second_frame():
+    """LongCat-Image editing: the VAE latents of the input image follow the noise rows with modality
+    id 2 on the first rotary axis; only the noise rows are stepped; the result depends on the image;
+    a request without an image is refused."""
+    import numpy as np
+    from PIL import Image
+    from vllm_omni_b200.diffusion.models.longcat_image.transformer import longcat_rope_angles
+    a1 = longcat_rope_angles(2, 3, 4, (8, 12, 12), 16)
+    a2 = longcat_rope_angles(2, 3, 4, (8, 12, 12), 16, frames=2)
+    assert a2.shape[0] == 2 * 6 + 4
+    assert torch.equal(a2[:6], a1[:6]) and torch.equal(a2[12:], a1[6:])
+    assert torch.allclose(a2[6:12, 4:], a1[:6, 4:]) and not torch.allclose(a2[6:12, :4], a1[:6, :4])   # same (y, x), modality 2
+    vae = dict(SMALL_KL)
+    o = OmniDiffusion("LongCatImageEditPipeline", dtype="float32", device="cpu", tf_model_config=TINY["LongCatImageEditPipeline"],
+                      vae_config=vae)
+    try:
+        sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0, guidance_scale=3.0)
+        rng = np.random.default_rng(0)
+        imgs = [Image.fromarray(rng.integers(0, 255, (64, 64, 3), dtype=np.uint8)) for _ in range(2)]
+        outs = [np.asarray(o.generate([{"prompt": "make it red", "negative_prompt": " ",
+                                        "multi_modal_data": {"image": im}}], sp)[0].images[0], dtype=np.float32)
+                for im in imgs]
+        assert outs[0].shape == (64, 64, 3)
+        assert np.abs(outs[0] - outs[1]).max() > 0          # the condition image reaches the network
+        with pytest.raises(Exception):
+            o.generate([{"prompt": "no image"}], sp)
     finally:
         o.close()

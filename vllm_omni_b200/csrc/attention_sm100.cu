@@ -16,15 +16,16 @@
 //   warp 1        MMA issuer (one elected thread):
 //                   S_t = Q_t K_j^T      (SS form, both operands K-major in shared memory)
 //                   O_t += P_t V_j       (TS form: P_t read from TMEM, V_j MN-major in smem)
-//   warps 4-11    softmax of tile 0, warps 12-19 softmax of tile 1.  Two warps share each group
-//                 of 32 rows (TMEM lanes) and take 64 S columns each: tcgen05.ld of S, row maximum
-//                 exchanged through shared memory, exp2 in packed fp32 (a quarter of the
-//                 exponentials on an FMA-pipe polynomial), bf16 P written back with tcgen05.st
-//                 over S columns already read, then the final O / l epilogue (local stores,
-//                 peer stores for the fused Ulysses exchange, or fp32 partials for split-KV)
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t sits in columns
-// [0,32) and [64,96) of S_t.  O is rescaled lazily: only when a row maximum grows by more
-// than 2^8, so the steady state never touches O outside the MMAs.
+//   warps 4-7     softmax of tile 0, warps 8-11 softmax of tile 1.  One THREAD owns one query row
+//                 (TMEM lane): a single tcgen05.ld pass brings the row's 128 scores into
+//                 registers, the row maximum needs no exchange with other threads, exp2 runs in
+//                 packed fp32 (a quarter of the exponentials on an FMA-pipe polynomial), bf16 P is
+//                 written back with tcgen05.st over the S columns, then the final O / l epilogue
+//                 (local stores, peer stores for the fused Ulysses exchange, or fp32 partials
+//                 for split-KV)
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t (bf16, two keys per
+// column) sits in columns [0,64) of S_t.  O is rescaled lazily: only when a row maximum grows by
+// more than 2^8, so the steady state never touches O outside the MMAs.
 // The MMA stream is software-pipelined (PV_t(j) is followed at once by S_t(j+1)) so that
 // the tensor pipe works on one tile while the other tile's softmax runs.  Every wait is bounded.
 #include "host_util.h"
@@ -36,7 +37,7 @@ namespace omni {
 constexpr int ATT_D = 128;
 constexpr int ATT_BM = 128;   // rows per query tile
 constexpr int ATT_BN = 128;   // keys per KV tile
-constexpr int ATT_THREADS = 640;  // TMA, MMA, 2 idle warps, 2 x 8 softmax warps
+constexpr int ATT_THREADS = 384;  // TMA, MMA, 2 idle warps, 2 x 4 softmax warps (one row per thread)
 constexpr int ATT_TILE_BYTES = ATT_BM * ATT_D * 2;  // 32 KiB
 constexpr int ATT_HALF_BYTES = ATT_TILE_BYTES / 2;  // one 64-wide TMA box
 constexpr int ATT_SMEM = 2 * ATT_TILE_BYTES /*Q*/ + 2 * ATT_TILE_BYTES /*K*/ + 2 * ATT_TILE_BYTES /*V*/ + 1024;
@@ -143,7 +144,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
-  __shared__ float s_xmax[2][2][2][ATT_BM];  // [parity][tile][half][row]: partial row max / sum
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -174,7 +174,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(smem_u32(&v_full[i]), 1);
       mbar_init(smem_u32(&v_empty[i]), 1);
       mbar_init(smem_u32(&s_full[i]), 1);
-      mbar_init(smem_u32(&p_full[i]), 256);
+      mbar_init(smem_u32(&p_full[i]), 128);
       mbar_init(smem_u32(&o_done[i]), 1);
     }
     fence_mbar_init();
@@ -263,8 +263,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // ATT_HALF_BYTES apart
           const uint32_t addr = sV + st * ATT_TILE_BYTES + k * 2048;
           const uint64_t bd = umma_desc_sw128(addr, ATT_HALF_BYTES, 1024);
-          // P of keys [0, 64) sits in columns [0, 32) of the S block, keys [64, 128) in [64, 96)
-          mma_f16_ts(d, p + (k >> 2) * 64 + (k & 3) * 8, bd, idesc_pv, (j | k) != 0);
+          // P of keys [16k, 16k + 16) sits in columns [8k, 8k + 8) of the S block
+          mma_f16_ts(d, p + k * 8, bd, idesc_pv, (j | k) != 0);
         }
       };
       mbar_wait(smem_u32(&q_full), 0, &s_abort, status, ERR_WAIT_FULL);
@@ -299,21 +299,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------- softmax + epilogue
-    // Eight warps per query tile: warps with the same (warp % 4) own the same 32 TMEM lanes
-    // (rows); the first of the pair takes S columns [0, 64), the second [64, 128).  The pair
-    // exchanges its partial row maxima through shared memory and a 64-thread named barrier.
-    const int t = (warp - 4) >> 3;       // query tile of this warp
+    // Four warps per query tile; warp (warp % 4) owns TMEM lanes [32 (warp % 4), +32), i.e. one
+    // thread per query row, all 128 keys of the KV tile.
+    const int t = (warp - 4) >> 2;       // query tile of this warp
     const int q = warp & 3;              // TMEM lane quadrant this warp may access
-    const int hf = ((warp - 4) >> 2) & 1;  // column half
     const int row_in_tile = q * 32 + lane;
     const int srow = qblk * 2 * ATT_BM + t * ATT_BM + row_in_tile;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t tS = tmem_base + lane_addr + t * 128 + hf * 64;   // P overwrites the first 32 of these
-    const uint32_t tO = tmem_base + lane_addr + 256 + t * 128 + hf * 64;
-    const int bar_id = 1 + t * 4 + q;
+    const uint32_t tS = tmem_base + lane_addr + t * 128;           // P overwrites the first 64 of these
+    const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
     const uint64_t scale2 = pack2(scale_log2, scale_log2);
     float m = -INFINITY;  // running maximum in log2 units that P and l are relative to
-    uint64_t l2a = 0ull, l2b = 0ull;     // four partial row sums (two packed pairs) over this half
+    uint64_t l2a = 0ull, l2b = 0ull;     // four partial row sums (two packed pairs)
     // A tile that is not in use has no work at all; a warp whose 32 rows all lie past the last
     // query row (decode: a handful of real rows per tile) only keeps the barrier protocol going.
     // Its rows of S come from zero-filled Q rows, so the stale bits the P*V MMA reads as their P
@@ -328,41 +325,46 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_after_sync();
       const int row_limit = causal ? min(kv_len, srow + q_offset + 1) : kv_len;
-      const int valid = row_limit - (j0 + j) * ATT_BN - hf * 64;  // keys of this half-tile this row may see
-      const bool masked = valid < 64;
-      // pass 1: row maximum over this warp's 64 columns, four independent chains
-      float mx;
-      {
-        uint32_t va[32], vb[32];
-        tmem_ld_32x32(tS, va);
-        tmem_ld_32x32(tS + 32, vb);
+      const int valid = row_limit - (j0 + j) * ATT_BN;   // keys of this tile this row may see
+      const bool any_masked = __any_sync(0xffffffffu, valid < ATT_BN);
+      // the whole row of scores in registers: one TMEM pass
+      uint32_t v0[32], v1[32], v2[32], v3[32];
+      auto load_scores = [&]() {
+        tmem_ld_32x32(tS, v0);
+        tmem_ld_32x32(tS + 32, v1);
+        tmem_ld_32x32(tS + 64, v2);
+        tmem_ld_32x32(tS + 96, v3);
         tmem_wait_ld();
-        if (__any_sync(0xffffffffu, masked)) {
+        if (any_masked) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            if (e >= valid) va[e] = 0xff800000u;  // -inf
-            if (e + 32 >= valid) vb[e] = 0xff800000u;
+            if (e >= valid) v0[e] = 0xff800000u;  // -inf
+            if (e + 32 >= valid) v1[e] = 0xff800000u;
+            if (e + 64 >= valid) v2[e] = 0xff800000u;
+            if (e + 96 >= valid) v3[e] = 0xff800000u;
           }
         }
-        float m0 = __uint_as_float(va[0]), m1 = __uint_as_float(va[1]);
-        float m2 = __uint_as_float(vb[0]), m3 = __uint_as_float(vb[1]);
+      };
+      load_scores();
+      float mx;
+      {
+        float m0 = __uint_as_float(v0[0]), m1 = __uint_as_float(v1[0]);
+        float m2 = __uint_as_float(v2[0]), m3 = __uint_as_float(v3[0]);
 #pragma unroll
-        for (int e = 2; e < 32; e += 4) {
-          m0 = max3(m0, __uint_as_float(va[e]), __uint_as_float(va[e + 1]));
-          m2 = max3(m2, __uint_as_float(vb[e]), __uint_as_float(vb[e + 1]));
-          if (e + 2 < 32) {
-            m1 = max3(m1, __uint_as_float(va[e + 2]), __uint_as_float(va[e + 3]));
-            m3 = max3(m3, __uint_as_float(vb[e + 2]), __uint_as_float(vb[e + 3]));
-          }
+        for (int e = 1; e < 31; e += 2) {
+          m0 = max3(m0, __uint_as_float(v0[e]), __uint_as_float(v0[e + 1]));
+          m1 = max3(m1, __uint_as_float(v1[e]), __uint_as_float(v1[e + 1]));
+          m2 = max3(m2, __uint_as_float(v2[e]), __uint_as_float(v2[e + 1]));
+          m3 = max3(m3, __uint_as_float(v3[e]), __uint_as_float(v3[e + 1]));
         }
-        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        m0 = fmaxf(m0, __uint_as_float(v0[31]));
+        m1 = fmaxf(m1, __uint_as_float(v1[31]));
+        m2 = fmaxf(m2, __uint_as_float(v2[31]));
+        m3 = fmaxf(m3, __uint_as_float(v3[31]));
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * scale_log2;
       }
-      s_xmax[j & 1][t][hf][row_in_tile] = mx;
-      named_bar_sync(bar_id, 64);
-      mx = fmaxf(mx, s_xmax[j & 1][t][hf ^ 1][row_in_tile]) * scale_log2;
       const float m_new = fmaxf(m, mx);
-      // lazy rescale, decided per warp because tcgen05.ld/st are warp-wide (both warps of a pair
-      // see the same m and mx, so they decide alike)
+      // lazy rescale, decided per warp because tcgen05.ld/st are warp-wide
       const bool grow = m_new > m + 8.0f;
       if (j == 0) {
         m = m_new;
@@ -372,7 +374,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         l2a = mul2(l2a, alpha2);
         l2b = mul2(l2b, alpha2);
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(tO + c * 32, v);
           tmem_wait_ld();
@@ -382,18 +384,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tmem_wait_st();
         m = m_new;
+        load_scores();   // rare path: the scores were dropped to make room for the O chunks; read them again
       }
-      // pass 2: P = exp2(S * scale - m) as packed bf16 over the first half of this warp's S
-      // columns.  One pair in four goes through a degree-3 polynomial on the FMA pipe instead
-      // of the MUFU unit, which is otherwise as busy as the tensor pipe at head_dim 128.
+      // P = exp2(S * scale - m) as packed bf16 over the first 64 columns of the S block.  One pair
+      // in four goes through a degree-3 polynomial on the FMA pipe instead of the MUFU unit,
+      // which is otherwise as busy as the tensor pipe at head_dim 128.
       const float m_use = m == -INFINITY ? 0.f : m;
       const uint64_t negm2 = pack2(-m_use, -m_use);
       auto softmax_chunk = [&](uint32_t (&v)[32], int c) {
-        if (__any_sync(0xffffffffu, masked)) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (c * 32 + e >= valid) v[e] = 0xff800000u;
-        }
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -414,21 +412,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tmem_st_32x16(tS + c * 16, pk);
       };
-      {
-        // the second chunk's load is in flight while the first is processed
-        uint32_t va[32], vb[32];
-        tmem_ld_32x32(tS, va);
-        tmem_wait_ld();
-        tmem_ld_32x32(tS + 32, vb);
-        softmax_chunk(va, 0);
-        tmem_wait_ld(vb);
-        softmax_chunk(vb, 1);
-      }
+      softmax_chunk(v0, 0);
+      softmax_chunk(v1, 1);
+      softmax_chunk(v2, 2);
+      softmax_chunk(v3, 3);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&p_full[t]));
     }
-    // epilogue: O / l -> bf16; the row sum is the total of both halves
+    // epilogue: O / l -> bf16
     if (rows_used) {
       float l;
       {
@@ -436,9 +428,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         unpack2(l2a, a0, a1);
         unpack2(l2b, b0, b1);
         l = (a0 + a1) + (b0 + b1);
-        s_xmax[n_kv & 1][t][hf][row_in_tile] = l;
-        named_bar_sync(bar_id, 64);
-        l += s_xmax[n_kv & 1][t][hf ^ 1][row_in_tile];
       }
       if (n_kv > 0) {
         mbar_wait(smem_u32(&o_done[t]), 0, &s_abort, status, ERR_WAIT_PV);
@@ -447,12 +436,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (out.kv_splits > 1) {
         // split-KV share: unnormalised O, reference exponent and row sum for the merge kernel
         const long pidx = (((long)b * H + h) * Sq + srow) * out.kv_splits + split;
-        if (srow < Sq && hf == 0) {
+        if (srow < Sq) {
           out.part_ml[pidx * 2] = n_kv > 0 ? m : -INFINITY;
           out.part_ml[pidx * 2 + 1] = l;
         }
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
           if (n_kv > 0) {
             tmem_ld_32x32(tO + c * 32, v);
@@ -462,7 +451,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int e = 0; e < 32; ++e) v[e] = 0u;
           }
           if (srow < Sq) {
-            float4* dst = reinterpret_cast<float4*>(out.part_o + pidx * ATT_D + hf * 64 + c * 32);
+            float4* dst = reinterpret_cast<float4*>(out.part_o + pidx * ATT_D + c * 32);
 #pragma unroll
             for (int g = 0; g < 8; ++g)
               dst[g] = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
@@ -471,33 +460,71 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       } else {
         const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-        __nv_bfloat16* orow = nullptr;
-        if (srow < Sq && out.n_peers > 1) {
-          if (srow >= out.split) {
-            const int t2 = srow - out.split;
-            const int owner = t2 / out.rows_per_rank2;
-            orow = out.o2_peers[owner] + (long)b * out.o2_bs + (long)(t2 - owner * out.rows_per_rank2) * out.o2_rs + (long)h * out.o2_hs;
-          } else {
-            const int owner = srow / out.rows_per_rank;
-            orow = out.o_peers[owner] + (long)b * out.o_bs + (long)(srow - owner * out.rows_per_rank) * out.o_rs + (long)h * out.o_hs;
-          }
-        } else if (srow < Sq) {
-          if (out.o2 && srow >= out.split)
-            orow = out.o2 + (long)b * out.o2_bs + (long)(srow - out.split) * out.o2_rs + (long)h * out.o2_hs;
-          else
-            orow = out.o + (long)b * out.o_bs + (long)srow * out.o_rs + (long)h * out.o_hs;
-        }
-        if (srow < Sq && out.lse && hf == 0)
+        if (srow < Sq && out.lse)
           out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
         if (out.n_peers > 1) {
           // Fused exchange: rows go to their owner ranks over NVLink.  A store from the thread that
           // owns the row would put 32 separate 16-byte writes on the link per instruction, so the
-          // warp's 32 rows x 64 columns pass through shared memory (the Q tile of this query tile is
-          // no longer read once o_done has fired) and leave as whole 128-byte row segments: 8 lanes
-          // per row, 4 rows per store instruction.
-          const uint32_t stg = sQ + t * ATT_TILE_BYTES + (q * 2 + hf) * 4096;
+          // warp's 32 rows pass through shared memory (the Q tile of this query tile is no longer
+          // read once o_done has fired), 64 columns at a time, and leave as whole 128-byte row
+          // segments: 8 lanes per row, 4 rows per store instruction.
+          const uint32_t stg = sQ + t * ATT_TILE_BYTES + q * 4096;
+          const int k = lane & 7;
+          const int row_base = qblk * 2 * ATT_BM + t * ATT_BM + q * 32;
 #pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
+          for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+              uint32_t v[32];
+              if (n_kv > 0) {
+                tmem_ld_32x32(tO + hf * 64 + c * 32, v);
+                tmem_wait_ld();
+              } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) v[e] = 0u;
+              }
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+                o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+                o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+                o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+                const int kk = c * 4 + g;
+                st_shared_v4(stg + lane * 128 + ((kk ^ (lane & 7)) << 4), o);
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3);
+              const int sr = row_base + r;
+              if (sr < Sq) {
+                __nv_bfloat16* dst;
+                if (sr >= out.split) {
+                  const int t2 = sr - out.split;
+                  const int owner = t2 / out.rows_per_rank2;
+                  dst = out.o2_peers[owner] + (long)b * out.o2_bs + (long)(t2 - owner * out.rows_per_rank2) * out.o2_rs + (long)h * out.o2_hs;
+                } else {
+                  const int owner = sr / out.rows_per_rank;
+                  dst = out.o_peers[owner] + (long)b * out.o_bs + (long)(sr - owner * out.rows_per_rank) * out.o_rs + (long)h * out.o_hs;
+                }
+                const uint4 val = ld_shared_v4(stg + r * 128 + ((k ^ (r & 7)) << 4));
+                *reinterpret_cast<uint4*>(dst + hf * 64 + k * 8) = val;
+              }
+            }
+            __syncwarp();
+          }
+        } else {
+          __nv_bfloat16* orow = nullptr;
+          if (srow < Sq) {
+            if (out.o2 && srow >= out.split)
+              orow = out.o2 + (long)b * out.o2_bs + (long)(srow - out.split) * out.o2_rs + (long)h * out.o2_hs;
+            else
+              orow = out.o + (long)b * out.o_bs + (long)srow * out.o_rs + (long)h * out.o_hs;
+          }
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
             uint32_t v[32];
             if (n_kv > 0) {
               tmem_ld_32x32(tO + c * 32, v);
@@ -506,61 +533,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
               for (int e = 0; e < 32; ++e) v[e] = 0u;
             }
+            if (orow) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 o;
-              o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
-              o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
-              o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
-              o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
-              const int k = c * 4 + g;
-              st_shared_v4(stg + lane * 128 + ((k ^ (lane & 7)) << 4), o);
-            }
-          }
-          __syncwarp();
-          const int k = lane & 7;
-          const int row_base = qblk * 2 * ATT_BM + t * ATT_BM + q * 32;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = i * 4 + (lane >> 3);
-            const int sr = row_base + r;
-            if (sr < Sq) {
-              __nv_bfloat16* dst;
-              if (sr >= out.split) {
-                const int t2 = sr - out.split;
-                const int owner = t2 / out.rows_per_rank2;
-                dst = out.o2_peers[owner] + (long)b * out.o2_bs + (long)(t2 - owner * out.rows_per_rank2) * out.o2_rs + (long)h * out.o2_hs;
-              } else {
-                const int owner = sr / out.rows_per_rank;
-                dst = out.o_peers[owner] + (long)b * out.o_bs + (long)(sr - owner * out.rows_per_rank) * out.o_rs + (long)h * out.o_hs;
+              for (int g = 0; g < 4; ++g) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+                o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+                o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+                o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+                *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
               }
-              const uint4 val = ld_shared_v4(stg + r * 128 + ((k ^ (r & 7)) << 4));
-              *reinterpret_cast<uint4*>(dst + hf * 64 + k * 8) = val;
             }
           }
-        } else {
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          if (n_kv > 0) {
-            tmem_ld_32x32(tO + c * 32, v);
-            tmem_wait_ld();
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = 0u;
-          }
-          if (orow) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 o;
-              o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
-              o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
-              o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
-              o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + hf * 64 + c * 32 + g * 8) = o;
-            }
-          }
-        }
         }
       }
     }

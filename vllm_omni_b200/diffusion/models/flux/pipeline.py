@@ -29,6 +29,7 @@ class FluxPipeline(nn.Module):
     # guidance embedding (LongCat-Image, Ovis-Image) run true classifier-free guidance against a negative prompt:
     true_cfg = False
     cfg_renorm_clamp = False            # rescale the guided velocity per token to at most the conditional one's norm
+    needs_vae_encoder = False           # editing pipelines encode their input image
 
     def __init__(self, od_config: OmniDiffusionConfig | None = None, transformer_config=None, vae_config=None,
                  device=None, **_):
@@ -38,13 +39,19 @@ class FluxPipeline(nn.Module):
         self.device_ = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
         tcfg = transformer_config or self.config_cls.from_dict(self.od_config.tf_model_config.to_dict())
         self.transformer = self.transformer_cls(tcfg, dtype=dtype, device=self.device_)
-        self.vae = build_vae(vae_config or self.od_config.vae_config, "kl").to(device=self.device_, dtype=dtype)
+        self.vae = build_vae(vae_config or self.od_config.vae_config, "kl",
+                             with_encoder=self.needs_vae_encoder).to(device=self.device_, dtype=dtype)
         self.vae.use_tiling = self.od_config.vae_use_tiling
         self.scheduler = FlowMatchEulerDiscreteScheduler(**FLUX_SCHEDULER)
         self.text_encoder = HashTextEncoder(tcfg.joint_attention_dim, max_len=self.max_text_len)
         self.pooled_encoder = HashTextEncoder(getattr(tcfg, "pooled_projection_dim", 768), max_len=1)
         self.vae_decode = None
         self.cfg_exchange = None        # set by CFG-parallel
+
+    def condition_latents(self, req: OmniDiffusionRequest, B: int, h: int, w: int):
+        """Packed latents [B, k*S_img, 4C] of conditioning images that ride along with the noise rows
+        (editing pipelines), or None."""
+        return None
 
     def _guided(self, v, vn, scale, renorm_min=0.0):
         out = vn.float() + scale * (v.float() - vn.float())
@@ -93,10 +100,17 @@ class FluxPipeline(nn.Module):
         guidance = torch.full((B,), scale, device=self.device_)
         lat_in = lat.to(self.od_config.dtype)
         tv = torch.empty(B, device=self.device_)
+        S_img = lat.shape[1]
+        cond = self.condition_latents(req, B, h, w)
+        frames = 1 if cond is None else 1 + cond.shape[1] // S_img
         for i in range(len(ts)):
             tv.fill_(float(self.scheduler.sigmas[i]))
-            call = lambda enc, ln, branch=0: self.transformer(lat_in, enc, tv, (1, h // 2, w // 2), pooled_projections=pooled,
-                                                              guidance=guidance, txt_seq_lens=ln, branch=branch)
+
+            def call(enc, ln, branch=0):
+                x = lat_in if cond is None else torch.cat([lat_in, cond.to(lat_in.dtype)], dim=1)
+                v = self.transformer(x, enc, tv, (frames, h // 2, w // 2), pooled_projections=pooled,
+                                     guidance=guidance, txt_seq_lens=ln, branch=branch)
+                return v if cond is None else v[:, :S_img].contiguous()      # only the noise rows are stepped
             dt = self.scheduler.dt(i)
             if do_cfg and self.cfg_exchange is not None:     # one guidance branch per rank
                 mine = call(ne, nlens) if self.cfg_exchange.is_negative_rank else call(pe, lens)

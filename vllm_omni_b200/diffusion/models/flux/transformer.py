@@ -33,14 +33,16 @@ class FluxTransformerConfig(QwenImageTransformerConfig):
     out_channels: int = 16
 
 
-def flux_rope_angles(h: int, w: int, txt_len: int, axes, theta: float = 10000.0) -> torch.Tensor:
+def flux_rope_angles(h: int, w: int, txt_len: int, axes, theta: float = 10000.0, frames: int = 1) -> torch.Tensor:
     """Image token (y, x) -> ids (0, y, x); text tokens -> (0, 0, 0).  Image rows first."""
     def ang(idx, dim):
         inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
         return torch.outer(idx.float(), inv)
     ys = torch.arange(h).repeat_interleave(w)
     xs = torch.arange(w).repeat(h)
-    img = torch.cat([ang(torch.zeros(h * w), axes[0]), ang(ys, axes[1]), ang(xs, axes[2])], dim=-1)
+    # frame f (f > 0: a conditioning image appended to the image sequence) carries f on the first axis
+    img = torch.cat([torch.cat([ang(torch.full((h * w,), float(f)), axes[0]), ang(ys, axes[1]), ang(xs, axes[2])], dim=-1)
+                     for f in range(frames)], dim=0)
     txt = torch.zeros(txt_len, img.shape[1])
     return torch.cat([img, txt], dim=0)
 
@@ -72,10 +74,10 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
         self.stack_hook = None            # cache backends: called once per step with a BlockStack over double + single blocks
         self.block_hook = None            # (the Qwen-Image in-place entry is not used by this forward)
 
-    def _cos_sin(self, h, w, txt_len, device):
-        key = (h, w, txt_len, str(device))
+    def _cos_sin(self, h, w, txt_len, device, frames: int = 1):
+        key = (h, w, txt_len, str(device), frames)
         if key not in self._angles:
-            a = flux_rope_angles(h, w, txt_len, self.cfg.axes_dims_rope, self.cfg.rope_theta)
+            a = flux_rope_angles(h, w, txt_len, self.cfg.axes_dims_rope, self.cfg.rope_theta, frames=frames)
             self._angles[key] = (a.cos().contiguous().to(device), a.sin().contiguous().to(device))
         return self._angles[key]
 
@@ -133,8 +135,8 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
         dev = hidden_states.device
         while isinstance(img_shapes[0], (list, tuple)):
             img_shapes = img_shapes[0]
-        _, h, w = img_shapes
-        cos, sin = self._cos_sin(h, w, S_txt, dev)
+        frames, h, w = img_shapes         # frames > 1: conditioning images follow the noise rows (editing)
+        cos, sin = self._cos_sin(h, w, S_txt, dev, frames) if frames > 1 else self._cos_sin(h, w, S_txt, dev)
         kv_lens = None
         if txt_seq_lens is not None and any(int(l) != S_txt for l in txt_seq_lens):
             kv_lens = torch.tensor([S_img + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)

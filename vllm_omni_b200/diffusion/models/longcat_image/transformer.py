@@ -24,16 +24,19 @@ class LongCatTransformerConfig(FluxTransformerConfig):
 
 
 def longcat_rope_angles(h: int, w: int, txt_len: int, axes, offset: int, theta: float = 10000.0,
-                        image_modality: int = 1) -> torch.Tensor:
-    """Angles [h*w + txt_len, sum(axes)/2]; image rows first, then text rows.  Text token i sits at
-    (0, i, i), image patch (y, x) at (image_modality, y + offset, x + offset)."""
+                        image_modality: int = 1, frames: int = 1) -> torch.Tensor:
+    """Angles [frames*h*w + txt_len, sum(axes)/2]; image rows first, then text rows.  Text token i
+    sits at (0, i, i), image patch (y, x) of frame f at (image_modality + f, y + offset, x + offset):
+    the noise rows are modality 1, a conditioning image appended for editing is modality 2
+    (pipeline_longcat_image_edit.py:456-470)."""
     def ang(idx, dim):
         inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
         return torch.outer(idx.double(), inv).float()
     ys = torch.arange(h).repeat_interleave(w) + offset
     xs = torch.arange(w).repeat(h) + offset
     t = torch.arange(txt_len)
-    img = torch.cat([ang(torch.full((h * w,), float(image_modality)), axes[0]), ang(ys, axes[1]), ang(xs, axes[2])], dim=-1)
+    img = torch.cat([torch.cat([ang(torch.full((h * w,), float(image_modality + f)), axes[0]), ang(ys, axes[1]),
+                                ang(xs, axes[2])], dim=-1) for f in range(frames)], dim=0)
     txt = torch.cat([ang(torch.zeros(txt_len), axes[0]), ang(t, axes[1]), ang(t, axes[2])], dim=-1)
     return torch.cat([img, txt], dim=0)
 
@@ -45,10 +48,11 @@ class LongCatImageTransformer2DModel(FluxTransformer2DModel):
         super().__init__(cfg, dtype=dtype, device=device)
         self.pooled_1 = self.pooled_2 = None            # conditioned on the timestep alone
 
-    def _cos_sin(self, h, w, txt_len, device):
-        key = (h, w, txt_len, str(device))
+    def _cos_sin(self, h, w, txt_len, device, frames: int = 1):
+        key = (h, w, txt_len, str(device), frames)
         if key not in self._angles:
-            a = longcat_rope_angles(h, w, txt_len, self.cfg.axes_dims_rope, self.cfg.text_position_offset, self.cfg.rope_theta)
+            a = longcat_rope_angles(h, w, txt_len, self.cfg.axes_dims_rope, self.cfg.text_position_offset, self.cfg.rope_theta,
+                                    frames=frames)
             self._angles[key] = (a.cos().contiguous().to(device), a.sin().contiguous().to(device))
         return self._angles[key]
 

@@ -24,6 +24,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ....parallel.sp_plan import SequenceParallelInput, SequenceParallelOutput
 from ....ops import _native as _nv
 from ....ops import fused, gemm
 from ....ops.attention import attention
@@ -183,9 +184,12 @@ class QwenImageTransformer2DModel(nn.Module):
     # checkpoint name -> (fused parameter, slice index) in the style of the reference's
     # stacked_params_mapping (qwen_image_transformer.py:1073-1113)
     _repeated_blocks = ["QwenImageTransformerBlock"]
+    # layout of the sequence-parallel run (validated at load by parallel/apply.install_sp_plan): image
+    # rows are split along dim 1 of ``hidden_states`` and gathered after ``proj_out``.  The split
+    # itself happens once per image in the pipeline loop, not in a hook per forward.
     _sp_plan = {
-        "hidden_states": {"split_dim": 1, "expected_dims": 3, "auto_pad": True},
-        "proj_out": {"gather_dim": 1},
+        "": {"hidden_states": SequenceParallelInput(split_dim=1, expected_dims=3, auto_pad=True)},
+        "proj_out": SequenceParallelOutput(gather_dim=1, expected_dims=3),
     }
 
     def __init__(self, cfg: QwenImageTransformerConfig | None = None, dtype=torch.bfloat16, device=None):

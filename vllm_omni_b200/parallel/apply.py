@@ -7,9 +7,29 @@ import os
 from . import parallel_state as ps
 
 
+def install_sp_plan(tr, group) -> None:
+    """Validate a transformer's declarative ``_sp_plan`` and, for models that ask for it
+    (``sp_hooks = True``: custom pipelines and models that do not shard rows in their own forward),
+    install the split / gather hooks (vllm_omni/diffusion/hooks/sequence_parallel.py:149,412).  The
+    built-in families shard inside ``forward`` / the pipeline loop, where the split costs no extra
+    copy and the fused exchange kernels see this rank's rows directly; their plan documents the
+    layout and is checked here so that a malformed declaration fails at load, not at run time."""
+    from .sp_plan import apply_sp_plan, validate_sp_plan
+    plan = getattr(tr, "_sp_plan", None)
+    if not plan:
+        return
+    validate_sp_plan(plan)
+    if getattr(tr, "sp_hooks", False) and getattr(tr, "_sp_hook_registry", None) is None:
+        tr._sp_hook_registry = apply_sp_plan(tr, plan, group)
+
+
 def apply_parallelism(pipe, od_config) -> None:
     pc = od_config.parallel_config
     tr = getattr(pipe, "transformer", None)
+    if tr is not None and pc.ulysses_degree * pc.ring_degree > 1:
+        for t in (tr, getattr(pipe, "transformer_2", None)):
+            if t is not None:
+                install_sp_plan(t, ps.get_sp_group())
     if tr is not None and getattr(tr, "sp_style", "joint") == "attention" and pc.ulysses_degree * pc.ring_degree > 1:
         # single-stream models shard rows themselves and only need a sequence-parallel attention
         from .sp_attention import SequenceParallelAttention
