@@ -62,9 +62,35 @@ __global__ void peer_barrier_kernel(PeerPtrs peers, int rank, int world, unsigne
   __threadfence_system();
 }
 
+// Flat copy into (or out of) a peer-mapped buffer with ordinary 16-byte loads and stores: every
+// warp instruction moves 512 contiguous bytes, so the NVLink packets are full.  Used by the
+// device-to-device stage connector to push a payload into the consumer stage's arena.
+__global__ void __launch_bounds__(256)
+peer_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t n16, unsigned char* __restrict__ dst_tail,
+                 const unsigned char* __restrict__ src_tail, int tail) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = src[i];
+  if (blockIdx.x == 0 && (int)threadIdx.x < tail) dst_tail[threadIdx.x] = src_tail[threadIdx.x];
+}
+
 }  // namespace omni
 
 using namespace omni;
+
+// dst / src: device pointers (either may be a peer mapping), both 16-byte aligned.
+extern "C" int omni_peer_copy(void* dst, const void* src, size_t nbytes, void* stream) {
+  if (nbytes == 0) return RC_OK;
+  if ((reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(src) & 15)) return RC_BAD_ARG;
+  const size_t n16 = nbytes >> 4;
+  const int tail = (int)(nbytes & 15);
+  size_t blocks = (n16 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks == 0) blocks = 1;
+  peer_copy_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      static_cast<uint4*>(dst), static_cast<const uint4*>(src), n16, static_cast<unsigned char*>(dst) + (n16 << 4),
+      static_cast<const unsigned char*>(src) + (n16 << 4), tail);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int omni_peer_alloc(size_t bytes, void** out) {
   void* p = nullptr;

@@ -50,9 +50,41 @@ class ResizeMLP(nn.Module):
         return loaded
 
 
+class _PredictorState:
+    """Static buffers of the cached code-predictor loop for one row-count bucket."""
+
+    def __init__(self, n, core_cfg, talker_hidden, G, vocab, dtype, device):
+        z = lambda *s, dt=dtype: torch.zeros(*s, dtype=dt, device=device)
+        self.n = n
+        page = 32                                    # one page per row holds the whole context (<= G + 1 tokens)
+        self.page = page
+        self.caches = [(z(n, page, core_cfg.num_key_value_heads, core_cfg.head_dim),
+                        z(n, page, core_cfg.num_key_value_heads, core_cfg.head_dim))
+                       for _ in range(core_cfg.num_hidden_layers)]
+        self.tables = torch.arange(n, dtype=torch.int32, device=device)[:, None].contiguous()
+        self.rows = torch.arange(n, dtype=torch.long, device=device)
+        self.ids = torch.zeros(n, dtype=torch.long, device=device)
+        self.emask = torch.ones(n, dtype=torch.bool, device=device)
+        steps = G                                    # tokens fed: talker hidden, code 0, codes 1 .. G-2
+        self.pos = [torch.full((n,), t, dtype=torch.long, device=device) for t in range(steps)]
+        self.slots = [(torch.arange(n, dtype=torch.int32, device=device) * page + t).contiguous() for t in range(steps)]
+        self.lens = [torch.full((n,), t + 1, dtype=torch.int32, device=device) for t in range(steps)]
+        self.hidden_in, self.code0_in = z(n, talker_hidden), z(n, talker_hidden)
+        self.codes = torch.zeros(n, G - 1, dtype=torch.long, device=device)
+        self.summed = z(n, talker_hidden)
+        self.sample_rows = None                      # uint8 [(G-1) * n * row_bytes] on the device when sampling
+        self.sample_out = torch.zeros(n, dtype=torch.int32, device=device)
+        self.sample_work = torch.zeros(n, vocab, dtype=torch.float32, device=device) if device.type == "cuda" else None
+        self.graph, self.graph_mode, self.warm = None, None, 0
+
+
 class CodePredictor(nn.Module):
-    """G-1 sequential steps over a tiny context (<= G+1 tokens), no KV cache: at these sizes the
-    whole loop is launch-bound, so the step is written to be captured in a CUDA graph."""
+    """G-1 sequential steps over a tiny context (<= G+1 tokens).  Every token is fed once: its K/V
+    go to a one-page-per-row cache and attention is the paged decode kernel, and the whole loop
+    (G decoder steps, G-1 heads, samplings and embedding look-ups) is captured in ONE CUDA graph per
+    row-count bucket, because at these sizes it is launch-bound.  The reference runs it as CUDA
+    graphs of a re-prefilled HF-style module (qwen3_omni_moe_code_predictor_mtp.py:413-524).
+    ``generate_uncached`` is the straight restatement without a cache (the oracle of the tests)."""
 
     def __init__(self, cfg: CodePredictorConfig, talker_hidden: int, dtype, device):
         super().__init__()
@@ -116,10 +148,105 @@ class CodePredictor(nn.Module):
             layer.down(fused.silu_mul(layer.gate_up(xn)), residual=x, out=x)
         return fused.norm_modulate(x, weight=core.norm, rms=True, eps=cfg.rms_norm_eps).view(n, L, D)
 
+    # ------------------------------------------------------------------ cached loop
+    def _bucket(self, n: int, device) -> "_PredictorState":
+        nb = 1
+        while nb < n:
+            nb *= 2
+        st = self._states.get((nb, str(device))) if hasattr(self, "_states") else None
+        if st is None:
+            if not hasattr(self, "_states"):
+                self._states = {}
+            st = _PredictorState(nb, self.core.cfg, self.codec_embedding.shape[-1], self.cfg.num_code_groups,
+                                 self.cfg.vocab_size, self.codec_embedding.dtype, device)
+            self._states[(nb, str(device))] = st
+        return st
+
+    def _loop_body(self, st: "_PredictorState", sampling: bool):
+        """The whole frame on static buffers: reads st.hidden_in / st.code0_in (and st.sample_rows),
+        writes st.codes / st.summed."""
+        from ...ops.sampler import row_bytes, sample_packed
+        from ..qwen_decoder import ModelBatch
+        from ...ops import gemm
+        G, n = self.cfg.num_code_groups, st.n
+        st.summed.zero_()
+        x = st.hidden_in
+        for t in range(G):
+            xin = x if self.in_proj is None else self.in_proj(x)
+            b = ModelBatch(st.ids, st.pos[t], st.slots[t], [], decode_rows=st.rows, decode_block_tables=st.tables,
+                           decode_seq_lens=st.lens[t], input_embeds=xin, embeds_mask=st.emask)
+            h, _ = self.core(b, st.caches)                                    # [n, D]
+            if t == 0:
+                x = st.code0_in
+                continue
+            g = t - 1                                                          # this token predicts residual code g + 1
+            if h.is_cuda:
+                logits = gemm.linear(h, self.lm_heads[g])
+            else:
+                logits = F.linear(h.float(), self.lm_heads[g].float())
+            if not sampling:
+                c = logits.argmax(-1)
+            elif h.is_cuda:
+                rb = row_bytes() * n
+                c = sample_packed(logits, st.sample_rows[g * rb:(g + 1) * rb], st.sample_out, st.sample_work).long()
+            else:
+                c = sample(logits, st.cpu_rows[g])[0].long()
+            st.codes[:, g] = c
+            e = self.codec_embedding[g][c]
+            st.summed.add_(e)
+            x = e
+
     @torch.no_grad()
     def generate(self, talker_hidden, code0_embed, temperature=0.0, seed=0, step=0):
         """talker_hidden, code0_embed: [n, Dt].  Returns (codes [n, G-1] int64, summed embeddings
         of codes 1..G-1 [n, Dt])."""
+        import os
+        from ...ops.sampler import pack_rows
+        G, n, dev = self.cfg.num_code_groups, talker_hidden.shape[0], talker_hidden.device
+        if G > 32 or self.core.cfg.head_dim not in (64, 128) and dev.type == "cuda":
+            return self.generate_uncached(talker_hidden, code0_embed, temperature, seed, step)
+        st = self._bucket(n, dev)
+        st.hidden_in[:n].copy_(talker_hidden)
+        st.code0_in[:n].copy_(code0_embed)
+        if st.n > n:                                   # padding rows repeat row 0 (their results are dropped)
+            st.hidden_in[n:].copy_(talker_hidden[:1].expand(st.n - n, -1))
+            st.code0_in[n:].copy_(code0_embed[:1].expand(st.n - n, -1))
+        sampling = temperature > 0
+        if sampling:
+            rows = [[RowParams(temperature=temperature, top_k=50, seed=seed + 7919 * (g + 1), step=step)
+                     for _ in range(st.n)] for g in range(G - 1)]
+            if dev.type == "cuda":
+                packed = torch.cat([pack_rows(r) for r in rows]).to(dev, non_blocking=True)
+                if st.sample_rows is None:
+                    st.sample_rows = packed.clone()
+                else:
+                    st.sample_rows.copy_(packed)
+            else:
+                st.cpu_rows = rows
+        use_graph = dev.type == "cuda" and os.environ.get("OMNI_PREDICTOR_GRAPH", "1") == "1"
+        if not use_graph:
+            self._loop_body(st, sampling)
+        else:
+            if st.graph is not None and st.graph_mode != sampling:
+                st.graph, st.warm = None, 0            # greedy <-> sampling: capture again
+            if st.graph is None:
+                if st.warm < 1:
+                    st.warm += 1
+                    self._loop_body(st, sampling)      # eager once: builds workspaces, loads libraries
+                else:
+                    torch.cuda.synchronize()
+                    g_ = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g_):
+                        self._loop_body(st, sampling)
+                    st.graph, st.graph_mode = g_, sampling
+                    st.graph.replay()
+            else:
+                st.graph.replay()
+        return st.codes[:n].clone(), st.summed[:n].clone()
+
+    @torch.no_grad()
+    def generate_uncached(self, talker_hidden, code0_embed, temperature=0.0, seed=0, step=0):
+        """Re-prefills the growing sequence at every step with plain fp32 attention: the oracle."""
         G = self.cfg.num_code_groups
         n = talker_hidden.shape[0]
         seq = torch.stack([talker_hidden, code0_embed], dim=1)               # [n, 2, Dt]

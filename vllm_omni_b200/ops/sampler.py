@@ -107,6 +107,41 @@ def sample_reference(logits: torch.Tensor, rows: list[RowParams]):
 _work: dict = {}
 
 
+def pack_rows(rows: list[RowParams]) -> torch.Tensor:
+    """Row parameters as the byte tensor the kernel reads (host memory).  Rows that use penalties or
+    suppression lists are not supported here (their side tables vary in size): plain temperature /
+    top-k / top-p / min-p / seed / step rows only, which is what a captured sampling step needs."""
+    arr = (_Row * len(rows))()
+    for r, p in enumerate(rows):
+        a = arr[r]
+        if p.repetition_penalty != 1.0 or p.presence_penalty or p.frequency_penalty or p.suppressed:
+            raise ValueError("pack_rows: penalties and suppression lists need sample()")
+        a.temperature, a.top_p, a.min_p, a.top_k = p.temperature, p.top_p, p.min_p, int(p.top_k or 0)
+        a.rep_penalty, a.presence_penalty, a.frequency_penalty = 1.0, 0.0, 0.0
+        a.seed, a.step = int(p.seed) & 0xFFFFFFFFFFFFFFFF, int(p.step)
+        a.range_lo, a.range_hi = p.allowed_range if p.allowed_range is not None else (0, 0)
+    return torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
+
+
+def row_bytes() -> int:
+    return ctypes.sizeof(_Row)
+
+
+def sample_packed(logits: torch.Tensor, rows_dev: torch.Tensor, out: torch.Tensor, work: torch.Tensor,
+                  logprob: torch.Tensor | None = None) -> torch.Tensor:
+    """Sampling on rows already packed on the device (``pack_rows(...).to(device)``): no host work and
+    no allocation, so the call can be captured in a CUDA graph and the rows refreshed between replays.
+    ``work``: fp32 [B, V] scratch; ``out``: int32 [B]."""
+    B, V = logits.shape
+    assert logits.is_cuda and logits.stride(1) == 1 and rows_dev.numel() >= B * row_bytes()
+    rc = nv.lib("sampler").omni_sample(nv.ptr(logits), ctypes.c_int(1 if logits.dtype == torch.bfloat16 else 0),
+                                       ctypes.c_long(logits.stride(0)), ctypes.c_int(V), ctypes.c_int(B), nv.ptr(rows_dev),
+                                       nv.ptr(None), nv.ptr(None), nv.ptr(work), nv.ptr(None), nv.ptr(out),
+                                       nv.ptr(logprob), nv.stream_ptr())
+    nv.check_rc(rc, "omni_sample")
+    return out
+
+
 def sample(logits: torch.Tensor, rows: list[RowParams]):
     """logits [B, V] (fp32 or bf16).  Returns (ids int32 [B] on the logits' device, logprobs)."""
     if not logits.is_cuda:
