@@ -321,3 +321,47 @@ def test_gemm_two_problems_one_launch(dev):
     _status_ok(dev)
     refj = torch.cat([gemm.linear_reference(x1, w1, b1).float(), gemm.linear_reference(x2, w2, b2).float()], 1)
     assert (joint.float() - refj).abs().max().item() <= 0.02 * refj.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("S1,S2,N,K", [(1024, 64, 3072, 512), (1024, 64, 1536, 256), (300, 40, 9216, 128), (64, 8, 3080, 64)])
+def test_gemm_two_small_problems_share_a_one_cta_launch(dev, S1, S2, N, K):
+    """Row counts of a sequence-parallel rank: too few 256-row tiles for a wave, so the launcher takes
+    128-row tiles and runs the text rows' tiles beside the image rows' (epilogue variants and the
+    joint-buffer output included); forcing the CTA-pair kernel gives the same numbers."""
+    from vllm_omni_b200.ops import gemm
+    torch.manual_seed(S1 + N)
+    B = 1
+    mk = lambda *s: torch.randn(*s, device=dev, dtype=torch.bfloat16)
+    x1, x2 = mk(B, S1, K), mk(B, S2, K)
+    w1, w2 = mk(N, K) * 0.05, mk(N, K) * 0.05
+    b1, b2 = mk(N), mk(N)
+    r1, r2 = mk(B, S1, N), mk(B, S2, N)
+    g1, g2 = mk(B, N), mk(B, N)
+    ref1 = gemm.linear_reference(x1, w1, b1, "gelu_tanh", r1, g1).float()
+    ref2 = gemm.linear_reference(x2, w2, b2, None, r2, g2).float()
+    for force in (False, True):
+        o1, o2 = torch.empty_like(r1), torch.empty_like(r2)
+        gemm.linear_pair(dict(x=x1, w=w1, bias=b1, act="gelu_tanh", residual=r1, gate=g1, out=o1),
+                         dict(x=x2, w=w2, bias=b2, residual=r2, gate=g2, out=o2), force_pair=force)
+        _status_ok(dev)
+        assert (o1.float() - ref1).abs().max().item() <= 0.02 * ref1.abs().max().item() + 1e-2
+        assert (o2.float() - ref2).abs().max().item() <= 0.02 * ref2.abs().max().item() + 1e-2
+    joint = torch.zeros(B, S1 + S2, N, device=dev, dtype=torch.bfloat16)
+    gemm.linear_pair(dict(x=x1, w=w1, bias=b1, out=joint[:, :S1], out_rows_per_batch=S1, out_batch_stride=(S1 + S2) * N),
+                     dict(x=x2, w=w2, bias=b2, out=joint[:, S1:], out_rows_per_batch=S2, out_batch_stride=(S1 + S2) * N))
+    _status_ok(dev)
+    refj = torch.cat([gemm.linear_reference(x1, w1, b1).float(), gemm.linear_reference(x2, w2, b2).float()], 1)
+    assert (joint.float() - refj).abs().max().item() <= 0.02 * refj.abs().max().item() + 1e-2
+    # the scatter epilogue through local "peer" pointers: two column groups into two buffers
+    if N % 128 == 0:
+        G = N // 2
+        bufs = [torch.zeros(B, S1 + S2, G, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+        es = 2
+        sc1 = (2, G, [b_.data_ptr() for b_ in bufs], G)
+        sc2 = (2, G, [b_.data_ptr() + S1 * G * es for b_ in bufs], G)
+        gemm.linear_pair(dict(x=x1, w=w1, bias=b1, scatter=sc1, out_rows_per_batch=S1, out_batch_stride=(S1 + S2) * G),
+                         dict(x=x2, w=w2, bias=b2, scatter=sc2, out_rows_per_batch=S2, out_batch_stride=(S1 + S2) * G))
+        _status_ok(dev)
+        for r in range(2):
+            want = refj[:, :, r * G:(r + 1) * G]
+            assert (bufs[r].float() - want).abs().max().item() <= 0.02 * want.abs().max().item() + 1e-2

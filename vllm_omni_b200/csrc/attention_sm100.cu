@@ -28,6 +28,8 @@
 // more than 2^8, so the steady state never touches O outside the MMAs.
 // The MMA stream is software-pipelined (PV_t(j) is followed at once by S_t(j+1)) so that
 // the tensor pipe works on one tile while the other tile's softmax runs.  Every wait is bounded.
+#include <stdlib.h>
+
 #include "host_util.h"
 #include "ptx_sm100.cuh"
 #include "peer_signal.cuh"
@@ -134,6 +136,13 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// NH = how many times per KV tile the softmax warps hand P over to the MMA warp (4: every 32 keys,
+// 2: every 64 keys, 1: once): earlier hand-offs let P*V start while the later exponentials of the
+// tile are still being computed, at the price of one tcgen05.wait::st per hand-off.  Measured on
+// B2 S4352 H24 (one box, medians): 4 hand-offs 0.396 ms, 1 hand-off 0.409 ms; packed-bf16 MUFU
+// exponentials and polynomial shares of 0, 1/8, 3/8 and 1/2 were within 1 % of, or slower than,
+// fp32 MUFU with a quarter of the pairs on the FMA-pipe polynomial.
+template <int NH>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnOut out, int Sq, int Skv, int H, int Hkv,
@@ -141,7 +150,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 PeerSignal sig, int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
-  __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
+  __shared__ __align__(8) uint64_t s_full[2], p_full[2][4], o_done[2];   // p_full: per 32-key chunk of P
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
 
@@ -174,7 +183,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(smem_u32(&v_full[i]), 1);
       mbar_init(smem_u32(&v_empty[i]), 1);
       mbar_init(smem_u32(&s_full[i]), 1);
-      mbar_init(smem_u32(&p_full[i]), 128);
+      for (int c = 0; c < 4; ++c) mbar_init(smem_u32(&p_full[i][c]), 4);   // one arrival per softmax warp
       mbar_init(smem_u32(&o_done[i]), 1);
     }
     fence_mbar_init();
@@ -244,27 +253,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (elect_one() && n_kv > 0) {
       constexpr uint32_t idesc_qk = umma_idesc(ATT_BM, ATT_BN, 1, 1, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc(ATT_BM, ATT_D, 1, 1, 0, 1);  // V is MN-major
+      // The issuing thread is a serial resource: the shared-memory descriptors are built ONCE; a
+      // tile, a ring stage or a K step is a constant added to the 14-bit address field (16-byte units).
+      constexpr uint64_t TILE16 = ATT_TILE_BYTES >> 4, HALF16 = ATT_HALF_BYTES >> 4;
+      const uint64_t dQ = umma_desc_kmajor_sw128(sQ);
+      const uint64_t dK = umma_desc_kmajor_sw128(sK);
+      const uint64_t dV = umma_desc_sw128(sV, ATT_HALF_BYTES, 1024);
       auto issue_s = [&](int t, int st) {
         const uint32_t d = tmem_base + t * 128;
+        const uint64_t a0 = dQ + (uint64_t)t * TILE16, b0 = dK + (uint64_t)st * TILE16;
 #pragma unroll
         for (int k = 0; k < ATT_D / 16; ++k) {
-          const uint32_t off = (k >> 2) * ATT_HALF_BYTES + (k & 3) * 32;
-          const uint64_t a = umma_desc_kmajor_sw128(sQ + t * ATT_TILE_BYTES + off);
-          const uint64_t bd = umma_desc_kmajor_sw128(sK + st * ATT_TILE_BYTES + off);
-          mma_f16_ss(d, a, bd, idesc_qk, k != 0);
+          const uint64_t off = (uint64_t)((k >> 2) * HALF16 + (k & 3) * 2);   // 16 bf16 = 32 bytes along K
+          mma_f16_ss(d, a0 + off, b0 + off, idesc_qk, k == 0 ? 0u : 1u);
         }
       };
-      auto issue_pv = [&](int t, int st, int j) {
+      // P*V for the 32 keys of chunk c (two K=16 steps); the chunks of one KV tile are issued as the
+      // softmax warps hand them over, so the tensor pipe starts on P*V while later exponentials
+      // of the same tile are still being computed
+      auto issue_pv_chunk = [&](int t, uint64_t v0, uint32_t first, int c) {
         const uint32_t d = tmem_base + 256 + t * 128;
         const uint32_t p = tmem_base + t * 128;
 #pragma unroll
-        for (int k = 0; k < ATT_BN / 16; ++k) {
-          // 16 keys = two 8-row groups of 1024 B; the two 64-wide halves of D are
-          // ATT_HALF_BYTES apart
-          const uint32_t addr = sV + st * ATT_TILE_BYTES + k * 2048;
-          const uint64_t bd = umma_desc_sw128(addr, ATT_HALF_BYTES, 1024);
-          // P of keys [16k, 16k + 16) sits in columns [8k, 8k + 8) of the S block
-          mma_f16_ts(d, p + k * 8, bd, idesc_pv, (j | k) != 0);
+        for (int kk = 0; kk < 2; ++kk) {
+          const int k = 2 * c + kk;
+          // 16 keys = two 8-row groups of 1024 B (2048 B per K step); the two 64-wide halves of D are
+          // ATT_HALF_BYTES apart (the descriptor's leading-dimension offset).  P of keys
+          // [16k, 16k + 16) sits in columns [8k, 8k + 8) of the S block.
+          mma_f16_ts(d, p + k * 8, v0 + (uint64_t)(k * 128), idesc_pv, k == 0 ? first : 1u);
         }
       };
       mbar_wait(smem_u32(&q_full), 0, &s_abort, status, ERR_WAIT_FULL);
@@ -282,10 +298,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int st1 = (j + 1) & 1;
         mbar_wait(smem_u32(&v_full[st]), ph, &s_abort, status, ERR_WAIT_FULL);
         if (more) mbar_wait(smem_u32(&k_full[st1]), ((j + 1) >> 1) & 1, &s_abort, status, ERR_WAIT_FULL);
+        const uint64_t v0 = dV + (uint64_t)st * TILE16;
+        const uint32_t first = j != 0 ? 1u : 0u;      // the first P*V of a tile overwrites O
         for (int t = 0; t < n_qt; ++t) {
-          mbar_wait(smem_u32(&p_full[t]), j & 1, &s_abort, status, ERR_WAIT_SOFTMAX);
-          tc_fence_after_sync();
-          issue_pv(t, st, j);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            mbar_wait(smem_u32(&p_full[t][c]), j & 1, &s_abort, status, ERR_WAIT_SOFTMAX);
+            tc_fence_after_sync();
+            issue_pv_chunk(t, v0, first, c);
+          }
           if (more) {
             issue_s(t, st1);
             tc_commit(smem_u32(&s_full[t]));
@@ -320,7 +341,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int j = 0; tile_used && j < n_kv; ++j) {
       mbar_wait(smem_u32(&s_full[t]), j & 1, &s_abort, status, ERR_WAIT_FULL);
       if (!rows_used) {
-        mbar_arrive(smem_u32(&p_full[t]));
+        if (lane == 0)
+          for (int c = 0; c < 4; ++c) mbar_arrive(smem_u32(&p_full[t][c]));
         continue;
       }
       tc_fence_after_sync();
@@ -411,14 +433,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           pk[e >> 1] = pack_bf16(p0, p1);
         }
         tmem_st_32x16(tS + c * 16, pk);
+        if (((c + 1) * NH) % 4 == 0) {
+          // hand the keys finished so far to the MMA warp: every lane's stores are complete, then
+          // ONE lane arrives for the warp (128 separate arrivals would serialise on the barrier)
+          tmem_wait_st();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0)
+            for (int cc = c + 1 - 4 / NH; cc <= c; ++cc) mbar_arrive(smem_u32(&p_full[t][cc]));
+        }
       };
       softmax_chunk(v0, 0);
       softmax_chunk(v1, 1);
       softmax_chunk(v2, 2);
       softmax_chunk(v3, 3);
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&p_full[t]));
     }
     // epilogue: O / l -> bf16
     if (rows_used) {
@@ -603,11 +631,18 @@ static int make_qkv_tmap(CUtensorMap* tm, const void* p, int S, int Hn, int B, l
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnOut& out, int B, int H,
                        int Hkv, int Sq, int Skv, const int* kv_lens, float scale, int causal, int q_offset,
                        const AttnPaging& pg, int* status, cudaStream_t stream, const OmniSync* sync = nullptr) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+  // OMNI_ATTN_HANDOFFS (4 | 2 | 1): tuning switch, see attn_fwd_kernel
+  static int nh = -1;
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, AttnOut, int, int, int, int, const int*,
+                           float, int, int, AttnPaging, PeerSignal, int*);
+  static KernelFn fn = nullptr;
+  if (nh < 0) {
+    const char* ev = getenv("OMNI_ATTN_HANDOFFS");
+    int want = ev ? atoi(ev) : 4;
+    fn = want == 1 ? attn_fwd_kernel<1> : (want == 2 ? attn_fwd_kernel<2> : attn_fwd_kernel<4>);
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    nh = want;
   }
   const int splits = out.kv_splits > 1 ? out.kv_splits : 1;
   dim3 grid(((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM)) * splits, H, B);
@@ -615,8 +650,8 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   PeerSignal sig;
   PeerWait unused;
   unpack_sync(sync, sig, unused);
-  attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens, scale_log2,
-                                                           causal, q_offset, pg, sig, status);
+  fn<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens, scale_log2, causal, q_offset, pg,
+                                              sig, status);
   return (int)cudaGetLastError();
 }
 

@@ -638,13 +638,197 @@ gemm_bf16_pair_kernel(const __grid_constant__ PairArgs args, int* status) {
   if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
+
+// ------------------------------------------------------------------------------------------
+// One-CTA tiles (128 x BN) over the tile list of up to TWO problems that share N and K: the same
+// scheduling idea as the CTA-pair kernel for problems too small to fill a wave of 256-row tiles
+// (a sequence-parallel rank's rows, a text stream of a few dozen rows).  With 128-row tiles and
+// 148 schedulable units instead of 74 the launcher can usually find a tile width whose tile count
+// fits whole waves, and the short problem's tiles run beside the long one's instead of in a launch
+// of their own that would last a full K loop for a handful of tiles.
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_multi_kernel(const __grid_constant__ PairArgs args, int* status) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  const int N = args.N, K = args.K;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  const int num_n = (N + BN - 1) / BN;
+  const int num_m0 = (args.p[0].M + BM - 1) / BM;
+  const int num_m1 = args.n_problems > 1 ? (args.p[1].M + BM - 1) / BM : 0;
+  const int tiles0 = num_m0 * num_n;
+  const int num_tiles = tiles0 + num_m1 * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+  auto locate = [&](int t, int& prob, int& mb, int& nb) {
+    prob = t >= tiles0 ? 1 : 0;
+    tile_coords(prob ? t - tiles0 : t, prob ? num_m1 : num_m0, num_n, mb, nb);
+  };
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 1);
+      mbar_init(smem_u32(&empty_bar[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tempty_bar[i]), 8);
+    }
+    fence_mbar_init();
+    for (int i = 0; i < args.n_problems; ++i) {
+      tma_prefetch_desc(&args.p[i].tmA);
+      tma_prefetch_desc(&args.p[i].tmB);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      peer_wait_arrivals(args.wt, &s_abort, status);   // A may hold rows that peers write (fused exchange)
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int prob, mb, nb;
+        locate(t, prob, mb, nb);
+        const CUtensorMap* tmA = &args.p[prob].tmA;
+        const CUtensorMap* tmB = &args.p[prob].tmB;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+          tma_load_2d(sa, tmA, fb, kb * BK, mb * BM);
+          tma_load_2d(sa + Cfg::A_BYTES, tmB, fb, kb * BK, nb * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, &s_abort, status, ERR_WAIT_TMEM_EMPTY);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(smem_u32(&full_bar[stage]), phase, &s_abort, status, ERR_WAIT_FULL);
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint64_t a_desc = umma_desc_kmajor_sw128(sa);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) mma_f16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          tc_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        tc_commit(smem_u32(&tfull_bar[acc]));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int CH_PER_WARP = BN / 64;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int prob, mb, nb;
+      locate(t, prob, mb, nb);
+      const GemmEpilogue& epi = args.p[prob].epi;
+      __nv_bfloat16* C = args.p[prob].C;
+      const int ldc = args.p[prob].ldc;
+      const int M = args.p[prob].M;
+      mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, &s_abort, status, ERR_WAIT_TMEM_FULL);
+      tc_fence_after_sync();
+      const int row = mb * BM + q * 32 + lane;
+      const bool row_ok = row < M;
+      const __nv_bfloat16* gate_row = nullptr;
+      if (epi.gate && row_ok) gate_row = epi.gate + (size_t)(row / epi.rows_per_batch) * epi.gate_stride;
+      if (epi.scatter_P > 1 || epi.scatter_rows > 0) {
+        const uint32_t stg = smem_base + STAGES * Cfg::STAGE_BYTES + (warp - 2) * EPI_STAGE_BYTES;
+#pragma unroll 1
+        for (int c = half * CH_PER_WARP; c < (half + 1) * CH_PER_WARP; c += 2) {
+          const int col0 = nb * BN + c * 32;
+          if (col0 >= N) break;
+          const int nsub = min(2, (half + 1) * CH_PER_WARP - c);
+          uint4 o[8];
+          for (int sidx = 0; sidx < nsub; ++sidx) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * Cfg::ACC_STRIDE + (c + sidx) * 32, v);
+            tmem_wait_ld();
+            if (row_ok) epilogue_math32(v, row, col0 + sidx * 32, N, epi, gate_row, o + sidx * 4);
+          }
+          epilogue_store_staged(stg, o, nsub * 4, lane, mb * BM + q * 32, M, col0, N, C, ldc, epi);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = half * CH_PER_WARP; c < (half + 1) * CH_PER_WARP; ++c) {
+          const int col0 = nb * BN + c * 32;
+          if (col0 >= N) break;
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * Cfg::ACC_STRIDE + c * 32, v);
+          tmem_wait_ld();
+          if (row_ok) epilogue_store32(v, row, col0, N, C, ldc, epi, gate_row);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    peer_signal_cta_done(args.sig, gridDim.x);
+    peer_wait_cta_exit(args.wt, gridDim.x);
+  }
+  if (s_abort) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
 static int g_pair_mode = 1;   // 0: never unless forced, 1: automatic for large problems
 
+// w_box_rows: rows of W one TMA box brings (half a tile for the CTA-pair kernel, a whole tile for the
+// one-CTA kernel)
 static int fill_pair_problem(PairProblem& pp, const void* A, int lda, const void* W, int ldw, __nv_bfloat16* C,
-                             int ldc, int M, int N, int K, const GemmEpilogue& epi, int tn) {
+                             int ldc, int M, int N, int K, const GemmEpilogue& epi, int w_box_rows) {
   int rc = make_tmap_2d(&pp.tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, BK);
   if (rc) return rc;
-  rc = make_tmap_2d(&pp.tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, tn / 2, BK);
+  rc = make_tmap_2d(&pp.tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, w_box_rows, BK);
   if (rc) return rc;
   pp.C = C; pp.ldc = ldc; pp.M = M; pp.epi = epi;
   return RC_OK;
@@ -743,6 +927,58 @@ static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, 
   return (int)cudaGetLastError();
 }
 
+
+template <int BN>
+static int launch_gemm_multi(const PairArgs& args, int* status, int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_multi_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int num_n = (args.N + BN - 1) / BN;
+  int num_tiles = 0;
+  for (int i = 0; i < args.n_problems; ++i) num_tiles += ((args.p[i].M + BM - 1) / BM) * num_n;
+  const int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
+  gemm_bf16_multi_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(args, status);
+  return (int)cudaGetLastError();
+}
+
+static int launch_multi_bn(int bn, const PairArgs& args, int* status, int ctas, cudaStream_t s) {
+  switch (bn) {
+    case 256: return launch_gemm_multi<256>(args, status, ctas, s);
+    case 192: return launch_gemm_multi<192>(args, status, ctas, s);
+    default: return launch_gemm_multi<128>(args, status, ctas, s);
+  }
+}
+
+// Which kernel and tile width finish a list of (one or two) problems soonest.  A wave of tiles costs
+// time in proportion to the tile width (K and the 128 rows per SM are the same for every choice);
+// the CTA-pair kernel runs 74 tiles of 256 rows per wave and streams about 14 % faster per SM, the
+// one-CTA kernel 148 tiles of 128 rows; narrow tiles re-read A more often.
+struct TilePlan { bool pair; int bn; };
+static TilePlan plan_tiles(const int* Ms, int n_problems, int N, int ctas, int pairs, bool allow_pair) {
+  const int cand[3] = {256, 192, 128};
+  TilePlan best = {false, 256};
+  double best_cost = -1.0;
+  for (int kind = 0; kind < 2; ++kind) {
+    if (kind == 1 && (!allow_pair || pairs <= 0)) continue;
+    for (int i = 0; i < 3; ++i) {
+      const int bn = cand[i];
+      const int rows = kind ? 2 * BM : BM;
+      long tiles = 0;
+      for (int p = 0; p < n_problems; ++p) tiles += (long)((Ms[p] + rows - 1) / rows) * ((N + bn - 1) / bn);
+      const int units = kind ? pairs : ctas;
+      const long waves = (tiles + units - 1) / units;
+      const double width_penalty = bn == 128 ? 1.08 : (bn == 192 ? 1.03 : 1.0);
+      const double cost = (double)waves * bn * width_penalty * (kind ? 0.88 : 1.0);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best.pair = kind == 1; best.bn = bn; }
+    }
+  }
+  return best;
+}
+
 static int pick_bn(int M, int N, int ctas) {
   // minimise waves x tile width (time per tile is proportional to BN); wide tiles win ties
   const int cand[3] = {256, 192, 128};
@@ -818,18 +1054,20 @@ extern "C" int omni_gemm_bf16_sync(const void* A, int lda, const void* W, int ld
   // force_bn = 576 / 448 / 384 selects the CTA-pair kernel with a 256 / 192 / 128 wide tile on two
   // SMs, 512 the pair kernel with the launcher's choice of width; in automatic mode the pair kernel takes every
   // problem with at least one full wave of 256 x 256 tiles
-  const long pair_tiles = (long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-  if (force_bn >= 384 || (force_bn == 0 && g_pair_mode == 1 && pair_tiles >= ctas / 2)) {
+  TilePlan plan = {false, 0};
+  if (force_bn == 0) plan = plan_tiles(&M, 1, N, ctas, g_pair_mode == 1 ? max_resident_pairs() : 0, g_pair_mode == 1);
+  if (force_bn >= 384 || (force_bn == 0 && plan.pair)) {
     const int pairs = max_resident_pairs();
-    const int tn = force_bn == 576 ? 256 : (force_bn == 448 ? 192 : (force_bn == 384 ? 128 : pick_pair_tn(M, N, pairs)));
+    const int tn = force_bn == 576 ? 256 : (force_bn == 448 ? 192 : (force_bn == 384 ? 128 :
+                   (force_bn == 512 ? pick_pair_tn(M, N, pairs) : plan.bn)));
     PairArgs args = {};
     args.n_problems = 1; args.N = N; args.K = K;
     unpack_sync(sync, args.sig, args.wt);
-    rc = fill_pair_problem(args.p[0], A, lda, W, ldw, c, ldc, M, N, K, epi, tn);
+    rc = fill_pair_problem(args.p[0], A, lda, W, ldw, c, ldc, M, N, K, epi, tn / 2);
     if (rc) return rc;
     return launch_pair_tn(tn, args, status, pairs, s);
   }
-  const int bn = force_bn ? force_bn : pick_bn(M, N, ctas);
+  const int bn = force_bn ? force_bn : plan.bn;
   switch (bn) {
     case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s, 1, nullptr, nullptr, sync);
     case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, ldw, epi, status, ctas, s, 1, nullptr, nullptr, sync);
@@ -884,43 +1122,28 @@ static int desc_epilogue(const OmniGemmDesc& d, omni::GemmEpilogue& epi) {
   return omni::RC_OK;
 }
 
-// With `sync`: the wait goes to the first launch and the arrivals are reported by the last one, so
-// the group sees exactly one report per call whichever path (one paired launch, or two) is taken.
+// One launch for both problems: the CTA-pair kernel (256-row tiles) or the one-CTA kernel (128-row
+// tiles), whichever tile plan finishes sooner.  With `sync` the launch waits and reports once.
 extern "C" int omni_gemm_bf16_dual_sync(const OmniGemmDesc* d0, const OmniGemmDesc* d1, int N, int K, int force_pair,
                                         const omni::OmniSync* sync, int* status, void* stream) {
   using namespace omni;
   if (!d0 || !d1 || N <= 0 || K <= 0 || (N & 7) || (K & 7)) return RC_BAD_ARG;
   const OmniGemmDesc* ds[2] = {d0, d1};
   const int ctas = sm_count();
-  long tiles = 0;
-  for (int i = 0; i < 2; ++i) tiles += (long)((ds[i]->M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-  if (d0->M <= 0 || d1->M <= 0 || (!force_pair && (g_pair_mode != 1 || tiles < ctas / 2))) {
-    const int first = d0->M > 0 ? 0 : 1, last = d1->M > 0 ? 1 : 0;
-    for (int i = 0; i < 2; ++i) {
-      const OmniGemmDesc& d = *ds[i];
-      if (d.M <= 0) continue;
-      if (d.scatter_P > 1 && (N % d.scatter_G)) return RC_BAD_ARG;
-      OmniSync part = {};
-      if (sync) {
-        if (i == first) {
-          part.wait_counter = sync->wait_counter; part.wait_epoch = sync->wait_epoch;
-          part.wait_per_use = sync->wait_per_use; part.wait_timeout_ns = sync->wait_timeout_ns;
-        }
-        if (i == last) {
-          part.signal_n = sync->signal_n; part.signal_done = sync->signal_done;
-          for (int j = 0; j < SIGNAL_MAX_PEERS; ++j) part.signal_counters[j] = sync->signal_counters[j];
-        }
-      }
-      int rc = omni_gemm_bf16_sync(d.A, d.lda, d.W, d.ldw, d.C, d.ldc, d.M, N, K, d.bias, d.residual, d.ldr, d.gate,
-                                   d.gate_stride, d.rows_per_batch, d.act, d.c_rows_per_batch, d.c_batch_stride,
-                                   d.scatter_P > 1 ? d.scatter_P : 0, d.scatter_P > 1 ? d.scatter_G : 0, 0,
-                                   d.scatter_P > 1 ? d.peer_out : nullptr, 0, sync ? &part : nullptr, status, stream);
-      if (rc) return rc;
-    }
-    return RC_OK;
+  if (d0->M <= 0 || d1->M <= 0) {
+    // one of the two is empty: a plain launch of the other carries the whole synchronisation
+    const OmniGemmDesc& d = d0->M > 0 ? *d0 : *d1;
+    if (d.M <= 0) return sync ? RC_BAD_ARG : RC_OK;
+    if (d.scatter_P > 1 && (N % d.scatter_G)) return RC_BAD_ARG;
+    return omni_gemm_bf16_sync(d.A, d.lda, d.W, d.ldw, d.C, d.ldc, d.M, N, K, d.bias, d.residual, d.ldr, d.gate,
+                               d.gate_stride, d.rows_per_batch, d.act, d.c_rows_per_batch, d.c_batch_stride,
+                               d.scatter_P > 1 ? d.scatter_P : 0, d.scatter_P > 1 ? d.scatter_G : 0, 0,
+                               d.scatter_P > 1 ? d.peer_out : nullptr, 0, sync, status, stream);
   }
   const int pairs = max_resident_pairs();
-  const int tn = pick_pair_tn(d0->M + d1->M, N, pairs);
+  const int Ms[2] = {d0->M, d1->M};
+  TilePlan plan = plan_tiles(Ms, 2, N, ctas, pairs, g_pair_mode == 1 || force_pair);
+  if (force_pair) { plan.pair = true; plan.bn = pick_pair_tn(d0->M + d1->M, N, pairs); }
   PairArgs args = {};
   args.n_problems = 2; args.N = N; args.K = K;
   unpack_sync(sync, args.sig, args.wt);
@@ -930,10 +1153,11 @@ extern "C" int omni_gemm_bf16_dual_sync(const OmniGemmDesc* d0, const OmniGemmDe
     if (rc) return rc;
     if (epi.scatter_P > 1 && (N % epi.scatter_G)) return RC_BAD_ARG;
     rc = fill_pair_problem(args.p[i], ds[i]->A, ds[i]->lda, ds[i]->W, ds[i]->ldw, static_cast<__nv_bfloat16*>(ds[i]->C),
-                           ds[i]->ldc, ds[i]->M, N, K, epi, tn);
+                           ds[i]->ldc, ds[i]->M, N, K, epi, plan.pair ? plan.bn / 2 : plan.bn);
     if (rc) return rc;
   }
-  return launch_pair_tn(tn, args, status, pairs, static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return plan.pair ? launch_pair_tn(plan.bn, args, status, pairs, st) : launch_multi_bn(plan.bn, args, status, ctas, st);
 }
 
 extern "C" int omni_gemm_bf16_dual(const OmniGemmDesc* d0, const OmniGemmDesc* d1, int N, int K, int force_pair,
