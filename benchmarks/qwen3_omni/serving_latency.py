@@ -6,6 +6,11 @@ token, time to first audio packet and the audio real-time factor — the second 
     # full-size architecture with random weights, all three stages on GPU 0
     python benchmarks/qwen3_omni/serving_latency.py --device cuda --num-prompts 128 --max-concurrency 64 \
         --request-rate 8 --input-len 256 --max-tokens 128
+    # the published configuration: 1024 text tokens + 30 s of audio features per request, 512 output tokens,
+    # 64 concurrent requests with Poisson arrivals; thinker on 4 GPUs (tensor / expert parallel)
+    python benchmarks/qwen3_omni/serving_latency.py --device cuda --num-prompts 128 --max-concurrency 64 \
+        --request-rate 8 --input-len 1024 --audio-seconds 30 --max-tokens 512 --codec-frames 512 \
+        --thinker-tp 4 --thinker-ep
     # CPU smoke run with the tiny geometry
     python benchmarks/qwen3_omni/serving_latency.py --tiny --num-prompts 6 --max-concurrency 3
 
@@ -27,10 +32,11 @@ async_chunk: ASYNC_CHUNK
 stage_args:
   - stage_id: 0
     stage_type: llm
-    runtime: {devices: "0", max_batch_size: MAXB}
+    runtime: {devices: "THINKER_DEVS", max_batch_size: MAXB, process: THINKER_PROC}
     engine_args: {model_stage: thinker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
                   engine_output_type: latent, device: DEVICE, max_num_batched_tokens: 8192, gpu_memory_utilization: 0.55,
-                  load_format: dummy, model_overrides: OVERRIDES}
+                  load_format: dummy, model_overrides: OVERRIDES, tensor_parallel_size: THINKER_TP,
+                  enable_expert_parallel: THINKER_EP}
     final_output: true
     final_output_type: text
     default_sampling_params: {temperature: 0.0, max_tokens: MAXTOK, ignore_eos: true, detokenize: false}
@@ -61,12 +67,47 @@ def _pct(xs, q):
     return xs[min(len(xs) - 1, int(round(q / 100 * (len(xs) - 1))))] if xs else None
 
 
+def _stage_split(summary: dict) -> dict:
+    """Per-stage totals from the orchestrator's aggregator: generation time, tokens in / out, and the
+    bytes and time of the hand-offs into the stage."""
+    out: dict = {}
+    if not isinstance(summary, dict):
+        return out
+    for ev in summary.get("stages", []):
+        d = out.setdefault(str(ev.get("stage_id")), {"gen_time_ms": 0.0, "tokens_in": 0, "tokens_out": 0, "requests": 0})
+        d["gen_time_ms"] += float(ev.get("stage_gen_time_ms") or 0.0)
+        d["tokens_in"] += int(ev.get("num_tokens_in") or 0)
+        d["tokens_out"] += int(ev.get("num_tokens_out") or 0)
+        d["requests"] += 1
+    for tr in summary.get("transfers", []):
+        to = str(tr.get("edge", "->").split("->")[-1])
+        d = out.setdefault(to, {})
+        d["rx_kbytes"] = d.get("rx_kbytes", 0.0) + float(tr.get("size_kbytes") or 0.0)
+        d["rx_time_ms"] = d.get("rx_time_ms", 0.0) + float(tr.get("tx_time_ms") or 0.0) + float(tr.get("rx_decode_time_ms") or 0.0)
+        d["device_direct"] = bool(tr.get("device_direct"))
+    for d in out.values():
+        for k in ("gen_time_ms", "rx_kbytes", "rx_time_ms"):
+            if k in d:
+                d[k] = round(d[k], 2)
+    return out
+
+
 async def _run(a, path):
     from vllm_omni_b200.entrypoints.async_omni import AsyncOmni
     eng = AsyncOmni("qwen3-omni-bench", stage_configs_path=path)
     rng = random.Random(a.seed)
     vocab = 400 if a.tiny else 150000
     prompts = [{"prompt_token_ids": [rng.randrange(10, vocab) for _ in range(a.input_len)]} for _ in range(a.num_prompts)]
+    if a.audio_seconds > 0:
+        # 100 mel frames per second of audio, N(0,1) features; one placeholder token marks where they go
+        import torch
+        from vllm_omni_b200.models.qwen3_omni.config import Qwen3OmniConfig
+        cfg = Qwen3OmniConfig.tiny() if a.tiny else Qwen3OmniConfig()
+        n_mels = cfg.audio.num_mel_bins
+        g = torch.Generator().manual_seed(a.seed)
+        for p in prompts:
+            p["prompt_token_ids"].insert(1, cfg.audio_token_id)
+            p["multi_modal_data"] = {"audio": torch.randn(n_mels, int(a.audio_seconds * 100), generator=g)}
     sem = asyncio.Semaphore(a.max_concurrency)
     recs = []
 
@@ -98,6 +139,10 @@ async def _run(a, path):
             await asyncio.sleep(rng.expovariate(a.request_rate))
     await asyncio.gather(*tasks)
     wall = time.perf_counter() - t0
+    try:
+        eng_stats = eng.metrics.build_summary(wall)
+    except Exception:   # noqa: BLE001
+        eng_stats = {}
     eng.close()
     toks = sum(r["tokens"] for r in recs)
     out = {"metric": "qwen3_omni_e2e_tok_s", "requests": len(recs), "wall_s": round(wall, 3),
@@ -106,7 +151,9 @@ async def _run(a, path):
            "ttft_s": {f"p{q}": _pct([r["ttft"] for r in recs if r["ttft"] is not None], q) for q in (50, 90, 99)},
            "audio_ttfp_s": {f"p{q}": _pct([r["ttfp"] for r in recs if r["ttfp"] is not None], q) for q in (50, 90, 99)},
            "e2el_s": {f"p{q}": _pct([r["latency"] for r in recs], q) for q in (50, 90, 99)},
-           "config": {"tiny": a.tiny, "input_len": a.input_len, "max_tokens": a.max_tokens, "codec_frames": a.codec_frames,
+           "stages": _stage_split(eng_stats),
+           "config": {"tiny": a.tiny, "input_len": a.input_len, "audio_seconds": a.audio_seconds,
+                      "thinker_tp": a.thinker_tp, "thinker_ep": a.thinker_ep, "max_tokens": a.max_tokens, "codec_frames": a.codec_frames,
                       "max_concurrency": a.max_concurrency, "request_rate": a.request_rate, "async_chunk": a.async_chunk,
                       "data": "synthetic token ids; random-init weights"}}
     print(json.dumps(out))
@@ -125,6 +172,9 @@ def main(argv=None):
     ap.add_argument("--codec-frames", type=int, default=64)
     ap.add_argument("--async-chunk", action="store_true")
     ap.add_argument("--thinker-layers", type=int, default=None)
+    ap.add_argument("--audio-seconds", type=float, default=0.0, help="seconds of audio features (100 mel frames / s) per request")
+    ap.add_argument("--thinker-tp", type=int, default=1, help="GPUs of the thinker stage (tensor parallel)")
+    ap.add_argument("--thinker-ep", action="store_true", help="whole experts per rank instead of sliced FFNs")
     ap.add_argument("--seed", type=int, default=0)
     a = ap.parse_args(argv)
     ov = {"tiny": True} if a.tiny else {}
@@ -132,7 +182,10 @@ def main(argv=None):
         ov["thinker_layers"] = a.thinker_layers
     y = (YAML.replace("ASYNC_CHUNK", "true" if a.async_chunk else "false").replace("DEVICE", a.device)
          .replace("MAXB", str(a.max_concurrency)).replace("MAXTOK", str(a.max_tokens)).replace("CODEC", str(a.codec_frames))
-         .replace("OVERRIDES", json.dumps(ov)))
+         .replace("OVERRIDES", json.dumps(ov)).replace("THINKER_TP", str(a.thinker_tp))
+         .replace("THINKER_EP", "true" if a.thinker_ep else "false")
+         .replace("THINKER_DEVS", ",".join(str(i) for i in range(a.thinker_tp)))
+         .replace("THINKER_PROC", "true" if a.thinker_tp > 1 else "false"))
     f = tempfile.NamedTemporaryFile("w", suffix=".yaml", delete=False)
     f.write(y)
     f.close()

@@ -12,8 +12,10 @@ PROMPTS = [{"prompt_token_ids": [506, 509, 11, 12, 507, 506, 510, 13]},
 
 def _run(arch, tp, ep=False, device="cpu", overrides=None, max_tokens=8):
     from vllm_omni_b200.entrypoints.omni_llm import OmniLLM
+    ov = dict(overrides or {"tiny": True, "vocab_size": 600})
+    ov["moe"] = "Moe" in arch
     llm = OmniLLM(None, model_arch=arch, device=device, num_gpu_blocks=64, block_size=4 if device == "cpu" else 16,
-                  tensor_parallel_size=tp, enable_expert_parallel=ep, model_overrides=overrides or {"tiny": True})
+                  tensor_parallel_size=tp, enable_expert_parallel=ep, model_overrides=ov)
     try:
         sp = SamplingParams(temperature=0.0, max_tokens=max_tokens, detokenize=False, ignore_eos=True)
         outs = llm.generate(PROMPTS, sp)
@@ -81,7 +83,7 @@ def test_two_gpu_engine_matches_single_gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.distributed as dist
-    ov = {"tiny": True, "head_dim": 128}
+    ov = {"tiny": True, "head_dim": 128, "vocab_size": 600}
     one = _run("Qwen3MoeForCausalLM", 1, device=None, overrides=ov)
     try:
         two = _run("Qwen3MoeForCausalLM", 2, True, device=None, overrides=ov)

@@ -365,3 +365,28 @@ def test_gemm_two_small_problems_share_a_one_cta_launch(dev, S1, S2, N, K):
         for r in range(2):
             want = refj[:, :, r * G:(r + 1) * G]
             assert (bufs[r].float() - want).abs().max().item() <= 0.02 * want.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,kvl,causal", [(1, 128, 1, 1, None, False), (2, 600, 4, 2, [600, 333], False),
+                                                  (1, 2100, 3, 3, None, False), (1, 700, 2, 2, None, True)])
+def test_attention_head_dim_64(dev, B, S, H, Hkv, kvl, causal):
+    """Head size 64 (SD3, Stable Audio, audio / vision towers): one 64-wide TMA box per tile, N = 64
+    for P*V, 4-deep K/V rings; same checks as the 128 case, plus split outputs."""
+    from vllm_omni_b200.ops import attention as A
+    torch.manual_seed(5)
+    qkv = torch.randn(B, S, H + 2 * Hkv, 64, device=dev, dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+    kl = torch.tensor(kvl, dtype=torch.int32, device=dev) if kvl else None
+    o, lse = A.attention(q, k, v, kv_lens=kl, return_lse=True, causal=causal)
+    ref, rl = A.attention_reference(q, k, v, kv_lens=kl, return_lse=True, causal=causal)
+    _status_ok(dev)
+    assert (o.float() - ref.float()).abs().max().item() < 0.02
+    assert (lse - rl).abs().max().item() < 1e-3
+    if kvl is None and not causal:
+        split = S - 60
+        o1 = torch.empty(B, split, H, 64, device=dev, dtype=torch.bfloat16)
+        o2 = torch.empty(B, S - split, H, 64, device=dev, dtype=torch.bfloat16)
+        A.attention(q, k, v, out=o1, out2=o2, split=split)
+        _status_ok(dev)
+        assert (o1.float() - ref[:, :split].float()).abs().max().item() < 0.02
+        assert (o2.float() - ref[:, split:].float()).abs().max().item() < 0.02

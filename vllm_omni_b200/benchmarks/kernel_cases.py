@@ -1,6 +1,6 @@
 """Single-kernel workloads for profiling and roofline reports.
 
-    python -m vllm_omni_b200.benchmarks.kernel_cases gemm|gemm_gelu|attn|norm|qkrope|decode [--iters N]
+    python -m vllm_omni_b200.benchmarks.kernel_cases gemm|gemm_gelu|attn|attn64|attn_sdpa|norm|qkrope|decode [--iters N]
 
 Each case runs one kernel on the Qwen-Image 1024x1024 shapes (inputs larger than L2), prints
 the CUDA-event time (median, L2 flushed between iterations) and the achieved fraction of the
@@ -44,12 +44,19 @@ def main(argv=None):
         out = torch.empty(M, N, device=dev, dtype=bf)
         fn = lambda: gemm.linear(x, w, b, act="gelu_tanh" if a.case == "gemm_gelu" else None, out=out, force_bn=a.bn)
         flops = 2.0 * M * N * K
-    elif a.case == "attn":
-        B, S, H = 2, 4352, 24
-        qkv = torch.randn(B, S, 3, H, 128, device=dev, dtype=bf)
-        out = torch.empty(B, S, H, 128, device=dev, dtype=bf)
-        fn = lambda: A.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], out=out)
-        flops = 4.0 * B * H * S * S * 128
+    elif a.case in ("attn", "attn64", "attn_sdpa"):
+        # attn: the Qwen-Image joint attention; attn64: head size 64 at the same width (48 heads);
+        # attn_sdpa: torch SDPA (the library path the reference takes on this GPU) on the attn shape
+        B, S = 2, 4352
+        H, D = (48, 64) if a.case == "attn64" else (24, 128)
+        qkv = torch.randn(B, S, 3, H, D, device=dev, dtype=bf)
+        out = torch.empty(B, S, H, D, device=dev, dtype=bf)
+        if a.case == "attn_sdpa":
+            qt, kt, vt = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+            fn = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt)
+        else:
+            fn = lambda: A.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], out=out)
+        flops = 4.0 * B * H * S * S * D
     elif a.case == "norm":
         x = torch.randn(2, 4096, 3072, device=dev, dtype=bf)
         mod = torch.randn(2, 6 * 3072, device=dev, dtype=bf)

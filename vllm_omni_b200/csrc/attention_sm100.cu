@@ -36,13 +36,17 @@
 
 namespace omni {
 
-constexpr int ATT_D = 128;
+constexpr int ATT_D = 128;    // the larger of the two head sizes (64 and 128) the kernel is built for
 constexpr int ATT_BM = 128;   // rows per query tile
 constexpr int ATT_BN = 128;   // keys per KV tile
 constexpr int ATT_THREADS = 384;  // TMA, MMA, 2 idle warps, 2 x 4 softmax warps (one row per thread)
-constexpr int ATT_TILE_BYTES = ATT_BM * ATT_D * 2;  // 32 KiB
-constexpr int ATT_HALF_BYTES = ATT_TILE_BYTES / 2;  // one 64-wide TMA box
-constexpr int ATT_SMEM = 2 * ATT_TILE_BYTES /*Q*/ + 2 * ATT_TILE_BYTES /*K*/ + 2 * ATT_TILE_BYTES /*V*/ + 1024;
+constexpr int ATT_HALF_BYTES = ATT_BM * 64 * 2;     // one 64-wide TMA box of 128 rows: 16 KiB
+// per head size D: a tile is D / 64 boxes; the K and V rings are 2 deep at D = 128 and 4 deep at D = 64
+template <int D> struct AttCfg {
+  static constexpr int TILE_BYTES = ATT_BM * D * 2;
+  static constexpr int STAGES = D == 64 ? 4 : 2;
+  static constexpr int SMEM = 2 * TILE_BYTES /*Q*/ + 2 * STAGES * TILE_BYTES /*K, V*/ + 1024;
+};
 
 struct AttnOut {
   __nv_bfloat16* o;   // rows [0, split) of every batch
@@ -142,14 +146,16 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 // B2 S4352 H24 (one box, medians): 4 hand-offs 0.396 ms, 1 hand-off 0.409 ms; packed-bf16 MUFU
 // exponentials and polynomial shares of 0, 1/8, 3/8 and 1/2 were within 1 % of, or slower than,
 // fp32 MUFU with a quarter of the pairs on the FMA-pipe polynomial.
-template <int NH>
+template <int NH, int HD>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnOut out, int Sq, int Skv, int H, int Hkv,
                 const int* __restrict__ kv_lens, float scale_log2, int causal, int q_offset, AttnPaging pg,
                 PeerSignal sig, int* status) {
+  constexpr int ATT_TILE_BYTES = AttCfg<HD>::TILE_BYTES;
+  constexpr int KV_STAGES = AttCfg<HD>::STAGES;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
+  __shared__ __align__(8) uint64_t q_full, k_full[4], k_empty[4], v_full[4], v_empty[4];
   __shared__ __align__(8) uint64_t s_full[2], p_full[2][4], o_done[2];   // p_full: per 32-key chunk of P
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
@@ -162,8 +168,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int hkv = h / (H / Hkv);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = smem_base;                         // 2 tiles
-  const uint32_t sK = smem_base + 2 * ATT_TILE_BYTES;    // 2 stages
-  const uint32_t sV = smem_base + 4 * ATT_TILE_BYTES;    // 2 stages
+  const uint32_t sK = smem_base + 2 * ATT_TILE_BYTES;                    // KV_STAGES tiles
+  const uint32_t sV = smem_base + (2 + KV_STAGES) * ATT_TILE_BYTES;      // KV_STAGES tiles
   const int kv_len = kv_lens ? min(kv_lens[b], Skv) : Skv;
   // causal: query row s sees keys [0, s + q_offset]; the CTA only visits tiles its last row sees
   const int kv_cta = causal ? min(kv_len, qblk * 2 * ATT_BM + 2 * ATT_BM + q_offset) : kv_len;
@@ -177,11 +183,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(smem_u32(&q_full), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(smem_u32(&k_full[i]), 1);
       mbar_init(smem_u32(&k_empty[i]), 1);
       mbar_init(smem_u32(&v_full[i]), 1);
       mbar_init(smem_u32(&v_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&s_full[i]), 1);
       for (int c = 0; c < 4; ++c) mbar_init(smem_u32(&p_full[i][c]), 4);   // one arrival per softmax warp
       mbar_init(smem_u32(&o_done[i]), 1);
@@ -207,8 +215,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_expect_tx(qb, 2 * ATT_TILE_BYTES);
       for (int t = 0; t < 2; ++t) {
         const int s0 = qblk * 2 * ATT_BM + t * ATT_BM;
-        tma_load_4d(sQ + t * ATT_TILE_BYTES, &tmQ, qb, 0, s0, h, b);
-        tma_load_4d(sQ + t * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmQ, qb, 64, s0, h, b);
+#pragma unroll
+        for (int x = 0; x < HD / 64; ++x)
+          tma_load_4d(sQ + t * ATT_TILE_BYTES + x * ATT_HALF_BYTES, &tmQ, qb, 64 * x, s0, h, b);
       }
       const int* bt = pg.block_table ? pg.block_table + (long)b * pg.bt_stride : nullptr;
       const int last_page = bt ? max(0, (kv_len + pg.block_size - 1) / pg.block_size - 1) : 0;
@@ -216,8 +225,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t page_bytes = bt ? (uint32_t)pg.block_size * 128u : 0u;   // per 64-wide half
       for (int jj = 0; jj < n_kv; ++jj) {
         const int j = j0 + jj;
-        const int st = jj & 1;
-        const uint32_t ph = (jj >> 1) & 1;
+        const int st = jj % KV_STAGES;
+        const uint32_t ph = (jj / KV_STAGES) & 1;
         mbar_wait(smem_u32(&k_empty[st]), ph ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
         const uint32_t kb = smem_u32(&k_full[st]);
         mbar_expect_tx(kb, ATT_TILE_BYTES);
@@ -226,12 +235,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // last page (finite data that the key mask discards)
           for (int i = 0; i < pages_per_tile; ++i) {
             const int page = bt[min(j * pages_per_tile + i, last_page)];
-            tma_load_4d(sK + st * ATT_TILE_BYTES + i * page_bytes, &tmK, kb, 0, page * pg.block_size, hkv, 0);
-            tma_load_4d(sK + st * ATT_TILE_BYTES + ATT_HALF_BYTES + i * page_bytes, &tmK, kb, 64, page * pg.block_size, hkv, 0);
+#pragma unroll
+            for (int x = 0; x < HD / 64; ++x)
+              tma_load_4d(sK + st * ATT_TILE_BYTES + x * ATT_HALF_BYTES + i * page_bytes, &tmK, kb, 64 * x,
+                          page * pg.block_size, hkv, 0);
           }
         } else {
-          tma_load_4d(sK + st * ATT_TILE_BYTES, &tmK, kb, 0, j * ATT_BN, hkv, b);
-          tma_load_4d(sK + st * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmK, kb, 64, j * ATT_BN, hkv, b);
+#pragma unroll
+          for (int x = 0; x < HD / 64; ++x)
+            tma_load_4d(sK + st * ATT_TILE_BYTES + x * ATT_HALF_BYTES, &tmK, kb, 64 * x, j * ATT_BN, hkv, b);
         }
         mbar_wait(smem_u32(&v_empty[st]), ph ^ 1, &s_abort, status, ERR_WAIT_EMPTY);
         const uint32_t vb = smem_u32(&v_full[st]);
@@ -239,12 +251,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (bt) {
           for (int i = 0; i < pages_per_tile; ++i) {
             const int page = bt[min(j * pages_per_tile + i, last_page)];
-            tma_load_4d(sV + st * ATT_TILE_BYTES + i * page_bytes, &tmV, vb, 0, page * pg.block_size, hkv, 0);
-            tma_load_4d(sV + st * ATT_TILE_BYTES + ATT_HALF_BYTES + i * page_bytes, &tmV, vb, 64, page * pg.block_size, hkv, 0);
+#pragma unroll
+            for (int x = 0; x < HD / 64; ++x)
+              tma_load_4d(sV + st * ATT_TILE_BYTES + x * ATT_HALF_BYTES + i * page_bytes, &tmV, vb, 64 * x,
+                          page * pg.block_size, hkv, 0);
           }
         } else {
-          tma_load_4d(sV + st * ATT_TILE_BYTES, &tmV, vb, 0, j * ATT_BN, hkv, b);
-          tma_load_4d(sV + st * ATT_TILE_BYTES + ATT_HALF_BYTES, &tmV, vb, 64, j * ATT_BN, hkv, b);
+#pragma unroll
+          for (int x = 0; x < HD / 64; ++x)
+            tma_load_4d(sV + st * ATT_TILE_BYTES + x * ATT_HALF_BYTES, &tmV, vb, 64 * x, j * ATT_BN, hkv, b);
         }
       }
     }
@@ -252,7 +267,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // -------------------------------------------------------------- MMA issuer
     if (elect_one() && n_kv > 0) {
       constexpr uint32_t idesc_qk = umma_idesc(ATT_BM, ATT_BN, 1, 1, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc(ATT_BM, ATT_D, 1, 1, 0, 1);  // V is MN-major
+      constexpr uint32_t idesc_pv = umma_idesc(ATT_BM, HD, 1, 1, 0, 1);  // V is MN-major, N = head size
       // The issuing thread is a serial resource: the shared-memory descriptors are built ONCE; a
       // tile, a ring stage or a K step is a constant added to the 14-bit address field (16-byte units).
       constexpr uint64_t TILE16 = ATT_TILE_BYTES >> 4, HALF16 = ATT_HALF_BYTES >> 4;
@@ -263,7 +278,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t d = tmem_base + t * 128;
         const uint64_t a0 = dQ + (uint64_t)t * TILE16, b0 = dK + (uint64_t)st * TILE16;
 #pragma unroll
-        for (int k = 0; k < ATT_D / 16; ++k) {
+        for (int k = 0; k < HD / 16; ++k) {
           const uint64_t off = (uint64_t)((k >> 2) * HALF16 + (k & 3) * 2);   // 16 bf16 = 32 bytes along K
           mma_f16_ss(d, a0 + off, b0 + off, idesc_qk, k == 0 ? 0u : 1u);
         }
@@ -292,12 +307,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_commit(smem_u32(&k_empty[0]));
       for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int st = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
         const bool more = j + 1 < n_kv;
-        const int st1 = (j + 1) & 1;
+        const int st1 = (j + 1) % KV_STAGES;
         mbar_wait(smem_u32(&v_full[st]), ph, &s_abort, status, ERR_WAIT_FULL);
-        if (more) mbar_wait(smem_u32(&k_full[st1]), ((j + 1) >> 1) & 1, &s_abort, status, ERR_WAIT_FULL);
+        if (more) mbar_wait(smem_u32(&k_full[st1]), ((j + 1) / KV_STAGES) & 1, &s_abort, status, ERR_WAIT_FULL);
         const uint64_t v0 = dV + (uint64_t)st * TILE16;
         const uint32_t first = j != 0 ? 1u : 0u;      // the first P*V of a tile overwrites O
         for (int t = 0; t < n_qt; ++t) {
@@ -396,7 +411,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         l2a = mul2(l2a, alpha2);
         l2b = mul2(l2b, alpha2);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(tO + c * 32, v);
           tmem_wait_ld();
@@ -469,7 +484,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           out.part_ml[pidx * 2 + 1] = l;
         }
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t v[32];
           if (n_kv > 0) {
             tmem_ld_32x32(tO + c * 32, v);
@@ -479,7 +494,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int e = 0; e < 32; ++e) v[e] = 0u;
           }
           if (srow < Sq) {
-            float4* dst = reinterpret_cast<float4*>(out.part_o + pidx * ATT_D + c * 32);
+            float4* dst = reinterpret_cast<float4*>(out.part_o + pidx * HD + c * 32);
 #pragma unroll
             for (int g = 0; g < 8; ++g)
               dst[g] = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
@@ -500,7 +515,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const int k = lane & 7;
           const int row_base = qblk * 2 * ATT_BM + t * ATT_BM + q * 32;
 #pragma unroll 1
-          for (int hf = 0; hf < 2; ++hf) {
+          for (int hf = 0; hf < HD / 64; ++hf) {
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
               uint32_t v[32];
@@ -552,7 +567,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               orow = out.o + (long)b * out.o_bs + (long)srow * out.o_rs + (long)h * out.o_hs;
           }
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < HD / 32; ++c) {
             uint32_t v[32];
             if (n_kv > 0) {
               tmem_ld_32x32(tO + c * 32, v);
@@ -591,7 +606,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 // out[b, row, h, :] = sum_s 2^(m_s - m*) O_s / sum_s 2^(m_s - m*) l_s over the split-KV shares
-__global__ void __launch_bounds__(ATT_D)
+__global__ void __launch_bounds__(ATT_D)      // launched with D (64 or 128) threads
 attn_merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
                          __nv_bfloat16* __restrict__ o, long o_bs, long o_rs, long o_hs, float* __restrict__ lse,
                          int H, int Sq) {
@@ -607,18 +622,18 @@ attn_merge_splits_kernel(const float* __restrict__ part_o, const float* __restri
     const float ms = part_ml[(r * splits + s) * 2];
     const float a = ms == -INFINITY ? 0.f : exp2f(ms - mm);
     ll += part_ml[(r * splits + s) * 2 + 1] * a;
-    acc += part_o[(r * splits + s) * ATT_D + d] * a;
+    acc += part_o[(r * splits + s) * blockDim.x + d] * a;
   }
   o[b * o_bs + (long)row * o_rs + (long)h * o_hs + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
   if (lse && d == 0) lse[r] = ll > 0.f ? (mm + log2f(ll)) * 0.6931471805599453f : -INFINITY;
 }
 
 static int make_qkv_tmap(CUtensorMap* tm, const void* p, int S, int Hn, int B, long rs, long hs, long bs,
-                         int box_rows = ATT_BM) {
+                         int box_rows = ATT_BM, int D = ATT_D) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return RC_NO_DRIVER;
   if ((reinterpret_cast<uintptr_t>(p) & 15) || (rs & 7) || (hs & 7) || (bs & 7)) return RC_BAD_ARG;
-  cuuint64_t gdim[4] = {(cuuint64_t)ATT_D, (cuuint64_t)S, (cuuint64_t)Hn, (cuuint64_t)B};
+  cuuint64_t gdim[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)Hn, (cuuint64_t)B};
   cuuint64_t gstr[3] = {(cuuint64_t)rs * 2, (cuuint64_t)hs * 2, (cuuint64_t)bs * 2};
   cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -630,19 +645,23 @@ static int make_qkv_tmap(CUtensorMap* tm, const void* p, int S, int Hn, int B, l
 
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnOut& out, int B, int H,
                        int Hkv, int Sq, int Skv, const int* kv_lens, float scale, int causal, int q_offset,
-                       const AttnPaging& pg, int* status, cudaStream_t stream, const OmniSync* sync = nullptr) {
+                       const AttnPaging& pg, int* status, cudaStream_t stream, const OmniSync* sync = nullptr,
+                       int D = ATT_D) {
   // OMNI_ATTN_HANDOFFS (4 | 2 | 1): tuning switch, see attn_fwd_kernel
-  static int nh = -1;
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, AttnOut, int, int, int, int, const int*,
                            float, int, int, AttnPaging, PeerSignal, int*);
-  static KernelFn fn = nullptr;
-  if (nh < 0) {
+  static KernelFn fns[2] = {nullptr, nullptr};     // [0]: head size 64, [1]: head size 128
+  const int di = D == 64 ? 0 : 1;
+  if (fns[di] == nullptr) {
     const char* ev = getenv("OMNI_ATTN_HANDOFFS");
-    int want = ev ? atoi(ev) : 4;
-    fn = want == 1 ? attn_fwd_kernel<1> : (want == 2 ? attn_fwd_kernel<2> : attn_fwd_kernel<4>);
-    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    const int want = ev ? atoi(ev) : 4;
+    KernelFn f;
+    if (di == 0) f = want == 1 ? attn_fwd_kernel<1, 64> : (want == 2 ? attn_fwd_kernel<2, 64> : attn_fwd_kernel<4, 64>);
+    else f = want == 1 ? attn_fwd_kernel<1, 128> : (want == 2 ? attn_fwd_kernel<2, 128> : attn_fwd_kernel<4, 128>);
+    cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         di == 0 ? AttCfg<64>::SMEM : AttCfg<128>::SMEM);
     if (e != cudaSuccess) return (int)e;
-    nh = want;
+    fns[di] = f;
   }
   const int splits = out.kv_splits > 1 ? out.kv_splits : 1;
   dim3 grid(((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM)) * splits, H, B);
@@ -650,8 +669,8 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   PeerSignal sig;
   PeerWait unused;
   unpack_sync(sync, sig, unused);
-  fn<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens, scale_log2, causal, q_offset, pg,
-                                              sig, status);
+  fns[di]<<<grid, ATT_THREADS, di == 0 ? AttCfg<64>::SMEM : AttCfg<128>::SMEM, stream>>>(
+      tq, tk, tv, out, Sq, Skv, H, Hkv, kv_lens, scale_log2, causal, q_offset, pg, sig, status);
   return (int)cudaGetLastError();
 }
 
@@ -672,15 +691,15 @@ extern "C" int omni_attn_fwd_sync(const void* q, long q_rs, long q_hs, long q_bs
                                   int rows_per_rank2, void* const* o_peers, void* const* o2_peers,
                                   const omni::OmniSync* sync, int* status, void* stream) {
   using namespace omni;
-  if (D != ATT_D || H <= 0 || Hkv <= 0 || (H % Hkv) || B <= 0) return RC_BAD_ARG;
+  if ((D != 64 && D != 128) || H <= 0 || Hkv <= 0 || (H % Hkv) || B <= 0) return RC_BAD_ARG;
   if (Sq <= 0) return RC_OK;
   if ((o_rs & 7) || (o_hs & 7) || (o_bs & 7) || (o2_rs & 7) || (o2_hs & 7) || (o2_bs & 7)) return RC_BAD_ARG;
   CUtensorMap tq, tk, tv;
-  int rc = make_qkv_tmap(&tq, q, Sq, H, B, q_rs, q_hs, q_bs);
+  int rc = make_qkv_tmap(&tq, q, Sq, H, B, q_rs, q_hs, q_bs, ATT_BM, D);
   if (rc) return rc;
-  rc = make_qkv_tmap(&tk, k, Skv, Hkv, B, k_rs, k_hs, k_bs);
+  rc = make_qkv_tmap(&tk, k, Skv, Hkv, B, k_rs, k_hs, k_bs, ATT_BM, D);
   if (rc) return rc;
-  rc = make_qkv_tmap(&tv, v, Skv, Hkv, B, v_rs, v_hs, v_bs);
+  rc = make_qkv_tmap(&tv, v, Skv, Hkv, B, v_rs, v_hs, v_bs, ATT_BM, D);
   if (rc) return rc;
   AttnOut out;
   out.o = (__nv_bfloat16*)o; out.o2 = (__nv_bfloat16*)o2;
@@ -701,7 +720,7 @@ extern "C" int omni_attn_fwd_sync(const void* q, long q_rs, long q_hs, long q_bs
   out.kv_splits = 1; out.part_o = nullptr; out.part_ml = nullptr;
   AttnPaging pg = {nullptr, 0, 0};
   return launch_attn(tq, tk, tv, out, B, H, Hkv, Sq, Skv, kv_lens, scale, causal, q_offset, pg, status,
-                     (cudaStream_t)stream, sync);
+                     (cudaStream_t)stream, sync, D);
 }
 
 extern "C" int omni_attn_fwd(const void* q, long q_rs, long q_hs, long q_bs, const void* k, long k_rs,

@@ -47,7 +47,7 @@ class Qwen25VisionConfig:
 
 
 def _mha(q, k, v, kv_lens=None):
-    if q.is_cuda and q.shape[-1] == 128 and q.dtype == torch.bfloat16:
+    if q.is_cuda and q.shape[-1] in (64, 128) and q.dtype == torch.bfloat16:
         return attention(q, k, v, kv_lens=kv_lens)
     return attention_reference(q, k, v, kv_lens=kv_lens)
 

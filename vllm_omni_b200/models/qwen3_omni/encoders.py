@@ -34,7 +34,7 @@ from .config import AudioEncoderConfig, VisionEncoderConfig
 
 def _mha(q, k, v, kv_lens=None):
     """[B, S, H, D] non-causal attention with an optional per-batch key length."""
-    if q.is_cuda and q.shape[-1] == 128 and q.dtype == torch.bfloat16:
+    if q.is_cuda and q.shape[-1] in (64, 128) and q.dtype == torch.bfloat16:
         return attention(q, k, v, kv_lens=kv_lens)
     return attention_reference(q, k, v, kv_lens=kv_lens)
 

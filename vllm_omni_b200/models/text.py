@@ -17,6 +17,9 @@ def build_text_model(model_stage, hf_config: dict, dtype, device, **kw):
     if "num_experts" not in cfg:
         dc.num_experts = 0
     if kw.get("tiny"):
-        dc = DecoderConfig(vocab_size=259, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
-                           num_key_value_heads=2, head_dim=16, intermediate_size=128)
+        # test geometry; ``moe`` / ``head_dim`` choose the mixture-of-experts layers and the head size
+        dc = DecoderConfig(vocab_size=int(kw.get("vocab_size", 259)), hidden_size=64, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=int(kw.get("head_dim", 16)),
+                           intermediate_size=128, num_experts=8 if kw.get("moe") else 0, num_experts_per_tok=2,
+                           moe_intermediate_size=64)
     return TextDecoderModel(dc, dtype, device)

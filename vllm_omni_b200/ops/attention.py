@@ -68,7 +68,7 @@ def attention(q, k, v, scale=None, kv_lens=None, out=None, out2=None, split=0, r
         else:
             out = o
         return (out, lse) if return_lse else out
-    assert q.dtype == torch.bfloat16 and D == 128, "tcgen05 attention path: bf16, head_dim 128"
+    assert q.dtype == torch.bfloat16 and D in (64, 128), "tcgen05 attention path: bf16, head_dim 64 or 128"
     for t in (q, k, v):
         assert t.stride(3) == 1
     sc = scatter
