@@ -101,3 +101,23 @@ def test_wan_cfg_parallel_matches_single_process():
             omni.close()
     a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(cfg_parallel_size=2))
     assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4
+
+
+def test_flux_tensor_parallel_matches_single_process():
+    """FLUX (double-stream + single-stream blocks) with heads and MLP columns split over two ranks."""
+    tf = dict(num_layers=1, num_single_layers=2, attention_head_dim=32, num_attention_heads=2, joint_attention_dim=32,
+              pooled_projection_dim=16, in_channels=64, out_channels=16, axes_dims_rope=(8, 12, 12))
+    vae = dict(block_out_channels=(8, 16, 16, 16), layers_per_block=1, norm_num_groups=4)
+
+    def run(par):
+        omni = Omni("FluxPipeline", dtype="float32", device="cpu", tf_model_config=tf, vae_config=vae,
+                    diffusion_load_format="dummy", parallel_config=par, output_type="latent")
+        try:
+            sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=3, guidance_scale=3.5, seed=0,
+                                             output_type="latent", max_sequence_length=8)
+            out = omni.generate(["a cube"], sp)[0]
+            return torch.as_tensor(out.latents if out.latents is not None else out.images[0]).float()
+        finally:
+            omni.close()
+    a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(tensor_parallel_size=2))
+    assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4

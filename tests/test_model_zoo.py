@@ -26,9 +26,9 @@ TINY = {
     "WanPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
     "WanImageToVideoPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
     "Wan22TI2VPipeline": dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=1),
-    "HunyuanImage3Pipeline": dict(vocab_size=64, hidden_size=64, num_hidden_layers=1, num_attention_heads=2,
-                                  num_key_value_heads=2, head_dim=32, num_experts=4, num_experts_per_tok=2,
-                                  moe_intermediate_size=32),
+    "HunyuanImage3Pipeline": dict(vocab_size=128, hidden_size=64, num_hidden_layers=1, num_attention_heads=2,
+                                  num_key_value_heads=1, head_dim=32, num_experts=4, moe_topk=2, intermediate_size=32,
+                                  moe_intermediate_size=32, patch_embed_hidden_dim=32, latent_channels=4),
     "StableAudioPipeline": dict(num_attention_heads=2, attention_head_dim=16, num_key_value_attention_heads=1, in_channels=8,
                                 out_channels=8, cross_attention_dim=24, cross_attention_input_dim=24, global_states_input_dim=48,
                                 time_proj_dim=16, num_layers=1, sample_size=6),
@@ -47,7 +47,7 @@ def small_vae(monkeypatch):
         k.setdefault("num_res_blocks", 1)
         return orig(*a, **k)
     for mod in ("vllm_omni_b200.diffusion.models.qwen_image.pipeline",
-                "vllm_omni_b200.diffusion.models.wan.pipeline", "vllm_omni_b200.diffusion.models.hunyuan_image_3.pipeline"):
+                "vllm_omni_b200.diffusion.models.wan.pipeline"):
         import importlib
         m = importlib.import_module(mod)
         monkeypatch.setattr(m, "QwenImageVAEConfig", tiny)
@@ -57,6 +57,8 @@ def small_vae(monkeypatch):
 def test_pipeline_runs_tiny(name):
     vae = SMALL_KL if name != "StableAudioPipeline" else dict(decoder_channels=8, channel_multiples=(1, 2),
                                                                 downsampling_ratios=(2, 4), sampling_rate=800)
+    if name == "HunyuanImage3Pipeline":                    # 1/16 fold-shuffle autoencoder: five levels
+        vae = dict(block_out_channels=(8, 8, 8, 8, 8), layers_per_block=1, norm_num_groups=4)
     o = OmniDiffusion(name, dtype="float32", device="cpu", tf_model_config=TINY[name], vae_config=vae)
     try:
         sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, seed=0, num_frames=5,

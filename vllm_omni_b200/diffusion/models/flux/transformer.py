@@ -111,21 +111,32 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
         return m
 
     def single_forward(self, blk: SingleBlock, x, m3, cos, sin, kv_lens, S_img):
-        """x: joint [B, S, D] in place; m3 [B, 3D] = shift, scale, gate."""
+        """x: joint [B, S, D] in place; m3 [B, 3D] = shift, scale, gate.  Under tensor parallelism
+        (``parallel/tensor_parallel.shard_transformer``) ``linear1`` holds this rank's heads of q, k, v and
+        its slice of the MLP columns, ``linear2`` the matching input features; the partial products of
+        ``linear2`` are summed across the ranks (the reference all-gathers the heads instead,
+        vllm_omni/diffusion/models/flux/flux_transformer.py:230)."""
         cfg = self.cfg
-        D, H, Hd = cfg.inner_dim, cfg.num_attention_heads, cfg.attention_head_dim
+        D, Hd = cfg.inner_dim, cfg.attention_head_dim
+        tp = getattr(self, "tp_heads", 0)
+        H = tp or cfg.num_attention_heads
+        Dl = H * Hd                                  # this rank's share of the attention width
+        Fl = blk.linear1.out_features - 3 * Dl       # ... and of the MLP width
         B, S, _ = x.shape
         xn = fused.norm_modulate(x, shift=m3[:, 0:D], scale=m3[:, D:2 * D], eps=cfg.eps)
-        y = blk.linear1(xn)                                                    # [B,S,3D+F]
-        qkv = y[..., :3 * D].contiguous()
+        y = blk.linear1(xn)                                                    # [B,S,3Dl+Fl]
+        qkv = y[..., :3 * Dl].contiguous()
         fused.qk_norm_rope_(qkv, H, H, Hd, wq=blk.norm_q, wk=blk.norm_k, cos=cos, sin=sin, interleaved=True,
                             eps=cfg.eps)
         q5 = qkv.view(B, S, 3, H, Hd)
-        cat = torch.empty(B, S, D + blk.F, dtype=x.dtype, device=x.device)
+        cat = torch.empty(B, S, Dl + Fl, dtype=x.dtype, device=x.device)
         o = attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2], kv_lens=kv_lens)
-        cat[..., :D] = o.reshape(B, S, D)
-        cat[..., D:] = F.gelu(y[..., 3 * D:].float(), approximate="tanh").to(x.dtype)
-        blk.linear2(cat, residual=x, gate=m3[:, 2 * D:3 * D], out=x)
+        cat[..., :Dl] = o.reshape(B, S, Dl)
+        cat[..., Dl:] = F.gelu(y[..., 3 * Dl:].float(), approximate="tanh").to(x.dtype)
+        if tp:
+            self.tp_reducer.linear(blk.linear2, cat, bias=blk.linear2_bias, gate=m3[:, 2 * D:3 * D], residual=x, out=x)
+        else:
+            blk.linear2(cat, residual=x, gate=m3[:, 2 * D:3 * D], out=x)
         return x
 
     def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, pooled_projections=None,

@@ -53,5 +53,8 @@ def apply_parallelism(pipe, od_config) -> None:
         from .cfg_parallel import CFGExchange
         pipe.cfg_exchange = CFGExchange(ps.get_cfg_group())
     if pc.tensor_parallel_size > 1 and tr is not None:
-        from .tensor_parallel import shard_transformer
-        shard_transformer(tr, ps.get_tp_group())
+        if hasattr(tr, "enable_tensor_parallel"):        # decoder-style denoisers shard themselves (heads + experts)
+            tr.enable_tensor_parallel(ps.get_tp_group())
+        else:
+            from .tensor_parallel import shard_transformer
+            shard_transformer(tr, ps.get_tp_group())

@@ -198,3 +198,30 @@ def shard_transformer(tr, group, mode: str | None = None) -> None:
             sp.tp_mlp = TPLinearPair(sp.mlp_up, sp.mlp_down, group, reducer=reducer)
             sp.to_qkv = sp.to_out = sp.mlp_up = sp.mlp_down = None
     tr.tp_heads = H // P
+    # FLUX-family single-stream blocks: linear1 = [q | k | v | mlp] rows, linear2 = [attn | mlp] input features
+    for blk in getattr(tr, "single_blocks", []) or []:
+        shard_flux_single_block(blk, tr.cfg.inner_dim, group)
+
+
+def shard_flux_single_block(blk, D: int, group) -> None:
+    """Column-parallel ``linear1`` (this rank's heads of q, k and v and its slice of the MLP columns)
+    and row-parallel ``linear2`` (the matching input features; its bias is applied once, by the
+    reduce)."""
+    P, r = group.world_size, group.rank_in_group
+    F_ = blk.linear1.out_features - 3 * D
+    if D % P or F_ % P:
+        raise ValueError(f"attention width {D} and MLP width {F_} must be divisible by tensor_parallel_size {P}")
+    Dl, Fl = D // P, F_ // P
+    w1, b1 = blk.linear1.weight.data, (blk.linear1.bias.data if blk.linear1.bias is not None else None)
+    rows = torch.cat([torch.arange(g * D + r * Dl, g * D + (r + 1) * Dl) for g in range(3)] +
+                     [torch.arange(3 * D + r * Fl, 3 * D + (r + 1) * Fl)]).to(w1.device)
+    lin1 = FusedLinear(w1.shape[1], rows.numel(), bias=b1 is not None, dtype=w1.dtype, device=w1.device)
+    lin1.weight.data = w1[rows].contiguous()
+    if b1 is not None:
+        lin1.bias.data = b1[rows].contiguous()
+    w2 = blk.linear2.weight.data
+    cols = torch.cat([torch.arange(r * Dl, (r + 1) * Dl), torch.arange(D + r * Fl, D + (r + 1) * Fl)]).to(w2.device)
+    lin2 = FusedLinear(cols.numel(), w2.shape[0], bias=False, dtype=w2.dtype, device=w2.device)
+    lin2.weight.data = w2[:, cols].contiguous()
+    blk.linear2_bias = blk.linear2.bias
+    blk.linear1, blk.linear2 = lin1, lin2
