@@ -57,14 +57,24 @@ class TPControl:
 def init_tp_process(rank: int, world: int, port: int, use_cuda: bool, device_index: int, timeout_s: float = 600.0):
     """Join the stage's process group and build its tensor-parallel group."""
     from ..parallel import parallel_state as ps
-    os.environ["MASTER_ADDR"] = "127.0.0.1"
-    os.environ["MASTER_PORT"] = str(port)
-    os.environ["RANK"], os.environ["WORLD_SIZE"], os.environ["LOCAL_RANK"] = str(rank), str(world), str(device_index)
+    mine = {"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world),
+            "LOCAL_RANK": str(device_index)}
+    saved = {k: os.environ.get(k) for k in mine}
+    os.environ.update(mine)
     if use_cuda:
         torch.cuda.set_device(device_index)
     backend = "nccl" if use_cuda else "gloo"
-    ps.init_distributed_environment(world_size=world, rank=rank, local_rank=device_index, backend=backend,
-                                    timeout_s=timeout_s)
+    try:
+        ps.init_distributed_environment(world_size=world, rank=rank, local_rank=device_index, backend=backend,
+                                        timeout_s=timeout_s)
+    finally:
+        # the rendezvous variables are this stage's business only: rank 0 is the caller's own process, and
+        # whatever it starts next (another stage, a diffusion executor) must not mistake itself for a rank
+        for k, v in saved.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
     if not ps.model_parallel_is_initialized():
         ps.initialize_model_parallel(tensor_parallel_size=world, backend=backend)
     return ps.get_tp_group()
