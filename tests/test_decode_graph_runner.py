@@ -1,5 +1,6 @@
 """Static-buffer decode step (the body a CUDA graph replays): bucket padding, slot masking and
 MRoPE positions give the same hidden states and cache contents as the direct decoder call."""
+import pytest
 import torch
 
 from vllm_omni_b200.engine.graph_runner import DecodeGraphRunner
@@ -105,3 +106,29 @@ def test_engine_with_the_static_buffer_step_generates_the_same_tokens(monkeypatc
     r = llm.engine.runner.graph_runner if hasattr(llm.engine, "runner") else None
     assert graphed == plain
     assert r is not None and r.replays > 0
+
+
+@pytest.mark.gpu
+def test_captured_decode_graph_generates_the_same_tokens_on_gpu(monkeypatch):
+    """On a GPU the decode step is replayed from a CUDA graph by default; greedy tokens equal the eager
+    engine's (two requests fill the two-row bucket, so both runs launch identical kernels)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from vllm_omni_b200.entrypoints.omni_llm import OmniLLM
+    from vllm_omni_b200.inputs import SamplingParams
+    kw = dict(model_arch="Qwen3OmniMoeForConditionalGeneration", model_stage="thinker", device="cuda", num_gpu_blocks=64,
+              model_overrides={"tiny": True, "head_dim": 64}, engine_output_type="latent")
+    prompts = [{"prompt_token_ids": [506, 509, 11, 12, 507, 506, 510, 13]}, {"prompt_token_ids": [506, 509, 20, 507, 506, 510]}]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, detokenize=False)
+
+    def run(flag):
+        monkeypatch.setenv("OMNI_AR_CUDA_GRAPH", flag)
+        llm = OmniLLM(None, **kw)
+        outs = llm.generate(prompts, sp)
+        return llm, [list(o.outputs[0].token_ids) for o in outs]
+    _, eager = run("0")
+    monkeypatch.delenv("OMNI_AR_CUDA_GRAPH")
+    llm, graphed = run("1")
+    r = llm.engine.runner.graph_runner
+    assert r is not None and r.use_graph and r.replays > 0 and any(b.graph is not None for b in r._state.values())
+    assert graphed == eager

@@ -69,6 +69,7 @@ def test_cross_process_put_get_is_byte_exact():
     from vllm_omni_b200.connectors.device_connector import DeviceConnector
     n_dev = torch.cuda.device_count()
     cons_dev, prod_dev = (1, 0) if n_dev >= 2 else (0, 0)
+    prev_dev = torch.cuda.current_device()
     torch.cuda.set_device(cons_dev)
     c = DeviceConnector({"cross_process": True, "name": "omni_dc_test", "arena_mb": 8})
     c.open_receiver(0, 1)
@@ -97,4 +98,5 @@ def test_cross_process_put_get_is_byte_exact():
         if p.is_alive():
             p.terminate()
         c.close()
+        torch.cuda.set_device(prev_dev)
     assert p.exitcode == 0

@@ -390,3 +390,30 @@ def test_attention_head_dim_64(dev, B, S, H, Hkv, kvl, causal):
         _status_ok(dev)
         assert (o1.float() - ref[:, :split].float()).abs().max().item() < 0.02
         assert (o2.float() - ref[:, split:].float()).abs().max().item() < 0.02
+
+
+def test_kernels_launch_on_every_device_of_the_process():
+    """One process driving two GPUs (stages of a pipeline as threads): the large-shared-memory kernels
+    are prepared per device, so the second device launches as well as the first."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from vllm_omni_b200.ops import gemm
+    from vllm_omni_b200.ops.attention import attention, attention_reference
+    prev = torch.cuda.current_device()
+    try:
+        for d in (0, 1, 0):
+            torch.cuda.set_device(d)
+            dv = torch.device("cuda", d)
+            torch.manual_seed(d)
+            x = torch.randn(300, 256, device=dv, dtype=torch.bfloat16)
+            w = torch.randn(512, 256, device=dv, dtype=torch.bfloat16) * 0.05
+            for bn in (0, 128, 384):
+                y = gemm.linear(x, w, force_bn=bn).float()
+                ref = x.float() @ w.float().t()
+                assert (y - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3
+            q, k, v = (torch.randn(1, 200, 2, 128, device=dv, dtype=torch.bfloat16) for _ in range(3))
+            o = attention(q, k, v).float()
+            assert (o - attention_reference(q.float(), k.float(), v.float())).abs().max().item() < 0.03
+            _status_ok(dv)
+    finally:
+        torch.cuda.set_device(prev)

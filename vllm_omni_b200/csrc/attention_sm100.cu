@@ -658,11 +658,10 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     KernelFn f;
     if (di == 0) f = want == 1 ? attn_fwd_kernel<1, 64> : (want == 2 ? attn_fwd_kernel<2, 64> : attn_fwd_kernel<4, 64>);
     else f = want == 1 ? attn_fwd_kernel<1, 128> : (want == 2 ? attn_fwd_kernel<2, 128> : attn_fwd_kernel<4, 128>);
-    cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         di == 0 ? AttCfg<64>::SMEM : AttCfg<128>::SMEM);
-    if (e != cudaSuccess) return (int)e;
     fns[di] = f;
   }
+  static unsigned long long prepared[2] = {0, 0};
+  if (int e = ensure_dynamic_smem((const void*)fns[di], di == 0 ? AttCfg<64>::SMEM : AttCfg<128>::SMEM, prepared[di])) return e;
   const int splits = out.kv_splits > 1 ? out.kv_splits : 1;
   dim3 grid(((Sq + 2 * ATT_BM - 1) / (2 * ATT_BM)) * splits, H, B);
   const float scale_log2 = scale * 1.4426950408889634f;

@@ -234,12 +234,8 @@ extern "C" int omni_gemm_fp8(const void* A, long lda, const float* sa, int lds_a
   if (rc) return rc;
   rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, F8_BN, F8_BK);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
+  static unsigned long long prepared = 0;
+  if (int e = ensure_dynamic_smem((const void*)gemm_fp8_kernel, F8_SMEM, prepared)) return e;
   Fp8Epilogue epi;
   epi.bias = (const __nv_bfloat16*)bias; epi.residual = (const __nv_bfloat16*)residual; epi.gate = (const __nv_bfloat16*)gate;
   epi.ldr = ldr; epi.gate_stride = gate_stride; epi.rows_per_batch = rows_per_batch > 0 ? rows_per_batch : 1; epi.act = act;

@@ -837,12 +837,8 @@ static int fill_pair_problem(PairProblem& pp, const void* A, int lda, const void
 template <int TN>
 static int launch_gemm_pair(const PairArgs& args, int* status, int max_pairs, cudaStream_t stream) {
   using Cfg = PairCfg<TN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
+  static unsigned long long prepared = 0;
+  if (int e = ensure_dynamic_smem((const void*)gemm_bf16_pair_kernel<TN>, Cfg::SMEM_BYTES, prepared)) return e;
   const int num_n = (args.N + TN - 1) / TN;
   int num_tiles = 0;
   for (int i = 0; i < args.n_problems; ++i) num_tiles += ((args.p[i].M + 2 * BM - 1) / (2 * BM)) * num_n;
@@ -909,13 +905,8 @@ static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, 
   int rc = make_tmap_3d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)K, (uint64_t)N,
                         (uint64_t)num_experts, (uint64_t)ldw * 2, (uint64_t)N * ldw * 2, BK, BN);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
+  static unsigned long long prepared = 0;
+  if (int e = ensure_dynamic_smem((const void*)gemm_bf16_kernel<BN>, Cfg::SMEM_BYTES, prepared)) return e;
   const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
   ConvGeom geom = {};
@@ -931,12 +922,8 @@ static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, 
 template <int BN>
 static int launch_gemm_multi(const PairArgs& args, int* status, int max_ctas, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_multi_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
+  static unsigned long long prepared = 0;
+  if (int e = ensure_dynamic_smem((const void*)gemm_bf16_multi_kernel<BN>, Cfg::SMEM_BYTES, prepared)) return e;
   const int num_n = (args.N + BN - 1) / BN;
   int num_tiles = 0;
   for (int i = 0; i < args.n_problems; ++i) num_tiles += ((args.p[i].M + BM - 1) / BM) * num_n;

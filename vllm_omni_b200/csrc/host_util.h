@@ -76,6 +76,20 @@ inline int make_tmap_3d(CUtensorMap* out, const void* ptr, CUtensorMapDataType d
   return r == CUDA_SUCCESS ? RC_OK : RC_TMAP;
 }
 
+// cudaFuncSetAttribute applies to the CURRENT device only, and one process may launch on several
+// (stages of a pipeline running as threads, each on its own GPU).  `mask` remembers, one bit per
+// device index, where the kernel has been prepared; returns 0 or the CUDA error.
+inline int ensure_dynamic_smem(const void* fn, int bytes, unsigned long long& mask) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (mask & bit) return 0;
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return (int)e;
+  mask |= bit;
+  return 0;
+}
+
 inline int sm_count() {
   static int n = 0;
   if (n == 0) {

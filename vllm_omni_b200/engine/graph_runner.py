@@ -11,8 +11,8 @@ The reference gets the same effect from vLLM's CUDA-graph runner plus dedicated 
 talker's multi-token step (vllm_omni/worker/gpu_model_runner.py:71-89, 1085-1112).
 
 Off the GPU (or with ``use_graph=False``) the runner executes the same static-buffer step eagerly,
-which is how the host-side logic is tested.  Capture is enabled per engine with
-``OMNI_AR_CUDA_GRAPH=1``.
+which is how the host-side logic is tested.  On a GPU the runner is on by default
+(``OMNI_AR_CUDA_GRAPH=0`` switches it off).
 """
 from __future__ import annotations
 
@@ -127,10 +127,18 @@ class DecodeGraphRunner:
                 st.warm = True
                 torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            try:
+                with torch.cuda.graph(g):
+                    self._step(st)
+            except Exception as e:   # noqa: BLE001  (a step that cannot be captured runs eagerly from here on)
+                import logging
+                logging.getLogger(__name__).warning("decode step not capturable (%s); running it eagerly", e)
+                self.use_graph = False
+                torch.cuda.synchronize(self.device)
                 self._step(st)
-            st.graph = g
-            g.replay()
+            else:
+                st.graph = g
+                g.replay()
         else:
             st.graph.replay()
         self.replays += 1

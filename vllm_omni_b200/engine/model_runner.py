@@ -35,10 +35,12 @@ class ARModelRunner:
                            torch.zeros(num_blocks, block_size, kvh, dec.head_dim, dtype=dtype, device=device))
                           for _ in range(dec.num_hidden_layers)]
         self.tp_group = None        # set by OmniLLM: sampled ids of every step come from rank 0
-        # decode-only steps replay a captured graph per batch-size bucket (``OMNI_AR_CUDA_GRAPH=1``); contexts
-        # longer than ``OMNI_AR_GRAPH_MAX_TOKENS`` (default 4096) and mixed prefill/decode steps run eagerly
+        # decode-only steps replay a captured graph per batch-size bucket (on by default on a GPU,
+        # ``OMNI_AR_CUDA_GRAPH=0`` switches it off); contexts longer than ``OMNI_AR_GRAPH_MAX_TOKENS``
+        # (default 4096) and mixed prefill/decode steps run eagerly
         self.graph_runner = None
-        if os.environ.get("OMNI_AR_CUDA_GRAPH", "0") == "1" and hasattr(model, "decoder"):
+        on = os.environ.get("OMNI_AR_CUDA_GRAPH", "1" if torch.device(device).type == "cuda" else "0") == "1"
+        if on and hasattr(model, "decoder"):
             from .graph_runner import DecodeGraphRunner
             max_tokens = int(os.environ.get("OMNI_AR_GRAPH_MAX_TOKENS", "4096"))
             self.graph_runner = DecodeGraphRunner(model.decoder, self.kv_caches, max(1, max_tokens // block_size),
