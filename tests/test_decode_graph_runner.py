@@ -116,10 +116,10 @@ def test_captured_decode_graph_generates_the_same_tokens_on_gpu(monkeypatch):
         pytest.skip("needs a GPU")
     from vllm_omni_b200.entrypoints.omni_llm import OmniLLM
     from vllm_omni_b200.inputs import SamplingParams
-    kw = dict(model_arch="Qwen3OmniMoeForConditionalGeneration", model_stage="thinker", device="cuda", num_gpu_blocks=64,
-              model_overrides={"tiny": True, "head_dim": 64}, engine_output_type="latent")
-    prompts = [{"prompt_token_ids": [506, 509, 11, 12, 507, 506, 510, 13]}, {"prompt_token_ids": [506, 509, 20, 507, 506, 510]}]
-    sp = SamplingParams(temperature=0.0, max_tokens=12, detokenize=False)
+    kw = dict(model_arch="Qwen3MoeForCausalLM", device="cuda", num_gpu_blocks=64, block_size=16,
+              model_overrides={"tiny": True, "head_dim": 128, "vocab_size": 600, "moe": True})
+    prompts = [{"prompt_token_ids": [3, 17, 42, 99, 7, 150, 23, 8, 64]}, {"prompt_token_ids": [5, 9, 11, 300, 2, 77]}]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, detokenize=False, ignore_eos=True)
 
     def run(flag):
         monkeypatch.setenv("OMNI_AR_CUDA_GRAPH", flag)

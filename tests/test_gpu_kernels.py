@@ -417,3 +417,32 @@ def test_kernels_launch_on_every_device_of_the_process():
             _status_ok(dv)
     finally:
         torch.cuda.set_device(prev)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+def test_attention_continuation_merges_two_key_sets(dev, D):
+    """A launch over keys B with ``merge_prev`` = the result over keys A equals attention over A + B;
+    an empty second key set leaves the first result untouched; in-place (prev is out) is allowed."""
+    from vllm_omni_b200.ops.attention import attention, attention_reference
+    torch.manual_seed(5)
+    B, Sq, H, Hkv = 2, 300, 4, 2
+    q = torch.randn(B, Sq, H, D, device=dev, dtype=torch.bfloat16)
+    ka, va = (torch.randn(B, 200, Hkv, D, device=dev, dtype=torch.bfloat16) for _ in range(2))
+    kb, vb = (torch.randn(B, 333, Hkv, D, device=dev, dtype=torch.bfloat16) for _ in range(2))
+    lens_b = torch.tensor([333, 150], dtype=torch.int32, device=dev)
+    o, lse = attention(q, ka, va, return_lse=True)
+    o2, lse2 = attention(q, kb, vb, kv_lens=lens_b, merge_prev=(o, lse), out=o, return_lse=True)
+    assert o2.data_ptr() == o.data_ptr()
+    for b in range(B):
+        n = int(lens_b[b])
+        k_all, v_all = torch.cat([ka[b:b + 1], kb[b:b + 1, :n]], 1), torch.cat([va[b:b + 1], vb[b:b + 1, :n]], 1)
+        ref, ref_lse = attention_reference(q[b:b + 1].float(), k_all.float(), v_all.float(), return_lse=True)
+        assert (o2[b:b + 1].float() - ref).abs().max().item() < 0.03
+        assert (lse2[b:b + 1] - ref_lse).abs().max().item() < 0.02
+    # no valid key in the continuation: the earlier rows and LSE come back unchanged
+    o3, lse3 = attention(q, ka, va, return_lse=True)
+    keep = o3.clone()
+    zero = torch.zeros(B, dtype=torch.int32, device=dev)
+    o4, lse4 = attention(q, kb, vb, kv_lens=zero, merge_prev=(o3, lse3), out=o3, return_lse=True)
+    assert torch.equal(o4, keep) and torch.equal(lse4, lse3)
+    _status_ok(dev)

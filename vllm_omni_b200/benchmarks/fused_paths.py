@@ -19,6 +19,8 @@ Paths (rank 0 prints one JSON line):
   tp_row_reduce   row-parallel GEMM with the reduce-scatter in its epilogue + local reduce + peer gather
                                                 vs GEMM + NCCL all-reduce
   peer_kv_attn    attention reading K/V of the peer through plain TMA loads   vs local K/V
+  ring_gather_attn  own-chunk attention overlapped with a pull of the peers' K/V, then the continuation
+                  launch (the ring path as built)   vs one launch over all keys held locally
   cfg_exchange    guidance mix + Euler step reading the partner's prediction over NVLink  vs local
 """
 from __future__ import annotations
@@ -137,6 +139,20 @@ def multi(a):
     t_pkv = _time(lambda: A.attention(q_loc, peer[:, :, 0], peer[:, :, 1], out=o2), a.reps, grp, flush)
     t_lkv = _time(lambda: A.attention(q_loc, kv_sym.local[:, :, 0], kv_sym.local[:, :, 1], out=o2), a.reps, grp, flush)
     out["peer_kv_attn"] = _entry(t_pkv, 4.0 * H * M * M * Dh, M * 2 * H * Dh * 2, t_lkv)
+
+    # ---- ring_gather_attn: the sequence-parallel ring as built (parallel/ring.py): own-chunk attention while a
+    # side stream pulls the peers' K/V into local memory, then the continuation launch that combines both
+    from vllm_omni_b200.parallel.ring import RingJointAttention
+    ring = RingJointAttention(grp, H, Dh, "peer")
+    ring.setup(1, M, 0, dev, bf)
+    ring.qkv_local.normal_()
+    grp.barrier()
+    t_ring = _time(lambda: ring.attend(None, None), a.reps, grp, flush)
+    kv_full = torch.randn(1, P * M, 2, H, Dh, device=dev, dtype=bf)
+    t_full = _time(lambda: A.attention(q_loc, kv_full[:, :, 0], kv_full[:, :, 1], out=o2), a.reps, grp, flush)
+    out["ring_gather_attn"] = _entry(t_ring, 4.0 * H * M * (P * M) * Dh, (P - 1) * M * 2 * H * Dh * 2, t_full)
+    out["ring_gather_attn"]["local_twin"] = "one attention launch over all P*M keys held locally"
+    ring.close()
 
     # ---- tp_row_reduce: MLP down-projection, K sharded over the ranks
     Kp = 4 * D // P

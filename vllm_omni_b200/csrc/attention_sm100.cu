@@ -69,7 +69,34 @@ struct AttnOut {
   int kv_splits;
   float* part_o;    // [.., kv_splits, 128]
   float* part_ml;   // [.., kv_splits, 2]
+  // Continuation of an attention over another set of keys (sequence-parallel K/V shards): with
+  // prev_o set, the epilogue blends this launch's normalised rows with the earlier result by their
+  // log-sum-exps, out = prev + sigmoid(lse - prev_lse) (this - prev), and stores the combined LSE.
+  // prev_o may alias o (every element is read and written by the same thread).
+  const __nv_bfloat16* prev_o;
+  const float* prev_lse;   // [B, H, Sq], natural-log units
+  long p_bs, p_rs, p_hs;
 };
+
+// C view of the continuation operands (all strides in elements)
+struct AttnPrev {
+  const void* o;
+  const float* lse;
+  long rs, hs, bs;
+};
+
+// eight accumulator values scaled by `sb`, plus eight earlier bf16 values scaled by `wp`
+__device__ __forceinline__ uint4 blend8(const uint32_t* v, float sb, uint4 pv, float wp) {
+  const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&pv);
+  uint4 o;
+  uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 pf = __bfloat1622float2(p2[j]);
+    ow[j] = pack_bf16(fmaf(__uint_as_float(v[2 * j]), sb, pf.x * wp), fmaf(__uint_as_float(v[2 * j + 1]), sb, pf.y * wp));
+  }
+  return o;
+}
 
 // Paged K/V: the tensor maps cover the page pool as [num_blocks * block_size, Hkv, 128] and token
 // t of batch row b lives in page block_table[b * bt_stride + t / block_size].
@@ -502,9 +529,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       } else {
-        const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-        if (srow < Sq && out.lse)
-          out.lse[((long)b * H + h) * Sq + srow] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        float inv_l = l > 0.f ? 1.0f / l : 0.f;
+        float lse_row = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        float wp = 0.f;                          // weight of the earlier result (continuation launches)
+        const __nv_bfloat16* prow = nullptr;
+        if (out.prev_o != nullptr && srow < Sq) {
+          const float lp = out.prev_lse[((long)b * H + h) * Sq + srow];
+          prow = out.prev_o + (long)b * out.p_bs + (long)srow * out.p_rs + (long)h * out.p_hs;
+          if (!(l > 0.f)) {                      // no key seen here: the earlier result stands
+            wp = 1.f;
+            lse_row = lp;
+          } else if (lp != -INFINITY) {
+            const float d = lse_row - lp;
+            const float wb = 1.0f / (1.0f + __expf(-d));
+            wp = 1.0f - wb;
+            inv_l *= wb;
+            lse_row = fmaxf(lse_row, lp) + log1pf(__expf(-fabsf(d)));
+          }
+        }
+        if (srow < Sq && out.lse) out.lse[((long)b * H + h) * Sq + srow] = lse_row;
         if (out.n_peers > 1) {
           // Fused exchange: rows go to their owner ranks over NVLink.  A store from the thread that
           // owns the row would put 32 separate 16-byte writes on the link per instruction, so the
@@ -529,10 +572,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 uint4 o;
-                o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
-                o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
-                o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
-                o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+                if (prow) {
+                  o = blend8(v + g * 8, inv_l, *reinterpret_cast<const uint4*>(prow + hf * 64 + c * 32 + g * 8), wp);
+                } else {
+                  o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+                  o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+                  o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+                  o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+                }
                 const int kk = c * 4 + g;
                 st_shared_v4(stg + lane * 128 + ((kk ^ (lane & 7)) << 4), o);
               }
@@ -580,10 +627,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 uint4 o;
-                o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
-                o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
-                o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
-                o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+                if (prow) {
+                  o = blend8(v + g * 8, inv_l, *reinterpret_cast<const uint4*>(prow + c * 32 + g * 8), wp);
+                } else {
+                  o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+                  o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+                  o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+                  o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
+                }
                 *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
               }
             }
@@ -681,6 +732,15 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
 // projections).  kv_lens: optional int32[B] valid key counts.  lse: optional fp32 [B,H,Sq].
 // `sync` (may be null): the arrival this launch reports to the group once its peer stores are out
 // (see peer_signal.cuh); only the signalling half is used.
+extern "C" int omni_attn_fwd_cont(const void* q, long q_rs, long q_hs, long q_bs, const void* k, long k_rs,
+                                  long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
+                                  void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
+                                  long o2_bs, int split, float* lse, int B, int H, int Hkv, int Sq, int Skv,
+                                  int D, const int* kv_lens, float scale, int causal, int q_offset, int n_peers,
+                                  int rows_per_rank,
+                                  int rows_per_rank2, void* const* o_peers, void* const* o2_peers,
+                                  const omni::AttnPrev* prev, const omni::OmniSync* sync, int* status, void* stream);
+
 extern "C" int omni_attn_fwd_sync(const void* q, long q_rs, long q_hs, long q_bs, const void* k, long k_rs,
                                   long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
                                   void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
@@ -689,8 +749,27 @@ extern "C" int omni_attn_fwd_sync(const void* q, long q_rs, long q_hs, long q_bs
                                   int rows_per_rank,
                                   int rows_per_rank2, void* const* o_peers, void* const* o2_peers,
                                   const omni::OmniSync* sync, int* status, void* stream) {
+  return omni_attn_fwd_cont(q, q_rs, q_hs, q_bs, k, k_rs, k_hs, k_bs, v, v_rs, v_hs, v_bs, o, o_rs, o_hs, o_bs, o2,
+                            o2_rs, o2_hs, o2_bs, split, lse, B, H, Hkv, Sq, Skv, D, kv_lens, scale, causal, q_offset,
+                            n_peers, rows_per_rank, rows_per_rank2, o_peers, o2_peers, nullptr, sync, status, stream);
+}
+
+// `prev` (may be null): result and LSE of an attention of the same queries over other keys; this
+// launch's output is the combination of both (see AttnOut::prev_o).  Needs `lse` when the caller
+// goes on combining.
+extern "C" int omni_attn_fwd_cont(const void* q, long q_rs, long q_hs, long q_bs, const void* k, long k_rs,
+                                  long k_hs, long k_bs, const void* v, long v_rs, long v_hs, long v_bs,
+                                  void* o, long o_rs, long o_hs, long o_bs, void* o2, long o2_rs, long o2_hs,
+                                  long o2_bs, int split, float* lse, int B, int H, int Hkv, int Sq, int Skv,
+                                  int D, const int* kv_lens, float scale, int causal, int q_offset, int n_peers,
+                                  int rows_per_rank,
+                                  int rows_per_rank2, void* const* o_peers, void* const* o2_peers,
+                                  const omni::AttnPrev* prev, const omni::OmniSync* sync, int* status, void* stream) {
   using namespace omni;
   if ((D != 64 && D != 128) || H <= 0 || Hkv <= 0 || (H % Hkv) || B <= 0) return RC_BAD_ARG;
+  if (prev && (prev->o == nullptr || prev->lse == nullptr || (prev->rs & 7) || (prev->hs & 7) || (prev->bs & 7) ||
+               (reinterpret_cast<uintptr_t>(prev->o) & 15)))
+    return RC_BAD_ARG;
   if (Sq <= 0) return RC_OK;
   if ((o_rs & 7) || (o_hs & 7) || (o_bs & 7) || (o2_rs & 7) || (o2_hs & 7) || (o2_bs & 7)) return RC_BAD_ARG;
   CUtensorMap tq, tk, tv;
@@ -717,6 +796,11 @@ extern "C" int omni_attn_fwd_sync(const void* q, long q_rs, long q_hs, long q_bs
     }
   }
   out.kv_splits = 1; out.part_o = nullptr; out.part_ml = nullptr;
+  out.prev_o = nullptr; out.prev_lse = nullptr; out.p_bs = out.p_rs = out.p_hs = 0;
+  if (prev) {
+    out.prev_o = static_cast<const __nv_bfloat16*>(prev->o); out.prev_lse = prev->lse;
+    out.p_rs = prev->rs; out.p_hs = prev->hs; out.p_bs = prev->bs;
+  }
   AttnPaging pg = {nullptr, 0, 0};
   return launch_attn(tq, tk, tv, out, B, H, Hkv, Sq, Skv, kv_lens, scale, causal, q_offset, pg, status,
                      (cudaStream_t)stream, sync, D);
@@ -774,6 +858,7 @@ extern "C" int omni_attn_fwd_paged(const void* q, long q_rs, long q_hs, long q_b
   for (int i = 0; i < 16; ++i) { out.o_peers[i] = nullptr; out.o2_peers[i] = nullptr; }
   out.kv_splits = kv_splits > 1 ? kv_splits : 1;
   out.part_o = part_o; out.part_ml = part_ml;
+  out.prev_o = nullptr; out.prev_lse = nullptr; out.p_bs = out.p_rs = out.p_hs = 0;
   AttnPaging pg = {block_table, bt_stride, block_size};
   cudaStream_t st = (cudaStream_t)stream;
   rc = launch_attn(tq, tk, tv, out, B, H, Hkv, Sq, max_kv, kv_lens, scale, causal, q_offset, pg, status, st);

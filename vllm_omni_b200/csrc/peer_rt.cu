@@ -73,9 +73,38 @@ peer_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t 
   if (blockIdx.x == 0 && (int)threadIdx.x < tail) dst_tail[threadIdx.x] = src_tail[threadIdx.x];
 }
 
+// Pitched copy: `rows` segments of `row16` 16-byte words each (K and V of every row of a packed
+// [rows, q | k | v] buffer, for example), either side may be a peer mapping.  A warp moves 512
+// contiguous bytes of one segment per instruction.
+__global__ void __launch_bounds__(256)
+peer_copy_2d_kernel(unsigned char* __restrict__ dst, size_t dst_pitch, const unsigned char* __restrict__ src, size_t src_pitch,
+                    int row16, long rows) {
+  const long total = rows * (long)row16;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / row16;
+    const int c = (int)(i - r * row16);
+    reinterpret_cast<uint4*>(dst + r * dst_pitch)[c] = reinterpret_cast<const uint4*>(src + r * src_pitch)[c];
+  }
+}
+
 }  // namespace omni
 
 using namespace omni;
+
+// Pitches and row_bytes in bytes, all multiples of 16; dst / src 16-byte aligned.
+extern "C" int omni_peer_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                                 long rows, void* stream) {
+  if (rows <= 0 || row_bytes == 0) return RC_OK;
+  if ((reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (dst_pitch & 15) ||
+      (src_pitch & 15) || (row_bytes & 15) || row_bytes > dst_pitch || row_bytes > src_pitch || (row_bytes >> 4) > 0x7fffffff)
+    return RC_BAD_ARG;
+  const long total = rows * (long)(row_bytes >> 4);
+  long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  peer_copy_2d_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      static_cast<unsigned char*>(dst), dst_pitch, static_cast<const unsigned char*>(src), src_pitch, (int)(row_bytes >> 4), rows);
+  return (int)cudaGetLastError();
+}
 
 // dst / src: device pointers (either may be a peer mapping), both 16-byte aligned.
 extern "C" int omni_peer_copy(void* dst, const void* src, size_t nbytes, void* stream) {

@@ -8,10 +8,12 @@ S / (U R) rows.  Per block:
 1. head <-> sequence all-to-all INSIDE the Ulysses group (the fused GEMM-epilogue scatter on
    GPUs): the rank now holds q, k, v of ring chunk r (S / R rows) for its H / U heads;
 2. attention of that chunk's queries against the keys of EVERY ring chunk: the R ranks of the ring
-   group publish their K/V in symmetric memory and each rank's attention kernel reads chunk
-   (r + step) mod R from its peer through TMA descriptors on the peer pointer (plain loads);
-   partial results are merged with their log-sum-exp, as in ring attention;
-3. the reverse all-to-all inside the Ulysses group gives the local rows all heads again.
+   group publish their K/V in symmetric memory; a side stream pulls the other chunks into one
+   local buffer with this library's copy kernel (each remote byte crosses NVLink once) while the
+   main stream attends to the own chunk; a second launch attends to the gathered chunks and
+   combines both results by their log-sum-exps in its epilogue;
+3. that same epilogue stores every output row into the Ulysses peer that owns it (the reverse
+   all-to-all), so the local rows have all heads again after one barrier.
 
 ``mode="nccl"`` does steps 1-3 with collectives and send/recv (baseline and CPU test path).
 """
@@ -26,7 +28,7 @@ from .ulysses import UlyssesJointAttention
 
 
 class HybridJointAttention:
-    graph_safe = False        # the reverse all-to-all is an NCCL call
+    graph_safe = False        # the NCCL baseline mode is not capturable; the peer mode would be
 
     def __init__(self, sp_group, num_heads: int, head_dim: int, mode: str | None = None):
         self.group = sp_group
@@ -42,6 +44,7 @@ class HybridJointAttention:
         self.H, self.Dh, self.Hp = num_heads, head_dim, num_heads // self.U
         self.arena = None
         self._key = None
+        self._side = self._gath = None
 
     def setup(self, B, Si_loc, St_loc, device, dtype):
         self.uly.setup(B, Si_loc, St_loc, device, dtype)
@@ -49,6 +52,7 @@ class HybridJointAttention:
         if self._key == key:
             return
         self._key = key
+        self._side = self._gath = None
         self.B, self.Si_loc, self.St_loc = B, Si_loc, St_loc
         self.Si_c, self.St_c = Si_loc * self.U, St_loc * self.U          # rows of one ring chunk
         self.S_c = self.Si_c + self.St_c
@@ -84,16 +88,46 @@ class HybridJointAttention:
         q = q5[:, :, 0]
         out = lse = None
         if self.mode == "peer":
-            from .peer_memory import tensor_from_ptr
+            from .peer_memory import pull_rows
+            R, r, Sc = self.R, self.r, self.S_c
+            dev = q.device
             self.kv.local.copy_(q5[:, :, 1:3])
             self.arena.barrier()                                  # every chunk's K/V is published
-            for step in range(self.R):
-                src = (self.r + step) % self.R
-                kv = tensor_from_ptr(self.kv.ptrs[src], (B, self.S_c, 2, self.Hp, self.Dh), q.dtype, q.device)
-                o_b, lse_b = attention(q, kv[:, :, 0], kv[:, :, 1], kv_lens=self._chunk_kv_lens(kv_lens, src),
-                                       return_lse=True)
-                out, lse = merge_attention(out, lse, o_b, lse_b)
+            sc = self.uly._attn_scatter                           # rows go to their owner inside the Ulysses group
+            if R == 1:
+                attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._chunk_kv_lens(kv_lens, r), scatter=sc)
+            else:
+                main = torch.cuda.current_stream(dev)
+                if self._side is None:
+                    self._side = torch.cuda.Stream(dev)
+                    # the other chunks' image rows in ring order, then their text rows: valid keys stay a prefix
+                    self._gath = torch.empty(B, (R - 1) * Sc, 2 * self.Hp * self.Dh, dtype=q.dtype, device=dev)
+                    self._own = torch.empty(B, Sc, self.Hp, self.Dh, dtype=q.dtype, device=dev)
+                    self._others = [c for c in range(R) if c != r]
+                    self._others_t = torch.tensor(self._others, device=dev, dtype=torch.int32)
+                row = 2 * self.Hp * self.Dh
+                es = q.element_size()
+                self._side.wait_stream(main)
+                with torch.cuda.stream(self._side):
+                    for j, src in enumerate(self._others):
+                        for b in range(B):
+                            base = self.kv.ptrs[src] + b * Sc * row * es
+                            pull_rows(self._gath[b, j * self.Si_c:(j + 1) * self.Si_c], base, row * es)
+                            if self.St_c:
+                                t0 = (R - 1) * self.Si_c + j * self.St_c
+                                pull_rows(self._gath[b, t0:t0 + self.St_c], base + self.Si_c * row * es, row * es)
+                _, lse0 = attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._chunk_kv_lens(kv_lens, r), return_lse=True,
+                                    out=self._own)
+                main.wait_stream(self._side)
+                g5 = self._gath.view(B, (R - 1) * Sc, 2, self.Hp, self.Dh)
+                rem = None
+                if kv_lens is not None:
+                    txt = (kv_lens[:, None] - self.S_img - self._others_t[None] * self.St_c).clamp(0, self.St_c).sum(dim=1)
+                    rem = ((R - 1) * self.Si_c + txt).to(torch.int32)
+                attention(q, g5[:, :, 0], g5[:, :, 1], kv_lens=rem, merge_prev=(self._own, lse0), scatter=sc)
             self.arena.barrier()                                  # published K/V may be overwritten
+            self.uly.arena.barrier()                              # every owner has its rows
+            return self.uly.attn_img.local, self.uly.attn_txt.local
         else:
             comm = RingComm(self.group.ring.device_group)
             k, v = q5[:, :, 1].contiguous(), q5[:, :, 2].contiguous()

@@ -41,6 +41,19 @@ def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device: torch.device, o
     return raw[:nbytes].view(dtype).view(*shape)
 
 
+def pull_rows(dst: torch.Tensor, src_ptr: int, src_pitch_bytes: int) -> None:
+    """Copy ``dst.shape[0]`` row segments of ``dst.shape[1]`` elements from (peer) memory at ``src_ptr``
+    (segment r starts ``r * src_pitch_bytes`` further) into the 2-D view ``dst`` (unit inner stride),
+    with this library's own copy kernel on the current stream: a remote tile that several CTAs are
+    going to read crosses NVLink once."""
+    assert dst.dim() == 2 and dst.stride(1) == 1 and dst.is_cuda
+    es = dst.element_size()
+    rc = nv.lib("peer_rt").omni_peer_copy_2d(
+        ctypes.c_void_p(dst.data_ptr()), ctypes.c_size_t(dst.stride(0) * es), ctypes.c_void_p(src_ptr),
+        ctypes.c_size_t(src_pitch_bytes), ctypes.c_size_t(dst.shape[1] * es), ctypes.c_long(dst.shape[0]), nv.stream_ptr())
+    nv.check_rc(rc, "omni_peer_copy_2d")
+
+
 class SymTensor:
     """A symmetric allocation: the local tensor and the device pointer of its twin on every rank."""
 

@@ -6,10 +6,14 @@ sequence = merge of P partial attentions, one per K/V shard:
 (the update rule of vllm_omni/diffusion/attention/backends/ring/ring_utils.py:79-80).
 
 ``mode="peer"`` (GPU): every rank publishes its K/V shard in symmetric peer memory once per
-layer; behind NVSwitch there is no ring to walk — each rank's attention kernel reads the
-shard of rank (r + step) mod P straight from that peer through TMA descriptors built on the
-peer pointer (plain, non-multicast loads), one kernel launch per shard, LSE-merged.  One
-bounded-wait barrier before (shards written) and one after (shards consumed) per layer.
+layer; behind NVSwitch there is no ring to walk.  A side stream pulls the K/V of ALL other ranks
+into one local buffer with this library's copy kernel (each remote byte crosses NVLink once;
+reading the peer's tiles straight from the attention kernel makes every query-tile CTA fetch them
+again: 354 us against 107 us with local K/V at 2048 rows x 24 heads on two B200s), while the main
+stream attends to the local shard.  A second launch attends to the gathered remote keys and its
+epilogue combines both results by their log-sum-exps (``attention(..., merge_prev=...)``): two
+launches per layer whatever the degree, and no merge kernels.  One bounded-wait barrier before
+(shards written) and one after (shards consumed) per layer.
 ``mode="nccl"``: classic ring with batched isend/irecv of K and V (the baseline; also the CPU
 test path).
 """
@@ -41,12 +45,14 @@ class RingJointAttention:
         self.mode = mode or ("peer" if torch.cuda.is_available() else "nccl")
         self.arena = None
         self._key = None
+        self._side = self._gath = None
 
     def setup(self, B, Si_loc, St_loc, device, dtype):
         key = (B, Si_loc, St_loc, str(device), dtype)
         if self._key == key:
             return
         self._key = key
+        self._side = self._gath = None
         self.B, self.Si_loc, self.St_loc = B, Si_loc, St_loc
         self.S_loc = Si_loc + St_loc
         self.S_img, self.S_txt = Si_loc * self.P, St_loc * self.P
@@ -93,16 +99,43 @@ class RingJointAttention:
         q = q5[:, :, 0]
         out = lse = None
         if self.mode == "peer":
-            from .peer_memory import tensor_from_ptr
+            from .peer_memory import pull_rows
+            P, r, Si, St = self.P, self.rank, self.Si_loc, self.St_loc
+            dev, dt = self.qkv_local.device, self.qkv_local.dtype
+            es = self.qkv_local.element_size()
+            o4 = self.attn.view(B, self.S_loc, self.H, self.Dh)
             self.arena.barrier()                                  # every rank's K/V shard is in place
-            for step in range(self.P):
-                src = (self.rank + step) % self.P
-                kv = tensor_from_ptr(self.qkv.ptrs[src], (B, self.S_loc, 3, self.H, self.Dh), self.qkv_local.dtype,
-                                     self.qkv_local.device)
-                o_b, lse_b = attention(q, kv[:, :, 1], kv[:, :, 2], kv_lens=self._shard_kv_lens(kv_lens, src),
-                                       return_lse=True)
-                out, lse = merge_attention(out, lse, o_b, lse_b)
+            if P == 1:
+                attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._shard_kv_lens(kv_lens, r), out=o4)
+            else:
+                main = torch.cuda.current_stream(dev)
+                if self._side is None:
+                    self._side = torch.cuda.Stream(dev)
+                    # remote rows: the image rows of the other ranks in rank order, then their text rows, so
+                    # that the valid keys (text is padded at the end of the global text) stay a prefix
+                    self._gath = torch.empty(B, (P - 1) * self.S_loc, 2 * HD, dtype=dt, device=dev)
+                    self._others = [s for s in range(P) if s != r]
+                    self._others_t = torch.tensor(self._others, device=dev, dtype=torch.int32)
+                self._side.wait_stream(main)
+                with torch.cuda.stream(self._side):
+                    pitch = 3 * HD * es
+                    for j, src in enumerate(self._others):
+                        for b in range(B):
+                            base = self.qkv.ptrs[src] + ((b * self.S_loc) * 3 * HD + HD) * es
+                            pull_rows(self._gath[b, j * Si:(j + 1) * Si], base, pitch)
+                            if St:
+                                t0 = (P - 1) * Si + j * St
+                                pull_rows(self._gath[b, t0:t0 + St], base + Si * pitch, pitch)
+                _, lse0 = attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._shard_kv_lens(kv_lens, r), return_lse=True, out=o4)
+                main.wait_stream(self._side)
+                g5 = self._gath.view(B, (P - 1) * self.S_loc, 2, self.H, self.Dh)
+                rem_lens = None
+                if kv_lens is not None:
+                    txt = (kv_lens[:, None] - self.S_img - self._others_t[None] * St).clamp(0, St).sum(dim=1)
+                    rem_lens = ((P - 1) * Si + txt).to(torch.int32)
+                attention(q, g5[:, :, 0], g5[:, :, 1], kv_lens=rem_lens, merge_prev=(o4, lse0), out=o4)
             self.arena.barrier()                                  # shards may be overwritten by the next layer
+            return self.attn[:, :self.Si_loc], self.attn[:, self.Si_loc:]
         else:
             comm = RingComm(self.group.device_group)
             k, v = q5[:, :, 1].contiguous(), q5[:, :, 2].contiguous()

@@ -6,9 +6,10 @@ normalised and rotated with the rows' own positions) and returns the local ``[B,
 attention output over the FULL sequence:
 
 * Ulysses degree U: head <-> sequence all-to-all inside the Ulysses group before and after;
-* ring degree R: the chunk's queries against every ring chunk's K/V — peer-KV reads through TMA
-  descriptors on the peer pointer (``mode="peer"``) or send/recv (``mode="nccl"``) — merged by
-  log-sum-exp;
+* ring degree R: the chunk's queries against every ring chunk's K/V — ``mode="peer"``: the other
+  chunks are pulled once into a local buffer by this library's copy kernel on a side stream while
+  the own chunk is attended to, and a second launch combines both results by their log-sum-exps in
+  its epilogue; ``mode="nccl"``: send/recv around the ring with an eager merge (baseline, CPU);
 * both: the hybrid grid of vllm_omni/diffusion/distributed/parallel_state.py:477-621.
 
 ``valid_len`` masks padding rows at the end of the global sequence (a model pads S up to a multiple
@@ -37,6 +38,7 @@ class SequenceParallelAttention:
         self.mode = mode or ("peer" if torch.cuda.is_available() else "nccl")
         self.arena = None
         self._key = None
+        self._gath = self._own = self._side = None
 
     # rows ------------------------------------------------------------------------------
     def shard_rows(self, x: torch.Tensor, dim: int = 1):
@@ -97,17 +99,37 @@ class SequenceParallelAttention:
                 raise ValueError("padding may not cover a whole ring chunk")
             out = lse = None
             if self.mode == "peer" and q5.is_cuda:
-                from .peer_memory import tensor_from_ptr
-                shape = (B, S_c, 2, q5.shape[3], self.Dh)
+                # the other ring chunks' K/V are pulled once into a local buffer (side stream) while the own
+                # chunk is attended to; the second launch combines both results in its epilogue
+                from .peer_memory import pull_rows
+                R, r = self.R, self.r
+                Hu = q5.shape[3]
+                shape = (B, S_c, 2, Hu, self.Dh)
                 self._setup_arena(shape, q5.dtype, dev)
                 self.kv.local.copy_(q5[:, :, 1:3])
                 self.arena.barrier()
-                for step in range(self.R):
-                    src = (self.r + step) % self.R
-                    kv = tensor_from_ptr(self.kv.ptrs[src], shape, q5.dtype, dev)
-                    o_b, lse_b = attention(q, kv[:, :, 0], kv[:, :, 1], scale=scale, return_lse=True,
-                                           kv_lens=self._chunk_lens(valid_len, src, S_c, B, dev))
-                    out, lse = merge_attention(out, lse, o_b, lse_b)
+                chunk = S_c * 2 * Hu * self.Dh
+                es = q5.element_size()
+                if self._gath is None or self._gath.shape != (B, (R - 1) * chunk):
+                    self._gath = torch.empty(B, (R - 1) * chunk, dtype=q5.dtype, device=dev)
+                    self._own = torch.empty(B, S_c, Hu, self.Dh, dtype=q5.dtype, device=dev)
+                    self._side = self._side or torch.cuda.Stream(dev)
+                others = [c for c in range(R) if c != r]
+                main = torch.cuda.current_stream(dev)
+                self._side.wait_stream(main)
+                with torch.cuda.stream(self._side):
+                    for j, src in enumerate(others):                       # one launch per chunk: a row per batch
+                        pull_rows(self._gath[:, j * chunk:(j + 1) * chunk], self.kv.ptrs[src], chunk * es)
+                _, lse0 = attention(q, k, v, scale=scale, return_lse=True, out=self._own,
+                                    kv_lens=self._chunk_lens(valid_len, r, S_c, B, dev))
+                main.wait_stream(self._side)
+                g5 = self._gath.view(B, (R - 1) * S_c, 2, Hu, self.Dh)
+                rem = None
+                if valid_len is not None:                                   # padding sits at the end of the LAST chunk
+                    lens = [self._chunk_lens(valid_len, c, S_c, B, dev) for c in others]
+                    rem = torch.stack(lens).sum(dim=0).to(torch.int32)
+                out = attention(q, g5[:, :, 0], g5[:, :, 1], scale=scale, kv_lens=rem, merge_prev=(self._own, lse0),
+                                out=self._own)
                 self.arena.barrier()
             else:
                 comm = RingComm(self.group.ring.device_group)
