@@ -121,3 +121,23 @@ def test_flux_tensor_parallel_matches_single_process():
             omni.close()
     a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(tensor_parallel_size=2))
     assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4
+
+
+def test_wan_tensor_parallel_matches_single_process():
+    """Wan with heads / FFN columns over two ranks; the q / k RMSNorms span all heads, so their mean
+    squares are summed across the ranks."""
+    tf = dict(num_attention_heads=2, attention_head_dim=24, text_dim=32, ffn_dim=64, num_layers=2)
+
+    def run(par):
+        omni = Omni("WanPipeline", dtype="float32", device="cpu", tf_model_config=tf, vae_config=dict(base_dim=8, num_res_blocks=1),
+                    diffusion_load_format="dummy", parallel_config=par, output_type="latent")
+        try:
+            sp = OmniDiffusionSamplingParams(height=32, width=32, num_frames=5, num_inference_steps=2, guidance_scale=3.0, seed=0,
+                                             output_type="latent")
+            out = omni.generate([{"prompt": "a cube", "negative_prompt": "blurry"}], sp)[0]
+            lat = out.latents if out.latents is not None else out.multimodal_output.get("video")
+            return torch.as_tensor(lat).float()
+        finally:
+            omni.close()
+    a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(tensor_parallel_size=2))
+    assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4

@@ -73,12 +73,20 @@ struct GemmEpilogue {
 // blocks of 64.  The A tile of one (tap, channel block) is ONE 4-D TMA box
 // {64 channels, CONV_BW, CONV_BH, 1 image} of the input, shifted by the tap's offset; pixels
 // outside the image are filled with zeros by TMA, which is the padding.  taps == 0: plain GEMM.
+//
+// One-dimensional mode (one_d, vocoder stacks, channels-last [B, T, C]): the M dimension is the
+// output time steps in runs of 128; tap j of a kernel of `taps` taps reads the input `j * dil - pad`
+// steps away, so the A tile of one (tap, channel block) is the box {64 channels, 128 steps} shifted by
+// that offset, and both paddings (causal left, "same", the ragged end) are TMA's zero fill.  A
+// transposed convolution of stride r is the same kernel on weights stacked by output phase: its
+// [B, Tq, r * Cout] result read as [B, Tq * r, Cout].
 constexpr int CONV_BW = 16, CONV_BH = 8;
 struct ConvGeom {
-  int taps;        // 0 (GEMM), 1 (1x1) or 9 (3x3)
-  int H, W;        // output (= input) height and width
+  int taps;        // 0 (GEMM); 2-D: 1 (1x1) or 9 (3x3); 1-D: kernel size
+  int H, W;        // output (= input) height and width; 1-D: H = 1, W = output steps
   int tiles_x, tiles_y;
   int cin_blocks;  // ceil(Cin / 64); the weight matrix is [Cout, taps * cin_blocks * 64]
+  int one_d, dil, pad;
 };
 
 template <int BN>
@@ -286,8 +294,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int img = mb / per_img, rem = mb - img * per_img;
             const int y0 = (rem / conv.tiles_x) * CONV_BH, x0 = (rem % conv.tiles_x) * CONV_BW;
             const int tap = kb / conv.cin_blocks, cb = kb - tap * conv.cin_blocks;
-            const int dy = conv.taps == 9 ? tap / 3 - 1 : 0, dx = conv.taps == 9 ? tap % 3 - 1 : 0;
-            tma_load_4d(sa, &tmA, fb, cb * BK, x0 + dx, y0 + dy, img);
+            if (conv.one_d) {
+              tma_load_4d(sa, &tmA, fb, cb * BK, rem * BM + tap * conv.dil - conv.pad, 0, img);
+            } else {
+              const int dy = conv.taps == 9 ? tap / 3 - 1 : 0, dx = conv.taps == 9 ? tap % 3 - 1 : 0;
+              tma_load_4d(sa, &tmA, fb, cb * BK, x0 + dx, y0 + dy, img);
+            }
           } else {
             tma_load_2d(sa, &tmA, fb, kb * BK, mb * BM);
           }
@@ -353,7 +365,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int per_img = conv.tiles_x * conv.tiles_y;
         const int img = mb / per_img, rem = mb - img * per_img;
         const int r = q * 32 + lane;
-        const int y = (rem / conv.tiles_x) * CONV_BH + r / CONV_BW, x = (rem % conv.tiles_x) * CONV_BW + r % CONV_BW;
+        int y = (rem / conv.tiles_x) * CONV_BH + r / CONV_BW, x = (rem % conv.tiles_x) * CONV_BW + r % CONV_BW;
+        if (conv.one_d) { y = 0; x = rem * BM + r; }
         row_ok = y < conv.H && x < conv.W;
         row = (img * conv.H + y) * conv.W + x;
       }
@@ -1073,6 +1086,57 @@ extern "C" int omni_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
                              force_bn, nullptr, status, stream);
 }
 
+// One-dimensional convolution, stride 1, channels-last bf16:
+//   y[b, t, :] = act(sum_j x[b, t + j * dil - pad, :] W_j^T + bias) (+ residual),  t in [0, T_out)
+// x: [B, T_in, Cin] with step pitch ldx (elements, multiple of 8) and batch pitch x_bs; inputs outside [0, T_in)
+// read as zero.  w: [Cout, k * cin_pad], tap-major, cin_pad = ceil(Cin / 64) * 64, zero in the padding
+// columns.  y / residual: rows b * T_out + t with pitch ldy / ldr.
+extern "C" int omni_conv1d_nlc_bf16(const void* x, long ldx, long x_bs, const void* w, void* y, int ldy, int B, int T_in,
+                                    int T_out, int Cin, int Cout, int k, int dil, int pad, const void* bias,
+                                    const void* residual, int ldr, int act, int* status, void* stream) {
+  using namespace omni;
+  if (B <= 0 || T_in <= 0 || T_out <= 0 || Cin <= 0 || Cout <= 0) return RC_OK;
+  if (k < 1 || k > 64 || dil < 1 || (Cout & 7) || (ldx & 7) || (x_bs & 7) || (ldy & 7) || (ldr & 7)) return RC_BAD_ARG;
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return RC_NO_DRIVER;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return RC_BAD_ARG;
+  ConvGeom g = {};
+  g.taps = k;
+  g.H = 1; g.W = T_out;
+  g.tiles_x = (T_out + BM - 1) / BM;
+  g.tiles_y = 1;
+  g.cin_blocks = (Cin + BK - 1) / BK;
+  g.one_d = 1; g.dil = dil; g.pad = pad;
+  CUtensorMap tmA;
+  {
+    cuuint64_t gdim[4] = {(cuuint64_t)Cin, (cuuint64_t)T_in, 1, (cuuint64_t)B};
+    cuuint64_t gstr[3] = {(cuuint64_t)ldx * 2, (cuuint64_t)ldx * 2 * T_in, (cuuint64_t)x_bs * 2};
+    cuuint32_t box[4] = {BK, BM, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(x), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return RC_TMAP;
+  }
+  GemmEpilogue epi = {};
+  epi.bias = static_cast<const __nv_bfloat16*>(bias);
+  epi.residual = static_cast<const __nv_bfloat16*>(residual);
+  epi.ldr = ldr;
+  epi.rows_per_batch = 1;
+  epi.act = act;
+  const int K = g.taps * g.cin_blocks * BK;
+  const int M = B * g.tiles_x * BM;
+  const int ctas = sm_count();
+  const int bn = pick_bn(M, Cout, ctas);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* c = static_cast<__nv_bfloat16*>(y);
+  switch (bn) {
+    case 256: return launch_gemm<256>(tmA, w, c, ldy, M, Cout, K, K, epi, status, ctas, s, 1, nullptr, &g);
+    case 192: return launch_gemm<192>(tmA, w, c, ldy, M, Cout, K, K, epi, status, ctas, s, 1, nullptr, &g);
+    default: return launch_gemm<128>(tmA, w, c, ldy, M, Cout, K, K, epi, status, ctas, s, 1, nullptr, &g);
+  }
+}
+
 // Two linear layers of the same shape (N, K) in one launch of the CTA-pair kernel: the image and
 // text streams of a dual-stream DiT block.  Each descriptor carries its own activations, weights,
 // output mapping and epilogue operands.  Falls back to two launches when the pair kernel does not
@@ -1197,7 +1261,7 @@ extern "C" int omni_conv2d_nhwc_bf16(const void* x, long ldx, const void* w, voi
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return RC_NO_DRIVER;
   if (reinterpret_cast<uintptr_t>(x) & 15) return RC_BAD_ARG;
-  ConvGeom g;
+  ConvGeom g = {};
   g.taps = ksize * ksize;
   g.H = H; g.W = W;
   g.tiles_x = (W + CONV_BW - 1) / CONV_BW;

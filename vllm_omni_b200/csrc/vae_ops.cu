@@ -114,6 +114,66 @@ static unsigned grid_for(long total) {
   return (unsigned)(b < 1 ? 1 : b);
 }
 
+// Snake activation of the vocoders, channels-last: y = x + inv_b[c] * sin^2(x * a[c]) with per-channel
+// a = exp(alpha) and inv_b = 1 / (exp(beta) + 1e-9) computed by the caller (fp32, [C]).  One thread per
+// 8 channels (16-byte load and store); C is a multiple of 8, rows have pitch ldx / ldy elements.
+__global__ void __launch_bounds__(256)
+snake_nlc_kernel(const __nv_bfloat16* __restrict__ x, long ldx, const float* __restrict__ a, const float* __restrict__ inv_b,
+                 __nv_bfloat16* __restrict__ y, long ldy, long rows, int C8) {
+  const long total = rows * C8;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / C8;
+    const int c = (int)(i - r * C8) * 8;
+    const uint4 v = *reinterpret_cast<const uint4*>(x + r * ldx + c);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    uint4 o;
+    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(p[j]);
+      const float s0 = sinf(f.x * a[c + 2 * j]), s1 = sinf(f.y * a[c + 2 * j + 1]);
+      q[j] = __floats2bfloat162_rn(fmaf(inv_b[c + 2 * j] * s0, s0, f.x), fmaf(inv_b[c + 2 * j + 1] * s1, s1, f.y));
+    }
+    *reinterpret_cast<uint4*>(y + r * ldy + c) = o;
+  }
+}
+
+// Depthwise convolution over time, channels-last (the ConvNeXt blocks of the vocoders):
+// y[b, t, c] = bias[c] + sum_j x[b, t + j * dil - pad, c] * w[j, c]; one thread per 8 channels of one step.
+__global__ void __launch_bounds__(256)
+dwconv1d_nlc_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                    __nv_bfloat16* __restrict__ y, int B, int T, int C8, int k, int dil, int pad) {
+  const long total = (long)B * T * C8;
+  const int C = C8 * 8;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8) * 8;
+    const long bt = i / C8;
+    const int t = (int)(bt % T);
+    const long b = bt / T;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int ti = t + j * dil - pad;
+      if (ti < 0 || ti >= T) continue;
+      const uint4 v = *reinterpret_cast<const uint4*>(x + ((b * T + ti) * (long)C + c));
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const float* wj = w + (long)j * C + c;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p[e]);
+        acc[2 * e] = fmaf(f.x, wj[2 * e], acc[2 * e]);
+        acc[2 * e + 1] = fmaf(f.y, wj[2 * e + 1], acc[2 * e + 1]);
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) q[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    *reinterpret_cast<uint4*>(y + ((b * T + t) * (long)C + c)) = o;
+  }
+}
+
 }  // namespace omni
 
 using namespace omni;
@@ -152,5 +212,30 @@ extern "C" int omni_nhwc_to_image(const void* x, long ldx, void* out, int N, int
   const long pixels = (long)N * H * W;
   nhwc_to_image_kernel<<<grid_for(pixels), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, out, pixels,
                                                                          (long)H * W, mode);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int omni_snake_nlc(const void* x, long ldx, const float* a, const float* inv_b, void* y, long ldy, long rows, int C,
+                              void* stream) {
+  if (rows <= 0 || C <= 0) return omni::RC_OK;
+  if ((C & 7) || (ldx & 7) || (ldy & 7)) return omni::RC_BAD_ARG;
+  const long total = rows * (C / 8);
+  long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  omni::snake_nlc_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, ldx, a, inv_b, (__nv_bfloat16*)y, ldy, rows, C / 8);
+  return (int)cudaGetLastError();
+}
+
+// x, y: contiguous [B, T, C] bf16, C a multiple of 8; w: fp32 [k, C]; bias: fp32 [C] or null.
+extern "C" int omni_dwconv1d_nlc(const void* x, const float* w, const float* bias, void* y, int B, int T, int C, int k,
+                                 int dil, int pad, void* stream) {
+  if (B <= 0 || T <= 0 || C <= 0) return omni::RC_OK;
+  if ((C & 7) || k < 1 || dil < 1) return omni::RC_BAD_ARG;
+  const long total = (long)B * T * (C / 8);
+  long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  omni::dwconv1d_nlc_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, w, bias, (__nv_bfloat16*)y, B, T, C / 8, k, dil, pad);
   return (int)cudaGetLastError();
 }

@@ -98,11 +98,77 @@ class WanTransformer3DModel(nn.Module):
         self.blocks = nn.ModuleList([WanBlock(cfg, dtype, device) for _ in range(cfg.num_layers)])
         self.out_table = nn.Parameter(torch.randn(2, D, dtype=dtype, device=device) / D ** 0.5, requires_grad=False)
         self.proj_out = FusedLinear(D, cfg.out_channels * pt * ph * pw, dtype=dtype, device=device)
+        self.tp_group = self.tp_reduce = None      # tensor parallelism: heads and FFN columns split over the group
         self.sp = None                   # SequenceParallelAttention when the sequence is sharded
         self.sp_style = "attention"
         self._sp_valid_len = None
         self.stack_hook = None            # cache backends: called once per step with a BlockStack over the blocks
         self._rope = {}
+
+    # -------------------------------------------------------------- tensor parallelism
+    def enable_tensor_parallel(self, group, mode: str | None = None) -> None:
+        """Heads of both attentions and the FFN columns are split over ``group``; the three output
+        projections become row-parallel (partial sums finished by ``RowParallelReduce``, with the
+        AdaLN gate and the residual applied once by the reduce).  The q / k RMSNorms of Wan run over ALL
+        heads' channels, so each rank norms its slice with the mean square summed over the group: one
+        small all-reduce of per-row sums for q and k together (the reference's ``DistributedRMSNorm``,
+        vllm_omni/diffusion/models/wan2_2/wan2_2_transformer.py)."""
+        from ....parallel.tensor_parallel import RowParallelReduce
+        n, r = group.world_size, group.rank_in_group
+        if n == 1:
+            return
+        cfg = self.cfg
+        D, H = cfg.inner_dim, cfg.num_attention_heads
+        if H % n or cfg.ffn_dim % n:
+            raise ValueError(f"heads ({H}) and ffn_dim ({cfg.ffn_dim}) must be divisible by tensor_parallel_size ({n})")
+        Dl, Fl = D // n, cfg.ffn_dim // n
+
+        def cols(lin, parts):           # keep this rank's slice of each of the `parts` equal row groups of the weight
+            w, b = lin.weight.data, (lin.bias.data if lin.bias is not None else None)
+            per = w.shape[0] // parts
+            sl = per // n
+            idx = torch.cat([torch.arange(g * per + r * sl, g * per + (r + 1) * sl) for g in range(parts)]).to(w.device)
+            new = FusedLinear(w.shape[1], idx.numel(), bias=b is not None, dtype=w.dtype, device=w.device)
+            new.weight.data.copy_(w[idx])
+            if b is not None:
+                new.bias.data.copy_(b[idx])
+            return new
+
+        def rows(lin, width):           # keep this rank's input features; the bias is added once, by the reduce
+            w = lin.weight.data
+            new = FusedLinear(width, w.shape[0], bias=False, dtype=w.dtype, device=w.device)
+            new.weight.data.copy_(w[:, r * width:(r + 1) * width])
+            new.full_bias = lin.bias.data.clone() if lin.bias is not None else None
+            return new
+        sl = slice(r * Dl, (r + 1) * Dl)
+        for blk in self.blocks:
+            blk.attn1_qkv, blk.attn1_out = cols(blk.attn1_qkv, 3), rows(blk.attn1_out, Dl)
+            blk.attn2_q, blk.attn2_kv, blk.attn2_out = cols(blk.attn2_q, 1), cols(blk.attn2_kv, 2), rows(blk.attn2_out, Dl)
+            blk.ffn_up, blk.ffn_down = cols(blk.ffn_up, 1), rows(blk.ffn_down, Fl)
+            for nm in ("attn1_norm_q", "attn1_norm_k", "attn2_norm_q", "attn2_norm_k"):
+                setattr(blk, nm, nn.Parameter(getattr(blk, nm).data[sl].clone(), requires_grad=False))
+        self.tp_group, self.tp_reduce = group, RowParallelReduce(group, mode)
+
+    def _rms_across_ranks(self, parts, weights):
+        """RMSNorm of tensors whose channel dimension is split over the TP group: ``parts`` are this rank's
+        [.., D/P] slices; their mean squares are summed over the group in one all-reduce."""
+        D, eps = self.cfg.inner_dim, self.cfg.eps
+        ss = [p.float().pow(2).sum(-1, keepdim=True) for p in parts]
+        flat = torch.cat([t.reshape(-1) for t in ss])
+        self.tp_group.all_reduce(flat)
+        out, o = [], 0
+        for p, t, w in zip(parts, ss, weights):
+            tot = flat[o:o + t.numel()].view_as(t)
+            o += t.numel()
+            out.append((p.float() * torch.rsqrt(tot / D + eps) * w.float()).to(p.dtype))
+        return out
+
+    def _row_out(self, lin, a, x, gate=None):
+        """x += gate * (lin(a) summed over the TP group + bias)."""
+        if self.tp_reduce is None:
+            lin(a, residual=x, gate=gate, out=x)
+        else:
+            self.tp_reduce.linear(lin, a, bias=getattr(lin, "full_bias", None), gate=gate, residual=x, out=x)
 
     # -------------------------------------------------------------- patchify
     def patchify(self, x):          # [B, C, T, H, W] -> [B, S, C*pt*ph*pw], grid
@@ -134,27 +200,38 @@ class WanTransformer3DModel(nn.Module):
         B, S, _ = x.shape
         mod = (blk.scale_shift_table[None].float() + e6.float()).to(x.dtype).reshape(B, 6 * D)
         xn = fused.norm_modulate(x, shift=mod[:, 0:D], scale=mod[:, D:2 * D], eps=cfg.eps)
-        qkv = blk.attn1_qkv(xn)                                              # [B,S,3D]
-        q = fused.norm_modulate(qkv[..., :D].contiguous(), weight=blk.attn1_norm_q, rms=True, eps=cfg.eps)
-        k = fused.norm_modulate(qkv[..., D:2 * D].contiguous(), weight=blk.attn1_norm_k, rms=True, eps=cfg.eps)
-        qk = torch.cat([q, k, qkv[..., 2 * D:]], dim=-1).contiguous()
+        tp = self.tp_group is not None
+        if tp:
+            H = H // self.tp_group.world_size
+        Dl = H * Dh                                                           # this rank's attention width
+        qkv = blk.attn1_qkv(xn)                                              # [B,S,3*Dl]
+        if tp:
+            q, k = self._rms_across_ranks([qkv[..., :Dl], qkv[..., Dl:2 * Dl]], [blk.attn1_norm_q, blk.attn1_norm_k])
+        else:
+            q = fused.norm_modulate(qkv[..., :D].contiguous(), weight=blk.attn1_norm_q, rms=True, eps=cfg.eps)
+            k = fused.norm_modulate(qkv[..., D:2 * D].contiguous(), weight=blk.attn1_norm_k, rms=True, eps=cfg.eps)
+        qk = torch.cat([q, k, qkv[..., 2 * Dl:]], dim=-1).contiguous()
         fused.qk_norm_rope_(qk, H, H, Dh, cos=cos, sin=sin, interleaved=True, eps=cfg.eps)
         q5 = qk.view(B, S, 3, H, Dh)
         if self.sp is not None:
             # sequence parallel: x holds this rank's rows; only self-attention sees the other ranks
-            o = self.sp(q5, valid_len=self._sp_valid_len).reshape(B, S, D)
+            o = self.sp(q5, valid_len=self._sp_valid_len).reshape(B, S, Dl)
         else:
-            o = attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2]).reshape(B, S, D)
-        blk.attn1_out(o, residual=x, gate=mod[:, 2 * D:3 * D], out=x)
+            o = attention(q5[:, :, 0], q5[:, :, 1], q5[:, :, 2]).reshape(B, S, Dl)
+        self._row_out(blk.attn1_out, o, x, gate=mod[:, 2 * D:3 * D])
         xn = fused.norm_modulate(x, weight=blk.norm2_w, bias=blk.norm2_b, eps=cfg.eps)
-        q = fused.norm_modulate(blk.attn2_q(xn), weight=blk.attn2_norm_q, rms=True, eps=cfg.eps)
         kv = blk.attn2_kv(ctx)
         L = ctx.shape[1]
-        k2 = fused.norm_modulate(kv[..., :D].contiguous(), weight=blk.attn2_norm_k, rms=True, eps=cfg.eps)
-        o = attention(q.view(B, S, H, Dh), k2.view(B, L, H, Dh), kv[..., D:].reshape(B, L, H, Dh)).reshape(B, S, D)
-        blk.attn2_out(o, residual=x, out=x)
+        if tp:
+            q, = self._rms_across_ranks([blk.attn2_q(xn)], [blk.attn2_norm_q])
+            k2, = self._rms_across_ranks([kv[..., :Dl]], [blk.attn2_norm_k])
+        else:
+            q = fused.norm_modulate(blk.attn2_q(xn), weight=blk.attn2_norm_q, rms=True, eps=cfg.eps)
+            k2 = fused.norm_modulate(kv[..., :D].contiguous(), weight=blk.attn2_norm_k, rms=True, eps=cfg.eps)
+        o = attention(q.reshape(B, S, H, Dh), k2.reshape(B, L, H, Dh), kv[..., Dl:].reshape(B, L, H, Dh)).reshape(B, S, Dl)
+        self._row_out(blk.attn2_out, o, x)
         xn = fused.norm_modulate(x, shift=mod[:, 3 * D:4 * D], scale=mod[:, 4 * D:5 * D], eps=cfg.eps)
-        blk.ffn_down(blk.ffn_up(xn, act="gelu_tanh"), residual=x, gate=mod[:, 5 * D:6 * D], out=x)
+        self._row_out(blk.ffn_down, blk.ffn_up(xn, act="gelu_tanh"), x, gate=mod[:, 5 * D:6 * D])
         return x
 
     def forward(self, hidden_states, timestep, encoder_hidden_states, **_):

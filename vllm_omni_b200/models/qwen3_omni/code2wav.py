@@ -19,9 +19,20 @@ import torch.nn.functional as F
 from torch import nn
 
 from ...diffusion.layers.linear import FusedLinear
+from ...ops import conv as CV
 from ...ops import fused
 from ..base import StageModel
 from .config import Code2WavConfig, Qwen3OmniConfig
+
+
+def use_channels_last(model, x) -> bool:
+    """GPU bf16 runs take the channels-last vocoder kernels (``OMNI_VOCODER_NLC=0`` keeps the library
+    convolutions); ``model.vocoder_layout`` = "nlc" / "nct" forces either (tests)."""
+    forced = getattr(model, "vocoder_layout", None)
+    if forced is not None:
+        return forced == "nlc"
+    import os
+    return x.is_cuda and x.dtype == torch.bfloat16 and os.environ.get("OMNI_VOCODER_NLC", "1") != "0"
 
 
 class SnakeBeta(nn.Module):
@@ -37,6 +48,12 @@ class SnakeBeta(nn.Module):
         b = self.beta.float().exp()[None, :, None]
         xf = x.float()
         return (xf + (1.0 / (b + 1e-9)) * torch.sin(xf * a).pow(2)).to(x.dtype)
+
+    def forward_nlc(self, x):       # x: [B, T, C]; one fused kernel on the GPU
+        key = (self.alpha._version, self.beta._version)
+        if getattr(self, "_ab", None) is None or self._ab[0] != key:
+            self._ab = (key, self.alpha.float().exp().contiguous(), (1.0 / (self.beta.float().exp() + 1e-9)).contiguous())
+        return CV.snake_nlc(x, self._ab[1], self._ab[2])
 
 
 class CausalConv1d(nn.Module):
@@ -54,6 +71,26 @@ class CausalConv1d(nn.Module):
         extra = (frames - 1) * self.stride + (self.k_eff - self.pad) - L
         return self.conv(F.pad(x, (self.pad, extra)))
 
+    def forward_nlc(self, x, residual=None):
+        """Channels-last twin ([B, T, C] in and out, stride 1): the implicit-GEMM convolution of ops/conv.py,
+        or the depthwise kernel when every channel is its own group."""
+        cv = self.conv
+        assert self.stride == 1
+        k, dil = cv.kernel_size[0], cv.dilation[0]
+        key = (cv.weight._version, x.dtype)
+        if getattr(self, "_pk", None) is None or self._pk[0] != key:
+            if cv.groups == 1:
+                self._pk = (key,) + CV.pack_conv1d_weight(cv.weight.data, cv.bias.data if cv.bias is not None else None, x.dtype)
+            else:
+                assert cv.groups == cv.in_channels == cv.out_channels
+                self._pk = (key, cv.weight.data[:, 0].t().float().contiguous(),
+                            cv.bias.data.float().contiguous() if cv.bias is not None else None)
+        if cv.groups != 1:
+            y = CV.dwconv1d_nlc(x.contiguous(), self._pk[1], self._pk[2], k, dil, self.pad)
+            return y if residual is None else y + residual
+        y = CV.conv1d_nlc(x, self._pk[1], self._pk[2], k, cv.in_channels, dil, self.pad, residual=residual)
+        return y if y.shape[-1] == cv.out_channels else y[..., :cv.out_channels]
+
 
 class CausalTransConv1d(nn.Module):
     """Transposed convolution with (kernel - stride) samples cut from both ends (Qwen3-Omni code2wav)
@@ -68,6 +105,19 @@ class CausalTransConv1d(nn.Module):
     def forward(self, x):
         y = self.conv(x)
         return y[..., self.left: y.shape[-1] - self.trim].contiguous()
+
+    def forward_nlc(self, x):
+        """[B, T, Cin] -> [B, T_out, Cout]: all output phases from one stride-1 convolution on weights
+        stacked by phase (ops/conv.pack_conv_transpose1d_weight)."""
+        cv = self.conv
+        k, r = cv.kernel_size[0], cv.stride[0]
+        key = (cv.weight._version, x.dtype)
+        if getattr(self, "_pk", None) is None or self._pk[0] != key:
+            self._pk = (key, CV.pack_conv_transpose1d_weight(cv.weight.data, cv.bias.data if cv.bias is not None else None,
+                                                             r, self.left, x.dtype))
+        t_out = (x.shape[1] - 1) * r + k - self.left - self.trim
+        y = CV.conv_transpose1d_nlc(x, self._pk[1], cv.in_channels, r, t_out)
+        return y if y.shape[-1] == cv.out_channels else y[..., :cv.out_channels]
 
 
 class ConvNeXtBlock(nn.Module):
@@ -85,6 +135,11 @@ class ConvNeXtBlock(nn.Module):
         h = self.pwconv2(F.gelu(self.pwconv1(h.contiguous())))
         return x + (self.gamma * h).transpose(1, 2)
 
+    def forward_nlc(self, x):       # [B, T, C]
+        h = F.layer_norm(self.dwconv.forward_nlc(x), (x.shape[-1],), self.norm.weight, self.norm.bias, self.norm.eps)
+        h = F.gelu(self.pwconv1(h))
+        return self.pwconv2(h, gate=self.gamma.view(1, -1), residual=x)      # x + gamma * pwconv2(h) in the GEMM epilogue
+
 
 class ResUnit(nn.Module):
     def __init__(self, ch, dilation, dtype, device):
@@ -96,6 +151,10 @@ class ResUnit(nn.Module):
 
     def forward(self, x):
         return x + self.conv2(self.act2(self.conv1(self.act1(x))))
+
+    def forward_nlc(self, x):
+        h = self.conv1.forward_nlc(self.act1.forward_nlc(x))
+        return self.conv2.forward_nlc(self.act2.forward_nlc(h), residual=x)   # the skip rides in the epilogue
 
 
 class DecoderBlock(nn.Module):
@@ -111,6 +170,11 @@ class DecoderBlock(nn.Module):
     def forward(self, x):
         for b in self.block:
             x = b(x)
+        return x
+
+    def forward_nlc(self, x):
+        for b in self.block:
+            x = b.forward_nlc(x)
         return x
 
 
@@ -230,12 +294,24 @@ class Qwen3OmniCode2Wav(StageModel):
             raise ValueError(f"expected {c.num_quantizers} codebooks per frame, got {G}")
         off = torch.arange(G, device=codes.device)[None, :, None] * c.codebook_size
         x = self.code_embedding[codes.clamp(0, c.codebook_size - 1) + off].float().mean(1).to(self.code_embedding.dtype)
-        x = self.pre_transformer(x.contiguous()).transpose(1, 2)
+        x = self.pre_transformer(x.contiguous())
+        if self._use_nlc(x):
+            # channels-last all the way: the transformer's [B, T, D] output is the layout the 1-D implicit
+            # GEMM, the depthwise kernel and the fused snake kernel work on
+            for up, nxt in self.upsample:
+                x = nxt.forward_nlc(up.forward_nlc(x))
+            for blk in self.decoder:
+                x = blk.forward_nlc(x)
+            return x[..., 0].float().clamp(-1.0, 1.0)
+        x = x.transpose(1, 2)
         for up, nxt in self.upsample:
             x = nxt(up(x))
         for blk in self.decoder:
             x = blk(x)
         return x.float().clamp(-1.0, 1.0)[:, 0]
+
+    def _use_nlc(self, x) -> bool:
+        return use_channels_last(self, x)
 
     @torch.no_grad()
     def chunked_decode(self, codes: torch.Tensor, chunk_size=None, left_context=None) -> torch.Tensor:

@@ -71,6 +71,15 @@ class Qwen3TTSTokenizerDecoder(nn.Module):
             raise ValueError(f"expected {c.num_quantizers} codebooks per frame, got {G}")
         off = torch.arange(G, device=codes.device)[None, :, None] * c.codebook_size
         x = self.code_table[codes.clamp(0, c.codebook_size - 1) + off].float().sum(1).to(self.code_table.dtype)   # [B, T, cd]
+        from ..qwen3_omni.code2wav import use_channels_last
+        if use_channels_last(self, x):             # [B, T, C] throughout: own conv / snake kernels (ops/conv.py)
+            x = self.pre_conv.forward_nlc(x.contiguous())
+            x = self.output_proj(self.pre_transformer(self.input_proj(x.contiguous())))
+            for up, nxt in self.upsample:
+                x = nxt.forward_nlc(up.forward_nlc(x.contiguous()))
+            for blk in self.decoder:
+                x = blk.forward_nlc(x)
+            return x[..., 0].float().clamp(-1.0, 1.0)
         x = self.pre_conv(x.transpose(1, 2)).transpose(1, 2).contiguous()
         x = self.output_proj(self.pre_transformer(self.input_proj(x))).transpose(1, 2)
         for up, nxt in self.upsample:

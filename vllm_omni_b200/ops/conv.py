@@ -128,3 +128,138 @@ def nhwc_to_image(x, uint8: bool = False):
                                               c_int(0 if uint8 else 1), nv.stream_ptr())
     nv.check_rc(rc, "omni_nhwc_to_image")
     return out
+
+
+# ------------------------------------------------------------------ K15: vocoder stacks, channels-last [B, T, C]
+def pack_conv1d_weight(w: torch.Tensor, bias: torch.Tensor | None, dtype=torch.bfloat16):
+    """[Cout, Cin, k] -> ([Cout8, k * cin_pad] tap-major with zero padding, bias [Cout8])."""
+    Cout, Cin, k = w.shape
+    cin_pad, cout8 = (Cin + 63) // 64 * 64, (Cout + 7) // 8 * 8
+    p = torch.zeros(cout8, k, cin_pad, dtype=dtype, device=w.device)
+    p[:Cout, :, :Cin] = w.permute(0, 2, 1).to(dtype)
+    b = torch.zeros(cout8, dtype=dtype, device=w.device)
+    if bias is not None:
+        b[:Cout] = bias.to(dtype)
+    return p.reshape(cout8, -1).contiguous(), b
+
+
+def conv1d_nlc_reference(x, w_packed, bias, k, cin, dil=1, pad=0, t_out=None, act=None, residual=None):
+    """fp32 restatement: y[b, t] = sum_j x[b, t + j*dil - pad] W_j^T, zeros outside the input."""
+    B, T, _ = x.shape
+    t_out = T if t_out is None else t_out
+    cout8 = w_packed.shape[0]
+    w = w_packed.view(cout8, k, -1)[:, :, :cin].float().permute(0, 2, 1)            # [Cout8, cin, k]
+    right = max(0, (t_out - 1) + (k - 1) * dil - pad - (T - 1))
+    xp = F.pad(x[..., :cin].float().transpose(1, 2), (max(pad, 0), right))
+    if pad < 0:
+        xp = xp[..., -pad:]
+    y = F.conv1d(xp, w, bias.float(), dilation=dil)[..., :t_out].transpose(1, 2)
+    if act == "silu":
+        y = F.silu(y)
+    if residual is not None:
+        y = y + residual.float()
+    return y
+
+
+def conv1d_nlc(x, w_packed, bias, k: int, cin: int, dil: int = 1, pad: int = 0, t_out: int | None = None, act=None,
+               residual=None, out=None):
+    """Stride-1 convolution over time, channels-last: x [B, T, ldx >= cin] bf16 -> [B, t_out, Cout8].
+    ``pad`` input steps of zeros precede the signal (causal: (k-1)*dil, "same": (k-1)*dil // 2); reads
+    past the end are zeros too.  On the GPU this is the implicit GEMM of csrc/gemm_sm100.cu (1-D mode)."""
+    B, T, ldx = x.shape
+    t_out = T if t_out is None else t_out
+    cout8 = w_packed.shape[0]
+    if not x.is_cuda:
+        y = conv1d_nlc_reference(x, w_packed, bias, k, cin, dil, pad, t_out, act, residual).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    assert x.dtype == torch.bfloat16 and w_packed.dtype == torch.bfloat16 and x.stride(2) == 1 and x.stride(1) % 8 == 0
+    if out is None:
+        out = torch.empty(B, t_out, cout8, dtype=x.dtype, device=x.device)
+    assert out.is_contiguous() or (out.stride(2) == 1 and out.stride(0) == t_out * out.stride(1))
+    if residual is not None:
+        assert residual.stride(-1) == 1 and residual.shape[0] == B and residual.shape[1] == t_out
+        assert B == 1 or residual.stride(0) == t_out * residual.stride(1)
+    st = nv.status_word(x.device)
+    rc = nv.lib("gemm_sm100").omni_conv1d_nlc_bf16(
+        nv.ptr(x), c_long(x.stride(1)), c_long(x.stride(0)), nv.ptr(w_packed), nv.ptr(out), c_int(out.stride(1)), c_int(B),
+        c_int(T), c_int(t_out), c_int(cin), c_int(cout8), c_int(k), c_int(dil), c_int(pad), nv.ptr(bias), nv.ptr(residual),
+        c_int(residual.stride(1) if residual is not None else 0), c_int(ACT[act]), nv.ptr(st), nv.stream_ptr())
+    nv.check_rc(rc, "omni_conv1d_nlc_bf16")
+    return out
+
+
+def pack_conv_transpose1d_weight(w: torch.Tensor, bias: torch.Tensor | None, stride: int, padding: int = 0,
+                                 dtype=torch.bfloat16):
+    """Weights of ``ConvTranspose1d`` ([Cin, Cout, k], stride r, ``padding`` samples cut from the left
+    end) re-stacked by output phase so that ONE stride-1 convolution produces all r phases at once:
+    output sample t = q*r + phi is  sum_m x[q + d_phi - m] W[:, :, phi' + m*r]  with
+    phi' = (phi + padding) % r, d_phi = (phi + padding) // r.  Returns (packed [r*Cout8, K*cin_pad],
+    bias [r*Cout8], K taps, pad) for ``conv1d_nlc`` (tap j reads x[q + j - pad]); the convolution's
+    [B, Tq, r*Cout8] result, read as [B, Tq*r, Cout8], is the transposed convolution."""
+    Cin, Cout, k = w.shape
+    r = stride
+    cin_pad, cout8 = (Cin + 63) // 64 * 64, (Cout + 7) // 8 * 8
+    offs = []
+    for phi in range(r):
+        pp, d = (phi + padding) % r, (phi + padding) // r
+        m = 0
+        while pp + m * r < k:
+            offs.append((phi, d - m, pp + m * r))
+            m += 1
+    lo, hi = min(o for _, o, _ in offs), max(o for _, o, _ in offs)
+    K, pad = hi - lo + 1, -lo
+    p = torch.zeros(r, cout8, K, cin_pad, dtype=dtype, device=w.device)
+    for phi, o, j in offs:
+        p[phi, :Cout, o + pad, :Cin] = w[:, :, j].t().to(dtype)
+    b = torch.zeros(r, cout8, dtype=dtype, device=w.device)
+    if bias is not None:
+        b[:, :Cout] = bias.to(dtype)
+    return p.reshape(r * cout8, -1).contiguous(), b.reshape(-1).contiguous(), K, pad
+
+
+def conv_transpose1d_nlc(x, packed, cin: int, stride: int, t_out: int, act=None):
+    """x [B, T, >=cin] -> [B, t_out, Cout8]: ``packed`` from ``pack_conv_transpose1d_weight``; ``t_out`` is
+    the number of output samples kept (counted after the left ``padding`` cut)."""
+    w, b, K, pad = packed
+    Tq = -(-t_out // stride)
+    y = conv1d_nlc(x, w, b, K, cin, 1, pad, t_out=Tq, act=act)
+    B = x.shape[0]
+    y = y.view(B, Tq * stride, -1)
+    return y if Tq * stride == t_out else y[:, :t_out].contiguous()
+
+
+def snake_nlc(x, a, inv_b, out=None):
+    """x + inv_b[c] * sin^2(x * a[c]) over the last (channel) dimension; a / inv_b fp32 [C]."""
+    C = x.shape[-1]
+    if not x.is_cuda:
+        xf = x.float()
+        y = (xf + inv_b.float() * torch.sin(xf * a.float()).pow(2)).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and C % 8 == 0 and a.dtype == torch.float32 and inv_b.dtype == torch.float32
+    if out is None:
+        out = torch.empty_like(x)
+    rc = nv.lib("vae_ops").omni_snake_nlc(nv.ptr(x), c_long(C), nv.ptr(a), nv.ptr(inv_b), nv.ptr(out), c_long(C),
+                                          c_long(x.numel() // C), c_int(C), nv.stream_ptr())
+    nv.check_rc(rc, "omni_snake_nlc")
+    return out
+
+
+def dwconv1d_nlc(x, w_kc, bias, k: int, dil: int = 1, pad: int = 0):
+    """Depthwise convolution over time, channels-last: x [B, T, C], w_kc fp32 [k, C], bias fp32 [C] or None."""
+    B, T, C = x.shape
+    if not x.is_cuda:
+        xp = F.pad(x.float().transpose(1, 2), (pad, max(0, (k - 1) * dil - pad)))
+        y = F.conv1d(xp, w_kc.float().t()[:, None, :], None if bias is None else bias.float(), dilation=dil, groups=C)
+        return y[..., :T].transpose(1, 2).to(x.dtype)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and C % 8 == 0 and w_kc.dtype == torch.float32 and w_kc.is_contiguous()
+    out = torch.empty_like(x)
+    rc = nv.lib("vae_ops").omni_dwconv1d_nlc(nv.ptr(x), nv.ptr(w_kc), nv.ptr(bias), nv.ptr(out), c_int(B), c_int(T), c_int(C),
+                                             c_int(k), c_int(dil), c_int(pad), nv.stream_ptr())
+    nv.check_rc(rc, "omni_dwconv1d_nlc")
+    return out
