@@ -42,7 +42,7 @@ stage_args:
     default_sampling_params: {temperature: 0.0, max_tokens: MAXTOK, ignore_eos: true, detokenize: false}
   - stage_id: 1
     stage_type: llm
-    runtime: {devices: "0", max_batch_size: MAXB}
+    runtime: {devices: "0", max_batch_size: MAXB, process: STAGE_PROC}
     engine_args: {model_stage: talker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
                   engine_output_type: latent, device: DEVICE, gpu_memory_utilization: 0.75, load_format: dummy,
                   model_overrides: OVERRIDES}
@@ -52,7 +52,7 @@ stage_args:
                               stop_token_ids: [], detokenize: false}
   - stage_id: 2
     stage_type: llm
-    runtime: {devices: "0", max_batch_size: MAXB}
+    runtime: {devices: "0", max_batch_size: MAXB, process: STAGE_PROC}
     engine_args: {model_stage: code2wav, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: generation,
                   engine_output_type: audio, device: DEVICE, load_format: dummy, model_overrides: OVERRIDES}
     engine_input_source: [1]
@@ -133,11 +133,29 @@ async def _run(a, path):
 
     t0 = time.perf_counter()
     tasks = []
+    live: dict = {}
+
+    async def progress():
+        while True:
+            await asyncio.sleep(a.progress)
+            done = len(recs)
+            print(f"[{time.perf_counter() - t0:7.1f}s] finished {done}/{len(prompts)} requests, "
+                  f"{sum(r['tokens'] for r in recs)} text tokens of finished requests", file=sys.stderr, flush=True)
+    mon = asyncio.create_task(progress()) if a.progress > 0 else None
     for i, p in enumerate(prompts):
         tasks.append(asyncio.create_task(one(i, p)))
         if a.request_rate > 0:
             await asyncio.sleep(rng.expovariate(a.request_rate))
-    await asyncio.gather(*tasks)
+    timed_out = False
+    if a.time_limit > 0:
+        done_set, pending = await asyncio.wait(tasks, timeout=max(1.0, a.time_limit - (time.perf_counter() - t0)))
+        timed_out = bool(pending)
+        for t in pending:
+            t.cancel()
+    else:
+        await asyncio.gather(*tasks)
+    if mon is not None:
+        mon.cancel()
     wall = time.perf_counter() - t0
     try:
         eng_stats = eng.metrics.build_summary(wall)
@@ -151,7 +169,7 @@ async def _run(a, path):
            "ttft_s": {f"p{q}": _pct([r["ttft"] for r in recs if r["ttft"] is not None], q) for q in (50, 90, 99)},
            "audio_ttfp_s": {f"p{q}": _pct([r["ttfp"] for r in recs if r["ttfp"] is not None], q) for q in (50, 90, 99)},
            "e2el_s": {f"p{q}": _pct([r["latency"] for r in recs], q) for q in (50, 90, 99)},
-           "stages": _stage_split(eng_stats),
+           "stages": _stage_split(eng_stats), "timed_out": timed_out,
            "config": {"tiny": a.tiny, "input_len": a.input_len, "audio_seconds": a.audio_seconds,
                       "thinker_tp": a.thinker_tp, "thinker_ep": a.thinker_ep, "max_tokens": a.max_tokens, "codec_frames": a.codec_frames,
                       "max_concurrency": a.max_concurrency, "request_rate": a.request_rate, "async_chunk": a.async_chunk,
@@ -176,6 +194,9 @@ def main(argv=None):
     ap.add_argument("--thinker-tp", type=int, default=1, help="GPUs of the thinker stage (tensor parallel)")
     ap.add_argument("--thinker-ep", action="store_true", help="whole experts per rank instead of sliced FFNs")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--stage-processes", action="store_true", help="every stage in a process of its own (own interpreter lock)")
+    ap.add_argument("--progress", type=float, default=0.0, help="seconds between progress lines on stderr (0 = none)")
+    ap.add_argument("--time-limit", type=float, default=0.0, help="stop waiting after this many seconds and report what finished")
     a = ap.parse_args(argv)
     ov = {"tiny": True} if a.tiny else {}
     if a.thinker_layers:
@@ -185,7 +206,8 @@ def main(argv=None):
          .replace("OVERRIDES", json.dumps(ov)).replace("THINKER_TP", str(a.thinker_tp))
          .replace("THINKER_EP", "true" if a.thinker_ep else "false")
          .replace("THINKER_DEVS", ",".join(str(i) for i in range(a.thinker_tp)))
-         .replace("THINKER_PROC", "true" if a.thinker_tp > 1 else "false"))
+         .replace("THINKER_PROC", "true" if (a.thinker_tp > 1 or a.stage_processes) else "false")
+         .replace("STAGE_PROC", "true" if a.stage_processes else "false"))
     f = tempfile.NamedTemporaryFile("w", suffix=".yaml", delete=False)
     f.write(y)
     f.close()

@@ -23,6 +23,14 @@ def _entry(rank, world, port, fn, backend, args, errq):
     except Exception:
         errq.put((rank, traceback.format_exc()))
         raise
+    finally:
+        # a process group that is still alive when the interpreter tears down its threads can abort the process
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            try:
+                dist.destroy_process_group()
+            except Exception:   # noqa: BLE001
+                pass
 
 
 def run_distributed(fn, world: int, backend: str = "gloo", args=(), timeout: float = 240.0):

@@ -19,8 +19,9 @@ Paths (rank 0 prints one JSON line):
   tp_row_reduce   row-parallel GEMM with the reduce-scatter in its epilogue + local reduce + peer gather
                                                 vs GEMM + NCCL all-reduce
   peer_kv_attn    attention reading K/V of the peer through plain TMA loads   vs local K/V
-  ring_gather_attn  own-chunk attention overlapped with a pull of the peers' K/V, then the continuation
-                  launch (the ring path as built)   vs one launch over all keys held locally
+  ring_gather_attn_single / _overlap   the ring path as built (parallel/ring.py): the peers' K/V pulled once into
+                  local memory, then one launch over all keys / own shard during the pull plus a continuation
+                  launch                        vs one launch over all keys held locally
   cfg_exchange    guidance mix + Euler step reading the partner's prediction over NVLink  vs local
 """
 from __future__ import annotations
@@ -147,11 +148,16 @@ def multi(a):
     ring.setup(1, M, 0, dev, bf)
     ring.qkv_local.normal_()
     grp.barrier()
-    t_ring = _time(lambda: ring.attend(None, None), a.reps, grp, flush)
     kv_full = torch.randn(1, P * M, 2, H, Dh, device=dev, dtype=bf)
     t_full = _time(lambda: A.attention(q_loc, kv_full[:, :, 0], kv_full[:, :, 1], out=o2), a.reps, grp, flush)
-    out["ring_gather_attn"] = _entry(t_ring, 4.0 * H * M * (P * M) * Dh, (P - 1) * M * 2 * H * Dh * 2, t_full)
-    out["ring_gather_attn"]["local_twin"] = "one attention launch over all P*M keys held locally"
+    for mode in ("single", "overlap"):
+        os.environ["OMNI_RING_MODE"] = mode
+        ring._side = None
+        t_ring = _time(lambda: ring.attend(None, None), a.reps, grp, flush)
+        key = f"ring_gather_attn_{mode}"
+        out[key] = _entry(t_ring, 4.0 * H * M * (P * M) * Dh, (P - 1) * M * 2 * H * Dh * 2, t_full)
+        out[key]["local_twin"] = "one attention launch over all P*M keys held locally"
+    os.environ.pop("OMNI_RING_MODE", None)
     ring.close()
 
     # ---- tp_row_reduce: MLP down-projection, K sharded over the ranks

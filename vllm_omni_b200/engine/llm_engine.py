@@ -9,6 +9,7 @@ multimodal tensors (the role of vllm_omni/engine/output_processor.py).
 """
 from __future__ import annotations
 
+import os
 import time
 
 import torch
@@ -125,7 +126,53 @@ class LLMEngine:
         return self._reqs.get(request_id)
 
     # ------------------------------------------------------------------ loop
+    def _timing(self):
+        """Per-phase wall time of the engine loop (``OMNI_ENGINE_TIMING=1``; the device is synchronised at
+        the phase boundaries, so use it for diagnosis, not while benchmarking).  Printed at exit."""
+        if getattr(self, "_phase", None) is None:
+            import atexit
+            import json
+            import sys
+            self._phase = {"steps": 0, "schedule": 0.0, "execute": 0.0, "update": 0.0, "outputs": 0.0, "tokens": 0,
+                           "decode_only_steps": 0}
+            name = type(self.model).__name__
+            atexit.register(lambda: print(json.dumps({"engine_timing": name, **{k: (round(v, 3) if isinstance(v, float) else v)
+                                                                              for k, v in self._phase.items()}}),
+                                          file=sys.stderr, flush=True))
+        return self._phase
+
     def step(self) -> list[RequestOutput]:
+        if os.environ.get("OMNI_ENGINE_TIMING") == "1":
+            return self._timed_step()
+        return self._step()
+
+    def _timed_step(self) -> list[RequestOutput]:
+        ph = self._timing()
+        sync = (lambda: torch.cuda.synchronize(self.device)) if self.device.type == "cuda" else (lambda: None)
+        outs, self._errors = self._errors, []
+        t0 = time.perf_counter()
+        sched = self.scheduler.schedule()
+        t1 = time.perf_counter()
+        ph["schedule"] += t1 - t0
+        if sched.empty:
+            if self.scheduler.has_unfinished() and not self.scheduler.has_schedulable():
+                time.sleep(0.001)
+            return outs
+        sampled, kv_done = self.runner.execute(sched, self.kv)
+        sync()
+        t2 = time.perf_counter()
+        ph["execute"] += t2 - t1
+        ph["steps"] += 1
+        ph["tokens"] += sum(s.num_new_tokens for s in sched.scheduled)
+        ph["decode_only_steps"] += int(all(s.num_new_tokens == 1 for s in sched.scheduled))
+        touched = self.scheduler.update_from_output(sched, sampled, kv_done)
+        t3 = time.perf_counter()
+        ph["update"] += t3 - t2
+        outs += self._finish_step(sched, touched)
+        ph["outputs"] += time.perf_counter() - t3
+        return outs
+
+    def _step(self) -> list[RequestOutput]:
         outs, self._errors = self._errors, []
         sched = self.scheduler.schedule()
         if sched.empty:
@@ -134,6 +181,10 @@ class LLMEngine:
             return outs
         sampled, kv_done = self.runner.execute(sched, self.kv)
         touched = self.scheduler.update_from_output(sched, sampled, kv_done)
+        return outs + self._finish_step(sched, touched)
+
+    def _finish_step(self, sched, touched) -> list[RequestOutput]:
+        outs: list[RequestOutput] = []
         if sched.kv_transfer_ids and self.kv_transfer_manager is not None:
             done = self.kv_transfer_manager.handle_finished_requests_kv_transfer(
                 [self._reqs[r] for r in sched.kv_transfer_ids if r in self._reqs], self.runner)

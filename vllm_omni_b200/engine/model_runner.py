@@ -57,7 +57,7 @@ class ARModelRunner:
         max_blocks = 1
         for s in sched.scheduled:
             r = s.request
-            toks = r.all_token_ids[s.start:s.start + s.num_new_tokens]
+            toks = r.token_slice(s.start, s.num_new_tokens)
             if len(toks) < s.num_new_tokens:            # decode of a request without tokens yet (talker)
                 toks = toks + [0] * (s.num_new_tokens - len(toks))
             ids.extend(toks)
@@ -136,8 +136,9 @@ class ARModelRunner:
         # a process-independent default seed (Python's str hash is salted per process)
         seed = sp.seed if sp.seed is not None else (zlib.crc32(r.request_id.encode()) & 0x7FFFFFFF)
         allowed = sp.extra_args.get("allowed_token_range") if sp.extra_args else None
+        pen = sp.repetition_penalty != 1.0 or sp.presence_penalty != 0.0 or sp.frequency_penalty != 0.0
         return RowParams(sp.temperature, sp.top_p, sp.min_p, sp.top_k, sp.repetition_penalty, sp.presence_penalty,
-                         sp.frequency_penalty, seed, len(r.output_token_ids), r.all_token_ids, r.num_prompt_tokens,
+                         sp.frequency_penalty, seed, len(r.output_token_ids), r.all_token_ids if pen else (), r.num_prompt_tokens,
                          list(sp.suppress_token_ids or []), tuple(allowed) if allowed else None)
 
     # ------------------------------------------------------------------ KV hand-off

@@ -34,7 +34,7 @@ FINISH_REASON = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_
                  RequestStatus.FINISHED_ABORTED: "abort", RequestStatus.FINISHED_ERROR: "error"}
 
 
-@dataclass
+@dataclass(eq=False)          # identity semantics: queues look requests up by object, never by field values
 class Request:
     request_id: str
     prompt_token_ids: list[int]
@@ -72,6 +72,16 @@ class Request:
     @property
     def all_token_ids(self) -> list[int]:
         return self.prompt_token_ids + self.output_token_ids
+
+    def token_slice(self, start: int, n: int) -> list[int]:
+        """``all_token_ids[start:start + n]`` without building the concatenated list (the decode step asks
+        for one token of every running request)."""
+        P = len(self.prompt_token_ids)
+        if start >= P:
+            return self.output_token_ids[start - P:start - P + n]
+        if start + n <= P:
+            return self.prompt_token_ids[start:start + n]
+        return self.prompt_token_ids[start:] + self.output_token_ids[:start + n - P]
 
     @property
     def max_tokens(self) -> int:

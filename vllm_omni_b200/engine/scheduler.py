@@ -220,10 +220,8 @@ class OmniARScheduler:
     def _release(self, req: Request) -> None:
         if req in self.running:
             self.running.remove(req)
-        try:
+        if req in self.waiting:            # (a failed ``deque.remove`` formats the request, tensors included, into its error)
             self.waiting.remove(req)
-        except ValueError:
-            pass
         if req.kv_transfer_requested and not req.kv_transfer_done and req.status != RequestStatus.FINISHED_ABORTED:
             self.waiting_for_kv_extract[req.request_id] = req     # pages freed once the KV is extracted
         else:

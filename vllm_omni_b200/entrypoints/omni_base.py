@@ -38,6 +38,11 @@ class OmniBase:
             shm_threshold_bytes=shm_threshold_bytes, worker_backend=worker_backend, batch_timeout=batch_timeout)
         from ..metrics.stats import OrchestratorAggregator
         self.metrics = OrchestratorAggregator(len(self.stage_list), log_stats, log_file)
+        if len(self.stage_list) > 1:
+            # Stages that run as threads of this process share one interpreter lock.  A stage loop that comes
+            # back from a device wait must not sit out another thread's whole 5 ms slice before its next launch.
+            import sys
+            sys.setswitchinterval(min(sys.getswitchinterval(), 0.0005))
         self._closed = False
 
     @property

@@ -44,7 +44,7 @@ class HybridJointAttention:
         self.H, self.Dh, self.Hp = num_heads, head_dim, num_heads // self.U
         self.arena = None
         self._key = None
-        self._side = self._gath = None
+        self._side = self._gath = self._overlap = None
 
     def setup(self, B, Si_loc, St_loc, device, dtype):
         self.uly.setup(B, Si_loc, St_loc, device, dtype)
@@ -97,34 +97,48 @@ class HybridJointAttention:
             if R == 1:
                 attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._chunk_kv_lens(kv_lens, r), scatter=sc)
             else:
+                from .ring import two_launches_pay
                 main = torch.cuda.current_stream(dev)
-                if self._side is None:
-                    self._side = torch.cuda.Stream(dev)
-                    # the other chunks' image rows in ring order, then their text rows: valid keys stay a prefix
-                    self._gath = torch.empty(B, (R - 1) * Sc, 2 * self.Hp * self.Dh, dtype=q.dtype, device=dev)
+                overlap = two_launches_pay(B, Sc, self.Hp)
+                if self._side is None or self._overlap != overlap:
+                    self._side, self._overlap = torch.cuda.Stream(dev), overlap
+                    # chunks in ring order (image rows, then text rows: valid keys stay a prefix); the overlapped
+                    # form leaves the own chunk out of the buffer and reads it in place
+                    self._srcs = [c for c in range(R) if c != r] if overlap else list(range(R))
+                    self._gath = torch.empty(B, len(self._srcs) * Sc, 2 * self.Hp * self.Dh, dtype=q.dtype, device=dev)
                     self._own = torch.empty(B, Sc, self.Hp, self.Dh, dtype=q.dtype, device=dev)
-                    self._others = [c for c in range(R) if c != r]
-                    self._others_t = torch.tensor(self._others, device=dev, dtype=torch.int32)
+                    self._srcs_t = torch.tensor(self._srcs, device=dev, dtype=torch.int32)
+                n = len(self._srcs)
                 row = 2 * self.Hp * self.Dh
                 es = q.element_size()
+
+                def pull(j, src):
+                    for b in range(B):
+                        base = self.kv.ptrs[src] + b * Sc * row * es
+                        pull_rows(self._gath[b, j * self.Si_c:(j + 1) * self.Si_c], base, row * es)
+                        if self.St_c:
+                            t0 = n * self.Si_c + j * self.St_c
+                            pull_rows(self._gath[b, t0:t0 + self.St_c], base + self.Si_c * row * es, row * es)
                 self._side.wait_stream(main)
                 with torch.cuda.stream(self._side):
-                    for j, src in enumerate(self._others):
-                        for b in range(B):
-                            base = self.kv.ptrs[src] + b * Sc * row * es
-                            pull_rows(self._gath[b, j * self.Si_c:(j + 1) * self.Si_c], base, row * es)
-                            if self.St_c:
-                                t0 = (R - 1) * self.Si_c + j * self.St_c
-                                pull_rows(self._gath[b, t0:t0 + self.St_c], base + self.Si_c * row * es, row * es)
-                _, lse0 = attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._chunk_kv_lens(kv_lens, r), return_lse=True,
-                                    out=self._own)
-                main.wait_stream(self._side)
-                g5 = self._gath.view(B, (R - 1) * Sc, 2, self.Hp, self.Dh)
-                rem = None
-                if kv_lens is not None:
-                    txt = (kv_lens[:, None] - self.S_img - self._others_t[None] * self.St_c).clamp(0, self.St_c).sum(dim=1)
-                    rem = ((R - 1) * self.Si_c + txt).to(torch.int32)
-                attention(q, g5[:, :, 0], g5[:, :, 1], kv_lens=rem, merge_prev=(self._own, lse0), scatter=sc)
+                    for j, src in enumerate(self._srcs):
+                        if src != r:
+                            pull(j, src)
+                g5 = self._gath.view(B, n * Sc, 2, self.Hp, self.Dh)
+                if overlap:
+                    _, lse0 = attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._chunk_kv_lens(kv_lens, r), return_lse=True,
+                                        out=self._own)
+                    main.wait_stream(self._side)
+                    rem = None
+                    if kv_lens is not None:
+                        txt = (kv_lens[:, None] - self.S_img - self._srcs_t[None] * self.St_c).clamp(0, self.St_c).sum(dim=1)
+                        rem = (n * self.Si_c + txt).to(torch.int32)
+                    attention(q, g5[:, :, 0], g5[:, :, 1], kv_lens=rem, merge_prev=(self._own, lse0), scatter=sc)
+                else:
+                    pull(r, r)
+                    main.wait_stream(self._side)
+                    attention(q, g5[:, :, 0], g5[:, :, 1], kv_lens=kv_lens.to(torch.int32) if kv_lens is not None else None,
+                              scatter=sc)
             self.arena.barrier()                                  # published K/V may be overwritten
             self.uly.arena.barrier()                              # every owner has its rows
             return self.uly.attn_img.local, self.uly.attn_txt.local

@@ -9,9 +9,10 @@ sequence = merge of P partial attentions, one per K/V shard:
 layer; behind NVSwitch there is no ring to walk.  A side stream pulls the K/V of ALL other ranks
 into one local buffer with this library's copy kernel (each remote byte crosses NVLink once;
 reading the peer's tiles straight from the attention kernel makes every query-tile CTA fetch them
-again: 354 us against 107 us with local K/V at 2048 rows x 24 heads on two B200s), while the main
-stream attends to the local shard.  A second launch attends to the gathered remote keys and its
-epilogue combines both results by their log-sum-exps (``attention(..., merge_prev=...)``): two
+again: 354 us against 107 us with local K/V at 2048 rows x 24 heads on two B200s).  Small grids
+then run ONE launch over all keys in global order; grids that fill the GPU several times over
+attend to the own shard while the pulls run and finish with a second launch whose epilogue combines
+both results by their log-sum-exps (``attention(..., merge_prev=...)``).  Either way at most two
 launches per layer whatever the degree, and no merge kernels.  One bounded-wait barrier before
 (shards written) and one after (shards consumed) per layer.
 ``mode="nccl"``: classic ring with batched isend/irecv of K and V (the baseline; also the CPU
@@ -25,6 +26,18 @@ import torch.nn.functional as F
 from ..ops import fused
 from ..ops.attention import attention
 from .comm import RingComm
+
+
+def two_launches_pay(B: int, S_q: int, H: int) -> bool:
+    """Whether the ring's "own shard while the remote ones are pulled, then the rest" form beats one
+    launch over all gathered keys: only when a launch fills the GPU several times over, so that cutting
+    the key set in two does not leave both launches with a ragged last wave.  ``OMNI_RING_MODE`` =
+    ``overlap`` / ``single`` forces either."""
+    import os
+    mode = os.environ.get("OMNI_RING_MODE")
+    if mode in ("overlap", "single"):
+        return mode == "overlap"
+    return B * H * -(-S_q // 256) >= 4 * 148
 
 
 def merge_attention(out, lse, out_b, lse_b):
@@ -45,7 +58,7 @@ class RingJointAttention:
         self.mode = mode or ("peer" if torch.cuda.is_available() else "nccl")
         self.arena = None
         self._key = None
-        self._side = self._gath = None
+        self._side = self._gath = self._overlap = None
 
     def setup(self, B, Si_loc, St_loc, device, dtype):
         key = (B, Si_loc, St_loc, str(device), dtype)
@@ -109,31 +122,48 @@ class RingJointAttention:
                 attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._shard_kv_lens(kv_lens, r), out=o4)
             else:
                 main = torch.cuda.current_stream(dev)
-                if self._side is None:
-                    self._side = torch.cuda.Stream(dev)
-                    # remote rows: the image rows of the other ranks in rank order, then their text rows, so
-                    # that the valid keys (text is padded at the end of the global text) stay a prefix
-                    self._gath = torch.empty(B, (P - 1) * self.S_loc, 2 * HD, dtype=dt, device=dev)
-                    self._others = [s for s in range(P) if s != r]
-                    self._others_t = torch.tensor(self._others, device=dev, dtype=torch.int32)
+                overlap = two_launches_pay(B, self.S_loc, self.H)
+                if self._side is None or self._overlap != overlap:
+                    self._side, self._overlap = torch.cuda.Stream(dev), overlap
+                    # rows in the gathered buffer: image rows in rank order, then text rows in rank order, so that
+                    # valid keys (text is padded at the end of the global text) stay a prefix.  The overlapped
+                    # form leaves the own shard out (it is read in place by the first launch).
+                    self._srcs = [s for s in range(P) if s != r] if overlap else list(range(P))
+                    n = len(self._srcs)
+                    self._gath = torch.empty(B, n * self.S_loc, 2 * HD, dtype=dt, device=dev)
+                    self._srcs_t = torch.tensor(self._srcs, device=dev, dtype=torch.int32)
+                n = len(self._srcs)
+                pitch = 3 * HD * es
+
+                def pull(j, src):
+                    for b in range(B):
+                        base = self.qkv.ptrs[src] + ((b * self.S_loc) * 3 * HD + HD) * es
+                        pull_rows(self._gath[b, j * Si:(j + 1) * Si], base, pitch)
+                        if St:
+                            t0 = n * Si + j * St
+                            pull_rows(self._gath[b, t0:t0 + St], base + Si * pitch, pitch)
                 self._side.wait_stream(main)
                 with torch.cuda.stream(self._side):
-                    pitch = 3 * HD * es
-                    for j, src in enumerate(self._others):
-                        for b in range(B):
-                            base = self.qkv.ptrs[src] + ((b * self.S_loc) * 3 * HD + HD) * es
-                            pull_rows(self._gath[b, j * Si:(j + 1) * Si], base, pitch)
-                            if St:
-                                t0 = (P - 1) * Si + j * St
-                                pull_rows(self._gath[b, t0:t0 + St], base + Si * pitch, pitch)
-                _, lse0 = attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._shard_kv_lens(kv_lens, r), return_lse=True, out=o4)
-                main.wait_stream(self._side)
-                g5 = self._gath.view(B, (P - 1) * self.S_loc, 2, self.H, self.Dh)
-                rem_lens = None
-                if kv_lens is not None:
-                    txt = (kv_lens[:, None] - self.S_img - self._others_t[None] * St).clamp(0, St).sum(dim=1)
-                    rem_lens = ((P - 1) * Si + txt).to(torch.int32)
-                attention(q, g5[:, :, 0], g5[:, :, 1], kv_lens=rem_lens, merge_prev=(o4, lse0), out=o4)
+                    for j, src in enumerate(self._srcs):
+                        if src != r:
+                            pull(j, src)
+                g5 = self._gath.view(B, n * self.S_loc, 2, self.H, self.Dh)
+                if overlap:
+                    # big grids: the own shard is attended to in place while the pulls run; the second launch
+                    # takes the remote rows and combines both results in its epilogue
+                    _, lse0 = attention(q, q5[:, :, 1], q5[:, :, 2], kv_lens=self._shard_kv_lens(kv_lens, r), return_lse=True, out=o4)
+                    main.wait_stream(self._side)
+                    rem_lens = None
+                    if kv_lens is not None:
+                        txt = (kv_lens[:, None] - self.S_img - self._srcs_t[None] * St).clamp(0, St).sum(dim=1)
+                        rem_lens = (n * Si + txt).to(torch.int32)
+                    attention(q, g5[:, :, 0], g5[:, :, 1], kv_lens=rem_lens, merge_prev=(o4, lse0), out=o4)
+                else:
+                    # small grids (a launch is a wave or two): ONE launch over all keys in global order; the own
+                    # shard is copied locally on the main stream while the side stream pulls the others
+                    pull(r, r)
+                    main.wait_stream(self._side)
+                    attention(q, g5[:, :, 0], g5[:, :, 1], kv_lens=kv_lens.to(torch.int32) if kv_lens is not None else None, out=o4)
             self.arena.barrier()                                  # shards may be overwritten by the next layer
             return self.attn[:, :self.Si_loc], self.attn[:, self.Si_loc:]
         else:

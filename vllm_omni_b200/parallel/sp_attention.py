@@ -110,26 +110,39 @@ class SequenceParallelAttention:
                 self.arena.barrier()
                 chunk = S_c * 2 * Hu * self.Dh
                 es = q5.element_size()
-                if self._gath is None or self._gath.shape != (B, (R - 1) * chunk):
-                    self._gath = torch.empty(B, (R - 1) * chunk, dtype=q5.dtype, device=dev)
+                from .ring import two_launches_pay
+                overlap = two_launches_pay(B, S_c, Hu)
+                srcs = [c for c in range(R) if c != r] if overlap else list(range(R))
+                n = len(srcs)
+                if self._gath is None or self._gath.shape != (B, n * chunk):
+                    self._gath = torch.empty(B, n * chunk, dtype=q5.dtype, device=dev)
                     self._own = torch.empty(B, S_c, Hu, self.Dh, dtype=q5.dtype, device=dev)
                     self._side = self._side or torch.cuda.Stream(dev)
-                others = [c for c in range(R) if c != r]
                 main = torch.cuda.current_stream(dev)
                 self._side.wait_stream(main)
                 with torch.cuda.stream(self._side):
-                    for j, src in enumerate(others):                       # one launch per chunk: a row per batch
-                        pull_rows(self._gath[:, j * chunk:(j + 1) * chunk], self.kv.ptrs[src], chunk * es)
-                _, lse0 = attention(q, k, v, scale=scale, return_lse=True, out=self._own,
-                                    kv_lens=self._chunk_lens(valid_len, r, S_c, B, dev))
-                main.wait_stream(self._side)
-                g5 = self._gath.view(B, (R - 1) * S_c, 2, Hu, self.Dh)
-                rem = None
-                if valid_len is not None:                                   # padding sits at the end of the LAST chunk
-                    lens = [self._chunk_lens(valid_len, c, S_c, B, dev) for c in others]
-                    rem = torch.stack(lens).sum(dim=0).to(torch.int32)
-                out = attention(q, g5[:, :, 0], g5[:, :, 1], scale=scale, kv_lens=rem, merge_prev=(self._own, lse0),
-                                out=self._own)
+                    for j, src in enumerate(srcs):                         # one launch per chunk: a row per batch
+                        if src != r:
+                            pull_rows(self._gath[:, j * chunk:(j + 1) * chunk], self.kv.ptrs[src], chunk * es)
+                g5 = self._gath.view(B, n * S_c, 2, Hu, self.Dh)
+                if overlap:
+                    # the own chunk in place while the pulls run, then the remote chunks with the combination
+                    _, lse0 = attention(q, k, v, scale=scale, return_lse=True, out=self._own,
+                                        kv_lens=self._chunk_lens(valid_len, r, S_c, B, dev))
+                    main.wait_stream(self._side)
+                    rem = None
+                    if valid_len is not None:                               # padding sits at the end of the LAST chunk
+                        rem = torch.stack([self._chunk_lens(valid_len, c, S_c, B, dev) for c in srcs]).sum(dim=0).to(torch.int32)
+                    out = attention(q, g5[:, :, 0], g5[:, :, 1], scale=scale, kv_lens=rem, merge_prev=(self._own, lse0),
+                                    out=self._own)
+                else:
+                    # small grids: one launch over every chunk in order
+                    pull_rows(self._gath[:, r * chunk:(r + 1) * chunk], self.kv.ptrs[r], chunk * es)
+                    main.wait_stream(self._side)
+                    lens = None
+                    if valid_len is not None:
+                        lens = (valid_len.to(dev) if torch.is_tensor(valid_len) else torch.full((B,), int(valid_len), device=dev)).to(torch.int32)
+                    out = attention(q, g5[:, :, 0], g5[:, :, 1], scale=scale, kv_lens=lens, out=self._own)
                 self.arena.barrier()
             else:
                 comm = RingComm(self.group.ring.device_group)
