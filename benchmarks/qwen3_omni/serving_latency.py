@@ -44,7 +44,7 @@ stage_args:
     stage_type: llm
     runtime: {devices: "0", max_batch_size: MAXB, process: STAGE_PROC}
     engine_args: {model_stage: talker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
-                  engine_output_type: latent, device: DEVICE, gpu_memory_utilization: 0.75, load_format: dummy,
+                  engine_output_type: latent, device: DEVICE, gpu_memory_utilization: 0.3, load_format: dummy,
                   model_overrides: OVERRIDES}
     engine_input_source: [0]
     custom_process_input_func: vllm_omni_b200.models.stage_input_processors.qwen3_omni.thinker2talker
@@ -194,10 +194,14 @@ def main(argv=None):
     ap.add_argument("--thinker-tp", type=int, default=1, help="GPUs of the thinker stage (tensor parallel)")
     ap.add_argument("--thinker-ep", action="store_true", help="whole experts per rank instead of sliced FFNs")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--stage-processes", action="store_true", help="every stage in a process of its own (own interpreter lock)")
+    ap.add_argument("--stage-processes", action="store_true", help="every stage in a process of its own (own interpreter lock); "
+                    "the default on a GPU")
+    ap.add_argument("--stage-threads", action="store_true", help="keep the stages on threads of this process on a GPU too")
     ap.add_argument("--progress", type=float, default=0.0, help="seconds between progress lines on stderr (0 = none)")
     ap.add_argument("--time-limit", type=float, default=0.0, help="stop waiting after this many seconds and report what finished")
     a = ap.parse_args(argv)
+    if a.device != "cpu" and not a.stage_threads:
+        a.stage_processes = True          # one interpreter (and one CUDA context) per stage, as a deployment runs them
     ov = {"tiny": True} if a.tiny else {}
     if a.thinker_layers:
         ov["thinker_layers"] = a.thinker_layers

@@ -5,12 +5,17 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_moe_forward_matches_reference():
+@pytest.mark.parametrize("padded", ["0", "1"])
+@pytest.mark.parametrize("T,E,k", [(37, 16, 4), (700, 4, 2), (5, 16, 2)])
+def test_moe_forward_matches_reference(monkeypatch, padded, T, E, k):
+    """Both row layouts (experts' rows back to back: the default; padded to 128 per expert), experts with
+    more than one M tile of rows, and batches smaller than the number of experts."""
     from vllm_omni_b200.ops.moe import MoEWorkspace, moe_forward
     from vllm_omni_b200.ops import gemm, _native as nv
+    monkeypatch.setenv("OMNI_MOE_PADDED", padded)
     dev = torch.device("cuda")
     torch.manual_seed(0)
-    T, D, E, Fd, k = 37, 256, 16, 128, 4
+    D, Fd = 256, 128
     x = torch.randn(T, D, device=dev, dtype=torch.bfloat16)
     rw = torch.randn(E, D, device=dev, dtype=torch.bfloat16) * 0.1
     w13 = torch.randn(E, 2 * Fd, D, device=dev, dtype=torch.bfloat16) * 0.05
@@ -42,9 +47,12 @@ def test_moe_forward_matches_reference():
     err = (y.cpu() - ref).abs().max().item()
     assert err < 0.05 * max(1.0, ref.abs().max().item()), f"moe max abs err {err} (ref max {ref.abs().max().item()})"
     # expert-parallel halves sum to the whole
-    a = moe_forward(x, logits, w13[:8].contiguous(), w2[:8].contiguous(), k, e_lo=0, e_hi=8).float()
-    b = moe_forward(x, logits, w13[8:].contiguous(), w2[8:].contiguous(), k, e_lo=8, e_hi=16).float()
+    h = E // 2
+    a = moe_forward(x, logits, w13[:h].contiguous(), w2[:h].contiguous(), k, e_lo=0, e_hi=h).float()
+    b = moe_forward(x, logits, w13[h:].contiguous(), w2[h:].contiguous(), k, e_lo=h, e_hi=E).float()
     assert ((a + b) - y).abs().max().item() < 0.05
+    torch.cuda.synchronize()
+    assert int(nv.status_word(dev).item()) == 0
 
 
 def test_sampler_greedy_topk_topp_and_masks():

@@ -23,10 +23,14 @@ NVCC_FLAGS = [
     "-shared", "-Xcompiler", "-fPIC",
 ]
 CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-pthread"]
+# libraries that also get a checked twin (-DOMNI_BOUNDS_CHECK, ``libomni_<name>_checked.so``): kernels that take
+# addresses from index operands test them and report through the status word instead of faulting;
+# ``OMNI_BOUNDS_CHECK=1`` makes ``ops/_native.lib`` load the twin
+CHECKED = ("kv_cache",)
 
 
-def lib_path(name: str) -> Path:
-    return LIB / f"libomni_{name}.so"
+def lib_path(name: str, checked: bool = False) -> Path:
+    return LIB / f"libomni_{name}{'_checked' if checked else ''}.so"
 
 
 def _newest_header_mtime() -> float:
@@ -34,14 +38,14 @@ def _newest_header_mtime() -> float:
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
-def _compile(src: Path, force: bool) -> str:
-    out = lib_path(src.stem)
+def _compile(src: Path, force: bool, checked: bool = False) -> str:
+    out = lib_path(src.stem, checked)
     dep_m = max(src.stat().st_mtime, _newest_header_mtime())
     if not force and out.exists() and out.stat().st_mtime >= dep_m:
         return f"up-to-date {out.name}"
     if src.suffix == ".cu":
         nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(out), str(src)]
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DOMNI_BOUNDS_CHECK"] if checked else []), "-I", str(CSRC), "-o", str(out), str(src)]
     else:
         cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")     # NVTX v3 headers
         inc = ["-I", cuda_inc] if os.path.isdir(cuda_inc) else []
@@ -55,8 +59,9 @@ def _compile(src: Path, force: bool) -> str:
 def build_all(force: bool = False, verbose: bool = True) -> list[str]:
     LIB.mkdir(exist_ok=True)
     srcs = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp"))
-    with ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
-        msgs = list(ex.map(lambda s: _compile(s, force), srcs))
+    jobs = [(s, False) for s in srcs] + [(s, True) for s in srcs if s.stem in CHECKED]
+    with ThreadPoolExecutor(max_workers=min(8, len(jobs) or 1)) as ex:
+        msgs = list(ex.map(lambda j: _compile(j[0], force, j[1]), jobs))
     if verbose:
         for m in msgs:
             print("[build]", m)

@@ -89,6 +89,17 @@ struct ConvGeom {
   int one_d, dil, pad;
 };
 
+// Grouped (MoE) mode without row padding: the rows of all experts sit back to back in A and C; M-tile
+// t starts at row0[t] and owns rows[t] (<= 128) rows of expert tile_expert[t].  The TMA box always
+// brings 128 rows (the surplus belongs to the next expert or is zero fill past the end; its products
+// are never stored), so the activations are read and the results written once per REAL row instead
+// of once per 128-row padded segment.  row0 == nullptr: rows of tile t start at t * 128.
+struct GroupTiles {
+  const int* row0;
+  const int* rows;
+  int num_m;        // number of M tiles when row0 is set
+};
+
 template <int BN>
 struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -228,7 +239,7 @@ template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  __nv_bfloat16* __restrict__ C, int ldc, int M, int N, int K, GemmEpilogue epi,
-                 const int* __restrict__ tile_expert, ConvGeom conv, PeerSignal sig, PeerWait wt, int* status) {
+                 const int* __restrict__ tile_expert, GroupTiles gt, ConvGeom conv, PeerSignal sig, PeerWait wt, int* status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
 
@@ -244,7 +255,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
-  const int num_m = (M + BM - 1) / BM;
+  const int num_m = gt.row0 ? gt.num_m : (M + BM - 1) / BM;
   const int num_n = (N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (K + BK - 1) / BK;
@@ -301,7 +312,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_4d(sa, &tmA, fb, cb * BK, x0 + dx, y0 + dy, img);
             }
           } else {
-            tma_load_2d(sa, &tmA, fb, kb * BK, mb * BM);
+            tma_load_2d(sa, &tmA, fb, kb * BK, gt.row0 ? gt.row0[mb] : mb * BM);
           }
           tma_load_3d(sa + Cfg::A_BYTES, &tmB, fb, kb * BK, nb * BN, ex);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -360,6 +371,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after_sync();
       int row = mb * BM + q * 32 + lane;
       bool row_ok = row < M;
+      if (gt.row0) {
+        row = gt.row0[mb] + q * 32 + lane;
+        row_ok = q * 32 + lane < gt.rows[mb] && row < M;
+      }
       if (conv.taps) {
         // row of the tile -> pixel of the patch -> row of the [N*H*W, Cout] output
         const int per_img = conv.tiles_x * conv.tiles_y;
@@ -911,7 +926,7 @@ template <int BN>
 static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, int ldc, int M,
                        int N, int K, int ldw, const GemmEpilogue& epi, int* status, int max_ctas,
                        cudaStream_t stream, int num_experts = 1, const int* tile_expert = nullptr,
-                       const ConvGeom* conv = nullptr, const OmniSync* sync = nullptr) {
+                       const ConvGeom* conv = nullptr, const OmniSync* sync = nullptr, const GroupTiles* gtiles = nullptr) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmB;
   // weights as [E, N, K]; a plain linear layer is E = 1
@@ -920,14 +935,16 @@ static int launch_gemm(const CUtensorMap& tmA, const void* W, __nv_bfloat16* C, 
   if (rc) return rc;
   static unsigned long long prepared = 0;
   if (int e = ensure_dynamic_smem((const void*)gemm_bf16_kernel<BN>, Cfg::SMEM_BYTES, prepared)) return e;
-  const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  GroupTiles gt = {nullptr, nullptr, 0};
+  if (gtiles) gt = *gtiles;
+  const int num_tiles = (gt.row0 ? gt.num_m : (M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
   ConvGeom geom = {};
   if (conv) geom = *conv;
   PeerSignal sig;
   PeerWait wt;
   unpack_sync(sync, sig, wt);
-  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, tile_expert, geom, sig, wt, status);
+  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, ldc, M, N, K, epi, tile_expert, gt, geom, sig, wt, status);
   return (int)cudaGetLastError();
 }
 
@@ -1243,6 +1260,36 @@ extern "C" int omni_gemm_bf16_grouped(const void* A, int lda, const void* W, int
     case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert);
     case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert);
     case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert);
+    default: return RC_BAD_ARG;
+  }
+}
+
+
+// Grouped GEMM over experts whose rows sit back to back (no padding): M rows in A and C in total, M-tile t
+// covers rows [tile_row0[t], tile_row0[t] + tile_rows[t]) of expert tile_expert[t] (-1 = unused tile).
+extern "C" int omni_gemm_bf16_grouped_compact(const void* A, int lda, const void* W, int num_experts, void* C, int ldc,
+                                              int M, int N, int K, const int* tile_expert, const int* tile_row0,
+                                              const int* tile_rows, int num_tiles, int act, int force_bn, int* status,
+                                              void* stream) {
+  using namespace omni;
+  if (M <= 0 || N <= 0 || K <= 0 || num_tiles <= 0) return RC_OK;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldc & 7) || !tile_expert || !tile_row0 || !tile_rows) return RC_BAD_ARG;
+  CUtensorMap tmA;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K,
+                        (uint64_t)lda * 2, BM, BK);
+  if (rc) return rc;
+  GemmEpilogue epi = {};
+  epi.rows_per_batch = 1;
+  epi.act = act;
+  GroupTiles gt = {tile_row0, tile_rows, num_tiles};
+  const int ctas = sm_count();
+  const int bn = force_bn ? force_bn : pick_bn(num_tiles * BM, N, ctas);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* c = static_cast<__nv_bfloat16*>(C);
+  switch (bn) {
+    case 256: return launch_gemm<256>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert, nullptr, nullptr, &gt);
+    case 192: return launch_gemm<192>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert, nullptr, nullptr, &gt);
+    case 128: return launch_gemm<128>(tmA, W, c, ldc, M, N, K, K, epi, status, ctas, s, num_experts, tile_expert, nullptr, nullptr, &gt);
     default: return RC_BAD_ARG;
   }
 }

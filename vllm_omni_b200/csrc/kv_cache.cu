@@ -18,12 +18,22 @@
 
 namespace omni {
 
+// Limits for the checked build (see OMNI_IN_BOUNDS in ptx_sm100.cuh): 0 = unknown / unchecked.  Set by the
+// host through omni_kv_set_bounds before the launches of a step; passed to the kernels by value.
+struct KvBounds {
+  long num_slots;   // pages x page size of the cache the slot mapping addresses
+  int num_blocks;   // pages of the cache the block tables address
+  int* status;      // device status word
+};
+static KvBounds g_kv_bounds = {0, 0, nullptr};
+enum { KID_KV_WRITE = 1, KID_KV_GATHER = 2 };
+
 // ---------------------------------------------------------------------------- write
 // k, v: [T, Hkv, D] with row pitch ld (elements); slot[t] = block * block_size + offset, <0 skips.
 __global__ void __launch_bounds__(256)
 kv_write_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, long ldk, long ldv,
                 __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, const int* __restrict__ slot, int T,
-                int row_elems) {
+                int row_elems, KvBounds bd) {
   const int chunks = row_elems >> 3;  // 16-byte chunks per token
   const long total = (long)T * chunks;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -31,6 +41,7 @@ kv_write_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
     const int c = (int)(i % chunks) * 8;
     const int s = slot[t];
     if (s < 0) continue;
+    if (!OMNI_IN_BOUNDS(bd.num_slots == 0 || s < bd.num_slots, bd.status, KID_KV_WRITE)) continue;
     *reinterpret_cast<uint4*>(kc + (size_t)s * row_elems + c) = *reinterpret_cast<const uint4*>(k + (size_t)t * ldk + c);
     *reinterpret_cast<uint4*>(vc + (size_t)s * row_elems + c) = *reinterpret_cast<const uint4*>(v + (size_t)t * ldv + c);
   }
@@ -41,13 +52,15 @@ kv_write_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
 __global__ void __launch_bounds__(256)
 kv_gather_kernel(const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                  const int* __restrict__ block_table, int block_size, int T, int row_elems,
-                 __nv_bfloat16* __restrict__ out_k, __nv_bfloat16* __restrict__ out_v) {
+                 __nv_bfloat16* __restrict__ out_k, __nv_bfloat16* __restrict__ out_v, KvBounds bd) {
   const int chunks = row_elems >> 3;
   const long total = (long)T * chunks;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const int t = (int)(i / chunks);
     const int c = (int)(i % chunks) * 8;
-    const size_t s = (size_t)block_table[t / block_size] * block_size + (t % block_size);
+    const int blk = block_table[t / block_size];
+    if (!OMNI_IN_BOUNDS(blk >= 0 && (bd.num_blocks == 0 || blk < bd.num_blocks), bd.status, KID_KV_GATHER)) continue;
+    const size_t s = (size_t)blk * block_size + (t % block_size);
     *reinterpret_cast<uint4*>(out_k + (size_t)t * row_elems + c) = *reinterpret_cast<const uint4*>(kc + s * row_elems + c);
     *reinterpret_cast<uint4*>(out_v + (size_t)t * row_elems + c) = *reinterpret_cast<const uint4*>(vc + s * row_elems + c);
   }
@@ -206,6 +219,21 @@ paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restr
 
 using namespace omni;
 
+// 1 when this library was compiled with -DOMNI_BOUNDS_CHECK
+extern "C" int omni_kv_bounds_check_enabled(void) {
+#ifdef OMNI_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+extern "C" void omni_kv_set_bounds(long num_slots, int num_blocks, int* status) {
+  g_kv_bounds.num_slots = num_slots;
+  g_kv_bounds.num_blocks = num_blocks;
+  g_kv_bounds.status = status;
+}
+
 extern "C" int omni_kv_write(const void* k, const void* v, long ldk, long ldv, void* kc, void* vc,
                              const int* slot, int T, int row_elems, void* stream) {
   if (T <= 0) return RC_OK;
@@ -214,7 +242,8 @@ extern "C" int omni_kv_write(const void* k, const void* v, long ldk, long ldv, v
   long blocks = (total + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   kv_write_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, ldk, ldv, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot, T, row_elems);
+      (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, ldk, ldv, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot, T, row_elems,
+      g_kv_bounds);
   return (int)cudaGetLastError();
 }
 
@@ -227,7 +256,7 @@ extern "C" int omni_kv_gather(const void* kc, const void* vc, const int* block_t
   if (blocks > 148 * 8) blocks = 148 * 8;
   kv_gather_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, block_size, T, row_elems,
-      (__nv_bfloat16*)out_k, (__nv_bfloat16*)out_v);
+      (__nv_bfloat16*)out_k, (__nv_bfloat16*)out_v, g_kv_bounds);
   return (int)cudaGetLastError();
 }
 

@@ -116,6 +116,61 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int e_lo, int e
   }
 }
 
+// Plan without padding: the rows of expert e are [off[e], off[e] + cnt[e]); expert e owns ceil(cnt[e] / 128)
+// M tiles; tile t = (expert, first row, rows <= 128).  Unused tiles get expert -1.
+__global__ void __launch_bounds__(1024)
+moe_plan_compact_kernel(const int* __restrict__ ids, int n_pairs, int E, int e_lo, int e_hi, int max_tiles,
+                        int* __restrict__ row_of_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                        int* __restrict__ tile_rows, int* __restrict__ n_rows_out) {
+  __shared__ int cnt[1024];
+  __shared__ int off[1025];
+  __shared__ int toff[1025];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0, tacc = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = acc;
+      toff[e] = tacc;
+      acc += cnt[e];
+      tacc += (cnt[e] + MOE_TILE - 1) / MOE_TILE;
+    }
+    off[E] = acc;
+    toff[E] = tacc;
+    *n_rows_out = acc;
+  }
+  __syncthreads();
+  for (int tile = threadIdx.x; tile < max_tiles; tile += blockDim.x) {
+    int ex = -1, r0 = 0, nr = 0;
+    if (tile < toff[E]) {
+      int lo = 0, hi = E - 1;            // the last e with toff[e] <= tile that owns tiles
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (toff[mid] <= tile) lo = mid; else hi = mid - 1;
+      }
+      ex = lo;
+      const int within = tile - toff[ex];
+      r0 = off[ex] + within * MOE_TILE;
+      nr = min(MOE_TILE, cnt[ex] - within * MOE_TILE);
+    }
+    tile_expert[tile] = ex;
+    tile_row0[tile] = r0;
+    tile_rows[tile] = nr;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;   // reuse as cursors
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    row_of_pair[i] = (e >= e_lo && e < e_hi) ? off[e] + atomicAdd(&cnt[e], 1) : -1;
+  }
+}
+
 // x: [T, D] (pitch ldx) -> xp[row_of_pair[t*k+j], :] ; rows not written stay as they are (the GEMM
 // output rows of padding are never read back)
 __global__ void __launch_bounds__(256)
@@ -231,6 +286,14 @@ extern "C" int omni_moe_plan(const int* ids, int n_pairs, int E, int e_lo, int e
                              int* tile_expert, int* offsets, int* n_rows_out, void* stream) {
   if (E > 1024) return RC_BAD_ARG;
   moe_plan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, n_pairs, E, e_lo, e_hi, max_tiles, row_of_pair, tile_expert, offsets, n_rows_out);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int omni_moe_plan_compact(const int* ids, int n_pairs, int E, int e_lo, int e_hi, int max_tiles, int* row_of_pair,
+                                     int* tile_expert, int* tile_row0, int* tile_rows, int* n_rows_out, void* stream) {
+  if (E > 1024) return RC_BAD_ARG;
+  moe_plan_compact_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, n_pairs, E, e_lo, e_hi, max_tiles, row_of_pair, tile_expert,
+                                                                tile_row0, tile_rows, n_rows_out);
   return (int)cudaGetLastError();
 }
 

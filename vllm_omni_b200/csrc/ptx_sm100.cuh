@@ -27,7 +27,23 @@ enum ErrCode : int {
   ERR_WAIT_SOFTMAX = 6,
   ERR_WAIT_PV = 7,
   ERR_BAD_ARG = 8,
+  ERR_BOUNDS = 9,         // checked builds (-DOMNI_BOUNDS_CHECK): an index operand pointed outside its buffer
 };
+
+// Checked builds (compute-sanitizer is not available to this project): a kernel that takes its
+// addresses from index operands (slot mappings, block tables, routing tables) tests them against
+// the limits its launcher passes, records the FIRST failure in the status word as
+//   ERR_BOUNDS | kernel_id << 8 | (blockIdx.x & 0xffff) << 16
+// and skips the access, so a bad index never becomes a fault.  Release builds compile the test out.
+#ifdef OMNI_BOUNDS_CHECK
+#define OMNI_IN_BOUNDS(ok, status, kernel_id) (omni::bounds_ok((ok), (status), (kernel_id)))
+#else
+#define OMNI_IN_BOUNDS(ok, status, kernel_id) (true)
+#endif
+__device__ __forceinline__ bool bounds_ok(bool ok, int* status, int kernel_id) {
+  if (!ok && status) atomicCAS(status, 0, (int)(ERR_BOUNDS | (kernel_id << 8) | ((blockIdx.x & 0xffffu) << 16)));
+  return ok;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -128,7 +128,7 @@ class DecodeGraphRunner:
                 torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             try:
-                with torch.cuda.graph(g):
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):   # other stages' threads keep issuing CUDA calls
                     self._step(st)
             except Exception as e:   # noqa: BLE001  (a step that cannot be captured runs eagerly from here on)
                 import logging

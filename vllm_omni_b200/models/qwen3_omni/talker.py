@@ -236,7 +236,7 @@ class CodePredictor(nn.Module):
                 else:
                     torch.cuda.synchronize()
                     g_ = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g_):
+                    with torch.cuda.graph(g_, capture_error_mode="thread_local"):   # other stages' threads keep issuing CUDA calls
                         self._loop_body(st, sampling)
                     st.graph, st.graph_mode = g_, sampling
                     st.graph.replay()

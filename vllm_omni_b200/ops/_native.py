@@ -7,6 +7,7 @@ PyTorch reference implementations so that the host-side logic stays testable.
 from __future__ import annotations
 
 import ctypes
+import os
 import functools
 from pathlib import Path
 
@@ -80,9 +81,20 @@ class _CountingLib:
         return fn
 
 
+def bounds_check_enabled() -> bool:
+    """``OMNI_BOUNDS_CHECK=1``: load the checked twins (built with -DOMNI_BOUNDS_CHECK) of the libraries
+    that have one; their kernels test index operands against the limits the wrappers pass and report
+    ``ERR_BOUNDS`` through the status word instead of touching memory outside a buffer."""
+    return os.environ.get("OMNI_BOUNDS_CHECK", "0") == "1"
+
+
 @functools.lru_cache(maxsize=None)
 def lib(name: str) -> _CountingLib:
     p: Path = lib_path(name)
+    if bounds_check_enabled():
+        twin = lib_path(name, checked=True)
+        if twin.exists():
+            p = twin
     if not p.exists():
         raise NativeError(
             f"{p} is missing: run `python -m vllm_omni_b200.build` (nvcc, sm_100a) before using the GPU ops")

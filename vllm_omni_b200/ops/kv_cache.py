@@ -16,6 +16,13 @@ from . import _native as nv
 c_int, c_long, c_float = ctypes.c_int, ctypes.c_long, ctypes.c_float
 
 
+def _set_bounds(k_cache) -> None:
+    """Checked build only: tell the library how many slots / pages the cache holds."""
+    if nv.bounds_check_enabled():
+        nb, bs = k_cache.shape[0], k_cache.shape[1]
+        nv.lib("kv_cache").omni_kv_set_bounds(c_long(nb * bs), c_int(nb), nv.ptr(nv.status_word(k_cache.device)))
+
+
 def kv_write(k, v, k_cache, v_cache, slots):
     """k, v: [T, Hkv, D]; caches: [num_blocks, block_size, Hkv, D]; slots int32 [T] (<0 = skip)."""
     T = k.shape[0]
@@ -27,6 +34,7 @@ def kv_write(k, v, k_cache, v_cache, slots):
         vf[slots[ok].long()] = v.reshape(T, row)[ok]
         return
     assert k.stride(-1) == 1 and k.stride(1) == k.shape[2] and slots.dtype == torch.int32
+    _set_bounds(k_cache)
     rc = nv.lib("kv_cache").omni_kv_write(nv.ptr(k), nv.ptr(v), c_long(k.stride(0)), c_long(v.stride(0)),
                                           nv.ptr(k_cache), nv.ptr(v_cache), nv.ptr(slots), c_int(T), c_int(row),
                                           nv.stream_ptr())
@@ -45,6 +53,7 @@ def kv_gather(k_cache, v_cache, block_table, T, out_k=None, out_v=None):
         out_k.copy_(k_cache.view(-1, Hkv, D)[idx])
         out_v.copy_(v_cache.view(-1, Hkv, D)[idx])
         return out_k, out_v
+    _set_bounds(k_cache)
     rc = nv.lib("kv_cache").omni_kv_gather(nv.ptr(k_cache), nv.ptr(v_cache), nv.ptr(block_table), c_int(bs), c_int(T),
                                            c_int(Hkv * D), nv.ptr(out_k), nv.ptr(out_v), nv.stream_ptr())
     nv.check_rc(rc, "omni_kv_gather")

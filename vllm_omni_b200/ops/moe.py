@@ -47,17 +47,34 @@ def moe_reference(x, router_w, w13, w2, k, renorm=True, e_lo=0, e_hi=None):
     return out.to(x.dtype)
 
 
+def padded_rows() -> bool:
+    """``OMNI_MOE_PADDED=1`` keeps the first layout (every expert's rows padded to a multiple of 128);
+    the default packs the rows of all experts back to back."""
+    import os
+    return os.environ.get("OMNI_MOE_PADDED", "0") == "1"
+
+
 class MoEWorkspace:
     def __init__(self):
         self.key = None
 
     def get(self, T, k, E, D, Fd, device, dtype):
-        key = (T, k, E, D, Fd, str(device), dtype)
+        pad = padded_rows()
+        key = (T, k, E, D, Fd, str(device), dtype, pad)
         if self.key != key:
             self.key = key
+            self.padded = pad
             n_pairs = T * k
-            self.max_rows = ((n_pairs + E * 127) + 127) // 128 * 128
-            self.max_tiles = self.max_rows // 128
+            if pad:
+                self.max_rows = ((n_pairs + E * 127) + 127) // 128 * 128
+                self.max_tiles = self.max_rows // 128
+            else:
+                # rows back to back: every (token, choice) pair is one row; an expert starts a new M tile, so at
+                # most one partly filled tile per expert that got rows
+                self.max_rows = n_pairs
+                self.max_tiles = min(E, n_pairs) + (n_pairs + 127) // 128
+            self.tile_row0 = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
+            self.tile_rows = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
             i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=device)
             self.ids, self.row_of_pair = i32(T, k), i32(n_pairs)
             self.tile_expert, self.offsets, self.n_rows = i32(self.max_tiles), i32(E + 1), i32(1)
@@ -104,25 +121,39 @@ def moe_forward(x, router_logits, w13, w2, k, renorm=True, e_lo=0, e_hi=None, ws
     assert router_logits.dtype == torch.bfloat16 and router_logits.stride(1) == 1
     nv.check_rc(lib.omni_moe_route(nv.ptr(router_logits), c_int(router_logits.stride(0)), c_int(T), c_int(E), c_int(k),
                                    c_int(1 if renorm else 0), nv.ptr(ws.ids), nv.ptr(ws.weights), st), "omni_moe_route")
-    nv.check_rc(lib.omni_moe_plan(nv.ptr(ws.ids), c_int(T * k), c_int(E), c_int(e_lo), c_int(e_hi),
-                                  c_int(ws.max_tiles), nv.ptr(ws.row_of_pair), nv.ptr(ws.tile_expert),
-                                  nv.ptr(ws.offsets), nv.ptr(ws.n_rows), st), "omni_moe_plan")
-    nv.check_rc(lib.omni_moe_dispatch(nv.ptr(x), c_long(x.stride(0)), nv.ptr(ws.row_of_pair), c_int(T * k), c_int(k),
-                                      c_int(D), nv.ptr(ws.xp), st), "omni_moe_dispatch")
     g = nv.lib("gemm_sm100")
     status = nv.status_word(x.device)
+    El = w13.shape[0]
+    if ws.padded:
+        nv.check_rc(lib.omni_moe_plan(nv.ptr(ws.ids), c_int(T * k), c_int(E), c_int(e_lo), c_int(e_hi),
+                                      c_int(ws.max_tiles), nv.ptr(ws.row_of_pair), nv.ptr(ws.tile_expert),
+                                      nv.ptr(ws.offsets), nv.ptr(ws.n_rows), st), "omni_moe_plan")
+    else:
+        nv.check_rc(lib.omni_moe_plan_compact(nv.ptr(ws.ids), c_int(T * k), c_int(E), c_int(e_lo), c_int(e_hi),
+                                              c_int(ws.max_tiles), nv.ptr(ws.row_of_pair), nv.ptr(ws.tile_expert),
+                                              nv.ptr(ws.tile_row0), nv.ptr(ws.tile_rows), nv.ptr(ws.n_rows), st),
+                    "omni_moe_plan_compact")
+    nv.check_rc(lib.omni_moe_dispatch(nv.ptr(x), c_long(x.stride(0)), nv.ptr(ws.row_of_pair), c_int(T * k), c_int(k),
+                                      c_int(D), nv.ptr(ws.xp), st), "omni_moe_dispatch")
     # tile_expert holds GLOBAL expert ids; the local weight tensors start at e_lo
     te = ws.tile_expert
     if e_lo:
         te = torch.where(te >= 0, te - e_lo, te)
-    El = w13.shape[0]
-    nv.check_rc(g.omni_gemm_bf16_grouped(nv.ptr(ws.xp), c_int(D), nv.ptr(w13), c_int(El), nv.ptr(ws.h13),
-                                         c_int(2 * Fd), c_int(ws.max_rows), c_int(2 * Fd), c_int(D), nv.ptr(te),
-                                         c_int(0), c_int(0), nv.ptr(status), st), "omni_gemm_bf16_grouped")
+
+    def grouped(a, lda, w, c, ldc, n, kk):
+        if ws.padded:
+            nv.check_rc(g.omni_gemm_bf16_grouped(nv.ptr(a), c_int(lda), nv.ptr(w), c_int(El), nv.ptr(c), c_int(ldc),
+                                                 c_int(ws.max_rows), c_int(n), c_int(kk), nv.ptr(te), c_int(0), c_int(0),
+                                                 nv.ptr(status), st), "omni_gemm_bf16_grouped")
+        else:
+            nv.check_rc(g.omni_gemm_bf16_grouped_compact(nv.ptr(a), c_int(lda), nv.ptr(w), c_int(El), nv.ptr(c), c_int(ldc),
+                                                         c_int(ws.max_rows), c_int(n), c_int(kk), nv.ptr(te),
+                                                         nv.ptr(ws.tile_row0), nv.ptr(ws.tile_rows), c_int(ws.max_tiles),
+                                                         c_int(0), c_int(0), nv.ptr(status), st),
+                        "omni_gemm_bf16_grouped_compact")
+    grouped(ws.xp, D, w13, ws.h13, 2 * Fd, 2 * Fd, D)
     fused.silu_mul(ws.h13, out=ws.h)
-    nv.check_rc(g.omni_gemm_bf16_grouped(nv.ptr(ws.h), c_int(Fd), nv.ptr(w2), c_int(El), nv.ptr(ws.y), c_int(D),
-                                         c_int(ws.max_rows), c_int(D), c_int(Fd), nv.ptr(te), c_int(0), c_int(0),
-                                         nv.ptr(status), st), "omni_gemm_bf16_grouped")
+    grouped(ws.h, Fd, w2, ws.y, D, D, Fd)
     if scatter is not None:
         per, ptrs = scatter
         arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
