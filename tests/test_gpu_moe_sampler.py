@@ -6,7 +6,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("padded", ["0", "1"])
-@pytest.mark.parametrize("T,E,k", [(37, 16, 4), (700, 4, 2), (5, 16, 2)])
+@pytest.mark.parametrize("T,E,k", [(37, 16, 4), (700, 8, 2), (5, 16, 2)])
 def test_moe_forward_matches_reference(monkeypatch, padded, T, E, k):
     """Both row layouts (experts' rows back to back: the default; padded to 128 per expert), experts with
     more than one M tile of rows, and batches smaller than the number of experts."""

@@ -35,6 +35,7 @@ class LLMEngine:
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda" if torch.cuda.is_available() else "cpu")
         self.dtype = dtype
+        self.max_num_batched_tokens = max_num_batched_tokens
         self.tokenizer = tokenizer or get_tokenizer(None)
         if hasattr(model, "text_tokenizer"):             # models that tokenize request fields themselves (TTS instructions)
             model.text_tokenizer = self.tokenizer
@@ -61,6 +62,15 @@ class LLMEngine:
         self._reqs: dict[str, Request] = {}
         self._errors: list[RequestOutput] = []
 
+    def _activation_reserve(self, dec) -> int:
+        rows = int(getattr(self, "max_num_batched_tokens", 8192) or 8192)
+        es = torch.empty(0, dtype=self.dtype).element_size()
+        D = dec.hidden_size
+        per_row = 12 * D + 4 * max(dec.intermediate_size or 0, (dec.num_experts_per_tok or 0) * (dec.moe_intermediate_size or 0))
+        if dec.num_experts:
+            per_row += 2 * (dec.num_experts_per_tok or 1) * (2 * D + 3 * (dec.moe_intermediate_size or 0))   # two token buckets live
+        return int(rows * per_row * es) + (2 << 30)
+
     def _profile_num_blocks(self, dec, block_size, util, max_model_len, max_num_seqs) -> int:
         per_block = 2 * dec.num_hidden_layers * block_size * dec.num_key_value_heads * dec.head_dim * \
             torch.empty(0, dtype=self.dtype).element_size()
@@ -69,6 +79,9 @@ class LLMEngine:
             free, total = torch.cuda.mem_get_info(self.device)
             # per-process accounting: stages that share this GPU may be initialising concurrently
             budget = kv_cache_budget(total, free, util, self.device.index or 0)
+            # the share covers the stage's activations too (prefill scratch of max_num_batched_tokens rows,
+            # MoE dispatch buffers, logits of the sampled rows, library workspaces): leave room for them
+            budget = max(0, budget - self._activation_reserve(dec))
         else:
             budget = 256 << 20
         want = (max_model_len // block_size + 1) * max_num_seqs

@@ -54,35 +54,59 @@ def padded_rows() -> bool:
     return os.environ.get("OMNI_MOE_PADDED", "0") == "1"
 
 
+class _MoEBuffers:
+    """Scratch of the MoE chain for up to ``cap`` tokens.  Every allocation lands in a local first: an
+    out-of-memory error half way must not leave an object whose key says "ready" over short buffers."""
+
+    def __init__(self, cap, k, E, D, Fd, device, dtype, pad):
+        n_pairs = cap * k
+        rows, tiles = _rows_tiles(cap, k, E, pad)
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=device)
+        t = dict(ids=i32(cap, k), row_of_pair=i32(n_pairs), tile_expert=i32(tiles), tile_row0=i32(tiles), tile_rows=i32(tiles),
+                 offsets=i32(E + 1), n_rows=i32(1), weights=torch.empty(cap, k, dtype=torch.float32, device=device),
+                 xp=torch.zeros(rows, D, dtype=dtype, device=device), h13=torch.empty(rows, 2 * Fd, dtype=dtype, device=device),
+                 h=torch.empty(rows, Fd, dtype=dtype, device=device), y=torch.empty(rows, D, dtype=dtype, device=device))
+        self.__dict__.update(t)
+
+
+def _rows_tiles(T, k, E, pad):
+    n_pairs = T * k
+    if pad:
+        rows = ((n_pairs + E * 127) + 127) // 128 * 128
+        return rows, rows // 128
+    # rows back to back: every (token, choice) pair is one row; an expert starts a new M tile, so at most one
+    # partly filled tile per expert that got rows
+    return n_pairs, min(E, n_pairs) + (n_pairs + 127) // 128
+
+
+_pool: dict = {}
+
+
 class MoEWorkspace:
+    """Handle a layer keeps for its MoE scratch.  The buffers themselves are shared by every layer of
+    the process (layers run one after the other on a stream) and sized by power-of-two token buckets
+    that are never freed: a CUDA graph captured at one batch size keeps pointing at live memory when a
+    larger prefill comes along, and a 48-layer model holds one set of scratch, not 48."""
+
     def __init__(self):
         self.key = None
 
     def get(self, T, k, E, D, Fd, device, dtype):
         pad = padded_rows()
-        key = (T, k, E, D, Fd, str(device), dtype, pad)
-        if self.key != key:
-            self.key = key
-            self.padded = pad
-            n_pairs = T * k
-            if pad:
-                self.max_rows = ((n_pairs + E * 127) + 127) // 128 * 128
-                self.max_tiles = self.max_rows // 128
-            else:
-                # rows back to back: every (token, choice) pair is one row; an expert starts a new M tile, so at
-                # most one partly filled tile per expert that got rows
-                self.max_rows = n_pairs
-                self.max_tiles = min(E, n_pairs) + (n_pairs + 127) // 128
-            self.tile_row0 = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
-            self.tile_rows = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
-            i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=device)
-            self.ids, self.row_of_pair = i32(T, k), i32(n_pairs)
-            self.tile_expert, self.offsets, self.n_rows = i32(self.max_tiles), i32(E + 1), i32(1)
-            self.weights = torch.empty(T, k, dtype=torch.float32, device=device)
-            self.xp = torch.zeros(self.max_rows, D, dtype=dtype, device=device)
-            self.h13 = torch.empty(self.max_rows, 2 * Fd, dtype=dtype, device=device)
-            self.h = torch.empty(self.max_rows, Fd, dtype=dtype, device=device)
-            self.y = torch.empty(self.max_rows, D, dtype=dtype, device=device)
+        cap = max(64, 1 << (max(T, 1) - 1).bit_length())
+        key = (cap, k, E, D, Fd, str(device), dtype, pad)
+        buf = _pool.get(key)
+        if buf is None:
+            buf = _pool[key] = _MoEBuffers(cap, k, E, D, Fd, device, dtype, pad)
+        self.key, self.padded = (T,) + key, pad
+        self.max_rows, self.max_tiles = _rows_tiles(T, k, E, pad)
+        n_pairs = T * k
+        self.ids, self.weights, self.row_of_pair = buf.ids[:T], buf.weights[:T], buf.row_of_pair[:n_pairs]
+        self.tile_expert, self.tile_row0, self.tile_rows = (buf.tile_expert[:self.max_tiles], buf.tile_row0[:self.max_tiles],
+                                                            buf.tile_rows[:self.max_tiles])
+        self.offsets, self.n_rows = buf.offsets, buf.n_rows
+        self.xp, self.h13, self.h, self.y = (buf.xp[:self.max_rows], buf.h13[:self.max_rows], buf.h[:self.max_rows],
+                                             buf.y[:self.max_rows])
         return self
 
 
