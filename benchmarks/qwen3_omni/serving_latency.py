@@ -42,7 +42,7 @@ stage_args:
     default_sampling_params: {temperature: 0.0, max_tokens: MAXTOK, ignore_eos: true, detokenize: false}
   - stage_id: 1
     stage_type: llm
-    runtime: {devices: "0", max_batch_size: MAXB, process: STAGE_PROC}
+    runtime: {devices: "TAIL_DEV", max_batch_size: MAXB, process: STAGE_PROC}
     engine_args: {model_stage: talker, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: ar,
                   engine_output_type: latent, device: DEVICE, gpu_memory_utilization: 0.3, load_format: dummy,
                   model_overrides: OVERRIDES}
@@ -52,7 +52,7 @@ stage_args:
                               stop_token_ids: [], detokenize: false}
   - stage_id: 2
     stage_type: llm
-    runtime: {devices: "0", max_batch_size: MAXB, process: STAGE_PROC}
+    runtime: {devices: "TAIL_DEV", max_batch_size: MAXB, process: STAGE_PROC}
     engine_args: {model_stage: code2wav, model_arch: Qwen3OmniMoeForConditionalGeneration, worker_type: generation,
                   engine_output_type: audio, device: DEVICE, load_format: dummy, model_overrides: OVERRIDES}
     engine_input_source: [1]
@@ -171,7 +171,8 @@ async def _run(a, path):
            "e2el_s": {f"p{q}": _pct([r["latency"] for r in recs], q) for q in (50, 90, 99)},
            "stages": _stage_split(eng_stats), "timed_out": timed_out,
            "config": {"tiny": a.tiny, "input_len": a.input_len, "audio_seconds": a.audio_seconds,
-                      "thinker_tp": a.thinker_tp, "thinker_ep": a.thinker_ep, "max_tokens": a.max_tokens, "codec_frames": a.codec_frames,
+                      "thinker_tp": a.thinker_tp, "thinker_ep": a.thinker_ep, "tail_device": a.tail_device,
+                      "stage_processes": a.stage_processes, "max_tokens": a.max_tokens, "codec_frames": a.codec_frames,
                       "max_concurrency": a.max_concurrency, "request_rate": a.request_rate, "async_chunk": a.async_chunk,
                       "data": "synthetic token ids; random-init weights"}}
     print(json.dumps(out))
@@ -196,6 +197,7 @@ def main(argv=None):
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--stage-processes", action="store_true", help="every stage in a process of its own (own interpreter lock); "
                     "the default on a GPU")
+    ap.add_argument("--tail-device", type=int, default=0, help="GPU of the talker and code2wav stages (the thinker uses GPUs 0..tp-1)")
     ap.add_argument("--stage-threads", action="store_true", help="keep the stages on threads of this process on a GPU too")
     ap.add_argument("--progress", type=float, default=0.0, help="seconds between progress lines on stderr (0 = none)")
     ap.add_argument("--time-limit", type=float, default=0.0, help="stop waiting after this many seconds and report what finished")
@@ -211,7 +213,7 @@ def main(argv=None):
          .replace("THINKER_EP", "true" if a.thinker_ep else "false")
          .replace("THINKER_DEVS", ",".join(str(i) for i in range(a.thinker_tp)))
          .replace("THINKER_PROC", "true" if (a.thinker_tp > 1 or a.stage_processes) else "false")
-         .replace("STAGE_PROC", "true" if a.stage_processes else "false"))
+         .replace("STAGE_PROC", "true" if a.stage_processes else "false").replace("TAIL_DEV", str(a.tail_device)))
     f = tempfile.NamedTemporaryFile("w", suffix=".yaml", delete=False)
     f.write(y)
     f.close()
