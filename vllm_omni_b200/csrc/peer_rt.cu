@@ -79,11 +79,20 @@ peer_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t 
 __global__ void __launch_bounds__(256)
 peer_copy_2d_kernel(unsigned char* __restrict__ dst, size_t dst_pitch, const unsigned char* __restrict__ src, size_t src_pitch,
                     int row16, long rows) {
-  const long total = rows * (long)row16;
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-    const long r = i / row16;
-    const int c = (int)(i - r * row16);
-    reinterpret_cast<uint4*>(dst + r * dst_pitch)[c] = reinterpret_cast<const uint4*>(src + r * src_pitch)[c];
+  // blockIdx.y walks the segments, blockIdx.x the 16-byte words of a segment; four independent 16-byte loads per
+  // thread are in flight before the first store (remote loads have microseconds of latency)
+  for (long r = blockIdx.y; r < rows; r += gridDim.y) {
+    const uint4* s = reinterpret_cast<const uint4*>(src + r * src_pitch);
+    uint4* d = reinterpret_cast<uint4*>(dst + r * dst_pitch);
+    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4; c < row16; c += gridDim.x * blockDim.x * 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + j < row16) v[j] = s[c + j];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + j < row16) d[c + j] = v[j];
+    }
   }
 }
 
@@ -98,11 +107,17 @@ extern "C" int omni_peer_copy_2d(void* dst, size_t dst_pitch, const void* src, s
   if ((reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (dst_pitch & 15) ||
       (src_pitch & 15) || (row_bytes & 15) || row_bytes > dst_pitch || row_bytes > src_pitch || (row_bytes >> 4) > 0x7fffffff)
     return RC_BAD_ARG;
-  const long total = rows * (long)(row_bytes >> 4);
-  long blocks = (total + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  peer_copy_2d_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-      static_cast<unsigned char*>(dst), dst_pitch, static_cast<const unsigned char*>(src), src_pitch, (int)(row_bytes >> 4), rows);
+  const int row16 = (int)(row_bytes >> 4);
+  // about 16 blocks per SM in total: few long segments spread over blockIdx.x, many short ones over blockIdx.y
+  const long budget = 148 * 16;
+  long gx = (row16 + 1023) / 1024;                    // 256 threads x 4 words per block
+  long gy = rows < 65535 ? rows : 65535;
+  if (gx * gy > budget) {
+    if (gy >= budget) { gx = 1; gy = budget; }
+    else gx = (budget + gy - 1) / gy < gx ? (budget + gy - 1) / gy : gx;
+  }
+  peer_copy_2d_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, (cudaStream_t)stream>>>(
+      static_cast<unsigned char*>(dst), dst_pitch, static_cast<const unsigned char*>(src), src_pitch, row16, rows);
   return (int)cudaGetLastError();
 }
 

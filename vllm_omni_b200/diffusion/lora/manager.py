@@ -159,6 +159,9 @@ class DiffusionLoRAManager:
                     Bp[:, :r] = Bf
                     m.lora = (m.lora or []) + [(Ap, Bp, ad.scaling * scale)]
         self.active = resolved
+        tr = getattr(self.pipeline, "transformer", None) if hasattr(self, "pipeline") else None
+        if tr is not None:
+            tr._lora_active = bool(resolved)       # captured forwards bake the linears in: run eagerly with adapters
 
     def activate_request(self, req: LoRARequest, scale: float = 1.0) -> None:
         self.add_adapter_from_request(req, scale)

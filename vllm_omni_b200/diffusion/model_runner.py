@@ -39,6 +39,10 @@ class DiffusionModelRunner:
             from .cache.selector import get_cache_backend
             self.cache_backend = get_cache_backend(cfg.cache_backend, cfg.cache_config)
             self.cache_backend.enable(self.pipeline)
+        if not (cfg.enable_cpu_offload or cfg.enable_layerwise_offload):
+            from .graphed import maybe_graph_transformer
+            if maybe_graph_transformer(self.pipeline, cfg):
+                logger.info("denoiser forward will be replayed from CUDA graphs")
         if cfg.omni_kv_config:
             from ..connectors.kv_transfer_manager import OmniKVTransferManager
             self.kv_transfer_manager = OmniKVTransferManager.from_config(cfg.omni_kv_config)

@@ -307,9 +307,13 @@ class QwenDecoderModel(nn.Module):
                           out=o[None, s:s + n])
         if batch.decode_rows is not None and batch.decode_rows.numel():
             rows = batch.decode_rows
-            qd = q[rows].contiguous()
-            od = KC.paged_decode(qd, k_cache, v_cache, batch.decode_block_tables, batch.decode_seq_lens, scale=scale)
-            o[rows] = od
+            if not batch.prefills and rows.numel() == T and q.is_cuda:
+                # a decode-only step: the rows ARE the batch in order; read q and write o in place
+                KC.paged_decode(q, k_cache, v_cache, batch.decode_block_tables, batch.decode_seq_lens, scale=scale, out=o)
+            else:
+                qd = q[rows].contiguous()
+                od = KC.paged_decode(qd, k_cache, v_cache, batch.decode_block_tables, batch.decode_seq_lens, scale=scale)
+                o[rows] = od
         return out
 
     def forward(self, batch: ModelBatch, kv_caches=None, capture_layers=(), deepstack=None):
