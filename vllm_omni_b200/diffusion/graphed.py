@@ -133,8 +133,8 @@ def maybe_graph_transformer(pipe, od_config) -> bool:
     tr = getattr(pipe, "transformer", None)
     if tr is None or getattr(od_config, "enforce_eager", False) or os.environ.get("OMNI_DIT_CUDA_GRAPH", "1") == "0":
         return False
-    if hasattr(tr, "prepare_loop") or isinstance(getattr(tr, "forward", None), GraphedForward):
-        return False                                  # has a captured loop of its own / already wrapped
+    if hasattr(pipe, "_loop_state") or isinstance(getattr(tr, "forward", None), GraphedForward):
+        return False                                  # the pipeline drives a captured loop of its own / already wrapped
     try:
         dev = next(tr.parameters()).device
     except StopIteration:
