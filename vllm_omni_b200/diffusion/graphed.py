@@ -7,7 +7,8 @@ plus the plain values of the other arguments) is captured into a CUDA graph on i
 replayed afterwards: inputs are copied into the static tensors the capture ran on, the output is the
 capture's static output (valid until the next call with the same signature).
 
-Only forwards whose arguments are tensors, ``None``, numbers, strings, or (nested) tuples / lists of
+A model opts in with the class attribute ``graph_safe_forward = True`` (its forward keeps no state
+between calls of one signature).  Only forwards whose arguments are tensors, ``None``, numbers, strings, or (nested) tuples / lists of
 those are graphed; anything else runs eagerly.  Qwen-Image keeps its own captured loop
 (``prepare_loop`` / ``forward_step``).
 """
@@ -133,6 +134,8 @@ def maybe_graph_transformer(pipe, od_config) -> bool:
     tr = getattr(pipe, "transformer", None)
     if tr is None or getattr(od_config, "enforce_eager", False) or os.environ.get("OMNI_DIT_CUDA_GRAPH", "1") == "0":
         return False
+    if not getattr(tr, "graph_safe_forward", False):
+        return False                                  # forwards that keep state between calls (condition-image K/V caches ...)
     if hasattr(pipe, "_loop_state") or isinstance(getattr(tr, "forward", None), GraphedForward):
         return False                                  # the pipeline drives a captured loop of its own / already wrapped
     try:

@@ -58,6 +58,7 @@ class SingleBlock(nn.Module):
 
 
 class FluxTransformer2DModel(QwenImageTransformer2DModel):
+    graph_safe_forward = True          # stateless between calls of one signature: may be replayed from a CUDA graph
     def __init__(self, cfg: FluxTransformerConfig | None = None, dtype=torch.bfloat16, device=None):
         cfg = cfg or FluxTransformerConfig()
         super().__init__(cfg, dtype=dtype, device=device)

@@ -125,6 +125,7 @@ class SingleBlock(nn.Module):
 
 
 class Flux2Transformer2DModel(nn.Module):
+    graph_safe_forward = True          # stateless between calls of one signature: may be replayed from a CUDA graph
     def __init__(self, cfg: Flux2TransformerConfig | None = None, dtype=torch.bfloat16, device=None):
         super().__init__()
         self.cfg = c = cfg or Flux2TransformerConfig()

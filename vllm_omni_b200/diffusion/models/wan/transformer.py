@@ -83,6 +83,7 @@ class WanBlock(nn.Module):
 
 
 class WanTransformer3DModel(nn.Module):
+    graph_safe_forward = True          # stateless between calls of one signature: may be replayed from a CUDA graph
     def __init__(self, cfg: WanTransformerConfig | None = None, dtype=torch.bfloat16, device=None):
         super().__init__()
         self.cfg = cfg = cfg or WanTransformerConfig()

@@ -92,6 +92,7 @@ class ZBlock(nn.Module):
 
 
 class ZImageTransformer2DModel(nn.Module):
+    graph_safe_forward = True          # stateless between calls of one signature: may be replayed from a CUDA graph
     _sp_plan = {"": {"hidden_states": SequenceParallelInput(split_dim=1, expected_dims=3, auto_pad=True)},
                 "proj_out": SequenceParallelOutput(gather_dim=1)}
 
