@@ -224,3 +224,103 @@ def test_ar_stage_cache_equals_the_generation_stage_prefill(pair):
     ctx = m.prefill_text(ids)
     for (kp, vp), (k, v) in zip(sess.caches, ctx):
         assert (kp.flatten(0, 1)[:6] - k).abs().max().item() < 1e-5 and (vp.flatten(0, 1)[:6] - v).abs().max().item() < 1e-5
+
+
+def test_image_context_blocks_match_the_oracle(pair):
+    """Editing context: clean VAE latents (generation weights, timestep 0) and vision tokens (understanding
+    weights), each between the image markers at ONE rotary position with full attention, appended to the cache."""
+    sd, m = pair
+    c = CFG
+    torch.manual_seed(3)
+    h, w = 2, 3
+    N = h * w
+    lat = torch.randn(N, c.patch_latent_dim)
+    ctx = m.prefill_image_latents(lat, (h, w), None, 0)
+    # oracle: [start, latents..., end] at position 0, t = 0
+    emb = sd["language_model.model.embed_tokens.weight"]
+    seq = torch.zeros(N + 2, c.hidden_size)
+    text_idx, vae_idx = torch.tensor([0, N + 1]), torch.arange(1, N + 1)
+    seq[text_idx] = emb[[c.start_of_image, c.end_of_image]]
+    tf = torch.cat([torch.ones(128), torch.zeros(128)])[None]            # sinusoid of t = 0: cosines first
+    temb = F.linear(F.silu(F.linear(tf, sd["time_embedder.mlp.0.weight"], sd["time_embedder.mlp.0.bias"])),
+                    sd["time_embedder.mlp.2.weight"], sd["time_embedder.mlp.2.bias"])
+    pos_ids = (torch.arange(h)[:, None] * c.max_latent_size + torch.arange(w)).flatten()
+    seq[vae_idx] = F.linear(lat, sd["vae2llm.weight"], sd["vae2llm.bias"]) + temb + sd["latent_pos_embed.pos_embed"][pos_ids]
+    _, kv = mot_forward(sd, c, seq, torch.zeros(N + 2, dtype=torch.long), text_idx, vae_idx, None, causal=False)
+    order = torch.cat([vae_idx, text_idx])                               # this build keeps the latent rows first
+    for (k, v), (ko, vo) in zip(ctx, kv):
+        assert k.shape[0] == N + 2 and torch.allclose(k, ko[order], atol=1e-5) and torch.allclose(v, vo[order], atol=1e-5)
+    # vision tokens after it, at position 1, against the grown context
+    vt = torch.randn(5, c.hidden_size)
+    ctx2 = m.prefill_vision_tokens(vt, ctx, 1)
+    seq2 = torch.cat([emb[[c.start_of_image]], vt, emb[[c.end_of_image]]])
+    past = [(ko[order], vo[order]) for ko, vo in kv]
+    _, kv2 = mot_forward(sd, c, seq2, torch.ones(7, dtype=torch.long), torch.arange(7), torch.tensor([], dtype=torch.long), past, causal=False)
+    order2 = torch.tensor([1, 2, 3, 4, 5, 0, 6])
+    for (k, v), (ko, vo) in zip(ctx2, kv2):
+        assert k.shape[0] == N + 2 + 7 and torch.allclose(k[N + 2:], ko[order2], atol=1e-5) and torch.allclose(v[N + 2:], vo[order2], atol=1e-5)
+    # the prompt follows causally from position 2
+    ids = torch.tensor([c.bos_token_id, 5, 9, c.eos_token_id])
+    ctx3 = m.prefill_text(ids, ctx2, 2)
+    assert ctx3[0][0].shape[0] == N + 2 + 7 + 4
+
+
+def test_vision_tower_matches_hf_siglip_encoder():
+    from transformers import SiglipVisionConfig, SiglipVisionModel
+    from vllm_omni_b200.diffusion.models.bagel.vision import BagelVisionTower, BagelVitConfig, flat_position_ids, patchify_pixels
+    torch.manual_seed(4)
+    hf_cfg = SiglipVisionConfig(hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4, patch_size=4,
+                                image_size=24, hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6)
+    hf = SiglipVisionModel(hf_cfg).eval()
+    vc = BagelVitConfig(hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4, patch_size=4,
+                        max_patches_per_side=6)
+    tower = BagelVisionTower(vc, llm_width=40, dtype=torch.float32, device="cpu")
+    sd = {"vit_model." + k: v for k, v in hf.state_dict().items()}
+    sd["connector.fc1.weight"], sd["connector.fc1.bias"] = torch.randn(40, 32) * 0.1, torch.randn(40) * 0.1
+    sd["connector.fc2.weight"], sd["connector.fc2.bias"] = torch.randn(40, 40) * 0.1, torch.randn(40) * 0.1
+    loaded = tower.load_weights(sd.items())
+    skipped = {k for k in sd if k not in loaded}
+    assert all("post_layernorm" in k or ".head." in k for k in skipped), skipped     # the encoder output is used as is
+    px = torch.rand(3, 12, 20) * 2 - 1                                     # 3 x 5 patches, native aspect ratio
+    got = tower(px)
+    with torch.no_grad():
+        ids = flat_position_ids(3, 5, 6)
+        w = hf.vision_model.embeddings.patch_embedding.weight
+        x = F.linear(patchify_pixels(px, 4), w.view(w.shape[0], -1), hf.vision_model.embeddings.patch_embedding.bias)
+        x = x + hf.vision_model.embeddings.position_embedding(ids)
+        y = hf.vision_model.encoder(inputs_embeds=x[None]).last_hidden_state[0]
+        want = F.linear(F.gelu(F.linear(y, sd["connector.fc1.weight"], sd["connector.fc1.bias"]), approximate="tanh"),
+                        sd["connector.fc2.weight"], sd["connector.fc2.bias"]) + tower.vit_pos_embed[ids]
+    assert got.shape == (15, 40) and (got - want).abs().max() < 1e-4
+
+
+def test_bagel_stage_edits_a_reference_image():
+    import numpy as np
+    from PIL import Image
+    from vllm_omni_b200.diffusion.data import OmniDiffusionConfig, TransformerConfig
+    from vllm_omni_b200.diffusion.models.bagel.pipeline import BagelPipeline
+    from vllm_omni_b200.diffusion.request import OmniDiffusionRequest
+    from vllm_omni_b200.inputs import OmniDiffusionSamplingParams
+    torch.manual_seed(1)
+    tf = {k: getattr(CFG, k) for k in CFG.__dataclass_fields__}
+    tf["max_latent_size"] = 32
+    tf["vit_config"] = dict(hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=4, patch_size=14)
+    vae = dict(block_out_channels=(8, 16, 16, 16), layers_per_block=1, norm_num_groups=4)
+    cfg = OmniDiffusionConfig(dtype=torch.float32, tf_model_config=TransformerConfig.from_dict(tf), vae_config=vae, output_type="latent")
+    pipe = BagelPipeline(cfg, device="cpu")
+    rng = np.random.default_rng(0)
+    imgs = [Image.fromarray(rng.integers(0, 255, (250, 300, 3), dtype=np.uint8)) for _ in range(2)]
+    assert pipe._fit_reference(imgs[0], 512, 16).size == (304, 256)        # shortest side up to 256, both multiples of 16
+
+    def run(img, **extra):
+        sp = OmniDiffusionSamplingParams(num_inference_steps=3, seed=2, output_type="latent", extra_args=extra or None)
+        req = OmniDiffusionRequest(prompts=[{"prompt": "make it red", "multi_modal_data": {"image": img}}], sampling_params=sp,
+                                   request_ids=["r"])
+        return pipe(req).output
+    a, b = run(imgs[0]), run(imgs[1])
+    assert a.shape == (1, 4, 32, 38) and torch.isfinite(a).all()           # the result has the reference image's (fitted) size
+    assert (a - b).abs().max() > 0                                         # the image reaches the network
+    assert (a - run(imgs[0], cfg_img_scale=1.0)).abs().max() > 0           # and so does the image-guidance branch
+    ctx, pos = pipe._image_context(pipe._fit_reference(imgs[0], 512, 16))
+    n_lat, n_vit = (256 // 16) * (304 // 16), (256 // 14) * (304 // 14)
+    assert pos == 2 and ctx[0][0].shape[0] == n_lat + 2 + n_vit + 2

@@ -207,19 +207,31 @@ class BagelMoT(nn.Module):
             x = s.down(fused.silu_mul(s.gate_up(h)), residual=x)
         return out
 
-    def _gen_layer(self, li, x, N, cos, sin, past):
-        """One layer in generation mode: latent rows [0, N) on the generation weights, marker rows on the understanding weights."""
+    def _gen_layer(self, li, x, N, cos, sin, past, collect=None):
+        """One layer in generation mode: latent rows [0, N) on the generation weights, the other rows on the
+        understanding weights, full attention among them and over the context.  ``collect``: a list that
+        receives this layer's (k, v) of the rows (batch 0), for callers that grow the context."""
         c = self.cfg
         eps = c.rms_norm_eps
         B, S = x.shape[0], x.shape[1]
         layer = self.layers[li]
         g, u = layer.gen, layer.und
-        hv = fused.norm_modulate(x[:, :N].contiguous(), weight=g.input_layernorm, rms=True, eps=eps)
-        ht = fused.norm_modulate(x[:, N:].contiguous(), weight=u.input_layernorm, rms=True, eps=eps)
-        qkv = torch.cat([g.qkv(hv), u.qkv(ht)], dim=1).contiguous()
-        qkv = self._norm_rope(qkv, cos, sin, g.q_norm, g.k_norm, u.q_norm, u.k_norm, N)
+        if N == 0:                                       # understanding rows only (vision-tower tokens + markers)
+            ht = fused.norm_modulate(x.contiguous(), weight=u.input_layernorm, rms=True, eps=eps)
+            qkv = self._norm_rope(u.qkv(ht).contiguous(), cos, sin, u.q_norm, u.k_norm)
+        else:
+            hv = fused.norm_modulate(x[:, :N].contiguous(), weight=g.input_layernorm, rms=True, eps=eps)
+            ht = fused.norm_modulate(x[:, N:].contiguous(), weight=u.input_layernorm, rms=True, eps=eps)
+            qkv = torch.cat([g.qkv(hv), u.qkv(ht)], dim=1).contiguous()
+            qkv = self._norm_rope(qkv, cos, sin, g.q_norm, g.k_norm, u.q_norm, u.k_norm, N)
         q, k, v = self._qkv_heads(qkv)
+        if collect is not None:
+            collect.append((k[0].clone(), v[0].clone()))
         o = self._attend(q, k, v, past, li, causal=False).reshape(B, S, -1)
+        if N == 0:
+            xt = u.o(o.contiguous(), residual=x.contiguous())
+            ht = fused.norm_modulate(xt, weight=u.post_attention_layernorm, rms=True, eps=eps)
+            return u.down(fused.silu_mul(u.gate_up(ht)), residual=xt)
         xv = g.o(o[:, :N].contiguous(), residual=x[:, :N].contiguous())
         xt = u.o(o[:, N:].contiguous(), residual=x[:, N:].contiguous())
         hv = fused.norm_modulate(xv, weight=g.post_attention_layernorm, rms=True, eps=eps)
@@ -227,6 +239,56 @@ class BagelMoT(nn.Module):
         xv = g.down(fused.silu_mul(g.gate_up(hv)), residual=xv)
         xt = u.down(fused.silu_mul(u.gate_up(ht)), residual=xt)
         return torch.cat([xv, xt], dim=1)
+
+    # ------------------------------------------------------------------ editing context: images in front of the prompt
+    def _latent_rows(self, x_t, t, grid):
+        """Latent tokens -> language-model rows: projection + timestep embedding + 2-D position table."""
+        c = self.cfg
+        dt = self.dtype_
+        B = x_t.shape[0]
+        h, w = grid
+        pos_ids = latent_position_ids(h, w, c.max_latent_size).to(x_t.device)
+        tt = t.reshape(-1).expand(B) if t.numel() == 1 else t.reshape(-1)
+        temb = self.time_2(self.time_1(timestep_sinusoid(tt, 256, scale=1.0).to(dt), act="silu"))
+        return self.vae2llm(x_t.to(dt).contiguous()) + temb[:, None] + self.latent_pos_embed[pos_ids][None]
+
+    @torch.no_grad()
+    def _append_block(self, x, n_gen, past, position):
+        """Run ``x`` [1, S, D] (first ``n_gen`` rows on the generation weights) against the context, all rows at
+        rotary position ``position`` with full attention among them, and return the context grown by the
+        block's K/V (bagel_transformer.py:1012-1071, :1136-1189: ``update_past_key_values`` with
+        ``is_causal=False``)."""
+        S = x.shape[1]
+        cos, sin = self._cos_sin(torch.full((S,), int(position), device=x.device))
+        grown = []
+        for li in range(len(self.layers)):
+            got = []
+            x = self._gen_layer(li, x, n_gen, cos, sin, past, collect=got)
+            k, v = got[0]
+            pk, pv = (past[li] if past is not None and past[li] is not None else (k[:0], v[:0]))
+            grown.append((torch.cat([pk.to(k), k], 0), torch.cat([pv.to(v), v], 0)))
+        return grown
+
+    @torch.no_grad()
+    def prefill_image_latents(self, latent_tokens: torch.Tensor, grid, past=None, position: int = 0):
+        """A clean image as context: its VAE latents [N, patch_latent_dim] at timestep 0 between the two image
+        markers (latent rows on the generation weights, markers on the understanding weights).  Occupies ONE
+        rotary position; returns the grown context."""
+        c = self.cfg
+        dev = latent_tokens.device
+        lat = self._latent_rows(latent_tokens[None], torch.zeros(1, device=dev), grid)
+        marks = self._embed(torch.tensor([c.start_of_image, c.end_of_image], device=dev)).to(self.dtype_)
+        x = torch.cat([lat, marks[None]], dim=1).contiguous()
+        return self._append_block(x, latent_tokens.shape[0], past, position)
+
+    @torch.no_grad()
+    def prefill_vision_tokens(self, tokens: torch.Tensor, past=None, position: int = 0):
+        """Vision-tower tokens [Nv, D] (already in the language model's width, position table added) between
+        the image markers, all on the understanding weights, at one rotary position."""
+        c = self.cfg
+        marks = self._embed(torch.tensor([c.start_of_image, c.end_of_image], device=tokens.device)).to(self.dtype_)
+        x = torch.cat([tokens.to(self.dtype_), marks], dim=0)[None].contiguous()
+        return self._append_block(x, 0, past, position)
 
     # ------------------------------------------------------------------ generation mode: one velocity evaluation
     @torch.no_grad()
@@ -240,9 +302,7 @@ class BagelMoT(nn.Module):
         B, N, _ = x_t.shape
         dev = x_t.device
         h, w = grid
-        pos_ids = latent_position_ids(h, w, c.max_latent_size).to(dev)
-        temb = self.time_2(self.time_1(timestep_sinusoid(t.reshape(-1).expand(B) if t.numel() == 1 else t.reshape(-1), 256, scale=1.0).to(dt), act="silu"))
-        lat = self.vae2llm(x_t.to(dt).contiguous()) + temb[:, None] + self.latent_pos_embed[pos_ids][None]
+        lat = self._latent_rows(x_t, t, grid)
         marks = self._embed(torch.tensor([c.start_of_image, c.end_of_image], device=dev)).to(dt)
         x = torch.cat([lat, marks[None].expand(B, -1, -1)], dim=1).contiguous()            # [B, N + 2, D]
         S = N + 2
