@@ -142,3 +142,58 @@ def test_tts_tokenizer_decoder_channels_last_equals_channels_first():
     m.vocoder_layout = "nlc"
     b = m.decode(codes)
     assert a.shape == b.shape == (2, 11 * 2 * 4 * 2) and (a - b).abs().max() < 1e-3
+
+
+def _bigvgan(dev, dtype):
+    from vllm_omni_b200.models.qwen2_5_omni.config import BigVGANConfig
+    from vllm_omni_b200.models.qwen2_5_omni.token2wav import BigVGAN
+    torch.manual_seed(0)
+    cfg = BigVGANConfig(mel_dim=16, upsample_initial_channel=64, upsample_rates=(5, 2), upsample_kernel_sizes=(11, 4),
+                        resblock_kernel_sizes=(3, 7), resblock_dilation_sizes=((1, 3), (1, 5)))
+    m = BigVGAN(cfg).to(dev, dtype)
+    for p in m.parameters():
+        p.data.normal_(0, 0.15)
+    mel = torch.randn(2, 16, 13, device=dev)
+    return m, mel
+
+
+def test_anti_aliased_snake_and_bigvgan_channels_last():
+    from vllm_omni_b200.models.qwen2_5_omni.token2wav import FilteredActivation
+    torch.manual_seed(1)
+    fa = FilteredActivation(8)
+    fa.act.alpha.data.normal_(0, 0.3)
+    fa.act.beta.data.normal_(0, 0.3)
+    x = torch.randn(2, 8, 11)
+    want = fa(x).transpose(1, 2)
+    got = C.aa_snake_nlc(x.transpose(1, 2).contiguous(), fa.act.alpha.exp(), 1.0 / (fa.act.beta.exp() + 1e-9),
+                         fa.up_filter.flatten(), fa.down_filter.flatten())
+    assert (got - want).abs().max() < 1e-5
+    m, mel = _bigvgan("cpu", torch.float32)
+    m.vocoder_layout = "nct"
+    a = m(mel)
+    m.vocoder_layout = "nlc"
+    b = m(mel)
+    assert a.shape == b.shape == (2, 130) and (a - b).abs().max() < 1e-3 and (a.abs() < 1).any()
+
+
+@pytest.mark.gpu
+def test_anti_aliased_snake_and_bigvgan_gpu():
+    from vllm_omni_b200.models.qwen2_5_omni.token2wav import FilteredActivation
+    torch.manual_seed(1)
+    fa = FilteredActivation(64).cuda()
+    fa.act.alpha.data.normal_(0, 0.3)
+    fa.act.beta.data.normal_(0, 0.3)
+    for T in (1, 3, 1001):                                   # ends of the signal are replicate-padded twice
+        x = torch.randn(2, 64, T, device="cuda").bfloat16()
+        want = fa(x.float()).transpose(1, 2)
+        got = C.aa_snake_nlc(x.transpose(1, 2).contiguous(), fa.act.alpha.exp().contiguous(),
+                             (1.0 / (fa.act.beta.exp() + 1e-9)).contiguous(), fa.up_filter.flatten().contiguous(),
+                             fa.down_filter.flatten().contiguous()).float()
+        assert (got - want).abs().max().item() < 0.05, T
+    m, mel = _bigvgan("cuda", torch.bfloat16)
+    m.vocoder_layout = "nct"
+    want = m(mel.bfloat16())
+    m.vocoder_layout = None
+    assert m.use_nlc(mel)
+    got = m(mel.bfloat16())
+    assert got.shape == want.shape and (got - want).abs().max().item() < 0.1

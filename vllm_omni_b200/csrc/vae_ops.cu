@@ -174,6 +174,93 @@ dwconv1d_nlc_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
   }
 }
 
+// Anti-aliased snake activation of BigVGAN, channels-last: 2x up-sampling by a 12-tap windowed-sinc
+// filter (replicate padding), snake, 2x down-sampling by a 12-tap filter (replicate padding), in one pass:
+//   u[s]   = 2 * sum_j x[clamp((s + 15 - j) / 2 - 5)] * fu[j]        over the j with (s + 15 - j) even, s in [0, 2T)
+//   a[s]   = u[s] + inv_b[c] * sin^2(u[s] * alpha[c])
+//   out[t] = sum_j a[clamp(2t + j - 5, 0, 2T - 1)] * fd[j]
+// (the index arithmetic of conv_transpose1d(stride 2) on the input padded by 5, cropped by 15 on both sides,
+// then conv1d(stride 2) on the result padded by (5, 6)).  One thread owns 8 channels of AA_RUN consecutive
+// output steps, so that the up-sampled values are computed once per two outputs, not once per tap.
+constexpr int AA_K = 12, AA_RUN = 4;
+__global__ void __launch_bounds__(128)
+aa_snake_nlc_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ alpha, const float* __restrict__ inv_b,
+                    const float* __restrict__ fu, const float* __restrict__ fd, __nv_bfloat16* __restrict__ y, int B, int T,
+                    int C8) {
+  __shared__ float s_fu[AA_K], s_fd[AA_K];
+  if (threadIdx.x < AA_K) { s_fu[threadIdx.x] = fu[threadIdx.x]; s_fd[threadIdx.x] = fd[threadIdx.x]; }
+  __syncthreads();
+  const int runs = (T + AA_RUN - 1) / AA_RUN;
+  const long total = (long)B * runs * C8;
+  const int C = C8 * 8;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8) * 8;
+    const long br = i / C8;
+    const int t0 = (int)(br % runs) * AA_RUN;
+    const long b = br / runs;
+    const __nv_bfloat16* xb = x + b * (long)T * C + c;
+    float al[8], ib[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { al[e] = alpha[c + e]; ib[e] = inv_b[c + e]; }
+    // up-sampled, activated values a[s] for s in [2 t0 - 5, 2 (t0 + AA_RUN - 1) + 6], clamped to [0, 2T - 1]
+    constexpr int NS = 2 * AA_RUN + 10;
+    float a[NS][8];
+    int prev_s = -1;
+#pragma unroll
+    for (int k = 0; k < NS; ++k) {
+      int s = 2 * t0 - 5 + k;
+      s = s < 0 ? 0 : (s > 2 * T - 1 ? 2 * T - 1 : s);
+      if (s == prev_s) {                              // clamped repeats at the ends of the signal
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[k][e] = a[k > 0 ? k - 1 : 0][e];
+        continue;
+      }
+      prev_s = s;
+      float u[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) u[e] = 0.f;
+      const int sp = s + 15;
+      for (int j = sp & 1; j < AA_K; j += 2) {        // taps with (sp - j) even
+        int xi = (sp - j) / 2 - 5;
+        xi = xi < 0 ? 0 : (xi > T - 1 ? T - 1 : xi);
+        const uint4 v = *reinterpret_cast<const uint4*>(xb + (long)xi * C);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const float w = 2.0f * s_fu[j];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(p[e]);
+          u[2 * e] = fmaf(f.x, w, u[2 * e]);
+          u[2 * e + 1] = fmaf(f.y, w, u[2 * e + 1]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float sn = sinf(u[e] * al[e]);
+        a[k][e] = fmaf(ib[e] * sn, sn, u[e]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < AA_RUN; ++r) {
+      const int t = t0 + r;
+      if (t >= T) break;
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = 0.f;
+#pragma unroll
+      for (int j = 0; j < AA_K; ++j) {
+        const float w = s_fd[j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = fmaf(a[2 * r + j][e], w, o[e]);
+      }
+      uint4 ov;
+      __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) q[e] = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+      *reinterpret_cast<uint4*>(y + (b * (long)T + t) * C + c) = ov;
+    }
+  }
+}
+
 }  // namespace omni
 
 using namespace omni;
@@ -237,5 +324,18 @@ extern "C" int omni_dwconv1d_nlc(const void* x, const float* w, const float* bia
   if (blocks > 148 * 16) blocks = 148 * 16;
   omni::dwconv1d_nlc_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, w, bias, (__nv_bfloat16*)y, B, T, C / 8, k, dil, pad);
+  return (int)cudaGetLastError();
+}
+
+// x, y: contiguous [B, T, C] bf16, C a multiple of 8; alpha, inv_b: fp32 [C]; fu, fd: fp32 [12] (up / down filters).
+extern "C" int omni_aa_snake_nlc(const void* x, const float* alpha, const float* inv_b, const float* fu, const float* fd, void* y,
+                                 int B, int T, int C, void* stream) {
+  if (B <= 0 || T <= 0 || C <= 0) return omni::RC_OK;
+  if (C & 7) return omni::RC_BAD_ARG;
+  const long total = (long)B * ((T + omni::AA_RUN - 1) / omni::AA_RUN) * (C / 8);
+  long blocks = (total + 127) / 128;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  omni::aa_snake_nlc_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, alpha, inv_b, fu, fd, (__nv_bfloat16*)y, B, T, C / 8);
   return (int)cudaGetLastError();
 }

@@ -22,7 +22,7 @@ from typing import Any
 from ..inputs.data import OmniDiffusionSamplingParams, OmniTokensPrompt, SamplingParams
 from ..logger import init_logger
 from ..outputs import OmniRequestOutput
-from .stage_utils import OmniStageTaskType, set_stage_devices
+from .stage_utils import OmniStageTaskType, set_stage_devices, to_host
 from .utils import (OmniPipelineConfig, StageConfig, inject_omni_kv_config, load_stage_configs_from_yaml,
                     resolve_callable, resolve_model_config_path)
 
@@ -290,7 +290,7 @@ def _stage_worker(cfg: StageConfig, model: str, in_q, out_q, batch_timeout_s: fl
                 task = None
         if adapter.has_work():
             for r in adapter.step():
-                out_q.put(r)
+                out_q.put(r if in_process else to_host(r))       # queue messages between processes carry host data only
 
 
 # =============================================================================== stage
@@ -403,7 +403,7 @@ class OmniStage:
     def submit(self, task: dict) -> None:
         task.setdefault("type", OmniStageTaskType.GENERATE)
         task.setdefault("submit_ts", time.time())
-        self._in_q.put(task)
+        self._in_q.put(task if self.in_process else to_host(task))
 
     def try_collect(self) -> dict | None:
         try:

@@ -71,3 +71,39 @@ def maybe_load_from_ipc(desc: dict, connector, stage_id: int, key: str):
     if res is None:
         raise RuntimeError(f"stage {stage_id}: result {key} never arrived")
     return res[0]
+
+
+def to_host(obj, _seen=None):
+    """Move every CUDA tensor inside a message (dicts, lists, tuples, plain objects) to host memory, in place
+    where the container allows it.  Messages between the orchestrator and a stage PROCESS travel through
+    ``multiprocessing`` queues: a CUDA tensor in them becomes a CUDA-IPC handle whose memory the producer must
+    keep alive, which the receiver cannot pass on to a third process ("Attempted to send CUDA tensor received
+    from another process") and which costs a handle per tensor.  Device payloads have their own path (the
+    device connector); everything on the queues is host data."""
+    import torch
+    if isinstance(obj, torch.Tensor):
+        return obj.detach().cpu() if obj.is_cuda else obj
+    if obj is None or isinstance(obj, (str, bytes, int, float, bool)):
+        return obj
+    _seen = set() if _seen is None else _seen
+    if id(obj) in _seen:
+        return obj
+    _seen.add(id(obj))
+    if isinstance(obj, dict):
+        for k in list(obj):
+            obj[k] = to_host(obj[k], _seen)
+        return obj
+    if isinstance(obj, list):
+        for i in range(len(obj)):
+            obj[i] = to_host(obj[i], _seen)
+        return obj
+    if isinstance(obj, tuple):
+        return type(obj)(to_host(v, _seen) for v in obj) if type(obj) is tuple else obj
+    d = getattr(obj, "__dict__", None)
+    if isinstance(d, dict) and not isinstance(obj, type) and type(obj).__module__.startswith("vllm_omni_b200"):
+        for k in list(d):
+            try:
+                setattr(obj, k, to_host(d[k], _seen))
+            except Exception:   # noqa: BLE001  (read-only attribute)
+                pass
+    return obj

@@ -376,9 +376,81 @@ class BigVGAN(nn.Module):
         db = 20 * torch.log10(amp.clamp(min=floor)) - 20
         return torch.clamp(2 * ((db + 115) / 115) - 1, -1, 1)
 
+    # ------------------------------------------------------------------ channels-last path (own kernels)
+    def _packed(self, m, dtype):
+        """Weights of a convolution in the layout of the 1-D implicit GEMM, packed once per module."""
+        from ...ops import conv as CV
+        cache = self.__dict__.setdefault("_pk", {})
+        key = (id(m), m.weight._version, dtype)
+        if key not in cache:
+            b = m.bias.data if m.bias is not None else None
+            if isinstance(m, nn.ConvTranspose1d):
+                cache[key] = CV.pack_conv_transpose1d_weight(m.weight.data, b, m.stride[0], m.padding[0], dtype)
+            else:
+                cache[key] = CV.pack_conv1d_weight(m.weight.data, b, dtype)
+        return cache[key]
+
+    def _conv_nlc(self, m, x, residual=None):
+        from ...ops import conv as CV
+        k, d = m.kernel_size[0], m.dilation[0]
+        pw, pb = self._packed(m, x.dtype)
+        y = CV.conv1d_nlc(x, pw, pb, k, m.in_channels, d, m.padding[0], residual=residual)
+        return y if y.shape[-1] == m.out_channels else y[..., :m.out_channels]
+
+    def _act_nlc(self, fa, x):
+        from ...ops import conv as CV
+        cache = self.__dict__.setdefault("_ab", {})
+        key = (id(fa), fa.act.alpha._version, fa.act.beta._version)
+        if key not in cache:
+            cache[key] = (fa.act.alpha.float().exp().contiguous(), (1.0 / (fa.act.beta.float().exp() + 1e-9)).contiguous(),
+                          fa.up_filter.float().flatten().contiguous(), fa.down_filter.float().flatten().contiguous())
+        a, ib, fu, fd = cache[key]
+        return CV.aa_snake_nlc(x.contiguous(), a, ib, fu, fd)
+
+    @torch.no_grad()
+    def forward_nlc(self, mel):
+        """Same network on [B, T, C] tensors: the convolutions are the 1-D implicit GEMM (transposed ones as one
+        stride-1 convolution on phase-stacked weights), every anti-aliased activation is one fused kernel, the
+        residual adds ride in the GEMM epilogues (ops/conv.py)."""
+        from ...ops import conv as CV
+        n = len(self.c.resblock_kernel_sizes)
+        dt = self.conv_pre.weight.dtype
+        x = self.process_mel(mel).transpose(1, 2).to(dt)
+        pad_c = (-x.shape[-1]) % 8
+        if pad_c:                                          # TMA rows start on 16 bytes
+            x = F.pad(x, (0, pad_c))
+        x = self._conv_nlc(self.conv_pre, x.contiguous())
+        for i, up in enumerate(self.ups):
+            m = up[0]
+            k, r, p = m.kernel_size[0], m.stride[0], m.padding[0]
+            t_out = (x.shape[1] - 1) * r - 2 * p + k
+            y = CV.conv_transpose1d_nlc(x, self._packed(m, x.dtype), m.in_channels, r, t_out)
+            x = (y if y.shape[-1] == m.out_channels else y[..., :m.out_channels]).contiguous()
+            acc = None
+            for j in range(n):
+                blk = self.resblocks[i * n + j]
+                h = x
+                for q, (c1, c2) in enumerate(zip(blk.convs1, blk.convs2)):
+                    t = self._conv_nlc(c1, self._act_nlc(blk.activations[2 * q], h))
+                    h = self._conv_nlc(c2, self._act_nlc(blk.activations[2 * q + 1], t), residual=h)
+                acc = h.float() if acc is None else acc + h.float()
+            x = (acc / n).to(dt)
+        x = self._conv_nlc(self.conv_post, self._act_nlc(self.activation_post, x))
+        return torch.clamp(x[..., 0].float(), -1.0, 1.0)
+
+    def use_nlc(self, mel) -> bool:
+        forced = getattr(self, "vocoder_layout", None)
+        if forced is not None:
+            return forced == "nlc"
+        import os
+        return (mel.is_cuda and self.conv_pre.weight.dtype == torch.bfloat16 and os.environ.get("OMNI_VOCODER_NLC", "1") != "0"
+                and all(ch % 8 == 0 for ch in (self.conv_pre.out_channels, self.conv_post.in_channels)))
+
     @torch.no_grad()
     def forward(self, mel):
         """mel [B, mel_dim, T] -> waveform [B, T * total_upsample] in [-1, 1]."""
+        if self.use_nlc(mel):
+            return self.forward_nlc(mel)
         n = len(self.c.resblock_kernel_sizes)
         x = self.conv_pre(self.process_mel(mel))
         for i, up in enumerate(self.ups):

@@ -263,3 +263,35 @@ def dwconv1d_nlc(x, w_kc, bias, k: int, dil: int = 1, pad: int = 0):
                                              c_int(k), c_int(dil), c_int(pad), nv.stream_ptr())
     nv.check_rc(rc, "omni_dwconv1d_nlc")
     return out
+
+
+def aa_snake_nlc_reference(x, a, inv_b, up_filter, down_filter):
+    """The anti-aliased snake of BigVGAN restated with PyTorch ops (x [B, T, C]): replicate-pad, 2x
+    transposed-convolution up-sampling with ``up_filter`` [12], snake, replicate-pad, stride-2 convolution
+    with ``down_filter`` [12]."""
+    B, T, C = x.shape
+    k = up_filter.numel()
+    pad = k // 2 - 1
+    xc = x.float().transpose(1, 2)
+    y = F.pad(xc, (pad, pad), mode="replicate")
+    y = 2 * F.conv_transpose1d(y, up_filter.float().view(1, 1, k).expand(C, -1, -1), stride=2, groups=C)
+    pl, pr = pad * 2 + (k - 2) // 2, pad * 2 + (k - 2 + 1) // 2
+    y = y[..., pl:-pr]
+    y = y + inv_b.float()[None, :, None] * torch.sin(y * a.float()[None, :, None]).pow(2)
+    y = F.pad(y, (k // 2 - (1 - k % 2), k // 2), mode="replicate")
+    y = F.conv1d(y, down_filter.float().view(1, 1, k).expand(C, -1, -1), stride=2, groups=C)
+    return y.transpose(1, 2)
+
+
+def aa_snake_nlc(x, a, inv_b, up_filter, down_filter):
+    """Up-sample x2, snake, down-sample x2 in one kernel (csrc/vae_ops.cu ``omni_aa_snake_nlc``); x [B, T, C]
+    bf16 contiguous, a / inv_b fp32 [C], filters fp32 [12]."""
+    if not x.is_cuda:
+        return aa_snake_nlc_reference(x, a, inv_b, up_filter, down_filter).to(x.dtype)
+    B, T, C = x.shape
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and C % 8 == 0 and up_filter.numel() == 12 and down_filter.numel() == 12
+    out = torch.empty_like(x)
+    rc = nv.lib("vae_ops").omni_aa_snake_nlc(nv.ptr(x), nv.ptr(a), nv.ptr(inv_b), nv.ptr(up_filter), nv.ptr(down_filter),
+                                             nv.ptr(out), c_int(B), c_int(T), c_int(C), nv.stream_ptr())
+    nv.check_rc(rc, "omni_aa_snake_nlc")
+    return out
