@@ -224,3 +224,48 @@ def _zimage_sp_worker(rank, world, backend, uly, ring):
 @pytest.mark.parametrize("uly,ring", [(2, 1), (2, 2)])
 def test_zimage_sequence_parallel_cpu_gloo(uly, ring):
     run_distributed(_zimage_sp_worker, uly * ring, "gloo", args=("gloo", uly, ring))
+
+
+def _spa_worker(rank, world, uly, ring, forced):
+    """``SequenceParallelAttention`` in peer mode (pulled head exchange, gathered ring K/V, scatter epilogue)
+    against one attention over the whole sequence; called twice so that buffers are reused."""
+    import os
+    from vllm_omni_b200.ops import _native as nv
+    from vllm_omni_b200.ops.attention import attention_reference
+    from vllm_omni_b200.parallel import parallel_state as ps
+    from vllm_omni_b200.parallel.sp_attention import SequenceParallelAttention
+    if forced:
+        os.environ["OMNI_RING_MODE"] = forced
+    dev = torch.device("cuda", rank)
+    ps.init_distributed_environment(world, rank, local_rank=rank, backend="nccl")
+    ps.initialize_model_parallel(sequence_parallel_size=world, ulysses_degree=uly, ring_degree=ring, backend="nccl")
+    H, Dh, B, per = 4, 128, 2, 160
+    S = per * world
+    sp = SequenceParallelAttention(ps.get_sp_group(), H, Dh, mode="peer")
+    for it, valid in enumerate((S, S - 37)):
+        g = torch.Generator(device="cpu").manual_seed(7 + it)
+        full = torch.randn(B, S, 3, H, Dh, generator=g).to(dev, torch.bfloat16)
+        ref = attention_reference(full[:, :, 0].float(), full[:, :valid, 1].float(), full[:, :valid, 2].float())
+        o = sp(full[:, rank * per:(rank + 1) * per].contiguous(), valid_len=None if valid == S else valid).float()
+        torch.cuda.synchronize()
+        assert int(nv.status_word(dev).item()) == 0
+        err = (o - ref[:, rank * per:(rank + 1) * per]).abs().max().item()
+        assert err < 0.03, f"rank {rank} uly {uly} ring {ring} valid {valid}: {err}"
+    sp.close()
+    ps.destroy_distributed_environment()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("uly,ring,forced", [(2, 1, None), (1, 2, "single"), (1, 2, "overlap")])
+def test_single_stream_sp_attention_peer_mode_gpu(uly, ring, forced):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_distributed(_spa_worker, 2, "nccl", args=(uly, ring, forced))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("forced", ["single", "overlap"])
+def test_single_stream_sp_attention_hybrid_gpu(forced):
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    run_distributed(_spa_worker, 4, "nccl", args=(2, 2, forced))

@@ -5,7 +5,10 @@ row-local.  ``SequenceParallelAttention`` takes the local ``[B, S_loc, 3, H, Dh]
 normalised and rotated with the rows' own positions) and returns the local ``[B, S_loc, H, Dh]``
 attention output over the FULL sequence:
 
-* Ulysses degree U: head <-> sequence all-to-all inside the Ulysses group before and after;
+* Ulysses degree U: head <-> sequence exchange inside the Ulysses group before and after; ``mode="peer"``:
+  every rank publishes its rows in symmetric memory and pulls its heads of everybody's rows with the
+  library's pitched copy kernel, and the attention kernel's epilogue stores each output row into the
+  peer that owns it (two bounded barriers, no library collective); ``mode="nccl"``: all-to-all calls;
 * ring degree R: the chunk's queries against every ring chunk's K/V — ``mode="peer"``: the other
   chunks are pulled once into a local buffer by this library's copy kernel on a side stream while
   the own chunk is attended to, and a second launch combines both results by their log-sum-exps in
@@ -39,6 +42,7 @@ class SequenceParallelAttention:
         self.arena = None
         self._key = None
         self._gath = self._own = self._side = None
+        self._uly_arena = self._uly_key = None
 
     # rows ------------------------------------------------------------------------------
     def shard_rows(self, x: torch.Tensor, dim: int = 1):
@@ -85,15 +89,62 @@ class SequenceParallelAttention:
         self.arena = PeerArena(self.group.ring, n * torch.empty(0, dtype=dtype).element_size() + 8192, device)
         self.kv = self.arena.alloc(shape, dtype)
 
+    # Ulysses exchange on own kernels ------------------------------------------------------
+    def _uly_setup(self, B, S_loc, dtype, device):
+        """Symmetric buffers of the Ulysses group: every rank publishes its [B, S_loc, 3, H, Dh] rows; the output
+        rows of the attention come back through the kernel's scatter epilogue into [B, S_loc, H*Dh]."""
+        key = (B, S_loc, dtype, str(device))
+        if self._uly_key == key:
+            return
+        self._uly_key = key
+        from .peer_memory import PeerArena
+        if self._uly_arena is not None:
+            self._uly_arena.close()
+        es = torch.empty(0, dtype=dtype).element_size()
+        HD = self.H * self.Dh
+        self._uly_arena = PeerArena(self.group.ulysses, B * S_loc * 4 * HD * es + 16384, device)
+        self._uly_pub = self._uly_arena.alloc((B, S_loc, 3, self.H, self.Dh), dtype)
+        self._uly_out = self._uly_arena.alloc((B, S_loc, HD), dtype)
+        Hu = self.H // self.U
+        self._uly_joint = torch.empty(B, self.U * S_loc, 3, Hu, self.Dh, dtype=dtype, device=device)
+        hoff = self.u * Hu * self.Dh * es
+        self._uly_scatter = dict(n_peers=self.U, rows_per_rank=S_loc, rows_per_rank2=1, split=self.U * S_loc,
+                                 o_ptrs=self._uly_out.peer_ptrs(hoff), o2_ptrs=self._uly_out.peer_ptrs(hoff),
+                                 o_strides=(HD, self.Dh, S_loc * HD), o2_strides=(HD, self.Dh, S_loc * HD))
+
+    def _uly_gather(self, q5):
+        """Head <-> sequence exchange by pulls: this rank's H/U heads of q, k and v of every Ulysses peer's rows,
+        one pitched copy per (peer, batch, q|k|v); rows end up ordered by source rank as an all-to-all leaves them."""
+        from .peer_memory import pull_rows
+        B, S_loc = q5.shape[0], q5.shape[1]
+        self._uly_setup(B, S_loc, q5.dtype, q5.device)
+        Hu, es = self.H // self.U, q5.element_size()
+        seg = Hu * self.Dh
+        self._uly_pub.local.copy_(q5)
+        self._uly_arena.barrier()                         # every peer's rows are published
+        j5 = self._uly_joint
+        for p in range(self.U):
+            for b in range(B):
+                for w in range(3):
+                    src = self._uly_pub.ptrs[p] + (((b * S_loc) * 3 + w) * self.H + self.u * Hu) * self.Dh * es
+                    dst = j5[b, p * S_loc:(p + 1) * S_loc, w].reshape(S_loc, seg)      # a view: pitch 3 * seg elements
+                    pull_rows(dst, src, 3 * self.H * self.Dh * es)
+        return j5
+
     def __call__(self, q5: torch.Tensor, valid_len=None, scale: float | None = None) -> torch.Tensor:
         B, S_loc = q5.shape[0], q5.shape[1]
-        if self.U > 1:
+        uly_peer = self.U > 1 and self.mode == "peer" and q5.is_cuda
+        sc = None
+        if uly_peer:
+            q5 = self._uly_gather(q5.contiguous())                                        # [B, S_c, 3, H/U, Dh]
+            sc = self._uly_scatter                                                        # O rows go back to their owners
+        elif self.U > 1:
             q5 = all_to_all_5d(q5.contiguous(), 3, 1, self.group.ulysses.device_group)    # [B, S_c, 3, H/U, Dh]
         S_c = q5.shape[1]
         q, k, v = q5[:, :, 0], q5[:, :, 1], q5[:, :, 2]
         dev = q5.device
         if self.R == 1:
-            o = attention(q, k, v, kv_lens=self._chunk_lens(valid_len, 0, S_c, B, dev), scale=scale)
+            o = attention(q, k, v, kv_lens=self._chunk_lens(valid_len, 0, S_c, B, dev), scale=scale, scatter=sc)
         else:
             if valid_len is not None and int(torch.as_tensor(valid_len).min()) <= (self.R - 1) * S_c:
                 raise ValueError("padding may not cover a whole ring chunk")
@@ -134,7 +185,7 @@ class SequenceParallelAttention:
                     if valid_len is not None:                               # padding sits at the end of the LAST chunk
                         rem = torch.stack([self._chunk_lens(valid_len, c, S_c, B, dev) for c in srcs]).sum(dim=0).to(torch.int32)
                     out = attention(q, g5[:, :, 0], g5[:, :, 1], scale=scale, kv_lens=rem, merge_prev=(self._own, lse0),
-                                    out=self._own)
+                                    out=self._own, scatter=sc)
                 else:
                     # small grids: one launch over every chunk in order
                     pull_rows(self._gath[:, r * chunk:(r + 1) * chunk], self.kv.ptrs[r], chunk * es)
@@ -142,7 +193,7 @@ class SequenceParallelAttention:
                     lens = None
                     if valid_len is not None:
                         lens = (valid_len.to(dev) if torch.is_tensor(valid_len) else torch.full((B,), int(valid_len), device=dev)).to(torch.int32)
-                    out = attention(q, g5[:, :, 0], g5[:, :, 1], scale=scale, kv_lens=lens, out=self._own)
+                    out = attention(q, g5[:, :, 0], g5[:, :, 1], scale=scale, kv_lens=lens, out=self._own, scatter=sc)
                 self.arena.barrier()
             else:
                 comm = RingComm(self.group.ring.device_group)
@@ -158,12 +209,18 @@ class SequenceParallelAttention:
                     if step + 1 < self.R:
                         comm.wait()
                         k, v = nk, nv_
-            o = out.to(q5.dtype)
+            o = out.to(q5.dtype) if out is not None else None
+        if uly_peer:
+            self._uly_arena.barrier()                     # every owner has all heads of its rows
+            return self._uly_out.local.view(B, S_loc, self.H, self.Dh)
         if self.U > 1:
             o = all_to_all_4d(o.contiguous(), 1, 2, self.group.ulysses.device_group)      # [B, S_loc, H, Dh]
         return o
 
     def close(self):
+        if self._uly_arena is not None:
+            self._uly_arena.close()
+            self._uly_arena = None
         if self.arena is not None:
             self.arena.close()
             self.arena = None
