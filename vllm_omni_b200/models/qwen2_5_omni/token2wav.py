@@ -269,8 +269,9 @@ class Token2WavDiT(nn.Module):
 
     @torch.no_grad()
     def sample(self, codes, xvec=None, ref_mel=None, num_steps=None, guidance_scale=None, sway=None, generator=None,
-               noise=None):
-        """codes [B, T_code] -> mel [B, mel_dim, T_code * repeats]."""
+               noise=None, solver="rk4"):
+        """codes [B, T_code] -> mel [B, mel_dim, T_code * repeats].  ``solver``: "rk4" (3/8 rule, the
+        Qwen2.5-Omni vocoder) or "euler" (one evaluation per interval, the Qwen3-TTS 25 Hz decoder)."""
         c = self.c
         B, Tc = codes.shape
         p = self.proj_out.weight
@@ -291,6 +292,11 @@ class Token2WavDiT(nn.Module):
             cond, null = self(x, ref_mel, xv, codes, t, apply_cfg=True).chunk(2, dim=0)
             return cond + (cond - null) * g
 
+        if solver == "euler":
+            x = x0
+            for t0, t1 in zip(times[:-1], times[1:]):
+                x = x + fn(t0, x) * (t1 - t0)
+            return x.transpose(1, 2)
         return rk4_38_integrate(fn, x0, times).transpose(1, 2)
 
 
