@@ -129,3 +129,41 @@ def test_builder_picks_the_class_by_model_type():
     assert isinstance(m, Qwen3TTSTokenizer25Hz) and m.encoder is None and m.cfg.decode_upsample_rate == 8
     with pytest.raises(ValueError):
         build_speech_tokenizer({"model_type": "nope"})
+
+
+def test_stage_model_loads_and_uses_the_25hz_tokenizer(tmp_path):
+    """A ``speech_tokenizer/`` folder whose config names the 25 Hz type replaces the 12 Hz decoder on the
+    stage model: frames' first column is decoded with the voice's tokenizer x-vector and reference mel."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from vllm_omni_b200.models.qwen3_tts.model import Qwen3TTSConfig, Qwen3TTSModel
+    src = _tiny(3)
+    tiny = src.cfg
+    folder = tmp_path / "speech_tokenizer"
+    folder.mkdir()
+    lst = lambda d: {k: (list(map(list, v)) if v and isinstance(v, tuple) and isinstance(v[0], tuple) else
+                         list(v) if isinstance(v, tuple) else v) for k, v in d.items()}
+    (folder / "config.json").write_text(json.dumps({
+        "model_type": "qwen3_tts_tokenizer_25hz",
+        "encoder_config": lst(tiny.encoder.__dict__),
+        "decoder_config": {"dit_config": lst(tiny.dit.__dict__), "bigvgan_config": lst(tiny.bigvgan.__dict__)},
+        "decode_upsample_rate": tiny.decode_upsample_rate}))
+    sd = {"encoder.tokenizer." + n: p.clone() for n, p in src.encoder.named_parameters()}
+    sd["encoder.tokenizer.audio_quantizer.rvqs.0.embed"] = src.encoder.codebook.clone()[None]
+    sd.update({"decoder.dit." + n: p.clone() for n, p in src.dit.named_parameters()})
+    sd.update({"decoder.bigvgan." + n: p.clone() for n, p in src.bigvgan.named_parameters()})
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(folder / "model.safetensors"))
+    m = Qwen3TTSModel(Qwen3TTSConfig.tiny(), torch.float32, "cpu")
+    assert m.load_auxiliary(str(tmp_path)) == len(sd)
+    assert m.tokenizer_25hz is not None
+    clip = 0.3 * torch.sin(torch.arange(6400) / 16000 * 2 * 3.14159 * 200)
+    voice = m.create_voice_clone_prompt(clip, 16000, x_vector_only_mode=True)
+    assert voice["ref_mel"].shape == (40, 80) if tiny.dit.mel_dim == 80 else voice["ref_mel"].shape[0] == 40
+    frames = torch.tensor([[3], [9], [1], [4]])
+    # the tiny flow model takes 8 mel bins: hand it a reference of that width
+    v = {"tokenizer_xvector": torch.zeros(tiny.dit.enc_emb_dim), "ref_mel": torch.zeros(12, tiny.dit.mel_dim)}
+    wav = m.decode_codes(frames, v)
+    want = src.decode(frames[:, 0][None], v["tokenizer_xvector"][None], v["ref_mel"][None])[0]
+    assert wav.shape == (4 * tiny.decode_upsample_rate,) and torch.allclose(wav, want, atol=1e-6)

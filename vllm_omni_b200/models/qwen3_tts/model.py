@@ -159,6 +159,7 @@ class Qwen3TTSModel(StageModel):
         self.speaker_encoder = Qwen3TTSSpeakerEncoder(cfg.speaker_encoder, device) if cfg.speaker_encoder else None
         self.decoder = Qwen3TTSTokenizerDecoder(cfg.tokenizer_decoder, dtype, device)     # speech tokenizer decoder
         self.tokenizer_encoder = None                   # speech tokenizer encoder, built when the checkpoint ships one
+        self.tokenizer_25hz = None                      # the single-codebook 25 Hz tokenizer, when the checkpoint names it
         self.voices: dict[str, dict] = {}               # registered cloned voices
         self.text_tokenizer = None                      # set by the engine; turns instruction / transcript strings into ids
         self._session = None
@@ -344,6 +345,14 @@ class Qwen3TTSModel(StageModel):
         (their context shapes the first samples) and the matching share of the output is cut."""
         if codes.shape[0] == 0:
             return torch.zeros(0, device=codes.device)
+        if self.tokenizer_25hz is not None:
+            # one codebook; the voice carries the tokenizer's own x-vector and reference mel
+            tk, v = self.tokenizer_25hz, voice or {}
+            row = codes.reshape(codes.shape[0], -1)[:, 0][None]
+            xv = v.get("tokenizer_xvector")
+            mel = v.get("ref_mel")
+            return tk.decode(row, None if xv is None else torch.as_tensor(xv)[None],
+                             None if mel is None else torch.as_tensor(mel)[None])[0].float()
         ref = None
         if voice is not None and voice.get("icl_mode") and voice.get("ref_code") is not None:
             ref = torch.as_tensor(voice["ref_code"], dtype=torch.long, device=codes.device)
@@ -370,11 +379,17 @@ class Qwen3TTSModel(StageModel):
             from .speaker import resample_sinc
             clip = resample_sinc(ref_audio.reshape(1, -1), int(sr), self.tokenizer_encoder.cfg.sampling_rate)[0]
             ref_code = self.tokenizer_encoder.encode(clip)
+        extra = {}
+        if self.tokenizer_25hz is not None and self.tokenizer_25hz.encoder is not None:
+            c25, xv25, mel25 = self.tokenizer_25hz.encode([ref_audio.reshape(-1)], int(sr))
+            extra = {"tokenizer_xvector": xv25[0], "ref_mel": mel25[0]}
+            if ref_code is None and not x_vector_only_mode:
+                ref_code = c25[0][:, None]
         icl = (not x_vector_only_mode) and ref_code is not None
         if icl and not ref_ids:
             raise ValueError("in-context voice cloning needs the reference transcript (ref_ids)")
         v = {"ref_spk_embedding": xvec, "ref_code": torch.as_tensor(ref_code).long() if icl else None,
-             "x_vector_only_mode": not icl, "icl_mode": icl, "ref_ids": list(ref_ids or [])}
+             "x_vector_only_mode": not icl, "icl_mode": icl, "ref_ids": list(ref_ids or []), **extra}
         if name:
             self.voices[name] = v
         return v
@@ -462,6 +477,12 @@ class Qwen3TTSModel(StageModel):
         if os.path.exists(cfg_path):
             with open(cfg_path) as f:
                 tok_cfg = json.load(f)
+            if tok_cfg.get("model_type") == "qwen3_tts_tokenizer_25hz":
+                from .tokenizer_25hz import build_speech_tokenizer
+                self.tokenizer_25hz = build_speech_tokenizer(tok_cfg, self.text_embedding.device,
+                                                             with_encoder=self.speaker_encoder is not None)
+                files = _shard_files(folder)
+                return len(self.tokenizer_25hz.load_weights(safetensors_weights_iterator(files))) if files else 0
             dc = TokenizerDecoderConfig.from_dict(tok_cfg.get("decoder_config") or {})
             if dc != self.cfg.tokenizer_decoder:
                 self.cfg.tokenizer_decoder = dc
