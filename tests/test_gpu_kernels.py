@@ -295,6 +295,26 @@ def test_vae_decoder_nhwc_matches_torch(dev):
     assert (out - ref).abs().mean().item() < 0.02 and (out - ref).abs().max().item() < 0.25
 
 
+def test_wide_head_attention_gemm_softmax_gemm(dev):
+    """The VAE's one-head attention: two GEMM launches around the row-softmax kernel, queries in chunks."""
+    import torch.nn.functional as F
+    torch.manual_seed(9)
+    B, N, ch = 2, 1000, 384
+    t = torch.randn(B, N, 3, ch, device=dev, dtype=torch.bfloat16)
+    q, k, v = t[:, :, 0], t[:, :, 1], t[:, :, 2]
+    ref = F.scaled_dot_product_attention(q.float()[:, None], k.float()[:, None], v.float()[:, None])[:, 0]
+    for rows in (4096, 384):
+        out = C.wide_head_attention(q, k, v, chunk_rows=rows)
+        _status_ok(dev)
+        assert (out.float() - ref).abs().max().item() < 0.03, rows
+    x = torch.randn(37, 4096, device=dev, dtype=torch.bfloat16) * 4
+    keep = x.clone()
+    want = torch.softmax(x.float()[:, :2056] * 0.3, dim=-1)
+    got = C.softmax_rows_(x[:, :2056], 0.3)                # a pitched view: row stride 4096, 2056 columns
+    assert (got.float() - want).abs().max().item() < 4e-3 and abs(got.float().sum(-1) - 1).max().item() < 2e-2
+    assert torch.equal(x[:, 2056:], keep[:, 2056:])        # columns past the view are untouched
+
+
 def test_gemm_two_problems_one_launch(dev):
     """Image-stream and text-stream linears of one layer through a single CTA-pair launch."""
     from vllm_omni_b200.ops import gemm

@@ -197,3 +197,15 @@ def test_anti_aliased_snake_and_bigvgan_gpu():
     assert m.use_nlc(mel)
     got = m(mel.bfloat16())
     assert got.shape == want.shape and (got - want).abs().max().item() < 0.1
+
+
+def test_wide_head_attention_and_softmax_cpu_fallback():
+    from vllm_omni_b200.ops import conv as C
+    torch.manual_seed(0)
+    t = torch.randn(1, 40, 3, 16)
+    o = C.wide_head_attention(t[:, :, 0], t[:, :, 1], t[:, :, 2])
+    want = torch.softmax(t[0, :, 0] @ t[0, :, 1].T / 4.0, -1) @ t[0, :, 2]
+    assert torch.allclose(o[0], want, atol=1e-5)
+    x = torch.randn(5, 16)
+    w = torch.softmax(x * 0.5, -1)
+    assert torch.allclose(C.softmax_rows_(x, 0.5), w)

@@ -43,6 +43,64 @@ print("BOUNDS-OK")
 """
 
 
+MOE_CHILD = r"""
+import ctypes, torch
+from vllm_omni_b200.ops import _native as nv
+lib = nv.lib("moe")
+assert lib._cdll.omni_moe_bounds_check_enabled() == 1, "checked twin not loaded"
+c_int, c_long = ctypes.c_int, ctypes.c_long
+dev = torch.device("cuda")
+st = nv.status_word(dev)
+T, k, D, E = 4, 2, 64, 8
+x = torch.randn(T, D, device=dev, dtype=torch.bfloat16)
+big = torch.zeros(32, D, device=dev, dtype=torch.bfloat16)            # the allocation: 32 rows
+lib.omni_moe_set_bounds(c_long(16), nv.ptr(st))                       # the buffer the kernels are told about: 16 rows
+rows = torch.tensor([0, 1, 2, 3, 20, 5, -1, 7], dtype=torch.int32, device=dev)     # pair 4 -> row 20: outside
+nv.check_rc(lib.omni_moe_dispatch(nv.ptr(x), c_long(D), nv.ptr(rows), c_int(T * k), c_int(k), c_int(D), nv.ptr(big),
+                                  nv.stream_ptr()), "dispatch")
+torch.cuda.synchronize()
+code = int(st.item())
+assert code & 0xff == 9 and (code >> 8) & 0xff == 4, hex(code)
+assert float(big[20].abs().sum()) == 0.0 and torch.equal(big[5], x[2]) and torch.equal(big[0], x[0])
+st.zero_()
+# combine reading a row past the declared buffer: reported (kernel id 5), that pair contributes nothing
+w = torch.ones(T * k, device=dev)
+out = torch.empty(T, D, device=dev, dtype=torch.bfloat16)
+big[20] = 100.0
+nv.check_rc(lib.omni_moe_combine(nv.ptr(big), nv.ptr(rows), nv.ptr(w), c_int(T), c_int(k), c_int(D), None, c_long(0),
+                                 nv.ptr(out), c_long(D), nv.stream_ptr()), "combine")
+torch.cuda.synchronize()
+code = int(st.item())
+assert code & 0xff == 9 and (code >> 8) & 0xff == 5, hex(code)
+assert torch.equal(out[2], big[5])                                     # token 2 = pairs (4 -> skipped, 5)
+st.zero_()
+# an expert id outside [0, E) in the plan: reported (kernel id 3), the pair gets no row
+ids = torch.tensor([0, 1, 2, 9, 3, 3, 7, 0], dtype=torch.int32, device=dev)
+rop = torch.empty(8, dtype=torch.int32, device=dev)
+te, t0, tr = (torch.empty(16, dtype=torch.int32, device=dev) for _ in range(3))
+nr = torch.zeros(1, dtype=torch.int32, device=dev)
+nv.check_rc(lib.omni_moe_plan_compact(nv.ptr(ids), c_int(8), c_int(E), c_int(0), c_int(E), c_int(16), nv.ptr(rop),
+                                      nv.ptr(te), nv.ptr(t0), nv.ptr(tr), nv.ptr(nr), nv.stream_ptr()), "plan")
+torch.cuda.synchronize()
+code = int(st.item())
+assert code & 0xff == 9 and (code >> 8) & 0xff == 3, hex(code)
+assert int(nr.item()) == 7 and int(rop[3].item()) == -1
+st.zero_()
+print("BOUNDS-OK")
+"""
+
+
+@pytest.mark.gpu
+def test_checked_moe_kernels_report_and_skip():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    env = dict(os.environ, OMNI_BOUNDS_CHECK="1")
+    r = subprocess.run([sys.executable, "-c", MOE_CHILD], env=env, capture_output=True, text=True, timeout=300,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "BOUNDS-OK" in r.stdout, r.stdout + r.stderr
+
+
 @pytest.mark.gpu
 def test_checked_kv_kernels_report_and_skip():
     import torch

@@ -26,7 +26,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-pthread"]
 # libraries that also get a checked twin (-DOMNI_BOUNDS_CHECK, ``libomni_<name>_checked.so``): kernels that take
 # addresses from index operands test them and report through the status word instead of faulting;
 # ``OMNI_BOUNDS_CHECK=1`` makes ``ops/_native.lib`` load the twin
-CHECKED = ("kv_cache",)
+CHECKED = ("kv_cache", "moe")
 
 
 def lib_path(name: str, checked: bool = False) -> Path:

@@ -17,6 +17,15 @@ namespace omni {
 
 constexpr int MOE_TILE = 128;
 
+// Limits for the checked build (OMNI_IN_BOUNDS in ptx_sm100.cuh; 0 = unknown / unchecked), set by the host
+// through omni_moe_set_bounds and passed to the kernels by value: the rows the expert-major buffers hold.
+struct MoeBounds {
+  long max_rows;
+  int* status;
+};
+static MoeBounds g_moe_bounds = {0, nullptr};
+enum { KID_MOE_PLAN = 3, KID_MOE_DISPATCH = 4, KID_MOE_COMBINE = 5 };
+
 // one warp per token; E <= 256 (8 per lane), k <= 16
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int T, int E, int k, int renorm,
@@ -70,13 +79,14 @@ moe_route_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int T, int E,
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int e_lo, int e_hi, int max_tiles,
                 int* __restrict__ row_of_pair, int* __restrict__ tile_expert, int* __restrict__ offsets,
-                int* __restrict__ n_rows_out) {
+                int* __restrict__ n_rows_out, MoeBounds bd) {
   __shared__ int cnt[1024];
   __shared__ int off[1025];
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
     const int e = ids[i];
+    if (!OMNI_IN_BOUNDS(e >= 0 && e < E, bd.status, KID_MOE_PLAN)) continue;
     if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
@@ -121,7 +131,7 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int e_lo, int e
 __global__ void __launch_bounds__(1024)
 moe_plan_compact_kernel(const int* __restrict__ ids, int n_pairs, int E, int e_lo, int e_hi, int max_tiles,
                         int* __restrict__ row_of_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                        int* __restrict__ tile_rows, int* __restrict__ n_rows_out) {
+                        int* __restrict__ tile_rows, int* __restrict__ n_rows_out, MoeBounds bd) {
   __shared__ int cnt[1024];
   __shared__ int off[1025];
   __shared__ int toff[1025];
@@ -129,6 +139,7 @@ moe_plan_compact_kernel(const int* __restrict__ ids, int n_pairs, int E, int e_l
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
     const int e = ids[i];
+    if (!OMNI_IN_BOUNDS(e >= 0 && e < E, bd.status, KID_MOE_PLAN)) continue;
     if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
@@ -175,7 +186,7 @@ moe_plan_compact_kernel(const int* __restrict__ ids, int n_pairs, int E, int e_l
 // output rows of padding are never read back)
 __global__ void __launch_bounds__(256)
 moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long ldx, const int* __restrict__ row_of_pair, int n_pairs,
-                    int k, int D, __nv_bfloat16* __restrict__ xp) {
+                    int k, int D, __nv_bfloat16* __restrict__ xp, MoeBounds bd) {
   const int chunks = D >> 3;
   const long total = (long)n_pairs * chunks;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -183,6 +194,7 @@ moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long ldx, const int* __
     const int c = (int)(i % chunks) * 8;
     const int r = row_of_pair[p];
     if (r < 0) continue;
+    if (!OMNI_IN_BOUNDS(bd.max_rows == 0 || r < bd.max_rows, bd.status, KID_MOE_DISPATCH)) continue;
     *reinterpret_cast<uint4*>(xp + (size_t)r * D + c) = *reinterpret_cast<const uint4*>(x + (size_t)(p / k) * ldx + c);
   }
 }
@@ -192,7 +204,7 @@ moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long ldx, const int* __
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ row_of_pair,
                    const float* __restrict__ weights, int T, int k, int D, const __nv_bfloat16* __restrict__ residual,
-                   long ldr, __nv_bfloat16* __restrict__ out, long ldo) {
+                   long ldr, __nv_bfloat16* __restrict__ out, long ldo, MoeBounds bd) {
   const int chunks = D >> 3;
   const long total = (long)T * chunks;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -207,6 +219,7 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ 
     for (int j = 0; j < k; ++j) {
       const int r = row_of_pair[(size_t)t * k + j];
       if (r < 0) continue;
+      if (!OMNI_IN_BOUNDS(bd.max_rows == 0 || r < bd.max_rows, bd.status, KID_MOE_COMBINE)) continue;
       const float w = weights[(size_t)t * k + j];
       const uint4 u = *reinterpret_cast<const uint4*>(y + (size_t)r * D + c);
       const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
@@ -229,7 +242,8 @@ struct MoePeers {
 };
 __global__ void __launch_bounds__(256)
 moe_combine_scatter_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ row_of_pair,
-                           const float* __restrict__ weights, int T, int k, int D, int rows_per_owner, MoePeers peers) {
+                           const float* __restrict__ weights, int T, int k, int D, int rows_per_owner, MoePeers peers,
+                           MoeBounds bd) {
   const int chunks = D >> 3;
   const long total = (long)T * chunks;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -239,6 +253,7 @@ moe_combine_scatter_kernel(const __nv_bfloat16* __restrict__ y, const int* __res
     for (int j = 0; j < k; ++j) {
       const int r = row_of_pair[(size_t)t * k + j];
       if (r < 0) continue;
+      if (!OMNI_IN_BOUNDS(bd.max_rows == 0 || r < bd.max_rows, bd.status, KID_MOE_COMBINE)) continue;
       const float w = weights[(size_t)t * k + j];
       const uint4 u = *reinterpret_cast<const uint4*>(y + (size_t)r * D + c);
       const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
@@ -257,6 +272,20 @@ moe_combine_scatter_kernel(const __nv_bfloat16* __restrict__ y, const int* __res
 
 using namespace omni;
 
+// 1 when this library was compiled with -DOMNI_BOUNDS_CHECK
+extern "C" int omni_moe_bounds_check_enabled(void) {
+#ifdef OMNI_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+extern "C" void omni_moe_set_bounds(long max_rows, int* status) {
+  g_moe_bounds.max_rows = max_rows;
+  g_moe_bounds.status = status;
+}
+
 extern "C" int omni_moe_combine_scatter(const void* y, const int* row_of_pair, const float* weights, int T, int k, int D,
                                         int rows_per_owner, void* const* peer_out, void* stream) {
   if (T <= 0) return RC_OK;
@@ -268,7 +297,7 @@ extern "C" int omni_moe_combine_scatter(const void* y, const int* row_of_pair, c
   long blocks = ((long)T * (D >> 3) + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   moe_combine_scatter_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)y, row_of_pair, weights, T, k, D, rows_per_owner, peers);
+      (const __nv_bfloat16*)y, row_of_pair, weights, T, k, D, rows_per_owner, peers, g_moe_bounds);
   return (int)cudaGetLastError();
 }
 
@@ -285,7 +314,8 @@ extern "C" int omni_moe_route(const void* logits, int ld, int T, int E, int k, i
 extern "C" int omni_moe_plan(const int* ids, int n_pairs, int E, int e_lo, int e_hi, int max_tiles, int* row_of_pair,
                              int* tile_expert, int* offsets, int* n_rows_out, void* stream) {
   if (E > 1024) return RC_BAD_ARG;
-  moe_plan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, n_pairs, E, e_lo, e_hi, max_tiles, row_of_pair, tile_expert, offsets, n_rows_out);
+  moe_plan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, n_pairs, E, e_lo, e_hi, max_tiles, row_of_pair, tile_expert, offsets, n_rows_out,
+                                                        g_moe_bounds);
   return (int)cudaGetLastError();
 }
 
@@ -293,7 +323,7 @@ extern "C" int omni_moe_plan_compact(const int* ids, int n_pairs, int E, int e_l
                                      int* tile_expert, int* tile_row0, int* tile_rows, int* n_rows_out, void* stream) {
   if (E > 1024) return RC_BAD_ARG;
   moe_plan_compact_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, n_pairs, E, e_lo, e_hi, max_tiles, row_of_pair, tile_expert,
-                                                                tile_row0, tile_rows, n_rows_out);
+                                                                tile_row0, tile_rows, n_rows_out, g_moe_bounds);
   return (int)cudaGetLastError();
 }
 
@@ -303,7 +333,8 @@ extern "C" int omni_moe_dispatch(const void* x, long ldx, const int* row_of_pair
   if (D & 7) return RC_BAD_ARG;
   long blocks = ((long)n_pairs * (D >> 3) + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  moe_dispatch_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, row_of_pair, n_pairs, k, D, (__nv_bfloat16*)xp);
+  moe_dispatch_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, row_of_pair, n_pairs, k, D, (__nv_bfloat16*)xp,
+                                                                          g_moe_bounds);
   return (int)cudaGetLastError();
 }
 
@@ -314,6 +345,7 @@ extern "C" int omni_moe_combine(const void* y, const int* row_of_pair, const flo
   long blocks = ((long)T * (D >> 3) + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   moe_combine_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)y, row_of_pair, weights, T, k, D, (const __nv_bfloat16*)residual, ldr, (__nv_bfloat16*)out, ldo);
+      (const __nv_bfloat16*)y, row_of_pair, weights, T, k, D, (const __nv_bfloat16*)residual, ldr, (__nv_bfloat16*)out, ldo,
+      g_moe_bounds);
   return (int)cudaGetLastError();
 }

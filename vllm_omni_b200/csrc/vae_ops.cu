@@ -339,3 +339,72 @@ extern "C" int omni_aa_snake_nlc(const void* x, const float* alpha, const float*
       (const __nv_bfloat16*)x, alpha, inv_b, fu, fd, (__nv_bfloat16*)y, B, T, C / 8);
   return (int)cudaGetLastError();
 }
+
+namespace omni {
+
+// Row softmax in place over bf16 scores: x[r, :] = softmax(scale * x[r, :]).  One CTA per row; the row
+// is read twice (running maximum and sum in one pass, then the normalised write), the second time
+// from L2.  N % 8 == 0, ld % 8 == 0.  Used by the VAE's single-head attention, whose head width (the
+// channel count) is outside the flash kernel's head sizes: scores and P*V run as tcgen05 GEMMs.
+__global__ void __launch_bounds__(256)
+softmax_rows_kernel(__nv_bfloat16* __restrict__ x, long ld, int nvec, float scale_log2e) {
+  __nv_bfloat16* row = x + (long)blockIdx.x * ld;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += 256) {
+    const uint4 u = reinterpret_cast<const uint4*>(row)[i];
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    const float f[8] = {a.x * scale_log2e, a.y * scale_log2e, b.x * scale_log2e, b.y * scale_log2e,
+                        c.x * scale_log2e, c.y * scale_log2e, d.x * scale_log2e, d.y * scale_log2e};
+    float lm = f[0];
+#pragma unroll
+    for (int e = 1; e < 8; ++e) lm = fmaxf(lm, f[e]);
+    if (lm > m) {
+      s *= exp2f(m - lm);
+      m = lm;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s += exp2f(f[e] - m);
+  }
+  // combine (m, s) over the warp, then over the 8 warps
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
+    const float nm = fmaxf(m, om);
+    s = (nm == -INFINITY) ? 0.f : s * exp2f(m - nm) + os * exp2f(om - nm);
+    m = nm;
+  }
+  __shared__ float sm[8], ss[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sm[warp] = m;
+    ss[warp] = s;
+  }
+  __syncthreads();
+  float M = sm[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) M = fmaxf(M, sm[w]);
+  float S = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) S += (sm[w] == -INFINITY) ? 0.f : ss[w] * exp2f(sm[w] - M);
+  const float inv = S > 0.f ? 1.f / S : 0.f;
+  for (int i = threadIdx.x; i < nvec; i += 256) {
+    uint4 u = reinterpret_cast<const uint4*>(row)[i];
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    u.x = pack_bf16(exp2f(a.x * scale_log2e - M) * inv, exp2f(a.y * scale_log2e - M) * inv);
+    u.y = pack_bf16(exp2f(b.x * scale_log2e - M) * inv, exp2f(b.y * scale_log2e - M) * inv);
+    u.z = pack_bf16(exp2f(c.x * scale_log2e - M) * inv, exp2f(c.y * scale_log2e - M) * inv);
+    u.w = pack_bf16(exp2f(d.x * scale_log2e - M) * inv, exp2f(d.y * scale_log2e - M) * inv);
+    reinterpret_cast<uint4*>(row)[i] = u;
+  }
+}
+
+}  // namespace omni
+
+// x: bf16 [rows, N] with row pitch ld (elements), rewritten in place.
+extern "C" int omni_softmax_rows(void* x, long ld, long rows, int N, float scale, void* stream) {
+  if (rows <= 0 || N <= 0) return omni::RC_OK;
+  if ((N & 7) || (ld & 7) || ld < N || rows > 0x7fffffffL) return omni::RC_BAD_ARG;
+  omni::softmax_rows_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, ld, N / 8,
+                                                                             scale * 1.4426950408889634f);
+  return (int)cudaGetLastError();
+}

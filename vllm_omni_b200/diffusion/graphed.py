@@ -9,7 +9,8 @@ capture's static output (valid until the next call with the same signature).
 
 A model opts in with the class attribute ``graph_safe_forward = True`` (its forward keeps no state
 between calls of one signature).  Only forwards whose arguments are tensors, ``None``, numbers, strings, or (nested) tuples / lists of
-those are graphed; anything else runs eagerly.  Qwen-Image keeps its own captured loop
+those are graphed; anything else runs eagerly.  Small host tensors among the arguments (position ids) count
+by value.  Qwen-Image keeps its own captured loop
 (``prepare_loop`` / ``forward_step``).
 """
 from __future__ import annotations
@@ -24,9 +25,35 @@ total_replays = 0                 # over all wrappers of the process (tests, sta
 _SIMPLE = (type(None), bool, int, float, str)
 
 
+_CONSTS: dict = {}
+
+
+def device_constant(values, dtype, device) -> torch.Tensor:
+    """A small device tensor holding ``values`` (a flat sequence of numbers), created once per
+    (values, dtype, device) and kept for the life of the process.  A forward that builds such tensors from
+    Python numbers at every call (key lengths, position offsets) copies host memory to the device, which a
+    stream capture refuses; taking them from here makes the eager warm-up call create them and the captured
+    call reuse them.  Entries are never dropped (a captured graph may read them); past 512 entries new ones
+    are built uncached."""
+    key = (tuple(values), dtype, str(device))
+    t = _CONSTS.get(key)
+    if t is None:
+        t = torch.tensor(list(values), dtype=dtype, device=device)
+        if len(_CONSTS) < 512:
+            _CONSTS[key] = t
+    return t
+
+
 def _sig(x):
     if isinstance(x, torch.Tensor):
-        return ("T", tuple(x.shape), x.dtype, tuple(x.stride()), str(x.device))
+        if x.is_cuda:
+            return ("T", tuple(x.shape), x.dtype, tuple(x.stride()), str(x.device))
+        if x.numel() > (1 << 20):
+            raise TypeError("large host tensor")
+        # host tensors (position ids, small tables) are part of the signature by VALUE: the captured call saw
+        # these exact numbers, so a call with other numbers is another entry
+        raw = x.detach().contiguous().reshape(-1).view(torch.uint8).numpy().tobytes()
+        return ("C", tuple(x.shape), x.dtype, hash(raw))
     if isinstance(x, _SIMPLE):
         return ("V", x)
     if isinstance(x, (tuple, list)):
@@ -48,7 +75,8 @@ def _map(x, fn):
 
 def _copy_in(dst, src):
     if isinstance(dst, torch.Tensor):
-        dst.copy_(src)
+        if dst.is_cuda:
+            dst.copy_(src)
     elif isinstance(dst, (tuple, list)):
         for d, s in zip(dst, src):
             _copy_in(d, s)
@@ -83,7 +111,7 @@ class GraphedForward:
         except TypeError:
             return self._eager(args, kwargs)
         tens = [t for t in _flatten((args, kwargs)) if isinstance(t, torch.Tensor)]
-        if not tens or not all(t.is_cuda for t in tens):
+        if not any(t.is_cuda for t in tens):
             return self._eager(args, kwargs)
         ent = self.entries.get(key)
         if ent is None:
@@ -94,7 +122,8 @@ class GraphedForward:
             if ent.calls < self.warmup:
                 ent.calls += 1
                 return self._eager(args, kwargs)       # eager first: lazy tables, workspaces, function attributes
-            ent.args, ent.kwargs = _map(args, torch.clone), _map(kwargs, torch.clone)
+            own = lambda t: t.clone() if t.is_cuda else t          # host tensors are fixed by the signature
+            ent.args, ent.kwargs = _map(args, own), _map(kwargs, own)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             try:

@@ -151,7 +151,8 @@ class FluxTransformer2DModel(QwenImageTransformer2DModel):
         cos, sin = self._cos_sin(h, w, S_txt, dev, frames) if frames > 1 else self._cos_sin(h, w, S_txt, dev)
         kv_lens = None
         if txt_seq_lens is not None and any(int(l) != S_txt for l in txt_seq_lens):
-            kv_lens = torch.tensor([S_img + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
+            from ...graphed import device_constant
+            kv_lens = device_constant([S_img + int(l) for l in txt_seq_lens], torch.int32, dev)
         img = self.img_in(hidden_states.to(self.dtype_))
         txt = self.txt_in(encoder_hidden_states.to(self.dtype_).contiguous())
         vec = self.time_embed(timestep, self.dtype_)

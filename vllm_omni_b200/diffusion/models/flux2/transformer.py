@@ -214,7 +214,8 @@ class Flux2Transformer2DModel(nn.Module):
         cos, sin = self.cos_sin(img_ids, txt_ids, dev)
         kv_lens = None
         if txt_seq_lens is not None and any(int(l) != St for l in txt_seq_lens):
-            kv_lens = torch.tensor([Si + int(l) for l in txt_seq_lens], dtype=torch.int32, device=dev)
+            from ...graphed import device_constant
+            kv_lens = device_constant([Si + int(l) for l in txt_seq_lens], torch.int32, dev)
         t = timestep.reshape(-1).expand(B) if timestep.numel() == 1 else timestep.reshape(-1)
         temb = self.time_embed(t, c.timestep_guidance_channels, dt)
         if guidance is not None and self.guidance_embed is not None:

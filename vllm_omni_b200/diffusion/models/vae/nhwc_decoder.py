@@ -3,14 +3,14 @@
 Built from a ``Decoder2d`` (same parameters, repacked once): every convolution is an implicit
 GEMM on the tcgen05 kernel with bias / residual in its epilogue, RMS-norm + SiLU is one fused
 kernel per pixel row, activations stay NHWC bf16 from the latent to the image.  The single
-mid-block attention (one head of width C) stays on PyTorch's SDPA.  Replaces the cuDNN path the
+mid-block attention (one head of width C, outside the flash kernel's head sizes) is two GEMMs on the
+same kernel around a row-softmax kernel (``ops.conv.wide_head_attention``).  Replaces the cuDNN path the
 reference takes through diffusers (vllm_omni/diffusion/models/qwen_image/
 autoencoder_kl_qwenimage.py).
 """
 from __future__ import annotations
 
 import torch
-import torch.nn.functional as F
 
 from ....ops import conv as C
 
@@ -64,7 +64,7 @@ class NHWCDecoder:
                 _, gn, qkv, proj = st
                 B, H, W, ch = x.shape
                 t = qkv(C.rmsnorm_silu_nhwc(x, gn, silu=False)).view(B, H * W, 3, ch)
-                o = F.scaled_dot_product_attention(t[:, None, :, 0], t[:, None, :, 1], t[:, None, :, 2])[:, 0]
+                o = C.wide_head_attention(t[:, :, 0], t[:, :, 1], t[:, :, 2])
                 x = proj(o.reshape(B, H, W, ch).contiguous(), residual=x)
             else:
                 x = st[1](C.upsample2x_nhwc(x))

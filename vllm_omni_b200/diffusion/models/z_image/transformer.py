@@ -120,6 +120,7 @@ class ZImageTransformer2DModel(nn.Module):
         self.sp = None                   # SequenceParallelAttention when the unified sequence is sharded
         self.sp_style = "attention"
         self._tables = None
+        self._layouts: dict = {}          # geometry -> position tables and masks (see _layout)
 
     @staticmethod
     def validate_tp(c, tp):
@@ -184,6 +185,42 @@ class ZImageTransformer2DModel(nn.Module):
         f = fused.norm_modulate(blk.w2(fused.silu_mul(blk.w13(xn))), weight=blk.ffn_norm2, rms=True, eps=c.norm_eps)
         return (x + (torch.tanh(g2.float()).to(x.dtype)[:, None] * f if g2 is not None else f)).contiguous()
 
+    # ------------------------------------------------------------------ positions
+    def _layout(self, B, S_img, L, Fr, h, w, lens: tuple, dev) -> dict:
+        """Everything of a forward that depends only on the shapes and caption lengths: padded lengths, position
+        ids of image / caption / unified rows with their rotary tables, the rows that take the pad token and the
+        rows past every caption, the key lengths.  Built on the host once per geometry and kept on the device:
+        the denoising steps of a request (and a captured replay of them) reuse it."""
+        key = (B, S_img, L, Fr, h, w, lens, str(dev))
+        hit = self._layouts.get(key)
+        if hit is not None:
+            return hit
+        cap_p = [n + (-n) % SEQ_MULTI_OF for n in lens]                 # caption lengths with their pad tokens
+        S_x = S_img + (-S_img) % SEQ_MULTI_OF
+        Lc = max(cap_p)
+        grid = torch.stack(torch.meshgrid(torch.arange(Fr), torch.arange(h), torch.arange(w), indexing="ij"), -1).reshape(-1, 3)
+        x_ids = torch.zeros(B, S_x, 3, dtype=torch.long)
+        for b in range(B):
+            x_ids[b, :S_img] = grid + torch.tensor([cap_p[b] + 1, 0, 0])
+        j = torch.arange(Lc)[None, :]
+        lens_t, capp_t = torch.tensor(lens)[:, None], torch.tensor(cap_p)[:, None]
+        c_ids = torch.zeros(B, Lc, 3, dtype=torch.long)
+        c_ids[:, :, 0] = torch.where(j < capp_t, j + 1, torch.zeros_like(j))
+
+        def tables(ids):
+            n = ids.shape[1]
+            cs, sn = self._rope(ids.reshape(-1, 3).to(dev))
+            pos = torch.arange(B * n, dtype=torch.int32, device=dev).view(B, n)
+            return cs, sn, pos
+        ragged = min(cap_p) != Lc
+        lay = {"S_x": S_x, "Lc": Lc, "x": tables(x_ids), "c": tables(c_ids), "u": tables(torch.cat([x_ids, c_ids], dim=1)),
+               "pad_rows": ((j >= lens_t) & (j < capp_t)).to(dev), "dead_rows": (j >= capp_t).to(dev),
+               "cap_lens": torch.tensor(cap_p, dtype=torch.int32, device=dev) if ragged else None,
+               "kv_lens": torch.tensor([S_x + n for n in cap_p], dtype=torch.int32, device=dev) if ragged else None}
+        if len(self._layouts) < 16:           # never evicted: a captured graph may read these tensors
+            self._layouts[key] = lay
+        return lay
+
     # ------------------------------------------------------------------ forward
     def forward(self, hidden_states, encoder_hidden_states, timestep, img_shapes, txt_seq_lens=None, **_):
         """hidden_states: patchified latents [B, S_img, patch_dim]; encoder_hidden_states: caption features
@@ -197,51 +234,36 @@ class ZImageTransformer2DModel(nn.Module):
             img_shapes = img_shapes[0]
         Fr, h, w = img_shapes
         lens = [int(n) for n in txt_seq_lens] if txt_seq_lens is not None else [L] * B
-        cap_p = [n + (-n) % SEQ_MULTI_OF for n in lens]                 # caption lengths with their pad tokens
-        S_x = S_img + (-S_img) % SEQ_MULTI_OF
-        Lc = max(cap_p)
+        lay = self._layout(B, S_img, L, Fr, h, w, tuple(lens), dev)
+        S_x, Lc = lay["S_x"], lay["Lc"]
 
         temb = self.t_mlp2(self.t_mlp1(timestep_sinusoid(timestep, 256, c.t_scale).to(self.dtype_), act="silu"))
 
-        # image tokens, their pad tokens and positions
+        # image tokens and their pad tokens
         x = self.x_embedder(hidden_states.to(self.dtype_).contiguous())
         if S_x > S_img:
             x = torch.cat([x, self.x_pad_token.to(x.dtype).expand(B, S_x - S_img, -1)], dim=1)
-        grid = torch.stack(torch.meshgrid(torch.arange(Fr), torch.arange(h), torch.arange(w), indexing="ij"), -1).reshape(-1, 3)
-        x_ids = torch.zeros(B, S_x, 3, dtype=torch.long)
-        for b in range(B):
-            x_ids[b, :S_img] = grid + torch.tensor([cap_p[b] + 1, 0, 0])
         # caption tokens: the last real row repeated under the pad positions is replaced by the pad token
         enc = encoder_hidden_states[:, :min(L, Lc)].to(self.dtype_).contiguous()       # rows beyond the longest caption are padding
         L = enc.shape[1]
         cap = self.cap_embedder(fused.norm_modulate(enc, weight=self.cap_norm, rms=True, eps=c.norm_eps))
         if Lc > L:
             cap = torch.cat([cap, cap.new_zeros(B, Lc - L, D)], dim=1)
-        j = torch.arange(Lc, device=dev)[None, :]
-        lens_t, capp_t = torch.tensor(lens, device=dev)[:, None], torch.tensor(cap_p, device=dev)[:, None]
-        cap = torch.where(((j >= lens_t) & (j < capp_t))[..., None], self.cap_pad_token.to(cap.dtype)[None], cap)
-        cap = torch.where((j >= capp_t)[..., None], torch.zeros_like(cap), cap).contiguous()
-        c_ids = torch.zeros(B, Lc, 3, dtype=torch.long)
-        c_ids[:, :, 0] = torch.where(j.cpu() < capp_t.cpu(), j.cpu() + 1, torch.zeros_like(j.cpu()))
+        cap = torch.where(lay["pad_rows"][..., None], self.cap_pad_token.to(cap.dtype)[None], cap)
+        cap = torch.where(lay["dead_rows"][..., None], torch.zeros_like(cap), cap).contiguous()
 
-        def tables(ids):
-            n = ids.shape[1]
-            cs, sn = self._rope(ids.reshape(-1, 3).to(dev))
-            pos = torch.arange(B * n, dtype=torch.int32, device=dev).view(B, n)
-            return cs, sn, pos
-
-        xc, xs, xpos = tables(x_ids)
+        xc, xs, xpos = lay["x"]
         for blk in self.noise_refiner:
             x = self._block(blk, x, temb, xc, xs, xpos, None)
-        cc, cs_, cpos = tables(c_ids)
-        cap_lens = torch.tensor(cap_p, dtype=torch.int32, device=dev) if min(cap_p) != Lc else None
+        cc, cs_, cpos = lay["c"]
+        cap_lens = lay["cap_lens"]
         for blk in self.context_refiner:
             cap = self._block(blk, cap, None, cc, cs_, cpos, cap_lens)
 
         u = torch.cat([x, cap], dim=1).contiguous()                      # [B, S_x + Lc, D]; rows beyond S_x + cap_p[b] are padding
-        uc, us, upos = tables(torch.cat([x_ids, c_ids], dim=1))
+        uc, us, upos = lay["u"]
         S_full = u.shape[1]
-        kv_lens = torch.tensor([S_x + n for n in cap_p], dtype=torch.int32, device=dev) if min(cap_p) != Lc else None
+        kv_lens = lay["kv_lens"]
         sp, sp_lens = self.sp, None
         if sp is not None:
             # rows of the unified sequence are split over the SP group; padding rows are masked as keys

@@ -61,6 +61,10 @@ class LLMEngine:
         self._detok: dict[str, IncrementalDetokenizer] = {}
         self._reqs: dict[str, Request] = {}
         self._errors: list[RequestOutput] = []
+        # Steps between progress reports of a running request: 1 = every step (a stage whose output is streamed
+        # to the client), n > 1 = every n generated tokens (a stage whose frames feed a chunked consumer),
+        # 0 = only the finished request is reported (a stage nobody watches while it runs).
+        self.stream_interval = 1
 
     def _activation_reserve(self, dec) -> int:
         rows = int(getattr(self, "max_num_batched_tokens", 8192) or 8192)
@@ -206,9 +210,12 @@ class LLMEngine:
             # a hand-off criterion without a transfer manager: nothing will ever extract the KV
             self.scheduler.update_from_output(type(sched)(), {}, list(sched.kv_transfer_ids))
         now = time.time()
+        every = self.stream_interval
         for req in touched:
             if req.first_token_time is None:
                 req.first_token_time = now
+            if every != 1 and not req.is_finished() and (every <= 0 or len(req.output_token_ids) % every):
+                continue        # unreported progress rides in the next report: nothing is marked as sent
             outs.append(self._make_output(req))
             if req.is_finished():
                 self._reqs.pop(req.request_id, None)

@@ -34,6 +34,7 @@ class OmniEngineArgs:
     custom_process_next_stage_input_func: str | None = None
     stage_connector_spec: dict | None = None
     async_chunk: bool = False
+    stream_interval: int = 1              # generated tokens between progress reports of a running request (0 = none)
     omni_kv_config: dict = field(default_factory=dict)
     worker_type: str = "ar"
     scheduler_cls: str | None = None
@@ -135,6 +136,7 @@ class OmniLLM:
                                 max_num_batched_tokens=a.max_num_batched_tokens, max_model_len=a.max_model_len,
                                 kv_transfer_criteria=crit, chunk_adapter=chunk_adapter, kv_transfer_manager=kv_mgr,
                                 stage_id=stage_id, engine_output_type=a.engine_output_type)
+        self.engine.stream_interval = int(a.stream_interval)
         if tp_group is not None and hasattr(self.engine.runner, "tp_group"):
             self.engine.runner.tp_group = tp_group
         self._profiler = None

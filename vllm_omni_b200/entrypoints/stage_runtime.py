@@ -188,7 +188,19 @@ def make_adapter(cfg: StageConfig, model: str, batch_timeout_s: float) -> StageE
     if cfg.stage_type == "diffusion":
         return DiffusionStageAdapter(cfg.stage_id, model, dict(cfg.engine_args), int(rt.get("max_batch_size", 1)),
                                      batch_timeout_s)
-    return LLMStageAdapter(cfg.stage_id, model, dict(cfg.engine_args))
+    args = dict(cfg.engine_args)
+    if "stream_interval" not in args:
+        # Progress reports cross a process boundary one message (and one device-to-host copy per tensor) each:
+        # only the stage the client watches reports every step; a talker that feeds a chunked vocoder reports
+        # once per chunk of frames; other intermediate stages report the finished request only.
+        if cfg.final_output:
+            args["stream_interval"] = 1
+        elif args.get("async_chunk") and args.get("model_stage") == "talker":
+            from ..models.stage_input_processors.qwen3_omni import CHUNK_FRAMES
+            args["stream_interval"] = CHUNK_FRAMES
+        else:
+            args["stream_interval"] = 0
+    return LLMStageAdapter(cfg.stage_id, model, args)
 
 
 # adapters of stages that run on a thread of this process, by stage id (introspection, tests)

@@ -295,3 +295,40 @@ def aa_snake_nlc(x, a, inv_b, up_filter, down_filter):
                                              nv.ptr(out), c_int(B), c_int(T), c_int(C), nv.stream_ptr())
     nv.check_rc(rc, "omni_aa_snake_nlc")
     return out
+
+
+def softmax_rows_(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """x [rows, N] bf16 (row pitch a multiple of 8 elements) <- softmax(scale * x) along the last dim, in place
+    (csrc/vae_ops.cu ``omni_softmax_rows``)."""
+    if not x.is_cuda:
+        x.copy_(torch.softmax(x.float() * scale, dim=-1))
+        return x
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+    rc = nv.lib("vae_ops").omni_softmax_rows(nv.ptr(x), ctypes.c_long(x.stride(0)), ctypes.c_long(x.shape[0]),
+                                             c_int(x.shape[1]), ctypes.c_float(scale), nv.stream_ptr())
+    nv.check_rc(rc, "omni_softmax_rows")
+    return x
+
+
+def wide_head_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunk_rows: int = 4096) -> torch.Tensor:
+    """One attention head whose width is the channel count (the VAE mid block: 384 or 512), which the flash
+    kernel's head sizes do not cover.  q, k, v: [B, N, C] bf16 views with the last dim contiguous.  On a GPU:
+    scores = q k^T on the tcgen05 GEMM for ``chunk_rows`` queries at a time, row softmax in place, P v on the
+    GEMM again against v transposed once; the score block (chunk_rows x N bf16) is the only scratch."""
+    B, N, C = q.shape
+    scale = C ** -0.5
+    if not q.is_cuda or q.dtype != torch.bfloat16 or N % 8 or C % 8:
+        return F.scaled_dot_product_attention(q[:, None], k[:, None], v[:, None])[:, 0]
+    from .gemm import linear
+    out = torch.empty(B, N, C, dtype=q.dtype, device=q.device)
+    rows = min(chunk_rows, N)
+    scores = torch.empty(rows, N, dtype=q.dtype, device=q.device)
+    for b in range(B):
+        vt = v[b].t().contiguous()
+        for r0 in range(0, N, rows):
+            n = min(rows, N - r0)
+            s = scores[:n]
+            linear(q[b, r0:r0 + n], k[b], out=s)
+            softmax_rows_(s, scale)
+            linear(s, vt, out=out[b, r0:r0 + n])
+    return out

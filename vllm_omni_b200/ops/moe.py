@@ -148,6 +148,9 @@ def moe_forward(x, router_logits, w13, w2, k, renorm=True, e_lo=0, e_hi=None, ws
     g = nv.lib("gemm_sm100")
     status = nv.status_word(x.device)
     El = w13.shape[0]
+    if nv.bounds_check_enabled():
+        # checked build: expert ids outside [0, E) and rows outside the expert-major buffers are reported, not used
+        lib.omni_moe_set_bounds(c_long(ws.xp.shape[0]), nv.ptr(status))
     if ws.padded:
         nv.check_rc(lib.omni_moe_plan(nv.ptr(ws.ids), c_int(T * k), c_int(E), c_int(e_lo), c_int(e_hi),
                                       c_int(ws.max_tiles), nv.ptr(ws.row_of_pair), nv.ptr(ws.tile_expert),
