@@ -174,3 +174,38 @@ stage_args:
         assert state["actors"] == 1 and state["bundles"] == [{"GPU": 1.0, "CPU": 1.0}]
     finally:
         omni.close()
+
+
+def test_custom_pipeline_class_runs_behind_the_engine(tmp_path, monkeypatch):
+    """``diffusion_load_format='custom_pipeline'``: the workers build the class named in
+    ``custom_pipeline_args`` with the remaining keys as constructor arguments."""
+    import sys
+
+    import torch
+
+    from vllm_omni_b200.entrypoints.omni import Omni
+    from vllm_omni_b200.inputs import OmniDiffusionSamplingParams
+    (tmp_path / "my_pipes.py").write_text(
+        "from vllm_omni_b200.diffusion.models.tiny_mmdit.pipeline import TinyMMDiTPipeline\n"
+        "class Doubled(TinyMMDiTPipeline):\n"
+        "    def __init__(self, od_config, device=None, gain=1.0):\n"
+        "        super().__init__(od_config, device=device)\n"
+        "        self.gain = gain\n"
+        "    def forward(self, req):\n"
+        "        out = super().forward(req)\n"
+        "        out.output = out.output * self.gain\n"
+        "        return out\n")
+    monkeypatch.syspath_prepend(str(tmp_path))
+    monkeypatch.setenv("PYTHONPATH", str(tmp_path) + ":" + __import__("os").environ.get("PYTHONPATH", ""))
+    sp = OmniDiffusionSamplingParams(height=32, width=32, num_inference_steps=2, seed=3, output_type="pt")
+
+    def run(**kw):
+        o = Omni("TinyMMDiTPipeline", dtype="float32", device="cpu", output_type="pt", **kw)
+        try:
+            return torch.as_tensor(o.generate(["x"], sp)[0].images[0]).float()
+        finally:
+            o.close()
+    base = run(diffusion_load_format="dummy")
+    got = run(diffusion_load_format="custom_pipeline", custom_pipeline_args={"pipeline_class": "my_pipes.Doubled", "gain": 0.0})
+    assert base.abs().max() > 0 and got.shape == base.shape and got.abs().max() == 0      # the subclass's forward ran
+    sys.modules.pop("my_pipes", None)

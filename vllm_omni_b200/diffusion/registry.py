@@ -71,8 +71,20 @@ def _local_pkgs():
 
 def initialize_model(od_config: OmniDiffusionConfig, device=None):
     """Instantiate the pipeline, attach sequence-parallel plans and VAE patch parallelism."""
-    cls = resolve_pipeline_class(od_config.model_class_name)
-    pipe = cls(od_config, device=device)
+    extra = {}
+    if od_config.diffusion_load_format == "custom_pipeline":
+        # a user class behind the engine (vllm_omni/diffusion/model_loader/diffusers_loader.py:217-226,
+        # worker/diffusion_worker.py:291-311): ``custom_pipeline_args["pipeline_class"]`` is its qualified
+        # name, the other keys are keyword arguments of its constructor
+        args = dict(od_config.custom_pipeline_args or {})
+        name = args.pop("pipeline_class", None)
+        if not name:
+            raise ValueError("diffusion_load_format='custom_pipeline' needs custom_pipeline_args['pipeline_class']")
+        mod, _, attr = name.rpartition(".")
+        cls, extra = getattr(importlib.import_module(mod), attr), args
+    else:
+        cls = resolve_pipeline_class(od_config.model_class_name)
+    pipe = cls(od_config, device=device, **extra)
     pc = od_config.parallel_config
     if pc.sequence_parallel_size > 1 or pc.cfg_parallel_size > 1 or pc.tensor_parallel_size > 1:
         from ..parallel.apply import apply_parallelism

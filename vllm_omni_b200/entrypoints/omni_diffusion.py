@@ -53,7 +53,8 @@ def build_diffusion_config(model: str | None = None, od_config: OmniDiffusionCon
                 cfg.vae_config = vc
         elif m in _DIFFUSION_MODELS:
             cfg.model_class_name = m
-            cfg.diffusion_load_format = "dummy"
+            if cfg.diffusion_load_format != "custom_pipeline":
+                cfg.diffusion_load_format = "dummy"
         elif m:
             guess = {"qwen-image": "QwenImagePipeline", "wan": "WanPipeline", "flux": "FluxPipeline",
                      "z-image": "ZImagePipeline", "stable-diffusion-3": "StableDiffusion3Pipeline",
@@ -62,7 +63,8 @@ def build_diffusion_config(model: str | None = None, od_config: OmniDiffusionCon
             for k, v in guess.items():
                 if k in low:
                     cfg.model_class_name = v
-                    cfg.diffusion_load_format = "dummy"
+                    if cfg.diffusion_load_format != "custom_pipeline":
+                        cfg.diffusion_load_format = "dummy"
                     break
     if cfg.model_class_name is None:
         raise ValueError(f"cannot determine the pipeline class for model {m!r}; pass model_class_name")
