@@ -64,6 +64,6 @@ def test_z_image_forward_replayed_from_a_graph_equals_eager(monkeypatch):
     captured call copies nothing from the host."""
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
-    tf = dict(dim=128, n_layers=1, n_refiner_layers=1, n_heads=2, n_kv_heads=2, cap_feat_dim=32,
+    tf = dict(dim=192, n_layers=1, n_refiner_layers=1, n_heads=3, n_kv_heads=3, cap_feat_dim=32,     # MLP width 512
               axes_dims=(16, 24, 24), axes_lens=(128, 32, 32))
     _replay_vs_eager(monkeypatch, "ZImagePipeline", tf, 16)

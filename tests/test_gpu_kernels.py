@@ -298,6 +298,8 @@ def test_vae_decoder_nhwc_matches_torch(dev):
 def test_wide_head_attention_gemm_softmax_gemm(dev):
     """The VAE's one-head attention: two GEMM launches around the row-softmax kernel, queries in chunks."""
     import torch.nn.functional as F
+
+    from vllm_omni_b200.ops import conv as C
     torch.manual_seed(9)
     B, N, ch = 2, 1000, 384
     t = torch.randn(B, N, 3, ch, device=dev, dtype=torch.bfloat16)

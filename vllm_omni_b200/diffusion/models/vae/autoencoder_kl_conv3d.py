@@ -23,6 +23,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ....ops.conv import wide_head_attention
+
 
 @dataclass
 class Conv3dVAEConfig:
@@ -89,8 +91,8 @@ class AttnBlock3d(nn.Module):
     def forward(self, x):
         B, C, Fr, H, W = x.shape
         h = self.norm(x)
-        q, k, v = (m(h).flatten(2).transpose(1, 2)[:, None] for m in (self.q, self.k, self.v))   # [B, 1, L, C]
-        o = F.scaled_dot_product_attention(q, k, v)[:, 0].transpose(1, 2).reshape(B, C, Fr, H, W)
+        q, k, v = (m(h).flatten(2).transpose(1, 2).contiguous() for m in (self.q, self.k, self.v))   # [B, L, C]
+        o = wide_head_attention(q, k, v).transpose(1, 2).reshape(B, C, Fr, H, W)
         return x + self.proj_out(o)
 
 

@@ -18,6 +18,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ....ops.conv import wide_head_attention
+
 
 @dataclass
 class QwenImageVAEConfig:
@@ -77,8 +79,8 @@ class AttnBlock(nn.Module):
 
     def forward(self, x):
         B, C, H, W = x.shape
-        qkv = self.to_qkv(self.norm(x)).reshape(B, 3, C, H * W).permute(1, 0, 3, 2)   # 3, B, HW, C
-        o = F.scaled_dot_product_attention(qkv[0][:, None], qkv[1][:, None], qkv[2][:, None])[:, 0]
+        qkv = self.to_qkv(self.norm(x)).reshape(B, 3, C, H * W).permute(1, 0, 3, 2).contiguous()   # 3, B, HW, C
+        o = wide_head_attention(qkv[0], qkv[1], qkv[2])
         o = o.permute(0, 2, 1).reshape(B, C, H, W)
         return x + self.proj(o)
 
