@@ -166,6 +166,15 @@ def _audio_to_wav(audio) -> bytes:
     return buf.getvalue()
 
 
+def _frames_to_gif(frames, fps: int = 8) -> bytes:
+    from PIL import Image
+    arr = np.asarray(frames.cpu() if hasattr(frames, "cpu") else frames)
+    ims = [Image.fromarray((np.clip(a, 0, 1) * 255).astype(np.uint8)) for a in arr]
+    buf = io.BytesIO()
+    ims[0].save(buf, format="GIF", save_all=True, append_images=ims[1:], duration=int(1000 / fps), loop=0)
+    return buf.getvalue()
+
+
 def check_server(server: str, model: str):
     """ComfyUI ``VALIDATE_INPUTS`` helper: True or the message shown on the node."""
     if not isinstance(server, str) or not server.startswith(("http://", "https://")):
@@ -384,12 +393,11 @@ class OmniComprehension(OmniChat):
             for i in range(len(image) if hasattr(image, "__len__") and getattr(image, "ndim", 4) == 4 else 1):
                 b64 = base64.b64encode(_image_to_png(image[i:i + 1] if getattr(image, "ndim", 4) == 4 else image)).decode()
                 content.append({"type": "image_url", "image_url": {"url": "data:image/png;base64," + b64}})
-        if video is not None:          # a frame batch: sent as a list of frames
-            frames = ["data:image/png;base64," + base64.b64encode(_image_to_png(video[i:i + 1])).decode() for i in range(len(video))]
-            content.append({"type": "video_frames", "video_frames": {"frames": frames}})
+        if video is not None:          # a frame batch: sent as an animated GIF in a data URL
+            content.append({"type": "video_url", "video_url": {"url": "data:image/gif;base64," + base64.b64encode(_frames_to_gif(video)).decode()}})
         if audio is not None:
-            content.append({"type": "input_audio",
-                            "input_audio": {"data": base64.b64encode(_audio_to_wav(audio)).decode(), "format": "wav"}})
+            content.append({"type": "audio_url",
+                            "audio_url": {"url": "data:audio/wav;base64," + base64.b64encode(_audio_to_wav(audio)).decode()}})
         content.append({"type": "text", "text": prompt})
         msgs = ([{"role": "system", "content": system_prompt}] if system_prompt.strip() else []) + [{"role": "user", "content": content}]
         body = {"model": model, "messages": msgs,

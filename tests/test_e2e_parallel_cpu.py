@@ -141,3 +141,23 @@ def test_wan_tensor_parallel_matches_single_process():
             omni.close()
     a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(tensor_parallel_size=2))
     assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4
+
+
+def test_z_image_ulysses_matches_single_process():
+    """Z-Image (single stream, unified [image | caption] rows sharded over the group) through ``Omni``."""
+    tf = dict(dim=64, n_layers=1, n_refiner_layers=1, n_heads=2, n_kv_heads=2, cap_feat_dim=32, axes_dims=(8, 12, 12),
+              axes_lens=(128, 32, 32))
+    vae = dict(block_out_channels=(8, 16, 16, 16), layers_per_block=1, norm_num_groups=4)
+
+    def run(par):
+        omni = Omni("ZImagePipeline", dtype="float32", device="cpu", tf_model_config=tf, vae_config=vae,
+                    diffusion_load_format="dummy", parallel_config=par, output_type="latent")
+        try:
+            sp = OmniDiffusionSamplingParams(height=64, width=64, num_inference_steps=2, guidance_scale=3.5, seed=0,
+                                             output_type="latent", max_sequence_length=8)
+            out = omni.generate([{"prompt": "a cube", "negative_prompt": "blurry"}], sp)[0]
+            return torch.as_tensor(out.latents if out.latents is not None else out.images[0]).float()
+        finally:
+            omni.close()
+    a, b = run(DiffusionParallelConfig()), run(DiffusionParallelConfig(ulysses_degree=2))
+    assert a.shape == b.shape and (a - b).abs().max().item() < 1e-4

@@ -40,6 +40,11 @@ def test_comfy_nodes_round_trip(monkeypatch):
 
     def fake_post(url, **kw):
         seen[url.rsplit("/", 1)[-1]] = kw
+        if url.endswith("videos"):
+            buf = io.BytesIO()
+            Image.new("RGB", (8, 4), (0, 255, 0)).save(buf, format="PNG")
+            b = base64.b64encode(buf.getvalue()).decode()
+            return Resp({"data": [{"frames_b64": [b, b, b], "fps": 12}]})
         if url.endswith("generations") or url.endswith("edits"):
             buf = io.BytesIO()
             Image.new("RGB", (8, 4), (255, 0, 0)).save(buf, format="PNG")
@@ -65,6 +70,35 @@ def test_comfy_nodes_round_trip(monkeypatch):
     text, audio = NODE_CLASS_MAPPINGS["OmniChat"]().run("http://s", "m", "hello", True, image=img[:1])
     assert text == "hi" and tuple(audio["waveform"].shape) == (1, 1, 4)
     assert seen["completions"]["json"]["messages"][0]["content"][1]["type"] == "image_url"
+    frames, fps = NODE_CLASS_MAPPINGS["OmniVideoGenerate"]().run("http://s", "m", "p", 8, 4, 3, 12, 2, 4.0, 0, image=img[:1])
+    assert tuple(frames.shape) == (3, 4, 8, 3) and fps == 12 and seen["videos"]["json"]["response_format"] == "frames_b64"
+    assert "image" in seen["videos"]["json"]
+    # parameter nodes feed the request bodies; cloning sends the clip inline; the chat node sends audio and video inline
+    ar, = NODE_CLASS_MAPPINGS["OmniARSampling"]().get(seed=-1, top_k=0, max_tokens=64, temperature=0.7, top_p=0.9, repetition_penalty=1.0)
+    dif, = NODE_CLASS_MAPPINGS["OmniDiffusionSampling"]().get(seed=3, n=2, num_inference_steps=20, guidance_scale=0.0, true_cfg_scale=4.0)
+    lst, = NODE_CLASS_MAPPINGS["OmniSamplingParamsList"]().get(ar, dif)
+    assert lst["list"][0]["max_tokens"] == 64 and "seed" not in lst["list"][0] and lst["list"][1]["seed"] == 3
+    tts, = NODE_CLASS_MAPPINGS["OmniQwenTTSParams"]().get(task_type="VoiceDesign", language="Auto", instructions="calm", max_new_tokens=99)
+    NODE_CLASS_MAPPINGS["OmniTTS"]().run("http://s", "m", "hello", "Vivian", tts_params=tts)
+    body = seen["speech"]["json"]
+    assert body["task_type"] == "VoiceDesign" and body["instructions"] == "calm" and "language" not in body and body["max_new_tokens"] == 99
+    clip = {"waveform": audio["waveform"], "sample_rate": 24000}
+    NODE_CLASS_MAPPINGS["OmniVoiceClone"]().run("http://s", "m", "hello", clip, "the transcript", False)
+    body = seen["speech"]["json"]
+    assert body["task_type"] == "Base" and body["ref_text"] == "the transcript" and "voice" not in body
+    assert base64.b64decode(body["ref_audio"].split(",", 1)[1])[:4] == b"RIFF"
+    with pytest.raises(ValueError):
+        NODE_CLASS_MAPPINGS["OmniVoiceClone"]().run("http://s", "m", "hello", clip, "  ", False)
+    text, _ = NODE_CLASS_MAPPINGS["OmniComprehension"]().run("http://s", "m", "what?", True, False, image=img[:1], audio=clip,
+                                                             video=img, system_prompt="be brief", sampling_params=lst)
+    body = seen["completions"]["json"]
+    kinds = [p["type"] for p in body["messages"][1]["content"]]
+    assert text == "hi" and kinds == ["image_url", "video_url", "audio_url", "text"] and body["modalities"] == ["text"]
+    assert body["messages"][0]["role"] == "system" and len(body["sampling_params_list"]) == 2 and "type" not in body["sampling_params_list"][0]
+    assert base64.b64decode(body["messages"][1]["content"][1]["video_url"]["url"].split(",", 1)[1])[:3] == b"GIF"
+    assert NODE_CLASS_MAPPINGS["OmniComprehension"].VALIDATE_INPUTS("ftp://x", "m") is not True
+    assert NODE_CLASS_MAPPINGS["OmniComprehension"].VALIDATE_INPUTS("http://x", "m", False, False) is not True
+    assert NODE_CLASS_MAPPINGS["OmniTTS"].VALIDATE_INPUTS("http://x", "m") is True
 
 
 def test_offline_throughput_benchmark_tiny():

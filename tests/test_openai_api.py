@@ -121,3 +121,50 @@ def test_real_tiny_omni_chat_and_speech(tmp_path):
             assert "Vivian" in c.get("/v1/audio/voices").json()["voices"]
     finally:
         eng.close()
+
+
+def test_chat_with_audio_and_image_parts_reaches_the_engine_as_features():
+    """Audio / image parts of a chat message arrive at the engine as log-mel features and pixel tensors, and the
+    prompt text carries one placeholder group per item where the item stood."""
+    import io
+    import wave
+
+    import numpy as np
+    from PIL import Image
+
+    from vllm_omni_b200.inputs.omni_processor import PLACEHOLDER
+
+    class Capture:
+        tokenizer = None
+        mm_processor_kwargs = {"vision_factor": 16, "n_mels": 16}
+
+        def __init__(self):
+            self.prompts = []
+
+        async def generate(self, prompt, request_id=None, sampling_params_list=None, output_modalities=None):
+            self.prompts.append(prompt)
+            return
+            yield   # pragma: no cover  (an async generator that yields nothing)
+
+    buf = io.BytesIO()
+    with wave.open(buf, "wb") as f:
+        f.setnchannels(1)
+        f.setsampwidth(2)
+        f.setframerate(16000)
+        f.writeframes((np.sin(np.arange(3200) / 5) * 12000).astype("<i2").tobytes())
+    png = io.BytesIO()
+    Image.new("RGB", (96, 64), (9, 9, 200)).save(png, format="PNG")
+    eng = Capture()
+    with TestClient(build_app(eng, "cap", kind="omni")) as c:
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+            {"type": "audio_url", "audio_url": {"url": "data:audio/wav;base64," + base64.b64encode(buf.getvalue()).decode()}},
+            {"type": "image_url", "image_url": {"url": "data:image/png;base64," + base64.b64encode(png.getvalue()).decode()}},
+            {"type": "text", "text": "what is this?"}]}]})
+        assert r.status_code == 200, r.text
+        p = eng.prompts[0]
+        assert PLACEHOLDER["audio"] + PLACEHOLDER["image"] + "what is this?" in p["prompt"]
+        mm = p["multi_modal_data"]
+        assert tuple(mm["audio"][0].shape) == (16, 20) and tuple(mm["image"][0].shape) == (1, 3, 64, 96)
+        bad = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+            {"type": "input_audio", "input_audio": {"data": base64.b64encode(b"ID3 not a wav").decode(), "format": "mp3"}}]}]})
+        assert bad.status_code == 400 and "WAV" in bad.text

@@ -49,23 +49,51 @@ def _parse_lora_request(lora: dict | None) -> tuple[LoRARequest | None, float]:
     return LoRARequest(name, lid or 1, path, float(lora.get("scale", 1.0))), float(lora.get("scale", 1.0))
 
 
-def _flatten_content(content) -> tuple[str, dict]:
-    """OpenAI message content -> (text, multi_modal_data)."""
+def _flatten_content(content, placeholders: bool = False) -> tuple[str, dict]:
+    """OpenAI message content -> (text, raw multimodal items).  Items: ``image`` PIL images, ``audio`` (waveform,
+    rate) pairs, ``video`` frame lists.  With ``placeholders`` the text carries one placeholder group per item at
+    the item's position in the message (the omni thinker expands it to the item's feature length)."""
     if content is None:
         return "", {}
     if isinstance(content, str):
         return content, {}
+    from ...inputs import omni_processor as op
     text, mm = [], {}
+
+    def _url(part, key):
+        v = part.get(key)
+        return v.get("url") if isinstance(v, dict) else v
+
     for part in content:
         t = part.get("type")
         if t == "text":
             text.append(part.get("text", ""))
         elif t == "image_url":
-            url = part["image_url"]["url"] if isinstance(part.get("image_url"), dict) else part.get("image_url")
+            url = _url(part, "image_url")
             if isinstance(url, str) and (url.startswith("data:") or len(url) > 256):
                 mm.setdefault("image", []).append(mu.decode_image_base64(url))
+                if placeholders:
+                    text.append(op.PLACEHOLDER["image"])
         elif t in ("input_audio", "audio_url"):
-            mm.setdefault("audio_ref", []).append(part.get(t))
+            src = part.get("input_audio") if t == "input_audio" else _url(part, "audio_url")
+            data = src.get("data") if isinstance(src, dict) else src
+            if not isinstance(data, str) or data.startswith(("http://", "https://")):
+                raise ValueError("audio input must be inline (base64 or a data: URL); remote URLs are not fetched")
+            mm.setdefault("audio", []).append(op.decode_audio_bytes(op.decode_data_url(data)))
+            if placeholders:
+                text.append(op.PLACEHOLDER["audio"])
+        elif t == "video_url":
+            url = _url(part, "video_url")
+            if not isinstance(url, str) or url.startswith(("http://", "https://")):
+                raise ValueError("video input must be inline (a data: URL of an animated GIF); remote URLs are not fetched")
+            mm.setdefault("video", []).append(op.gif_frames(op.decode_data_url(url)))
+            if placeholders:
+                text.append(op.PLACEHOLDER["video"])
+        elif t == "video_frames":
+            fr = (part.get("video_frames") or {}).get("frames") or []
+            mm.setdefault("video", []).append([mu.decode_image_base64(f) for f in fr])
+            if placeholders:
+                text.append(op.PLACEHOLDER["video"])
     return "".join(text), mm
 
 
@@ -338,11 +366,18 @@ def build_app(engine, model_name: str = "omni", kind: str = "omni", default_stag
         tok = getattr(engine, "tokenizer", None)
         msgs = []
         mm_all: dict = {}
-        for m in req.messages:
-            t, mm = _flatten_content(m.content)
-            msgs.append({"role": m.role, "content": t})
-            for k, v in mm.items():
-                mm_all.setdefault(k, []).extend(v)
+        try:
+            for m in req.messages:
+                t, mm = _flatten_content(m.content, placeholders=True)
+                msgs.append({"role": m.role, "content": t})
+                for k, v in mm.items():
+                    mm_all.setdefault(k, []).extend(v)
+            if mm_all:
+                # raw items -> the tensors the thinker's towers take (pixels, frames, log-mel features)
+                from ...inputs.omni_processor import thinker_inputs
+                mm_all = thinker_inputs(mm_all, **(getattr(engine, "mm_processor_kwargs", None) or {}))
+        except ValueError as e:
+            return _err(400, str(e))
         if tok is not None and hasattr(tok, "apply_chat_template"):
             text = tok.apply_chat_template(msgs, add_generation_prompt=True, tokenize=False)
         else:

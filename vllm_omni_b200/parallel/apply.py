@@ -23,6 +23,13 @@ def install_sp_plan(tr, group) -> None:
         tr._sp_hook_registry = apply_sp_plan(tr, plan, group)
 
 
+def _heads_of(cfg) -> tuple[int, int]:
+    """(attention heads, head width) of a transformer config, whichever of the two naming schemes it uses."""
+    h = getattr(cfg, "num_attention_heads", None) or getattr(cfg, "n_heads")
+    d = getattr(cfg, "attention_head_dim", None) or getattr(cfg, "head_dim")
+    return int(h), int(d)
+
+
 def apply_parallelism(pipe, od_config) -> None:
     pc = od_config.parallel_config
     tr = getattr(pipe, "transformer", None)
@@ -35,8 +42,7 @@ def apply_parallelism(pipe, od_config) -> None:
         from .sp_attention import SequenceParallelAttention
         for t in (tr, getattr(pipe, "transformer_2", None)):
             if t is not None:
-                t.sp = SequenceParallelAttention(ps.get_sp_group(), t.cfg.num_attention_heads, t.cfg.attention_head_dim,
-                                                 mode=os.environ.get("OMNI_SP_MODE"))
+                t.sp = SequenceParallelAttention(ps.get_sp_group(), *_heads_of(t.cfg), mode=os.environ.get("OMNI_SP_MODE"))
     elif pc.ulysses_degree > 1 and pc.ring_degree > 1 and tr is not None:
         from .hybrid import HybridJointAttention
         tr.sp = HybridJointAttention(ps.get_sp_group(), tr.cfg.num_attention_heads, tr.cfg.attention_head_dim,
