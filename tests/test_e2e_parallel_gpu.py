@@ -82,3 +82,28 @@ def test_flux_cfg_parallel_is_refused_or_matches():
         _check("flux", DiffusionParallelConfig(cfg_parallel_size=2))
     except (ValueError, RuntimeError, NotImplementedError) as e:
         assert "cfg" in str(e).lower() or "guidance" in str(e).lower()
+
+
+def test_fp8_pipeline_one_gpu_close_to_bf16():
+    """``quantization="fp8"`` through the public API on a GPU: the block-scaled e4m3 GEMM kernel carries the
+    eligible linear layers; the latents stay close to the bf16 run and are not identical to it."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    tf = dict(num_layers=2, num_single_layers=2, attention_head_dim=128, num_attention_heads=2, joint_attention_dim=128,
+              pooled_projection_dim=32, in_channels=64, out_channels=16, axes_dims_rope=(32, 48, 48))
+
+    def run(**kw):
+        omni = Omni("FluxPipeline", dtype="bfloat16", device="cuda", tf_model_config=tf, vae_config=VAE_KL,
+                    diffusion_load_format="dummy", output_type="latent", **kw)
+        try:
+            sp = OmniDiffusionSamplingParams(num_inference_steps=3, seed=0, output_type="latent", height=256, width=256,
+                                             guidance_scale=3.5, max_sequence_length=16)
+            out = omni.generate(["a cube"], sp)[0]
+            return torch.as_tensor(out.latents if out.latents is not None else out.images[0]).float().cpu()
+        finally:
+            omni.close()
+    a = run()
+    b = run(quantization="fp8", quantization_config={"min_features": 128})
+    assert a.shape == b.shape and torch.isfinite(b).all()
+    rel = ((a - b).norm() / a.norm()).item()
+    assert 0.0 < rel < 0.15, rel
