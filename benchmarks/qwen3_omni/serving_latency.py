@@ -170,6 +170,7 @@ async def _run(a, path):
            "audio_ttfp_s": {f"p{q}": _pct([r["ttfp"] for r in recs if r["ttfp"] is not None], q) for q in (50, 90, 99)},
            "e2el_s": {f"p{q}": _pct([r["latency"] for r in recs], q) for q in (50, 90, 99)},
            "stages": _stage_split(eng_stats), "timed_out": timed_out,
+           "talkers_started_from_running_thinker": int(getattr(eng, "stream_starts", 0)),
            "config": {"tiny": a.tiny, "input_len": a.input_len, "audio_seconds": a.audio_seconds,
                       "thinker_tp": a.thinker_tp, "thinker_ep": a.thinker_ep, "tail_device": a.tail_device,
                       "stage_processes": a.stage_processes, "max_tokens": a.max_tokens, "codec_frames": a.codec_frames,

@@ -76,3 +76,30 @@ def test_async_chunk_streams_audio_in_pieces(tmp_path):
         assert len(audio) >= 2 and total >= 25 * 16 - 64
     finally:
         eng.close()
+
+
+def test_async_chunk_talker_starts_from_the_running_thinker_and_matches_whole_request_hand_off(tmp_path):
+    """Under ``async_chunk`` the talker is started once the thinker's prompt rows and first reply row exist and
+    gets the later rows as updates; a decode step whose reply row has not arrived waits for it.  The codec
+    frames and the text must equal the run in which the talker starts after the thinker has finished."""
+    def run(async_chunk):
+        y = YAML.replace("async_chunk: false", f"async_chunk: {'true' if async_chunk else 'false'}")
+        y = y.replace("max_tokens: 7", "max_tokens: 40").replace("max_tokens: 5", "max_tokens: 30, ignore_eos: true")
+        y = y.replace("stop_token_ids: [66]", "stop_token_ids: [], ignore_eos: true")
+        p = tmp_path / f"cfg_{async_chunk}.yaml"
+        p.write_text(y)
+        eng = AsyncOmni("qwen3-omni-tiny", stage_configs_path=str(p))
+        try:
+            outs = asyncio.run(_collect(eng, _prompt(), "r"))
+            text = [o for o in outs if o.final_output_type == "text"][-1].outputs[0].token_ids
+            ro = eng.stage_list[1].engine_outputs[0]
+            ro = getattr(ro, "request_output", None) or ro
+            codes = ro.outputs[0].multimodal_output["codes"].clone()
+            return list(text), codes, eng.stream_starts
+        finally:
+            eng.close()
+    t0, c0, n0 = run(False)
+    t1, c1, n1 = run(True)
+    assert n0 == 0 and n1 == 1                      # the streamed start really happened
+    assert t0 == t1 and len(t0) == 30
+    assert c0.shape == c1.shape and c0.shape[0] == 40 and torch.equal(c0, c1)

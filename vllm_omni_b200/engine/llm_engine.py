@@ -65,6 +65,9 @@ class LLMEngine:
         # to the client), n > 1 = every n generated tokens (a stage whose frames feed a chunked consumer),
         # 0 = only the finished request is reported (a stage nobody watches while it runs).
         self.stream_interval = 1
+        # Tensors among the progress reports (the model's ``stream_output_keys``) ride only on every n-th generated
+        # token of a request; in between they accumulate.  Token ids and text still ride on every report.
+        self.stream_mm_interval = 1
 
     def _activation_reserve(self, dec) -> int:
         rows = int(getattr(self, "max_num_batched_tokens", 8192) or 8192)
@@ -236,7 +239,8 @@ class LLMEngine:
                                 finish_reason=FINISH_REASON.get(req.status) if fin else None,
                                 stop_reason=req.stop_reason)
         stream_keys = getattr(self.model, "stream_output_keys", ())
-        if not fin and not self.generation and stream_keys:
+        if not fin and not self.generation and stream_keys and (
+                self.stream_mm_interval <= 1 or len(req.output_token_ids) % self.stream_mm_interval == 0):
             # streaming: only what is new since the last report (e.g. codec frames for the vocoder)
             sent = req.runtime_state.setdefault("_mm_sent", {})
             mm = {}
@@ -259,6 +263,16 @@ class LLMEngine:
         return RequestOutput(request_id=req.request_id, prompt=req.prompt, prompt_token_ids=req.prompt_token_ids,
                              outputs=[comp], finished=fin, metrics=metrics,
                              multimodal_output=comp.multimodal_output)
+
+    def update_request(self, request_id: str, payload: dict) -> bool:
+        """Late input for a running request (rows of an upstream stage that is still generating): handed to the
+        model's ``on_stream_update``.  Unknown or finished requests are ignored."""
+        req = self._reqs.get(request_id)
+        fn = getattr(self.model, "on_stream_update", None)
+        if req is None or fn is None or req.is_finished():
+            return False
+        fn(req, payload)
+        return True
 
     def generate(self, prompts, sampling_params=None) -> list[RequestOutput]:
         """Blocking convenience wrapper: run the given prompts to completion."""

@@ -59,6 +59,7 @@ class Request:
     kv_transfer_requested: bool = False
     kv_transfer_done: bool = False
     stop_reason: Any = None
+    decode_blocked: bool = False       # the model cannot build this request's next input yet (it waits for a stream update)
     runtime_state: dict[str, Any] = field(default_factory=dict)   # per-request model scratch (e.g. talker codes)
 
     @property

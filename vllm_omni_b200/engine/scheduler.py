@@ -79,7 +79,7 @@ class OmniARScheduler:
         return bool(self.waiting or self.running)
 
     def has_schedulable(self) -> bool:
-        return bool(self.running) or any(r.status == RequestStatus.WAITING for r in self.waiting)
+        return any(not r.decode_blocked for r in self.running) or any(r.status == RequestStatus.WAITING for r in self.waiting)
 
     # ------------------------------------------------------------------ scheduling
     def _poll_chunks(self):
@@ -103,6 +103,8 @@ class OmniARScheduler:
                 break
             if req.status != RequestStatus.RUNNING:
                 continue                      # preempted earlier in this very step
+            if req.decode_blocked:
+                continue                      # its next input depends on a stream update that has not arrived
             remaining = req.num_tokens - req.num_computed_tokens
             if remaining <= 0:
                 continue                      # everything consumed; waiting for the next chunk

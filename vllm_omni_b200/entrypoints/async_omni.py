@@ -43,6 +43,12 @@ class _ReqState:
         self.audio_chunks_seen = 0
         self.first_output_ts: dict[str, float] = {}
         self.codes_parts: list = []
+        self.row_parts: list = []        # async-chunk bookkeeping (thinker -> talker): rows not yet forwarded
+        self.hid_parts: list = []
+        self.tts_rows: dict = {}
+        self.talker_started = False
+        self.rows_sent = 0
+        self.hid_key = None
 
 
 class AsyncOmni(OmniBase):
@@ -53,6 +59,7 @@ class AsyncOmni(OmniBase):
         self.auto_restart = bool(kwargs.pop("auto_restart_stages", False))
         super().__init__(model, **kwargs)
         self.async_chunk = bool(self.stage_configs.async_chunk)
+        self.stream_starts = 0            # requests whose talker was started from a thinker that was still running
         self._states: dict[str, _ReqState] = {}
         self._lock = threading.Lock()
         self._paused = asyncio.Event() if False else None
@@ -245,6 +252,7 @@ class AsyncOmni(OmniBase):
                     self._post(st, w)
         if self.async_chunk and not finished:
             self._forward_chunks(stage, st, outs, finished=False)
+            self._stream_rows(stage, st, outs, finished=False)
         if not finished:
             return
         stage.set_engine_outputs(outs)
@@ -255,6 +263,8 @@ class AsyncOmni(OmniBase):
             plain = [d for d in self.consumers[sid] if d not in self._chunk_consumers(stage)]
         else:
             plain = self.consumers[sid]
+        if self.async_chunk and self._stream_rows(stage, st, outs, finished=True):
+            plain = [d for d in plain if d not in self._row_consumers(stage)]      # they were started from the stream
         if self._is_chunk_sink(stage):
             # the vocoder finishes once per chunk; the stage is done for this request only when
             # the talker has finished and every chunk it produced has come back
@@ -269,6 +279,68 @@ class AsyncOmni(OmniBase):
         if self.must_finish <= st.done_stages:
             self.metrics.on_finalize_request(rid)
             self._post(st, _DONE)
+
+    # ------------------------------------------------------------------ async chunk (thinker -> talker)
+    def _row_consumers(self, stage):
+        """Consumers that can start from a thinker that is still generating."""
+        if stage.model_stage != "thinker":
+            return []
+        return [d for d in self.consumers[stage.stage_id] if d.model_stage == "talker"]
+
+    def _stream_rows(self, stage, st: _ReqState, outs, finished: bool) -> bool:
+        """The thinker's progress reports carry its new rows every few tokens.  The talker is started as soon as
+        the prompt rows and the first reply row exist (marked ``thinker_stream``); later rows, and the news that
+        the thinker has finished, follow as UPDATE tasks.  Returns True when the talker runs from the stream
+        (the whole-request hand-off is then skipped)."""
+        dsts = self._row_consumers(stage)
+        if not dsts:
+            return False
+        ro = getattr(outs[0], "request_output", None) or outs[0]
+        comp = ro.outputs[0] if getattr(ro, "outputs", None) else None
+        mm = (comp.multimodal_output if comp is not None else None) or {}
+        if finished:
+            if not st.talker_started:
+                return False
+            full = mm.get("0")
+            new = full[st.rows_sent:] if full is not None else None
+            for dst in dsts:
+                dst.submit({"type": OmniStageTaskType.UPDATE, "request_id": st.rid,
+                            "payload": {"thinker_embeddings": new, "finished": True}})
+            return True
+        hk = next((k for k in mm if k != "0" and str(k).isdigit()), None)
+        if mm.get("0") is not None and mm["0"].shape[0]:
+            st.row_parts.append(mm["0"])
+            if hk is not None:
+                st.hid_parts.append(mm[hk])
+                st.hid_key = hk
+        for k in ("tts_bos_embed", "tts_eos_embed", "tts_pad_embed"):
+            if k in mm:
+                st.tts_rows[k] = mm[k]
+        if not st.row_parts:
+            return st.talker_started
+        rows = torch.cat(st.row_parts, 0)
+        if not st.talker_started:
+            n_prompt = len(ro.prompt_token_ids or [])
+            if rows.shape[0] < n_prompt + 1 or len(st.tts_rows) < 3 or st.hid_key is None:
+                return False
+            import copy
+            comp2 = copy.copy(comp)
+            comp2.multimodal_output = {"0": rows, st.hid_key: torch.cat(st.hid_parts, 0), **st.tts_rows}
+            comp2.token_ids = list(comp.token_ids)
+            syn = copy.copy(ro)
+            syn.outputs, syn.multimodal_output, syn.finished = [comp2], comp2.multimodal_output, False
+            stage.set_engine_outputs([syn])
+            for dst in dsts:
+                send_downstream(self, stage, dst, st.rid, st.prompt, st.sps[dst.stage_id], mark={"thinker_stream": True})
+            st.talker_started = True
+            self.stream_starts += 1
+        else:
+            for dst in dsts:
+                dst.submit({"type": OmniStageTaskType.UPDATE, "request_id": st.rid,
+                            "payload": {"thinker_embeddings": rows, "finished": False}})
+        st.rows_sent += rows.shape[0]
+        st.row_parts, st.hid_parts = [], []
+        return True
 
     # ------------------------------------------------------------------ async chunk (talker -> code2wav)
     def _chunk_consumers(self, stage):

@@ -35,6 +35,8 @@ class OmniEngineArgs:
     stage_connector_spec: dict | None = None
     async_chunk: bool = False
     stream_interval: int = 1              # generated tokens between progress reports of a running request (0 = none)
+    stream_mm_interval: int = 1           # progress reports carry the model's streamed tensors on every n-th token only
+    stream_output_keys: Any = None        # overrides the model's list of tensors that ride on progress reports
     omni_kv_config: dict = field(default_factory=dict)
     worker_type: str = "ar"
     scheduler_cls: str | None = None
@@ -137,6 +139,14 @@ class OmniLLM:
                                 kv_transfer_criteria=crit, chunk_adapter=chunk_adapter, kv_transfer_manager=kv_mgr,
                                 stage_id=stage_id, engine_output_type=a.engine_output_type)
         self.engine.stream_interval = int(a.stream_interval)
+        self.engine.stream_mm_interval = int(a.stream_mm_interval)
+        if a.stream_output_keys is not None:
+            self.model.stream_output_keys = tuple(a.stream_output_keys)
+        elif a.async_chunk and hasattr(self.model, "chunk_stream_keys"):
+            # a producer of a chunk stream (the thinker under ``async_chunk``): its rows ride on every 8th token's report
+            self.model.stream_output_keys = tuple(self.model.chunk_stream_keys)
+            if a.stream_mm_interval <= 1:
+                self.engine.stream_mm_interval = 8
         if tp_group is not None and hasattr(self.engine.runner, "tp_group"):
             self.engine.runner.tp_group = tp_group
         self._profiler = None
@@ -189,6 +199,10 @@ class OmniLLM:
 
     def has_unfinished_requests(self):
         return self.engine.has_unfinished_requests()
+
+    def update_request(self, request_id: str, payload: dict) -> bool:
+        """Late input for a running request (see ``LLMEngine.update_request``)."""
+        return self.engine.update_request(request_id, payload)
 
     def abort_request(self, request_ids):
         if isinstance(request_ids, str):

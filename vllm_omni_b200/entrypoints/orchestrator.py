@@ -33,11 +33,16 @@ def wrap_stage_output(stage, out) -> OmniRequestOutput:
     raise TypeError(f"unexpected stage output {type(out)!r}")
 
 
-def send_downstream(omni, src_stage, dst_stage, request_id: str, prompt, sampling_params) -> None:
+def send_downstream(omni, src_stage, dst_stage, request_id: str, prompt, sampling_params, mark: dict | None = None) -> None:
     """Build the next stage's inputs from ``src_stage.engine_outputs`` and submit them,
-    moving the payload through the edge connector (connectors/adapter.py)."""
+    moving the payload through the edge connector (connectors/adapter.py).  ``mark`` is merged into the
+    ``additional_information`` of every input (e.g. "the producer is still running")."""
     from ..connectors.adapter import try_send_via_connector
     inputs = dst_stage.process_engine_inputs(omni.stage_list, prompt)
+    if mark:
+        for it in (inputs if isinstance(inputs, list) else [inputs]):
+            if isinstance(it, dict):
+                it.setdefault("additional_information", {}).update(mark)
     connector = omni.connectors.get((src_stage.stage_id, dst_stage.stage_id))
     task = {"type": OmniStageTaskType.GENERATE, "request_id": request_id, "sampling_params": sampling_params,
             "from_stage": src_stage.stage_id}

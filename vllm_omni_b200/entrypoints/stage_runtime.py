@@ -35,6 +35,7 @@ class StageEngineAdapter:
     def has_work(self) -> bool: ...
     def step(self) -> list[dict]: ...
     def abort(self, request_ids: list[str]) -> None: ...
+    def update(self, task: dict) -> None: ...          # late input for a running request; ignored by default
     def shutdown(self) -> None: ...
     def start_profile(self, trace_dir=None): ...
     def stop_profile(self): ...
@@ -138,6 +139,9 @@ class LLMStageAdapter(StageEngineAdapter):
 
     def has_work(self):
         return self.llm.has_unfinished_requests()
+
+    def update(self, task):
+        self.llm.update_request(task["request_id"], task.get("payload") or {})
 
     def abort(self, request_ids):
         ids = set(request_ids)
@@ -275,6 +279,15 @@ def _stage_worker(cfg: StageConfig, model: str, in_q, out_q, batch_timeout_s: fl
                     except Exception as e:
                         out_q.put({"request_id": task.get("request_id"), "stage_id": sid,
                                    "error": f"{type(e).__name__}: {e}", "error_tb": traceback.format_exc()})
+            elif tt == OmniStageTaskType.UPDATE:
+                if paused and any(t["request_id"] == task.get("request_id") for t in held):
+                    held.append(task)           # keep it behind the request it belongs to
+                else:
+                    try:
+                        adapter.update(task)
+                    except Exception as e:
+                        out_q.put({"request_id": task.get("request_id"), "stage_id": sid,
+                                   "error": f"{type(e).__name__}: {e}", "error_tb": traceback.format_exc()})
             elif tt == OmniStageTaskType.ABORT:
                 adapter.abort(list(task.get("request_ids") or [task.get("request_id")]))
                 held = [t for t in held if t["request_id"] not in set(task.get("request_ids") or [task.get("request_id")])]
@@ -293,7 +306,10 @@ def _stage_worker(cfg: StageConfig, model: str, in_q, out_q, batch_timeout_s: fl
             elif tt == OmniStageTaskType.RESUME:
                 paused = False
                 for t in held:
-                    adapter.add_task(t)
+                    if t.get("type") == OmniStageTaskType.UPDATE:
+                        adapter.update(t)
+                    else:
+                        adapter.add_task(t)
                 held = []
             drained += 1
             try:

@@ -16,6 +16,7 @@ class OmniStageTaskType(enum.Enum):
     PROFILER_STOP = "profiler_stop"
     PAUSE = "pause"
     RESUME = "resume"
+    UPDATE = "update"          # late input for a running request (rows of an upstream stage that is still generating)
 
 
 SHUTDOWN_TASK = {"type": OmniStageTaskType.SHUTDOWN}

@@ -306,7 +306,12 @@ class Qwen3OmniMoeTalker(StageModel):
             codec side   0  0  0 nothink think_bos think_eos speaker codec_pad codec_bos
 
         added row by row.  The remaining reply tokens followed by tts-eos are fed one per decode
-        step on top of the previous frame's code embeddings, tts-pad afterwards."""
+        step on top of the previous frame's code embeddings, tts-pad afterwards.
+
+        With ``thinker_stream`` in the request the thinker is still generating: the reply rows known so
+        far are used, later ones arrive through ``on_stream_update``, and a decode step whose reply row
+        has not arrived yet waits for it (``decode_blocked``) instead of guessing, so the frames equal
+        those of the whole-request hand-off."""
         info = req.additional_information
         cfg = self.cfg
         dev = self.decoder.embed_tokens.device
@@ -337,12 +342,16 @@ class Qwen3OmniMoeTalker(StageModel):
                 text = torch.where(m[:, None], self.hidden_projection(hid[a:b].contiguous()), text)
             return text
 
+        streaming = bool(info.get("thinker_stream"))
+
         def assistant_part(a, header):
             """a: first row of the turn; header: number of ChatML header rows (3, or 0 without ChatML)."""
             h = self.text_projection(emb[a:L].contiguous()) if L > a else emb.new_zeros(0, pad.shape[1])
             first = h[header:header + 1] if h.shape[0] > header else torch.zeros_like(pad)
             text = torch.cat([h[:header], pad.expand(4, -1), bos, first], dim=0)
             text[header:] += codec_rows
+            if streaming:                     # the reply is still growing: no end marker yet
+                return text, h[header + 1:].contiguous()
             trailing = torch.cat([h[header + 1:], eos], dim=0) if h.shape[0] > header + 1 else torch.zeros_like(eos)
             return text, trailing
 
@@ -371,7 +380,35 @@ class Qwen3OmniMoeTalker(StageModel):
         head = torch.cat(parts, dim=0).contiguous()
         req.prompt_embeds = head
         req.prompt_token_ids = [0] * head.shape[0]
-        req.runtime_state.update(text_steps=trailing, tts_pad=pad, frames=[], next_embed=None)
+        req.runtime_state.update(text_steps=trailing, tts_pad=pad, frames=[], next_embed=None, stream_open=streaming,
+                                 tts_eos=eos, pending=None)
+
+    @torch.no_grad()
+    def on_stream_update(self, req, payload: dict) -> None:
+        """More reply rows of a thinker that is still running (``thinker_embeddings`` [n, D_thinker], may be
+        empty) and / or the news that it has finished.  A request that was waiting for its next row goes on."""
+        st = req.runtime_state
+        if not st.get("stream_open"):
+            return
+        dev = self.decoder.embed_tokens.device
+        rows = payload.get("thinker_embeddings")
+        ts = st["text_steps"]
+        if rows is not None and rows.shape[0]:
+            ts = torch.cat([ts, self.text_projection(rows.to(dev, self.dtype_).contiguous())], dim=0)
+        if payload.get("finished"):
+            ts = torch.cat([ts, st["tts_eos"]], dim=0) if ts.shape[0] else torch.zeros_like(st["tts_eos"])
+            st["stream_open"] = False
+        st["text_steps"] = ts
+        if req.decode_blocked and st.get("pending") is not None:
+            k, base = st["pending"]
+            if k < ts.shape[0]:
+                st["next_embed"] = base + ts[k:k + 1]
+            elif not st["stream_open"]:
+                st["next_embed"] = base + st["tts_pad"]
+            else:
+                return
+            st["pending"] = None
+            req.decode_blocked = False
 
     def input_embeds_for(self, req, start, n):
         if start < req.num_prompt_tokens:
@@ -398,9 +435,14 @@ class Qwen3OmniMoeTalker(StageModel):
             st = r.runtime_state
             k = len(r.output_token_ids)                                      # index of this frame
             ts = st.get("text_steps")
-            text = ts[k:k + 1] if ts is not None and k < ts.shape[0] else st.get("tts_pad")
             nxt = e0[i:i + 1] + summed[i:i + 1]
-            st["next_embed"] = nxt + text if text is not None else nxt
+            if ts is not None and k >= ts.shape[0] and st.get("stream_open"):
+                # the thinker has not produced this step's reply row yet: wait for it
+                st["pending"], st["next_embed"] = (k, nxt), None
+                r.decode_blocked = True
+            else:
+                text = ts[k:k + 1] if ts is not None and k < ts.shape[0] else st.get("tts_pad")
+                st["next_embed"] = nxt + text if text is not None else nxt
             r.multimodal_outputs.setdefault("codes", []).append(frames[i:i + 1])
         return ids
 

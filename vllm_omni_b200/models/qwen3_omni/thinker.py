@@ -31,6 +31,12 @@ class Qwen3OmniMoeThinker(StageModel):
     def eos_token_id(self):
         return self.cfg.im_end_token_id
 
+    @property
+    def chunk_stream_keys(self) -> tuple:
+        """What a talker that starts before this stage has finished needs from the progress reports: token
+        embeddings, the captured hidden layer, and the three TTS marker embeddings (sent once)."""
+        return ("0", str(self.cfg.accept_hidden_layer), "tts_bos_embed", "tts_eos_embed", "tts_pad_embed")
+
     # ---- request preprocessing: multimodal features -> prompt embedding overlay + MRoPE ids
     @torch.no_grad()
     def preprocess_request(self, req) -> None:
