@@ -4,9 +4,11 @@
 One background thread polls every stage's result queue and routes results: outputs of final
 stages go to the request's asyncio queue (text deltas stream while the stage is still
 running), finished outputs of a stage become the inputs of its consumers (sequential mode,
-async_omni.py:408-473).  With ``async_chunk`` enabled, codec frames of a running talker are
-forwarded to the vocoder stage in chunks of 25 frames (+25 frames of left context) so audio
-starts before the talker has finished (async_omni.py:363-406, chunk_transfer_adapter.py).
+async_omni.py:408-473).  With ``async_chunk`` enabled both edges of the omni pipeline stream: the
+talker starts from a thinker that is still generating (its rows follow as update tasks), and codec
+frames of a running talker are forwarded to the vocoder stage in chunks of 25 frames (+25 frames of
+left context), so audio starts shortly after the first text tokens
+(async_omni.py:363-406, chunk_transfer_adapter.py, stage_input_processors/qwen3_omni.py:86-141).
 ``abort`` reaches every stage; ``pause_generation`` / ``resume_generation`` gate new work.
 """
 from __future__ import annotations
