@@ -106,3 +106,13 @@ def test_processed_items_feed_the_tiny_thinker():
     assert req.prompt_token_ids.count(cfg.image_token_id) == n_img
     assert req.prompt_token_ids.count(cfg.audio_token_id) >= 1
     assert len(req.prompt_token_ids) == 3 + n_img + req.prompt_token_ids.count(cfg.audio_token_id)
+
+
+def test_processor_settings_come_from_the_checkpoint_config(tmp_path):
+    import json
+    (tmp_path / "config.json").write_text(json.dumps({"thinker_config": {
+        "vision_config": {"patch_size": 14, "spatial_merge_size": 2}, "audio_config": {"num_mel_bins": 80}}}))
+    assert op.processor_kwargs_for(str(tmp_path)) == {"vision_factor": 28, "n_mels": 80}
+    assert op.processor_kwargs_for(None) == {"vision_factor": 32, "n_mels": 128}
+    tiny_stage = type("S", (), {"engine_args": {"model_stage": "thinker", "model_overrides": {"tiny": True}}})()
+    assert op.processor_kwargs_for(None, [tiny_stage]) == {"vision_factor": 8, "n_mels": 16}

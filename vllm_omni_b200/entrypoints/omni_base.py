@@ -49,6 +49,14 @@ class OmniBase:
     def num_stages(self) -> int:
         return len(self.stage_list)
 
+    @property
+    def mm_processor_kwargs(self) -> dict:
+        """How chat-request images / audio are turned into thinker inputs for this model (server side)."""
+        if getattr(self, "_mm_kwargs", None) is None:
+            from ..inputs.omni_processor import processor_kwargs_for
+            self._mm_kwargs = processor_kwargs_for(self.model, getattr(self.stage_configs, "stages", None))
+        return self._mm_kwargs
+
     def start_profile(self, stages: Sequence[int] | None = None, trace_dir: str | None = None):
         for s in self.stage_list:
             if stages is None or s.stage_id in stages:

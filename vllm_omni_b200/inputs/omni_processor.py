@@ -148,3 +148,29 @@ def thinker_inputs(mm: dict, vision_factor: int = 32, n_mels: int = 128) -> dict
     if mm.get("audio"):
         out["audio"] = [audio_to_mel(w, r, n_mels) for w, r in mm["audio"]]
     return out
+
+
+def processor_kwargs_for(model: str | None, stage_cfgs=None) -> dict:
+    """``thinker_inputs`` keyword arguments for a served model: the vision rounding factor (patch x merge) and the
+    number of mel bins, read from the checkpoint's ``config.json`` (``thinker_config.vision_config`` /
+    ``audio_config``); tiny test geometries when a stage asks for them; the Qwen3-Omni values otherwise."""
+    import json
+    import os
+    for sc in stage_cfgs or []:
+        ov = (getattr(sc, "engine_args", None) or {}).get("model_overrides") or {}
+        if ov.get("tiny") and (getattr(sc, "engine_args", {}) or {}).get("model_stage") == "thinker":
+            from ..models.qwen3_omni.config import Qwen3OmniConfig
+            c = Qwen3OmniConfig.tiny()
+            return {"vision_factor": c.vision.patch_size * c.vision.spatial_merge_size, "n_mels": c.audio.num_mel_bins}
+    out = {"vision_factor": 32, "n_mels": 128}
+    path = os.path.join(model, "config.json") if model and os.path.isdir(model) else None
+    if path and os.path.isfile(path):
+        with open(path) as f:
+            cfg = json.load(f)
+        th = cfg.get("thinker_config") or cfg
+        v, a = th.get("vision_config") or {}, th.get("audio_config") or {}
+        if v.get("patch_size"):
+            out["vision_factor"] = int(v["patch_size"]) * int(v.get("spatial_merge_size", 2))
+        if a.get("num_mel_bins"):
+            out["n_mels"] = int(a["num_mel_bins"])
+    return out
