@@ -168,3 +168,33 @@ def test_chat_with_audio_and_image_parts_reaches_the_engine_as_features():
         bad = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
             {"type": "input_audio", "input_audio": {"data": base64.b64encode(b"ID3 not a wav").decode(), "format": "mp3"}}]}]})
         assert bad.status_code == 400 and "WAV" in bad.text
+
+
+def test_real_tiny_omni_chat_with_an_audio_clip(tmp_path):
+    """An audio part goes all the way: decoded, turned into log-mel features, its placeholder expanded by the
+    thinker to the clip's feature length (the prompt grows by more than the text alone), reply text comes back."""
+    import io
+    import wave
+
+    import numpy as np
+    from test_async_omni import _engine
+    buf = io.BytesIO()
+    with wave.open(buf, "wb") as f:
+        f.setnchannels(1)
+        f.setsampwidth(2)
+        f.setframerate(16000)
+        f.writeframes((np.sin(np.arange(6400) / 7) * 9000).astype("<i2").tobytes())
+    eng = _engine(tmp_path)
+    try:
+        assert eng.mm_processor_kwargs == {"vision_factor": 8, "n_mels": 16}
+        with TestClient(build_app(eng, "tiny-omni", kind="omni")) as c:
+            plain = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3})
+            withclip = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+                {"type": "audio_url", "audio_url": {"url": "data:audio/wav;base64," + base64.b64encode(buf.getvalue()).decode()}},
+                {"type": "text", "text": "hi"}]}], "max_tokens": 3})
+            assert plain.status_code == 200 and withclip.status_code == 200, withclip.text
+            extra = withclip.json()["usage"]["prompt_tokens"] - plain.json()["usage"]["prompt_tokens"]
+            # 0.4 s of audio = 40 mel frames -> several encoder positions, plus the start / end marker strings
+            assert extra > 28 + 1, extra      # 28 bytes of start / end marker text + the expanded placeholder
+    finally:
+        eng.close()

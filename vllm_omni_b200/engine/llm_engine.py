@@ -21,7 +21,7 @@ from .kv_cache_manager import KVCacheManager
 from .model_runner import ARModelRunner, GenerationModelRunner
 from .request import FINISH_REASON, Request, RequestStatus
 from .scheduler import OmniARScheduler, OmniGenerationScheduler
-from .tokenizer import IncrementalDetokenizer, get_tokenizer
+from .tokenizer import ByteTokenizer, IncrementalDetokenizer, get_tokenizer
 
 logger = init_logger(__name__)
 
@@ -112,7 +112,13 @@ class LLMEngine:
             raise TypeError(f"unsupported prompt type {type(prompt)!r}")
         if ids is None:
             if text is not None:
-                ids = self.tokenizer.encode(text)
+                special = getattr(self.model, "special_token_map", None)
+                if special and isinstance(self.tokenizer, ByteTokenizer):
+                    # no checkpoint tokenizer (random-weight runs): the model's chat markers and multimodal
+                    # placeholders still have to arrive as their single ids
+                    ids = self.tokenizer.encode(text, special=special() if callable(special) else special)
+                else:
+                    ids = self.tokenizer.encode(text)
             elif embeds is not None:
                 ids = [0] * embeds.shape[0]
             else:

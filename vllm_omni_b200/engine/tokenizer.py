@@ -10,8 +10,19 @@ class ByteTokenizer:
     bos_token_id, eos_token_id, pad_token_id = 256, 257, 258
     vocab_size = 259
 
-    def encode(self, text: str, add_special_tokens: bool = False) -> list[int]:
-        ids = list(text.encode("utf-8"))
+    def encode(self, text: str, add_special_tokens: bool = False, special: dict | None = None) -> list[int]:
+        """``special``: marker string -> token id (a model's chat and placeholder tokens); markers found in the text
+        become their one id, everything between them is encoded byte by byte."""
+        if special:
+            import re
+            ids = []
+            for part in re.split("(" + "|".join(re.escape(k) for k in sorted(special, key=len, reverse=True)) + ")", text):
+                if part in special:
+                    ids.append(int(special[part]))
+                elif part:
+                    ids.extend(part.encode("utf-8"))
+        else:
+            ids = list(text.encode("utf-8"))
         return ([self.bos_token_id] + ids) if add_special_tokens else ids
 
     def decode(self, ids, skip_special_tokens: bool = True) -> str:

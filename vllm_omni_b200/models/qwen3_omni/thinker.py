@@ -31,6 +31,12 @@ class Qwen3OmniMoeThinker(StageModel):
     def eos_token_id(self):
         return self.cfg.im_end_token_id
 
+    def special_token_map(self) -> dict:
+        """Marker strings of the chat template and the multimodal placeholders -> token ids of this checkpoint."""
+        c = self.cfg
+        return {"<|im_start|>": c.im_start_token_id, "<|im_end|>": c.im_end_token_id, "<|audio_pad|>": c.audio_token_id,
+                "<|image_pad|>": c.image_token_id, "<|video_pad|>": c.video_token_id}
+
     @property
     def chunk_stream_keys(self) -> tuple:
         """What a talker that starts before this stage has finished needs from the progress reports: token
