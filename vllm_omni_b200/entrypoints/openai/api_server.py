@@ -49,7 +49,7 @@ def _parse_lora_request(lora: dict | None) -> tuple[LoRARequest | None, float]:
     return LoRARequest(name, lid or 1, path, float(lora.get("scale", 1.0))), float(lora.get("scale", 1.0))
 
 
-def _flatten_content(content, placeholders: bool = False) -> tuple[str, dict]:
+def _flatten_content(content, placeholders: bool = False, style: str | None = None) -> tuple[str, dict]:
     """OpenAI message content -> (text, raw multimodal items).  Items: ``image`` PIL images, ``audio`` (waveform,
     rate) pairs, ``video`` frame lists.  With ``placeholders`` the text carries one placeholder group per item at
     the item's position in the message (the omni thinker expands it to the item's feature length)."""
@@ -59,6 +59,7 @@ def _flatten_content(content, placeholders: bool = False) -> tuple[str, dict]:
         return content, {}
     from ...inputs import omni_processor as op
     text, mm = [], {}
+    marks = op.placeholders_for(style)
 
     def _url(part, key):
         v = part.get(key)
@@ -73,7 +74,7 @@ def _flatten_content(content, placeholders: bool = False) -> tuple[str, dict]:
             if isinstance(url, str) and (url.startswith("data:") or len(url) > 256):
                 mm.setdefault("image", []).append(mu.decode_image_base64(url))
                 if placeholders:
-                    text.append(op.PLACEHOLDER["image"])
+                    text.append(marks["image"])
         elif t in ("input_audio", "audio_url"):
             src = part.get("input_audio") if t == "input_audio" else _url(part, "audio_url")
             data = src.get("data") if isinstance(src, dict) else src
@@ -81,19 +82,19 @@ def _flatten_content(content, placeholders: bool = False) -> tuple[str, dict]:
                 raise ValueError("audio input must be inline (base64 or a data: URL); remote URLs are not fetched")
             mm.setdefault("audio", []).append(op.decode_audio_bytes(op.decode_data_url(data)))
             if placeholders:
-                text.append(op.PLACEHOLDER["audio"])
+                text.append(marks["audio"])
         elif t == "video_url":
             url = _url(part, "video_url")
             if not isinstance(url, str) or url.startswith(("http://", "https://")):
                 raise ValueError("video input must be inline (a data: URL of an animated GIF); remote URLs are not fetched")
             mm.setdefault("video", []).append(op.gif_frames(op.decode_data_url(url)))
             if placeholders:
-                text.append(op.PLACEHOLDER["video"])
+                text.append(marks["video"])
         elif t == "video_frames":
             fr = (part.get("video_frames") or {}).get("frames") or []
             mm.setdefault("video", []).append([mu.decode_image_base64(f) for f in fr])
             if placeholders:
-                text.append(op.PLACEHOLDER["video"])
+                text.append(marks["video"])
     return "".join(text), mm
 
 
@@ -368,7 +369,8 @@ def build_app(engine, model_name: str = "omni", kind: str = "omni", default_stag
         mm_all: dict = {}
         try:
             for m in req.messages:
-                t, mm = _flatten_content(m.content, placeholders=True)
+                t, mm = _flatten_content(m.content, placeholders=True,
+                                         style=(getattr(engine, "mm_processor_kwargs", None) or {}).get("style"))
                 msgs.append({"role": m.role, "content": t})
                 for k, v in mm.items():
                     mm_all.setdefault(k, []).extend(v)

@@ -30,7 +30,16 @@ PLACEHOLDER = {
     "video": "<|vision_start|><|video_pad|><|vision_end|>",
     "audio": "<|audio_start|><|audio_pad|><|audio_end|>",
 }
+PLACEHOLDER_QWEN25 = {      # the Qwen2.5-Omni chat template's spelling
+    "image": "<|vision_bos|><|IMAGE|><|vision_eos|>",
+    "video": "<|vision_bos|><|VIDEO|><|vision_eos|>",
+    "audio": "<|audio_bos|><|AUDIO|><|audio_eos|>",
+}
 AUDIO_RATE = 16000
+
+
+def placeholders_for(style: str | None) -> dict:
+    return PLACEHOLDER_QWEN25 if style == "qwen2_5_omni" else PLACEHOLDER
 
 
 def smart_resize(height: int, width: int, factor: int = 32, min_pixels: int = 56 * 56, max_pixels: int = 1280 * 28 * 28) -> tuple[int, int]:
@@ -137,7 +146,7 @@ def gif_frames(blob: bytes) -> list:
     return [f.convert("RGB") for f in ImageSequence.Iterator(im)]
 
 
-def thinker_inputs(mm: dict, vision_factor: int = 32, n_mels: int = 128) -> dict:
+def thinker_inputs(mm: dict, vision_factor: int = 32, n_mels: int = 128, style: str | None = None) -> dict:
     """Raw items collected from a chat request ({"image": [PIL...], "audio": [(wave, rate)...], "video":
     [[frames]...]}) -> what ``Qwen3OmniMoeThinker.preprocess_request`` takes under the same keys."""
     out = {}
@@ -167,6 +176,8 @@ def processor_kwargs_for(model: str | None, stage_cfgs=None) -> dict:
     if path and os.path.isfile(path):
         with open(path) as f:
             cfg = json.load(f)
+        if "qwen2_5_omni" in str(cfg.get("model_type", "")):
+            out["style"] = "qwen2_5_omni"
         th = cfg.get("thinker_config") or cfg
         v, a = th.get("vision_config") or {}, th.get("audio_config") or {}
         if v.get("patch_size"):

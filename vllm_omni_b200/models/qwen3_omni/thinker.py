@@ -34,8 +34,12 @@ class Qwen3OmniMoeThinker(StageModel):
     def special_token_map(self) -> dict:
         """Marker strings of the chat template and the multimodal placeholders -> token ids of this checkpoint."""
         c = self.cfg
-        return {"<|im_start|>": c.im_start_token_id, "<|im_end|>": c.im_end_token_id, "<|audio_pad|>": c.audio_token_id,
-                "<|image_pad|>": c.image_token_id, "<|video_pad|>": c.video_token_id}
+        m = {"<|im_start|>": getattr(c, "im_start_token_id", None), "<|im_end|>": getattr(c, "im_end_token_id", None)}
+        for pads, key in ((("<|audio_pad|>", "<|AUDIO|>"), "audio_token_id"), (("<|image_pad|>", "<|IMAGE|>"), "image_token_id"),
+                          (("<|video_pad|>", "<|VIDEO|>"), "video_token_id")):     # Qwen3-Omni and Qwen2.5-Omni spellings
+            for p in pads:
+                m[p] = getattr(c, key, None)
+        return {k: v for k, v in m.items() if v is not None}
 
     @property
     def chunk_stream_keys(self) -> tuple:
