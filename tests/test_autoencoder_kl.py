@@ -70,3 +70,27 @@ def test_load_weights_accepts_old_attention_names_and_build_vae_picks_class():
     assert type(build_vae({"_class_name": "AutoencoderKL", "latent_channels": 4, "block_out_channels": [8, 8],
                            "norm_num_groups": 4}, "qwen")).__name__ == "AutoencoderKL"
     assert type(build_vae(None, "qwen")).__name__ == "AutoencoderKLQwenImage2d"
+
+
+def test_channels_last_video_decoder_equals_the_module_for_every_chunking():
+    """The causal 3-D decoder restated on the channels-last ops (temporal taps as accumulated 2-D convolutions,
+    frame caches per convolution) against the PyTorch module, on the ops' CPU paths in fp32."""
+    import torch
+    from vllm_omni_b200.diffusion.models.vae.autoencoder_kl_qwenimage import QwenImageVAEConfig
+    from vllm_omni_b200.diffusion.models.vae.autoencoder_kl_wan import AutoencoderKLWan
+    from vllm_omni_b200.diffusion.models.vae.nhwc_video_decoder import NHWCVideoDecoder
+    torch.manual_seed(0)
+    cfg = QwenImageVAEConfig(base_dim=8, num_res_blocks=1)
+    vae = AutoencoderKLWan(cfg).float()
+    for p in vae.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, (1.0 / p[0].numel()) ** 0.5)
+        else:
+            p.data.uniform_(0.5, 1.5)
+    z = torch.randn(2, cfg.z_dim, 3, 6, 8)
+    ref = vae.decode(z, chunk_frames=1)
+    dec = NHWCVideoDecoder(vae.decoder, vae.post_quant_conv, torch.float32)
+    for chunk in (1, 0, 2):
+        out = dec(vae.denormalize(z.float()), chunk_frames=chunk)
+        assert out.shape == ref.shape == (2, 3, 9, 48, 64)
+        assert (out - ref).abs().max().item() < 1e-4, chunk

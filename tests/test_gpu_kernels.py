@@ -295,6 +295,26 @@ def test_vae_decoder_nhwc_matches_torch(dev):
     assert (out - ref).abs().mean().item() < 0.02 and (out - ref).abs().max().item() < 0.25
 
 
+def test_video_vae_decoder_nhwc_matches_torch(dev):
+    """Causal 3-D decoder on the channels-last kernels (temporal taps accumulated through the residual operand,
+    per-convolution frame caches across chunks) against the cuDNN module, full-width channels."""
+    from vllm_omni_b200.diffusion.models.vae.autoencoder_kl_wan import AutoencoderKLWan
+    torch.manual_seed(11)
+    vae = AutoencoderKLWan().to(dev).bfloat16()
+    for p in vae.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, (1.0 / p[0].numel()) ** 0.5)
+    z = torch.randn(1, 16, 3, 12, 16, device=dev)
+    vae.decoder_impl = "torch"
+    ref = vae.decode(z).float()
+    vae.decoder_impl = "nhwc"
+    for chunk in (1, 0):
+        out = vae.decode(z, chunk_frames=chunk).float()
+        _status_ok(dev)
+        assert out.shape == ref.shape == (1, 3, 9, 96, 128)
+        assert (out - ref).abs().mean().item() < 0.02 and (out - ref).abs().max().item() < 0.3, chunk
+
+
 def test_wide_head_attention_gemm_softmax_gemm(dev):
     """The VAE's one-head attention: two GEMM launches around the row-softmax kernel, queries in chunks."""
     import torch.nn.functional as F

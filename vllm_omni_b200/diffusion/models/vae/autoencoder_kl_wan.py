@@ -8,8 +8,15 @@ Latent frames are decoded in a streaming fashion: each causal convolution keeps 
 input frames of the previous chunk (``feat cache``), so memory is bounded by one chunk and the
 result equals the full-clip decode.  Spatially the clip can be split into overlapping tiles
 across ranks (parallel/vae_patch_parallel.py).
+
+On a GPU with the module in bf16 the decoder runs channels-last on this library's kernels
+(``nhwc_video_decoder.NHWCVideoDecoder``: every causal 3-D convolution as kT launches of the 2-D
+implicit-GEMM kernel accumulating through its residual operand); ``OMNI_VAE_IMPL=torch`` or an fp32
+module keeps the cuDNN path below.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.nn.functional as F
@@ -141,6 +148,8 @@ class AutoencoderKLWan(nn.Module):
         self.cfg = cfg = cfg or QwenImageVAEConfig()
         self.post_quant_conv = CausalConv3d(cfg.z_dim, cfg.z_dim, 1)
         self.decoder = WanDecoder3d(cfg)
+        self.decoder_impl = os.environ.get("OMNI_VAE_IMPL", "nhwc")      # "nhwc" (own kernels) | "torch" (cuDNN)
+        self._nhwc = None
 
     @property
     def dtype(self):
@@ -154,6 +163,11 @@ class AutoencoderKLWan(nn.Module):
     @torch.no_grad()
     def decode(self, z: torch.Tensor, chunk_frames: int = 1) -> torch.Tensor:
         """Streaming decode, ``chunk_frames`` latent frames at a time (0 = whole clip at once)."""
+        if z.is_cuda and self.dtype == torch.bfloat16 and self.decoder_impl != "torch":
+            if self._nhwc is None:
+                from .nhwc_video_decoder import NHWCVideoDecoder
+                self._nhwc = NHWCVideoDecoder(self.decoder, self.post_quant_conv, torch.bfloat16)
+            return self._nhwc(self.denormalize(z.float()), chunk_frames)
         z = self.denormalize(z.float()).to(self.dtype)
         z = self.post_quant_conv(z)
         if chunk_frames <= 0 or z.shape[2] <= chunk_frames:
