@@ -94,3 +94,26 @@ def test_channels_last_video_decoder_equals_the_module_for_every_chunking():
         out = dec(vae.denormalize(z.float()), chunk_frames=chunk)
         assert out.shape == ref.shape == (2, 3, 9, 48, 64)
         assert (out - ref).abs().max().item() < 1e-4, chunk
+
+
+def test_channels_last_kl_decoder_equals_the_module():
+    """The GroupNorm decoder restated on the channels-last ops (CPU paths, fp32), incl. the post-quant convolution
+    and the attention projections as 1x1 convolutions."""
+    import torch
+    from vllm_omni_b200.diffusion.models.vae.autoencoder_kl import AutoencoderKL, AutoencoderKLConfig
+    from vllm_omni_b200.diffusion.models.vae.nhwc_decoder_kl import NHWCDecoderKL
+    torch.manual_seed(0)
+    cfg = AutoencoderKLConfig(block_out_channels=(32, 64, 64, 64), layers_per_block=1, norm_num_groups=8, use_post_quant_conv=True)
+    vae = AutoencoderKL(cfg).float()
+    for p in vae.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, (1.0 / p[0].numel()) ** 0.5)
+        else:
+            p.data.uniform_(0.5, 1.5)
+    z = torch.randn(2, 16, 6, 10)
+    ref = vae.decode(z)
+    assert NHWCDecoderKL.supported(vae.decoder)
+    out = NHWCDecoderKL(vae.decoder, vae.post_quant_conv, torch.float32)(vae.denormalize(z))
+    assert out.shape == ref.shape and (out - ref).abs().max().item() < 1e-4
+    odd = AutoencoderKL(AutoencoderKLConfig(block_out_channels=(24, 48, 48, 48), layers_per_block=1, norm_num_groups=4))
+    assert not NHWCDecoderKL.supported(odd.decoder)          # 24 channels: the native GroupNorm does not take them

@@ -295,6 +295,42 @@ def test_vae_decoder_nhwc_matches_torch(dev):
     assert (out - ref).abs().mean().item() < 0.02 and (out - ref).abs().max().item() < 0.25
 
 
+@pytest.mark.parametrize("N,H,W,ch,G", [(2, 17, 23, 128, 32), (1, 64, 64, 512, 32), (3, 5, 7, 32, 8), (1, 40, 40, 256, 32)])
+def test_groupnorm_nhwc(dev, N, H, W, ch, G):
+    """Channels-last GroupNorm (+ SiLU) against torch's GroupNorm in fp32; bit-identical between two runs."""
+    import torch.nn.functional as F
+    from vllm_omni_b200.ops import conv as C
+    torch.manual_seed(13)
+    x = (torch.randn(N, H, W, ch, device=dev) * 2 + 0.7).to(torch.bfloat16)
+    gamma, beta = torch.rand(ch, device=dev) + 0.5, torch.randn(ch, device=dev) * 0.2
+    for silu in (True, False):
+        y = C.groupnorm_nhwc(x, gamma, beta, G, 1e-6, silu=silu)
+        _status_ok(dev)
+        ref = F.group_norm(x.float().permute(0, 3, 1, 2), G, gamma, beta, 1e-6)
+        ref = (F.silu(ref) if silu else ref).permute(0, 2, 3, 1)
+        assert (y.float() - ref).abs().max().item() < 0.04, (silu, (y.float() - ref).abs().max().item())
+        assert torch.equal(y, C.groupnorm_nhwc(x, gamma, beta, G, 1e-6, silu=silu))
+
+
+def test_kl_vae_decoder_nhwc_matches_torch(dev):
+    """The FLUX-family AutoencoderKL decoder on the channels-last kernels against the cuDNN module, full width."""
+    from vllm_omni_b200.diffusion.models.vae.autoencoder_kl import AutoencoderKL
+    torch.manual_seed(12)
+    vae = AutoencoderKL().to(dev).bfloat16()
+    for p in vae.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, (1.0 / p[0].numel()) ** 0.5)
+    z = torch.randn(1, 16, 24, 20, device=dev)
+    vae.decoder_impl = "torch"
+    ref = vae.decode(z).float()
+    vae.decoder_impl = "nhwc"
+    out = vae.decode(z).float()
+    _status_ok(dev)
+    assert vae._nhwc, "the channels-last decoder was not used"
+    assert out.shape == ref.shape == (1, 3, 192, 160)
+    assert (out - ref).abs().mean().item() < 0.02 and (out - ref).abs().max().item() < 0.3
+
+
 def test_video_vae_decoder_nhwc_matches_torch(dev):
     """Causal 3-D decoder on the channels-last kernels (temporal taps accumulated through the residual operand,
     per-convolution frame caches across chunks) against the cuDNN module, full-width channels."""

@@ -88,6 +88,14 @@ def main(argv=None):
         z = torch.randn(1, 16, 128, 128, device=dev)
         fn = lambda: vae.decode(z)
         bytes_ = 0.0
+    elif a.case in ("kl_vae", "kl_vae_torch"):
+        # 1024 x 1024 image through the FLUX-family AutoencoderKL decoder (GroupNorm ResNet blocks)
+        from vllm_omni_b200.diffusion.models.vae.autoencoder_kl import AutoencoderKL
+        vae = AutoencoderKL().to(dev).bfloat16()
+        vae.decoder_impl = "torch" if a.case == "kl_vae_torch" else "nhwc"
+        z = torch.randn(1, 16, 128, 128, device=dev)
+        fn = lambda: vae.decode(z)
+        bytes_ = 0.0
     elif a.case in ("wan_vae", "wan_vae_torch"):
         # 17 frames of 480 x 832: latent 16 x 5 x 60 x 104 through the causal 3-D decoder, one latent frame per chunk
         from vllm_omni_b200.diffusion.models.vae.autoencoder_kl_wan import AutoencoderKLWan

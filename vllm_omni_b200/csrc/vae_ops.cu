@@ -408,3 +408,126 @@ extern "C" int omni_softmax_rows(void* x, long ld, long rows, int N, float scale
                                                                              scale * 1.4426950408889634f);
   return (int)cudaGetLastError();
 }
+
+namespace omni {
+
+// GroupNorm (+ SiLU) on channels-last activations, x: [N, P, C] bf16 (row pitch ld), G groups of C / G channels.
+// Two kernels.  gn_stats: grid (GN_SPLITS, N); a CTA takes every GN_SPLITS-th run of pixels, each thread keeps the sums of
+// ONE 8-channel vector position, the per-thread sums are combined per group in a fixed order, and the CTA writes
+// (sum, sum of squares) per group to partial[n][g][split].  gn_apply: sums the GN_SPLITS partials of each group in
+// order (so the result does not depend on scheduling), then normalises, scales, shifts and applies SiLU.
+// Requirements: C % 8 == 0 and (C / 8) divides 256, so that a thread's vector position is the same for all its pixels.
+constexpr int GN_SPLITS = 128;
+constexpr int GN_MAX_GROUPS = 64;
+
+__global__ void __launch_bounds__(256)
+gn_stats_kernel(const __nv_bfloat16* __restrict__ x, long ld, long P, int C, int G, float* __restrict__ partial) {
+  __shared__ float s_sum[256][8];
+  __shared__ float s_sq[256][8];
+  const int vecs = C >> 3;                      // vector positions per pixel
+  const int ppb = 256 / vecs;                   // pixels per CTA pass
+  const int v = threadIdx.x % vecs;
+  const int po = threadIdx.x / vecs;
+  const int n = blockIdx.y;
+  const __nv_bfloat16* xs = x + (long)n * P * ld;
+  float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, q[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (long p = (long)blockIdx.x * ppb + po; p < P; p += (long)GN_SPLITS * ppb) {
+    const uint4 u = *reinterpret_cast<const uint4*>(xs + p * ld + v * 8);
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    const float f[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      s[e] += f[e];
+      q[e] += f[e] * f[e];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    s_sum[threadIdx.x][e] = s[e];
+    s_sq[threadIdx.x][e] = q[e];
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    const int g = threadIdx.x;
+    const int cpg = C / G;
+    float ts = 0.f, tq = 0.f;
+    for (int c = g * cpg; c < (g + 1) * cpg; ++c) {          // channels of the group, then the pixel lanes, in order
+      const int vv = c >> 3, e = c & 7;
+      for (int lane = 0; lane < ppb; ++lane) {
+        ts += s_sum[lane * vecs + vv][e];
+        tq += s_sq[lane * vecs + vv][e];
+      }
+    }
+    float* out = partial + (((long)n * G + g) * GN_SPLITS + blockIdx.x) * 2;
+    out[0] = ts;
+    out[1] = tq;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+gn_apply_kernel(const __nv_bfloat16* __restrict__ x, long ldx, __nv_bfloat16* __restrict__ y, long ldy, long P, int C, int G,
+                const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ partial,
+                float eps, int apply_silu) {
+  __shared__ float s_mean[GN_MAX_GROUPS], s_rstd[GN_MAX_GROUPS];
+  const int n = blockIdx.y;
+  if (threadIdx.x < G) {
+    const float* pp = partial + ((long)n * G + threadIdx.x) * GN_SPLITS * 2;
+    float ts = 0.f, tq = 0.f;
+    for (int i = 0; i < GN_SPLITS; ++i) {
+      ts += pp[2 * i];
+      tq += pp[2 * i + 1];
+    }
+    const float cnt = (float)P * (float)(C / G);
+    const float mean = ts / cnt;
+    const float var = fmaxf(tq / cnt - mean * mean, 0.f);
+    s_mean[threadIdx.x] = mean;
+    s_rstd[threadIdx.x] = rsqrtf(var + eps);
+  }
+  __syncthreads();
+  const int vecs = C >> 3;
+  const int cpg = C / G;
+  const long total = P * vecs;
+  const __nv_bfloat16* xs = x + (long)n * P * ldx;
+  __nv_bfloat16* ys = y + (long)n * P * ldy;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long p = i / vecs;
+    const int c0 = (int)(i % vecs) * 8;
+    const uint4 u = *reinterpret_cast<const uint4*>(xs + p * ldx + c0);
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    float f[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int ch = c0 + e;
+      const int g = ch / cpg;
+      float vnorm = (f[e] - s_mean[g]) * s_rstd[g] * gamma[ch] + beta[ch];
+      if (apply_silu) vnorm = vnorm / (1.f + __expf(-vnorm));
+      f[e] = vnorm;
+    }
+    uint4 o;
+    o.x = pack_bf16(f[0], f[1]);
+    o.y = pack_bf16(f[2], f[3]);
+    o.z = pack_bf16(f[4], f[5]);
+    o.w = pack_bf16(f[6], f[7]);
+    *reinterpret_cast<uint4*>(ys + p * ldy + c0) = o;
+  }
+}
+
+}  // namespace omni
+
+// x, y: bf16 [N, P, C] with row pitches ldx / ldy (elements); gamma, beta: fp32 [C]; partial: fp32 scratch of
+// N * G * 128 * 2 floats (every element is written before it is read).
+extern "C" int omni_groupnorm_nhwc(const void* x, long ldx, void* y, long ldy, int N, long P, int C, int G, const float* gamma,
+                                   const float* beta, float eps, int apply_silu, float* partial, void* stream) {
+  if (N <= 0 || P <= 0) return omni::RC_OK;
+  if (C <= 0 || (C & 7) || G <= 0 || G > omni::GN_MAX_GROUPS || (C % G) || (256 % (C >> 3)) || (C >> 3) > 256 || (ldx & 7) ||
+      (ldy & 7) || partial == nullptr)
+    return omni::RC_BAD_ARG;
+  omni::gn_stats_kernel<<<dim3(omni::GN_SPLITS, N), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, P, C, G, partial);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  long blocks = (P * (C >> 3) + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  omni::gn_apply_kernel<<<dim3((unsigned)blocks, N), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)y, ldy, P, C, G, gamma, beta, partial, eps, apply_silu);
+  return (int)cudaGetLastError();
+}

@@ -15,6 +15,7 @@ the activation memory of large images and is what the patch-parallel wrapper dis
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -214,6 +215,8 @@ class AutoencoderKL(nn.Module):
         self.quant_conv = nn.Conv2d(2 * c.latent_channels, 2 * c.latent_channels, 1) if (c.use_quant_conv and with_encoder) else None
         self.use_tiling = False
         self.tile_latent, self.tile_overlap = 64, 16
+        self.decoder_impl = os.environ.get("OMNI_VAE_IMPL", "nhwc")      # "nhwc" (own kernels) | "torch" (cuDNN)
+        self._nhwc = None
         for p in self.parameters():
             p.requires_grad_(False)
 
@@ -238,6 +241,15 @@ class AutoencoderKL(nn.Module):
         z = z.to(self.dtype)
         if denormalize:
             z = self.denormalize(z)
+        tiled = self.use_tiling and max(z.shape[-2:]) > self.tile_latent
+        if z.is_cuda and self.dtype == torch.bfloat16 and not tiled and self.decoder_impl != "torch":
+            # channels-last decode on the implicit-GEMM / GroupNorm kernels of this library
+            if self._nhwc is None:
+                from .nhwc_decoder_kl import NHWCDecoderKL
+                self._nhwc = NHWCDecoderKL(self.decoder, self.post_quant_conv, torch.bfloat16) \
+                    if NHWCDecoderKL.supported(self.decoder) else False
+            if self._nhwc:
+                return self._nhwc(z.contiguous()).to(self.dtype)
         if self.post_quant_conv is not None:
             z = self.post_quant_conv(z)
         z = z.contiguous(memory_format=torch.channels_last)

@@ -332,3 +332,32 @@ def wide_head_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunk
             softmax_rows_(s, scale)
             linear(s, vt, out=out[b, r0:r0 + n])
     return out
+
+
+GN_SPLITS = 128          # partial sums per (sample, group) in the native kernel
+
+
+def groupnorm_nhwc(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, groups: int, eps: float = 1e-6,
+                   silu: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+    """GroupNorm over (pixels, channels of a group) per sample, then SiLU; x [N, H, W, C] channels-last (pitch >= C),
+    gamma / beta fp32 [C] (csrc/vae_ops.cu ``omni_groupnorm_nhwc``: per-group sums in a fixed order, then one
+    normalise-scale-shift-activate pass)."""
+    N, H, W, ld = x.shape
+    Cn = gamma.numel()
+    if not x.is_cuda:
+        xf = x[..., :Cn].float().permute(0, 3, 1, 2)
+        y = F.group_norm(xf, groups, gamma.float(), beta.float(), eps)
+        y = (F.silu(y) if silu else y).permute(0, 2, 3, 1).to(x.dtype)
+        if out is not None:
+            out[..., :Cn].copy_(y)
+            return out
+        return y.contiguous()
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and gamma.dtype == torch.float32 and beta.dtype == torch.float32
+    if out is None:
+        out = torch.empty(N, H, W, Cn, dtype=x.dtype, device=x.device)
+    partial = torch.empty(N * groups * GN_SPLITS * 2, dtype=torch.float32, device=x.device)
+    rc = nv.lib("vae_ops").omni_groupnorm_nhwc(nv.ptr(x), c_long(ld), nv.ptr(out), c_long(out.stride(2)), c_int(N), c_long(H * W),
+                                               c_int(Cn), c_int(groups), nv.ptr(gamma), nv.ptr(beta), ctypes.c_float(eps),
+                                               c_int(1 if silu else 0), nv.ptr(partial), nv.stream_ptr())
+    nv.check_rc(rc, "omni_groupnorm_nhwc")
+    return out
