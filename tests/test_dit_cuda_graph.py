@@ -20,7 +20,7 @@ def test_signature_and_cpu_passthrough():
     assert _sig((x,)) != _sig((torch.zeros(3),)) and _sig((x,)) != _sig((torch.ones(4),))
     with pytest.raises(TypeError):
         _sig(object())
-    assert torch.equal(g(x, object()) if False else g(x, 2), x * 2)
+    assert torch.equal(g(x, 2), x * 2)
 
 
 def _replay_vs_eager(monkeypatch, name, tf, prompt_len):

@@ -1,6 +1,5 @@
 """Qwen3-TTS 25 Hz speech tokenizer: Whisper features against the transformers extractor, windowed encoder
 attention against a per-window loop, nearest-code search, Euler flow decode, checkpoint names."""
-import numpy as np
 import pytest
 import torch
 import torch.nn.functional as F
