@@ -39,7 +39,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--text-len", type=int, default=256)
     ap.add_argument("--layers", type=int, default=60, help="60 = the 20B config; anything else is a smoke run")
-    ap.add_argument("--parallelism", default=None, help="e.g. sp8, cfg2xsp4, tp8 (default: sp{N})")
+    ap.add_argument("--parallelism", default=None, help="e.g. sp8, cfg2xsp4, tp8 (default: cfg2 at N=2, cfg2 x sp(N/2) above)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ref-eager", action="store_true", help="reference arm: skip its regional torch.compile")
     return ap.parse_args()
