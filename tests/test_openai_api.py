@@ -198,3 +198,45 @@ def test_real_tiny_omni_chat_with_an_audio_clip(tmp_path):
             assert extra > 28 + 1, extra      # 28 bytes of start / end marker text + the expanded placeholder
     finally:
         eng.close()
+
+
+def test_video_route_maps_the_request_and_returns_gif_or_frames():
+    """``/v1/videos``: fields reach the sampling parameters, a base64 first frame becomes the conditioning image,
+    the clip comes back as one GIF or as PNG frames."""
+    import numpy as np
+    from PIL import Image
+
+    class FakeVideoEngine:
+        stage_list = []
+
+        def __init__(self):
+            self.calls = []
+
+        async def generate(self, prompt, request_id=None, sampling_params_list=None, output_modalities=None):
+            sp = sampling_params_list[0]
+            self.calls.append((prompt, sp))
+            frames = np.zeros((sp.num_frames, sp.height, sp.width, 3), np.uint8)
+            frames[:, :, :, 1] = np.arange(sp.num_frames, dtype=np.uint8)[:, None, None] * 20
+            yield OmniRequestOutput.from_diffusion(request_id, [], prompt, multimodal_output={"video": frames},
+                                                   final_output_type="video")
+
+    eng = FakeVideoEngine()
+    with TestClient(build_app(eng, "fake-video", kind="diffusion")) as c:
+        png = io.BytesIO()
+        Image.new("RGB", (32, 16), (200, 10, 10)).save(png, format="PNG")
+        r = c.post("/v1/videos", json={"prompt": "a boat", "size": "32x16", "num_frames": 5, "fps": 8, "seed": 4,
+                                       "num_inference_steps": 3, "guidance_scale": 2.5, "negative_prompt": "blur",
+                                       "image": base64.b64encode(png.getvalue()).decode(), "response_format": "frames_b64"})
+        assert r.status_code == 200, r.text
+        clip = r.json()["data"][0]
+        assert len(clip["frames_b64"]) == 5 and clip["fps"] == 8 and clip["format"] == "png"
+        assert Image.open(io.BytesIO(base64.b64decode(clip["frames_b64"][2]))).size == (32, 16)
+        prompt, sp = eng.calls[0]
+        assert prompt["prompt"] == "a boat" and prompt["negative_prompt"] == "blur"
+        assert prompt["multi_modal_data"]["image"].size == (32, 16)
+        assert (sp.width, sp.height, sp.num_frames, sp.fps, sp.seed, sp.num_inference_steps, sp.guidance_scale) == \
+            (32, 16, 5, 8, 4, 3, 2.5)
+        r = c.post("/v1/videos", json={"prompt": "a boat", "size": "32x16", "num_frames": 3})
+        assert r.status_code == 200 and base64.b64decode(r.json()["data"][0]["b64_json"])[:3] == b"GIF"
+        assert c.post("/v1/videos", json={"prompt": "x", "size": "wide"}).status_code == 400
+        assert c.post("/v1/videos", json={"prompt": "x", "num_frames": 0}).status_code == 422
