@@ -188,3 +188,26 @@ def test_tensor_parallel_and_cfg_parallel_match_single_process():
     assert (a - b).abs().max().item() < 1e-4
     c = _run(DiffusionParallelConfig(cfg_parallel_size=2))
     assert (a - c).abs().max().item() < 1e-4
+
+
+@pytest.mark.gpu
+def test_tiny_pipeline_runs_on_a_gpu():
+    """The whole pipeline on the device kernels (two attention launches per layer against the kept prompt K/V, MoE
+    chain, token-layout convolutions, fold / unfold autoencoder): a finite image of the requested size."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from vllm_omni_b200.entrypoints.omni import Omni
+    from vllm_omni_b200.inputs import OmniDiffusionSamplingParams
+    tf = dict(vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+              intermediate_size=512, moe_intermediate_size=256, num_experts=8, moe_topk=2, num_shared_expert=1,
+              patch_embed_hidden_dim=128, latent_channels=32, vae_downsample=16, image_base_size=256,
+              vae=dict(block_out_channels=(32, 64, 64, 128, 128), layers_per_block=1, norm_num_groups=8))
+    o = Omni("HunyuanImage3Pipeline", dtype="bfloat16", device="cuda", tf_model_config=tf, diffusion_load_format="dummy",
+             output_type="pt")
+    try:
+        sp = OmniDiffusionSamplingParams(height=256, width=256, num_inference_steps=3, guidance_scale=5.0, seed=0, output_type="pt")
+        img = torch.as_tensor(o.generate([{"prompt": "a small red cube on a table"}], sp)[0].images[0]).float()
+        assert tuple(img.shape) == (3, 256, 256) and torch.isfinite(img).all()
+    finally:
+        o.close()
