@@ -123,3 +123,49 @@ def test_longcat_edit_appends_the_condition_image_as_a_second_frame():
             o.generate([{"prompt": "no image"}], sp)
     finally:
         o.close()
+
+
+F64 = dict(num_layers=1, num_single_layers=1, attention_head_dim=64, num_attention_heads=2, joint_attention_dim=64,
+           pooled_projection_dim=32, in_channels=64, out_channels=16, axes_dims_rope=(16, 24, 24))
+GPU_CASES = {
+    "WanPipeline": (dict(num_attention_heads=2, attention_head_dim=64, text_dim=64, ffn_dim=256, num_layers=1),
+                    dict(base_dim=32, num_res_blocks=1)),
+    "Flux2KleinPipeline": (dict(F64, out_channels=None, axes_dims_rope=(16, 16, 16, 16), timestep_guidance_channels=32), None),
+    "StableDiffusion3Pipeline": (dict(F64, num_single_layers=0), None),
+    "BagelPipeline": (dict(vocab_size=300, hidden_size=128, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1,
+                           intermediate_size=128, max_latent_size=16, z_channels=16, start_of_image=290, end_of_image=291,
+                           bos_token_id=288, eos_token_id=289), None),
+    "GlmImagePipeline": (dict(num_layers=1, attention_head_dim=64, num_attention_heads=2, time_embed_dim=64, condition_dim=32,
+                              prior_vq_quantizer_codebook_size=64, text_embed_dim=32, in_channels=16, out_channels=16), None),
+    "LongCatImagePipeline": (F64, None),
+    "OvisImagePipeline": (F64, None),
+    "StableAudioPipeline": (dict(num_attention_heads=2, attention_head_dim=64, num_key_value_attention_heads=1, in_channels=8,
+                                 out_channels=8, cross_attention_dim=32, cross_attention_input_dim=32, global_states_input_dim=64,
+                                 time_proj_dim=16, num_layers=1, sample_size=6),
+                            dict(decoder_channels=8, channel_multiples=(1, 2), downsampling_ratios=(2, 4), sampling_rate=800)),
+}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(GPU_CASES))
+def test_pipeline_runs_on_a_gpu(name):
+    """Kernel-friendly small geometries (head size 64) end to end on the device in bf16, VAE decode included (the
+    channels-last GroupNorm and causal 3-D decoders run inside the pipelines)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    tf, vae = GPU_CASES[name]
+    o = OmniDiffusion(name, dtype="bfloat16", device="cuda", tf_model_config=tf,
+                      vae_config=vae if vae is not None else dict(block_out_channels=(32, 32, 32, 32), layers_per_block=1, norm_num_groups=8))
+    try:
+        sp = OmniDiffusionSamplingParams(height=128, width=128, num_inference_steps=2, seed=0, num_frames=5, guidance_scale=3.0,
+                                         extra_args={"audio_seconds": 0.05})
+        out = o.generate([{"prompt": "a small test", "negative_prompt": " "}], sp)[0]
+        mm = out.multimodal_output or {}
+        if "video" in mm:
+            assert tuple(mm["video"].shape) == (5, 128, 128, 3)
+        elif "audio" in mm:
+            assert mm["audio"].shape[0] == 2 and torch.isfinite(torch.as_tensor(mm["audio"]).float()).all()
+        else:
+            assert out.images[0].size == (128, 128)
+    finally:
+        o.close()
